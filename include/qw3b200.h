@@ -1,0 +1,252 @@
+/* qw3b200 — C ABI of the B200 (sm_100a) MTP speculative-decode step for the qwen35 hybrid
+ * model (Q8_0 weights, paged fp16 KV, gated DeltaNet + gated full attention).
+ *
+ * This is the drop-in boundary: plain pointers and sizes, no C++ or torch types.  Every
+ * entry point names the reference interface it stands in for (path:line inside the
+ * kvmem-qw3 tree).  Functions return 0 on success and a non-zero code on failure;
+ * qb_last_error() returns the message of the last failure on the calling thread (the
+ * same lifetime rule as the reference's DeviceStatus::message,
+ * include/qw3/device_backend.hpp:24-27).  All device work is enqueued on the context's
+ * single stream in call order (the reference backend's exec stream,
+ * src/kernels_cuda.cu:9673-9695); nothing here falls back to the CPU.
+ */
+#ifndef QW3B200_H
+#define QW3B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QB_OK 0
+#define QB_ERR_INVALID 1
+#define QB_ERR_CUDA 2
+#define QB_ERR_UNSUPPORTED 3
+#define QB_ERR_CAPACITY 4
+
+typedef struct qb_ctx qb_ctx;
+typedef struct qb_weight qb_weight;
+typedef struct qb_model qb_model;
+typedef struct qb_batch qb_batch;
+
+/* Hyper-parameters of the qwen35 hybrid model; field meaning follows QwenConfig
+ * (include/qw3/qwen_config.hpp:15-68).  Layer i is full attention iff
+ * (i + 1) % full_attention_interval == 0. */
+typedef struct qb_model_config {
+    uint32_t n_layers;
+    uint32_t n_embd;
+    uint32_t n_ff;
+    uint32_t n_heads;
+    uint32_t n_kv_heads;
+    uint32_t head_dim;
+    uint32_t rope_dim;
+    float    rope_theta;
+    float    rms_eps;
+    uint32_t ssm_conv_kernel;      /* 4 */
+    uint32_t ssm_num_k_heads;      /* ssm_group_count */
+    uint32_t ssm_num_v_heads;      /* ssm_time_step_rank */
+    uint32_t ssm_head_dim;         /* ssm_state_size: head_k_dim == head_v_dim */
+    uint32_t full_attention_interval;
+    uint32_t vocab_size;
+    uint32_t mtp_layers;           /* 0 or 1 (nextn_predict_layers) */
+    float    weight_sigma;         /* std of the seeded random-init weights (0.02) */
+} qb_model_config;
+
+/* ---- context ---------------------------------------------------------------------- */
+
+/* make_cuda_device_backend (include/qw3/device_backend.hpp:2744) + the backend ctor's
+ * device/stream set-up (src/kernels_cuda.cu:9673-9695).  `device` is the CUDA ordinal. */
+int  qb_create(int device, qb_ctx **out);
+void qb_destroy(qb_ctx *ctx);
+const char *qb_last_error(void);
+/* DeviceBackend::synchronize / end (device_backend.hpp:93-95). */
+int  qb_synchronize(qb_ctx *ctx);
+/* Raw CUDA stream handle (cudaStream_t) of the context, for callers that time with events. */
+void *qb_stream(qb_ctx *ctx);
+int  qb_sm_count(qb_ctx *ctx);
+
+/* DeviceBackend::tensor_f32/f16/i32, scratch_f32 (device_backend.hpp:124-213) reduced to
+ * bytes; copy_to_host (:148), copy_i32_from_host (:2454), copy_d2d (:2514), zero_tensor. */
+int qb_malloc(qb_ctx *ctx, size_t bytes, void **dev_ptr);
+int qb_free(qb_ctx *ctx, void *dev_ptr);
+int qb_memcpy_h2d(qb_ctx *ctx, void *dev_dst, const void *host_src, size_t bytes);
+int qb_memcpy_d2h(qb_ctx *ctx, void *host_dst, const void *dev_src, size_t bytes);
+int qb_memcpy_d2d(qb_ctx *ctx, void *dev_dst, const void *dev_src, size_t bytes);
+int qb_memset(qb_ctx *ctx, void *dev_ptr, int value, size_t bytes);
+/* Pinned host buffers for end-to-end timing (cudaHostAlloc). */
+int qb_host_alloc(qb_ctx *ctx, size_t bytes, void **host_ptr);
+int qb_host_free(qb_ctx *ctx, void *host_ptr);
+
+/* CUDA-event timing on the context stream. */
+int qb_event_create(qb_ctx *ctx, void **event);
+int qb_event_record(qb_ctx *ctx, void *event);
+int qb_event_elapsed_ms(qb_ctx *ctx, void *start, void *stop, float *ms);
+int qb_event_destroy(qb_ctx *ctx, void *event);
+/* Writes `bytes` of a private buffer (larger than L2) so the next timed call starts cold. */
+int qb_flush_l2(qb_ctx *ctx);
+
+/* ---- Q8_0 weights ----------------------------------------------------------------- */
+
+/* DeviceBackend::weight_q8_0(data, rows, cols, label) (device_backend.hpp:215) and the
+ * CudaWeight Q8_0 ctor's repack (src/kernels_cuda.cu:1566-1594).  `host_blocks` is the GGUF
+ * layout: rows x (cols/32) blocks of 34 bytes [fp16 d | int8 q[32]].  The pointer is not
+ * retained.  cols must be a multiple of 128. */
+int qb_weight_q8_0(qb_ctx *ctx, const void *host_blocks, uint32_t rows, uint32_t cols, qb_weight **out);
+/* Seeded random-init weight generated on the device, byte-identical to uploading the
+ * blocks produced by qs_synth_q8_0_block (include/qw3b200_synth.h). */
+int qb_weight_q8_0_synth(qb_ctx *ctx, uint64_t seed, uint32_t tensor_id, uint32_t rows, uint32_t cols,
+                         float sigma, qb_weight **out);
+/* Inverse repack back to GGUF 34-byte blocks (test aid). */
+int qb_weight_q8_0_download(qb_ctx *ctx, const qb_weight *w, void *host_blocks);
+void qb_weight_free(qb_ctx *ctx, qb_weight *w);
+uint32_t qb_weight_rows(const qb_weight *w);
+uint32_t qb_weight_cols(const qb_weight *w);
+
+/* ---- activation quantisation ------------------------------------------------------ */
+
+/* quantize_q8_1_kernel (src/mmvq_q8.cu:83-112): out = M x (K/32) blocks of 36 bytes
+ * {half d, half sum, int8 q[32]}. */
+int qb_quantize_q8_1(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t K, uint32_t x_stride, void *out_dev);
+/* quantize_mmq_q8_1_kernel (src/mmvq_q8.cu:669-722): out = (K/128) x M blocks of 144 bytes
+ * {float d4[4], int8 q[128]}, block index sb * M + row. */
+int qb_quantize_q8_1_mmq(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t K, uint32_t x_stride, void *out_dev);
+/* The engine's own planar form of the same arithmetic as q8_1_mmq: q_dev = int8 [M][K],
+ * d_dev = float [K/32][M]. */
+int qb_quantize_act(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t K, uint32_t x_stride,
+                    int8_t *q_dev, float *d_dev);
+
+/* ---- Q8_0 x Q8 products ----------------------------------------------------------- */
+
+/* Number of K segments the engine uses for an [N x K] weight (a function of the shape only,
+ * never of M, so a row's result does not depend on how many rows share the launch). */
+uint32_t qb_ksplit_policy(uint32_t N, uint32_t K);
+
+/* Exact int32 block dots: out_dev = int32 [M][N][K/32], the integer part shared by
+ * mul_mat_vec_q8_0_kernel (src/mmvq_q8.cu:156-172) and the MMQ kernels (src/mmq_q8.cu:1738-1748). */
+int qb_q8_block_dots(qb_ctx *ctx, const qb_weight *w, const int8_t *q_dev, uint32_t M, int32_t *out_dev);
+
+/* DeviceBackend::q8_0_matmul / q8_0_matvec (device_backend.hpp:300-539):
+ * y[m][n] = sum_kb d_w[n][kb] * d_x[m][kb] * int32dot, fp32 in / fp32 out.
+ *   order = 0: engine order (K segments of qb_ksplit_policy or `ksplit` if non-zero; sequential
+ *              fma per 32-block inside a segment as in src/mmq_q8.cu:1738-1748; segments summed ascending)
+ *   impl  = 0: automatic, 1: CUDA-core dp4a streaming kernel, 2: tcgen05 INT8 tensor-core kernel.
+ * Both implementations produce identical bits. */
+int qb_q8_0_matmul(qb_ctx *ctx, const qb_weight *w, const float *x_dev, uint32_t M, uint32_t x_stride,
+                   float *y_dev, uint32_t y_stride, uint32_t ksplit, int impl);
+/* Same product from already-quantised activations, leaving the per-segment partial sums:
+ * part_dev = float [ksplit][M][N]. */
+int qb_q8_gemm_partials(qb_ctx *ctx, const qb_weight *w, const int8_t *q_dev, const float *d_dev, uint32_t M,
+                        float *part_dev, uint32_t ksplit, int impl);
+
+/* ---- element-wise / norm / rope / embedding --------------------------------------- */
+
+/* q8_get_rows_batch_kernel (src/kernels_cuda.cu:2075-2157): out[i][:] = dequant(row ids[i]). */
+int qb_q8_0_get_rows(qb_ctx *ctx, const qb_weight *w, const int32_t *ids_dev, uint32_t n, float *out_dev,
+                     uint32_t out_stride);
+/* rms_norm_batch (src/kernels_cuda.cu:1948-2010, :14781). */
+int qb_rms_norm(qb_ctx *ctx, const float *x_dev, const float *w_dev, uint32_t M, uint32_t n, uint32_t stride,
+                float eps, float *out_dev);
+/* rmsnorm_per_head_batch + rope_partial_batch_positions on q and k, then kv_append_batch_paged_device
+ * (src/kernels_cuda.cu:4622-4645, 4779-4799, 8921-8969) in one launch.  qkv_dev rows are
+ * [q: n_heads x (2*head_dim) | k: n_kv x head_dim | v: n_kv x head_dim]; q is normalised and rotated
+ * in place; k,v of row r go to physical slot page_table[seq][pos/page]*page + pos%page as fp16.
+ * inv_freq_dev = float [rope_dim/2]. */
+int qb_qk_norm_rope_append(qb_ctx *ctx, float *qkv_dev, uint32_t rows, uint32_t row_stride,
+                           const float *q_norm_w, const float *k_norm_w, const float *inv_freq_dev,
+                           uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t rope_dim, float eps,
+                           const int32_t *row_seq_dev, const int32_t *row_pos_dev,
+                           const int32_t *page_table_dev, uint32_t page_table_stride, uint32_t page_size,
+                           void *k_cache_dev, void *v_cache_dev);
+
+/* attention_decode_batch_paged_gated_device / ..._ragged_device (src/kernels_cuda.cu:20187-20358,
+ * device_backend.hpp:2204-2450): row r of sequence row_seq[r] attends keys [0, row_pos[r]] of that
+ * sequence's pages, scale 1/sqrt(head_dim), GQA, fp16 K/V, fp32 softmax, output x sigmoid(gate).
+ * out_dev = float [rows][n_heads*head_dim]. */
+int qb_attention_paged_gated(qb_ctx *ctx, const float *qkv_dev, uint32_t rows, uint32_t row_stride,
+                             uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                             const int32_t *row_seq_dev, const int32_t *row_pos_dev,
+                             const int32_t *page_table_dev, uint32_t page_table_stride, uint32_t page_size,
+                             const void *k_cache_dev, const void *v_cache_dev, uint32_t max_pos,
+                             float *out_dev);
+
+/* DeviceBackend::recurrent_batch with checkpoints (device_backend.hpp:665-933,
+ * src/kernels_cuda.cu:15053-15608): conv1d(4)+SiLU, L2-norm q/k, gated delta rule, RMSNorm x SiLU(z).
+ * proj_dev rows = [qkv (2*nk*hd + nv*hd) | z (nv*hd) | alpha (nv) | beta (nv)] with row stride
+ * proj_stride.  T rows of one sequence.  state slots: state_dev = float [n_slots][nv][hd][hd],
+ * conv_dev = float [n_slots][qkv_dim][3]; the state is read from slot `slot_in` and the state after
+ * row t is written to slot t if write_all != 0, else only the final state to slot 0.
+ * core_dev = float [T][nv*hd]. */
+int qb_deltanet_rows(qb_ctx *ctx, const float *proj_dev, uint32_t T, uint32_t proj_stride,
+                     const float *conv_w, const float *ssm_a, const float *dt_bias, const float *norm_w,
+                     uint32_t nk, uint32_t nv, uint32_t hd, float eps,
+                     float *state_dev, float *conv_dev, uint32_t n_slots, uint32_t slot_in, int write_all,
+                     float *core_dev);
+
+/* argmax_batch (src/kernels_cuda.cu:1765-1888, :20814): lowest index wins ties.  out_dev = int32 [M]. */
+int qb_argmax_rows(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t n, uint32_t stride, int32_t *out_dev);
+
+/* ---- model / sequences / the MTP step --------------------------------------------- */
+
+/* QwenWeights ctor (src/qwen_weights.cpp:170-208) with seeded random-init tensors instead of a
+ * GGUF file: every Q8_0 tensor ~ quantise(N(0, sigma^2)), norm gains 1, DeltaNet fp32 tensors from
+ * the same seed (recipe in qw3b200_synth.h and the engine source). */
+int  qb_model_create_synth(qb_ctx *ctx, const qb_model_config *cfg, uint64_t seed, qb_model **out);
+void qb_model_destroy(qb_ctx *ctx, qb_model *m);
+size_t qb_model_weight_bytes(const qb_model *m);
+
+/* Per-request executor state of `n_seqs` sequences (QwenExecutor state, src/qwen_executor.hpp:763-819
+ * KvPageTable; GlobalKvPagePool src/qwen_native_backend.cpp:1155-1265): paged fp16 K/V for the target
+ * and the MTP layer, DeltaNet/conv state slots, positions.  page_order: 0 = identity, 1 = reverse,
+ * 2 = seeded shuffle (the alloc modes of src/qwen_executor.cpp:1752-1774). */
+int  qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_ctx, uint32_t draft_k,
+                     uint32_t page_size, int page_order, qb_batch **out);
+void qb_batch_destroy(qb_ctx *ctx, qb_batch *b);
+
+/* forward_n_tokens prefill branch + prime_mtp_prefix (src/qwen_executor.cpp:6003-6836,
+ * 22543-22815): ingest `n` prompt tokens of sequence `seq` (chunked), leave next token = argmax of
+ * the last row. */
+int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n);
+
+/* forward_one_token + argmax (src/qwen_executor.cpp:5446-5816): one non-speculative greedy step
+ * for every sequence.  Emits one token per sequence. */
+int qb_decode_greedy_step(qb_ctx *ctx, qb_batch *b);
+
+/* forward_mtp_draft_chain_with_prefix_device (src/qwen_executor.cpp:6942-7023): k chained MTP-head
+ * forwards per sequence, argmax kept on the device. */
+int qb_mtp_draft(qb_ctx *ctx, qb_batch *b);
+/* Replace the drafts by forced ones before verification: draft i of a sequence becomes
+ * stream[pos + i] with probability `rate` (seeded per position) and a different token otherwise;
+ * stream_dev = int32 [n_seqs][stream_stride] holds that sequence's greedy continuation indexed by
+ * absolute position. */
+int qb_mtp_force_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *stream_dev, uint32_t stream_stride,
+                        float rate, uint64_t seed);
+/* forward_n_tokens verify branch (src/qwen_executor.cpp:6003-6836): (k+1)-row target forward per
+ * sequence with per-row DeltaNet/conv state checkpoints and per-row argmax. */
+int qb_mtp_verify(qb_ctx *ctx, qb_batch *b);
+/* Acceptance + commit (src/qwen_native_backend.cpp:15948-16154; restore_state_checkpoint
+ * src/qwen_executor.cpp:22304-22428; prime_mtp_prefix_from_last_batch_at :22543) on the device:
+ * longest draft prefix equal to the row argmaxes, emit accepted+1 tokens, select the state
+ * checkpoint, advance the position, rebuild the MTP-layer K/V of the committed positions. */
+int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b);
+/* draft + verify + accept_commit. */
+int qb_mtp_step(qb_ctx *ctx, qb_batch *b);
+
+/* Host view of what the last step emitted: n_out[seq] tokens in tokens[seq*(k+1) ...]. Performs
+ * the step's single device->host copy and a stream sync. */
+int qb_read_step_output(qb_ctx *ctx, qb_batch *b, int32_t *n_out_host, int32_t *tokens_host);
+/* Counters since creation: [steps, drafted, accepted, emitted] per batch. */
+int qb_batch_stats(qb_ctx *ctx, qb_batch *b, int64_t *out4);
+/* Position (committed tokens) of a sequence; reads a device counter (syncs). */
+int qb_seq_position(qb_ctx *ctx, qb_batch *b, uint32_t seq, int32_t *pos);
+/* Test aids: logits of the last verify/greedy/prefill rows (float [rows][vocab]) and hidden rows. */
+int qb_debug_last_logits(qb_ctx *ctx, qb_batch *b, float *host_out, uint32_t max_rows, uint32_t *rows_out);
+int qb_debug_set_keep_logits(qb_ctx *ctx, qb_batch *b, int keep);
+/* Number of kernels this library launched on the context since creation. */
+int64_t qb_launch_count(qb_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QW3B200_H */
