@@ -148,40 +148,45 @@ int qb_q8_0_get_rows(qb_ctx *ctx, const qb_weight *w, const int32_t *ids_dev, ui
 /* rms_norm_batch (src/kernels_cuda.cu:1948-2010, :14781). */
 int qb_rms_norm(qb_ctx *ctx, const float *x_dev, const float *w_dev, uint32_t M, uint32_t n, uint32_t stride,
                 float eps, float *out_dev);
-/* rmsnorm_per_head_batch + rope_partial_batch_positions on q and k, then kv_append_batch_paged_device
- * (src/kernels_cuda.cu:4622-4645, 4779-4799, 8921-8969) in one launch.  qkv_dev rows are
- * [q: n_heads x (2*head_dim) | k: n_kv x head_dim | v: n_kv x head_dim]; q is normalised and rotated
- * in place; k,v of row r go to physical slot page_table[seq][pos/page]*page + pos%page as fp16.
- * inv_freq_dev = float [rope_dim/2]. */
+/* Row grouping of the attention and DeltaNet entry points: sequence s owns rows
+ * [s*R, (s+1)*R) with R = rows / n_seqs, at consecutive positions seq_pos_dev[s] .. seq_pos_dev[s]+R-1
+ * (the (k+1) verify rows of a request, or one decode row).  seq_pos_dev is int32 [n_seqs] on the device. */
+
+/* rmsnorm_per_head_batch + rope_partial_batch on q and k, then kv_append_batch_paged_device
+ * (src/kernels_cuda.cu:4622-4645, 4697-4799, 8921-8969) in one launch.  qkv_dev rows are
+ * [q: n_heads x (2*head_dim, second half = output gate) | k: n_kv x head_dim | v: n_kv x head_dim]; q is
+ * normalised and rotated in place; k,v of a row at position pos go to physical slot
+ * page_table[seq][pos/page_size]*page_size + pos%page_size as fp16 (cache = [slot][n_kv][head_dim]).
+ * inv_freq_dev = float [rope_dim/2], theta^(-2i/rope_dim). */
 int qb_qk_norm_rope_append(qb_ctx *ctx, float *qkv_dev, uint32_t rows, uint32_t row_stride,
                            const float *q_norm_w, const float *k_norm_w, const float *inv_freq_dev,
                            uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t rope_dim, float eps,
-                           const int32_t *row_seq_dev, const int32_t *row_pos_dev,
+                           const int32_t *seq_pos_dev, uint32_t n_seqs,
                            const int32_t *page_table_dev, uint32_t page_table_stride, uint32_t page_size,
                            void *k_cache_dev, void *v_cache_dev);
 
 /* attention_decode_batch_paged_gated_device / ..._ragged_device (src/kernels_cuda.cu:20187-20358,
- * device_backend.hpp:2204-2450): row r of sequence row_seq[r] attends keys [0, row_pos[r]] of that
- * sequence's pages, scale 1/sqrt(head_dim), GQA, fp16 K/V, fp32 softmax, output x sigmoid(gate).
- * out_dev = float [rows][n_heads*head_dim]. */
+ * device_backend.hpp:2204-2450): a row at position pos attends keys [0, pos] of its sequence's pages,
+ * scale 1/sqrt(head_dim), GQA, fp16 K/V, fp32 softmax, output x sigmoid(gate).  max_pos is a host upper
+ * bound of every row position.  out_dev = float [rows][n_heads*head_dim]. */
 int qb_attention_paged_gated(qb_ctx *ctx, const float *qkv_dev, uint32_t rows, uint32_t row_stride,
                              uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
-                             const int32_t *row_seq_dev, const int32_t *row_pos_dev,
+                             const int32_t *seq_pos_dev, uint32_t n_seqs,
                              const int32_t *page_table_dev, uint32_t page_table_stride, uint32_t page_size,
                              const void *k_cache_dev, const void *v_cache_dev, uint32_t max_pos,
                              float *out_dev);
 
-/* DeviceBackend::recurrent_batch with checkpoints (device_backend.hpp:665-933,
- * src/kernels_cuda.cu:15053-15608): conv1d(4)+SiLU, L2-norm q/k, gated delta rule, RMSNorm x SiLU(z).
- * proj_dev rows = [qkv (2*nk*hd + nv*hd) | z (nv*hd) | alpha (nv) | beta (nv)] with row stride
- * proj_stride.  T rows of one sequence.  state slots: state_dev = float [n_slots][nv][hd][hd],
- * conv_dev = float [n_slots][qkv_dim][3]; the state is read from slot `slot_in` and the state after
- * row t is written to slot t if write_all != 0, else only the final state to slot 0.
- * core_dev = float [T][nv*hd]. */
-int qb_deltanet_rows(qb_ctx *ctx, const float *proj_dev, uint32_t T, uint32_t proj_stride,
+/* DeviceBackend::recurrent_batch / recurrent_batch_ragged with checkpoints (device_backend.hpp:665-933,
+ * src/kernels_cuda.cu:15053-15972): conv1d(4)+SiLU, L2-norm q/k, gated delta rule, RMSNorm x SiLU(z).
+ * proj_dev rows = [qkv (2*nk*hd + nv*hd) | z (nv*hd) | alpha (nv) | beta (nv)], row stride proj_stride,
+ * rows_per_seq rows per sequence.  State slots: state_dev = float [n_seqs][n_slots][nv][hd][hd],
+ * conv_dev = float [n_seqs][n_slots][qkv_dim][3].  Sequence s reads slot slot_in_dev[s]; with
+ * write_all != 0 the state after row t goes to slot t (rows_per_seq <= n_slots), else only the final
+ * state goes to slot 0.  core_dev = float [rows][nv*hd] (gated, normalised output). */
+int qb_deltanet_rows(qb_ctx *ctx, const float *proj_dev, uint32_t n_seqs, uint32_t rows_per_seq, uint32_t proj_stride,
                      const float *conv_w, const float *ssm_a, const float *dt_bias, const float *norm_w,
                      uint32_t nk, uint32_t nv, uint32_t hd, float eps,
-                     float *state_dev, float *conv_dev, uint32_t n_slots, uint32_t slot_in, int write_all,
+                     float *state_dev, float *conv_dev, uint32_t n_slots, const int32_t *slot_in_dev, int write_all,
                      float *core_dev);
 
 /* argmax_batch (src/kernels_cuda.cu:1765-1888, :20814): lowest index wins ties.  out_dev = int32 [M]. */

@@ -138,8 +138,7 @@ QS_HD uint32_t qs_rand_u32(uint64_t seed, uint32_t stream, uint64_t index) {
     return r.v[0];
 }
 
-#if !defined(__CUDA_ARCH__)
-/* Inverse normal CDF (Acklam's rational approximation + one Halley step on erfc). */
+/* Host only. Inverse normal CDF (Acklam's rational approximation + one Halley step on erfc). */
 static inline double qs_inv_normal_cdf(double p) {
     static const double a[6] = {-3.969683028665376e+01, 2.209460984245205e+02, -2.759285104469687e+02,
                                 1.383577518672690e+02, -3.066479806614716e+01, 2.506628277459239e+00};
@@ -174,6 +173,5 @@ static inline void qs_build_normal_table(float *table) {
         table[i] = (float)qs_inv_normal_cdf(((double)i + 0.5) / (double)QS_NORMAL_TABLE_SIZE);
     }
 }
-#endif
 
 #endif /* QW3B200_SYNTH_H */

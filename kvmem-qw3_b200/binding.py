@@ -1,0 +1,354 @@
+"""ctypes binding of libqw3b200.so — the C ABI declared in include/qw3b200.h.
+
+The library is CUDA-only: loading works anywhere, but creating a context without a B200 raises.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libqw3b200.so")
+_LIB = None
+
+u32, u64, i32, f32, vp, sz = C.c_uint32, C.c_uint64, C.c_int, C.c_float, C.c_void_p, C.c_size_t
+
+
+class ModelConfig(C.Structure):
+    """qb_model_config (include/qw3b200.h); field meaning follows the reference's QwenConfig."""
+    _fields_ = [
+        ("n_layers", u32), ("n_embd", u32), ("n_ff", u32), ("n_heads", u32), ("n_kv_heads", u32),
+        ("head_dim", u32), ("rope_dim", u32), ("rope_theta", f32), ("rms_eps", f32),
+        ("ssm_conv_kernel", u32), ("ssm_num_k_heads", u32), ("ssm_num_v_heads", u32),
+        ("ssm_head_dim", u32), ("full_attention_interval", u32), ("vocab_size", u32),
+        ("mtp_layers", u32), ("weight_sigma", f32),
+    ]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+# name -> (restype, argtypes); every symbol include/qw3b200.h declares
+SIGNATURES = {
+    "qb_create": (i32, [i32, C.POINTER(vp)]),
+    "qb_destroy": (None, [vp]),
+    "qb_last_error": (C.c_char_p, []),
+    "qb_synchronize": (i32, [vp]),
+    "qb_stream": (vp, [vp]),
+    "qb_sm_count": (i32, [vp]),
+    "qb_malloc": (i32, [vp, sz, C.POINTER(vp)]),
+    "qb_free": (i32, [vp, vp]),
+    "qb_memcpy_h2d": (i32, [vp, vp, vp, sz]),
+    "qb_memcpy_d2h": (i32, [vp, vp, vp, sz]),
+    "qb_memcpy_d2d": (i32, [vp, vp, vp, sz]),
+    "qb_memset": (i32, [vp, vp, i32, sz]),
+    "qb_host_alloc": (i32, [vp, sz, C.POINTER(vp)]),
+    "qb_host_free": (i32, [vp, vp]),
+    "qb_event_create": (i32, [vp, C.POINTER(vp)]),
+    "qb_event_record": (i32, [vp, vp]),
+    "qb_event_elapsed_ms": (i32, [vp, vp, vp, C.POINTER(f32)]),
+    "qb_event_destroy": (i32, [vp, vp]),
+    "qb_flush_l2": (i32, [vp]),
+    "qb_weight_q8_0": (i32, [vp, vp, u32, u32, C.POINTER(vp)]),
+    "qb_weight_q8_0_synth": (i32, [vp, u64, u32, u32, u32, f32, C.POINTER(vp)]),
+    "qb_weight_q8_0_download": (i32, [vp, vp, vp]),
+    "qb_weight_free": (None, [vp, vp]),
+    "qb_weight_rows": (u32, [vp]),
+    "qb_weight_cols": (u32, [vp]),
+    "qb_quantize_q8_1": (i32, [vp, vp, u32, u32, u32, vp]),
+    "qb_quantize_q8_1_mmq": (i32, [vp, vp, u32, u32, u32, vp]),
+    "qb_quantize_act": (i32, [vp, vp, u32, u32, u32, vp, vp]),
+    "qb_ksplit_policy": (u32, [u32, u32]),
+    "qb_q8_block_dots": (i32, [vp, vp, vp, u32, vp]),
+    "qb_q8_0_matmul": (i32, [vp, vp, vp, u32, u32, vp, u32, u32, i32]),
+    "qb_q8_gemm_partials": (i32, [vp, vp, vp, vp, u32, vp, u32, i32]),
+    "qb_q8_0_get_rows": (i32, [vp, vp, vp, u32, vp, u32]),
+    "qb_rms_norm": (i32, [vp, vp, vp, u32, u32, u32, f32, vp]),
+    "qb_qk_norm_rope_append": (i32, [vp, vp, u32, u32, vp, vp, vp, u32, u32, u32, u32, f32, vp, u32, vp, u32, u32, vp, vp]),
+    "qb_attention_paged_gated": (i32, [vp, vp, u32, u32, u32, u32, u32, vp, u32, vp, u32, u32, vp, vp, u32, vp]),
+    "qb_deltanet_rows": (i32, [vp, vp, u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, f32, vp, vp, u32, vp, i32, vp]),
+    "qb_argmax_rows": (i32, [vp, vp, u32, u32, u32, vp]),
+    "qb_model_create_synth": (i32, [vp, C.POINTER(ModelConfig), u64, C.POINTER(vp)]),
+    "qb_model_destroy": (None, [vp, vp]),
+    "qb_model_weight_bytes": (sz, [vp]),
+    "qb_batch_create": (i32, [vp, vp, u32, u32, u32, u32, i32, C.POINTER(vp)]),
+    "qb_batch_destroy": (None, [vp, vp]),
+    "qb_prefill": (i32, [vp, vp, u32, vp, u32]),
+    "qb_decode_greedy_step": (i32, [vp, vp]),
+    "qb_mtp_draft": (i32, [vp, vp]),
+    "qb_mtp_force_drafts": (i32, [vp, vp, vp, u32, f32, u64]),
+    "qb_mtp_verify": (i32, [vp, vp]),
+    "qb_mtp_accept_commit": (i32, [vp, vp]),
+    "qb_mtp_step": (i32, [vp, vp]),
+    "qb_read_step_output": (i32, [vp, vp, vp, vp]),
+    "qb_batch_stats": (i32, [vp, vp, vp]),
+    "qb_seq_position": (i32, [vp, vp, u32, C.POINTER(C.c_int32)]),
+    "qb_debug_last_logits": (i32, [vp, vp, vp, u32, C.POINTER(u32)]),
+    "qb_launch_count": (C.c_int64, [vp]),
+}
+
+
+class QbError(RuntimeError):
+    pass
+
+
+def lib():
+    """Loads the CUDA library; raises if it has not been built (there is no CPU fallback)."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise QbError("libqw3b200.so is missing: build it with kvmem-qw3_b200/build.py (no CPU fallback exists)")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _LIB = L
+    return _LIB
+
+
+def check(status):
+    if status != 0:
+        raise QbError("qw3b200 error %d: %s" % (status, lib().qb_last_error().decode()))
+
+
+def _np_ptr(a):
+    return a.ctypes.data_as(vp)
+
+
+class DeviceArray:
+    """Device buffer with numpy-shaped host transfer."""
+
+    def __init__(self, ctx, shape, dtype):
+        self.ctx, self.shape, self.dtype = ctx, tuple(np.atleast_1d(shape)), np.dtype(dtype)
+        self.nbytes = int(np.prod(self.shape)) * self.dtype.itemsize
+        p = vp()
+        check(lib().qb_malloc(ctx.h, max(self.nbytes, 16), C.byref(p)))
+        self.ptr = p
+
+    @classmethod
+    def from_host(cls, ctx, arr):
+        arr = np.ascontiguousarray(arr)
+        d = cls(ctx, arr.shape, arr.dtype)
+        d.upload(arr)
+        return d
+
+    def upload(self, arr):
+        arr = np.ascontiguousarray(arr, dtype=self.dtype)
+        assert arr.nbytes == self.nbytes
+        check(lib().qb_memcpy_h2d(self.ctx.h, self.ptr, _np_ptr(arr), self.nbytes))
+
+    def download(self):
+        out = np.empty(self.shape, self.dtype)
+        check(lib().qb_memcpy_d2h(self.ctx.h, _np_ptr(out), self.ptr, self.nbytes))
+        return out
+
+    def zero(self):
+        check(lib().qb_memset(self.ctx.h, self.ptr, 0, self.nbytes))
+
+    def free(self):
+        if self.ptr:
+            lib().qb_free(self.ctx.h, self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Context:
+    def __init__(self, device=0):
+        h = vp()
+        check(lib().qb_create(device, C.byref(h)))
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if self.h:
+            lib().qb_destroy(self.h)
+            self.h = None
+
+    def sync(self):
+        check(lib().qb_synchronize(self.h))
+
+    def flush_l2(self):
+        check(lib().qb_flush_l2(self.h))
+
+    @property
+    def sm_count(self):
+        return lib().qb_sm_count(self.h)
+
+    @property
+    def launches(self):
+        return int(lib().qb_launch_count(self.h))
+
+    def event(self):
+        e = vp()
+        check(lib().qb_event_create(self.h, C.byref(e)))
+        return e
+
+    def record(self, e):
+        check(lib().qb_event_record(self.h, e))
+
+    def elapsed_ms(self, a, b):
+        ms = f32()
+        check(lib().qb_event_elapsed_ms(self.h, a, b, C.byref(ms)))
+        return ms.value
+
+    def array(self, arr):
+        return DeviceArray.from_host(self, arr)
+
+    def empty(self, shape, dtype):
+        return DeviceArray(self, shape, dtype)
+
+
+class Weight:
+    """Q8_0 weight in device layout (DeviceWeight of the reference)."""
+
+    def __init__(self, ctx, h):
+        self.ctx, self.h = ctx, h
+
+    @classmethod
+    def from_blocks(cls, ctx, blocks, rows, cols):
+        blocks = np.ascontiguousarray(blocks, np.uint8)
+        assert blocks.size == rows * (cols // 32) * 34
+        h = vp()
+        check(lib().qb_weight_q8_0(ctx.h, _np_ptr(blocks), rows, cols, C.byref(h)))
+        return cls(ctx, h)
+
+    @classmethod
+    def synth(cls, ctx, seed, tensor_id, rows, cols, sigma=0.02):
+        h = vp()
+        check(lib().qb_weight_q8_0_synth(ctx.h, seed, tensor_id, rows, cols, sigma, C.byref(h)))
+        return cls(ctx, h)
+
+    @property
+    def rows(self):
+        return lib().qb_weight_rows(self.h)
+
+    @property
+    def cols(self):
+        return lib().qb_weight_cols(self.h)
+
+    def download(self):
+        out = np.empty(self.rows * (self.cols // 32) * 34, np.uint8)
+        check(lib().qb_weight_q8_0_download(self.ctx.h, self.h, _np_ptr(out)))
+        return out
+
+    def free(self):
+        if self.h:
+            lib().qb_weight_free(self.ctx.h, self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def act_ld(M):
+    return (M + 3) & ~3
+
+
+def quantize_act(ctx, x):
+    """x float32 [M][K] on host -> (q DeviceArray int8 [M][K], d DeviceArray float32 [K/32][ld])."""
+    x = np.ascontiguousarray(x, np.float32)
+    M, K = x.shape
+    xd = ctx.array(x)
+    q = ctx.empty((M, K), np.int8)
+    d = ctx.empty((K // 32, act_ld(M)), np.float32)
+    d.zero()
+    check(lib().qb_quantize_act(ctx.h, xd.ptr, M, K, K, q.ptr, d.ptr))
+    return q, d
+
+
+def matmul(ctx, w, x, ksplit=0, impl=0):
+    """DeviceBackend::q8_0_matmul: y[M][N] = W x, float32 host in / out."""
+    x = np.ascontiguousarray(x, np.float32)
+    M, K = x.shape
+    N = w.rows
+    xd = ctx.array(x)
+    yd = ctx.empty((M, N), np.float32)
+    check(lib().qb_q8_0_matmul(ctx.h, w.h, xd.ptr, M, K, yd.ptr, N, ksplit, impl))
+    return yd.download()
+
+
+class Model:
+    def __init__(self, ctx, cfg, seed):
+        self.ctx, self.cfg = ctx, cfg
+        h = vp()
+        check(lib().qb_model_create_synth(ctx.h, C.byref(cfg), seed, C.byref(h)))
+        self.h = h
+
+    @property
+    def weight_bytes(self):
+        return int(lib().qb_model_weight_bytes(self.h))
+
+    def close(self):
+        if self.h:
+            lib().qb_model_destroy(self.ctx.h, self.h)
+            self.h = None
+
+
+class Batch:
+    """Executor state of n_seqs requests (the QwenExecutor-side state of the reference)."""
+
+    def __init__(self, model, n_seqs, max_ctx, k, page_size=16, page_order=0):
+        self.ctx, self.model, self.n_seqs, self.k = model.ctx, model, n_seqs, k
+        h = vp()
+        check(lib().qb_batch_create(self.ctx.h, model.h, n_seqs, max_ctx, k, page_size, page_order, C.byref(h)))
+        self.h = h
+        self._n = np.zeros(n_seqs, np.int32)
+        self._t = np.zeros((n_seqs, k + 1), np.int32)
+
+    def close(self):
+        if self.h:
+            lib().qb_batch_destroy(self.ctx.h, self.h)
+            self.h = None
+
+    def prefill(self, seq, tokens):
+        t = np.ascontiguousarray(tokens, np.int32)
+        check(lib().qb_prefill(self.ctx.h, self.h, seq, _np_ptr(t), len(t)))
+
+    def greedy_step(self):
+        check(lib().qb_decode_greedy_step(self.ctx.h, self.h))
+
+    def mtp_draft(self):
+        check(lib().qb_mtp_draft(self.ctx.h, self.h))
+
+    def mtp_force_drafts(self, stream_dev, stride, rate, seed):
+        check(lib().qb_mtp_force_drafts(self.ctx.h, self.h, stream_dev.ptr, stride, rate, seed))
+
+    def mtp_verify(self):
+        check(lib().qb_mtp_verify(self.ctx.h, self.h))
+
+    def mtp_accept_commit(self):
+        check(lib().qb_mtp_accept_commit(self.ctx.h, self.h))
+
+    def mtp_step(self):
+        check(lib().qb_mtp_step(self.ctx.h, self.h))
+
+    def read_output(self):
+        """Returns a list (per sequence) of the tokens the last step emitted."""
+        check(lib().qb_read_step_output(self.ctx.h, self.h, _np_ptr(self._n), _np_ptr(self._t)))
+        return [self._t[s, :self._n[s]].tolist() for s in range(self.n_seqs)]
+
+    def stats(self):
+        out = np.zeros(4, np.int64)
+        check(lib().qb_batch_stats(self.ctx.h, self.h, _np_ptr(out)))
+        return dict(steps=int(out[0]), drafted=int(out[1]), accepted=int(out[2]), emitted=int(out[3]))
+
+    def position(self, seq):
+        p = C.c_int32()
+        check(lib().qb_seq_position(self.ctx.h, self.h, seq, C.byref(p)))
+        return p.value
+
+    def last_logits(self, max_rows):
+        V = self.model.cfg.vocab_size
+        buf = np.empty((max_rows, V), np.float32)
+        r = u32()
+        check(lib().qb_debug_last_logits(self.ctx.h, self.h, _np_ptr(buf), max_rows, C.byref(r)))
+        return buf[:r.value]

@@ -1,0 +1,785 @@
+// Host-side executor of the qwen35 MTP speculative-decode step.
+//
+// Mirrors the part of QwenExecutor / QwenNativeBackend that drives this path in the reference:
+//   forward_n_tokens                      src/qwen_executor.cpp:6003-6836  (prefill + verify rows)
+//   forward_one_token                     src/qwen_executor.cpp:5446-5816  (plain greedy step)
+//   forward_mtp_draft_chain_with_prefix_device / forward_mtp_draft_from   :6942-7255
+//   prime_mtp_prefix_from_last_batch_at   :22543-22815
+//   restore_state_checkpoint              :22304-22428
+//   the speculative loop and acceptance   src/qwen_native_backend.cpp:15770-16177
+// All per-step control values (positions, selected state slot, current token, drafts) live in
+// device memory and are updated by kernels, so a step needs no host decision and no mid-step
+// synchronisation; the host reads back one small record per step.
+#include "qb_internal.h"
+
+namespace {
+
+enum TensorKind : uint32_t {
+    T_ATTN_Q = 1, T_ATTN_K, T_ATTN_V, T_ATTN_OUT, T_FFN_GATE, T_FFN_UP, T_FFN_DOWN,
+    T_SSM_QKV, T_SSM_Z, T_SSM_ALPHA, T_SSM_BETA, T_SSM_OUT, T_SSM_CONV, T_SSM_A, T_SSM_DT,
+    T_EH_PROJ, T_TOKEN_EMBD, T_OUTPUT
+};
+inline uint32_t tensor_id(uint32_t layer, uint32_t kind) { return layer * 32u + kind; }
+inline double urand(uint64_t seed, uint32_t stream, uint64_t i) {
+    return (double)(qs_rand_u32(seed, stream, i) >> 8) / 16777216.0;
+}
+
+struct LayerW {
+    bool recurrent = false;
+    qb_weight *w_in = nullptr;       // attention: [q(+gate) ; k ; v]   DeltaNet: [qkv ; z ; alpha ; beta]
+    qb_weight *w_out = nullptr;      // attn_output / ssm_out
+    qb_weight *w_gate_up = nullptr;  // [gate ; up]
+    qb_weight *w_down = nullptr;
+    qb_weight w_kv;                  // view of the k and v rows of w_in (attention layers)
+    float *conv_w = nullptr, *ssm_a = nullptr, *dt_bias = nullptr;
+};
+
+}  // namespace
+
+struct qb_model {
+    qb_model_config cfg;
+    std::vector<LayerW> layers;      // n_layers (+ the MTP layer last)
+    qb_weight *token_embd = nullptr, *output = nullptr, *eh_proj = nullptr;
+    float *ones = nullptr;           // every RMSNorm gain of the seeded model is 1.0
+    float *inv_freq = nullptr;
+    size_t weight_bytes = 0;
+    uint32_t inner() const { return cfg.n_heads * cfg.head_dim; }
+    uint32_t kvd() const { return cfg.n_kv_heads * cfg.head_dim; }
+    uint32_t attn_in() const { return 2 * inner() + 2 * kvd(); }
+    uint32_t qkv_dim() const { return (2 * cfg.ssm_num_k_heads + cfg.ssm_num_v_heads) * cfg.ssm_head_dim; }
+    uint32_t vdim() const { return cfg.ssm_num_v_heads * cfg.ssm_head_dim; }
+    uint32_t dn_in() const { return qkv_dim() + vdim() + 2 * cfg.ssm_num_v_heads; }
+    bool is_attn(uint32_t i) const { return cfg.full_attention_interval && ((i + 1) % cfg.full_attention_interval) == 0; }
+};
+
+static size_t weight_bytes_of(const qb_weight *w) { return (size_t)w->rows * w->cols / 32 * 34; }
+
+static int upload_f32(qb_ctx *ctx, const std::vector<float> &v, float **out) {
+    QB_CUDA(cudaMalloc(out, v.size() * sizeof(float)));
+    QB_CUDA(cudaMemcpyAsync(*out, v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return QB_OK;
+}
+
+static int build_layer(qb_ctx *ctx, qb_model *m, LayerW &L, uint32_t il, bool recurrent, uint64_t seed) {
+    const qb_model_config &c = m->cfg;
+    const float sg = c.weight_sigma;
+    L.recurrent = recurrent;
+    if (!recurrent) {
+        const uint32_t inner = m->inner(), kvd = m->kvd();
+        QB_TRY(qb_weight_alloc(ctx, m->attn_in(), c.n_embd, &L.w_in));
+        QB_TRY(qb_weight_fill_synth(ctx, L.w_in, 0, 2 * inner, seed, tensor_id(il, T_ATTN_Q), sg));
+        QB_TRY(qb_weight_fill_synth(ctx, L.w_in, 2 * inner, kvd, seed, tensor_id(il, T_ATTN_K), sg));
+        QB_TRY(qb_weight_fill_synth(ctx, L.w_in, 2 * inner + kvd, kvd, seed, tensor_id(il, T_ATTN_V), sg));
+        QB_REQUIRE((2 * inner) % 128 == 0, "attention q rows %u not a multiple of 128", 2 * inner);
+        QB_TRY(qb_weight_view(ctx, L.w_in, 2 * inner, 2 * kvd, &L.w_kv));
+        QB_TRY(qb_weight_alloc(ctx, c.n_embd, inner, &L.w_out));
+        QB_TRY(qb_weight_fill_synth(ctx, L.w_out, 0, c.n_embd, seed, tensor_id(il, T_ATTN_OUT), sg));
+    } else {
+        const uint32_t C = m->qkv_dim(), vdim = m->vdim(), nv = c.ssm_num_v_heads;
+        QB_TRY(qb_weight_alloc(ctx, m->dn_in(), c.n_embd, &L.w_in));
+        QB_TRY(qb_weight_fill_synth(ctx, L.w_in, 0, C, seed, tensor_id(il, T_SSM_QKV), sg));
+        QB_TRY(qb_weight_fill_synth(ctx, L.w_in, C, vdim, seed, tensor_id(il, T_SSM_Z), sg));
+        QB_TRY(qb_weight_fill_synth(ctx, L.w_in, C + vdim, nv, seed, tensor_id(il, T_SSM_ALPHA), sg));
+        QB_TRY(qb_weight_fill_synth(ctx, L.w_in, C + vdim + nv, nv, seed, tensor_id(il, T_SSM_BETA), sg));
+        QB_TRY(qb_weight_alloc(ctx, c.n_embd, vdim, &L.w_out));
+        QB_TRY(qb_weight_fill_synth(ctx, L.w_out, 0, c.n_embd, seed, tensor_id(il, T_SSM_OUT), sg));
+        // fp32 DeltaNet tensors: ssm_a = -exp(U(0, log 16)), dt_bias ~ U(-4,-1), conv1d ~ U(-0.5,0.5)
+        std::vector<float> conv((size_t)C * c.ssm_conv_kernel), sa(nv), dt(nv);
+        for (size_t i = 0; i < conv.size(); ++i) conv[i] = (float)((urand(seed, tensor_id(il, T_SSM_CONV), i) * 2.0 - 1.0) * 0.5);
+        for (uint32_t v = 0; v < nv; ++v) {
+            sa[v] = (float)(-std::exp(urand(seed, tensor_id(il, T_SSM_A), v) * std::log(16.0)));
+            dt[v] = (float)(-4.0 + 3.0 * urand(seed, tensor_id(il, T_SSM_DT), v));
+        }
+        QB_TRY(upload_f32(ctx, conv, &L.conv_w));
+        QB_TRY(upload_f32(ctx, sa, &L.ssm_a));
+        QB_TRY(upload_f32(ctx, dt, &L.dt_bias));
+    }
+    QB_TRY(qb_weight_alloc(ctx, 2 * c.n_ff, c.n_embd, &L.w_gate_up));
+    QB_TRY(qb_weight_fill_synth(ctx, L.w_gate_up, 0, c.n_ff, seed, tensor_id(il, T_FFN_GATE), sg));
+    QB_TRY(qb_weight_fill_synth(ctx, L.w_gate_up, c.n_ff, c.n_ff, seed, tensor_id(il, T_FFN_UP), sg));
+    QB_TRY(qb_weight_alloc(ctx, c.n_embd, c.n_ff, &L.w_down));
+    QB_TRY(qb_weight_fill_synth(ctx, L.w_down, 0, c.n_embd, seed, tensor_id(il, T_FFN_DOWN), sg));
+    m->weight_bytes += weight_bytes_of(L.w_in) + weight_bytes_of(L.w_out) + weight_bytes_of(L.w_gate_up) + weight_bytes_of(L.w_down);
+    return QB_OK;
+}
+
+extern "C" int qb_model_create_synth(qb_ctx *ctx, const qb_model_config *cfg, uint64_t seed, qb_model **out) {
+    QB_REQUIRE(ctx && cfg && out, "qb_model_create_synth: null argument");
+    const qb_model_config &c = *cfg;
+    QB_REQUIRE(c.n_embd % 128 == 0 && c.n_ff % 128 == 0, "n_embd and n_ff must be multiples of 128");
+    QB_REQUIRE(c.head_dim == 64 || c.head_dim == 128 || c.head_dim == 256, "head_dim must be 64, 128 or 256");
+    QB_REQUIRE(c.ssm_head_dim == 64 || c.ssm_head_dim == 128, "ssm_head_dim must be 64 or 128");
+    QB_REQUIRE(c.ssm_conv_kernel == 4, "ssm_conv_kernel must be 4");
+    QB_REQUIRE(c.n_heads % c.n_kv_heads == 0 && c.n_heads / c.n_kv_heads <= 8, "GQA group must divide and be <= 8");
+    QB_REQUIRE((c.n_heads * c.head_dim) % 128 == 0 && (c.ssm_num_v_heads * c.ssm_head_dim) % 128 == 0, "inner dims must be multiples of 128");
+    QB_REQUIRE(c.mtp_layers <= 1, "at most one MTP layer");
+    QB_CUDA(cudaSetDevice(ctx->device));
+    qb_model *m = new qb_model();
+    m->cfg = c;
+    std::vector<float> ones(std::max({c.n_embd, c.head_dim, c.ssm_head_dim}), 1.0f);
+    QB_TRY(upload_f32(ctx, ones, &m->ones));
+    std::vector<float> invf(c.rope_dim / 2);
+    for (uint32_t i = 0; i < c.rope_dim / 2; ++i) invf[i] = (float)std::pow((double)c.rope_theta, -2.0 * (double)i / (double)c.rope_dim);
+    QB_TRY(upload_f32(ctx, invf, &m->inv_freq));
+    m->layers.resize(c.n_layers + (c.mtp_layers ? 1 : 0));
+    for (uint32_t il = 0; il < c.n_layers; ++il) QB_TRY(build_layer(ctx, m, m->layers[il], il, !m->is_attn(il), seed));
+    if (c.mtp_layers) {
+        QB_TRY(build_layer(ctx, m, m->layers[c.n_layers], c.n_layers, false, seed));
+        QB_TRY(qb_weight_q8_0_synth(ctx, seed, tensor_id(c.n_layers, T_EH_PROJ), c.n_embd, 2 * c.n_embd, c.weight_sigma, &m->eh_proj));
+        m->weight_bytes += weight_bytes_of(m->eh_proj);
+    }
+    QB_TRY(qb_weight_q8_0_synth(ctx, seed, tensor_id(0xFFFF, T_TOKEN_EMBD), c.vocab_size, c.n_embd, c.weight_sigma, &m->token_embd));
+    QB_TRY(qb_weight_q8_0_synth(ctx, seed, tensor_id(0xFFFF, T_OUTPUT), c.vocab_size, c.n_embd, c.weight_sigma, &m->output));
+    m->weight_bytes += weight_bytes_of(m->token_embd) + weight_bytes_of(m->output);
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    *out = m;
+    return QB_OK;
+}
+
+extern "C" void qb_model_destroy(qb_ctx *ctx, qb_model *m) {
+    if (!m) return;
+    cudaStreamSynchronize(ctx->stream);
+    for (LayerW &L : m->layers) {
+        qb_weight_free(ctx, L.w_in); qb_weight_free(ctx, L.w_out); qb_weight_free(ctx, L.w_gate_up); qb_weight_free(ctx, L.w_down);
+        if (L.conv_w) cudaFree(L.conv_w);
+        if (L.ssm_a) cudaFree(L.ssm_a);
+        if (L.dt_bias) cudaFree(L.dt_bias);
+    }
+    qb_weight_free(ctx, m->token_embd); qb_weight_free(ctx, m->output); qb_weight_free(ctx, m->eh_proj);
+    cudaFree(m->ones); cudaFree(m->inv_freq);
+    delete m;
+}
+extern "C" size_t qb_model_weight_bytes(const qb_model *m) { return m->weight_bytes; }
+
+// ================================================================================================
+// sequences
+// ================================================================================================
+struct QBuf {   // quantised activation buffer for one K
+    int8_t *q = nullptr; float *d = nullptr; uint32_t K = 0;
+};
+
+struct qb_batch {
+    qb_model *m = nullptr;
+    uint32_t n_seqs = 0, max_ctx = 0, k = 0, page_size = 0, pages_per_seq = 0, rows_cap = 0, chunk = 0, logit_rows = 0;
+    std::vector<__half *> kc, vc;          // per layer (attention layers only), + MTP layer at index n_layers
+    std::vector<float *> state, conv;      // per layer (recurrent layers only): [n_seqs][k+1][...]
+    int32_t *page_table = nullptr;         // [n_seqs][pages_per_seq]
+    // device control block (all int32)
+    int32_t *ctl = nullptr;
+    int32_t *pos = nullptr, *sel = nullptr, *cur = nullptr, *drafts = nullptr, *zero_sel = nullptr;
+    int32_t *tok_buf = nullptr, *seqpos_buf = nullptr, *prefix_pos = nullptr, *prefix_tok = nullptr;
+    int32_t *out_rec = nullptr;            // [n_out (n_seqs) | tokens (n_seqs*(k+1)) | pos (n_seqs)]
+    int32_t *map_prevh = nullptr, *map_prefix = nullptr, *map_chunk = nullptr, *map_last = nullptr;
+    long long *stats = nullptr;            // steps, drafted, accepted, emitted
+    int32_t *out_rec_host = nullptr;       // pinned mirror of out_rec
+    // activations
+    float *hid = nullptr;                  // [rows_cap + n_seqs][H]; rows rows_cap+s hold prev hidden of seq s
+    float *mtp_h = nullptr, *embd = nullptr, *act = nullptr, *xconv = nullptr, *core = nullptr, *parts = nullptr;
+    float *logits = nullptr, *am_val = nullptr, *att_acc = nullptr, *att_ml = nullptr;
+    int32_t *am_idx = nullptr;
+    QBuf xq_h, xq_attn, xq_dn, xq_ffn, xq_cat;
+    size_t parts_floats = 0;
+    std::vector<int32_t> host_pos;         // upper bound of pos per sequence
+    uint32_t last_logit_rows = 0;
+    int gemm_impl = 0;
+};
+
+static int alloc_qbuf(QBuf &b, uint32_t rows, uint32_t K) {
+    b.K = K;
+    QB_CUDA(cudaMalloc(&b.q, (size_t)rows * K));
+    QB_CUDA(cudaMalloc(&b.d, (size_t)(K / 32) * qb_act_ld(rows) * sizeof(float)));
+    return QB_OK;
+}
+
+static uint32_t env_u32(const char *name, uint32_t dflt) {
+    const char *v = getenv(name);
+    return (v && *v) ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
+}
+
+extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_ctx, uint32_t draft_k,
+                               uint32_t page_size, int page_order, qb_batch **out) {
+    QB_REQUIRE(ctx && m && out && n_seqs > 0 && max_ctx > 0 && page_size > 0, "qb_batch_create: bad arguments");
+    QB_REQUIRE(draft_k <= 7, "draft depth %u unsupported (<= 7)", draft_k);
+    QB_REQUIRE(draft_k == 0 || m->cfg.mtp_layers == 1, "draft depth > 0 needs the MTP layer");
+    QB_CUDA(cudaSetDevice(ctx->device));
+    const qb_model_config &c = m->cfg;
+    qb_batch *b = new qb_batch();
+    b->m = m; b->n_seqs = n_seqs; b->max_ctx = max_ctx; b->k = draft_k; b->page_size = page_size;
+    b->pages_per_seq = (max_ctx + draft_k + 1 + page_size - 1) / page_size;
+    b->chunk = std::max(1u, env_u32("QW3B200_PREFILL_CHUNK", 64));
+    b->logit_rows = n_seqs * (draft_k + 1);
+    b->rows_cap = std::max(b->chunk, b->logit_rows);
+    b->gemm_impl = (int)env_u32("QW3B200_GEMM_IMPL", 0);
+    const uint32_t H = c.n_embd, K1 = draft_k + 1, L = c.n_layers, rows = b->rows_cap;
+    const size_t slots = (size_t)n_seqs * b->pages_per_seq * page_size;
+    const uint32_t kvd = m->kvd();
+    b->kc.assign(L + 1, nullptr); b->vc.assign(L + 1, nullptr); b->state.assign(L, nullptr); b->conv.assign(L, nullptr);
+    for (uint32_t il = 0; il <= L; ++il) {
+        const bool attn = il == L ? c.mtp_layers == 1 : m->is_attn(il);
+        if (attn) {
+            QB_CUDA(cudaMalloc(&b->kc[il], slots * kvd * sizeof(__half)));
+            QB_CUDA(cudaMalloc(&b->vc[il], slots * kvd * sizeof(__half)));
+            QB_CUDA(cudaMemsetAsync(b->kc[il], 0, slots * kvd * sizeof(__half), ctx->stream));
+            QB_CUDA(cudaMemsetAsync(b->vc[il], 0, slots * kvd * sizeof(__half), ctx->stream));
+        } else if (il < L) {
+            const size_t ssz = (size_t)n_seqs * K1 * c.ssm_num_v_heads * c.ssm_head_dim * c.ssm_head_dim;
+            const size_t csz = (size_t)n_seqs * K1 * m->qkv_dim() * 3;
+            QB_CUDA(cudaMalloc(&b->state[il], ssz * sizeof(float)));
+            QB_CUDA(cudaMalloc(&b->conv[il], csz * sizeof(float)));
+            QB_CUDA(cudaMemsetAsync(b->state[il], 0, ssz * sizeof(float), ctx->stream));
+            QB_CUDA(cudaMemsetAsync(b->conv[il], 0, csz * sizeof(float), ctx->stream));
+        }
+    }
+    // page table: identity / reverse / seeded shuffle over the whole pool
+    {
+        const size_t total = (size_t)n_seqs * b->pages_per_seq;
+        std::vector<int32_t> pt(total);
+        for (size_t i = 0; i < total; ++i) pt[i] = (int32_t)i;
+        if (page_order == 1) std::reverse(pt.begin(), pt.end());
+        if (page_order == 2)
+            for (size_t i = total - 1; i > 0; --i) std::swap(pt[i], pt[qs_rand_u32(0x9a6e5, 7, i) % (i + 1)]);
+        QB_CUDA(cudaMalloc(&b->page_table, total * sizeof(int32_t)));
+        QB_CUDA(cudaMemcpyAsync(b->page_table, pt.data(), total * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    }
+    // control block
+    {
+        const size_t n = (size_t)n_seqs * (8 + 3 * K1) + 3 * rows + n_seqs * (size_t)std::max(1u, draft_k) * 2 + 64;
+        QB_CUDA(cudaMalloc(&b->ctl, n * sizeof(int32_t)));
+        QB_CUDA(cudaMemsetAsync(b->ctl, 0, n * sizeof(int32_t), ctx->stream));
+        int32_t *p = b->ctl;
+        auto take = [&](size_t cnt) { int32_t *r = p; p += cnt; return r; };
+        b->pos = take(n_seqs); b->sel = take(n_seqs); b->cur = take(n_seqs); b->zero_sel = take(n_seqs);
+        b->drafts = take((size_t)n_seqs * std::max(1u, draft_k));
+        b->tok_buf = take(rows); b->seqpos_buf = take(n_seqs); b->prefix_pos = take(n_seqs);
+        b->prefix_tok = take((size_t)n_seqs * std::max(1u, draft_k));
+        b->out_rec = take((size_t)n_seqs * (K1 + 2));
+        b->map_prevh = take(n_seqs); b->map_prefix = take((size_t)n_seqs * K1); b->map_chunk = take(rows); b->map_last = take(n_seqs);
+        std::vector<int32_t> prevh(n_seqs), mp((size_t)n_seqs * std::max(1u, draft_k));
+        for (uint32_t s = 0; s < n_seqs; ++s) prevh[s] = (int32_t)(rows + s);
+        for (uint32_t s = 0; s < n_seqs; ++s)
+            for (uint32_t i = 0; i < draft_k; ++i) mp[(size_t)s * draft_k + i] = (int32_t)(s * K1 + i);
+        QB_CUDA(cudaMemcpyAsync(b->map_prevh, prevh.data(), n_seqs * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        if (draft_k)
+            QB_CUDA(cudaMemcpyAsync(b->map_prefix, mp.data(), mp.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        QB_CUDA(cudaStreamSynchronize(ctx->stream));
+        QB_CUDA(cudaMalloc(&b->stats, 4 * sizeof(long long)));
+        QB_CUDA(cudaMemsetAsync(b->stats, 0, 4 * sizeof(long long), ctx->stream));
+        QB_CUDA(cudaHostAlloc(&b->out_rec_host, (size_t)n_seqs * (K1 + 2) * sizeof(int32_t), cudaHostAllocDefault));
+    }
+    // activations
+    const uint32_t inner = m->inner(), vdim = m->vdim(), F = c.n_ff, V = c.vocab_size;
+    const uint32_t act_cols = std::max({m->attn_in(), m->dn_in(), 2 * F});
+    QB_CUDA(cudaMalloc(&b->hid, (size_t)(rows + n_seqs) * H * sizeof(float)));
+    QB_CUDA(cudaMemsetAsync(b->hid, 0, (size_t)(rows + n_seqs) * H * sizeof(float), ctx->stream));
+    QB_CUDA(cudaMalloc(&b->mtp_h, (size_t)rows * H * sizeof(float)));
+    QB_CUDA(cudaMalloc(&b->embd, (size_t)rows * H * sizeof(float)));
+    QB_CUDA(cudaMalloc(&b->act, (size_t)rows * act_cols * sizeof(float)));
+    QB_CUDA(cudaMalloc(&b->xconv, (size_t)rows * m->qkv_dim() * sizeof(float)));
+    QB_CUDA(cudaMalloc(&b->core, (size_t)rows * vdim * sizeof(float)));
+    QB_CUDA(cudaMalloc(&b->logits, (size_t)b->logit_rows * V * sizeof(float)));
+    QB_CUDA(cudaMalloc(&b->am_val, (size_t)b->logit_rows * QB_ARGMAX_BLOCKS * sizeof(float)));
+    QB_CUDA(cudaMalloc(&b->am_idx, (size_t)b->logit_rows * QB_ARGMAX_BLOCKS * sizeof(int32_t)));
+    {
+        size_t per_row = 0;   // floats of split partials any GEMM of the model can need per row
+        auto consider = [&](uint32_t N, uint32_t K) { const uint32_t S = qb_ksplit(N, K); if (S > 1) per_row = std::max(per_row, (size_t)S * N); };
+        consider(m->attn_in(), H); consider(m->dn_in(), H); consider(H, inner); consider(H, vdim);
+        consider(2 * F, H); consider(H, F); consider(V, H); consider(H, 2 * H);
+        b->parts_floats = std::max<size_t>(per_row, 1) * rows;
+        QB_CUDA(cudaMalloc(&b->parts, b->parts_floats * sizeof(float)));
+    }
+    {
+        size_t ml = 0;
+        const size_t acc = qb_attention_scratch_floats(rows, c.n_heads, c.head_dim, max_ctx + draft_k + 1, &ml);
+        QB_CUDA(cudaMalloc(&b->att_acc, acc * sizeof(float)));
+        QB_CUDA(cudaMalloc(&b->att_ml, ml * sizeof(float)));
+    }
+    QB_TRY(alloc_qbuf(b->xq_h, rows, H));
+    QB_TRY(alloc_qbuf(b->xq_attn, rows, inner));
+    QB_TRY(alloc_qbuf(b->xq_dn, rows, vdim));
+    QB_TRY(alloc_qbuf(b->xq_ffn, rows, F));
+    QB_TRY(alloc_qbuf(b->xq_cat, rows, 2 * H));
+    b->host_pos.assign(n_seqs, 0);
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    *out = b;
+    return QB_OK;
+}
+
+extern "C" void qb_batch_destroy(qb_ctx *ctx, qb_batch *b) {
+    if (!b) return;
+    cudaStreamSynchronize(ctx->stream);
+    for (auto p : b->kc) if (p) cudaFree(p);
+    for (auto p : b->vc) if (p) cudaFree(p);
+    for (auto p : b->state) if (p) cudaFree(p);
+    for (auto p : b->conv) if (p) cudaFree(p);
+    void *ptrs[] = {b->page_table, b->ctl, b->stats, b->hid, b->mtp_h, b->embd, b->act, b->xconv, b->core, b->parts,
+                    b->logits, b->am_val, b->am_idx, b->att_acc, b->att_ml, b->xq_h.q, b->xq_h.d, b->xq_attn.q,
+                    b->xq_attn.d, b->xq_dn.q, b->xq_dn.d, b->xq_ffn.q, b->xq_ffn.d, b->xq_cat.q, b->xq_cat.d};
+    for (void *p : ptrs) if (p) cudaFree(p);
+    if (b->out_rec_host) cudaFreeHost(b->out_rec_host);
+    delete b;
+}
+
+// ================================================================================================
+// small control kernels
+// ================================================================================================
+namespace {
+
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+__device__ int final_argmax(const float *pval, const int32_t *pidx, uint32_t row) {
+    float bv = pval[(size_t)row * QB_ARGMAX_BLOCKS];
+    int bi = pidx[(size_t)row * QB_ARGMAX_BLOCKS];
+    for (uint32_t j = 1; j < QB_ARGMAX_BLOCKS; ++j) {
+        const float v = pval[(size_t)row * QB_ARGMAX_BLOCKS + j];
+        const int i = pidx[(size_t)row * QB_ARGMAX_BLOCKS + j];
+        if (better(v, i, bv, bi)) { bv = v; bi = i; }
+    }
+    return bi;
+}
+
+// tokens / positions of draft step i: token = i ? drafts[s][i-1] : cur[s], position = pos[s] + i
+__global__ void prep_draft_kernel(const int32_t *cur, const int32_t *drafts, const int32_t *pos, uint32_t n_seqs, uint32_t k,
+                                  uint32_t i, int32_t *tok, int32_t *seqpos) {
+    const uint32_t s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n_seqs) return;
+    tok[s] = i == 0 ? cur[s] : drafts[(size_t)s * k + i - 1];
+    seqpos[s] = pos[s] + (int)i;
+}
+
+__global__ void store_draft_kernel(const float *pval, const int32_t *pidx, uint32_t n_seqs, uint32_t k, uint32_t i, int32_t *drafts) {
+    const uint32_t s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n_seqs) return;
+    drafts[(size_t)s * k + i] = final_argmax(pval, pidx, s);
+}
+
+__global__ void prep_verify_kernel(const int32_t *cur, const int32_t *drafts, uint32_t n_seqs, uint32_t k, int32_t *tok) {
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_seqs * (k + 1)) return;
+    const uint32_t s = idx / (k + 1), j = idx % (k + 1);
+    tok[idx] = j == 0 ? cur[s] : drafts[(size_t)s * k + j - 1];
+}
+
+// Forced drafts: draft i of sequence s guesses the token at absolute position pos+1+i.
+__global__ void force_drafts_kernel(int32_t *drafts, const int32_t *pos, uint32_t n_seqs, uint32_t k, const int32_t *stream,
+                                    uint32_t stream_stride, float rate, uint64_t seed, uint32_t vocab) {
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_seqs * k) return;
+    const uint32_t s = idx / k, i = idx % k;
+    const uint32_t p = (uint32_t)pos[s] + 1 + i;
+    const int32_t truth = p < stream_stride ? stream[(size_t)s * stream_stride + p] : 0;
+    const float u = (float)(qs_rand_u32(seed, 0xD4AF7u + s, p) >> 8) * (1.0f / 16777216.0f);
+    drafts[idx] = u < rate ? truth : (int32_t)(((uint32_t)truth + 1u) % vocab);
+}
+
+// Greedy acceptance + commit, one CTA per sequence (src/qwen_native_backend.cpp:15948-16154,
+// src/qwen_executor.cpp:22304-22428): accepted = longest prefix with argmax(row i) == draft i+1;
+// emit the accepted drafts and argmax(row accepted); select checkpoint slot `accepted`; advance the
+// position; keep the hidden row `accepted` as the next step's MTP input.
+__global__ void accept_commit_kernel(const float *pval, const int32_t *pidx, uint32_t k, uint32_t rows_cap, uint32_t H,
+                                     int32_t *pos, int32_t *sel, int32_t *cur, const int32_t *drafts, int32_t *prefix_pos,
+                                     int32_t *prefix_tok, int32_t *out_rec, uint32_t n_seqs, float *hid,
+                                     unsigned long long *stats) {
+    __shared__ int s_acc;
+    const uint32_t s = blockIdx.x;
+    const uint32_t K1 = k + 1;
+    if (threadIdx.x == 0) {
+        int am[8];
+        for (uint32_t r = 0; r < K1; ++r) am[r] = final_argmax(pval, pidx, s * K1 + r);
+        uint32_t a = 0;
+        while (a < k && am[a] == drafts[(size_t)s * k + a]) ++a;
+        int32_t *n_out = out_rec, *toks = out_rec + n_seqs, *opos = out_rec + n_seqs + (size_t)n_seqs * K1;
+        for (uint32_t i = 0; i < a; ++i) toks[(size_t)s * K1 + i] = drafts[(size_t)s * k + i];
+        toks[(size_t)s * K1 + a] = am[a];
+        n_out[s] = (int)a + 1;
+        const int old = pos[s];
+        prefix_pos[s] = old + 1;
+        for (uint32_t i = 0; i < k; ++i) prefix_tok[(size_t)s * k + i] = drafts[(size_t)s * k + i];
+        pos[s] = old + (int)a + 1;
+        opos[s] = pos[s];
+        sel[s] = (int)a;
+        cur[s] = am[a];
+        s_acc = (int)a;
+        atomicAdd(&stats[0], 1ull);
+        atomicAdd(&stats[1], (unsigned long long)k);
+        atomicAdd(&stats[2], (unsigned long long)a);
+        atomicAdd(&stats[3], (unsigned long long)(a + 1));
+    }
+    __syncthreads();
+    const uint32_t a = (uint32_t)s_acc;
+    const float *src = hid + (size_t)(s * K1 + a) * H;
+    float *dst = hid + (size_t)(rows_cap + s) * H;
+    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+}
+
+// Greedy step / end of prefill: next token = argmax of the row; position advances by `adv`.
+__global__ void greedy_commit_kernel(const float *pval, const int32_t *pidx, uint32_t logit_row0, uint32_t hid_row0,
+                                     uint32_t hid_row_stride, uint32_t seq0, uint32_t n, uint32_t K1, uint32_t rows_cap, uint32_t H,
+                                     int32_t *pos, int32_t *sel, int32_t *cur, int32_t adv, int32_t *out_rec, uint32_t n_seqs,
+                                     float *hid, unsigned long long *stats) {
+    const uint32_t j = blockIdx.x, s = seq0 + j;
+    if (j >= n) return;
+    if (threadIdx.x == 0) {
+        const int tok = final_argmax(pval, pidx, logit_row0 + j);
+        int32_t *n_out = out_rec, *toks = out_rec + n_seqs, *opos = out_rec + n_seqs + (size_t)n_seqs * K1;
+        toks[(size_t)s * K1] = tok;
+        n_out[s] = 1;
+        pos[s] += adv;
+        opos[s] = pos[s];
+        sel[s] = 0;
+        cur[s] = tok;
+        atomicAdd(&stats[3], 1ull);
+    }
+    const float *src = hid + (size_t)(hid_row0 + j * hid_row_stride) * H;
+    float *dst = hid + (size_t)(rows_cap + s) * H;
+    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void advance_kernel(int32_t *pos, int32_t *sel, uint32_t s, int32_t adv, uint32_t rows_cap, uint32_t H, uint32_t last_row, float *hid) {
+    if (threadIdx.x == 0) { pos[s] += adv; sel[s] = 0; }
+    const float *src = hid + (size_t)last_row * H;
+    float *dst = hid + (size_t)(rows_cap + s) * H;
+    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+}
+
+}  // namespace
+
+// ================================================================================================
+// forward passes
+// ================================================================================================
+
+// y[rows][N] = W x, written to dst (row stride N).
+static int gemm_to(qb_ctx *ctx, qb_batch *b, const qb_weight *w, const QBuf &x, uint32_t rows, float *dst, uint32_t S_override = 0) {
+    const uint32_t S = S_override ? S_override : qb_ksplit(w->rows, w->cols);
+    if (S == 1) return qb_launch_gemm(ctx, w, x.q, x.d, rows, dst, 1, b->gemm_impl);
+    QB_REQUIRE((size_t)S * rows * w->rows <= b->parts_floats, "split scratch too small");
+    QB_TRY(qb_launch_gemm(ctx, w, x.q, x.d, rows, b->parts, S, b->gemm_impl));
+    return qb_launch_reduce_parts(ctx, b->parts, S, rows, w->rows, dst, w->rows);
+}
+
+// parts = split partials of W x (left in b->parts); returns S.
+static int gemm_parts(qb_ctx *ctx, qb_batch *b, const qb_weight *w, const QBuf &x, uint32_t rows, uint32_t *S_out) {
+    const uint32_t S = qb_ksplit(w->rows, w->cols);
+    QB_REQUIRE((size_t)S * rows * w->rows <= b->parts_floats || S == 1, "split scratch too small");
+    QB_REQUIRE((size_t)rows * w->rows <= b->parts_floats, "split scratch too small");
+    *S_out = S;
+    return qb_launch_gemm(ctx, w, x.q, x.d, rows, b->parts, S, b->gemm_impl);
+}
+
+// h += parts ; xq = quant(rmsnorm(h) * w)
+static int residual_norm_quant(qb_ctx *ctx, qb_batch *b, float *h, uint32_t rows, uint32_t S, const float *norm_w, const QBuf &dst,
+                               uint32_t q_col_off = 0, bool add_x = true) {
+    const qb_model_config &c = b->m->cfg;
+    NormQuantArgs a;
+    a.x = add_x ? h : nullptr; a.x_stride = c.n_embd;
+    a.parts = b->parts; a.S = S; a.part_ld = c.n_embd;
+    a.h_out = h; a.h_stride = c.n_embd;
+    a.w = norm_w; a.eps = c.rms_eps; a.n = c.n_embd; a.M = rows;
+    a.q = dst.q; a.q_pitch = dst.K; a.q_col_off = q_col_off; a.d = dst.d; a.d_ld = qb_act_ld(rows); a.d_kb_off = q_col_off / 32;
+    return qb_launch_norm_quant(ctx, a);
+}
+
+static int plain_norm_quant(qb_ctx *ctx, qb_batch *b, const float *x, const int32_t *row_map, uint32_t rows, const float *norm_w,
+                            const QBuf &dst, uint32_t q_col_off = 0) {
+    const qb_model_config &c = b->m->cfg;
+    NormQuantArgs a;
+    a.x = x; a.x_stride = c.n_embd; a.row_map = row_map;
+    a.w = norm_w; a.eps = c.rms_eps; a.n = c.n_embd; a.M = rows;
+    a.q = dst.q; a.q_pitch = dst.K; a.q_col_off = q_col_off; a.d = dst.d; a.d_ld = qb_act_ld(rows); a.d_kb_off = q_col_off / 32;
+    return qb_launch_norm_quant(ctx, a);
+}
+
+struct RowSet {
+    uint32_t seq0 = 0, ns = 0, R = 0;      // sequences [seq0, seq0+ns), R rows each
+    const int32_t *seq_pos = nullptr;      // device [ns]: position of each sequence's first row
+    uint32_t max_pos = 0;                  // host upper bound of any row position
+    uint32_t rows() const { return ns * R; }
+};
+
+// One attention block on h (xq_h already holds quant(rmsnorm(h))).  kv_only: K/V append only.
+static int attention_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t cache_idx, float *h, const RowSet &rs, bool kv_only,
+                           const float *next_norm_w) {
+    qb_model *m = b->m;
+    const qb_model_config &c = m->cfg;
+    const uint32_t rows = rs.rows();
+    AttnArgs a;
+    a.rows = rows; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.hd = c.head_dim; a.rope_dim = c.rope_dim; a.eps = c.rms_eps;
+    a.q_norm_w = m->ones; a.k_norm_w = m->ones; a.inv_freq = m->inv_freq;
+    a.page_table = b->page_table + (size_t)rs.seq0 * b->pages_per_seq; a.pt_stride = b->pages_per_seq; a.page_size = b->page_size;
+    a.k_cache = b->kc[cache_idx]; a.v_cache = b->vc[cache_idx];
+    a.max_pos = rs.max_pos; a.part_acc = b->att_acc; a.part_ml = b->att_ml; a.kv_only = kv_only;
+    if (kv_only) {
+        // only the k and v rows of the fused projection, with the split count of the fused weight so the
+        // values are bit-identical to the full projection; compact [k | v] rows, no q heads
+        const uint32_t S = qb_ksplit(L.w_in->rows, L.w_in->cols);
+        QB_TRY(gemm_to(ctx, b, &L.w_kv, b->xq_h, rows, b->act, S));
+        a.qkv = b->act; a.row_stride = 2 * m->kvd(); a.n_heads = 0;
+        return qb_attn_prepare(ctx, a, rs.seq_pos, rs.ns);
+    }
+    a.qkv = b->act; a.row_stride = m->attn_in();
+    QB_TRY(gemm_to(ctx, b, L.w_in, b->xq_h, rows, b->act));
+    QB_TRY(qb_attn_prepare(ctx, a, rs.seq_pos, rs.ns));
+    QB_TRY(qb_attn_run(ctx, a, rs.seq_pos, rs.ns, nullptr, b->xq_attn.q, b->xq_attn.K, b->xq_attn.d, qb_act_ld(rows)));
+    uint32_t S = 1;
+    QB_TRY(gemm_parts(ctx, b, L.w_out, b->xq_attn, rows, &S));
+    return residual_norm_quant(ctx, b, h, rows, S, next_norm_w, b->xq_h);
+}
+
+static int ffn_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, float *h, uint32_t rows, const float *next_norm_w) {
+    const qb_model_config &c = b->m->cfg;
+    QB_TRY(gemm_to(ctx, b, L.w_gate_up, b->xq_h, rows, b->act));
+    QB_TRY(qb_launch_swiglu_quant(ctx, b->act, 2 * c.n_ff, rows, c.n_ff, b->xq_ffn.q, b->xq_ffn.K, b->xq_ffn.d, qb_act_ld(rows)));
+    uint32_t S = 1;
+    QB_TRY(gemm_parts(ctx, b, L.w_down, b->xq_ffn, rows, &S));
+    return residual_norm_quant(ctx, b, h, rows, S, next_norm_w, b->xq_h);
+}
+
+static int deltanet_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t il, float *h, const RowSet &rs, bool checkpoints,
+                          const float *next_norm_w) {
+    qb_model *m = b->m;
+    const qb_model_config &c = m->cfg;
+    const uint32_t rows = rs.rows(), K1 = b->k + 1;
+    QB_TRY(gemm_to(ctx, b, L.w_in, b->xq_h, rows, b->act));
+    DnArgs d;
+    d.proj = b->act; d.proj_stride = m->dn_in(); d.n_seqs = rs.ns; d.rows_per_seq = rs.R;
+    d.conv_w = L.conv_w; d.ssm_a = L.ssm_a; d.dt_bias = L.dt_bias; d.norm_w = m->ones;
+    d.nk = c.ssm_num_k_heads; d.nv = c.ssm_num_v_heads; d.hd = c.ssm_head_dim; d.eps = c.rms_eps;
+    d.state = b->state[il] + (size_t)rs.seq0 * K1 * c.ssm_num_v_heads * c.ssm_head_dim * c.ssm_head_dim;
+    d.conv = b->conv[il] + (size_t)rs.seq0 * K1 * m->qkv_dim() * 3;
+    d.n_slots = K1; d.slot_in = b->sel + rs.seq0; d.write_all = checkpoints ? 1 : 0;
+    d.xconv = b->xconv; d.core = b->core;
+    d.q8 = b->xq_dn.q; d.q_pitch = b->xq_dn.K; d.d = b->xq_dn.d; d.d_ld = qb_act_ld(rows);
+    QB_TRY(qb_launch_deltanet(ctx, d));
+    uint32_t S = 1;
+    QB_TRY(gemm_parts(ctx, b, L.w_out, b->xq_dn, rows, &S));
+    return residual_norm_quant(ctx, b, h, rows, S, next_norm_w, b->xq_h);
+}
+
+// Target model on a row set.  tokens on the device ([rows]).  Leaves the pre-output-norm hidden rows
+// in b->hid[0 .. rows).  logits: 0 none, 1 every row, 2 last row of each sequence.
+static int target_forward(qb_ctx *ctx, qb_batch *b, const int32_t *tokens_dev, const RowSet &rs, bool checkpoints, int logits) {
+    qb_model *m = b->m;
+    const qb_model_config &c = m->cfg;
+    const uint32_t rows = rs.rows();
+    QB_REQUIRE(rows <= b->rows_cap, "forward: %u rows exceed capacity %u", rows, b->rows_cap);
+    float *h = b->hid;
+    QB_TRY(qb_launch_get_rows(ctx, m->token_embd, tokens_dev, rows, h, c.n_embd));
+    QB_TRY(plain_norm_quant(ctx, b, h, nullptr, rows, m->ones, b->xq_h));
+    for (uint32_t il = 0; il < c.n_layers; ++il) {
+        const LayerW &L = m->layers[il];
+        if (L.recurrent) QB_TRY(deltanet_block(ctx, b, L, il, h, rs, checkpoints, m->ones));
+        else QB_TRY(attention_block(ctx, b, L, il, h, rs, false, m->ones));
+        QB_TRY(ffn_block(ctx, b, L, h, rows, m->ones));   // the next norm is the next layer's attn_norm or output_norm
+    }
+    b->last_logit_rows = 0;
+    if (logits == 1) {
+        QB_REQUIRE(rows <= b->logit_rows, "logits for %u rows exceed capacity %u", rows, b->logit_rows);
+        QB_TRY(gemm_to(ctx, b, m->output, b->xq_h, rows, b->logits));
+        QB_TRY(qb_launch_argmax_partial(ctx, b->logits, rows, c.vocab_size, c.vocab_size, b->am_val, b->am_idx, QB_ARGMAX_BLOCKS));
+        b->last_logit_rows = rows;
+    } else if (logits == 2) {
+        // last row of each sequence: quantise those rows again as a compact batch
+        std::vector<int32_t> map(rs.ns);
+        for (uint32_t s = 0; s < rs.ns; ++s) map[s] = (int32_t)(s * rs.R + rs.R - 1);
+        QB_CUDA(cudaMemcpyAsync(b->map_last, map.data(), rs.ns * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        QB_TRY(plain_norm_quant(ctx, b, h, b->map_last, rs.ns, m->ones, b->xq_h));
+        QB_TRY(gemm_to(ctx, b, m->output, b->xq_h, rs.ns, b->logits));
+        QB_TRY(qb_launch_argmax_partial(ctx, b->logits, rs.ns, c.vocab_size, c.vocab_size, b->am_val, b->am_idx, QB_ARGMAX_BLOCKS));
+        b->last_logit_rows = rs.ns;
+    }
+    return QB_OK;
+}
+
+// MTP head on a row set (forward_mtp_draft_from, src/qwen_executor.cpp:7025-7255).  Row r uses token
+// tokens_dev[r] and the hidden row hsrc[hmap[r]] as h_prev.  kv_only stops after the K/V append.
+// Full mode leaves the post-layer hidden in b->mtp_h and the argmax partials of the logits.
+static int mtp_forward(qb_ctx *ctx, qb_batch *b, const int32_t *tokens_dev, const float *hsrc, const int32_t *hmap, const RowSet &rs,
+                       bool kv_only) {
+    qb_model *m = b->m;
+    const qb_model_config &c = m->cfg;
+    const uint32_t rows = rs.rows(), H = c.n_embd;
+    const LayerW &L = m->layers[c.n_layers];
+    QB_TRY(qb_launch_get_rows(ctx, m->token_embd, tokens_dev, rows, b->embd, H));
+    QB_TRY(plain_norm_quant(ctx, b, b->embd, nullptr, rows, m->ones, b->xq_cat, 0));      // enorm
+    QB_TRY(plain_norm_quant(ctx, b, hsrc, hmap, rows, m->ones, b->xq_cat, H));             // hnorm
+    uint32_t S = 1;
+    QB_TRY(gemm_parts(ctx, b, m->eh_proj, b->xq_cat, rows, &S));
+    QB_TRY(residual_norm_quant(ctx, b, b->mtp_h, rows, S, m->ones, b->xq_h, 0, /*add_x=*/false));
+    QB_TRY(attention_block(ctx, b, L, c.n_layers, b->mtp_h, rs, kv_only, m->ones));
+    if (kv_only) return QB_OK;
+    QB_TRY(ffn_block(ctx, b, L, b->mtp_h, rows, m->ones));   // next norm = shared_head_norm
+    QB_REQUIRE(rows <= b->logit_rows, "MTP logits rows exceed capacity");
+    QB_TRY(gemm_to(ctx, b, m->output, b->xq_h, rows, b->logits));
+    QB_TRY(qb_launch_argmax_partial(ctx, b->logits, rows, c.vocab_size, c.vocab_size, b->am_val, b->am_idx, QB_ARGMAX_BLOCKS));
+    b->last_logit_rows = rows;
+    return QB_OK;
+}
+
+static uint32_t max_host_pos(const qb_batch *b) {
+    int32_t mx = 0;
+    for (int32_t p : b->host_pos) mx = std::max(mx, p);
+    return (uint32_t)mx;
+}
+
+extern "C" int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n) {
+    QB_REQUIRE(ctx && b && tokens_host && n > 0 && seq < b->n_seqs, "qb_prefill: bad arguments");
+    QB_REQUIRE((uint32_t)b->host_pos[seq] + n + b->k + 1 <= b->max_ctx + b->k + 1 && (uint32_t)b->host_pos[seq] + n <= b->max_ctx,
+               "qb_prefill: %u tokens at position %d exceed max_ctx %u", n, b->host_pos[seq], b->max_ctx);
+    QB_CUDA(cudaSetDevice(ctx->device));
+    qb_model *m = b->m;
+    const qb_model_config &c = m->cfg;
+    const uint32_t K1 = b->k + 1;
+    for (uint32_t off = 0; off < n; off += b->chunk) {
+        const uint32_t M = std::min(b->chunk, n - off);
+        const bool last = off + M == n;
+        const uint32_t p0 = (uint32_t)b->host_pos[seq];
+        QB_CUDA(cudaMemcpyAsync(b->tok_buf, tokens_host + off, M * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        RowSet rs;
+        rs.seq0 = seq; rs.ns = 1; rs.R = M; rs.seq_pos = b->pos + seq; rs.max_pos = p0 + M;
+        QB_TRY(target_forward(ctx, b, b->tok_buf, rs, false, last ? 2 : 0));
+        if (c.mtp_layers && b->k > 0) {
+            std::vector<int32_t> map(M);
+            map[0] = (int32_t)(b->rows_cap + seq);
+            for (uint32_t r = 1; r < M; ++r) map[r] = (int32_t)(r - 1);
+            QB_CUDA(cudaMemcpyAsync(b->map_chunk, map.data(), M * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+            QB_CUDA(cudaStreamSynchronize(ctx->stream));   // map / token vectors go out of scope
+            QB_TRY(mtp_forward(ctx, b, b->tok_buf, b->hid, b->map_chunk, rs, true));
+        }
+        if (last) {
+            greedy_commit_kernel<<<1, 256, 0, ctx->stream>>>(b->am_val, b->am_idx, 0, M - 1, 0, seq, 1, K1, b->rows_cap, c.n_embd,
+                                                           b->pos, b->sel, b->cur, (int32_t)M, b->out_rec, b->n_seqs, b->hid,
+                                                           (unsigned long long *)b->stats);
+            QB_LAUNCHED(ctx, "greedy_commit_kernel");
+        } else {
+            advance_kernel<<<1, 256, 0, ctx->stream>>>(b->pos, b->sel, seq, (int32_t)M, b->rows_cap, c.n_embd, M - 1, b->hid);
+            QB_LAUNCHED(ctx, "advance_kernel");
+        }
+        b->host_pos[seq] += (int32_t)M;
+        QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    }
+    return QB_OK;
+}
+
+static int check_room(qb_batch *b, uint32_t need) {
+    for (uint32_t s = 0; s < b->n_seqs; ++s)
+        if ((uint32_t)b->host_pos[s] + need > b->max_ctx + b->k + 1 || (uint32_t)b->host_pos[s] >= b->max_ctx)
+            return qb_fail(QB_ERR_CAPACITY, "sequence %u at position %d has no room for %u more positions (max_ctx %u)", s,
+                           b->host_pos[s], need, b->max_ctx);
+    return QB_OK;
+}
+
+extern "C" int qb_decode_greedy_step(qb_ctx *ctx, qb_batch *b) {
+    QB_REQUIRE(ctx && b, "qb_decode_greedy_step: null argument");
+    QB_TRY(check_room(b, 1));
+    QB_CUDA(cudaSetDevice(ctx->device));
+    const qb_model_config &c = b->m->cfg;
+    RowSet rs;
+    rs.seq0 = 0; rs.ns = b->n_seqs; rs.R = 1; rs.seq_pos = b->pos; rs.max_pos = max_host_pos(b) + 1;
+    QB_TRY(target_forward(ctx, b, b->cur, rs, false, 1));
+    greedy_commit_kernel<<<b->n_seqs, 256, 0, ctx->stream>>>(b->am_val, b->am_idx, 0, 0, 1, 0, b->n_seqs, b->k + 1, b->rows_cap,
+                                                           c.n_embd, b->pos, b->sel, b->cur, 1, b->out_rec, b->n_seqs, b->hid,
+                                                           (unsigned long long *)b->stats);
+    QB_LAUNCHED(ctx, "greedy_commit_kernel");
+    for (auto &p : b->host_pos) p += 1;
+    return QB_OK;
+}
+
+extern "C" int qb_mtp_draft(qb_ctx *ctx, qb_batch *b) {
+    QB_REQUIRE(ctx && b && b->k > 0, "qb_mtp_draft: needs a batch with draft depth > 0");
+    QB_TRY(check_room(b, b->k + 1));
+    QB_CUDA(cudaSetDevice(ctx->device));
+    const uint32_t ns = b->n_seqs, k = b->k;
+    for (uint32_t i = 0; i < k; ++i) {
+        prep_draft_kernel<<<(ns + 127) / 128, 128, 0, ctx->stream>>>(b->cur, b->drafts, b->pos, ns, k, i, b->tok_buf, b->seqpos_buf);
+        QB_LAUNCHED(ctx, "prep_draft_kernel");
+        RowSet rs;
+        rs.seq0 = 0; rs.ns = ns; rs.R = 1; rs.seq_pos = b->seqpos_buf; rs.max_pos = max_host_pos(b) + i + 1;
+        // step 0 reads the target hidden of the last committed position, later steps the MTP hidden
+        if (i == 0) QB_TRY(mtp_forward(ctx, b, b->tok_buf, b->hid, b->map_prevh, rs, false));
+        else QB_TRY(mtp_forward(ctx, b, b->tok_buf, b->mtp_h, nullptr, rs, false));
+        store_draft_kernel<<<(ns + 127) / 128, 128, 0, ctx->stream>>>(b->am_val, b->am_idx, ns, k, i, b->drafts);
+        QB_LAUNCHED(ctx, "store_draft_kernel");
+    }
+    return QB_OK;
+}
+
+extern "C" int qb_mtp_force_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *stream_dev, uint32_t stream_stride, float rate,
+                                   uint64_t seed) {
+    QB_REQUIRE(ctx && b && stream_dev && b->k > 0, "qb_mtp_force_drafts: bad arguments");
+    const uint32_t n = b->n_seqs * b->k;
+    force_drafts_kernel<<<(n + 127) / 128, 128, 0, ctx->stream>>>(b->drafts, b->pos, b->n_seqs, b->k, stream_dev, stream_stride, rate,
+                                                                 seed, b->m->cfg.vocab_size);
+    QB_LAUNCHED(ctx, "force_drafts_kernel");
+    return QB_OK;
+}
+
+extern "C" int qb_mtp_verify(qb_ctx *ctx, qb_batch *b) {
+    QB_REQUIRE(ctx && b && b->k > 0, "qb_mtp_verify: needs a batch with draft depth > 0");
+    QB_TRY(check_room(b, b->k + 1));
+    QB_CUDA(cudaSetDevice(ctx->device));
+    const uint32_t ns = b->n_seqs, K1 = b->k + 1;
+    prep_verify_kernel<<<(ns * K1 + 127) / 128, 128, 0, ctx->stream>>>(b->cur, b->drafts, ns, b->k, b->tok_buf);
+    QB_LAUNCHED(ctx, "prep_verify_kernel");
+    RowSet rs;
+    rs.seq0 = 0; rs.ns = ns; rs.R = K1; rs.seq_pos = b->pos; rs.max_pos = max_host_pos(b) + K1;
+    return target_forward(ctx, b, b->tok_buf, rs, true, 1);
+}
+
+extern "C" int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b) {
+    QB_REQUIRE(ctx && b && b->k > 0, "qb_mtp_accept_commit: needs a batch with draft depth > 0");
+    QB_CUDA(cudaSetDevice(ctx->device));
+    const qb_model_config &c = b->m->cfg;
+    const uint32_t ns = b->n_seqs, k = b->k;
+    accept_commit_kernel<<<ns, 256, 0, ctx->stream>>>(b->am_val, b->am_idx, k, b->rows_cap, c.n_embd, b->pos, b->sel, b->cur, b->drafts,
+                                                    b->prefix_pos, b->prefix_tok, b->out_rec, ns, b->hid,
+                                                    (unsigned long long *)b->stats);
+    QB_LAUNCHED(ctx, "accept_commit_kernel");
+    // MTP-layer K/V of positions old_pos+1 .. old_pos+k from (draft_i, target hidden of row i-1); the
+    // rows beyond the accepted prefix land past the committed length and are overwritten later.
+    RowSet rs;
+    rs.seq0 = 0; rs.ns = ns; rs.R = k; rs.seq_pos = b->prefix_pos; rs.max_pos = max_host_pos(b) + k + 1;
+    QB_TRY(mtp_forward(ctx, b, b->prefix_tok, b->hid, b->map_prefix, rs, true));
+    for (auto &p : b->host_pos) p += (int32_t)(k + 1);   // upper bound until the host reads the step record
+    return QB_OK;
+}
+
+extern "C" int qb_mtp_step(qb_ctx *ctx, qb_batch *b) {
+    QB_TRY(qb_mtp_draft(ctx, b));
+    QB_TRY(qb_mtp_verify(ctx, b));
+    return qb_mtp_accept_commit(ctx, b);
+}
+
+extern "C" int qb_read_step_output(qb_ctx *ctx, qb_batch *b, int32_t *n_out_host, int32_t *tokens_host) {
+    QB_REQUIRE(ctx && b, "qb_read_step_output: null argument");
+    const uint32_t ns = b->n_seqs, K1 = b->k + 1;
+    const size_t n = (size_t)ns * (K1 + 2);
+    QB_CUDA(cudaMemcpyAsync(b->out_rec_host, b->out_rec, n * sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    QB_TRY(qb_synchronize(ctx));
+    if (n_out_host) memcpy(n_out_host, b->out_rec_host, ns * sizeof(int32_t));
+    if (tokens_host) memcpy(tokens_host, b->out_rec_host + ns, (size_t)ns * K1 * sizeof(int32_t));
+    for (uint32_t s = 0; s < ns; ++s) b->host_pos[s] = b->out_rec_host[ns + (size_t)ns * K1 + s];
+    return QB_OK;
+}
+
+extern "C" int qb_batch_stats(qb_ctx *ctx, qb_batch *b, int64_t *out4) {
+    QB_CUDA(cudaMemcpyAsync(out4, b->stats, 4 * sizeof(long long), cudaMemcpyDeviceToHost, ctx->stream));
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return QB_OK;
+}
+
+extern "C" int qb_seq_position(qb_ctx *ctx, qb_batch *b, uint32_t seq, int32_t *pos) {
+    QB_REQUIRE(seq < b->n_seqs, "qb_seq_position: sequence out of range");
+    QB_CUDA(cudaMemcpyAsync(pos, b->pos + seq, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return QB_OK;
+}
+
+extern "C" int qb_debug_last_logits(qb_ctx *ctx, qb_batch *b, float *host_out, uint32_t max_rows, uint32_t *rows_out) {
+    const uint32_t r = std::min(max_rows, b->last_logit_rows);
+    if (r) QB_CUDA(cudaMemcpyAsync(host_out, b->logits, (size_t)r * b->m->cfg.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (rows_out) *rows_out = r;
+    return QB_OK;
+}
+extern "C" int qb_debug_set_keep_logits(qb_ctx *, qb_batch *, int) { return QB_OK; }

@@ -1,0 +1,58 @@
+// Op-level C entry points for the attention and DeltaNet kernels (used by the parity tests and by
+// a DeviceBackend shim; the engine calls the launchers directly).
+#include "qb_internal.h"
+
+extern "C" int qb_qk_norm_rope_append(qb_ctx *ctx, float *qkv_dev, uint32_t rows, uint32_t row_stride, const float *q_norm_w,
+                                      const float *k_norm_w, const float *inv_freq_dev, uint32_t n_heads, uint32_t n_kv_heads,
+                                      uint32_t head_dim, uint32_t rope_dim, float eps, const int32_t *seq_pos_dev,
+                                      uint32_t n_seqs, const int32_t *page_table_dev, uint32_t page_table_stride,
+                                      uint32_t page_size, void *k_cache_dev, void *v_cache_dev) {
+    QB_REQUIRE(ctx && qkv_dev && q_norm_w && k_norm_w && inv_freq_dev && seq_pos_dev && page_table_dev && k_cache_dev && v_cache_dev,
+               "qb_qk_norm_rope_append: null argument");
+    QB_REQUIRE(n_seqs > 0 && rows > 0 && page_size > 0, "qb_qk_norm_rope_append: empty launch");
+    AttnArgs a;
+    a.qkv = qkv_dev; a.rows = rows; a.row_stride = row_stride; a.n_heads = n_heads; a.n_kv = n_kv_heads; a.hd = head_dim;
+    a.rope_dim = rope_dim; a.eps = eps; a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w; a.inv_freq = inv_freq_dev;
+    a.page_table = page_table_dev; a.pt_stride = page_table_stride; a.page_size = page_size;
+    a.k_cache = (__half *)k_cache_dev; a.v_cache = (__half *)v_cache_dev;
+    return qb_attn_prepare(ctx, a, seq_pos_dev, n_seqs);
+}
+
+extern "C" int qb_attention_paged_gated(qb_ctx *ctx, const float *qkv_dev, uint32_t rows, uint32_t row_stride, uint32_t n_heads,
+                                        uint32_t n_kv_heads, uint32_t head_dim, const int32_t *seq_pos_dev, uint32_t n_seqs,
+                                        const int32_t *page_table_dev, uint32_t page_table_stride, uint32_t page_size,
+                                        const void *k_cache_dev, const void *v_cache_dev, uint32_t max_pos, float *out_dev) {
+    QB_REQUIRE(ctx && qkv_dev && seq_pos_dev && page_table_dev && k_cache_dev && v_cache_dev && out_dev,
+               "qb_attention_paged_gated: null argument");
+    QB_REQUIRE(n_seqs > 0 && rows > 0 && page_size > 0, "qb_attention_paged_gated: empty launch");
+    AttnArgs a;
+    a.qkv = const_cast<float *>(qkv_dev); a.rows = rows; a.row_stride = row_stride; a.n_heads = n_heads; a.n_kv = n_kv_heads;
+    a.hd = head_dim; a.page_table = page_table_dev; a.pt_stride = page_table_stride; a.page_size = page_size;
+    a.k_cache = (__half *)const_cast<void *>(k_cache_dev); a.v_cache = (__half *)const_cast<void *>(v_cache_dev);
+    a.max_pos = max_pos;
+    size_t ml = 0;
+    const size_t acc = qb_attention_scratch_floats(rows, n_heads, head_dim, max_pos, &ml);
+    void *scr = nullptr;
+    QB_TRY(qb_ctx_scratch(ctx, (acc + ml) * sizeof(float), &scr));
+    a.part_acc = (float *)scr;
+    a.part_ml = a.part_acc + acc;
+    return qb_attn_run(ctx, a, seq_pos_dev, n_seqs, out_dev, nullptr, 0, nullptr, 0);
+}
+
+extern "C" int qb_deltanet_rows(qb_ctx *ctx, const float *proj_dev, uint32_t n_seqs, uint32_t rows_per_seq, uint32_t proj_stride,
+                                const float *conv_w, const float *ssm_a, const float *dt_bias, const float *norm_w, uint32_t nk,
+                                uint32_t nv, uint32_t hd, float eps, float *state_dev, float *conv_dev, uint32_t n_slots,
+                                const int32_t *slot_in_dev, int write_all, float *core_dev) {
+    QB_REQUIRE(ctx && proj_dev && conv_w && ssm_a && dt_bias && norm_w && state_dev && conv_dev && slot_in_dev && core_dev,
+               "qb_deltanet_rows: null argument");
+    const uint32_t rows = n_seqs * rows_per_seq, C = (2 * nk + nv) * hd, vdim = nv * hd;
+    QB_REQUIRE(proj_stride >= C + vdim + 2 * nv, "qb_deltanet_rows: proj_stride %u too small", proj_stride);
+    void *scr = nullptr;
+    QB_TRY(qb_ctx_scratch(ctx, ((size_t)rows * C + (size_t)rows * vdim) * sizeof(float), &scr));
+    DnArgs d;
+    d.proj = proj_dev; d.proj_stride = proj_stride; d.n_seqs = n_seqs; d.rows_per_seq = rows_per_seq;
+    d.conv_w = conv_w; d.ssm_a = ssm_a; d.dt_bias = dt_bias; d.norm_w = norm_w; d.nk = nk; d.nv = nv; d.hd = hd; d.eps = eps;
+    d.state = state_dev; d.conv = conv_dev; d.n_slots = n_slots; d.slot_in = slot_in_dev; d.write_all = write_all;
+    d.xconv = (float *)scr; d.core = d.xconv + (size_t)rows * C; d.core_out = core_dev;
+    return qb_launch_deltanet(ctx, d);
+}

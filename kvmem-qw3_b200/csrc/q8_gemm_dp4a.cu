@@ -1,0 +1,235 @@
+// Q8_0 x Q8 product on CUDA cores: weight-streaming kernel for a handful of activation rows.
+//
+// Stands in for mul_mat_vec_q8_0_kernel and its fused variants (src/mmvq_q8.cu:195-1113) on the
+// decode / draft / (k+1)-row verify shapes.  Arithmetic per output: exact int32 dot of each
+// 32-block (dp4a), acc = fma(d_w*d_x, float(dot), acc) over the blocks of a K segment in ascending
+// order (the per-output update of src/mmq_q8.cu:1738-1748); one partial sum per segment.
+//
+// Data movement: a CTA owns 128 weight rows and one K segment.  Weight bytes arrive through a
+// 4-stage cp.async pipeline, 128 rows x 128 bytes per stage, stored with a 16-byte XOR swizzle so
+// that "one thread = one weight row" reads are bank-conflict free; activations of the pass are
+// staged beside them and read as warp broadcasts.
+#include "qb_internal.h"
+
+namespace {
+
+constexpr int TILE_N = 128;
+constexpr int CHUNK = 128;
+constexpr int NSTAGE = 4;
+constexpr int THREADS = 256;
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem, bool valid) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__host__ __device__ inline uint32_t seg_begin(uint32_t s, uint32_t S, uint32_t nchunks) {
+    return (uint32_t)(((uint64_t)s * nchunks) / S);
+}
+
+template <int MPT>
+struct Smem {
+    static constexpr int NC = 2 * MPT;
+    static constexpr int WQ = TILE_N * CHUNK;          // 16384
+    static constexpr int WD = 4 * TILE_N * 2;          // 1024
+    static constexpr int XQ = NC * CHUNK;
+    static constexpr int STAGE = WQ + WD + XQ;
+    static constexpr int TOTAL = STAGE * NSTAGE;
+};
+
+template <int MPT>
+__global__ void __launch_bounds__(THREADS) gemm_dp4a_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ wd,
+                                                            uint32_t ld, uint32_t K, uint32_t N,
+                                                            const int8_t *__restrict__ xq, const float *__restrict__ xd,
+                                                            uint32_t M, uint32_t xld, float *__restrict__ part, uint32_t S) {
+    using L = Smem<MPT>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t tid = threadIdx.x;
+    const uint32_t row0 = blockIdx.x * TILE_N;
+    const uint32_t seg = blockIdx.y;
+    const uint32_t m0 = blockIdx.z * L::NC;
+    const uint32_t nchunks = K / CHUNK;
+    const uint32_t c_begin = seg_begin(seg, S, nchunks), c_end = seg_begin(seg + 1, S, nchunks);
+    const uint32_t n_it = c_end - c_begin;
+
+    auto load_stage = [&](uint32_t it, uint32_t slot) {
+        uint8_t *st = smem + (size_t)slot * L::STAGE;
+        const uint32_t k0 = (c_begin + it) * CHUNK;
+#pragma unroll
+        for (int i = 0; i < (TILE_N * 8) / THREADS; ++i) {
+            const uint32_t c = tid + i * THREADS, r = c >> 3, p = c & 7;
+            cp_async16(st + r * CHUNK + ((p ^ (r & 7)) << 4), wq + (size_t)(row0 + r) * K + k0 + p * 16, true);
+        }
+        if (tid < 64) {
+            const uint32_t kb = tid >> 4, p = tid & 15;
+            cp_async16(st + L::WQ + kb * 256 + p * 16, wd + (size_t)(k0 / 32 + kb) * ld + row0 + p * 8, true);
+        }
+        if (tid >= 64 && tid < 64 + L::NC * 8) {
+            const uint32_t c = tid - 64, col = c >> 3, p = c & 7;
+            const bool valid = m0 + col < M;
+            cp_async16(st + L::WQ + L::WD + col * CHUNK + p * 16, xq + (size_t)(valid ? m0 + col : 0) * K + k0 + p * 16, valid);
+        }
+    };
+
+    const uint32_t r = tid & 127, cg = tid >> 7;
+    float acc[MPT];
+#pragma unroll
+    for (int j = 0; j < MPT; ++j) acc[j] = 0.0f;
+
+    for (uint32_t s = 0; s < NSTAGE - 1; ++s) {
+        if (s < n_it) load_stage(s, s);
+        cp_async_commit();
+    }
+    for (uint32_t it = 0; it < n_it; ++it) {
+        cp_async_wait<NSTAGE - 2>();
+        __syncthreads();
+        if (it + NSTAGE - 1 < n_it) load_stage(it + NSTAGE - 1, (it + NSTAGE - 1) % NSTAGE);
+        cp_async_commit();
+
+        const uint8_t *st = smem + (size_t)(it % NSTAGE) * L::STAGE;
+        const uint32_t kb0 = (c_begin + it) * 4;
+        float sx[4][MPT];
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+            for (int j = 0; j < MPT; ++j) {
+                const uint32_t m = m0 + cg * MPT + j;
+                sx[kb][j] = (m < M) ? __ldg(xd + (size_t)(kb0 + kb) * xld + m) : 0.0f;
+            }
+        const __half *sd = reinterpret_cast<const __half *>(st + L::WQ);
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+            const int4 w0 = *reinterpret_cast<const int4 *>(st + r * CHUNK + (((2 * kb) ^ (r & 7)) << 4));
+            const int4 w1 = *reinterpret_cast<const int4 *>(st + r * CHUNK + (((2 * kb + 1) ^ (r & 7)) << 4));
+            const float dw = __half2float(sd[kb * TILE_N + r]);
+#pragma unroll
+            for (int j = 0; j < MPT; ++j) {
+                const uint8_t *xb = st + L::WQ + L::WD + (cg * MPT + j) * CHUNK + kb * 32;
+                const int4 x0 = *reinterpret_cast<const int4 *>(xb);
+                const int4 x1 = *reinterpret_cast<const int4 *>(xb + 16);
+                int c = __dp4a(w0.x, x0.x, 0);
+                c = __dp4a(w0.y, x0.y, c);
+                c = __dp4a(w0.z, x0.z, c);
+                c = __dp4a(w0.w, x0.w, c);
+                c = __dp4a(w1.x, x1.x, c);
+                c = __dp4a(w1.y, x1.y, c);
+                c = __dp4a(w1.z, x1.z, c);
+                c = __dp4a(w1.w, x1.w, c);
+                acc[j] = __fmaf_rn(__fmul_rn(dw, sx[kb][j]), (float)c, acc[j]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    const uint32_t row = row0 + r;
+    if (row < N) {
+#pragma unroll
+        for (int j = 0; j < MPT; ++j) {
+            const uint32_t m = m0 + cg * MPT + j;
+            if (m < M) part[((size_t)seg * M + m) * N + row] = acc[j];
+        }
+    }
+}
+
+template <int MPT>
+int launch(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S) {
+    using L = Smem<MPT>;
+    static bool attr = false;
+    if (!attr) {
+        QB_CUDA(cudaFuncSetAttribute(gemm_dp4a_kernel<MPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        attr = true;
+    }
+    dim3 grid(w->rows_pad / TILE_N, S, (M + L::NC - 1) / L::NC);
+    gemm_dp4a_kernel<MPT><<<grid, THREADS, L::TOTAL, ctx->stream>>>(w->q, w->d, w->ld, w->cols, w->rows, q, d, M,
+                                                                   qb_act_ld(M), part, S);
+    QB_LAUNCHED(ctx, "gemm_dp4a_kernel");
+    return QB_OK;
+}
+
+// Exact int32 block dots, out[m][n][kb] (test aid for the integer part).
+__global__ void block_dots_kernel(const int8_t *__restrict__ wq, uint32_t K, uint32_t N, const int8_t *__restrict__ xq,
+                                  uint32_t M, int32_t *out) {
+    const uint32_t nb = K / 32;
+    const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (uint64_t)N * nb) return;
+    const uint32_t n = (uint32_t)(idx / nb), kb = (uint32_t)(idx % nb);
+    const int *wp = reinterpret_cast<const int *>(wq + (size_t)n * K + (size_t)kb * 32);
+    int wv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) wv[i] = wp[i];
+    for (uint32_t m = 0; m < M; ++m) {
+        const int *xp = reinterpret_cast<const int *>(xq + (size_t)m * K + (size_t)kb * 32);
+        int c = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) c = __dp4a(wv[i], xp[i], c);
+        out[((size_t)m * N + n) * nb + kb] = c;
+    }
+}
+
+}  // namespace
+
+uint32_t qb_ksplit(uint32_t N, uint32_t K) {
+    const uint32_t tiles = (N + 127) / 128, nchunks = K / 128;
+    uint32_t S = 148 / std::max(tiles, 1u);
+    S = std::max(1u, std::min(S, 8u));
+    S = std::min(S, std::max(nchunks, 1u));
+    return S;
+}
+extern "C" uint32_t qb_ksplit_policy(uint32_t N, uint32_t K) { return qb_ksplit(N, K); }
+
+int qb_launch_gemm_dp4a(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
+                        uint32_t S) {
+    QB_REQUIRE(M > 0 && S > 0 && S <= w->cols / 128, "gemm: bad M=%u or ksplit=%u", M, S);
+    if (M <= 2) return launch<1>(ctx, w, q, d, M, part, S);
+    if (M <= 4) return launch<2>(ctx, w, q, d, M, part, S);
+    return launch<4>(ctx, w, q, d, M, part, S);
+}
+
+int qb_launch_gemm(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
+                   uint32_t S, int impl) {
+    if (impl == 2) {
+        if (!qb_gemm_tc_supported(w, M))
+            return qb_fail(QB_ERR_UNSUPPORTED, "tensor-core GEMM does not support this shape");
+        return qb_launch_gemm_tc(ctx, w, q, d, M, part, S);
+    }
+    if (impl == 0 && qb_gemm_tc_supported(w, M)) return qb_launch_gemm_tc(ctx, w, q, d, M, part, S);
+    return qb_launch_gemm_dp4a(ctx, w, q, d, M, part, S);
+}
+
+extern "C" int qb_q8_gemm_partials(qb_ctx *ctx, const qb_weight *w, const int8_t *q_dev, const float *d_dev, uint32_t M,
+                                   float *part_dev, uint32_t ksplit, int impl) {
+    QB_REQUIRE(ctx && w && q_dev && d_dev && part_dev, "qb_q8_gemm_partials: null argument");
+    const uint32_t S = ksplit ? ksplit : qb_ksplit(w->rows, w->cols);
+    return qb_launch_gemm(ctx, w, q_dev, d_dev, M, part_dev, S, impl);
+}
+
+extern "C" int qb_q8_0_matmul(qb_ctx *ctx, const qb_weight *w, const float *x_dev, uint32_t M, uint32_t x_stride,
+                              float *y_dev, uint32_t y_stride, uint32_t ksplit, int impl) {
+    QB_REQUIRE(ctx && w && x_dev && y_dev && M > 0, "qb_q8_0_matmul: bad arguments");
+    QB_REQUIRE(x_stride >= w->cols && y_stride >= w->rows, "qb_q8_0_matmul: strides smaller than the matrix");
+    const uint32_t S = ksplit ? ksplit : qb_ksplit(w->rows, w->cols);
+    const uint32_t K = w->cols, N = w->rows, ld = qb_act_ld(M);
+    const size_t qbytes = ((size_t)M * K + 255) & ~(size_t)255;
+    const size_t dbytes = (((size_t)(K / 32) * ld * 4) + 255) & ~(size_t)255;
+    const size_t pbytes = (size_t)S * M * N * 4;
+    void *scr = nullptr;
+    QB_TRY(qb_ctx_scratch(ctx, qbytes + dbytes + pbytes, &scr));
+    int8_t *q = (int8_t *)scr;
+    float *d = (float *)((uint8_t *)scr + qbytes);
+    float *part = (float *)((uint8_t *)scr + qbytes + dbytes);
+    QB_TRY(qb_quantize_act(ctx, x_dev, M, K, x_stride, q, d));
+    if (S == 1 && y_stride == N) return qb_launch_gemm(ctx, w, q, d, M, y_dev, 1, impl);
+    QB_TRY(qb_launch_gemm(ctx, w, q, d, M, part, S, impl));
+    return qb_launch_reduce_parts(ctx, part, S, M, N, y_dev, y_stride);
+}
+
+extern "C" int qb_q8_block_dots(qb_ctx *ctx, const qb_weight *w, const int8_t *q_dev, uint32_t M, int32_t *out_dev) {
+    QB_REQUIRE(ctx && w && q_dev && out_dev, "qb_q8_block_dots: null argument");
+    const uint64_t total = (uint64_t)w->rows * (w->cols / 32);
+    block_dots_kernel<<<(uint32_t)((total + 255) / 256), 256, 0, ctx->stream>>>(w->q, w->cols, w->rows, q_dev, M, out_dev);
+    QB_LAUNCHED(ctx, "block_dots_kernel");
+    return QB_OK;
+}

@@ -1,0 +1,174 @@
+// Internal declarations shared by the CUDA translation units of libqw3b200.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <tuple>
+#include <vector>
+
+#include "../../include/qw3b200.h"
+#include "../../include/qw3b200_synth.h"
+
+// ---- error convention: thread-local message, integer status ------------------------------
+int qb_fail(int code, const char *fmt, ...);
+#define QB_CUDA(expr)                                                                              \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess)                                                                     \
+            return qb_fail(QB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),   \
+                           __FILE__, __LINE__);                                                    \
+    } while (0)
+#define QB_REQUIRE(cond, ...)                                                                      \
+    do {                                                                                           \
+        if (!(cond)) return qb_fail(QB_ERR_INVALID, __VA_ARGS__);                                  \
+    } while (0)
+#define QB_TRY(expr)                                                                               \
+    do {                                                                                           \
+        int _s = (expr);                                                                           \
+        if (_s != QB_OK) return _s;                                                                \
+    } while (0)
+// Counts a kernel launch and checks the launch status.
+#define QB_LAUNCHED(ctx, name)                                                                     \
+    do {                                                                                           \
+        (ctx)->launches++;                                                                         \
+        cudaError_t _e = cudaGetLastError();                                                       \
+        if (_e != cudaSuccess)                                                                     \
+            return qb_fail(QB_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e));  \
+    } while (0)
+
+struct qb_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    int64_t launches = 0;
+    float *normal_table_dev = nullptr;     // 65536-entry inverse-normal table for seeded weights
+    void *flush_buf = nullptr;             // > L2 bytes, written by qb_flush_l2
+    size_t flush_bytes = 0;
+    int *err_flag_dev = nullptr;           // set by kernels whose bounded waits ran out
+    // scratch of the op-level entry points (grown on demand)
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+};
+int qb_ctx_scratch(qb_ctx *ctx, size_t bytes, void **out);
+
+// ---- Q8_0 weight in device layout ----------------------------------------------------------
+// q: int8 [rows_pad][cols] row-major (rows_pad = rows rounded up to 128, padding rows are zero);
+// d: fp16 [cols/32][ld] with ld >= rows_pad, scale of row n / block kb at d[kb*ld + n].
+// Bytes held stay 34 per 32 weights.  A view shares storage with its parent.
+struct qb_weight {
+    uint32_t rows = 0, cols = 0, rows_pad = 0, ld = 0;
+    int8_t *q = nullptr;
+    __half *d = nullptr;
+    bool owns = false;
+    CUtensorMap map_q;    // {cols, rows_pad} uint8, box {128, 128}, 128-byte swizzle
+    CUtensorMap map_d;    // {ld(rows), cols/32} fp16, box {128, 4}
+    bool has_maps = false;
+};
+int qb_weight_alloc(qb_ctx *ctx, uint32_t rows, uint32_t cols, qb_weight **out);
+int qb_weight_fill_synth(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, uint64_t seed,
+                         uint32_t tensor_id, float sigma);
+int qb_weight_fill_upload(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, const void *host_blocks);
+// rows [row_off, row_off+rows) of w as a weight of its own (row_off multiple of 128).
+int qb_weight_view(qb_ctx *ctx, const qb_weight *w, uint32_t row_off, uint32_t rows, qb_weight *out);
+
+// ---- TMA tensor maps -----------------------------------------------------------------------
+// 2-D row-major tensor map: inner extent `inner` elements, `outer` rows, row pitch `pitch_bytes`.
+int qb_make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, uint32_t elem_bytes, const void *base,
+                    uint64_t inner, uint64_t outer, uint64_t pitch_bytes, uint32_t box_inner,
+                    uint32_t box_outer, CUtensorMapSwizzle swz);
+
+// ---- quantised activations -----------------------------------------------------------------
+// q: int8 [M][K] (row pitch q_pitch bytes); d: float [K/32][ld], ld = round_up(M, 4).
+static inline uint32_t qb_act_ld(uint32_t M) { return (M + 3u) & ~3u; }
+
+// x (+ optional residual / split partials) -> optional h_out -> optional RMSNorm -> int8 + scales.
+struct NormQuantArgs {
+    const float *x = nullptr;        // [M][x_stride] or null (treated as zero)
+    uint32_t x_stride = 0;
+    const int32_t *row_map = nullptr;  // source row of x for output row m (null = identity)
+    const float *parts = nullptr;    // [S][M][part_ld] partial sums added in ascending s, or null
+    uint32_t S = 0;
+    uint32_t part_ld = 0;            // = n of the GEMM that produced them
+    float *h_out = nullptr;          // [M][h_stride] receives x + sum(parts), may alias x; or null
+    uint32_t h_stride = 0;
+    const float *w = nullptr;        // RMSNorm gain [n]; null = no normalisation
+    float eps = 0.f;
+    uint32_t n = 0;                  // row length, multiple of 32
+    int8_t *q = nullptr;             // [M][q_pitch] written at column q_col_off
+    uint32_t q_pitch = 0, q_col_off = 0;
+    float *d = nullptr;              // [..][d_ld] written from block row d_kb_off
+    uint32_t d_ld = 0, d_kb_off = 0;
+    float *normed_out = nullptr;     // optional fp32 copy of the normalised row [M][n]
+    uint32_t M = 0;
+};
+int qb_launch_norm_quant(qb_ctx *ctx, const NormQuantArgs &a);
+
+// gate/up fp32 [M][2F] (gate cols [0,F), up cols [F,2F)) -> silu(gate)*up -> int8 + scales.
+int qb_launch_swiglu_quant(qb_ctx *ctx, const float *gu, uint32_t gu_stride, uint32_t M, uint32_t F, int8_t *q,
+                           uint32_t q_pitch, float *d, uint32_t d_ld);
+
+// ---- GEMM ----------------------------------------------------------------------------------
+// part[s][m][n] for s < S; activations q [M][K] pitch K, d [K/32][ld].
+int qb_launch_gemm(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
+                   uint32_t S, int impl);
+int qb_launch_gemm_dp4a(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
+                        uint32_t S);
+int qb_launch_gemm_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
+                      uint32_t S);
+bool qb_gemm_tc_supported(const qb_weight *w, uint32_t M);
+uint32_t qb_ksplit(uint32_t N, uint32_t K);
+// y[m][n] = sum_s part[s][m][n] (ascending s).
+int qb_launch_reduce_parts(qb_ctx *ctx, const float *part, uint32_t S, uint32_t M, uint32_t N, float *y,
+                           uint32_t y_stride);
+
+// ---- misc ops used by the engine -----------------------------------------------------------
+int qb_launch_get_rows(qb_ctx *ctx, const qb_weight *w, const int32_t *ids_dev, uint32_t n, float *out,
+                       uint32_t out_stride);
+int qb_launch_argmax_partial(qb_ctx *ctx, const float *x, uint32_t M, uint32_t n, uint32_t stride, float *pval,
+                             int32_t *pidx, uint32_t nblk);
+static const uint32_t QB_ARGMAX_BLOCKS = 64;
+
+// Attention over the paged cache.  Rows are grouped per sequence: sequence s owns rows
+// [s*R, (s+1)*R), R = rows / n_seqs, at positions seq_pos[s] .. seq_pos[s]+R-1 (seq_pos on the device).
+struct AttnArgs {
+    float *qkv = nullptr; uint32_t rows = 0, row_stride = 0;   // rows [q(+gate) | k | v]
+    uint32_t n_heads = 0, n_kv = 0, hd = 0, rope_dim = 0; float eps = 0.f;
+    const float *q_norm_w = nullptr, *k_norm_w = nullptr, *inv_freq = nullptr;
+    const int32_t *page_table = nullptr;
+    uint32_t pt_stride = 0, page_size = 0;
+    __half *k_cache = nullptr, *v_cache = nullptr;
+    uint32_t max_pos = 0;            // upper bound of any row position (sizes the split grid)
+    float *part_acc = nullptr, *part_ml = nullptr;   // split partials
+    bool kv_only = false;            // prepare: skip the q heads
+};
+int qb_attn_prepare(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t n_seqs);
+// split partials, then merge + gate; out fp32 [rows][n_heads*hd] and/or int8 (q8 [rows][q_pitch], d [.][d_ld]).
+int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t n_seqs, float *out, int8_t *q8,
+                uint32_t q_pitch, float *d, uint32_t d_ld);
+size_t qb_attention_scratch_floats(uint32_t rows, uint32_t n_heads, uint32_t hd, uint32_t max_pos,
+                                   size_t *ml_floats);
+static const uint32_t QB_ATTN_SPLIT = 256;   // keys per split, fixed absolute boundaries
+
+struct DnArgs {
+    const float *proj = nullptr; uint32_t proj_stride = 0;   // rows [qkv | z | alpha | beta]
+    uint32_t n_seqs = 0, rows_per_seq = 0;                   // rows of sequence s: [s*rows_per_seq, ...)
+    const float *conv_w = nullptr, *ssm_a = nullptr, *dt_bias = nullptr, *norm_w = nullptr;
+    uint32_t nk = 0, nv = 0, hd = 0; float eps = 0.f;
+    float *state = nullptr, *conv = nullptr;                 // [n_seqs][n_slots][...]
+    uint32_t n_slots = 0;
+    const int32_t *slot_in = nullptr;                        // [n_seqs] device
+    int write_all = 0;
+    float *xconv = nullptr;                                  // scratch [rows][qkv_dim]
+    float *core = nullptr;                                   // scratch/out [rows][nv*hd]
+    int8_t *q8 = nullptr; uint32_t q_pitch = 0; float *d = nullptr; uint32_t d_ld = 0;   // quantised gated core
+    float *core_out = nullptr;                               // optional fp32 gated core
+};
+int qb_launch_deltanet(qb_ctx *ctx, const DnArgs &a);
