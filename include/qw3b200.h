@@ -247,7 +247,8 @@ int qb_batch_stats(qb_ctx *ctx, qb_batch *b, int64_t *out4);
 int qb_seq_position(qb_ctx *ctx, qb_batch *b, uint32_t seq, int32_t *pos);
 /* Test aids: logits of the last verify/greedy/prefill rows (float [rows][vocab]) and hidden rows. */
 int qb_debug_last_logits(qb_ctx *ctx, qb_batch *b, float *host_out, uint32_t max_rows, uint32_t *rows_out);
-int qb_debug_set_keep_logits(qb_ctx *ctx, qb_batch *b, int keep);
+/* Drafts of the last qb_mtp_draft / qb_mtp_force_drafts: int32 [n_seqs][k] (test aid, syncs). */
+int qb_debug_last_drafts(qb_ctx *ctx, qb_batch *b, int32_t *host_out);
 /* Number of kernels this library launched on the context since creation. */
 int64_t qb_launch_count(qb_ctx *ctx);
 

@@ -84,6 +84,7 @@ SIGNATURES = {
     "qb_batch_stats": (i32, [vp, vp, vp]),
     "qb_seq_position": (i32, [vp, vp, u32, C.POINTER(C.c_int32)]),
     "qb_debug_last_logits": (i32, [vp, vp, vp, u32, C.POINTER(u32)]),
+    "qb_debug_last_drafts": (i32, [vp, vp, vp]),
     "qb_launch_count": (C.c_int64, [vp]),
 }
 
@@ -125,6 +126,8 @@ class DeviceArray:
         p = vp()
         check(lib().qb_malloc(ctx.h, max(self.nbytes, 16), C.byref(p)))
         self.ptr = p
+        ctx._arrays.append(self)   # the context keeps the buffer alive: kernels that were handed
+                                   # `.ptr` may still be queued when the Python object is dropped
 
     @classmethod
     def from_host(cls, ctx, arr):
@@ -150,12 +153,10 @@ class DeviceArray:
         if self.ptr:
             lib().qb_free(self.ctx.h, self.ptr)
             self.ptr = None
-
-    def __del__(self):
-        try:
-            self.free()
-        except Exception:
-            pass
+            try:
+                self.ctx._arrays.remove(self)
+            except ValueError:
+                pass
 
 
 class Context:
@@ -164,9 +165,16 @@ class Context:
         check(lib().qb_create(device, C.byref(h)))
         self.h = h
         self.device = device
+        self._arrays = []
+
+    def release_arrays(self):
+        """Frees every DeviceArray created through this context."""
+        for a in list(self._arrays):
+            a.free()
 
     def close(self):
         if self.h:
+            self.release_arrays()
             lib().qb_destroy(self.h)
             self.h = None
 
@@ -345,6 +353,11 @@ class Batch:
         p = C.c_int32()
         check(lib().qb_seq_position(self.ctx.h, self.h, seq, C.byref(p)))
         return p.value
+
+    def last_drafts(self):
+        out = np.zeros((self.n_seqs, self.k), np.int32)
+        check(lib().qb_debug_last_drafts(self.ctx.h, self.h, _np_ptr(out)))
+        return out
 
     def last_logits(self, max_rows):
         V = self.model.cfg.vocab_size

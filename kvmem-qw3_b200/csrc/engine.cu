@@ -245,7 +245,7 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
     }
     // control block
     {
-        const size_t n = (size_t)n_seqs * (8 + 3 * K1) + 3 * rows + n_seqs * (size_t)std::max(1u, draft_k) * 2 + 64;
+        const size_t n = (size_t)n_seqs * (16 + 4 * K1) + 4 * (size_t)rows + 256;
         QB_CUDA(cudaMalloc(&b->ctl, n * sizeof(int32_t)));
         QB_CUDA(cudaMemsetAsync(b->ctl, 0, n * sizeof(int32_t), ctx->stream));
         int32_t *p = b->ctl;
@@ -283,9 +283,12 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
     QB_CUDA(cudaMalloc(&b->am_idx, (size_t)b->logit_rows * QB_ARGMAX_BLOCKS * sizeof(int32_t)));
     {
         size_t per_row = 0;   // floats of split partials any GEMM of the model can need per row
-        auto consider = [&](uint32_t N, uint32_t K) { const uint32_t S = qb_ksplit(N, K); if (S > 1) per_row = std::max(per_row, (size_t)S * N); };
-        consider(m->attn_in(), H); consider(m->dn_in(), H); consider(H, inner); consider(H, vdim);
-        consider(2 * F, H); consider(H, F); consider(V, H); consider(H, 2 * H);
+        auto consider = [&](uint32_t N, uint32_t K, bool always) {
+            const uint32_t S = qb_ksplit(N, K);
+            if (S > 1 || always) per_row = std::max(per_row, (size_t)S * N);
+        };
+        consider(m->attn_in(), H, false); consider(m->dn_in(), H, false); consider(2 * F, H, false); consider(V, H, false);
+        consider(H, inner, true); consider(H, vdim, true); consider(H, F, true); consider(H, 2 * H, true);
         b->parts_floats = std::max<size_t>(per_row, 1) * rows;
         QB_CUDA(cudaMalloc(&b->parts, b->parts_floats * sizeof(float)));
     }
@@ -782,4 +785,9 @@ extern "C" int qb_debug_last_logits(qb_ctx *ctx, qb_batch *b, float *host_out, u
     if (rows_out) *rows_out = r;
     return QB_OK;
 }
-extern "C" int qb_debug_set_keep_logits(qb_ctx *, qb_batch *, int) { return QB_OK; }
+extern "C" int qb_debug_last_drafts(qb_ctx *ctx, qb_batch *b, int32_t *host_out) {
+    QB_REQUIRE(ctx && b && host_out && b->k > 0, "qb_debug_last_drafts: bad arguments");
+    QB_CUDA(cudaMemcpyAsync(host_out, b->drafts, (size_t)b->n_seqs * b->k * sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return QB_OK;
+}

@@ -267,6 +267,9 @@ class Seq:
     def cur_token(self):
         return int(lib().orc_seq_cur_token(self.h))
 
+    def set_cur_token(self, tok):
+        lib().orc_seq_set_cur_token(self.h, C.c_int(int(tok)))
+
     def prefill(self, tokens, chunk=0):
         t = np.ascontiguousarray(tokens, np.int32)
         lib().orc_prefill(self.h, _p(t), C.c_uint32(len(t)), C.c_uint32(chunk))

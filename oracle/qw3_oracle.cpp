@@ -824,6 +824,7 @@ void *orc_seq_create(void *mp, uint32_t max_ctx) {
 void orc_seq_destroy(void *sp) { delete (Seq *)sp; }
 int orc_seq_position(void *sp) { return ((Seq *)sp)->pos; }
 int orc_seq_cur_token(void *sp) { return ((Seq *)sp)->cur_tok; }
+void orc_seq_set_cur_token(void *sp, int tok) { ((Seq *)sp)->cur_tok = tok; }
 
 // Prompt ingestion (generate_mtp prefill loop src/qwen_native_backend.cpp:12772-12821 +
 // prime_mtp_prefix src/qwen_executor.cpp:22543-22815): chunked target forward, MTP K/V for

@@ -32,6 +32,15 @@ def ctx(qb):
     c.close()
 
 
+@pytest.fixture(autouse=True)
+def _release_device_arrays(request):
+    yield
+    if "ctx" in request.fixturenames:
+        c = request.getfixturevalue("ctx")
+        c.sync()
+        c.release_arrays()
+
+
 @pytest.fixture(scope="session")
 def ref():
     """The reference's own CUDA kernels (oracle/_ref/libqw3ref.so), or None if not built."""
