@@ -227,6 +227,10 @@ int qb_mtp_draft(qb_ctx *ctx, qb_batch *b);
  * absolute position. */
 int qb_mtp_force_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *stream_dev, uint32_t stream_stride,
                         float rate, uint64_t seed);
+/* Drafts supplied by the host (int32 [n_seqs][k], pinned memory for an asynchronous copy): the
+ * host-driven form of the reference loop, where the host holds the chain it verifies
+ * (src/qwen_native_backend.cpp:15903). */
+int qb_mtp_set_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *drafts_host);
 /* forward_n_tokens verify branch (src/qwen_executor.cpp:6003-6836): (k+1)-row target forward per
  * sequence with per-row DeltaNet/conv state checkpoints and per-row argmax. */
 int qb_mtp_verify(qb_ctx *ctx, qb_batch *b);
@@ -249,6 +253,11 @@ int qb_seq_position(qb_ctx *ctx, qb_batch *b, uint32_t seq, int32_t *pos);
 int qb_debug_last_logits(qb_ctx *ctx, qb_batch *b, float *host_out, uint32_t max_rows, uint32_t *rows_out);
 /* Drafts of the last qb_mtp_draft / qb_mtp_force_drafts: int32 [n_seqs][k] (test aid, syncs). */
 int qb_debug_last_drafts(qb_ctx *ctx, qb_batch *b, int32_t *host_out);
+/* Per-launch CUDA-event timing of the Q8 GEMM kernels on the context stream (the reference's
+ * per-op timing, src/qwen_executor.cpp:1788-1804, without its synchronise-per-op): enable, run,
+ * then read the summed duration, the summed algorithmic bytes and the number of launches. */
+int qb_prof_enable(qb_ctx *ctx, int on);
+int qb_prof_summary(qb_ctx *ctx, double *total_ms, double *total_bytes, int64_t *launches);
 /* Number of kernels this library launched on the context since creation. */
 int64_t qb_launch_count(qb_ctx *ctx);
 

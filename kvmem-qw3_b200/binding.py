@@ -77,6 +77,7 @@ SIGNATURES = {
     "qb_decode_greedy_step": (i32, [vp, vp]),
     "qb_mtp_draft": (i32, [vp, vp]),
     "qb_mtp_force_drafts": (i32, [vp, vp, vp, u32, f32, u64]),
+    "qb_mtp_set_drafts": (i32, [vp, vp, vp]),
     "qb_mtp_verify": (i32, [vp, vp]),
     "qb_mtp_accept_commit": (i32, [vp, vp]),
     "qb_mtp_step": (i32, [vp, vp]),
@@ -85,6 +86,8 @@ SIGNATURES = {
     "qb_seq_position": (i32, [vp, vp, u32, C.POINTER(C.c_int32)]),
     "qb_debug_last_logits": (i32, [vp, vp, vp, u32, C.POINTER(u32)]),
     "qb_debug_last_drafts": (i32, [vp, vp, vp]),
+    "qb_prof_enable": (i32, [vp, i32]),
+    "qb_prof_summary": (i32, [vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
     "qb_launch_count": (C.c_int64, [vp]),
 }
 
@@ -204,6 +207,24 @@ class Context:
         ms = f32()
         check(lib().qb_event_elapsed_ms(self.h, a, b, C.byref(ms)))
         return ms.value
+
+    def prof_enable(self, on=True):
+        check(lib().qb_prof_enable(self.h, 1 if on else 0))
+
+    def prof_summary(self):
+        ms, by, n = C.c_double(), C.c_double(), C.c_int64()
+        check(lib().qb_prof_summary(self.h, C.byref(ms), C.byref(by), C.byref(n)))
+        return dict(ms=ms.value, bytes=by.value, launches=n.value)
+
+    def pinned(self, shape, dtype):
+        """Pinned host array (numpy view over cudaHostAlloc memory)."""
+        dt = np.dtype(dtype)
+        n = int(np.prod(shape)) * dt.itemsize
+        p = vp()
+        check(lib().qb_host_alloc(self.h, max(n, 16), C.byref(p)))
+        buf = (C.c_char * n).from_address(p.value)
+        arr = np.frombuffer(buf, dtype=dt).reshape(shape)
+        return arr
 
     def array(self, arr):
         return DeviceArray.from_host(self, arr)
@@ -329,6 +350,10 @@ class Batch:
 
     def mtp_force_drafts(self, stream_dev, stride, rate, seed):
         check(lib().qb_mtp_force_drafts(self.ctx.h, self.h, stream_dev.ptr, stride, rate, seed))
+
+    def mtp_set_drafts(self, drafts_host):
+        """drafts_host: int32 numpy array [n_seqs][k] (pinned for an asynchronous copy)."""
+        check(lib().qb_mtp_set_drafts(self.ctx.h, self.h, _np_ptr(drafts_host)))
 
     def mtp_verify(self):
         check(lib().qb_mtp_verify(self.ctx.h, self.h))

@@ -717,6 +717,12 @@ extern "C" int qb_mtp_force_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *stre
     return QB_OK;
 }
 
+extern "C" int qb_mtp_set_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *drafts_host) {
+    QB_REQUIRE(ctx && b && drafts_host && b->k > 0, "qb_mtp_set_drafts: bad arguments");
+    QB_CUDA(cudaMemcpyAsync(b->drafts, drafts_host, (size_t)b->n_seqs * b->k * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+    return QB_OK;
+}
+
 extern "C" int qb_mtp_verify(qb_ctx *ctx, qb_batch *b) {
     QB_REQUIRE(ctx && b && b->k > 0, "qb_mtp_verify: needs a batch with draft depth > 0");
     QB_TRY(check_room(b, b->k + 1));

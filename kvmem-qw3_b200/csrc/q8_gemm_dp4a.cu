@@ -188,14 +188,66 @@ int qb_launch_gemm_dp4a(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const 
     return launch<4>(ctx, w, q, d, M, part, S);
 }
 
+static int gemm_dispatch(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
+                         uint32_t S, int impl);
+
+// Algorithmic bytes of one launch: the Q8_0 weight once (34 B per 32 weights), the quantised
+// activations (int8 + one fp32 scale per 32) and the fp32 partial sums written.
+static double gemm_bytes(const qb_weight *w, uint32_t M, uint32_t S) {
+    return (double)w->rows * w->cols / 32.0 * 34.0 + (double)M * w->cols * 1.125 + (double)S * M * w->rows * 4.0;
+}
+
 int qb_launch_gemm(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
                    uint32_t S, int impl) {
+    if (!ctx->prof_on) return gemm_dispatch(ctx, w, q, d, M, part, S, impl);
+    if (ctx->prof_used + 2 > ctx->prof_ev.size()) {
+        for (int i = 0; i < 256; ++i) {
+            cudaEvent_t e;
+            QB_CUDA(cudaEventCreate(&e));
+            ctx->prof_ev.push_back(e);
+        }
+    }
+    QB_CUDA(cudaEventRecord(ctx->prof_ev[ctx->prof_used], ctx->stream));
+    const int st = gemm_dispatch(ctx, w, q, d, M, part, S, impl);
+    QB_CUDA(cudaEventRecord(ctx->prof_ev[ctx->prof_used + 1], ctx->stream));
+    ctx->prof_used += 2;
+    ctx->prof_bytes.push_back(gemm_bytes(w, M, S));
+    return st;
+}
+
+extern "C" int qb_prof_enable(qb_ctx *ctx, int on) {
+    ctx->prof_on = on != 0;
+    ctx->prof_used = 0;
+    ctx->prof_bytes.clear();
+    return QB_OK;
+}
+
+extern "C" int qb_prof_summary(qb_ctx *ctx, double *total_ms, double *total_bytes, int64_t *launches) {
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    double ms = 0.0, bytes = 0.0;
+    for (size_t i = 0; i + 1 < ctx->prof_used; i += 2) {
+        float t = 0.0f;
+        QB_CUDA(cudaEventElapsedTime(&t, ctx->prof_ev[i], ctx->prof_ev[i + 1]));
+        ms += t;
+        bytes += ctx->prof_bytes[i / 2];
+    }
+    *total_ms = ms; *total_bytes = bytes; *launches = (int64_t)(ctx->prof_used / 2);
+    return QB_OK;
+}
+
+static int gemm_dispatch(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
+                         uint32_t S, int impl) {
     if (impl == 2) {
         if (!qb_gemm_tc_supported(w, M))
             return qb_fail(QB_ERR_UNSUPPORTED, "tensor-core GEMM does not support this shape");
         return qb_launch_gemm_tc(ctx, w, q, d, M, part, S);
     }
-    if (impl == 0 && qb_gemm_tc_supported(w, M)) return qb_launch_gemm_tc(ctx, w, q, d, M, part, S);
+    // automatic choice: the tensor-core kernel from QW3B200_TC_MIN_M activation rows upwards
+    static const uint32_t tc_min_m = []() {
+        const char *e = getenv("QW3B200_TC_MIN_M");
+        return (e && *e) ? (uint32_t)strtoul(e, nullptr, 10) : 0xFFFFFFFFu;
+    }();
+    if (impl == 0 && M >= tc_min_m && qb_gemm_tc_supported(w, M)) return qb_launch_gemm_tc(ctx, w, q, d, M, part, S);
     return qb_launch_gemm_dp4a(ctx, w, q, d, M, part, S);
 }
 

@@ -53,6 +53,11 @@ struct qb_ctx {
     void *flush_buf = nullptr;             // > L2 bytes, written by qb_flush_l2
     size_t flush_bytes = 0;
     int *err_flag_dev = nullptr;           // set by kernels whose bounded waits ran out
+    // optional per-launch timing of the GEMM kernels (qb_prof_*): event pairs + algorithmic bytes
+    bool prof_on = false;
+    std::vector<cudaEvent_t> prof_ev;      // pool, two per recorded launch
+    size_t prof_used = 0;
+    std::vector<double> prof_bytes;
     // scratch of the op-level entry points (grown on demand)
     void *scratch = nullptr;
     size_t scratch_bytes = 0;

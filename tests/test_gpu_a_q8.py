@@ -99,6 +99,21 @@ def test_gemm_bit_exact_vs_oracle(qb, orc, ctx, N, K, M, ksplit, impl):
     w.free()
 
 
+@pytest.mark.parametrize("N,K,M,ksplit", [(256, 512, 16, 0), (384, 1024, 33, 2), (128, 2048, 64, 1), (640, 512, 128, 0),
+                                          (256, 640, 130, 3), (130, 256, 300, 0), (5120, 5120, 12, 0)])
+def test_gemm_tensor_core_bit_exact_large_m(qb, orc, ctx, N, K, M, ksplit):
+    """tcgen05 kernel over every activation-tile width (16/32/64/128) and several tiles."""
+    rng = np.random.default_rng(N * 3 + K + M)
+    blocks = _w(orc, rng, N, K)
+    w = qb.Weight.from_blocks(ctx, blocks, N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    y = qb.binding.matmul(ctx, w, x, ksplit=ksplit, impl=2)
+    want = orc.matmul_engine(blocks, N, K, x, ksplit=ksplit)
+    assert np.array_equal(y, want), float(np.abs(y - want).max())
+    ctx.sync()    # also reads the kernel's bounded-wait error flag
+    w.free()
+
+
 def test_gemm_partials_layout(qb, orc, ctx):
     rng = np.random.default_rng(14)
     N, K, M, S = 256, 1024, 3, 4
