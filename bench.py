@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=64, help="target layers (64 = the 27B-class shape)")
     ap.add_argument("--prompt", type=int, default=PROMPT_LEN)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-greedy", action="store_true", help="profiling aid: no greedy reference run (forced drafts then never match)")
     return ap.parse_args()
 
 
@@ -172,7 +173,7 @@ def run_ours(args, rank, world, local_rank, dist):
     cfg = pkg.configs.qwen27b(args.layers)
     K, W, k = args.steps, args.warmup, K_DRAFT
     prof_steps = min(K, 8)
-    total_steps = 2 * W + 2 * K + prof_steps + 4
+    total_steps = 2 * W + 2 * K + prof_steps + 6
     n_greedy = 4 * total_steps + 8
     max_ctx = args.prompt + n_greedy + 16
     model = pkg.Model(ctx, cfg, pkg.configs.MODEL_SEED)
@@ -181,19 +182,22 @@ def run_ours(args, rank, world, local_rank, dist):
     prompt = rs.randint(0, cfg.vocab_size, args.prompt).astype(np.int32)
 
     # 1. the non-speculative greedy continuation (also the losslessness reference of this run)
-    g = pkg.Batch(model, 1, max_ctx, 0)
-    g.prefill(0, prompt)
-    greedy = list(g.read_output()[0])
-    ctx.sync()
     ev = [ctx.event() for _ in range(8)]
-    ctx.record(ev[0])
-    for _ in range(n_greedy - 1):
-        g.greedy_step()
-        greedy += g.read_output()[0]
-    ctx.record(ev[1])
-    ctx.sync()
-    greedy_ms = ctx.elapsed_ms(ev[0], ev[1]) / (n_greedy - 1)
-    g.close()
+    if args.skip_greedy:
+        greedy, greedy_ms = [0] * n_greedy, float("nan")
+    else:
+        g = pkg.Batch(model, 1, max_ctx, 0)
+        g.prefill(0, prompt)
+        greedy = list(g.read_output()[0])
+        ctx.sync()
+        ctx.record(ev[0])
+        for _ in range(n_greedy - 1):
+            g.greedy_step()
+            greedy += g.read_output()[0]
+        ctx.record(ev[1])
+        ctx.sync()
+        greedy_ms = ctx.elapsed_ms(ev[0], ev[1]) / (n_greedy - 1)
+        g.close()
     stream = np.zeros(args.prompt + len(greedy) + 8, np.int32)
     stream[:args.prompt] = prompt
     stream[args.prompt:args.prompt + len(greedy)] = greedy
@@ -246,6 +250,12 @@ def run_ours(args, rank, world, local_rank, dist):
         b.read_output()
     prof = ctx.prof_summary()
     ctx.prof_enable(False)
+    # one traced step: per-kernel time shares measured live (event after every launch)
+    ctx.trace_enable(True)
+    device_step()
+    trace = ctx.trace_summary()
+    ctx.trace_enable(False)
+    b.read_output()
 
     # 4. end to end through the host-driven API: drafts come from pinned host memory every step and the
     #    step record goes back to the host every step
@@ -313,6 +323,8 @@ def run_ours(args, rank, world, local_rank, dist):
                  "weight_bytes_per_step": step_bytes + 3 * 1.28e9 * 0,
                  "step_hbm_frac": (step_bytes / 1e9) / ((agg[0] / K) * 1e-3) / peak if world == 1 else None},
     }
+    ttot = sum(t for _, _, t in trace) or 1.0
+    line["step"]["kernel_shares"] = {n: {"launches": c, "us": round(t, 1), "share": round(t / ttot, 4)} for n, c, t in trace}
     if O is not None:
         models, seqs = cpu_setup(O, pkg)
         cpu_step_sample(O, models, seqs)

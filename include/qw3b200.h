@@ -258,6 +258,11 @@ int qb_debug_last_drafts(qb_ctx *ctx, qb_batch *b, int32_t *host_out);
  * then read the summed duration, the summed algorithmic bytes and the number of launches. */
 int qb_prof_enable(qb_ctx *ctx, int on);
 int qb_prof_summary(qb_ctx *ctx, double *total_ms, double *total_bytes, int64_t *launches);
+/* Launch trace: while enabled an event is recorded after every kernel launch of the library; the
+ * summary gives, per kernel name, the number of launches and the summed time between its event and
+ * the preceding one, as "name<TAB>launches<TAB>microseconds" lines. */
+int qb_trace_enable(qb_ctx *ctx, int on);
+int qb_trace_summary(qb_ctx *ctx, char *buf, size_t buf_bytes);
 /* Number of kernels this library launched on the context since creation. */
 int64_t qb_launch_count(qb_ctx *ctx);
 

@@ -88,6 +88,8 @@ SIGNATURES = {
     "qb_debug_last_drafts": (i32, [vp, vp, vp]),
     "qb_prof_enable": (i32, [vp, i32]),
     "qb_prof_summary": (i32, [vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
+    "qb_trace_enable": (i32, [vp, i32]),
+    "qb_trace_summary": (i32, [vp, C.c_char_p, sz]),
     "qb_launch_count": (C.c_int64, [vp]),
 }
 
@@ -215,6 +217,19 @@ class Context:
         ms, by, n = C.c_double(), C.c_double(), C.c_int64()
         check(lib().qb_prof_summary(self.h, C.byref(ms), C.byref(by), C.byref(n)))
         return dict(ms=ms.value, bytes=by.value, launches=n.value)
+
+    def trace_enable(self, on=True):
+        check(lib().qb_trace_enable(self.h, 1 if on else 0))
+
+    def trace_summary(self):
+        """[(kernel name, launches, total microseconds)] since trace_enable(True)."""
+        buf = C.create_string_buffer(1 << 16)
+        check(lib().qb_trace_summary(self.h, buf, len(buf)))
+        out = []
+        for ln in buf.value.decode().splitlines():
+            n, c, t = ln.split("\t")
+            out.append((n, int(c), float(t)))
+        return out
 
     def pinned(self, shape, dtype):
         """Pinned host array (numpy view over cudaHostAlloc memory)."""

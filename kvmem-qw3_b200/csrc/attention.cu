@@ -42,6 +42,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ---- per-head RMSNorm + partial RoPE + paged K/V append --------------------------------------
 // grid (rows, units): units = q heads, then k heads, then v heads.  blockDim = head_dim.
 __global__ void qk_norm_rope_append_kernel(AttnArgs a, const int32_t *__restrict__ seq_pos, uint32_t R, uint32_t unit0) {
+    QB_PDL_ENTER();
     extern __shared__ float buf[];
     __shared__ float red[8];
     const uint32_t row = blockIdx.x, unit = blockIdx.y + unit0, i = threadIdx.x, hd = a.hd;
@@ -97,6 +98,7 @@ struct AttSmem {
 template <int HD, int QPW>
 __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, const int32_t *__restrict__ seq_pos, uint32_t R,
                                                                  uint32_t max_splits) {
+    QB_PDL_ENTER();
     using L = AttSmem<HD>;
     extern __shared__ __align__(16) uint8_t smem[];
     float *Qs = reinterpret_cast<float *>(smem + 2 * L::STAGE);
@@ -263,17 +265,40 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, con
 // grid (rows, n_heads), blockDim = HD.
 __global__ void attn_merge_kernel(AttnArgs a, const int32_t *__restrict__ seq_pos, uint32_t R, uint32_t max_splits,
                                   float *out, int8_t *q8, uint32_t q_pitch, float *dsc, uint32_t d_ld) {
+    QB_PDL_ENTER();
+    __shared__ float wsplit[256];
+    __shared__ float red_m[8];
     const uint32_t row = blockIdx.x, head = blockIdx.y, i = threadIdx.x, hd = a.hd, lane = i & 31;
     const int pos = seq_pos[row / R] + (int)(row % R);
     const uint32_t nsplit = ((uint32_t)pos + QB_ATTN_SPLIT) / QB_ATTN_SPLIT;
     const size_t p0 = ((size_t)row * a.n_heads + head) * max_splits;
+    // block-wide maximum of the split maxima (all loads in flight together)
     float mx = -INFINITY;
-    for (uint32_t s = 0; s < nsplit; ++s) mx = fmaxf(mx, a.part_ml[(p0 + s) * 2]);
+    for (uint32_t s = i; s < nsplit; s += hd) mx = fmaxf(mx, a.part_ml[(p0 + s) * 2]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red_m[i >> 5] = mx;
+    __syncthreads();
+    mx = red_m[0];
+    for (uint32_t k = 1; k < hd / 32; ++k) mx = fmaxf(mx, red_m[k]);
+    // splits in ascending order, 256 at a time: weights computed in parallel, then every thread walks them
     float num = 0.0f, den = 0.0f;
-    for (uint32_t s = 0; s < nsplit; ++s) {
-        const float wgt = expf(a.part_ml[(p0 + s) * 2] - mx);
-        num = fmaf(a.part_acc[(p0 + s) * hd + i], wgt, num);
-        den = fmaf(a.part_ml[(p0 + s) * 2 + 1], wgt, den);
+    for (uint32_t s0 = 0; s0 < nsplit; s0 += 256) {
+        const uint32_t cnt = min(256u, nsplit - s0);
+        __syncthreads();
+        for (uint32_t s = i; s < cnt; s += hd) wsplit[s] = expf(a.part_ml[(p0 + s0 + s) * 2] - mx);
+        __syncthreads();
+        const float *acc = a.part_acc + (p0 + s0) * hd + i;
+        const float *ml = a.part_ml + (p0 + s0) * 2 + 1;
+        uint32_t s = 0;
+        for (; s + 8 <= cnt; s += 8) {
+            float va[8], vl[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { va[u] = acc[(size_t)(s + u) * hd]; vl[u] = ml[(s + u) * 2]; }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { num = fmaf(va[u], wsplit[s + u], num); den = fmaf(vl[u], wsplit[s + u], den); }
+        }
+        for (; s < cnt; ++s) { num = fmaf(acc[(size_t)s * hd], wsplit[s], num); den = fmaf(ml[s * 2], wsplit[s], den); }
     }
     const float gate = a.qkv[(size_t)row * a.row_stride + (size_t)head * 2 * hd + hd + i];
     const float o = __fdiv_rn(num, den) * __fdiv_rn(1.0f, 1.0f + expf(-gate));
@@ -298,7 +323,7 @@ int launch_split(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_
         attr = true;
     }
     dim3 grid(max_splits, a.n_kv, n_seqs * ((R + QR - 1) / QR));
-    attn_split_kernel<HD, QPW><<<grid, ATT_THREADS, L::TOTAL, ctx->stream>>>(a, seq_pos, R, max_splits);
+    QB_CUDA(qb_launch_pdl(ctx->stream, attn_split_kernel<HD, QPW>, dim3(grid), dim3(ATT_THREADS), (size_t)(L::TOTAL), a, seq_pos, R, max_splits));
     QB_LAUNCHED(ctx, "attn_split_kernel");
     return QB_OK;
 }
@@ -320,7 +345,7 @@ int qb_attn_prepare(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint
     const uint32_t R = a.rows / n_seqs;
     const uint32_t unit0 = a.kv_only ? a.n_heads : 0;
     dim3 grid(a.rows, a.n_heads + 2 * a.n_kv - unit0);
-    qk_norm_rope_append_kernel<<<grid, a.hd, a.hd * sizeof(float), ctx->stream>>>(a, seq_pos, R, unit0);
+    QB_CUDA(qb_launch_pdl(ctx->stream, qk_norm_rope_append_kernel, dim3(grid), dim3(a.hd), (size_t)(a.hd * sizeof(float)), a, seq_pos, R, unit0));
     QB_LAUNCHED(ctx, "qk_norm_rope_append_kernel");
     return QB_OK;
 }
@@ -343,7 +368,7 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
 #undef QB_ATT_CASE
     QB_TRY(st);
     dim3 grid(a.rows, a.n_heads);
-    attn_merge_kernel<<<grid, a.hd, 0, ctx->stream>>>(a, seq_pos, R, ms, out, q8, q_pitch, d, d_ld);
+    QB_CUDA(qb_launch_pdl(ctx->stream, attn_merge_kernel, dim3(grid), dim3(a.hd), (size_t)(0), a, seq_pos, R, ms, out, q8, q_pitch, d, d_ld));
     QB_LAUNCHED(ctx, "attn_merge_kernel");
     return QB_OK;
 }

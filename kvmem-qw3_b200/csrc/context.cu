@@ -181,3 +181,52 @@ int qb_make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, uint32_t elem_byte
     (void)elem_bytes;
     return QB_OK;
 }
+
+// ---- launch trace: an event after every kernel launch; the time between consecutive events is the
+// duration of the kernel launched in between (kernels of one stream run back to back) ----------------
+void qb_trace_mark(qb_ctx *ctx, const char *name) {
+    if (ctx->trace_used >= ctx->trace_ev.size()) {
+        for (int i = 0; i < 1024; ++i) {
+            cudaEvent_t e;
+            if (cudaEventCreate(&e) != cudaSuccess) return;
+            ctx->trace_ev.push_back(e);
+        }
+    }
+    cudaEventRecord(ctx->trace_ev[ctx->trace_used++], ctx->stream);
+    ctx->trace_names.push_back(name);
+}
+
+extern "C" int qb_trace_enable(qb_ctx *ctx, int on) {
+    ctx->trace_on = false;
+    ctx->trace_used = 0;
+    ctx->trace_names.clear();
+    if (on) {
+        qb_trace_mark(ctx, "(start)");
+        ctx->trace_on = true;
+    }
+    return QB_OK;
+}
+
+// Writes "name\tlaunches\ttotal_us" lines (sorted by launch order of first appearance) into buf.
+extern "C" int qb_trace_summary(qb_ctx *ctx, char *buf, size_t buf_bytes) {
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    std::vector<std::pair<const char *, std::pair<long, double>>> agg;
+    for (size_t i = 1; i < ctx->trace_used; ++i) {
+        float ms = 0.0f;
+        QB_CUDA(cudaEventElapsedTime(&ms, ctx->trace_ev[i - 1], ctx->trace_ev[i]));
+        const char *n = ctx->trace_names[i];
+        size_t k = 0;
+        for (; k < agg.size(); ++k) if (strcmp(agg[k].first, n) == 0) break;
+        if (k == agg.size()) agg.push_back({n, {0, 0.0}});
+        agg[k].second.first += 1;
+        agg[k].second.second += ms * 1e3;
+    }
+    size_t off = 0;
+    for (auto &a : agg) {
+        int w = snprintf(buf + off, off < buf_bytes ? buf_bytes - off : 0, "%s\t%ld\t%.2f\n", a.first, a.second.first, a.second.second);
+        if (w < 0 || off + (size_t)w >= buf_bytes) break;
+        off += (size_t)w;
+    }
+    if (buf_bytes) buf[std::min(off, buf_bytes - 1)] = 0;
+    return QB_OK;
+}

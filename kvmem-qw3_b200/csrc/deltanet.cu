@@ -23,6 +23,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 // grid (qkv_dim / HD, n_seqs), block HD: one head-sized chunk of channels, all rows of a sequence.
 template <int HD>
 __global__ void __launch_bounds__(HD) dn_conv_kernel(DnArgs a) {
+    QB_PDL_ENTER();
     __shared__ float red[HD / 32];
     const uint32_t chunk = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
     const uint32_t C = 2 * a.nk * HD + a.nv * HD, R = a.rows_per_seq;
@@ -68,6 +69,7 @@ __global__ void __launch_bounds__(HD) dn_conv_kernel(DnArgs a) {
 // grid (nv, HD / 8, n_seqs), block 128: each warp owns 2 state columns, lanes stripe the k-dim.
 template <int HD>
 __global__ void __launch_bounds__(128) dn_delta_kernel(DnArgs a) {
+    QB_PDL_ENTER();
     constexpr int RPL = HD / 32, CPW = 2;
     const uint32_t vh = blockIdx.x, seq = blockIdx.z, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t col0 = blockIdx.y * 8 + warp * CPW;
@@ -130,6 +132,7 @@ __global__ void __launch_bounds__(128) dn_delta_kernel(DnArgs a) {
 // grid (rows, nv), block HD.
 template <int HD>
 __global__ void __launch_bounds__(HD) dn_normgate_kernel(DnArgs a) {
+    QB_PDL_ENTER();
     __shared__ float red[HD / 32];
     const uint32_t row = blockIdx.x, vh = blockIdx.y, i = threadIdx.x, lane = i & 31;
     const uint32_t C = 2 * a.nk * HD + a.nv * HD, vdim = a.nv * HD;
@@ -157,11 +160,11 @@ __global__ void __launch_bounds__(HD) dn_normgate_kernel(DnArgs a) {
 template <int HD>
 int launch_all(qb_ctx *ctx, const DnArgs &a) {
     const uint32_t C = 2 * a.nk * HD + a.nv * HD;
-    dn_conv_kernel<HD><<<dim3(C / HD, a.n_seqs), HD, 0, ctx->stream>>>(a);
+    QB_CUDA(qb_launch_pdl(ctx->stream, dn_conv_kernel<HD>, dim3(dim3(C / HD, a.n_seqs)), dim3(HD), (size_t)(0), a));
     QB_LAUNCHED(ctx, "dn_conv_kernel");
-    dn_delta_kernel<HD><<<dim3(a.nv, HD / 8, a.n_seqs), 128, 0, ctx->stream>>>(a);
+    QB_CUDA(qb_launch_pdl(ctx->stream, dn_delta_kernel<HD>, dim3(dim3(a.nv, HD / 8, a.n_seqs)), dim3(128), (size_t)(0), a));
     QB_LAUNCHED(ctx, "dn_delta_kernel");
-    dn_normgate_kernel<HD><<<dim3(a.n_seqs * a.rows_per_seq, a.nv), HD, 0, ctx->stream>>>(a);
+    QB_CUDA(qb_launch_pdl(ctx->stream, dn_normgate_kernel<HD>, dim3(dim3(a.n_seqs * a.rows_per_seq, a.nv)), dim3(HD), (size_t)(0), a));
     QB_LAUNCHED(ctx, "dn_normgate_kernel");
     return QB_OK;
 }

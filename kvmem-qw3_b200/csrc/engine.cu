@@ -345,6 +345,7 @@ __device__ int final_argmax(const float *pval, const int32_t *pidx, uint32_t row
 // tokens / positions of draft step i: token = i ? drafts[s][i-1] : cur[s], position = pos[s] + i
 __global__ void prep_draft_kernel(const int32_t *cur, const int32_t *drafts, const int32_t *pos, uint32_t n_seqs, uint32_t k,
                                   uint32_t i, int32_t *tok, int32_t *seqpos) {
+    QB_PDL_ENTER();
     const uint32_t s = blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= n_seqs) return;
     tok[s] = i == 0 ? cur[s] : drafts[(size_t)s * k + i - 1];
@@ -352,12 +353,14 @@ __global__ void prep_draft_kernel(const int32_t *cur, const int32_t *drafts, con
 }
 
 __global__ void store_draft_kernel(const float *pval, const int32_t *pidx, uint32_t n_seqs, uint32_t k, uint32_t i, int32_t *drafts) {
+    QB_PDL_ENTER();
     const uint32_t s = blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= n_seqs) return;
     drafts[(size_t)s * k + i] = final_argmax(pval, pidx, s);
 }
 
 __global__ void prep_verify_kernel(const int32_t *cur, const int32_t *drafts, uint32_t n_seqs, uint32_t k, int32_t *tok) {
+    QB_PDL_ENTER();
     const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_seqs * (k + 1)) return;
     const uint32_t s = idx / (k + 1), j = idx % (k + 1);
@@ -367,6 +370,7 @@ __global__ void prep_verify_kernel(const int32_t *cur, const int32_t *drafts, ui
 // Forced drafts: draft i of sequence s guesses the token at absolute position pos+1+i.
 __global__ void force_drafts_kernel(int32_t *drafts, const int32_t *pos, uint32_t n_seqs, uint32_t k, const int32_t *stream,
                                     uint32_t stream_stride, float rate, uint64_t seed, uint32_t vocab) {
+    QB_PDL_ENTER();
     const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_seqs * k) return;
     const uint32_t s = idx / k, i = idx % k;
@@ -384,6 +388,7 @@ __global__ void accept_commit_kernel(const float *pval, const int32_t *pidx, uin
                                      int32_t *pos, int32_t *sel, int32_t *cur, const int32_t *drafts, int32_t *prefix_pos,
                                      int32_t *prefix_tok, int32_t *out_rec, uint32_t n_seqs, float *hid,
                                      unsigned long long *stats) {
+    QB_PDL_ENTER();
     __shared__ int s_acc;
     const uint32_t s = blockIdx.x;
     const uint32_t K1 = k + 1;
@@ -421,6 +426,7 @@ __global__ void greedy_commit_kernel(const float *pval, const int32_t *pidx, uin
                                      uint32_t hid_row_stride, uint32_t seq0, uint32_t n, uint32_t K1, uint32_t rows_cap, uint32_t H,
                                      int32_t *pos, int32_t *sel, int32_t *cur, int32_t adv, int32_t *out_rec, uint32_t n_seqs,
                                      float *hid, unsigned long long *stats) {
+    QB_PDL_ENTER();
     const uint32_t j = blockIdx.x, s = seq0 + j;
     if (j >= n) return;
     if (threadIdx.x == 0) {
@@ -440,6 +446,7 @@ __global__ void greedy_commit_kernel(const float *pval, const int32_t *pidx, uin
 }
 
 __global__ void advance_kernel(int32_t *pos, int32_t *sel, uint32_t s, int32_t adv, uint32_t rows_cap, uint32_t H, uint32_t last_row, float *hid) {
+    QB_PDL_ENTER();
     if (threadIdx.x == 0) { pos[s] += adv; sel[s] = 0; }
     const float *src = hid + (size_t)last_row * H;
     float *dst = hid + (size_t)(rows_cap + s) * H;
@@ -650,12 +657,12 @@ extern "C" int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t 
             QB_TRY(mtp_forward(ctx, b, b->tok_buf, b->hid, b->map_chunk, rs, true));
         }
         if (last) {
-            greedy_commit_kernel<<<1, 256, 0, ctx->stream>>>(b->am_val, b->am_idx, 0, M - 1, 0, seq, 1, K1, b->rows_cap, c.n_embd,
+            QB_CUDA(qb_launch_pdl(ctx->stream, greedy_commit_kernel, dim3(1), dim3(256), (size_t)(0), b->am_val, b->am_idx, 0, M - 1, 0, seq, 1, K1, b->rows_cap, c.n_embd,
                                                            b->pos, b->sel, b->cur, (int32_t)M, b->out_rec, b->n_seqs, b->hid,
-                                                           (unsigned long long *)b->stats);
+                                                           (unsigned long long *)b->stats));
             QB_LAUNCHED(ctx, "greedy_commit_kernel");
         } else {
-            advance_kernel<<<1, 256, 0, ctx->stream>>>(b->pos, b->sel, seq, (int32_t)M, b->rows_cap, c.n_embd, M - 1, b->hid);
+            QB_CUDA(qb_launch_pdl(ctx->stream, advance_kernel, dim3(1), dim3(256), (size_t)(0), b->pos, b->sel, seq, (int32_t)M, b->rows_cap, c.n_embd, M - 1, b->hid));
             QB_LAUNCHED(ctx, "advance_kernel");
         }
         b->host_pos[seq] += (int32_t)M;
@@ -680,9 +687,9 @@ extern "C" int qb_decode_greedy_step(qb_ctx *ctx, qb_batch *b) {
     RowSet rs;
     rs.seq0 = 0; rs.ns = b->n_seqs; rs.R = 1; rs.seq_pos = b->pos; rs.max_pos = max_host_pos(b) + 1;
     QB_TRY(target_forward(ctx, b, b->cur, rs, false, 1));
-    greedy_commit_kernel<<<b->n_seqs, 256, 0, ctx->stream>>>(b->am_val, b->am_idx, 0, 0, 1, 0, b->n_seqs, b->k + 1, b->rows_cap,
+    QB_CUDA(qb_launch_pdl(ctx->stream, greedy_commit_kernel, dim3(b->n_seqs), dim3(256), (size_t)(0), b->am_val, b->am_idx, 0, 0, 1, 0, b->n_seqs, b->k + 1, b->rows_cap,
                                                            c.n_embd, b->pos, b->sel, b->cur, 1, b->out_rec, b->n_seqs, b->hid,
-                                                           (unsigned long long *)b->stats);
+                                                           (unsigned long long *)b->stats));
     QB_LAUNCHED(ctx, "greedy_commit_kernel");
     for (auto &p : b->host_pos) p += 1;
     return QB_OK;
@@ -694,14 +701,14 @@ extern "C" int qb_mtp_draft(qb_ctx *ctx, qb_batch *b) {
     QB_CUDA(cudaSetDevice(ctx->device));
     const uint32_t ns = b->n_seqs, k = b->k;
     for (uint32_t i = 0; i < k; ++i) {
-        prep_draft_kernel<<<(ns + 127) / 128, 128, 0, ctx->stream>>>(b->cur, b->drafts, b->pos, ns, k, i, b->tok_buf, b->seqpos_buf);
+        QB_CUDA(qb_launch_pdl(ctx->stream, prep_draft_kernel, dim3((ns + 127) / 128), dim3(128), (size_t)(0), b->cur, b->drafts, b->pos, ns, k, i, b->tok_buf, b->seqpos_buf));
         QB_LAUNCHED(ctx, "prep_draft_kernel");
         RowSet rs;
         rs.seq0 = 0; rs.ns = ns; rs.R = 1; rs.seq_pos = b->seqpos_buf; rs.max_pos = max_host_pos(b) + i + 1;
         // step 0 reads the target hidden of the last committed position, later steps the MTP hidden
         if (i == 0) QB_TRY(mtp_forward(ctx, b, b->tok_buf, b->hid, b->map_prevh, rs, false));
         else QB_TRY(mtp_forward(ctx, b, b->tok_buf, b->mtp_h, nullptr, rs, false));
-        store_draft_kernel<<<(ns + 127) / 128, 128, 0, ctx->stream>>>(b->am_val, b->am_idx, ns, k, i, b->drafts);
+        QB_CUDA(qb_launch_pdl(ctx->stream, store_draft_kernel, dim3((ns + 127) / 128), dim3(128), (size_t)(0), b->am_val, b->am_idx, ns, k, i, b->drafts));
         QB_LAUNCHED(ctx, "store_draft_kernel");
     }
     return QB_OK;
@@ -711,8 +718,8 @@ extern "C" int qb_mtp_force_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *stre
                                    uint64_t seed) {
     QB_REQUIRE(ctx && b && stream_dev && b->k > 0, "qb_mtp_force_drafts: bad arguments");
     const uint32_t n = b->n_seqs * b->k;
-    force_drafts_kernel<<<(n + 127) / 128, 128, 0, ctx->stream>>>(b->drafts, b->pos, b->n_seqs, b->k, stream_dev, stream_stride, rate,
-                                                                 seed, b->m->cfg.vocab_size);
+    QB_CUDA(qb_launch_pdl(ctx->stream, force_drafts_kernel, dim3((n + 127) / 128), dim3(128), (size_t)(0), b->drafts, b->pos, b->n_seqs, b->k, stream_dev, stream_stride, rate,
+                                                                 seed, b->m->cfg.vocab_size));
     QB_LAUNCHED(ctx, "force_drafts_kernel");
     return QB_OK;
 }
@@ -728,7 +735,7 @@ extern "C" int qb_mtp_verify(qb_ctx *ctx, qb_batch *b) {
     QB_TRY(check_room(b, b->k + 1));
     QB_CUDA(cudaSetDevice(ctx->device));
     const uint32_t ns = b->n_seqs, K1 = b->k + 1;
-    prep_verify_kernel<<<(ns * K1 + 127) / 128, 128, 0, ctx->stream>>>(b->cur, b->drafts, ns, b->k, b->tok_buf);
+    QB_CUDA(qb_launch_pdl(ctx->stream, prep_verify_kernel, dim3((ns * K1 + 127) / 128), dim3(128), (size_t)(0), b->cur, b->drafts, ns, b->k, b->tok_buf));
     QB_LAUNCHED(ctx, "prep_verify_kernel");
     RowSet rs;
     rs.seq0 = 0; rs.ns = ns; rs.R = K1; rs.seq_pos = b->pos; rs.max_pos = max_host_pos(b) + K1;
@@ -740,9 +747,9 @@ extern "C" int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b) {
     QB_CUDA(cudaSetDevice(ctx->device));
     const qb_model_config &c = b->m->cfg;
     const uint32_t ns = b->n_seqs, k = b->k;
-    accept_commit_kernel<<<ns, 256, 0, ctx->stream>>>(b->am_val, b->am_idx, k, b->rows_cap, c.n_embd, b->pos, b->sel, b->cur, b->drafts,
+    QB_CUDA(qb_launch_pdl(ctx->stream, accept_commit_kernel, dim3(ns), dim3(256), (size_t)(0), b->am_val, b->am_idx, k, b->rows_cap, c.n_embd, b->pos, b->sel, b->cur, b->drafts,
                                                     b->prefix_pos, b->prefix_tok, b->out_rec, ns, b->hid,
-                                                    (unsigned long long *)b->stats);
+                                                    (unsigned long long *)b->stats));
     QB_LAUNCHED(ctx, "accept_commit_kernel");
     // MTP-layer K/V of positions old_pos+1 .. old_pos+k from (draft_i, target hidden of row i-1); the
     // rows beyond the accepted prefix land past the committed length and are overwritten later.

@@ -5,10 +5,11 @@
 // 32-block (dp4a), acc = fma(d_w*d_x, float(dot), acc) over the blocks of a K segment in ascending
 // order (the per-output update of src/mmq_q8.cu:1738-1748); one partial sum per segment.
 //
-// Data movement: a CTA owns 128 weight rows and one K segment.  Weight bytes arrive through a
-// 4-stage cp.async pipeline, 128 rows x 128 bytes per stage, stored with a 16-byte XOR swizzle so
-// that "one thread = one weight row" reads are bank-conflict free; activations of the pass are
-// staged beside them and read as warp broadcasts.
+// Data movement: a CTA owns 128 weight rows and one K segment.  Each stage of a 4-deep cp.async
+// pipeline copies one 17 KB weight record (128 rows x 128 bytes of quants, already in the 16-byte
+// XOR-swizzled order that makes "one thread = one weight row" reads bank-conflict free, followed by
+// its fp16 scales) as one contiguous read; activations of the pass are staged beside it and read as
+// warp broadcasts.
 #include "qb_internal.h"
 
 namespace {
@@ -42,10 +43,10 @@ struct Smem {
 };
 
 template <int MPT>
-__global__ void __launch_bounds__(THREADS) gemm_dp4a_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ wd,
-                                                            uint32_t ld, uint32_t K, uint32_t N,
+__global__ void __launch_bounds__(THREADS) gemm_dp4a_kernel(const uint8_t *__restrict__ rec, uint32_t K, uint32_t N,
                                                             const int8_t *__restrict__ xq, const float *__restrict__ xd,
                                                             uint32_t M, uint32_t xld, float *__restrict__ part, uint32_t S) {
+    QB_PDL_ENTER();
     using L = Smem<MPT>;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t tid = threadIdx.x;
@@ -59,17 +60,11 @@ __global__ void __launch_bounds__(THREADS) gemm_dp4a_kernel(const int8_t *__rest
     auto load_stage = [&](uint32_t it, uint32_t slot) {
         uint8_t *st = smem + (size_t)slot * L::STAGE;
         const uint32_t k0 = (c_begin + it) * CHUNK;
-#pragma unroll
-        for (int i = 0; i < (TILE_N * 8) / THREADS; ++i) {
-            const uint32_t c = tid + i * THREADS, r = c >> 3, p = c & 7;
-            cp_async16(st + r * CHUNK + ((p ^ (r & 7)) << 4), wq + (size_t)(row0 + r) * K + k0 + p * 16, true);
-        }
-        if (tid < 64) {
-            const uint32_t kb = tid >> 4, p = tid & 15;
-            cp_async16(st + L::WQ + kb * 256 + p * 16, wd + (size_t)(k0 / 32 + kb) * ld + row0 + p * 8, true);
-        }
-        if (tid >= 64 && tid < 64 + L::NC * 8) {
-            const uint32_t c = tid - 64, col = c >> 3, p = c & 7;
+        // the record of (row tile, chunk) is already the shared-memory image: a straight 17 KB copy
+        const uint8_t *src = rec + ((size_t)blockIdx.x * nchunks + c_begin + it) * QB_REC_BYTES;
+        for (uint32_t c = tid; c < QB_REC_BYTES / 16; c += THREADS) cp_async16(st + c * 16, src + c * 16, true);
+        if (tid < L::NC * 8) {
+            const uint32_t c = tid, col = c >> 3, p = c & 7;
             const bool valid = m0 + col < M;
             cp_async16(st + L::WQ + L::WD + col * CHUNK + p * 16, xq + (size_t)(valid ? m0 + col : 0) * K + k0 + p * 16, valid);
         }
@@ -143,23 +138,21 @@ int launch(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uin
         attr = true;
     }
     dim3 grid(w->rows_pad / TILE_N, S, (M + L::NC - 1) / L::NC);
-    gemm_dp4a_kernel<MPT><<<grid, THREADS, L::TOTAL, ctx->stream>>>(w->q, w->d, w->ld, w->cols, w->rows, q, d, M,
-                                                                   qb_act_ld(M), part, S);
+    QB_CUDA(qb_launch_pdl(ctx->stream, gemm_dp4a_kernel<MPT>, dim3(grid), dim3(THREADS), (size_t)(L::TOTAL), w->rec, w->cols, w->rows, q, d, M, qb_act_ld(M), part, S));
     QB_LAUNCHED(ctx, "gemm_dp4a_kernel");
     return QB_OK;
 }
 
 // Exact int32 block dots, out[m][n][kb] (test aid for the integer part).
-__global__ void block_dots_kernel(const int8_t *__restrict__ wq, uint32_t K, uint32_t N, const int8_t *__restrict__ xq,
+__global__ void block_dots_kernel(const uint8_t *__restrict__ rec, uint32_t K, uint32_t N, const int8_t *__restrict__ xq,
                                   uint32_t M, int32_t *out) {
     const uint32_t nb = K / 32;
     const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (uint64_t)N * nb) return;
     const uint32_t n = (uint32_t)(idx / nb), kb = (uint32_t)(idx % nb);
-    const int *wp = reinterpret_cast<const int *>(wq + (size_t)n * K + (size_t)kb * 32);
     int wv[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) wv[i] = wp[i];
+    for (int i = 0; i < 8; ++i) wv[i] = *reinterpret_cast<const int *>(rec + qb_q_offset(K, n, kb * 32 + i * 4));
     for (uint32_t m = 0; m < M; ++m) {
         const int *xp = reinterpret_cast<const int *>(xq + (size_t)m * K + (size_t)kb * 32);
         int c = 0;
@@ -173,6 +166,7 @@ __global__ void block_dots_kernel(const int8_t *__restrict__ wq, uint32_t K, uin
 
 uint32_t qb_ksplit(uint32_t N, uint32_t K) {
     const uint32_t tiles = (N + 127) / 128, nchunks = K / 128;
+    // about one (row tile, segment) unit per SM of a 148-SM part, at most 8 segments
     uint32_t S = 148 / std::max(tiles, 1u);
     S = std::max(1u, std::min(S, 8u));
     S = std::min(S, std::max(nchunks, 1u));
@@ -242,10 +236,11 @@ static int gemm_dispatch(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const
             return qb_fail(QB_ERR_UNSUPPORTED, "tensor-core GEMM does not support this shape");
         return qb_launch_gemm_tc(ctx, w, q, d, M, part, S);
     }
-    // automatic choice: the tensor-core kernel from QW3B200_TC_MIN_M activation rows upwards
+    // automatic choice: matvec shapes (greedy / draft, M <= 2) on the CUDA-core streaming kernel, everything
+    // from the (k+1)-row verify upwards on the tensor cores (measured crossover; QW3B200_TC_MIN_M overrides)
     static const uint32_t tc_min_m = []() {
         const char *e = getenv("QW3B200_TC_MIN_M");
-        return (e && *e) ? (uint32_t)strtoul(e, nullptr, 10) : 0xFFFFFFFFu;
+        return (e && *e) ? (uint32_t)strtoul(e, nullptr, 10) : 3u;
     }();
     if (impl == 0 && M >= tc_min_m && qb_gemm_tc_supported(w, M)) return qb_launch_gemm_tc(ctx, w, q, d, M, part, S);
     return qb_launch_gemm_dp4a(ctx, w, q, d, M, part, S);
@@ -281,7 +276,7 @@ extern "C" int qb_q8_0_matmul(qb_ctx *ctx, const qb_weight *w, const float *x_de
 extern "C" int qb_q8_block_dots(qb_ctx *ctx, const qb_weight *w, const int8_t *q_dev, uint32_t M, int32_t *out_dev) {
     QB_REQUIRE(ctx && w && q_dev && out_dev, "qb_q8_block_dots: null argument");
     const uint64_t total = (uint64_t)w->rows * (w->cols / 32);
-    block_dots_kernel<<<(uint32_t)((total + 255) / 256), 256, 0, ctx->stream>>>(w->q, w->cols, w->rows, q_dev, M, out_dev);
+    block_dots_kernel<<<(uint32_t)((total + 255) / 256), 256, 0, ctx->stream>>>(w->rec, w->cols, w->rows, q_dev, M, out_dev);
     QB_LAUNCHED(ctx, "block_dots_kernel");
     return QB_OK;
 }

@@ -9,8 +9,9 @@
 // activation rows are its N dimension (16..128), and one tcgen05.mma.kind::i8 (K = 32 bytes) covers
 // exactly one Q8_0 block.  Every block therefore gets its OWN accumulator columns in tensor memory
 // (never accumulated across blocks), and the epilogue warps drain them and apply the per-block scales
-// in order.  Weight bytes, activation bytes and both scale planes arrive by TMA (128-byte swizzle for
-// the MMA operands) through an mbarrier pipeline; the kernel is an HBM streaming kernel until the
+// in order.  The weight record of a stage (quants already in the swizzled operand order + scales)
+// arrives as one 17 KB bulk copy, the activation tile and its scales by tensor-map TMA (128-byte
+// swizzle), all through one mbarrier pipeline; the kernel is an HBM streaming kernel until the
 // activation-row count reaches the hundreds.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (owns the TMEM allocation),
@@ -109,151 +110,261 @@ __host__ __device__ inline uint32_t tc_seg_begin(uint32_t s, uint32_t S, uint32_
 }
 
 // MT = activation rows per tile (MMA N).  NLD = accumulator columns the epilogue reads (<= MT).
+// A pipeline stage holds one weight record (17 KB, one bulk copy, already the swizzled operand image
+// plus its scales), the activation tile (MT x 128 B, tensor-map TMA with the 128-byte swizzle) and
+// the activation scales.  TMEM: every stage (MT <= 64) or half stage (MT = 128) has its own slot.
 template <int MT, int NLD>
 struct TcCfg {
     static constexpr int KPS = MT == 128 ? 2 : 4;              // 32-blocks per TMEM slot
     static constexpr int SPS = 4 / KPS;                        // slots per pipeline stage
-    static constexpr int NSLOT = 512 / (KPS * MT);
-    static constexpr int NST = MT <= 32 ? 8 : (MT == 64 ? 6 : 5);
-    static constexpr int A_BYTES = 128 * 128;
+    // Small tiles run two CTAs per SM (two independent producer/MMA/epilogue chains per SM: the per-stage
+    // handshake chain of one CTA, not the memory system, limits a single chain to ~33 GB/s), so each CTA
+    // takes half the tensor memory and half the shared memory.
+    static constexpr int CTAS_PER_SM = MT == 16 ? 2 : 1;
+    static constexpr int NSLOT = 512 / CTAS_PER_SM / (KPS * MT);
+    static constexpr int TMEM_COLS = NSLOT * KPS * MT;
+    static constexpr int B_OFF = (int)QB_REC_BYTES;            // 17 * 1024: the activation tile stays 1024-aligned
     static constexpr int B_BYTES = MT * 128;
-    static constexpr int WD_BYTES = 4 * 128 * 2;
+    static constexpr int XD_OFF = B_OFF + B_BYTES;
     static constexpr int XD_BYTES = 4 * MT * 4;
-    static constexpr int TX_BYTES = A_BYTES + B_BYTES + WD_BYTES + XD_BYTES;
-    static constexpr int STAGE = (TX_BYTES + 1023) / 1024 * 1024;
+    static constexpr int TX_BYTES = (int)QB_REC_BYTES + B_BYTES + XD_BYTES;
+    static constexpr int STAGE = (XD_OFF + XD_BYTES + 1023) / 1024 * 1024;
     static constexpr int BAR_BYTES = 1024;
+    static constexpr int NST_FIT = (232448 / CTAS_PER_SM - BAR_BYTES - 2048) / STAGE;
+    static constexpr int NST = NST_FIT > 8 ? 8 : NST_FIT;
     static constexpr int TOTAL = STAGE * NST + BAR_BYTES + 1024;   // + slack to align the base to 1024
     static constexpr int CH = NLD < 16 ? NLD : 16;               // columns per tcgen05.ld
 };
 
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// Persistent kernel: CTA b works on units b, b + gridDim.x, ...; a unit is (activation tile, K segment,
+// 128-row weight tile).  The TMA / MMA / TMEM pipeline keeps running across unit boundaries.
 template <int MT, int NLD>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_constant__ CUtensorMap map_wd,
-               const __grid_constant__ CUtensorMap map_xq, const __grid_constant__ CUtensorMap map_xd,
-               uint32_t K, uint32_t N, uint32_t M, float *__restrict__ part, uint32_t S, int *err_flag) {
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensorMap map_xq,
+               const __grid_constant__ CUtensorMap map_xd, uint32_t K, uint32_t N, uint32_t M, float *__restrict__ part,
+               uint32_t S, uint32_t tiles, uint32_t units, int *err_flag) {
     using C = TcCfg<MT, NLD>;
+    constexpr uint32_t NST = C::NST, NSLOT = C::NSLOT;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t *bar_mem = smem + (size_t)C::STAGE * C::NST;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(bar_mem);
+    uint8_t *bar_mem = smem + (size_t)C::STAGE * NST;
     // barrier layout: full[NST], empty[NST], tmem_full[NSLOT], tmem_empty[NSLOT]
-    const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * C::NST;
-    const uint32_t bar_tfull = bar_empty + 8 * C::NST, bar_tempty = bar_tfull + 8 * C::NSLOT;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_mem + 8 * (2 * C::NST + 2 * C::NSLOT));
+    const uint32_t bar_full = smem_u32(bar_mem), bar_empty = bar_full + 8 * NST;
+    const uint32_t bar_tfull = bar_empty + 8 * NST, bar_tempty = bar_tfull + 8 * NSLOT;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_mem + 8 * (2 * NST + 2 * NSLOT));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t row0 = blockIdx.x * 128, seg = blockIdx.y, m0 = blockIdx.z * MT;
     const uint32_t nchunks = K / 128;
-    const uint32_t c_begin = tc_seg_begin(seg, S, nchunks), n_it = tc_seg_begin(seg + 1, S, nchunks) - c_begin;
+    constexpr uint32_t tmem_cols = C::TMEM_COLS;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < C::NST; ++i) {
+        for (uint32_t i = 0; i < NST; ++i) {
             mbar_init(bar_full + 8 * i, 1);
-            mbar_init(bar_empty + 8 * i, 1 + 128);        // MMA commit + every epilogue thread
+            mbar_init(bar_empty + 8 * i, 1 + 4);          // MMA commit + one lane of every epilogue warp
         }
-        for (int i = 0; i < C::NSLOT; ++i) {
+        for (uint32_t i = 0; i < NSLOT; ++i) {
             mbar_init(bar_tfull + 8 * i, 1);
-            mbar_init(bar_tempty + 8 * i, 128);
+            mbar_init(bar_tempty + 8 * i, 4);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the consumer of the partials may be scheduled already
+
+    // unit -> (m tile, segment, row tile); consecutive units of a CTA differ in the row tile
+    auto decode = [&](uint32_t u, uint32_t &tile, uint32_t &seg, uint32_t &m0, uint32_t &c_begin, uint32_t &n_it) {
+        const uint32_t per_m = tiles * S;
+        m0 = (u / per_m) * MT;
+        const uint32_t rem = u % per_m;
+        seg = rem / tiles;
+        tile = rem % tiles;
+        c_begin = tc_seg_begin(seg, S, nchunks);
+        n_it = tc_seg_begin(seg + 1, S, nchunks) - c_begin;
+    };
 
     if (warp == 0) {
         if (lane == 0) {
-            for (uint32_t it = 0; it < n_it; ++it) {
-                const uint32_t st = it % C::NST, ph = (it / C::NST) & 1;
-                if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) break;
-                const uint32_t base = smem_u32(smem + (size_t)st * C::STAGE);
-                const uint32_t full = bar_full + 8 * st;
+            // Stage cursor over this CTA's units.  The launch is programmatically serialised behind the kernel
+            // that produces the activations: the weight records of the first NST stages (which depend on nothing)
+            // are requested at once, then the CTA waits for the preceding grid and only then requests activations.
+            struct Cursor { uint32_t u, it, n_it, tile, m0, c_begin; bool valid; };
+            auto start = [&](uint32_t u) {
+                Cursor c; c.u = u; c.it = 0; c.valid = u < units; c.n_it = 0; c.tile = c.m0 = c.c_begin = 0;
+                if (c.valid) { uint32_t seg; decode(u, c.tile, seg, c.m0, c.c_begin, c.n_it); }
+                return c;
+            };
+            auto next = [&](Cursor &c) {
+                if (++c.it >= c.n_it) c = start(c.u + gridDim.x);
+            };
+            auto load_w = [&](const Cursor &c, uint32_t st) {
+                const uint32_t base = smem_u32(smem + (size_t)st * C::STAGE), full = bar_full + 8 * st;
                 mbar_expect_tx(full, C::TX_BYTES);
-                const int k0 = (int)((c_begin + it) * 128);
-                tma_load_2d(base, &map_wq, k0, (int)row0, full);
-                tma_load_2d(base + C::A_BYTES, &map_xq, k0, (int)m0, full);
-                tma_load_2d(base + C::A_BYTES + C::B_BYTES, &map_wd, (int)row0, k0 / 32, full);
-                tma_load_2d(base + C::A_BYTES + C::B_BYTES + C::WD_BYTES, &map_xd, (int)m0, k0 / 32, full);
+                bulk_load(base, rec + ((size_t)c.tile * nchunks + c.c_begin + c.it) * QB_REC_BYTES, QB_REC_BYTES, full);
+            };
+            auto load_x = [&](const Cursor &c, uint32_t st) {
+                const uint32_t base = smem_u32(smem + (size_t)st * C::STAGE), full = bar_full + 8 * st;
+                const int k0 = (int)((c.c_begin + c.it) * 128);
+                tma_load_2d(base + C::B_OFF, &map_xq, k0, (int)c.m0, full);
+                tma_load_2d(base + C::XD_OFF, &map_xd, (int)c.m0, k0 / 32, full);
+            };
+            Cursor head = start(blockIdx.x), c = head;
+            uint32_t npre = 0;
+            for (; npre < NST && c.valid; ++npre, next(c)) load_w(c, npre);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            c = head;
+            for (uint32_t g = 0; g < npre; ++g, next(c)) load_x(c, g);
+            for (uint32_t git = npre; c.valid; ++git, next(c)) {
+                const uint32_t st = git % NST, ph = (git / NST) & 1;
+                if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) break;
+                load_w(c, st);
+                load_x(c, st);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N = MT, M = 128
             constexpr uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT >> 3) << 17) | ((128u >> 4) << 24);
-            uint32_t j = 0;
+            uint32_t git = 0, j = 0;
             bool ok = true;
-            for (uint32_t it = 0; it < n_it && ok; ++it) {
-                const uint32_t st = it % C::NST, ph = (it / C::NST) & 1;
-                if (!mbar_wait(bar_full + 8 * st, ph, abort_flag)) break;
-                tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + (size_t)st * C::STAGE), b_addr = a_addr + C::A_BYTES;
-                for (int sp = 0; sp < C::SPS; ++sp, ++j) {
-                    const uint32_t slot = j % C::NSLOT, sph = (j / C::NSLOT) & 1;
-                    if (!mbar_wait(bar_tempty + 8 * slot, sph ^ 1, abort_flag)) { ok = false; break; }
+            for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                uint32_t tile, seg, m0, c_begin, n_it;
+                decode(u, tile, seg, m0, c_begin, n_it);
+                for (uint32_t it = 0; it < n_it && ok; ++it, ++git) {
+                    const uint32_t st = git % NST, ph = (git / NST) & 1;
+                    if (!mbar_wait(bar_full + 8 * st, ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)st * C::STAGE), b_addr = a_addr + C::B_OFF;
+                    for (int sp = 0; sp < C::SPS; ++sp, ++j) {
+                        const uint32_t slot = j % NSLOT, sph = (j / NSLOT) & 1;
+                        if (!mbar_wait(bar_tempty + 8 * slot, sph ^ 1, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
 #pragma unroll
-                    for (int kl = 0; kl < C::KPS; ++kl) {
-                        const int kb = sp * C::KPS + kl;
-                        tc_mma_i8(tmem_base + slot * (C::KPS * MT) + kl * MT, smem_desc_sw128(a_addr + kb * 32),
-                                  smem_desc_sw128(b_addr + kb * 32), idesc);
+                        for (int kl = 0; kl < C::KPS; ++kl) {
+                            const int kb = sp * C::KPS + kl;
+                            tc_mma_i8(tmem_base + slot * (C::KPS * MT) + kl * MT, smem_desc_sw128(a_addr + kb * 32),
+                                      smem_desc_sw128(b_addr + kb * 32), idesc);
+                        }
+                        tc_commit(bar_tfull + 8 * slot);
                     }
-                    tc_commit(bar_tfull + 8 * slot);
+                    if (ok) tc_commit(bar_empty + 8 * st);
                 }
-                if (ok) tc_commit(bar_empty + 8 * st);
             }
         }
     } else {
         const uint32_t quarter = warp & 3;                     // TMEM lanes [32*quarter, +32)
         const uint32_t r = quarter * 32 + lane;                // weight row inside the tile
-        float acc[NLD];
-#pragma unroll
-        for (int i = 0; i < NLD; ++i) acc[i] = 0.0f;
-        uint32_t j = 0;
+        uint32_t git = 0, j = 0;
         bool ok = true;
-        for (uint32_t it = 0; it < n_it && ok; ++it) {
-            const uint32_t st = it % C::NST, ph = (it / C::NST) & 1;
-            if (!mbar_wait(bar_full + 8 * st, ph, abort_flag)) break;
-            const uint8_t *stage = smem + (size_t)st * C::STAGE;
-            const __half *wd = reinterpret_cast<const __half *>(stage + C::A_BYTES + C::B_BYTES);
-            const float *xd = reinterpret_cast<const float *>(stage + C::A_BYTES + C::B_BYTES + C::WD_BYTES);
-            for (int sp = 0; sp < C::SPS; ++sp, ++j) {
-                const uint32_t slot = j % C::NSLOT, sph = (j / C::NSLOT) & 1;
-                if (!mbar_wait(bar_tfull + 8 * slot, sph, abort_flag)) { ok = false; break; }
-                tc_fence_after();
+        for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
+            uint32_t tile, seg, m0, c_begin, n_it;
+            decode(u, tile, seg, m0, c_begin, n_it);
+            float acc[NLD];
 #pragma unroll
-                for (int kl = 0; kl < C::KPS; ++kl) {
-                    const int kb = sp * C::KPS + kl;
-                    const float dw = __half2float(wd[kb * 128 + r]);
-                    const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + slot * (C::KPS * MT) + kl * MT;
+            for (int i = 0; i < NLD; ++i) acc[i] = 0.0f;
+            if constexpr (NLD <= 16) {
+                // Small activation tiles (the HBM-bound regime): the scales of a stage are copied to registers
+                // as soon as the stage has landed and the stage is released at once, one stage ahead of the
+                // TMEM work, so the producer never waits for the accumulator drain.
+                float dw_n[4], dx_n[4][NLD];
+                auto fetch_scales = [&](uint32_t g) -> bool {
+                    const uint32_t st = g % NST, ph = (g / NST) & 1;
+                    if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * st, ph, abort_flag))) return false;
+                    const uint8_t *stage = smem + (size_t)st * C::STAGE;
+                    const __half *wd = reinterpret_cast<const __half *>(stage + QB_REC_Q_BYTES);
+                    const float *xd = reinterpret_cast<const float *>(stage + C::XD_OFF);
 #pragma unroll
-                    for (int c0 = 0; c0 < NLD; c0 += C::CH) {
-                        int32_t v[C::CH];
-                        tmem_ld<C::CH>(taddr + c0, v);
-                        tmem_ld_wait();
+                    for (int kb = 0; kb < 4; ++kb) {
+                        dw_n[kb] = __half2float(wd[kb * 128 + r]);
 #pragma unroll
-                        for (int i = 0; i < C::CH; ++i)
-                            acc[c0 + i] = __fmaf_rn(__fmul_rn(dw, xd[kb * MT + c0 + i]), (float)v[i], acc[c0 + i]);
+                        for (int i = 0; i < NLD; ++i) dx_n[kb][i] = xd[kb * MT + i];
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+                    return true;
+                };
+                if (n_it > 0 && !fetch_scales(git)) ok = false;
+                for (uint32_t it = 0; it < n_it && ok; ++it, ++git, ++j) {
+                    float sc[4][NLD];
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+                        for (int i = 0; i < NLD; ++i) sc[kb][i] = __fmul_rn(dw_n[kb], dx_n[kb][i]);
+                    if (it + 1 < n_it && !fetch_scales(git + 1)) { ok = false; break; }
+                    const uint32_t slot = j % NSLOT, sph = (j / NSLOT) & 1;      // one slot per stage here
+                    if (!__all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * slot, sph, abort_flag))) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + slot * (4 * MT);
+                    int32_t v[4][NLD];
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) tmem_ld<NLD>(taddr + kb * MT, v[kb]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+                        for (int i = 0; i < NLD; ++i) acc[i] = __fmaf_rn(sc[kb][i], (float)v[kb][i], acc[i]);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_tempty + 8 * slot);
+                }
+            } else {
+                for (uint32_t it = 0; it < n_it && ok; ++it, ++git) {
+                    const uint32_t st = git % NST, ph = (git / NST) & 1;
+                    // warp-uniform results: the TMEM loads below are .aligned
+                    if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * st, ph, abort_flag))) { ok = false; break; }
+                    const uint8_t *stage = smem + (size_t)st * C::STAGE;
+                    const __half *wd = reinterpret_cast<const __half *>(stage + QB_REC_Q_BYTES);
+                    const float *xd = reinterpret_cast<const float *>(stage + C::XD_OFF);
+                    for (int sp = 0; sp < C::SPS; ++sp, ++j) {
+                        const uint32_t slot = j % NSLOT, sph = (j / NSLOT) & 1;
+                        if (!__all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * slot, sph, abort_flag))) { ok = false; break; }
+                        tc_fence_after();
+#pragma unroll
+                        for (int kl = 0; kl < C::KPS; ++kl) {
+                                const int kb = sp * C::KPS + kl;
+                            const float dw = __half2float(wd[kb * 128 + r]);
+                            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + slot * (C::KPS * MT) + kl * MT;
+#pragma unroll
+                            for (int c0 = 0; c0 < NLD; c0 += C::CH) {
+                                int32_t v[C::CH];
+                                tmem_ld<C::CH>(taddr + c0, v);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int i = 0; i < C::CH; ++i)
+                                    acc[c0 + i] = __fmaf_rn(__fmul_rn(dw, xd[kb * MT + c0 + i]), (float)v[i], acc[c0 + i]);
+                            }
+                        }
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_tempty + 8 * slot);
+                    }
+                    if (ok) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_empty + 8 * st);
                     }
                 }
-                tc_fence_before();
-                mbar_arrive(bar_tempty + 8 * slot);
             }
-            if (ok) mbar_arrive(bar_empty + 8 * st);
-        }
-        const uint32_t row = row0 + r;
-        if (ok && !*abort_flag && row < N) {
+            const uint32_t row = tile * 128 + r;
+            if (ok && row < N) {
 #pragma unroll
-            for (int i = 0; i < NLD; ++i) {
-                const uint32_t m = m0 + i;
-                if (m < M) part[((size_t)seg * M + m) * N + row] = acc[i];
+                for (int i = 0; i < NLD; ++i) {
+                    const uint32_t m = m0 + i;
+                    if (m < M) part[((size_t)seg * M + m) * N + row] = acc[i];
+                }
             }
         }
     }
@@ -266,7 +377,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_constant
     }
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
 }
 
@@ -298,9 +409,22 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
         QB_TRY(qb_make_tmap_2d(&md, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, d, ld, K / 32, (uint64_t)ld * 4, MT, 4, CU_TENSOR_MAP_SWIZZLE_NONE));
         id = g_xd_maps.emplace(kd, md).first;
     }
-    dim3 grid(w->rows_pad / 128, S, (M + MT - 1) / MT);
-    gemm_tc_kernel<MT, NLD><<<grid, TC_THREADS, C::TOTAL, ctx->stream>>>(w->map_q, w->map_d, iq->second, id->second, K, w->rows, M,
-                                                                        part, S, ctx->err_flag_dev);
+    const uint32_t tiles = w->rows_pad / 128;
+    const uint32_t units = tiles * S * ((M + MT - 1) / MT);
+    const uint32_t grid = std::min<uint32_t>(units, (uint32_t)ctx->sm_count * C::CTAS_PER_SM);
+    const size_t smem_bytes = C::TOTAL;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start while the previous kernel drains
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    QB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, NLD>, (const uint8_t *)w->rec, iq->second, id->second, K, w->rows, M, part, S,
+                               tiles, units, ctx->err_flag_dev));
     QB_LAUNCHED(ctx, "gemm_tc_kernel");
     return QB_OK;
 }
@@ -308,7 +432,7 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
 }  // namespace
 
 bool qb_gemm_tc_supported(const qb_weight *w, uint32_t M) {
-    return w->has_maps && M >= 1 && w->cols % 128 == 0;
+    return w->rec != nullptr && M >= 1 && w->cols % 128 == 0;
 }
 
 int qb_launch_gemm_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S) {

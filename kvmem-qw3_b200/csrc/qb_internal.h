@@ -39,10 +39,34 @@ int qb_fail(int code, const char *fmt, ...);
 #define QB_LAUNCHED(ctx, name)                                                                     \
     do {                                                                                           \
         (ctx)->launches++;                                                                         \
+        if ((ctx)->trace_on) qb_trace_mark(ctx, name);                                             \
         cudaError_t _e = cudaGetLastError();                                                       \
         if (_e != cudaSuccess)                                                                     \
             return qb_fail(QB_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e));  \
     } while (0)
+
+// Programmatic dependent launch: every kernel of the step is launched with stream serialisation relaxed,
+// announces its own dependents at once and then waits for the complete preceding grid (memory flushed), so
+// scheduling and launch latency of kernel N+1 overlap the tail of kernel N; semantics stay those of a stream.
+#define QB_PDL_ENTER()                                                           \
+    do {                                                                         \
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");          \
+        asm volatile("griddepcontrol.wait;" ::: "memory");                       \
+    } while (0)
+template <typename K, typename... Args>
+inline cudaError_t qb_launch_pdl(cudaStream_t stream, K kernel, dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 struct qb_ctx {
     int device = 0;
@@ -53,6 +77,11 @@ struct qb_ctx {
     void *flush_buf = nullptr;             // > L2 bytes, written by qb_flush_l2
     size_t flush_bytes = 0;
     int *err_flag_dev = nullptr;           // set by kernels whose bounded waits ran out
+    // optional launch trace (qb_trace_*): one event after every launch, durations = event deltas
+    bool trace_on = false;
+    std::vector<cudaEvent_t> trace_ev;
+    std::vector<const char *> trace_names;
+    size_t trace_used = 0;
     // optional per-launch timing of the GEMM kernels (qb_prof_*): event pairs + algorithmic bytes
     bool prof_on = false;
     std::vector<cudaEvent_t> prof_ev;      // pool, two per recorded launch
@@ -63,20 +92,34 @@ struct qb_ctx {
     size_t scratch_bytes = 0;
 };
 int qb_ctx_scratch(qb_ctx *ctx, size_t bytes, void **out);
+void qb_trace_mark(qb_ctx *ctx, const char *name);
 
 // ---- Q8_0 weight in device layout ----------------------------------------------------------
-// q: int8 [rows_pad][cols] row-major (rows_pad = rows rounded up to 128, padding rows are zero);
-// d: fp16 [cols/32][ld] with ld >= rows_pad, scale of row n / block kb at d[kb*ld + n].
-// Bytes held stay 34 per 32 weights.  A view shares storage with its parent.
+// The matrix is cut into records of 128 rows x 128 columns (4 Q8_0 blocks per row), stored row-tile
+// major: record (tile, chunk) at rec + (tile * (cols/128) + chunk) * QB_REC_BYTES.  A record is what
+// one pipeline stage of the GEMM kernels consumes, so a stage is ONE contiguous 17 KB read:
+//   bytes [0, 16384)       the int8 quants as the 128-byte-swizzled shared-memory image the tensor
+//                          cores read: 16-byte piece p of row r at r*128 + ((p ^ (r & 7)) << 4)
+//   bytes [16384, 17408)   fp16 scales [4 blocks][128 rows]
+// Rows are padded to a multiple of 128 with zeros.  34 bytes per 32 weights, as in the GGUF file.
+// A view shares storage with its parent.
+static const uint32_t QB_REC_Q_BYTES = 16384, QB_REC_BYTES = 17408;
 struct qb_weight {
-    uint32_t rows = 0, cols = 0, rows_pad = 0, ld = 0;
-    int8_t *q = nullptr;
-    __half *d = nullptr;
+    uint32_t rows = 0, cols = 0, rows_pad = 0;
+    uint8_t *rec = nullptr;
     bool owns = false;
-    CUtensorMap map_q;    // {cols, rows_pad} uint8, box {128, 128}, 128-byte swizzle
-    CUtensorMap map_d;    // {ld(rows), cols/32} fp16, box {128, 4}
-    bool has_maps = false;
 };
+__host__ __device__ inline size_t qb_rec_offset(uint32_t cols, uint32_t row, uint32_t chunk) {
+    return ((size_t)(row >> 7) * (cols >> 7) + chunk) * QB_REC_BYTES;
+}
+// byte offset of quant (row, col) and of the scale of (row, block kb) inside the weight
+__host__ __device__ inline size_t qb_q_offset(uint32_t cols, uint32_t row, uint32_t col) {
+    const uint32_t r = row & 127, within = col & 127, p = within >> 4;
+    return qb_rec_offset(cols, row, col >> 7) + r * 128 + ((p ^ (r & 7)) << 4) + (within & 15);
+}
+__host__ __device__ inline size_t qb_d_offset(uint32_t cols, uint32_t row, uint32_t kb) {
+    return qb_rec_offset(cols, row, kb >> 2) + QB_REC_Q_BYTES + ((kb & 3) * 128 + (row & 127)) * 2;
+}
 int qb_weight_alloc(qb_ctx *ctx, uint32_t rows, uint32_t cols, qb_weight **out);
 int qb_weight_fill_synth(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, uint64_t seed,
                          uint32_t tensor_id, float sigma);
@@ -160,7 +203,7 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
                 uint32_t q_pitch, float *d, uint32_t d_ld);
 size_t qb_attention_scratch_floats(uint32_t rows, uint32_t n_heads, uint32_t hd, uint32_t max_pos,
                                    size_t *ml_floats);
-static const uint32_t QB_ATTN_SPLIT = 256;   // keys per split, fixed absolute boundaries
+static const uint32_t QB_ATTN_SPLIT = 64;    // keys per split (one tile), fixed absolute boundaries
 
 struct DnArgs {
     const float *proj = nullptr; uint32_t proj_stride = 0;   // rows [qkv | z | alpha | beta]

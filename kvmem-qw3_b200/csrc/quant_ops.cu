@@ -73,43 +73,53 @@ extern "C" int qb_quantize_q8_1_mmq(qb_ctx *ctx, const float *x_dev, uint32_t M,
 }
 
 // ---- fused: (x + split partials) -> residual stream -> RMSNorm -> int8 ----------------------
-// One CTA per row.  The row is staged in shared memory between the two passes.
+// One CTA of 1024 threads per row.  Pass 1 only loads (x and the split partials, independent loads the
+// compiler can keep in flight together) and stages the row in shared memory; pass 2 writes the residual
+// stream, the normalised copy and the int8 blocks.
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS) norm_quant_kernel(NormQuantArgs a) {
+    QB_PDL_ENTER();
     extern __shared__ float row[];
     __shared__ float red[THREADS / 32];
+    float *wsm = row + a.n;
     const uint32_t m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t src = a.row_map ? (uint32_t)a.row_map[m] : m;
-    const float *x = a.x ? a.x + (size_t)src * a.x_stride : nullptr;
+    const float *__restrict__ x = a.x ? a.x + (size_t)src * a.x_stride : nullptr;
+    const float *__restrict__ parts = a.parts ? a.parts + (size_t)m * a.part_ld : nullptr;
+    const size_t pstride = (size_t)a.M * a.part_ld;
     float ss = 0.0f;
+#pragma unroll 4
     for (uint32_t i = tid; i < a.n; i += THREADS) {
         float v = x ? x[i] : 0.0f;
         if (a.S > 0) {   // GEMM result first (segments ascending), then the residual
-            float y = a.parts[(size_t)m * a.part_ld + i];
-            for (uint32_t s = 1; s < a.S; ++s) y += a.parts[((size_t)s * a.M + m) * a.part_ld + i];
+            float p[8];  // all segment loads are issued before the first add (S <= 8)
+#pragma unroll
+            for (uint32_t s = 0; s < 8; ++s) p[s] = s < a.S ? parts[s * pstride + i] : 0.0f;
+            float y = p[0];
+#pragma unroll
+            for (uint32_t s = 1; s < 8; ++s) if (s < a.S) y += p[s];
             v = x ? v + y : y;
         }
         row[i] = v;
-        if (a.h_out) a.h_out[(size_t)m * a.h_stride + i] = v;
+        wsm[i] = a.w ? a.w[i] : 1.0f;    // gains staged now: pass 2 has no global load in its dependency chain
         ss += v * v;
     }
     float scale = 1.0f;
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
     if (a.w) {
-        ss = warp_sum(ss);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
         float tot = 0.0f;
 #pragma unroll
         for (int i = 0; i < THREADS / 32; ++i) tot += red[i];
         scale = rsqrtf(tot / (float)a.n + a.eps);
-    } else {
-        __syncthreads();
     }
     const uint32_t nblk = a.n / 32;
     for (uint32_t b = warp; b < nblk; b += THREADS / 32) {
         const uint32_t i = b * 32 + lane;
         float v = row[i];
-        if (a.w) v = v * scale * a.w[i];
+        if (a.h_out) a.h_out[(size_t)m * a.h_stride + i] = v;
+        if (a.w) v = v * scale * wsm[i];
         if (a.normed_out) a.normed_out[(size_t)m * a.n + i] = v;
         if (a.q)
             quant_block_store(v, lane, a.q + (size_t)m * a.q_pitch + a.q_col_off + b * 32,
@@ -118,15 +128,15 @@ __global__ void __launch_bounds__(THREADS) norm_quant_kernel(NormQuantArgs a) {
 }
 
 int qb_launch_norm_quant(qb_ctx *ctx, const NormQuantArgs &a) {
-    QB_REQUIRE(a.M > 0 && a.n > 0 && a.n % 32 == 0, "norm_quant: bad shape M=%u n=%u", a.M, a.n);
-    const size_t smem = (size_t)a.n * sizeof(float);
+    QB_REQUIRE(a.M > 0 && a.n > 0 && a.n % 32 == 0 && a.S <= 8, "norm_quant: bad shape M=%u n=%u S=%u", a.M, a.n, a.S);
+    const size_t smem = 2 * (size_t)a.n * sizeof(float);
     static bool attr_set = false;
     if (!attr_set) {
-        QB_CUDA(cudaFuncSetAttribute(norm_quant_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        QB_CUDA(cudaFuncSetAttribute(norm_quant_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         attr_set = true;
     }
     QB_REQUIRE(smem <= 160 * 1024, "norm_quant: row of %u floats does not fit shared memory", a.n);
-    norm_quant_kernel<256><<<a.M, 256, smem, ctx->stream>>>(a);
+    QB_CUDA(qb_launch_pdl(ctx->stream, norm_quant_kernel<1024>, dim3(a.M), dim3(1024), (size_t)(smem), a));
     QB_LAUNCHED(ctx, "norm_quant_kernel");
     return QB_OK;
 }
@@ -151,6 +161,7 @@ extern "C" int qb_rms_norm(qb_ctx *ctx, const float *x_dev, const float *w_dev, 
 // silu(gate) * up -> int8 (silu_mul_kernel src/kernels_cuda.cu:1894-1903 fused with the quantiser).
 __global__ void swiglu_quant_kernel(const float *__restrict__ gu, uint32_t gu_stride, uint32_t F, int8_t *q,
                                     uint32_t q_pitch, float *d, uint32_t d_ld) {
+    QB_PDL_ENTER();
     const uint32_t b = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32, m = blockIdx.y, lane = threadIdx.x & 31;
     if (b >= F / 32) return;
     const float g = gu[(size_t)m * gu_stride + b * 32 + lane];
@@ -162,13 +173,14 @@ __global__ void swiglu_quant_kernel(const float *__restrict__ gu, uint32_t gu_st
 int qb_launch_swiglu_quant(qb_ctx *ctx, const float *gu, uint32_t gu_stride, uint32_t M, uint32_t F, int8_t *q,
                            uint32_t q_pitch, float *d, uint32_t d_ld) {
     dim3 grid((F / 32 + 7) / 8, M);
-    swiglu_quant_kernel<<<grid, 256, 0, ctx->stream>>>(gu, gu_stride, F, q, q_pitch, d, d_ld);
+    QB_CUDA(qb_launch_pdl(ctx->stream, swiglu_quant_kernel, dim3(grid), dim3(256), (size_t)(0), gu, gu_stride, F, q, q_pitch, d, d_ld));
     QB_LAUNCHED(ctx, "swiglu_quant_kernel");
     return QB_OK;
 }
 
 __global__ void reduce_parts_kernel(const float *__restrict__ part, uint32_t S, uint32_t M, uint32_t N, float *y,
                                     uint32_t y_stride) {
+    QB_PDL_ENTER();
     const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x, m = blockIdx.y;
     if (n >= N) return;
     float v = part[(size_t)m * N + n];
@@ -179,7 +191,7 @@ __global__ void reduce_parts_kernel(const float *__restrict__ part, uint32_t S, 
 int qb_launch_reduce_parts(qb_ctx *ctx, const float *part, uint32_t S, uint32_t M, uint32_t N, float *y,
                            uint32_t y_stride) {
     dim3 grid((N + 255) / 256, M);
-    reduce_parts_kernel<<<grid, 256, 0, ctx->stream>>>(part, S, M, N, y, y_stride);
+    QB_CUDA(qb_launch_pdl(ctx->stream, reduce_parts_kernel, dim3(grid), dim3(256), (size_t)(0), part, S, M, N, y, y_stride));
     QB_LAUNCHED(ctx, "reduce_parts_kernel");
     return QB_OK;
 }
@@ -191,6 +203,7 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 
 __global__ void argmax_partial_kernel(const float *__restrict__ x, uint32_t n, uint32_t stride, float *pval, int32_t *pidx,
                                       uint32_t nblk) {
+    QB_PDL_ENTER();
     __shared__ float sv[8];
     __shared__ int si[8];
     const uint32_t m = blockIdx.y, blk = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -220,7 +233,7 @@ __global__ void argmax_partial_kernel(const float *__restrict__ x, uint32_t n, u
 int qb_launch_argmax_partial(qb_ctx *ctx, const float *x, uint32_t M, uint32_t n, uint32_t stride, float *pval,
                              int32_t *pidx, uint32_t nblk) {
     dim3 grid(nblk, M);
-    argmax_partial_kernel<<<grid, 256, 0, ctx->stream>>>(x, n, stride, pval, pidx, nblk);
+    QB_CUDA(qb_launch_pdl(ctx->stream, argmax_partial_kernel, dim3(grid), dim3(256), (size_t)(0), x, n, stride, pval, pidx, nblk));
     QB_LAUNCHED(ctx, "argmax_partial_kernel");
     return QB_OK;
 }

@@ -12,7 +12,8 @@ LOGIT_TOL = 1e-2     # max |gpu - oracle| / max |oracle|, the bound the step is 
 # that differ in the last bit somewhere (device rsqrt/exp, reduction order) take different rounding
 # decisions from then on, so their logits differ at the level of the int8 rounding noise itself
 # (about 0.6% of the logit range on this 256-wide model, measured).  Single-row steps stay inside
-# LOGIT_TOL; for the 4-row verify block the mean over rows must, and the worst row gets ROW_CAP.
+# LOGIT_TOL; in the 4-row verify block the later rows also consume the earlier rows' freshly written K/V
+# and DeltaNet state, so the first row must meet LOGIT_TOL and every row ROW_CAP.
 ROW_CAP = 2e-2
 
 
@@ -109,7 +110,7 @@ def test_mtp_step_pieces_match_oracle(qb, orc, ctx, tiny):
         otoks, _, orows = s.mtp_step(3, drafts)
         olg = s.last_logits(4)
         per_row = [rel_err(lg[r], olg[r]) for r in range(4)]
-        assert float(np.mean(per_row)) < LOGIT_TOL and max(per_row) < ROW_CAP, (step, per_row)
+        assert per_row[0] < LOGIT_TOL and max(per_row) < ROW_CAP, (step, per_row)
         rows = np.argmax(lg, 1).tolist()
         for r in range(4):
             assert rows[r] == orows[r] or margin(olg[r]) < 2 * LOGIT_TOL
