@@ -135,6 +135,15 @@ int qb_q8_block_dots(qb_ctx *ctx, const qb_weight *w, const int8_t *q_dev, uint3
  * Both implementations produce identical bits. */
 int qb_q8_0_matmul(qb_ctx *ctx, const qb_weight *w, const float *x_dev, uint32_t M, uint32_t x_stride,
                    float *y_dev, uint32_t y_stride, uint32_t ksplit, int impl);
+/* The same product as qb_q8_0_matmul (identical bits) for callers that must not allocate device memory:
+ * a server whose own arena already owns the whole device, or a loop that cannot take the device-wide
+ * synchronisation hidden in cudaMalloc / cudaFree.  It has no counterpart in the reference.  The work area
+ * (int8 activations, scales, K-segment partial sums) is an 8 MiB array built into the library image, held by
+ * every GPU that loads the library; shapes that need more are refused with QB_ERR_CAPACITY.  The first call on
+ * a device looks the array's address up (make that call before any stream capture starts).  All calls share
+ * the one array: calls that may overlap on the GPU (different streams or contexts of one device) race. */
+int qb_q8_0_matmul_noalloc(qb_ctx *ctx, const qb_weight *w, const float *x_dev, uint32_t M, uint32_t x_stride,
+                           float *y_dev, uint32_t y_stride, uint32_t ksplit);
 /* Same product from already-quantised activations, leaving the per-segment partial sums:
  * part_dev = float [ksplit][M][N]. */
 int qb_q8_gemm_partials(qb_ctx *ctx, const qb_weight *w, const int8_t *q_dev, const float *d_dev, uint32_t M,

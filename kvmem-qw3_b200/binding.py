@@ -61,6 +61,7 @@ SIGNATURES = {
     "qb_ksplit_policy": (u32, [u32, u32]),
     "qb_q8_block_dots": (i32, [vp, vp, vp, u32, vp]),
     "qb_q8_0_matmul": (i32, [vp, vp, vp, u32, u32, vp, u32, u32, i32]),
+    "qb_q8_0_matmul_noalloc": (i32, [vp, vp, vp, u32, u32, vp, u32, u32]),
     "qb_q8_gemm_partials": (i32, [vp, vp, vp, vp, u32, vp, u32, i32]),
     "qb_q8_0_get_rows": (i32, [vp, vp, vp, u32, vp, u32]),
     "qb_rms_norm": (i32, [vp, vp, vp, u32, u32, u32, f32, vp]),

@@ -280,3 +280,58 @@ extern "C" int qb_q8_block_dots(qb_ctx *ctx, const qb_weight *w, const int8_t *q
     QB_LAUNCHED(ctx, "block_dots_kernel");
     return QB_OK;
 }
+
+// ---- matmul for callers that must not allocate ---------------------------------------------------
+// qb_q8_0_matmul keeps its work area (int8 activations, their scales, the K-segment partial sums) in a
+// context buffer that grows with cudaMalloc.  Some hosts cannot afford that: an inference server whose own
+// arena already owns every byte of the device (cudaMalloc would fail or fragment it), or a decode loop in
+// which the implicit device-wide synchronisation of cudaMalloc / cudaFree is not acceptable.  This variant
+// needs no allocation at all: its work area is the fixed array below, part of the library image, so every
+// GPU that loads the library holds these QB_NOALLOC_SCRATCH_BYTES until the process exits.
+static const size_t QB_NOALLOC_SCRATCH_BYTES = (size_t)8 << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[QB_NOALLOC_SCRATCH_BYTES];
+
+// Device address of the array for the current device.  The symbol name is only a host-side handle: the
+// address a kernel may use comes from cudaGetSymbolAddress, once per device, with that device current.
+static int noalloc_scratch_ptr(qb_ctx *ctx, unsigned char **out) {
+    static unsigned char *ptrs[64] = {nullptr};
+    QB_REQUIRE(ctx->device >= 0 && ctx->device < 64, "no-alloc matmul: device ordinal %d out of range", ctx->device);
+    if (!ptrs[ctx->device]) {
+        QB_CUDA(cudaSetDevice(ctx->device));
+        void *p = nullptr;
+        QB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        QB_REQUIRE(p != nullptr, "no-alloc matmul: cudaGetSymbolAddress returned a null address");
+        ptrs[ctx->device] = (unsigned char *)p;
+    }
+    *out = ptrs[ctx->device];
+    return QB_OK;
+}
+
+extern "C" int qb_q8_0_matmul_noalloc(qb_ctx *ctx, const qb_weight *w, const float *x_dev, uint32_t M, uint32_t x_stride,
+                                      float *y_dev, uint32_t y_stride, uint32_t ksplit) {
+    QB_REQUIRE(ctx && w && x_dev && y_dev && M > 0, "qb_q8_0_matmul_noalloc: bad arguments");
+    QB_REQUIRE(x_stride >= w->cols && y_stride >= w->rows, "qb_q8_0_matmul_noalloc: strides smaller than the matrix");
+    const uint32_t S = ksplit ? ksplit : qb_ksplit(w->rows, w->cols);
+    const uint32_t K = w->cols, N = w->rows, ld = qb_act_ld(M);
+    const bool direct = S == 1 && y_stride == N;                    // a single segment is written straight to y
+    const size_t qbytes = ((size_t)M * K + 255) & ~(size_t)255;
+    const size_t dbytes = (((size_t)(K / 32) * ld * 4) + 255) & ~(size_t)255;
+    const size_t pbytes = direct ? 0 : (size_t)S * M * N * 4;
+    if (qbytes + dbytes + pbytes > QB_NOALLOC_SCRATCH_BYTES)
+        return qb_fail(QB_ERR_CAPACITY,
+                       "qb_q8_0_matmul_noalloc: M=%u rows of a %ux%u weight with %u K segments need %zu bytes of work area, "
+                       "the built-in area holds %zu; use qb_q8_0_matmul", M, N, K, S, qbytes + dbytes + pbytes,
+                       QB_NOALLOC_SCRATCH_BYTES);
+    unsigned char *scr = nullptr;
+    QB_TRY(noalloc_scratch_ptr(ctx, &scr));
+    int8_t *q = (int8_t *)scr;
+    float *d = (float *)(scr + qbytes);
+    float *part = (float *)(scr + qbytes + dbytes);
+    // the array keeps whatever the previous call left: the scale rows have padding columns the quantiser
+    // does not write, so that region starts from zero on every call
+    QB_CUDA(cudaMemsetAsync(d, 0, dbytes, ctx->stream));
+    QB_TRY(qb_quantize_act(ctx, x_dev, M, K, x_stride, q, d));
+    if (direct) return qb_launch_gemm_dp4a(ctx, w, q, d, M, y_dev, 1);
+    QB_TRY(qb_launch_gemm_dp4a(ctx, w, q, d, M, part, S));
+    return qb_launch_reduce_parts(ctx, part, S, M, N, y_dev, y_stride);
+}
