@@ -292,14 +292,8 @@ def run_ours(args, rank, world, local_rank, dist):
     lossless = e2e_tokens == list(stream[pos - len(e2e_tokens) + 1:pos + 1])
 
     # 5. aggregate over replicas: max time, summed tokens
-    agg = np.array([dev_ms, e2e_ms, float(dev_emitted), float(len(e2e_tokens)), float(l1 - l0)], np.float64)
-    if dist is not None:
-        import torch
-        tmax = torch.tensor(agg[:2], dtype=torch.float64, device="cuda")
-        tsum = torch.tensor(agg[2:], dtype=torch.float64, device="cuda")
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        agg = np.concatenate([tmax.cpu().numpy(), tsum.cpu().numpy()])
+    tmax, tsum = pkg.replicas.aggregate(dist, [dev_ms, e2e_ms], [float(dev_emitted), float(len(e2e_tokens)), float(l1 - l0)])
+    agg = np.concatenate([tmax, tsum])
     if rank != 0:
         b.close(); model.close(); ctx.close()
         return
