@@ -236,13 +236,16 @@ static int gemm_dispatch(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const
             return qb_fail(QB_ERR_UNSUPPORTED, "tensor-core GEMM does not support this shape");
         return qb_launch_gemm_tc(ctx, w, q, d, M, part, S);
     }
-    // automatic choice: matvec shapes (greedy / draft, M <= 2) on the CUDA-core streaming kernel, everything
-    // from the (k+1)-row verify upwards on the tensor cores (measured crossover; QW3B200_TC_MIN_M overrides)
+    // automatic choice (measured): the tensor-core kernel everywhere except the matvec over a very tall weight
+    // (the LM head at M <= 2), where three CUDA-core CTAs per SM stream a little faster.  QW3B200_TC_MIN_M
+    // overrides: the tensor-core kernel is then used from that many activation rows upwards only.
     static const uint32_t tc_min_m = []() {
         const char *e = getenv("QW3B200_TC_MIN_M");
-        return (e && *e) ? (uint32_t)strtoul(e, nullptr, 10) : 3u;
+        return (e && *e) ? (uint32_t)strtoul(e, nullptr, 10) : 0u;
     }();
-    if (impl == 0 && M >= tc_min_m && qb_gemm_tc_supported(w, M)) return qb_launch_gemm_tc(ctx, w, q, d, M, part, S);
+    const bool tall_matvec = M <= 2 && w->rows_pad / 128 >= 600;
+    if (impl == 0 && M >= tc_min_m && !(tc_min_m == 0 && tall_matvec) && qb_gemm_tc_supported(w, M))
+        return qb_launch_gemm_tc(ctx, w, q, d, M, part, S);
     return qb_launch_gemm_dp4a(ctx, w, q, d, M, part, S);
 }
 
