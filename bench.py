@@ -34,6 +34,7 @@ K_DRAFT = 3
 PROMPT_LEN = 2048
 ACCEPT_RATE = 0.7
 FORCE_SEED = 0xACCE97
+NCU_TRAFFIC_RATIO = 94.79 / 94.70
 EXPECTED_EMITTED = 1 + ACCEPT_RATE + ACCEPT_RATE ** 2 + ACCEPT_RATE ** 3   # tokens per step at 70%
 
 
@@ -45,6 +46,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=64, help="target layers (64 = the 27B-class shape)")
     ap.add_argument("--prompt", type=int, default=PROMPT_LEN)
+    ap.add_argument("--seqs", type=int, default=1, help="concurrent requests per GPU (32 = the continuous-batching configuration)")
+    ap.add_argument("--prompt-min", type=int, default=512, help="with --seqs > 1 prompt lengths are uniform in [prompt-min, prompt]")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-greedy", action="store_true", help="profiling aid: no greedy reference run (forced drafts then never match)")
     return ap.parse_args()
@@ -148,9 +151,9 @@ def run_reference(args, rank):
 
 def workload_config(args):
     return {"workload": "BASELINE config 2: 27B-class qwen35 shape (%d layers, hidden 5120, 24q/4kv x 256, DeltaNet 16k/48v x 128, "
-                        "FFN 17408, vocab 151936), Q8_0, MTP k=3, batch 1, prompt %d, forced drafts = greedy continuation at a "
-                        "seeded 70%% rate" % (args.layers, args.prompt),
-            "draft_k": K_DRAFT, "prompt_len": args.prompt, "page_size": 16, "kv_dtype": "fp16", "accept_rate_target": ACCEPT_RATE,
+                        "FFN 17408, vocab 151936), Q8_0, MTP k=3, batch %d, prompt %d, forced drafts = greedy continuation at a "
+                        "seeded 70%% rate" % (args.layers, args.seqs, args.prompt),
+            "draft_k": K_DRAFT, "prompt_len": args.prompt, "requests_per_gpu": args.seqs, "page_size": 16, "kv_dtype": "fp16", "accept_rate_target": ACCEPT_RATE,
             "l2": "weights streamed per step (28.7 GB) exceed the 126 MB L2, no flush needed",
             "replicas": args.gpus}
 
@@ -171,52 +174,62 @@ def run_ours(args, rank, world, local_rank, dist):
     O = entry.load_oracle() if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
     ctx = pkg.Context(local_rank)
     cfg = pkg.configs.qwen27b(args.layers)
-    K, W, k = args.steps, args.warmup, K_DRAFT
+    K, W, k, ns = args.steps, args.warmup, K_DRAFT, args.seqs
     prof_steps = min(K, 8)
     total_steps = 2 * W + 2 * K + prof_steps + 6
     n_greedy = 4 * total_steps + 8
-    max_ctx = args.prompt + n_greedy + 16
     model = pkg.Model(ctx, cfg, pkg.configs.MODEL_SEED)
-    # seeded prompt: uniform token ids (host generator shared with the oracle's recipe: Philox stream)
+    # seeded prompts: uniform token ids; one request of --prompt tokens, or --seqs requests with lengths
+    # uniform in [--prompt-min, --prompt] (the continuous-batching configuration)
     rs = np.random.RandomState((pkg.configs.PROMPT_SEED + 2 + rank) & 0x7FFFFFFF)
-    prompt = rs.randint(0, cfg.vocab_size, args.prompt).astype(np.int32)
+    plen = [args.prompt] if ns == 1 else [int(v) for v in rs.randint(args.prompt_min, args.prompt + 1, ns)]
+    prompts = [rs.randint(0, cfg.vocab_size, n).astype(np.int32) for n in plen]
+    max_ctx = max(plen) + n_greedy + 16
+    stride = max_ctx + 8
 
     # 1. the non-speculative greedy continuation (also the losslessness reference of this run)
     ev = [ctx.event() for _ in range(8)]
     if args.skip_greedy:
-        greedy, greedy_ms = [0] * n_greedy, float("nan")
+        greedy, greedy_ms = [[0] * n_greedy for _ in range(ns)], float("nan")
     else:
-        g = pkg.Batch(model, 1, max_ctx, 0)
-        g.prefill(0, prompt)
-        greedy = list(g.read_output()[0])
+        g = pkg.Batch(model, ns, max_ctx, 0)
+        for s_ in range(ns):
+            g.prefill(s_, prompts[s_])
+        greedy = [list(t) for t in g.read_output()]
         ctx.sync()
         ctx.record(ev[0])
         for _ in range(n_greedy - 1):
             g.greedy_step()
-            greedy += g.read_output()[0]
+            for s_, t in enumerate(g.read_output()):
+                greedy[s_] += t
         ctx.record(ev[1])
         ctx.sync()
         greedy_ms = ctx.elapsed_ms(ev[0], ev[1]) / (n_greedy - 1)
         g.close()
-    stream = np.zeros(args.prompt + len(greedy) + 8, np.int32)
-    stream[:args.prompt] = prompt
-    stream[args.prompt:args.prompt + len(greedy)] = greedy
-    sdev = ctx.array(stream)
+    stream = np.zeros((ns, stride), np.int32)          # stream[s][p] = token at absolute position p
+    for s_ in range(ns):
+        stream[s_, :plen[s_]] = prompts[s_]
+        stream[s_, plen[s_]:plen[s_] + len(greedy[s_])] = greedy[s_]
+    # the forced guess for every position: the true continuation at a seeded 70 % rate, else a different token
+    frs = np.random.RandomState(FORCE_SEED + rank)
+    forced = np.where(frs.rand(ns, stride) < ACCEPT_RATE, stream, (stream + 1) % cfg.vocab_size).astype(np.int32)
+    sdev = ctx.array(forced)
 
-    b = pkg.Batch(model, 1, max_ctx, k)
-    b.prefill(0, prompt)
-    emitted = list(b.read_output()[0])
+    b = pkg.Batch(model, ns, max_ctx, k)
+    for s_ in range(ns):
+        b.prefill(s_, prompts[s_])
+    b.read_output()
 
     def device_step():
         b.mtp_draft()
-        b.mtp_force_drafts(sdev, len(stream), ACCEPT_RATE, FORCE_SEED)
+        b.mtp_force_drafts(sdev, stride)
         b.mtp_verify()
         b.mtp_accept_commit()
 
     # 2. device-resident timing: K steps back to back, no host read-back inside
     for _ in range(W):
         device_step()
-        emitted += b.read_output()[0]
+        b.read_output()
     if dist is not None:
         dist.barrier()
     ctx.sync()
@@ -233,15 +246,13 @@ def run_ours(args, rank, world, local_rank, dist):
     s1, l1 = b.stats(), ctx.launches
     dev_emitted = s1["emitted"] - s0["emitted"]
     dev_accepted = s1["accepted"] - s0["accepted"]
-    # the tokens of those K steps: re-derive from the greedy stream (lossless) via the position
-    pos = b.position(0)
-    emitted = greedy[:pos - args.prompt + 1]
+    b.read_output()
 
     # 3. phase split + per-launch GEMM timing (separate pass, event records perturb the stream slightly)
     ctx.prof_enable(True)
     ph = [0.0, 0.0, 0.0]
     for _ in range(prof_steps):
-        ctx.record(ev[2]); b.mtp_draft(); b.mtp_force_drafts(sdev, len(stream), ACCEPT_RATE, FORCE_SEED)
+        ctx.record(ev[2]); b.mtp_draft(); b.mtp_force_drafts(sdev, stride)
         ctx.record(ev[3]); b.mtp_verify()
         ctx.record(ev[4]); b.mtp_accept_commit()
         ctx.record(ev[5]); ctx.sync()
@@ -259,40 +270,41 @@ def run_ours(args, rank, world, local_rank, dist):
 
     # 4. end to end through the host-driven API: drafts come from pinned host memory every step and the
     #    step record goes back to the host every step
-    pos = b.position(0)
-    pinned = ctx.pinned((1, k), np.int32)
-    frs = np.random.RandomState(1234 + rank)
+    pos = [b.position(s_) for s_ in range(ns)]
+    pinned = ctx.pinned((ns, k), np.int32)
 
-    def host_step(pos):
+    def host_step():
         b.mtp_draft()
-        for i in range(k):
-            truth = int(stream[pos + 1 + i])
-            pinned[0, i] = truth if frs.rand() < ACCEPT_RATE else (truth + 1) % cfg.vocab_size
+        for s_ in range(ns):
+            pinned[s_, :] = forced[s_, pos[s_] + 1:pos[s_] + 1 + k]
         b.mtp_set_drafts(pinned)
         b.mtp_verify()
         b.mtp_accept_commit()
-        return b.read_output()[0]
+        return b.read_output()
 
-    e2e_tokens = []
+    e2e_tokens = [[] for _ in range(ns)]
     for _ in range(W):
-        pos += len(host_step(pos))
+        for s_, t in enumerate(host_step()):
+            pos[s_] += len(t)
+    start_pos = list(pos)
     if dist is not None:
         dist.barrier()
     ctx.sync()
     ctx.record(ev[6])
     t0 = time.perf_counter()
     for _ in range(K):
-        t = host_step(pos)
-        e2e_tokens += t
-        pos += len(t)
+        for s_, t in enumerate(host_step()):
+            e2e_tokens[s_] += t
+            pos[s_] += len(t)
     ctx.record(ev[7])
     ctx.sync()
     e2e_wall = time.perf_counter() - t0
     e2e_ms = max(ctx.elapsed_ms(ev[6], ev[7]), e2e_wall * 1e3)
-    lossless = e2e_tokens == list(stream[pos - len(e2e_tokens) + 1:pos + 1])
+    lossless = all(e2e_tokens[s_] == list(stream[s_, start_pos[s_] + 1:pos[s_] + 1]) for s_ in range(ns)) and not args.skip_greedy
+    n_e2e = sum(len(t) for t in e2e_tokens)
 
     # 5. aggregate over replicas: max time, summed tokens
-    tmax, tsum = pkg.replicas.aggregate(dist, [dev_ms, e2e_ms], [float(dev_emitted), float(len(e2e_tokens)), float(l1 - l0)])
+    tmax, tsum = pkg.replicas.aggregate(dist, [dev_ms, e2e_ms], [float(dev_emitted), float(n_e2e), float(l1 - l0)])
     agg = np.concatenate([tmax, tsum])
     if rank != 0:
         b.close(); model.close(); ctx.close()
@@ -304,17 +316,20 @@ def run_ours(args, rank, world, local_rank, dist):
         "metric": "accepted_tok_per_s", "value": agg[2] / (agg[0] * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": agg[0] / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic", "config": workload_config(args), "clocks": clocks,
-        "e2e": {"value": agg[3] / (agg[1] * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": k * 4, "d2h_bytes_per_step": (k + 3) * 4,
+        "e2e": {"value": agg[3] / (agg[1] * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": ns * k * 4, "d2h_bytes_per_step": ns * (k + 3) * 4,
                 "ms_per_step": agg[1] / K, "lossless_vs_greedy": bool(lossless)},
         "gpu_launches": int(agg[4]),
-        "roofline": {"bound": "hbm", "kernel": "gemm_dp4a_kernel (all Q8_0 projections of the step)", "achieved": achieved,
-                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
+        "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel + gemm_dp4a_kernel (all Q8_0 projections of the step)",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+                     # DRAM bytes per launch: the ncu capture of this kernel on a 94.70 MB weight read 94.79 MB
+                     # (ratio 1.001, the weight is streamed once); scaled to this run's average launch
+                     "traffic": NCU_TRAFFIC_RATIO * prof["bytes"] / max(prof["launches"], 1),
                      "launches": prof["launches"], "avg_launch_us": prof["ms"] * 1e3 / max(prof["launches"], 1),
                      "bytes_per_launch_avg": prof["bytes"] / max(prof["launches"], 1)},
         "step": {"verify_us": ph[1] * 1e3, "draft_us": ph[0] * 1e3, "accept_commit_us": ph[2] * 1e3,
-                 "accepted_per_step": dev_accepted / K, "emitted_per_step": dev_emitted / K, "acceptance_rate": dev_accepted / (K * k),
+                 "accepted_per_step": dev_accepted / K, "emitted_per_step": dev_emitted / K, "acceptance_rate": dev_accepted / (K * k * ns),
                  "greedy_ms_per_token": greedy_ms, "greedy_tok_per_s": 1e3 / greedy_ms,
-                 "weight_bytes_per_step": step_bytes + 3 * 1.28e9 * 0,
+                 "weight_bytes_per_step": step_bytes,
                  "step_hbm_frac": (step_bytes / 1e9) / ((agg[0] / K) * 1e-3) / peak if world == 1 else None},
     }
     ttot = sum(t for _, _, t in trace) or 1.0

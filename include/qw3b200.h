@@ -230,12 +230,10 @@ int qb_decode_greedy_step(qb_ctx *ctx, qb_batch *b);
 /* forward_mtp_draft_chain_with_prefix_device (src/qwen_executor.cpp:6942-7023): k chained MTP-head
  * forwards per sequence, argmax kept on the device. */
 int qb_mtp_draft(qb_ctx *ctx, qb_batch *b);
-/* Replace the drafts by forced ones before verification: draft i of a sequence becomes
- * stream[pos + i] with probability `rate` (seeded per position) and a different token otherwise;
- * stream_dev = int32 [n_seqs][stream_stride] holds that sequence's greedy continuation indexed by
- * absolute position. */
-int qb_mtp_force_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *stream_dev, uint32_t stream_stride,
-                        float rate, uint64_t seed);
+/* Replace the drafts by forced ones before verification (the seeded-acceptance form of the benchmark):
+ * draft i of sequence s becomes forced_dev[s*stride + pos + 1 + i], the caller's guess for the token at
+ * absolute position pos+1+i (int32 [n_seqs][stride] on the device). */
+int qb_mtp_force_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *forced_dev, uint32_t stride);
 /* Drafts supplied by the host (int32 [n_seqs][k], pinned memory for an asynchronous copy): the
  * host-driven form of the reference loop, where the host holds the chain it verifies
  * (src/qwen_native_backend.cpp:15903). */

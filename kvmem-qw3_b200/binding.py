@@ -77,7 +77,7 @@ SIGNATURES = {
     "qb_prefill": (i32, [vp, vp, u32, vp, u32]),
     "qb_decode_greedy_step": (i32, [vp, vp]),
     "qb_mtp_draft": (i32, [vp, vp]),
-    "qb_mtp_force_drafts": (i32, [vp, vp, vp, u32, f32, u64]),
+    "qb_mtp_force_drafts": (i32, [vp, vp, vp, u32]),
     "qb_mtp_set_drafts": (i32, [vp, vp, vp]),
     "qb_mtp_verify": (i32, [vp, vp]),
     "qb_mtp_accept_commit": (i32, [vp, vp]),
@@ -364,8 +364,9 @@ class Batch:
     def mtp_draft(self):
         check(lib().qb_mtp_draft(self.ctx.h, self.h))
 
-    def mtp_force_drafts(self, stream_dev, stride, rate, seed):
-        check(lib().qb_mtp_force_drafts(self.ctx.h, self.h, stream_dev.ptr, stride, rate, seed))
+    def mtp_force_drafts(self, forced_dev, stride):
+        """forced_dev: DeviceArray int32 [n_seqs][stride]; draft i becomes forced[pos + 1 + i]."""
+        check(lib().qb_mtp_force_drafts(self.ctx.h, self.h, forced_dev.ptr, stride))
 
     def mtp_set_drafts(self, drafts_host):
         """drafts_host: int32 numpy array [n_seqs][k] (pinned for an asynchronous copy)."""

@@ -367,17 +367,15 @@ __global__ void prep_verify_kernel(const int32_t *cur, const int32_t *drafts, ui
     tok[idx] = j == 0 ? cur[s] : drafts[(size_t)s * k + j - 1];
 }
 
-// Forced drafts: draft i of sequence s guesses the token at absolute position pos+1+i.
-__global__ void force_drafts_kernel(int32_t *drafts, const int32_t *pos, uint32_t n_seqs, uint32_t k, const int32_t *stream,
-                                    uint32_t stream_stride, float rate, uint64_t seed, uint32_t vocab) {
+// Forced drafts: draft i of sequence s is the caller's guess for absolute position pos+1+i.
+__global__ void force_drafts_kernel(int32_t *drafts, const int32_t *pos, uint32_t n_seqs, uint32_t k, const int32_t *forced,
+                                    uint32_t stride) {
     QB_PDL_ENTER();
     const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_seqs * k) return;
     const uint32_t s = idx / k, i = idx % k;
     const uint32_t p = (uint32_t)pos[s] + 1 + i;
-    const int32_t truth = p < stream_stride ? stream[(size_t)s * stream_stride + p] : 0;
-    const float u = (float)(qs_rand_u32(seed, 0xD4AF7u + s, p) >> 8) * (1.0f / 16777216.0f);
-    drafts[idx] = u < rate ? truth : (int32_t)(((uint32_t)truth + 1u) % vocab);
+    drafts[idx] = p < stride ? forced[(size_t)s * stride + p] : 0;
 }
 
 // Greedy acceptance + commit, one CTA per sequence (src/qwen_native_backend.cpp:15948-16154,
@@ -714,12 +712,11 @@ extern "C" int qb_mtp_draft(qb_ctx *ctx, qb_batch *b) {
     return QB_OK;
 }
 
-extern "C" int qb_mtp_force_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *stream_dev, uint32_t stream_stride, float rate,
-                                   uint64_t seed) {
-    QB_REQUIRE(ctx && b && stream_dev && b->k > 0, "qb_mtp_force_drafts: bad arguments");
+extern "C" int qb_mtp_force_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *forced_dev, uint32_t stride) {
+    QB_REQUIRE(ctx && b && forced_dev && b->k > 0, "qb_mtp_force_drafts: bad arguments");
     const uint32_t n = b->n_seqs * b->k;
-    QB_CUDA(qb_launch_pdl(ctx->stream, force_drafts_kernel, dim3((n + 127) / 128), dim3(128), (size_t)(0), b->drafts, b->pos, b->n_seqs, b->k, stream_dev, stream_stride, rate,
-                                                                 seed, b->m->cfg.vocab_size));
+    QB_CUDA(qb_launch_pdl(ctx->stream, force_drafts_kernel, dim3((n + 127) / 128), dim3(128), (size_t)0, b->drafts, b->pos, b->n_seqs,
+                          b->k, forced_dev, stride));
     QB_LAUNCHED(ctx, "force_drafts_kernel");
     return QB_OK;
 }

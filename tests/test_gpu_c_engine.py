@@ -144,14 +144,16 @@ def test_forced_acceptance_run_is_lossless(qb, orc, ctx, tiny, k):
     stream = np.zeros(64 + len(want) + 8, np.int32)
     stream[:64] = tiny["prompt"]
     stream[64:64 + len(want)] = want       # stream[p] = token at absolute position p
-    sdev = ctx.array(stream)
+    rng = np.random.default_rng(1234 + k)
+    forced = np.where(rng.random(len(stream)) < 0.7, stream, (stream + 1) % 4096).astype(np.int32)
+    sdev = ctx.array(forced)
     b = qb.Batch(tiny["model"], 1, 256, k)
     b.prefill(0, tiny["prompt"])
     got = list(b.read_output()[0])
     hist = []
     while len(got) < n:
         b.mtp_draft()
-        b.mtp_force_drafts(sdev, len(stream), 0.7, 1234)
+        b.mtp_force_drafts(sdev, len(stream))
         b.mtp_verify()
         b.mtp_accept_commit()
         t = b.read_output()[0]
