@@ -268,8 +268,14 @@ def run_ours(args, rank, world, local_rank, dist):
     ctx.trace_enable(False)
     b.read_output()
 
-    # 4. end to end through the host-driven API: drafts come from pinned host memory every step and the
+    # 4. end to end through the host-driven API, on a fresh batch that replays the same trajectory (same
+    #    prompt, same warm-up, same forced guesses): drafts come from pinned host memory every step and the
     #    step record goes back to the host every step
+    b.close()
+    b = pkg.Batch(model, ns, max_ctx, k)
+    for s_ in range(ns):
+        b.prefill(s_, prompts[s_])
+    b.read_output()
     pos = [b.position(s_) for s_ in range(ns)]
     pinned = ctx.pinned((ns, k), np.int32)
 

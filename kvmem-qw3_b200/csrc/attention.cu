@@ -56,7 +56,7 @@ __global__ void qk_norm_rope_append_kernel(AttnArgs a, const int32_t *__restrict
     if (unit < a.n_heads) { base = rowp + (size_t)unit * 2 * hd; w = a.q_norm_w; kind = 0; }
     else if (unit < a.n_heads + a.n_kv) { base = rowp + (size_t)a.n_heads * 2 * hd + (size_t)(unit - a.n_heads) * hd; w = a.k_norm_w; kind = 1; }
     else { base = rowp + (size_t)a.n_heads * 2 * hd + kvd + (size_t)(unit - a.n_heads - a.n_kv) * hd; kind = 2; }
-    float v = base[i];
+    float v = qb_ldsum(base, i, a.in_S, a.in_pstride);
     if (kind != 2) {
         float ss = warp_sum(v * v);
         if ((i & 31) == 0) red[i >> 5] = ss;
@@ -300,7 +300,7 @@ __global__ void attn_merge_kernel(AttnArgs a, const int32_t *__restrict__ seq_po
         }
         for (; s < cnt; ++s) { num = fmaf(acc[(size_t)s * hd], wsplit[s], num); den = fmaf(ml[s * 2], wsplit[s], den); }
     }
-    const float gate = a.qkv[(size_t)row * a.row_stride + (size_t)head * 2 * hd + hd + i];
+    const float gate = qb_ldsum(a.qkv, (size_t)row * a.row_stride + (size_t)head * 2 * hd + hd + i, a.in_S, a.in_pstride);
     const float o = __fdiv_rn(num, den) * __fdiv_rn(1.0f, 1.0f + expf(-gate));
     const uint32_t col = head * hd + i;
     if (out) out[(size_t)row * a.n_heads * hd + col] = o;

@@ -36,9 +36,11 @@ __global__ void __launch_bounds__(HD) dn_conv_kernel(DnArgs a) {
     for (int k = 0; k < 3; ++k) st[k] = conv_seq[((size_t)slot * C + c) * 3 + k];
 #pragma unroll
     for (int k = 0; k < 4; ++k) w[k] = a.conv_w[(size_t)c * 4 + k];
+    float nxt = qb_ldsum(a.proj, (size_t)seq * R * a.proj_stride + c, a.proj_S, a.proj_pstride);
     for (uint32_t t = 0; t < R; ++t) {
         const size_t row = (size_t)seq * R + t;
-        const float cur = a.proj[row * a.proj_stride + c];
+        const float cur = nxt;
+        if (t + 1 < R) nxt = qb_ldsum(a.proj, (row + 1) * a.proj_stride + c, a.proj_S, a.proj_pstride);   // next row's load overlaps this row
         float acc = w[3] * cur;
 #pragma unroll
         for (int k = 0; k < 3; ++k) acc += w[k] * st[k];
@@ -86,25 +88,39 @@ __global__ void __launch_bounds__(128) dn_delta_kernel(DnArgs a) {
             s[cc][r] = state_seq[(size_t)slot * ssz + ((size_t)vh * HD + col0 + cc) * HD + r * 32 + lane];
     const float oscale = rsqrtf((float)HD);
     const float A = a.ssm_a[vh], bias = a.dt_bias[vh];
-    for (uint32_t t = 0; t < R; ++t) {
+    // operands of one row; the next row's are requested before this row's arithmetic
+    struct RowIn { float ga, gb, q[RPL], k[RPL], xv[CPW]; };
+    auto load_row = [&](uint32_t t) {
+        RowIn in;
         const size_t row = (size_t)seq * R + t;
         const float *x = a.xconv + row * C;
-        const float *pr = a.proj + row * a.proj_stride;
-        const float g = expf(log1pf(expf(pr[C + vdim + vh] + bias)) * A);
-        const float beta = __fdiv_rn(1.0f, 1.0f + expf(-pr[C + vdim + a.nv + vh]));
-        float kr[RPL], qr[RPL];
+        const size_t pr = row * a.proj_stride + C + vdim;
+        in.ga = qb_ldsum(a.proj, pr + vh, a.proj_S, a.proj_pstride);
+        in.gb = qb_ldsum(a.proj, pr + a.nv + vh, a.proj_S, a.proj_pstride);
 #pragma unroll
         for (int r = 0; r < RPL; ++r) {
-            qr[r] = x[kh * HD + r * 32 + lane];
-            kr[r] = x[a.nk * HD + kh * HD + r * 32 + lane];
+            in.q[r] = x[kh * HD + r * 32 + lane];
+            in.k[r] = x[a.nk * HD + kh * HD + r * 32 + lane];
         }
+#pragma unroll
+        for (int cc = 0; cc < CPW; ++cc) in.xv[cc] = x[2 * a.nk * HD + vh * HD + col0 + cc];
+        return in;
+    };
+    RowIn nxt = load_row(0);
+    for (uint32_t t = 0; t < R; ++t) {
+        const size_t row = (size_t)seq * R + t;
+        const RowIn in = nxt;
+        if (t + 1 < R) nxt = load_row(t + 1);
+        const float g = expf(log1pf(expf(in.ga + bias)) * A);
+        const float beta = __fdiv_rn(1.0f, 1.0f + expf(-in.gb));
+        const float *kr = in.k, *qr = in.q;
 #pragma unroll
         for (int cc = 0; cc < CPW; ++cc) {
             float kv = 0.0f;
 #pragma unroll
             for (int r = 0; r < RPL; ++r) kv += s[cc][r] * kr[r];
             kv = warp_sum(kv);
-            const float delta = (x[2 * a.nk * HD + vh * HD + col0 + cc] - g * kv) * beta;
+            const float delta = (in.xv[cc] - g * kv) * beta;
             float at = 0.0f;
 #pragma unroll
             for (int r = 0; r < RPL; ++r) {
@@ -143,7 +159,7 @@ __global__ void __launch_bounds__(HD) dn_normgate_kernel(DnArgs a) {
     float tot = 0.0f;
 #pragma unroll
     for (int k = 0; k < HD / 32; ++k) tot += red[k];
-    const float z = a.proj[(size_t)row * a.proj_stride + C + vh * HD + i];
+    const float z = qb_ldsum(a.proj, (size_t)row * a.proj_stride + C + vh * HD + i, a.proj_S, a.proj_pstride);
     const float o = v * rsqrtf(tot / (float)HD + a.eps) * a.norm_w[i] * __fdiv_rn(z, 1.0f + expf(-z));
     const uint32_t col = vh * HD + i;
     if (a.core_out) a.core_out[(size_t)row * vdim + col] = o;

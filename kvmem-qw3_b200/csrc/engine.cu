@@ -287,7 +287,7 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
             const uint32_t S = qb_ksplit(N, K);
             if (S > 1 || always) per_row = std::max(per_row, (size_t)S * N);
         };
-        consider(m->attn_in(), H, false); consider(m->dn_in(), H, false); consider(2 * F, H, false); consider(V, H, false);
+        consider(m->attn_in(), H, true); consider(m->dn_in(), H, true); consider(2 * F, H, false); consider(V, H, false);
         consider(H, inner, true); consider(H, vdim, true); consider(H, F, true); consider(H, 2 * H, true);
         b->parts_floats = std::max<size_t>(per_row, 1) * rows;
         QB_CUDA(cudaMalloc(&b->parts, b->parts_floats * sizeof(float)));
@@ -525,8 +525,10 @@ static int attention_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t c
         a.qkv = b->act; a.row_stride = 2 * m->kvd(); a.n_heads = 0;
         return qb_attn_prepare(ctx, a, rs.seq_pos, rs.ns);
     }
-    a.qkv = b->act; a.row_stride = m->attn_in();
-    QB_TRY(gemm_to(ctx, b, L.w_in, b->xq_h, rows, b->act));
+    // the consumers of the fused projection add its split partials themselves
+    uint32_t S_in = 1;
+    QB_TRY(gemm_parts(ctx, b, L.w_in, b->xq_h, rows, &S_in));
+    a.qkv = b->parts; a.row_stride = m->attn_in(); a.in_S = S_in; a.in_pstride = (size_t)rows * m->attn_in();
     QB_TRY(qb_attn_prepare(ctx, a, rs.seq_pos, rs.ns));
     QB_TRY(qb_attn_run(ctx, a, rs.seq_pos, rs.ns, nullptr, b->xq_attn.q, b->xq_attn.K, b->xq_attn.d, qb_act_ld(rows)));
     uint32_t S = 1;
@@ -548,9 +550,11 @@ static int deltanet_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t il
     qb_model *m = b->m;
     const qb_model_config &c = m->cfg;
     const uint32_t rows = rs.rows(), K1 = b->k + 1;
-    QB_TRY(gemm_to(ctx, b, L.w_in, b->xq_h, rows, b->act));
+    uint32_t S_in = 1;
+    QB_TRY(gemm_parts(ctx, b, L.w_in, b->xq_h, rows, &S_in));
     DnArgs d;
-    d.proj = b->act; d.proj_stride = m->dn_in(); d.n_seqs = rs.ns; d.rows_per_seq = rs.R;
+    d.proj = b->parts; d.proj_stride = m->dn_in(); d.proj_S = S_in; d.proj_pstride = (size_t)rows * m->dn_in();
+    d.n_seqs = rs.ns; d.rows_per_seq = rs.R;
     d.conv_w = L.conv_w; d.ssm_a = L.ssm_a; d.dt_bias = L.dt_bias; d.norm_w = m->ones;
     d.nk = c.ssm_num_k_heads; d.nv = c.ssm_num_v_heads; d.hd = c.ssm_head_dim; d.eps = c.rms_eps;
     d.state = b->state[il] + (size_t)rs.seq0 * K1 * c.ssm_num_v_heads * c.ssm_head_dim * c.ssm_head_dim;

@@ -166,8 +166,9 @@ __global__ void block_dots_kernel(const uint8_t *__restrict__ rec, uint32_t K, u
 
 uint32_t qb_ksplit(uint32_t N, uint32_t K) {
     const uint32_t tiles = (N + 127) / 128, nchunks = K / 128;
-    // about one (row tile, segment) unit per SM of a 148-SM part, at most 8 segments
-    uint32_t S = 148 / std::max(tiles, 1u);
+    // about one (row tile, segment) unit per resident CTA of the small-batch kernel (two per SM on a 148-SM
+    // part), at most 8 segments.  The count depends on the weight's shape only, never on the batch.
+    uint32_t S = 296 / std::max(tiles, 1u);
     S = std::max(1u, std::min(S, 8u));
     S = std::min(S, std::max(nchunks, 1u));
     return S;

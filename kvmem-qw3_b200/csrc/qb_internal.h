@@ -138,6 +138,15 @@ int qb_make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, uint32_t elem_byte
 static inline uint32_t qb_act_ld(uint32_t M) { return (M + 3u) & ~3u; }
 
 // x (+ optional residual / split partials) -> optional h_out -> optional RMSNorm -> int8 + scales.
+// Sum of the S split partials of one GEMM output element, ascending (the order of the split reduction).
+__device__ __forceinline__ float qb_ldsum(const float *p, size_t idx, uint32_t S, size_t pstride) {
+    const float p0 = p[idx];
+    const float p1 = S > 1 ? p[idx + pstride] : 0.0f;      // both loads in flight before the add
+    float v = S > 1 ? p0 + p1 : p0;
+    for (uint32_t s = 2; s < S; ++s) v += p[idx + s * pstride];
+    return v;
+}
+
 struct NormQuantArgs {
     const float *x = nullptr;        // [M][x_stride] or null (treated as zero)
     uint32_t x_stride = 0;
@@ -188,6 +197,8 @@ static const uint32_t QB_ARGMAX_BLOCKS = 64;
 // [s*R, (s+1)*R), R = rows / n_seqs, at positions seq_pos[s] .. seq_pos[s]+R-1 (seq_pos on the device).
 struct AttnArgs {
     float *qkv = nullptr; uint32_t rows = 0, row_stride = 0;   // rows [q(+gate) | k | v]
+    uint32_t in_S = 1; size_t in_pstride = 0;                  // qkv holds in_S split partials, in_pstride floats apart
+                                                               // (summed ascending on read; q is finalised in partial 0)
     uint32_t n_heads = 0, n_kv = 0, hd = 0, rope_dim = 0; float eps = 0.f;
     const float *q_norm_w = nullptr, *k_norm_w = nullptr, *inv_freq = nullptr;
     const int32_t *page_table = nullptr;
@@ -207,6 +218,7 @@ static const uint32_t QB_ATTN_SPLIT = 64;    // keys per split (one tile), fixed
 
 struct DnArgs {
     const float *proj = nullptr; uint32_t proj_stride = 0;   // rows [qkv | z | alpha | beta]
+    uint32_t proj_S = 1; size_t proj_pstride = 0;            // proj holds proj_S split partials, summed ascending on read
     uint32_t n_seqs = 0, rows_per_seq = 0;                   // rows of sequence s: [s*rows_per_seq, ...)
     const float *conv_w = nullptr, *ssm_a = nullptr, *dt_bias = nullptr, *norm_w = nullptr;
     uint32_t nk = 0, nv = 0, hd = 0; float eps = 0.f;

@@ -73,70 +73,145 @@ extern "C" int qb_quantize_q8_1_mmq(qb_ctx *ctx, const float *x_dev, uint32_t M,
 }
 
 // ---- fused: (x + split partials) -> residual stream -> RMSNorm -> int8 ----------------------
-// One CTA of 1024 threads per row.  Pass 1 only loads (x and the split partials, independent loads the
-// compiler can keep in flight together) and stages the row in shared memory; pass 2 writes the residual
-// stream, the normalised copy and the int8 blocks.
-template <int THREADS>
-__global__ void __launch_bounds__(THREADS) norm_quant_kernel(NormQuantArgs a) {
+// A thread-block cluster of 8 CTAs works on one row: CTA c owns a contiguous eighth of the row's 32-blocks,
+// a thread owns 4 consecutive elements (8 threads per 32-block, 16-byte loads and stores), everything stays in
+// registers.  The sum of squares crosses the cluster once: every CTA pushes its partial into the shared memory
+// of all 8 (st.shared::cluster) and one cluster barrier later each CTA adds the 8 partials in rank order, so all
+// of them apply the same scale.  P = passes of 32 blocks per CTA.
+constexpr uint32_t NQ_CLUSTER = 8, NQ_THREADS = 256;
+
+__device__ __forceinline__ float4 ld4(const float *p, bool vec) {
+    if (vec) return *reinterpret_cast<const float4 *>(p);
+    return make_float4(p[0], p[1], p[2], p[3]);
+}
+__device__ __forceinline__ void st4(float *p, float4 v, bool vec) {
+    if (vec) *reinterpret_cast<float4 *>(p) = v;
+    else { p[0] = v.x; p[1] = v.y; p[2] = v.z; p[3] = v.w; }
+}
+
+template <int P>
+__global__ void __launch_bounds__(NQ_THREADS) norm_quant_kernel(NormQuantArgs a, uint32_t vec) {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");   // "this CTA runs": awaited before the pushes
     QB_PDL_ENTER();
-    extern __shared__ float row[];
-    __shared__ float red[THREADS / 32];
-    float *wsm = row + a.n;
-    const uint32_t m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float red[NQ_THREADS / 32];
+    __shared__ float cl_part[NQ_CLUSTER];
+    uint32_t crank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+    const uint32_t m = blockIdx.x / NQ_CLUSTER, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t nblk = a.n / 32, per = (nblk + NQ_CLUSTER - 1) / NQ_CLUSTER;
+    const uint32_t b0 = crank * per, b1 = min(nblk, b0 + per), sub = tid & 7;
     const uint32_t src = a.row_map ? (uint32_t)a.row_map[m] : m;
     const float *__restrict__ x = a.x ? a.x + (size_t)src * a.x_stride : nullptr;
     const float *__restrict__ parts = a.parts ? a.parts + (size_t)m * a.part_ld : nullptr;
     const size_t pstride = (size_t)a.M * a.part_ld;
+    const bool vx = vec & 1, vp = vec & 2, vh = vec & 4;
+
+    float4 v[P], g[P];
     float ss = 0.0f;
-#pragma unroll 4
-    for (uint32_t i = tid; i < a.n; i += THREADS) {
-        float v = x ? x[i] : 0.0f;
-        if (a.S > 0) {   // GEMM result first (segments ascending), then the residual
-            float p[8];  // all segment loads are issued before the first add (S <= 8)
 #pragma unroll
-            for (uint32_t s = 0; s < 8; ++s) p[s] = s < a.S ? parts[s * pstride + i] : 0.0f;
-            float y = p[0];
+    for (int p = 0; p < P; ++p) {
+        const uint32_t b = b0 + (tid >> 3) + 32 * p;
+        v[p] = make_float4(0.f, 0.f, 0.f, 0.f);
+        g[p] = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (b < b1) {
+            const uint32_t i = b * 32 + sub * 4;
+            float4 xv = x ? ld4(x + i, vx) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (a.w) g[p] = ld4(a.w + i, true);
+            if (a.S > 0) {   // GEMM result first (segments ascending), then the residual
+                float4 q[8];  // all segment loads are issued before the first add (S <= 8)
 #pragma unroll
-            for (uint32_t s = 1; s < 8; ++s) if (s < a.S) y += p[s];
-            v = x ? v + y : y;
+                for (uint32_t s = 0; s < 8; ++s) q[s] = s < a.S ? ld4(parts + s * pstride + i, vp) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 y = q[0];
+#pragma unroll
+                for (uint32_t s = 1; s < 8; ++s)
+                    if (s < a.S) { y.x += q[s].x; y.y += q[s].y; y.z += q[s].z; y.w += q[s].w; }
+                if (x) { xv.x += y.x; xv.y += y.y; xv.z += y.z; xv.w += y.w; } else xv = y;
+            }
+            v[p] = xv;
+            ss += xv.x * xv.x; ss += xv.y * xv.y; ss += xv.z * xv.z; ss += xv.w * xv.w;
         }
-        row[i] = v;
-        wsm[i] = a.w ? a.w[i] : 1.0f;    // gains staged now: pass 2 has no global load in its dependency chain
-        ss += v * v;
     }
     float scale = 1.0f;
-    ss = warp_sum(ss);
-    if (lane == 0) red[warp] = ss;
-    __syncthreads();
-    if (a.w) {
+    if (a.w) {   // uniform over the cluster
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");            // all 8 CTAs are running
+        if (tid < NQ_CLUSTER) {
+            float tot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < (int)NQ_THREADS / 32; ++i) tot += red[i];
+            uint32_t local = (uint32_t)__cvta_generic_to_shared(&cl_part[crank]), remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(tid));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(tot) : "memory");
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         float tot = 0.0f;
 #pragma unroll
-        for (int i = 0; i < THREADS / 32; ++i) tot += red[i];
+        for (int i = 0; i < (int)NQ_CLUSTER; ++i) tot += cl_part[i];
         scale = rsqrtf(tot / (float)a.n + a.eps);
     }
-    const uint32_t nblk = a.n / 32;
-    for (uint32_t b = warp; b < nblk; b += THREADS / 32) {
-        const uint32_t i = b * 32 + lane;
-        float v = row[i];
-        if (a.h_out) a.h_out[(size_t)m * a.h_stride + i] = v;
-        if (a.w) v = v * scale * wsm[i];
-        if (a.normed_out) a.normed_out[(size_t)m * a.n + i] = v;
-        if (a.q)
-            quant_block_store(v, lane, a.q + (size_t)m * a.q_pitch + a.q_col_off + b * 32,
-                              a.d + (size_t)(a.d_kb_off + b) * a.d_ld + m);
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+        const uint32_t b = b0 + (tid >> 3) + 32 * p;
+        if (b >= b1) continue;          // whole 8-thread groups leave together; the shuffles below stay inside a group
+        const uint32_t i = b * 32 + sub * 4;
+        float4 t = v[p];
+        if (a.h_out) st4(a.h_out + (size_t)m * a.h_stride + i, t, vh);
+        if (a.w) {
+            t.x = t.x * scale * g[p].x; t.y = t.y * scale * g[p].y; t.z = t.z * scale * g[p].z; t.w = t.w * scale * g[p].w;
+        }
+        if (a.normed_out) st4(a.normed_out + (size_t)m * a.n + i, t, true);
+        if (a.q) {
+            // arithmetic of quantize_mmq_q8_1_kernel (src/mmvq_q8.cu:694-721)
+            const uint32_t grp = 0xffu << (lane & 24);
+            float amax = fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w)));
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(grp, amax, o));
+            const float d_inv = (amax == 0.0f) ? 0.0f : __fdiv_rn(127.0f, amax);
+            uint32_t packed = 0;
+            if (amax != 0.0f) {
+                const int q0 = __float2int_rn(__fmul_rn(t.x, d_inv)), q1 = __float2int_rn(__fmul_rn(t.y, d_inv));
+                const int q2 = __float2int_rn(__fmul_rn(t.z, d_inv)), q3 = __float2int_rn(__fmul_rn(t.w, d_inv));
+                packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+            }
+            *reinterpret_cast<uint32_t *>(a.q + (size_t)m * a.q_pitch + a.q_col_off + i) = packed;
+            if (sub == 0) a.d[(size_t)(a.d_kb_off + b) * a.d_ld + m] = (amax == 0.0f) ? 0.0f : __fdiv_rn(1.0f, d_inv);
+        }
     }
+    if (!a.w) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // complete the opening arrive
+}
+
+template <int P>
+static cudaError_t launch_norm_quant(cudaStream_t stream, const NormQuantArgs &a, uint32_t vec) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a.M * NQ_CLUSTER);
+    cfg.blockDim = dim3(NQ_THREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = NQ_CLUSTER;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, norm_quant_kernel<P>, a, vec);
 }
 
 int qb_launch_norm_quant(qb_ctx *ctx, const NormQuantArgs &a) {
     QB_REQUIRE(a.M > 0 && a.n > 0 && a.n % 32 == 0 && a.S <= 8, "norm_quant: bad shape M=%u n=%u S=%u", a.M, a.n, a.S);
-    const size_t smem = 2 * (size_t)a.n * sizeof(float);
-    static bool attr_set = false;
-    if (!attr_set) {
-        QB_CUDA(cudaFuncSetAttribute(norm_quant_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-        attr_set = true;
-    }
-    QB_REQUIRE(smem <= 160 * 1024, "norm_quant: row of %u floats does not fit shared memory", a.n);
-    QB_CUDA(qb_launch_pdl(ctx->stream, norm_quant_kernel<1024>, dim3(a.M), dim3(1024), (size_t)(smem), a));
+    const uint32_t per = (a.n / 32 + NQ_CLUSTER - 1) / NQ_CLUSTER;
+    QB_REQUIRE(per <= 128, "norm_quant: row of %u floats is longer than the kernel's 32768", a.n);
+    QB_REQUIRE(((uintptr_t)a.w & 15) == 0 && ((uintptr_t)a.normed_out & 15) == 0 && ((uintptr_t)a.q & 3) == 0 &&
+               a.q_pitch % 4 == 0 && a.q_col_off % 4 == 0, "norm_quant: gain / output buffers must be 16-byte aligned");
+    auto al = [](const void *p, size_t stride) { return ((uintptr_t)p & 15) == 0 && stride % 4 == 0; };
+    const uint32_t vec = (al(a.x, a.x_stride) ? 1u : 0u) | (al(a.parts, a.part_ld) ? 2u : 0u) | (al(a.h_out, a.h_stride) ? 4u : 0u);
+    if (per <= 32) QB_CUDA(launch_norm_quant<1>(ctx->stream, a, vec));
+    else if (per <= 64) QB_CUDA(launch_norm_quant<2>(ctx->stream, a, vec));
+    else QB_CUDA(launch_norm_quant<4>(ctx->stream, a, vec));
     QB_LAUNCHED(ctx, "norm_quant_kernel");
     return QB_OK;
 }

@@ -107,7 +107,7 @@ inline uint32_t seg_begin(uint32_t s, uint32_t S, uint32_t nchunks) { return (ui
 uint32_t ksplit_policy(uint32_t N, uint32_t K) {
     const uint32_t tiles = (N + 127) / 128;
     const uint32_t nchunks = K / 128;
-    uint32_t S = 148 / std::max(tiles, 1u);
+    uint32_t S = 296 / std::max(tiles, 1u);
     S = std::max(1u, std::min(S, 8u));
     S = std::min(S, std::max(nchunks, 1u));
     return S;
