@@ -270,6 +270,12 @@ int qb_prof_summary(qb_ctx *ctx, double *total_ms, double *total_bytes, int64_t 
  * the preceding one, as "name<TAB>launches<TAB>microseconds" lines. */
 int qb_trace_enable(qb_ctx *ctx, int on);
 int qb_trace_summary(qb_ctx *ctx, char *buf, size_t buf_bytes);
+/* Device timeline of the tensor-core GEMM launches: after qb_debug_timeline_enable(ctx, n) the next n such
+ * launches record, per CTA, {entry, dependency wait passed, exit} in nanoseconds of the GPU's global timer
+ * and the SM id (4 uint64 per CTA, 320 CTA slots per launch).  qb_debug_timeline_read copies the recorded
+ * launches out: out = uint64 [n][320][4], grids[i] = CTAs of launch i.  enable(ctx, 0) frees the buffer. */
+int qb_debug_timeline_enable(qb_ctx *ctx, uint32_t max_launches);
+int qb_debug_timeline_read(qb_ctx *ctx, uint64_t *out, uint32_t *grids, uint32_t max_launches, uint32_t *n_out);
 /* Number of kernels this library launched on the context since creation. */
 int64_t qb_launch_count(qb_ctx *ctx);
 

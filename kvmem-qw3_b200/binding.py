@@ -92,6 +92,8 @@ SIGNATURES = {
     "qb_trace_enable": (i32, [vp, i32]),
     "qb_trace_summary": (i32, [vp, C.c_char_p, sz]),
     "qb_launch_count": (C.c_int64, [vp]),
+    "qb_debug_timeline_enable": (i32, [vp, u32]),
+    "qb_debug_timeline_read": (i32, [vp, vp, vp, u32, C.POINTER(u32)]),
 }
 
 
@@ -231,6 +233,17 @@ class Context:
             n, c, t = ln.split("\t")
             out.append((n, int(c), float(t)))
         return out
+
+    def timeline_enable(self, max_launches):
+        check(lib().qb_debug_timeline_enable(self.h, max_launches))
+
+    def timeline_read(self, max_launches):
+        """Returns (stamps uint64 [n][320][4] = entry, wait passed, exit (ns), SM id; grids [n])."""
+        out = np.zeros((max_launches, 320, 4), np.uint64)
+        grids = np.zeros(max_launches, np.uint32)
+        n = u32()
+        check(lib().qb_debug_timeline_read(self.h, _np_ptr(out), _np_ptr(grids), max_launches, C.byref(n)))
+        return out[:n.value], grids[:n.value]
 
     def pinned(self, shape, dtype):
         """Pinned host array (numpy view over cudaHostAlloc memory)."""

@@ -19,8 +19,6 @@
 // the CTA raises the context's error flag, lets its copies land, frees its TMEM and returns.
 #include "qb_internal.h"
 
-#include <cstdlib>
-
 namespace {
 
 constexpr int TC_THREADS = 192;
@@ -115,14 +113,14 @@ __host__ __device__ inline uint32_t tc_seg_begin(uint32_t s, uint32_t S, uint32_
 // A pipeline stage holds one weight record (17 KB, one bulk copy, already the swizzled operand image
 // plus its scales), the activation tile (MT x 128 B, tensor-map TMA with the 128-byte swizzle) and
 // the activation scales.  TMEM: every stage (MT <= 64) or half stage (MT = 128) has its own slot.
-template <int MT, int NLD, bool DEEP = false>
+template <int MT, int NLD>
 struct TcCfg {
     static constexpr int KPS = MT == 128 ? 2 : 4;              // 32-blocks per TMEM slot
     static constexpr int SPS = 4 / KPS;                        // slots per pipeline stage
     // Small tiles run two CTAs per SM (two independent producer/MMA/epilogue chains per SM: the per-stage
     // handshake chain of one CTA, not the memory system, limits a single chain to ~33 GB/s), so each CTA
     // takes half the tensor memory and half the shared memory.
-    static constexpr int CTAS_PER_SM = (MT == 16 && !DEEP) ? 2 : 1;
+    static constexpr int CTAS_PER_SM = MT == 16 ? 2 : 1;
     static constexpr int NSLOT = 512 / CTAS_PER_SM / (KPS * MT);
     static constexpr int TMEM_COLS = NSLOT * KPS * MT;
     static constexpr int B_OFF = (int)QB_REC_BYTES;            // 17 * 1024: the activation tile stays 1024-aligned
@@ -133,7 +131,7 @@ struct TcCfg {
     static constexpr int STAGE = (XD_OFF + XD_BYTES + 1023) / 1024 * 1024;
     static constexpr int BAR_BYTES = 1024;
     static constexpr int NST_FIT = (232448 / CTAS_PER_SM - BAR_BYTES - 2048) / STAGE;
-    static constexpr int NST = DEEP ? (NST_FIT > 12 ? 12 : NST_FIT) : (NST_FIT > 8 ? 8 : NST_FIT);
+    static constexpr int NST = NST_FIT > 8 ? 8 : NST_FIT;
     static constexpr int TOTAL = STAGE * NST + BAR_BYTES + 1024;   // + slack to align the base to 1024
     static constexpr int CH = NLD < 16 ? NLD : 16;               // columns per tcgen05.ld
 };
@@ -145,12 +143,12 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
 
 // Persistent kernel: CTA b works on units b, b + gridDim.x, ...; a unit is (activation tile, K segment,
 // 128-row weight tile).  The TMA / MMA / TMEM pipeline keeps running across unit boundaries.
-template <int MT, int NLD, bool DEEP>
+template <int MT, int NLD>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensorMap map_xq,
                const __grid_constant__ CUtensorMap map_xd, uint32_t K, uint32_t N, uint32_t M, float *__restrict__ part,
-               uint32_t S, uint32_t tiles, uint32_t units, int *err_flag) {
-    using C = TcCfg<MT, NLD, DEEP>;
+               uint32_t S, uint32_t tiles, uint32_t units, int *err_flag, unsigned long long *tl) {
+    using C = TcCfg<MT, NLD>;
     constexpr uint32_t NST = C::NST, NSLOT = C::NSLOT;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -224,10 +222,12 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
                 tma_load_2d(base + C::B_OFF, &map_xq, k0, (int)c.m0, full);
                 tma_load_2d(base + C::XD_OFF, &map_xd, (int)c.m0, k0 / 32, full);
             };
+            if (tl) tl[blockIdx.x * 4 + 0] = qb_globaltimer();
             Cursor head = start(blockIdx.x), c = head;
             uint32_t npre = 0;
             for (; npre < NST && c.valid; ++npre, next(c)) load_w(c, npre);
             asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (tl) tl[blockIdx.x * 4 + 1] = qb_globaltimer();
             c = head;
             for (uint32_t g = 0; g < npre; ++g, next(c)) load_x(c, g);
             for (uint32_t git = npre; c.valid; ++git, next(c)) {
@@ -372,6 +372,12 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
     }
     tc_fence_before();
     __syncthreads();
+    if (tl && threadIdx.x == 0) {
+        tl[blockIdx.x * 4 + 2] = qb_globaltimer();
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        tl[blockIdx.x * 4 + 3] = smid;
+    }
     if (*abort_flag) {
         if (threadIdx.x == 0) atomicExch(err_flag, 1000 + (int)(blockIdx.x % 1000));
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);      // let this CTA's copies in flight land
@@ -389,12 +395,12 @@ struct MapKey {
 };
 std::map<MapKey, CUtensorMap> g_xq_maps, g_xd_maps;
 
-template <int MT, int NLD, bool DEEP = false>
+template <int MT, int NLD>
 int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S) {
-    using C = TcCfg<MT, NLD, DEEP>;
+    using C = TcCfg<MT, NLD>;
     static bool attr = false;
     if (!attr) {
-        QB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MT, NLD, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
+        QB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MT, NLD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
         attr = true;
     }
     const uint32_t K = w->cols, ld = qb_act_ld(M);
@@ -425,8 +431,8 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
     attrs[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
-    QB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, NLD, DEEP>, (const uint8_t *)w->rec, iq->second, id->second, K, w->rows, M, part, S,
-                               tiles, units, ctx->err_flag_dev));
+    QB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, NLD>, (const uint8_t *)w->rec, iq->second, id->second, K, w->rows, M, part, S,
+                               tiles, units, ctx->err_flag_dev, qb_timeline_slot(ctx, grid)));
     QB_LAUNCHED(ctx, "gemm_tc_kernel");
     return QB_OK;
 }
@@ -440,8 +446,6 @@ bool qb_gemm_tc_supported(const qb_weight *w, uint32_t M) {
 int qb_launch_gemm_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S) {
     QB_REQUIRE(M > 0 && S > 0 && S <= w->cols / 128, "gemm: bad M=%u or ksplit=%u", M, S);
     QB_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)d & 15) == 0, "gemm: activation buffers must be 16-byte aligned");
-    static const bool deep = getenv("QW3B200_DEEP") != nullptr;
-    if (deep && M <= 4 && (w->rows_pad / 128) * S <= (uint32_t)ctx->sm_count) return launch_tc<16, 4, true>(ctx, w, q, d, M, part, S);
     if (M <= 4) return launch_tc<16, 4>(ctx, w, q, d, M, part, S);
     if (M <= 8) return launch_tc<16, 8>(ctx, w, q, d, M, part, S);
     if (M <= 16) return launch_tc<16, 16>(ctx, w, q, d, M, part, S);

@@ -83,6 +83,9 @@ struct qb_ctx {
     std::vector<const char *> trace_names;
     size_t trace_used = 0;
     // optional per-launch timing of the GEMM kernels (qb_prof_*): event pairs + algorithmic bytes
+    unsigned long long *tl_dev = nullptr;  // device timeline slots
+    uint32_t tl_cap = 0, tl_used = 0;
+    std::vector<uint32_t> tl_grid;
     bool prof_on = false;
     std::vector<cudaEvent_t> prof_ev;      // pool, two per recorded launch
     size_t prof_used = 0;
@@ -93,6 +96,18 @@ struct qb_ctx {
 };
 int qb_ctx_scratch(qb_ctx *ctx, size_t bytes, void **out);
 void qb_trace_mark(qb_ctx *ctx, const char *name);
+// Device timeline (qb_debug_timeline_*): while enabled every tensor-core GEMM launch gets a slot of
+// QB_TL_CTAS x 4 words; CTA b stores {entry, dependency wait passed, exit} in nanoseconds of the global
+// timer and its SM id.  Returns null when disabled or full.
+static const uint32_t QB_TL_CTAS = 320;
+unsigned long long *qb_timeline_slot(qb_ctx *ctx, uint32_t grid);
+#ifdef __CUDACC__
+__device__ __forceinline__ unsigned long long qb_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#endif
 
 // ---- Q8_0 weight in device layout ----------------------------------------------------------
 // The matrix is cut into records of 128 rows x 128 columns (4 Q8_0 blocks per row), stored row-tile
