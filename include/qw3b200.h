@@ -270,6 +270,36 @@ int qb_prof_summary(qb_ctx *ctx, double *total_ms, double *total_bytes, int64_t 
  * the preceding one, as "name<TAB>launches<TAB>microseconds" lines. */
 int qb_trace_enable(qb_ctx *ctx, int on);
 int qb_trace_summary(qb_ctx *ctx, char *buf, size_t buf_bytes);
+/* ---- tensor-parallel FFN pair over NVLink peer memory ------------------------------------------------
+ * The one sharded case of the path: the FFN dimension F is split over `world` GPUs (one process each).
+ * Rank r holds gate/up rows [r*F/world, (r+1)*F/world) fused as [gate_r; up_r] (2*f_shard x n_in) and the
+ * matching K slice of down (n_out x f_shard).  qb_tp_ffn = quantise x, gate/up GEMM, SwiGLU, down GEMM
+ * whose epilogue stores its split partials into every rank's receive area and signals, then a reduce
+ * that adds all ranks' partials in (rank, segment) order: every rank ends with the same bits, equal to
+ * sum_r sum_s partial[r][s].  Stands where the reference would place ncclAllReduce after a row-parallel
+ * q8_0_matmul (the reference itself runs one GPU per model replica and has no such call).
+ *
+ * Receive areas: one allocation of qb_tp_recv_bytes() per GPU (qb_malloc), 256-byte aligned, passed as
+ * recv_ptrs[world] with this rank's own at [rank] and the peers' as mapped by qb_ipc_open.  All ranks
+ * must have created their group (which zeroes its own arrival counters) before any rank pushes, and
+ * must call push/reduce with the same M in the same order.  A reduce whose peers never arrive gives up
+ * after about a second; the next qb_synchronize reports it. */
+typedef struct qb_tp_group qb_tp_group;
+size_t qb_tp_recv_bytes(uint32_t world, uint32_t max_rows, uint32_t n_out, uint32_t k_shard);
+int qb_tp_group_create(qb_ctx *ctx, uint32_t rank, uint32_t world, void *const *recv_ptrs, uint32_t max_rows,
+                       uint32_t n_in, uint32_t f_shard, uint32_t n_out, qb_tp_group **out);
+int qb_tp_group_destroy(qb_ctx *ctx, qb_tp_group *g);
+int qb_tp_ffn_push(qb_ctx *ctx, qb_tp_group *g, const qb_weight *gate_up_shard, const qb_weight *down_shard,
+                   const float *x_dev, uint32_t M);
+int qb_tp_ffn_reduce(qb_ctx *ctx, qb_tp_group *g, uint32_t M, float *y_dev, uint32_t y_stride);
+int qb_tp_ffn(qb_ctx *ctx, qb_tp_group *g, const qb_weight *gate_up_shard, const qb_weight *down_shard,
+              const float *x_dev, uint32_t M, float *y_dev, uint32_t y_stride);
+/* CUDA IPC: export a qb_malloc'ed buffer as a 64-byte handle another process opens (peer access is
+ * enabled on open). */
+int qb_ipc_export(qb_ctx *ctx, const void *dev_ptr, void *handle64);
+int qb_ipc_open(qb_ctx *ctx, const void *handle64, void **dev_ptr_out);
+int qb_ipc_close(qb_ctx *ctx, void *dev_ptr);
+
 /* Device timeline of the tensor-core GEMM launches: after qb_debug_timeline_enable(ctx, n) the next n such
  * launches record, per CTA, {entry, dependency wait passed, exit} in nanoseconds of the GPU's global timer
  * and the SM id (4 uint64 per CTA, 320 CTA slots per launch).  qb_debug_timeline_read copies the recorded

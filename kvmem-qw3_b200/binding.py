@@ -92,6 +92,15 @@ SIGNATURES = {
     "qb_trace_enable": (i32, [vp, i32]),
     "qb_trace_summary": (i32, [vp, C.c_char_p, sz]),
     "qb_launch_count": (C.c_int64, [vp]),
+    "qb_tp_recv_bytes": (sz, [u32, u32, u32, u32]),
+    "qb_tp_group_create": (i32, [vp, u32, u32, C.POINTER(vp), u32, u32, u32, u32, C.POINTER(vp)]),
+    "qb_tp_group_destroy": (i32, [vp, vp]),
+    "qb_tp_ffn_push": (i32, [vp, vp, vp, vp, vp, u32]),
+    "qb_tp_ffn_reduce": (i32, [vp, vp, u32, vp, u32]),
+    "qb_tp_ffn": (i32, [vp, vp, vp, vp, vp, u32, vp, u32]),
+    "qb_ipc_export": (i32, [vp, vp, vp]),
+    "qb_ipc_open": (i32, [vp, vp, C.POINTER(vp)]),
+    "qb_ipc_close": (i32, [vp, vp]),
     "qb_debug_timeline_enable": (i32, [vp, u32]),
     "qb_debug_timeline_read": (i32, [vp, vp, vp, u32, C.POINTER(u32)]),
 }

@@ -147,7 +147,8 @@ template <int MT, int NLD>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensorMap map_xq,
                const __grid_constant__ CUtensorMap map_xd, uint32_t K, uint32_t N, uint32_t M, float *__restrict__ part,
-               uint32_t S, uint32_t tiles, uint32_t units, int *err_flag, unsigned long long *tl) {
+               uint32_t S, uint32_t tiles, uint32_t units, int *err_flag, unsigned long long *tl,
+               const __grid_constant__ QbGemmPush push) {
     using C = TcCfg<MT, NLD>;
     constexpr uint32_t NST = C::NST, NSLOT = C::NSLOT;
     extern __shared__ uint8_t smem_raw[];
@@ -365,13 +366,22 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
 #pragma unroll
                 for (int i = 0; i < NLD; ++i) {
                     const uint32_t m = m0 + i;
-                    if (m < M) part[((size_t)seg * M + m) * N + row] = acc[i];
+                    if (m < M) {
+                        const size_t o = ((size_t)seg * M + m) * N + row;
+                        if (push.n == 0) part[o] = acc[i];
+                        else for (uint32_t p = 0; p < push.n; ++p) push.dst[p][o] = acc[i];
+                    }
                 }
             }
         }
+        if (push.n) __threadfence_system();     // this thread's partial sums are visible to every GPU before the CTA signals
     }
     tc_fence_before();
     __syncthreads();
+    if (push.n && threadIdx.x == 0) {
+        __threadfence_system();
+        for (uint32_t p = 0; p < push.n; ++p) atomicAdd_system(push.counter[p], 1u);
+    }
     if (tl && threadIdx.x == 0) {
         tl[blockIdx.x * 4 + 2] = qb_globaltimer();
         uint32_t smid;
@@ -396,7 +406,8 @@ struct MapKey {
 std::map<MapKey, CUtensorMap> g_xq_maps, g_xd_maps;
 
 template <int MT, int NLD>
-int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S) {
+int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S,
+              const QbGemmPush *push, uint32_t *grid_out) {
     using C = TcCfg<MT, NLD>;
     static bool attr = false;
     if (!attr) {
@@ -432,7 +443,8 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
     QB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, NLD>, (const uint8_t *)w->rec, iq->second, id->second, K, w->rows, M, part, S,
-                               tiles, units, ctx->err_flag_dev, qb_timeline_slot(ctx, grid)));
+                               tiles, units, ctx->err_flag_dev, qb_timeline_slot(ctx, grid), push ? *push : QbGemmPush()));
+    if (grid_out) *grid_out = grid;
     QB_LAUNCHED(ctx, "gemm_tc_kernel");
     return QB_OK;
 }
@@ -443,13 +455,14 @@ bool qb_gemm_tc_supported(const qb_weight *w, uint32_t M) {
     return w->rec != nullptr && M >= 1 && w->cols % 128 == 0;
 }
 
-int qb_launch_gemm_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S) {
+int qb_launch_gemm_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S,
+                      const QbGemmPush *push, uint32_t *grid_out) {
     QB_REQUIRE(M > 0 && S > 0 && S <= w->cols / 128, "gemm: bad M=%u or ksplit=%u", M, S);
     QB_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)d & 15) == 0, "gemm: activation buffers must be 16-byte aligned");
-    if (M <= 4) return launch_tc<16, 4>(ctx, w, q, d, M, part, S);
-    if (M <= 8) return launch_tc<16, 8>(ctx, w, q, d, M, part, S);
-    if (M <= 16) return launch_tc<16, 16>(ctx, w, q, d, M, part, S);
-    if (M <= 32) return launch_tc<32, 32>(ctx, w, q, d, M, part, S);
-    if (M <= 64) return launch_tc<64, 64>(ctx, w, q, d, M, part, S);
-    return launch_tc<128, 128>(ctx, w, q, d, M, part, S);
+    if (M <= 4) return launch_tc<16, 4>(ctx, w, q, d, M, part, S, push, grid_out);
+    if (M <= 8) return launch_tc<16, 8>(ctx, w, q, d, M, part, S, push, grid_out);
+    if (M <= 16) return launch_tc<16, 16>(ctx, w, q, d, M, part, S, push, grid_out);
+    if (M <= 32) return launch_tc<32, 32>(ctx, w, q, d, M, part, S, push, grid_out);
+    if (M <= 64) return launch_tc<64, 64>(ctx, w, q, d, M, part, S, push, grid_out);
+    return launch_tc<128, 128>(ctx, w, q, d, M, part, S, push, grid_out);
 }

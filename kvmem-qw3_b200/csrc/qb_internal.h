@@ -183,9 +183,10 @@ struct NormQuantArgs {
 };
 int qb_launch_norm_quant(qb_ctx *ctx, const NormQuantArgs &a);
 
-// gate/up fp32 [M][2F] (gate cols [0,F), up cols [F,2F)) -> silu(gate)*up -> int8 + scales.
+// gate/up fp32 [M][2F] (gate cols [0,F), up cols [F,2F)) -> silu(gate)*up -> int8 + scales.  gu may hold S split
+// partials pstride floats apart (summed ascending on read).
 int qb_launch_swiglu_quant(qb_ctx *ctx, const float *gu, uint32_t gu_stride, uint32_t M, uint32_t F, int8_t *q,
-                           uint32_t q_pitch, float *d, uint32_t d_ld);
+                           uint32_t q_pitch, float *d, uint32_t d_ld, uint32_t S = 1, size_t pstride = 0);
 
 // ---- GEMM ----------------------------------------------------------------------------------
 // part[s][m][n] for s < S; activations q [M][K] pitch K, d [K/32][ld].
@@ -193,8 +194,16 @@ int qb_launch_gemm(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float
                    uint32_t S, int impl);
 int qb_launch_gemm_dp4a(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
                         uint32_t S);
+// Optional fan-out of the tensor-core GEMM's epilogue for the tensor-parallel FFN: every partial sum goes to
+// n destinations (this GPU's and its peers' receive areas, same [s][m][n] indexing as `part`), and once a CTA's
+// stores are fenced system-wide it adds 1 to each destination's arrival counter.
+struct QbGemmPush {
+    float *dst[8] = {};
+    unsigned int *counter[8] = {};
+    uint32_t n = 0;
+};
 int qb_launch_gemm_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
-                      uint32_t S);
+                      uint32_t S, const QbGemmPush *push = nullptr, uint32_t *grid_out = nullptr);
 bool qb_gemm_tc_supported(const qb_weight *w, uint32_t M);
 uint32_t qb_ksplit(uint32_t N, uint32_t K);
 // y[m][n] = sum_s part[s][m][n] (ascending s).

@@ -235,20 +235,20 @@ extern "C" int qb_rms_norm(qb_ctx *ctx, const float *x_dev, const float *w_dev, 
 
 // silu(gate) * up -> int8 (silu_mul_kernel src/kernels_cuda.cu:1894-1903 fused with the quantiser).
 __global__ void swiglu_quant_kernel(const float *__restrict__ gu, uint32_t gu_stride, uint32_t F, int8_t *q,
-                                    uint32_t q_pitch, float *d, uint32_t d_ld) {
+                                    uint32_t q_pitch, float *d, uint32_t d_ld, uint32_t S, size_t pstride) {
     QB_PDL_ENTER();
     const uint32_t b = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32, m = blockIdx.y, lane = threadIdx.x & 31;
     if (b >= F / 32) return;
-    const float g = gu[(size_t)m * gu_stride + b * 32 + lane];
-    const float u = gu[(size_t)m * gu_stride + F + b * 32 + lane];
+    const float g = qb_ldsum(gu, (size_t)m * gu_stride + b * 32 + lane, S, pstride);
+    const float u = qb_ldsum(gu, (size_t)m * gu_stride + F + b * 32 + lane, S, pstride);
     const float v = __fdiv_rn(g, 1.0f + expf(-g)) * u;
     quant_block_store(v, lane, q + (size_t)m * q_pitch + b * 32, d + (size_t)b * d_ld + m);
 }
 
 int qb_launch_swiglu_quant(qb_ctx *ctx, const float *gu, uint32_t gu_stride, uint32_t M, uint32_t F, int8_t *q,
-                           uint32_t q_pitch, float *d, uint32_t d_ld) {
+                           uint32_t q_pitch, float *d, uint32_t d_ld, uint32_t S, size_t pstride) {
     dim3 grid((F / 32 + 7) / 8, M);
-    QB_CUDA(qb_launch_pdl(ctx->stream, swiglu_quant_kernel, dim3(grid), dim3(256), (size_t)(0), gu, gu_stride, F, q, q_pitch, d, d_ld));
+    QB_CUDA(qb_launch_pdl(ctx->stream, swiglu_quant_kernel, dim3(grid), dim3(256), (size_t)(0), gu, gu_stride, F, q, q_pitch, d, d_ld, S, pstride));
     QB_LAUNCHED(ctx, "swiglu_quant_kernel");
     return QB_OK;
 }

@@ -6,6 +6,14 @@ timed launch starts with a cold L2 (a 256 MB buffer is rewritten before it); tim
 the launching stream.  Prints one JSON line per (shape, M, kernel).
 
     python kvmem-qw3_b200/gemm_sweep.py [--iters 10] [--shapes 17408x5120,5120x17408] [--m 1,4,16]
+
+--tp times the tensor-parallel FFN pair (5120 -> 17408 gate/up, SwiGLU, 17408 -> 5120 down, all-reduce fused
+into the down GEMM's epilogue) with the FFN dimension split over the ranks of the launch:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node P --master-addr 127.0.0.1 --master-port 29700 \
+        kvmem-qw3_b200/gemm_sweep.py --tp [--m 4,16,64,128,512]
+
+One JSON line per M on rank 0: the time is the max over ranks of the CUDA-event time of one FFN (cold L2).
 """
 import argparse
 import ctypes as C
@@ -19,6 +27,64 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import __graft_entry__ as entry  # noqa: E402
 
 
+def tp_sweep(args):
+    """FFN pair of the 27B shape with the FFN dimension split over WORLD_SIZE GPUs (one process each)."""
+    H, F = 5120, 17408
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    pkg = entry.load_package()
+    ctx = pkg.Context(local)
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("gloo")      # plumbing only: handle exchange, barriers, max of the times
+    Ms = [int(v) for v in args.m.split(",") if int(v) > 1] or [4]
+    f = F // world
+    w_gu = pkg.Weight.synth(ctx, 0x5EED, 500 + rank, 2 * f, H, 0.02)
+    w_dn = pkg.Weight.synth(ctx, 0x5EED, 600 + rank, H, f, 0.02)
+    if dist is not None:
+        group, area, opened = pkg.tp.ipc_group(ctx, dist, max(Ms), H, f, H)
+    else:
+        groups, area = pkg.tp.local_groups(ctx, 1, max(Ms), H, f, H)
+        group, opened = groups[0], []
+    rng = np.random.default_rng(5)
+    e0, e1 = ctx.event(), ctx.event()
+    for M in Ms:
+        x = ctx.array(rng.standard_normal((M, H)).astype(np.float32))
+        y = ctx.empty((M, H), np.float32)
+        times = []
+        for it in range(args.iters + 3):
+            if not args.no_flush:
+                ctx.flush_l2()
+            ctx.sync()
+            if dist is not None:
+                dist.barrier()
+            ctx.record(e0)
+            group.ffn(w_gu, w_dn, x, M, y)
+            ctx.record(e1)
+            ctx.sync()
+            if it >= 3:
+                times.append(ctx.elapsed_ms(e0, e1))
+        us = float(np.median(times)) * 1e3
+        if dist is not None:
+            import torch
+            t = torch.tensor([us], dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t[0])
+        if rank == 0:
+            wbytes = (2 * f * H + H * f) / 32 * 34
+            print(json.dumps({"tp": world, "M": M, "ffn_us": round(us, 2), "weight_MB_per_rank": round(wbytes / 1e6, 1),
+                              "GBps_per_rank": round(wbytes / us / 1e3, 1), "allreduce_bytes": M * H * 4,
+                              "TOPs_total": round(2.0 * M * 3 * F * H / us / 1e6, 2)}), flush=True)
+    group.close()
+    pkg.tp.ipc_release(ctx, opened)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
@@ -27,7 +93,10 @@ def main():
     ap.add_argument("--impls", default="1,2")
     ap.add_argument("--ksplit", type=int, default=0)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--tp", action="store_true", help="tensor-parallel FFN pair over the ranks of this launch")
     args = ap.parse_args()
+    if args.tp:
+        return tp_sweep(args)
     pkg = entry.load_package()
     L = pkg.lib()
     ctx = pkg.Context(0)
