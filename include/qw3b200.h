@@ -274,9 +274,10 @@ int qb_trace_summary(qb_ctx *ctx, char *buf, size_t buf_bytes);
  * The one sharded case of the path: the FFN dimension F is split over `world` GPUs (one process each).
  * Rank r holds gate/up rows [r*F/world, (r+1)*F/world) fused as [gate_r; up_r] (2*f_shard x n_in) and the
  * matching K slice of down (n_out x f_shard).  qb_tp_ffn = quantise x, gate/up GEMM, SwiGLU, down GEMM
- * whose epilogue stores its split partials into every rank's receive area and signals, then a reduce
- * that adds all ranks' partials in (rank, segment) order: every rank ends with the same bits, equal to
- * sum_r sum_s partial[r][s].  Stands where the reference would place ncclAllReduce after a row-parallel
+ * whose epilogue stores its split partials into every rank's receive area and signals (from 32 rows on:
+ * a rank adds its own segments first and pushes one slice), then a reduce that adds, in rank order, each
+ * rank's sum over its segments: every rank ends with the same bits, sum_r (sum_s partial[r][s]), whatever
+ * the row count.  Stands where the reference would place ncclAllReduce after a row-parallel
  * q8_0_matmul (the reference itself runs one GPU per model replica and has no such call).
  *
  * Receive areas: one allocation of qb_tp_recv_bytes() per GPU (qb_malloc), 256-byte aligned, passed as

@@ -4,9 +4,12 @@
 // The all-reduce is one-shot over peer memory and fused with the producing GEMM: the epilogue of the down GEMM
 // stores every split partial straight into the receive area of every GPU of the group (its own included),
 // fences system-wide and bumps an arrival counter on each of them; the reduce kernel of a GPU waits (bounded)
-// until all CTAs of all ranks have arrived and adds the partials in (rank, segment) order, so every GPU gets
-// the same bits.  Receive areas are double-buffered by step parity: a rank can only be one step ahead of a
-// peer, because its next reduce needs that peer's next push.
+// until all CTAs of all ranks have arrived and adds, in rank order, each rank's sum over its segments, so every
+// GPU gets the same bits.  With many rows the S-fold copy of the partials would make the exchange bandwidth
+// bound; from QB_TP_FUSED_ROWS rows on, a rank therefore adds its own segments first and pushes one [M][n_out]
+// slice (same order of additions, so the result does not depend on which form ran).  Receive areas are
+// double-buffered by step parity: a rank can only be one step ahead of a peer, because its next reduce needs
+// that peer's next push.
 //
 // Receive area of one GPU:  [0,256) arrival counters (parity p at byte 128*p), then for parity p
 // slot[p] = float [world][S][max_rows][n_out] with S = qb_ksplit_policy(n_out, k_shard); a push of M rows
@@ -21,10 +24,13 @@ struct qb_tp_group {
     int8_t *xq = nullptr, *hq = nullptr;
     float *xd = nullptr, *hd = nullptr, *gu_parts = nullptr;
     size_t region_floats = 0, slot_floats = 0;
+    float *dn_parts = nullptr;           // local split partials of the down GEMM (many-row form)
+    uint32_t pushed_S[2] = {1, 1};       // segments per rank in the slot of each parity
 };
 
 namespace {
 
+constexpr uint32_t QB_TP_FUSED_ROWS = 32;       // below: the GEMM epilogue pushes its split partials itself
 constexpr uint32_t TP_WAIT_LIMIT = 1u << 20;     // polls of >= 1 us (a system-scope load + 256 ns sleep): a second or so
 
 __global__ void tp_reduce_kernel(const float *__restrict__ slot, const unsigned int *counter, unsigned int expected,
@@ -48,14 +54,29 @@ __global__ void tp_reduce_kernel(const float *__restrict__ slot, const unsigned 
     const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x, m = blockIdx.y;
     if (n >= N) return;
     float acc = 0.0f;
-    bool first = true;
-    for (uint32_t r = 0; r < world; ++r)
-        for (uint32_t s = 0; s < S; ++s) {
-            const float v = __ldcg(slot + r * region_floats + ((size_t)s * M + m) * N + n);
-            acc = first ? v : acc + v;
-            first = false;
-        }
+    for (uint32_t r = 0; r < world; ++r) {
+        float mine = __ldcg(slot + r * region_floats + (size_t)m * N + n);
+        for (uint32_t s = 1; s < S; ++s) mine += __ldcg(slot + r * region_floats + ((size_t)s * M + m) * N + n);
+        acc = r == 0 ? mine : acc + mine;
+    }
     y[(size_t)m * y_stride + n] = acc;
+}
+
+// Many-row form: this rank's sum over its segments goes to every rank's receive area as one slice.
+__global__ void tp_local_reduce_push_kernel(const float *__restrict__ part, uint32_t S, uint32_t M, uint32_t N, QbGemmPush push) {
+    QB_PDL_ENTER();
+    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x, m = blockIdx.y;
+    if (n < N) {
+        float v = part[(size_t)m * N + n];
+        for (uint32_t s = 1; s < S; ++s) v += part[((size_t)s * M + m) * N + n];
+        for (uint32_t p = 0; p < push.n; ++p) push.dst[p][(size_t)m * N + n] = v;
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        for (uint32_t p = 0; p < push.n; ++p) atomicAdd_system(push.counter[p], 1u);
+    }
 }
 
 }  // namespace
@@ -86,6 +107,7 @@ extern "C" int qb_tp_group_create(qb_ctx *ctx, uint32_t rank, uint32_t world, vo
     QB_CUDA(cudaMalloc(&g->hq, (size_t)max_rows * f_shard));
     QB_CUDA(cudaMalloc(&g->hd, (size_t)(f_shard / 32) * ld * sizeof(float)));
     QB_CUDA(cudaMalloc(&g->gu_parts, (size_t)S_gu * max_rows * 2 * f_shard * sizeof(float)));
+    QB_CUDA(cudaMalloc(&g->dn_parts, g->region_floats * sizeof(float)));
     QB_CUDA(cudaMemsetAsync(g->recv[rank], 0, 256, ctx->stream));     // own arrival counters
     QB_CUDA(cudaStreamSynchronize(ctx->stream));
     *out = g;
@@ -95,7 +117,7 @@ extern "C" int qb_tp_group_create(qb_ctx *ctx, uint32_t rank, uint32_t world, vo
 extern "C" int qb_tp_group_destroy(qb_ctx *ctx, qb_tp_group *g) {
     if (!g) return QB_OK;
     if (ctx) cudaStreamSynchronize(ctx->stream);
-    cudaFree(g->xq); cudaFree(g->xd); cudaFree(g->hq); cudaFree(g->hd); cudaFree(g->gu_parts);
+    cudaFree(g->xq); cudaFree(g->xd); cudaFree(g->hq); cudaFree(g->hd); cudaFree(g->gu_parts); cudaFree(g->dn_parts);
     delete g;
     return QB_OK;
 }
@@ -126,12 +148,23 @@ extern "C" int qb_tp_ffn_push(qb_ctx *ctx, qb_tp_group *g, const qb_weight *gate
         push.counter[r] = reinterpret_cast<unsigned int *>(g->recv[r] + 128 * par);
     }
     uint32_t grid = 0;
-    QB_TRY(qb_launch_gemm_tc(ctx, down, g->hq, g->hd, M, nullptr, g->S_dn, &push, &grid));
+    if (M < QB_TP_FUSED_ROWS || g->S_dn == 1) {
+        QB_TRY(qb_launch_gemm_tc(ctx, down, g->hq, g->hd, M, nullptr, g->S_dn, &push, &grid));
+        g->pushed_S[par] = g->S_dn;
+    } else {
+        QB_TRY(qb_launch_gemm_tc(ctx, down, g->hq, g->hd, M, g->dn_parts, g->S_dn));
+        dim3 rg((g->n_out + 255) / 256, M);
+        QB_CUDA(qb_launch_pdl(ctx->stream, tp_local_reduce_push_kernel, rg, dim3(256), (size_t)0, (const float *)g->dn_parts, g->S_dn, M,
+                              g->n_out, push));
+        QB_LAUNCHED(ctx, "tp_local_reduce_push_kernel");
+        grid = rg.x * rg.y;
+        g->pushed_S[par] = 1;
+    }
     g->expected[par] += (uint64_t)g->world * grid;       // every rank launches the same grid for the same M
     return QB_OK;
 }
 
-// y[m][n] = sum over ranks (ascending) of the sum over segments (ascending) of the pushed partials.
+// y[m][n] = sum over ranks (ascending) of each rank's sum over its segments (ascending).
 extern "C" int qb_tp_ffn_reduce(qb_ctx *ctx, qb_tp_group *g, uint32_t M, float *y_dev, uint32_t y_stride) {
     QB_REQUIRE(ctx && g && y_dev && M > 0 && M <= g->max_rows && y_stride >= g->n_out, "qb_tp_ffn_reduce: bad arguments");
     const uint32_t par = g->step & 1;
@@ -139,7 +172,7 @@ extern "C" int qb_tp_ffn_reduce(qb_ctx *ctx, qb_tp_group *g, uint32_t M, float *
     const unsigned int *counter = reinterpret_cast<const unsigned int *>(g->recv[g->rank] + 128 * par);
     dim3 grid((g->n_out + 255) / 256, M);
     QB_CUDA(qb_launch_pdl(ctx->stream, tp_reduce_kernel, grid, dim3(256), (size_t)0, slot, counter, (unsigned int)g->expected[par], g->world,
-                          g->S_dn, M, g->n_out, g->region_floats, y_dev, y_stride, ctx->err_flag_dev));
+                          g->pushed_S[par], M, g->n_out, g->region_floats, y_dev, y_stride, ctx->err_flag_dev));
     QB_LAUNCHED(ctx, "tp_reduce_kernel");
     g->step += 1;
     return QB_OK;

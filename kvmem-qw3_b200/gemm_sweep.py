@@ -11,7 +11,7 @@ the launching stream.  Prints one JSON line per (shape, M, kernel).
 into the down GEMM's epilogue) with the FFN dimension split over the ranks of the launch:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node P --master-addr 127.0.0.1 --master-port 29700 \
-        kvmem-qw3_b200/gemm_sweep.py --tp [--m 4,16,64,128,512]
+        kvmem-qw3_b200/gemm_sweep.py --tp [--rows 4,16,64,128,512]
 
 One JSON line per M on rank 0: the time is the max over ranks of the CUDA-event time of one FFN (cold L2).
 """
@@ -77,8 +77,12 @@ def tp_sweep(args):
             print(json.dumps({"tp": world, "M": M, "ffn_us": round(us, 2), "weight_MB_per_rank": round(wbytes / 1e6, 1),
                               "GBps_per_rank": round(wbytes / us / 1e3, 1), "allreduce_bytes": M * H * 4,
                               "TOPs_total": round(2.0 * M * 3 * F * H / us / 1e6, 2)}), flush=True)
+    ctx.sync()
+    if dist is not None:
+        dist.barrier()                  # nobody unmaps a receive area a peer may still write
     group.close()
     pkg.tp.ipc_release(ctx, opened)
+    w_gu.free(); w_dn.free()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -89,7 +93,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--shapes", default="17408x5120,5120x17408,5120x6144,34816x5120,151936x5120")
-    ap.add_argument("--m", default="1,4,16,64,128,512")
+    ap.add_argument("--m", "--rows", dest="m", default="1,4,16,64,128,512")
     ap.add_argument("--impls", default="1,2")
     ap.add_argument("--ksplit", type=int, default=0)
     ap.add_argument("--no-flush", action="store_true")

@@ -40,16 +40,18 @@ def oracle_rank_partials(orc, gu, dn, f, x):
 
 
 def ordered_sum(parts):
-    """float32 sum of [R][S][M][N] in (rank, segment) order, one add at a time."""
-    flat = parts.reshape((-1,) + parts.shape[2:])
-    acc = flat[0].copy()
-    for p in flat[1:]:
-        acc = (acc + p).astype(np.float32)
+    """float32 sum of [R][S][M][N]: each rank's segments ascending, then the ranks ascending."""
+    acc = None
+    for rank_parts in parts:
+        mine = rank_parts[0].copy()
+        for p in rank_parts[1:]:
+            mine = (mine + p).astype(np.float32)
+        acc = mine if acc is None else (acc + mine).astype(np.float32)
     return acc
 
 
 @pytest.mark.parametrize("world", [1, 2, 4])
-@pytest.mark.parametrize("M", [1, 4, 17])
+@pytest.mark.parametrize("M", [1, 4, 17, 32])
 def test_tp_ffn_ranks_in_one_process(qb, orc, ctx, world, M):
     gate, up, down = make_weights(orc, 7)
     f = F // world
@@ -71,11 +73,13 @@ def test_tp_ffn_ranks_in_one_process(qb, orc, ctx, world, M):
         got = [y.download() for y in ys]
         for r in range(1, world):
             assert np.array_equal(got[0], got[r]), "ranks disagree"
-        # the receive area of every rank holds all ranks' partials; their (rank, segment) sum IS the result
+        # the receive area of every rank holds what all ranks pushed (their split partials, or from 32 rows on
+        # their sums over the segments); the rank-ordered sum of it IS the result
+        Sp = S if M < 32 else 1
         for r in range(world):
             raw = areas[r].download()
             slot = raw[256:].view(np.float32)[(step & 1) * world * region:((step & 1) + 1) * world * region]
-            parts = np.stack([slot[k * region:k * region + S * M * N_OUT].reshape(S, M, N_OUT) for k in range(world)])
+            parts = np.stack([slot[k * region:k * region + Sp * M * N_OUT].reshape(Sp, M, N_OUT) for k in range(world)])
             assert np.array_equal(ordered_sum(parts), got[r]), "reduce order"
         want_parts = np.stack([oracle_rank_partials(orc, shards[r][0], shards[r][1], f, x) for r in range(world)])
         want = ordered_sum(want_parts)
@@ -173,10 +177,12 @@ for step, M in enumerate([4, 1, 17, 4, 4, 32]):
             h = (g / (np.float32(1) + np.exp(-g, dtype=np.float32)) * u).astype(np.float32)
             hq, hd = O.quantize_act(h)
             parts.append(O.gemm_engine(d_r, N_OUT, f, hq, hd, want_partials=True)[1])
-        flat = np.concatenate(parts)
-        acc = flat[0].copy()
-        for p in flat[1:]:
-            acc = (acc + p).astype(np.float32)
+        acc = None
+        for rp in parts:
+            mine = rp[0].copy()
+            for p in rp[1:]:
+                mine = (mine + p).astype(np.float32)
+            acc = mine if acc is None else (acc + mine).astype(np.float32)
         worst = max(worst, float(np.abs(got - acc).max() / np.abs(acc).max()))
 dist.barrier()
 if rank == 0:
