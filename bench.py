@@ -75,9 +75,16 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def mark(self):
+        """Number of samples so far (brackets the timed region inside a longer sampling run)."""
+        return len(self.lines)
+
+    def stop(self, first=0):
+        """Summary of the samples from index `first` on; of all samples (taken under the warm-up load) when the
+        timed region was too short to catch one."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -85,7 +92,8 @@ class ClockSampler:
             pass
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        window = self.lines[first:] if len(self.lines) > first else self.lines
+        for ln in window:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 6:
                 continue
@@ -215,6 +223,10 @@ def run_ours(args, rank, world, local_rank, dist):
     forced = np.where(frs.rand(ns, stride) < ACCEPT_RATE, stream, (stream + 1) % cfg.vocab_size).astype(np.int32)
     sdev = ctx.array(forced)
 
+    # the clock sampler runs from the prompt ingestion on (nvidia-smi needs a moment to start); the samples of
+    # the timed region are cut out below
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     b = pkg.Batch(model, ns, max_ctx, k)
     for s_ in range(ns):
         b.prefill(s_, prompts[s_])
@@ -234,14 +246,13 @@ def run_ours(args, rank, world, local_rank, dist):
         dist.barrier()
     ctx.sync()
     s0, l0 = b.stats(), ctx.launches
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    first_sample = sampler.mark()
     ctx.record(ev[0])
     for _ in range(K):
         device_step()
     ctx.record(ev[1])
     ctx.sync()
-    clocks = sampler.stop()
+    clocks = sampler.stop(first_sample)
     dev_ms = ctx.elapsed_ms(ev[0], ev[1])
     s1, l1 = b.stats(), ctx.launches
     dev_emitted = s1["emitted"] - s0["emitted"]
