@@ -8,8 +8,9 @@
 // Rows come in groups: sequence s owns rows [s*R, (s+1)*R) at positions seq_pos[s] .. seq_pos[s]+R-1.
 // All query rows of a group that share a KV head are processed by one CTA in ONE pass over that
 // head's keys (the reference re-reads the cache once per row).  The key range is cut at fixed
-// absolute boundaries (QB_ATTN_SPLIT keys) and tiles (64 keys) and the split partials are merged in
-// ascending order, so a row's result does not depend on how many other rows are in the launch.
+// absolute boundaries (QB_ATTN_SPLIT keys) and tiles (64 keys), the tiles of a split are folded in ascending
+// order and the split partials merged in ascending order, so a row's result does not depend on how many other
+// rows are in the launch.
 #include "qb_internal.h"
 
 namespace {
@@ -84,26 +85,55 @@ __global__ void qk_norm_rope_append_kernel(AttnArgs a, const int32_t *__restrict
 }
 
 // ---- split attention ---------------------------------------------------------------------------
+// One CTA = one split (QB_ATTN_SPLIT keys = 4 tiles of 64) of one KV head for up to 32 queries (<= 4 rows x
+// GQA group).  Tensor-core math on fp16 operands with fp32 accumulation (mma.sync m16n8k16; the kernel streams
+// the cache once and is bound by HBM, not by the tensor pipe): S = Q K^T with Q (scaled, fp16) held in
+// registers as A fragments, P = exp(S - m) written to shared memory as fp16, O += P V with V read through
+// ldmatrix.trans.  Warp w = (h, j): query rows [16h, 16h+16), keys [16j, 16j+16) of the tile for S and
+// output dims [j*HD/4, (j+1)*HD/4) for O.  The running maximum of a row is shared by the four warps that hold
+// it (one exchange per tile through shared memory); each warp keeps its own partial row sum, added in warp
+// order at the end.  K/V tiles arrive through a 3-stage cp.async pipeline (zero-filled past the last key).
 template <int HD>
 struct AttSmem {
-    static constexpr int ROW = HD * 2 + 16;                 // bytes per key row (padded)
-    static constexpr int KV_TILE = TK * ROW;
+    static constexpr int ROWB = HD * 2 + 16;                // bytes per key / query row (padded: conflict-free ldmatrix)
+    static constexpr int KV_TILE = TK * ROWB;
     static constexpr int STAGE = 2 * KV_TILE;               // K then V
-    static constexpr int Q_BYTES = 32 * HD * 4;             // up to 32 queries
-    static constexpr int P_BYTES = 32 * TK * 4;
-    static constexpr int TOTAL = 2 * STAGE + Q_BYTES + P_BYTES;
+    static constexpr int NSTAGE = 3;
+    static constexpr int Q_OFF = NSTAGE * STAGE;
+    static constexpr int Q_BYTES = 32 * ROWB;
+    static constexpr int P_ROWB = TK * 2 + 16;
+    static constexpr int P_OFF = Q_OFF + Q_BYTES;
+    static constexpr int P_BYTES = 32 * P_ROWB;
+    static constexpr int RED_OFF = P_OFF + P_BYTES;         // float [4 warps j][32 rows]
+    static constexpr int TOTAL = RED_OFF + 4 * 32 * 4;
 };
 
-// grid (max_splits, n_kv, n_seqs * ceil(R/QR)).  QPW = queries per warp (QR*G <= 8*QPW).
-template <int HD, int QPW>
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// grid (max_splits, n_kv, n_seqs * ceil(R/QR)).
+template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, const int32_t *__restrict__ seq_pos, uint32_t R,
                                                                  uint32_t max_splits) {
     QB_PDL_ENTER();
     using L = AttSmem<HD>;
-    extern __shared__ __align__(16) uint8_t smem[];
-    float *Qs = reinterpret_cast<float *>(smem + 2 * L::STAGE);
-    float *Ps = reinterpret_cast<float *>(smem + 2 * L::STAGE + L::Q_BYTES);
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+    float *red = reinterpret_cast<float *>(smem + L::RED_OFF);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t h = warp & 1, j = warp >> 1;                  // query m-tile, key / output-dim quarter
+    const uint32_t g4 = lane >> 2, t4 = lane & 3;                // accumulator row / column pair of this lane
     const uint32_t split = blockIdx.x, kvh = blockIdx.y;
     const uint32_t chunks = (R + QR - 1) / QR;
     const uint32_t seq = blockIdx.z / chunks, chunk = blockIdx.z % chunks;
@@ -118,146 +148,179 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, con
     const int n_tiles = (k_end - k_begin + TK - 1) / TK;
     const float scale = rsqrtf((float)HD);
     const int32_t *pt = a.page_table + (size_t)seq * a.pt_stride;
+    const bool active = h * 16 < NQ;                             // this warp's query rows exist
 
-    // stage the queries (scaled): query index qi = r_local * G + g, head = kvh*G + g
-    for (uint32_t idx = tid; idx < NQ * HD; idx += ATT_THREADS) {
-        const uint32_t qi = idx / HD, dd = idx % HD;
-        const uint32_t rl = qi / G, g = qi % G;
-        const size_t row = (size_t)seq * R + r_begin + rl;
-        Qs[qi * HD + dd] = a.qkv[row * a.row_stride + (size_t)(kvh * G + g) * 2 * HD + dd] * scale;
-    }
-
+    // a thread copies one 16-byte column of every (256 / CH)-th key row: one page-table lookup per row, no
+    // division when the page size is a power of two
+    const uint32_t psz = a.page_size;
+    const bool pow2 = (psz & (psz - 1)) == 0;
+    const int psh = __ffs((int)psz) - 1;
     auto load_tile = [&](int tile, int slot) {
         uint8_t *ks = smem + slot * L::STAGE, *vs = ks + L::KV_TILE;
         constexpr int CH = HD * 2 / 16;                          // 16-byte chunks per key row
-        for (int c = tid; c < TK * CH; c += ATT_THREADS) {
-            const int t = c / CH, p = c % CH;
+        constexpr int RPP = ATT_THREADS / CH;                    // rows per pass
+        const int p = tid % CH;
+#pragma unroll
+        for (int t = tid / CH; t < TK; t += RPP) {
             const int key = k_begin + tile * TK + t;
             const bool valid = key < k_end;
             size_t off = 0;
             if (valid) {
-                const size_t slot_i = (size_t)pt[key / (int)a.page_size] * a.page_size + key % (int)a.page_size;
-                off = (slot_i * a.n_kv + kvh) * HD;
+                const uint32_t pg = pow2 ? (uint32_t)key >> psh : (uint32_t)key / psz;
+                const uint32_t in_pg = (uint32_t)key - pg * psz;
+                off = (((size_t)pt[pg] * psz + in_pg) * a.n_kv + kvh) * HD;
             }
-            cp_async16(ks + t * L::ROW + p * 16, a.k_cache + off + p * 8, valid);
-            cp_async16(vs + t * L::ROW + p * 16, a.v_cache + off + p * 8, valid);
+            cp_async16(ks + t * L::ROWB + p * 16, a.k_cache + off + p * 8, valid);
+            cp_async16(vs + t * L::ROWB + p * 16, a.v_cache + off + p * 8, valid);
         }
     };
-
-    constexpr int DPL = HD / 32;                                 // output dims per lane
-    float acc[QPW][DPL];
-    float m_run[QPW], l_run[QPW];
-#pragma unroll
-    for (int j = 0; j < QPW; ++j) {
-        m_run[j] = -INFINITY; l_run[j] = 0.0f;
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) acc[j][e] = 0.0f;
-    }
-
     load_tile(0, 0);
     cp_async_commit();
-    for (int tile = 0; tile < n_tiles; ++tile) {
-        if (tile + 1 < n_tiles) load_tile(tile + 1, (tile + 1) & 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        const uint8_t *ks = smem + (tile & 1) * L::STAGE, *vs = ks + L::KV_TILE;
-        const int key0 = k_begin + tile * TK;
+    if (n_tiles > 1) load_tile(1, 1);
+    cp_async_commit();
 
-        // scores: lane handles keys lane and lane+32 of the tile
-        float s0[QPW], s1[QPW];
+    // stage the queries (scaled, fp16): query index qi = r_local * G + g, head = kvh*G + g; missing rows are zero
+    for (uint32_t qi = warp; qi < 32; qi += ATT_WARPS) {
+        const uint32_t rl = qi / G, gq = qi - rl * G;
+        const float *src = a.qkv + ((size_t)seq * R + r_begin + rl) * a.row_stride + (size_t)(kvh * G + gq) * 2 * HD;
 #pragma unroll
-        for (int j = 0; j < QPW; ++j) { s0[j] = 0.0f; s1[j] = 0.0f; }
-        const uint8_t *k0p = ks + lane * L::ROW, *k1p = ks + (lane + 32) * L::ROW;
-#pragma unroll 4
-        for (int c = 0; c < HD / 8; ++c) {
-            const uint4 ka = *reinterpret_cast<const uint4 *>(k0p + c * 16);
-            const uint4 kb = *reinterpret_cast<const uint4 *>(k1p + c * 16);
-            float fa[8], fb[8];
-            {
-                const __half2 *ha = reinterpret_cast<const __half2 *>(&ka), *hb = reinterpret_cast<const __half2 *>(&kb);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 x = __half22float2(ha[e]), y = __half22float2(hb[e]);
-                    fa[2 * e] = x.x; fa[2 * e + 1] = x.y; fb[2 * e] = y.x; fb[2 * e + 1] = y.y;
-                }
+        for (uint32_t dd = lane * 2; dd < HD; dd += 64) {
+            __half2 v = __floats2half2_rn(0.0f, 0.0f);
+            if (qi < NQ) {
+                const float2 f = *reinterpret_cast<const float2 *>(src + dd);
+                v = __floats2half2_rn(f.x * scale, f.y * scale);
             }
+            *reinterpret_cast<__half2 *>(smem + L::Q_OFF + qi * L::ROWB + dd * 2) = v;
+        }
+    }
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
 #pragma unroll
-            for (int j = 0; j < QPW; ++j) {
-                const uint32_t qi = warp + j * ATT_WARPS;
-                if (qi < NQ) {
-                    const float4 qa = *reinterpret_cast<const float4 *>(Qs + qi * HD + c * 8);
-                    const float4 qb = *reinterpret_cast<const float4 *>(Qs + qi * HD + c * 8 + 4);
-                    s0[j] += qa.x * fa[0] + qa.y * fa[1] + qa.z * fa[2] + qa.w * fa[3] + qb.x * fa[4] + qb.y * fa[5] + qb.z * fa[6] + qb.w * fa[7];
-                    s1[j] += qa.x * fb[0] + qa.y * fb[1] + qa.z * fb[2] + qa.w * fb[3] + qb.x * fb[4] + qb.y * fb[5] + qb.z * fb[6] + qb.w * fb[7];
-                }
+    for (int ks = 0; ks < HD / 16; ++ks)
+        ldsm_x4(qf[ks], smem_base + L::Q_OFF + (h * 16 + (lane & 15)) * L::ROWB + (ks * 16 + (lane >> 4) * 8) * 2);
+
+    constexpr int NT_O = HD / 32;                                // 8-wide output tiles per warp (HD/4 dims)
+    float o[NT_O][4];
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};   // rows g4 and g4 + 8 of the m-tile
+    // positions of this lane's two query rows (rows past NQ get -1: everything masked)
+    int qpos[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const uint32_t qi = h * 16 + g4 + 8 * e;
+        qpos[e] = qi < NQ ? base_pos + (int)(qi / G) : -1;
+    }
+
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        cp_async_wait<1>();
+        __syncthreads();                                         // tile landed; everyone is done with tile - 1
+        if (tile + 2 < n_tiles) load_tile(tile + 2, (tile + 2) % L::NSTAGE);
+        cp_async_commit();
+        const uint32_t ks_base = smem_base + (tile % L::NSTAGE) * L::STAGE, vs_base = ks_base + L::KV_TILE;
+        const int key0 = k_begin + tile * TK + (int)j * 16;     // first key of this warp's 16
+
+        // S = Q K^T for 16 queries x 16 keys
+        float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        if (active) {
+            const uint32_t kaddr = ks_base + (j * 16 + (lane & 7) + ((lane >> 4) << 3)) * L::ROWB + (((lane >> 3) & 1) * 8) * 2;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+                uint32_t b[4];
+                ldsm_x4(b, kaddr + ks * 32);
+                mma_f16(sc[0], qf[ks], b[0], b[1]);
+                mma_f16(sc[1], qf[ks], b[2], b[3]);
             }
         }
-        // online softmax per query, probabilities to shared memory
+        // causal mask + this warp's row maxima
+        float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int j = 0; j < QPW; ++j) {
-            const uint32_t qi = warp + j * ATT_WARPS;
-            if (qi >= NQ) continue;
-            const int qpos = base_pos + (int)(qi / G);
-            const int ka_i = key0 + (int)lane, kb_i = ka_i + 32;
-            const float a0 = (ka_i <= qpos && ka_i < k_end) ? s0[j] : -INFINITY;
-            const float a1 = (kb_i <= qpos && kb_i < k_end) ? s1[j] : -INFINITY;
-            const float m_new = fmaxf(m_run[j], warp_max(fmaxf(a0, a1)));
-            float p0 = 0.0f, p1 = 0.0f, corr = 1.0f;
-            if (m_new != -INFINITY) {
-                p0 = expf(a0 - m_new);
-                p1 = expf(a1 - m_new);
-                corr = expf(m_run[j] - m_new);
-            }
-            l_run[j] = l_run[j] * corr + warp_sum(p0 + p1);
-            m_run[j] = m_new;
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int e = 0; e < DPL; ++e) acc[j][e] *= corr;
-            Ps[qi * TK + lane] = p0;
-            Ps[qi * TK + lane + 32] = p1;
-        }
-        __syncwarp();
-        // P x V: lane owns dims [lane*DPL, lane*DPL + DPL)
-        for (int t = 0; t < TK; ++t) {
-            float vv[DPL];
-            const __half *vp = reinterpret_cast<const __half *>(vs + t * L::ROW) + lane * DPL;
-            if constexpr (DPL == 8) {
-                const uint4 raw = *reinterpret_cast<const uint4 *>(vp);
-                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h2[e]); vv[2 * e] = f.x; vv[2 * e + 1] = f.y; }
-            } else if constexpr (DPL == 4) {
-                const uint2 raw = *reinterpret_cast<const uint2 *>(vp);
-                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
-#pragma unroll
-                for (int e = 0; e < 2; ++e) { const float2 f = __half22float2(h2[e]); vv[2 * e] = f.x; vv[2 * e + 1] = f.y; }
-            } else {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(vp));
-                vv[0] = f.x; vv[1] = f.y;
+            for (int c = 0; c < 4; ++c) {
+                const int key = key0 + nt * 8 + (int)t4 * 2 + (c & 1), e = c >> 1;
+                if (!(key <= qpos[e] && key < k_end)) sc[nt][c] = -INFINITY;
+                mx[e] = fmaxf(mx[e], sc[nt][c]);
             }
 #pragma unroll
-            for (int j = 0; j < QPW; ++j) {
-                const uint32_t qi = warp + j * ATT_WARPS;
-                if (qi < NQ) {
-                    const float p = Ps[qi * TK + t];
-#pragma unroll
-                    for (int e = 0; e < DPL; ++e) acc[j][e] = fmaf(p, vv[e], acc[j][e]);
-                }
-            }
+        for (int e = 0; e < 2; ++e) {
+            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 1));
+            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 2));
+            if (t4 == 0) red[j * 32 + h * 16 + g4 + 8 * e] = mx[e];
         }
         __syncthreads();
+        float corr[2];
+        uint32_t pk[2][2];                                       // P as fp16 pairs: [nt][row e]
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const uint32_t r = h * 16 + g4 + 8 * e;
+            const float m_tile = fmaxf(fmaxf(red[r], red[32 + r]), fmaxf(red[64 + r], red[96 + r]));
+            const float m_new = fmaxf(m_run[e], m_tile);
+            float p[4] = {0.f, 0.f, 0.f, 0.f};
+            corr[e] = 1.0f;
+            if (m_new != -INFINITY) {
+                corr[e] = expf(m_run[e] - m_new);
+                p[0] = expf(sc[0][2 * e] - m_new); p[1] = expf(sc[0][2 * e + 1] - m_new);
+                p[2] = expf(sc[1][2 * e] - m_new); p[3] = expf(sc[1][2 * e + 1] - m_new);
+            }
+            const __half2 h0 = __floats2half2_rn(p[0], p[1]), h1 = __floats2half2_rn(p[2], p[3]);
+            // the row sum uses the rounded probabilities, the values the tensor cores multiply with V
+            const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+            l_run[e] = l_run[e] * corr[e] + ((f0.x + f0.y) + (f1.x + f1.y));
+            m_run[e] = m_new;
+            pk[0][e] = *reinterpret_cast<const uint32_t *>(&h0);
+            pk[1][e] = *reinterpret_cast<const uint32_t *>(&h1);
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e)
+                *reinterpret_cast<uint32_t *>(smem + L::P_OFF + (h * 16 + g4 + 8 * e) * L::P_ROWB + (j * 16 + nt * 8 + t4 * 2) * 2) = pk[nt][e];
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
+        __syncthreads();
+        // O += P V for 16 queries x HD/4 dims over the tile's 64 keys
+        if (active) {
+#pragma unroll
+            for (int kk = 0; kk < TK / 16; ++kk) {
+                uint32_t pa[4];
+                ldsm_x4(pa, smem_base + L::P_OFF + (h * 16 + (lane & 15)) * L::P_ROWB + (kk * 16 + (lane >> 4) * 8) * 2);
+                const uint32_t vaddr = vs_base + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * L::ROWB + (j * (HD / 4) + (lane >> 4) * 8) * 2;
+#pragma unroll
+                for (int n2 = 0; n2 < NT_O / 2; ++n2) {
+                    uint32_t b[4];
+                    ldsm_x4_trans(b, vaddr + n2 * 32);
+                    mma_f16(o[2 * n2], pa, b[0], b[1]);
+                    mma_f16(o[2 * n2 + 1], pa, b[2], b[3]);
+                }
+            }
+        }
     }
     cp_async_wait<0>();
+    // row sums: quad first, then the four warps of a row in order
+    __syncthreads();
 #pragma unroll
-    for (int j = 0; j < QPW; ++j) {
-        const uint32_t qi = warp + j * ATT_WARPS;
+    for (int e = 0; e < 2; ++e) {
+        float l = l_run[e];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (t4 == 0) red[j * 32 + h * 16 + g4 + 8 * e] = l;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const uint32_t qi = h * 16 + g4 + 8 * e;
         if (qi >= NQ) continue;
         const size_t row = (size_t)seq * R + r_begin + qi / G;
         const uint32_t head = kvh * G + qi % G;
         const size_t pidx = (row * a.n_heads + head) * max_splits + split;
+        float *dst = a.part_acc + pidx * HD + j * (HD / 4) + t4 * 2;
 #pragma unroll
-        for (int e = 0; e < DPL; ++e) a.part_acc[pidx * HD + lane * DPL + e] = acc[j][e];
-        if (lane == 0) { a.part_ml[pidx * 2] = m_run[j]; a.part_ml[pidx * 2 + 1] = l_run[j]; }
+        for (int n = 0; n < NT_O; ++n) *reinterpret_cast<float2 *>(dst + n * 8) = make_float2(o[n][2 * e], o[n][2 * e + 1]);
+        if (j == 0 && t4 == 0) {
+            a.part_ml[pidx * 2] = m_run[e];
+            a.part_ml[pidx * 2 + 1] = ((red[qi] + red[32 + qi]) + red[64 + qi]) + red[96 + qi];
+        }
     }
 }
 
@@ -314,16 +377,16 @@ __global__ void attn_merge_kernel(AttnArgs a, const int32_t *__restrict__ seq_po
     }
 }
 
-template <int HD, int QPW>
+template <int HD>
 int launch_split(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t R, uint32_t n_seqs, uint32_t max_splits) {
     using L = AttSmem<HD>;
     static bool attr = false;
     if (!attr) {
-        QB_CUDA(cudaFuncSetAttribute(attn_split_kernel<HD, QPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        QB_CUDA(cudaFuncSetAttribute(attn_split_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         attr = true;
     }
     dim3 grid(max_splits, a.n_kv, n_seqs * ((R + QR - 1) / QR));
-    QB_CUDA(qb_launch_pdl(ctx->stream, attn_split_kernel<HD, QPW>, dim3(grid), dim3(ATT_THREADS), (size_t)(L::TOTAL), a, seq_pos, R, max_splits));
+    QB_CUDA(qb_launch_pdl(ctx->stream, attn_split_kernel<HD>, dim3(grid), dim3(ATT_THREADS), (size_t)(L::TOTAL), a, seq_pos, R, max_splits));
     QB_LAUNCHED(ctx, "attn_split_kernel");
     return QB_OK;
 }
@@ -357,15 +420,12 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
     const uint32_t G = a.n_heads / a.n_kv;
     QB_REQUIRE(G * a.n_kv == a.n_heads && G <= 8, "attention: GQA group %u unsupported (<= 8)", G);
     const uint32_t ms = max_splits_for(a.max_pos);
-    const uint32_t nq = std::min<uint32_t>(R, QR) * G;
-    const uint32_t qpw = (nq + ATT_WARPS - 1) / ATT_WARPS;
+    QB_REQUIRE(((uintptr_t)a.qkv & 7) == 0 && a.row_stride % 2 == 0, "attention: q rows must be 8-byte aligned");
     int st = QB_OK;
-#define QB_ATT_CASE(HD_, QPW_) st = launch_split<HD_, QPW_>(ctx, a, seq_pos, R, n_seqs, ms)
-    if (a.hd == 256) { if (qpw <= 1) QB_ATT_CASE(256, 1); else if (qpw <= 2) QB_ATT_CASE(256, 2); else if (qpw == 3) QB_ATT_CASE(256, 3); else QB_ATT_CASE(256, 4); }
-    else if (a.hd == 128) { if (qpw <= 1) QB_ATT_CASE(128, 1); else if (qpw <= 2) QB_ATT_CASE(128, 2); else if (qpw == 3) QB_ATT_CASE(128, 3); else QB_ATT_CASE(128, 4); }
-    else if (a.hd == 64) { if (qpw <= 1) QB_ATT_CASE(64, 1); else if (qpw <= 2) QB_ATT_CASE(64, 2); else if (qpw == 3) QB_ATT_CASE(64, 3); else QB_ATT_CASE(64, 4); }
+    if (a.hd == 256) st = launch_split<256>(ctx, a, seq_pos, R, n_seqs, ms);
+    else if (a.hd == 128) st = launch_split<128>(ctx, a, seq_pos, R, n_seqs, ms);
+    else if (a.hd == 64) st = launch_split<64>(ctx, a, seq_pos, R, n_seqs, ms);
     else return qb_fail(QB_ERR_UNSUPPORTED, "attention: head_dim %u unsupported", a.hd);
-#undef QB_ATT_CASE
     QB_TRY(st);
     dim3 grid(a.rows, a.n_heads);
     QB_CUDA(qb_launch_pdl(ctx->stream, attn_merge_kernel, dim3(grid), dim3(a.hd), (size_t)(0), a, seq_pos, R, ms, out, q8, q_pitch, d, d_ld));

@@ -79,7 +79,10 @@ def _attn_case(qb, orc, ctx, n_heads, n_kv, hd, rope_dim, page_size, seq_base, R
     gk, gv = d_kc.download(), d_vc.download()
     assert np.allclose(gk.view(np.float16).astype(np.float32), kc.view(np.float16).astype(np.float32), rtol=2e-3, atol=1e-3)
     assert np.array_equal(gv, vc)      # K within an fp16 ulp or two (device rsqrt / sincos), V exact
-    assert np.allclose(got, want, rtol=2e-3, atol=2e-4), float(np.abs(got - want).max())
+    # the kernel multiplies fp16 operands (q and the probabilities are rounded to fp16, as on the reference's
+    # FlashInfer path, whose OUTPUT is fp16 as well: ulp 1e-3 for values in [1, 2)) with fp32 accumulation; the
+    # oracle keeps q and p in fp32
+    assert np.allclose(got, want, rtol=2e-3, atol=1e-3), float(np.abs(got - want).max())
     return got
 
 
