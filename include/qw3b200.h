@@ -304,9 +304,11 @@ int qb_ipc_close(qb_ctx *ctx, void *dev_ptr);
 /* Device timeline of the tensor-core GEMM launches: after qb_debug_timeline_enable(ctx, n) the next n such
  * launches record, per CTA, {entry, dependency wait passed, exit} in nanoseconds of the GPU's global timer
  * and the SM id (4 uint64 per CTA, 320 CTA slots per launch).  qb_debug_timeline_read copies the recorded
- * launches out: out = uint64 [n][320][4], grids[i] = CTAs of launch i.  enable(ctx, 0) frees the buffer. */
+ * launches out: out = uint64 [n][320][4], grids[i] = CTAs of launch i, bytes[i] = its algorithmic bytes
+ * (weight records + int8 activations and scales + fp32 partials).  enable(ctx, 0) frees the buffer. */
 int qb_debug_timeline_enable(qb_ctx *ctx, uint32_t max_launches);
-int qb_debug_timeline_read(qb_ctx *ctx, uint64_t *out, uint32_t *grids, uint32_t max_launches, uint32_t *n_out);
+int qb_debug_timeline_read(qb_ctx *ctx, uint64_t *out, uint32_t *grids, double *bytes, uint32_t max_launches,
+                           uint32_t *n_out);
 /* Number of kernels this library launched on the context since creation. */
 int64_t qb_launch_count(qb_ctx *ctx);
 

@@ -102,7 +102,7 @@ SIGNATURES = {
     "qb_ipc_open": (i32, [vp, vp, C.POINTER(vp)]),
     "qb_ipc_close": (i32, [vp, vp]),
     "qb_debug_timeline_enable": (i32, [vp, u32]),
-    "qb_debug_timeline_read": (i32, [vp, vp, vp, u32, C.POINTER(u32)]),
+    "qb_debug_timeline_read": (i32, [vp, vp, vp, vp, u32, C.POINTER(u32)]),
 }
 
 
@@ -247,12 +247,27 @@ class Context:
         check(lib().qb_debug_timeline_enable(self.h, max_launches))
 
     def timeline_read(self, max_launches):
-        """Returns (stamps uint64 [n][320][4] = entry, wait passed, exit (ns), SM id; grids [n])."""
+        """Returns (stamps uint64 [n][320][4] = entry, wait passed, exit (ns), SM id; grids [n]; bytes [n])."""
         out = np.zeros((max_launches, 320, 4), np.uint64)
         grids = np.zeros(max_launches, np.uint32)
+        nbytes = np.zeros(max_launches, np.float64)
         n = u32()
-        check(lib().qb_debug_timeline_read(self.h, _np_ptr(out), _np_ptr(grids), max_launches, C.byref(n)))
-        return out[:n.value], grids[:n.value]
+        check(lib().qb_debug_timeline_read(self.h, _np_ptr(out), _np_ptr(grids), _np_ptr(nbytes), max_launches, C.byref(n)))
+        return out[:n.value], grids[:n.value], nbytes[:n.value]
+
+    def timeline_gemm_summary(self, stamps, grids, nbytes):
+        """In-stream figures of the recorded tensor-core GEMM launches: a launch occupies the stream from the
+        moment its dependency is satisfied (earliest CTA past its wait) to its last CTA's exit; the gap before
+        it is what ran between the previous GEMM's exit and that moment."""
+        busy, gaps, prev_exit = 0.0, 0.0, None
+        for i in range(len(grids)):
+            t = stamps[i, :int(grids[i])].astype(np.int64)
+            w0, x1 = int(t[:, 1].min()), int(t[:, 2].max())
+            busy += (x1 - w0) * 1e-3
+            if prev_exit is not None:
+                gaps += max(w0 - prev_exit, 0) * 1e-3
+            prev_exit = x1
+        return dict(launches=int(len(grids)), busy_us=busy, gap_us=gaps, bytes=float(nbytes.sum()))
 
     def pinned(self, shape, dtype):
         """Pinned host array (numpy view over cudaHostAlloc memory)."""

@@ -197,9 +197,10 @@ void qb_trace_mark(qb_ctx *ctx, const char *name) {
 }
 
 // ---- device timeline of the tensor-core GEMM launches ------------------------------------------
-unsigned long long *qb_timeline_slot(qb_ctx *ctx, uint32_t grid) {
+unsigned long long *qb_timeline_slot(qb_ctx *ctx, uint32_t grid, double bytes) {
     if (!ctx->tl_dev || ctx->tl_used >= ctx->tl_cap || grid > QB_TL_CTAS) return nullptr;
     ctx->tl_grid.push_back(grid);
+    ctx->tl_bytes.push_back(bytes);
     return ctx->tl_dev + (size_t)(ctx->tl_used++) * QB_TL_CTAS * 4;
 }
 
@@ -209,6 +210,7 @@ extern "C" int qb_debug_timeline_enable(qb_ctx *ctx, uint32_t max_launches) {
     if (ctx->tl_dev) { cudaFree(ctx->tl_dev); ctx->tl_dev = nullptr; }
     ctx->tl_cap = ctx->tl_used = 0;
     ctx->tl_grid.clear();
+    ctx->tl_bytes.clear();
     if (max_launches) {
         const size_t bytes = (size_t)max_launches * QB_TL_CTAS * 4 * sizeof(unsigned long long);
         QB_CUDA(cudaMalloc(&ctx->tl_dev, bytes));
@@ -218,12 +220,13 @@ extern "C" int qb_debug_timeline_enable(qb_ctx *ctx, uint32_t max_launches) {
     return QB_OK;
 }
 
-extern "C" int qb_debug_timeline_read(qb_ctx *ctx, uint64_t *out, uint32_t *grids, uint32_t max_launches, uint32_t *n_out) {
-    QB_REQUIRE(ctx && out && grids && n_out, "qb_debug_timeline_read: null argument");
+extern "C" int qb_debug_timeline_read(qb_ctx *ctx, uint64_t *out, uint32_t *grids, double *bytes, uint32_t max_launches,
+                                      uint32_t *n_out) {
+    QB_REQUIRE(ctx && out && grids && bytes && n_out, "qb_debug_timeline_read: null argument");
     QB_CUDA(cudaStreamSynchronize(ctx->stream));
     const uint32_t n = std::min(max_launches, ctx->tl_used);
     if (n) QB_CUDA(cudaMemcpy(out, ctx->tl_dev, (size_t)n * QB_TL_CTAS * 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-    for (uint32_t i = 0; i < n; ++i) grids[i] = ctx->tl_grid[i];
+    for (uint32_t i = 0; i < n; ++i) { grids[i] = ctx->tl_grid[i]; bytes[i] = ctx->tl_bytes[i]; }
     *n_out = n;
     return QB_OK;
 }

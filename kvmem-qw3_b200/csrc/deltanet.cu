@@ -5,11 +5,11 @@
 //   l2_norm_128_qk_batch_kernel (:4122-4156)      L2 norm of the q and k heads
 //   prep_g_sigmoid_beta_kernel + gated_delta_net_kernel (src/gated_delta_net.cu:44-177)
 //   recurrent_norm_gate_batch_kernel (:4595-4620) RMSNorm(core) * w * SiLU(z)
-// Three launches per layer for any number of sequences (the reference's ragged path loops on the
-// host per request).  State lives in slots: [seq][slot][v_head][col][i]; the rows of a step read the
-// slot named by slot_in[seq] (a device value written by the accept kernel) and, in checkpoint mode,
-// the state after row t goes to slot t, so accepting `a` drafts is "slot_in = a" and nothing is
-// copied.  Without checkpoints only the final state is written, to slot 0.
+// ONE launch per layer for any number of sequences (the reference's ragged path loops on the host per
+// request).  State lives in slots: [seq][slot][v_head][col][i]; the rows of a step read the slot named by
+// slot_in[seq] (a device value written by the accept kernel) and, in checkpoint mode, the state after row t
+// goes to slot t, so accepting `a` drafts is "slot_in = a" and nothing is copied.  Without checkpoints only
+// the final state is written, to slot 0.
 #include "qb_internal.h"
 
 namespace {
@@ -20,66 +20,50 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// grid (qkv_dim / HD, n_seqs), block HD: one head-sized chunk of channels, all rows of a sequence.
+// ---- one kernel for the whole layer -------------------------------------------------------------------------
+// grid (HD/32, nv, n_seqs), cluster (HD/32, 1, 1), block 512: the CTAs of a cluster share one v head, each owns 32
+// state columns (a warp 2 of them, lanes stripe the k dimension).  Rows are processed in blocks of 4:
+//   conv + SiLU of the head's q and k channels (every CTA of the head repeats them: 2*HD cheap channels) and of
+//   its own 32 v channels, L2 norm of q and k, all in shared memory;
+//   the delta rule for the block's rows on the register-resident state (checkpoints written as it goes);
+//   the head-wide mean square of the core output crosses the cluster once per block through distributed shared
+//   memory (push + one barrier.cluster); RMSNorm * gain * SiLU(z) and the int8 quantisation of the CTA's 32
+//   columns (= one quantisation block).
+// The q/k conv windows are read by several CTAs but written by one (v head < nk, column block 0), so the kernel
+// reads the conv state from conv and writes it to conv_out (a different buffer: the caller ping-pongs).
 template <int HD>
-__global__ void __launch_bounds__(HD) dn_conv_kernel(DnArgs a) {
+__global__ void __launch_bounds__(512, 2) dn_fused_kernel(DnArgs a) {
+    constexpr int NCB = HD / 32, RPL = HD / 32, CPW = 2, RB = 4, NCH = 2 * HD + 32;
+    constexpr int QK_WARPS = 2 * HD / 32;
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");     // "this CTA runs": awaited before the first push
     QB_PDL_ENTER();
-    __shared__ float red[HD / 32];
-    const uint32_t chunk = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
-    const uint32_t C = 2 * a.nk * HD + a.nv * HD, R = a.rows_per_seq;
-    const uint32_t c = chunk * HD + tid;
-    const bool is_qk = chunk < 2 * a.nk;
-    const uint32_t slot = (uint32_t)a.slot_in[seq];
-    float *conv_seq = a.conv + (size_t)seq * a.n_slots * C * 3;
-    float st[3], w[4];
-#pragma unroll
-    for (int k = 0; k < 3; ++k) st[k] = conv_seq[((size_t)slot * C + c) * 3 + k];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) w[k] = a.conv_w[(size_t)c * 4 + k];
-    float nxt = qb_ldsum(a.proj, (size_t)seq * R * a.proj_stride + c, a.proj_S, a.proj_pstride);
-    for (uint32_t t = 0; t < R; ++t) {
-        const size_t row = (size_t)seq * R + t;
-        const float cur = nxt;
-        if (t + 1 < R) nxt = qb_ldsum(a.proj, (row + 1) * a.proj_stride + c, a.proj_S, a.proj_pstride);   // next row's load overlaps this row
-        float acc = w[3] * cur;
-#pragma unroll
-        for (int k = 0; k < 3; ++k) acc += w[k] * st[k];
-        float x = __fdiv_rn(acc, 1.0f + expf(-acc));
-        st[0] = st[1]; st[1] = st[2]; st[2] = cur;
-        if (is_qk) {
-            const float ss = warp_sum(x * x);
-            __syncthreads();
-            if ((tid & 31) == 0) red[tid >> 5] = ss;
-            __syncthreads();
-            float tot = 0.0f;
-#pragma unroll
-            for (int k = 0; k < HD / 32; ++k) tot += red[k];
-            x *= rsqrtf(tot + a.eps);
-        }
-        a.xconv[row * C + c] = x;
-        if (a.write_all && t < a.n_slots) {
-#pragma unroll
-            for (int k = 0; k < 3; ++k) conv_seq[((size_t)t * C + c) * 3 + k] = st[k];
-        }
-    }
-    if (!a.write_all) {
-#pragma unroll
-        for (int k = 0; k < 3; ++k) conv_seq[(size_t)c * 3 + k] = st[k];
-    }
-}
-
-// grid (nv, HD / 8, n_seqs), block 128: each warp owns 2 state columns, lanes stripe the k-dim.
-template <int HD>
-__global__ void __launch_bounds__(128) dn_delta_kernel(DnArgs a) {
-    QB_PDL_ENTER();
-    constexpr int RPL = HD / 32, CPW = 2;
-    const uint32_t vh = blockIdx.x, seq = blockIdx.z, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t col0 = blockIdx.y * 8 + warp * CPW;
-    const uint32_t kh = vh % a.nk;                        // src/gated_delta_net.cu:105
+    __shared__ float xs[RB][NCH];
+    __shared__ float red[RB][8];
+    __shared__ float core_s[RB][32];
+    __shared__ float gbs[RB][2];
+    __shared__ float cl_ss[2][NCB][RB];
+    const uint32_t cb = blockIdx.x, vh = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t kh = vh % a.nk;                         // src/gated_delta_net.cu:105
     const uint32_t C = 2 * a.nk * HD + a.nv * HD, vdim = a.nv * HD, R = a.rows_per_seq;
+    const uint32_t slot = (uint32_t)a.slot_in[seq];
     const size_t ssz = (size_t)a.nv * HD * HD;
     float *state_seq = a.state + (size_t)seq * a.n_slots * ssz;
-    const uint32_t slot = (uint32_t)a.slot_in[seq];
+    const float *conv_in = a.conv + (size_t)seq * a.n_slots * C * 3;
+    float *conv_out = a.conv_out + (size_t)seq * a.n_slots * C * 3;
+
+    // thread tid < NCH convolves one channel: a q or k channel of head kh, or one of this CTA's 32 v channels
+    const bool has = tid < NCH, is_qk = tid < 2 * HD;
+    const uint32_t ch = tid < HD ? kh * HD + tid : tid < 2 * HD ? a.nk * HD + kh * HD + (tid - HD) : 2 * a.nk * HD + vh * HD + cb * 32 + (tid - 2 * HD);
+    const bool writes = is_qk ? (vh < a.nk && cb == 0) : true;
+    float st[3] = {0.f, 0.f, 0.f}, w[4] = {0.f, 0.f, 0.f, 0.f};
+    if (has) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) st[k] = conv_in[((size_t)slot * C + ch) * 3 + k];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) w[k] = a.conv_w[(size_t)ch * 4 + k];
+    }
+    // state columns of this warp
+    const uint32_t col0 = cb * 32 + warp * CPW;
     float s[CPW][RPL];
 #pragma unroll
     for (int cc = 0; cc < CPW; ++cc)
@@ -88,55 +72,137 @@ __global__ void __launch_bounds__(128) dn_delta_kernel(DnArgs a) {
             s[cc][r] = state_seq[(size_t)slot * ssz + ((size_t)vh * HD + col0 + cc) * HD + r * 32 + lane];
     const float oscale = rsqrtf((float)HD);
     const float A = a.ssm_a[vh], bias = a.dt_bias[vh];
-    // operands of one row; the next row's are requested before this row's arithmetic
-    struct RowIn { float ga, gb, q[RPL], k[RPL], xv[CPW]; };
-    auto load_row = [&](uint32_t t) {
-        RowIn in;
-        const size_t row = (size_t)seq * R + t;
-        const float *x = a.xconv + row * C;
-        const size_t pr = row * a.proj_stride + C + vdim;
-        in.ga = qb_ldsum(a.proj, pr + vh, a.proj_S, a.proj_pstride);
-        in.gb = qb_ldsum(a.proj, pr + a.nv + vh, a.proj_S, a.proj_pstride);
+    const float nw = a.norm_w[cb * 32 + lane];
+    uint32_t crank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+
+    for (uint32_t rb0 = 0, blk = 0; rb0 < R; rb0 += RB, ++blk) {
+        const uint32_t nrows = min((uint32_t)RB, R - rb0), par = blk & 1;
+        const size_t row0 = (size_t)seq * R + rb0;
+        // all loads of the block first
+        float cur[RB], zv = 0.0f;
 #pragma unroll
-        for (int r = 0; r < RPL; ++r) {
-            in.q[r] = x[kh * HD + r * 32 + lane];
-            in.k[r] = x[a.nk * HD + kh * HD + r * 32 + lane];
+        for (int t = 0; t < RB; ++t) {
+            cur[t] = 0.0f;
+            if (has && (uint32_t)t < nrows) cur[t] = qb_ldsum(a.proj, (row0 + t) * a.proj_stride + ch, a.proj_S, a.proj_pstride);
         }
+        if (warp < nrows) zv = qb_ldsum(a.proj, (row0 + warp) * a.proj_stride + C + vh * HD + cb * 32 + lane, a.proj_S, a.proj_pstride);
+        // decay and write strength of the block's rows: thread (t, which) of the last warp
+        if (warp == 15 && lane < 2 * nrows) {
+            const uint32_t t = lane >> 1, which = lane & 1;
+            const float raw = qb_ldsum(a.proj, (row0 + t) * a.proj_stride + C + vdim + which * a.nv + vh, a.proj_S, a.proj_pstride);
+            gbs[t][which] = which == 0 ? expf(log1pf(expf(raw + bias)) * A) : __fdiv_rn(1.0f, 1.0f + expf(-raw));
+        }
+        // conv + SiLU, conv-state checkpoints
+        float x[RB];
 #pragma unroll
-        for (int cc = 0; cc < CPW; ++cc) in.xv[cc] = x[2 * a.nk * HD + vh * HD + col0 + cc];
-        return in;
-    };
-    RowIn nxt = load_row(0);
-    for (uint32_t t = 0; t < R; ++t) {
-        const size_t row = (size_t)seq * R + t;
-        const RowIn in = nxt;
-        if (t + 1 < R) nxt = load_row(t + 1);
-        const float g = expf(log1pf(expf(in.ga + bias)) * A);
-        const float beta = __fdiv_rn(1.0f, 1.0f + expf(-in.gb));
-        const float *kr = in.k, *qr = in.q;
+        for (int t = 0; t < RB; ++t) {
+            x[t] = 0.0f;
+            if (has && (uint32_t)t < nrows) {
+                float acc = w[3] * cur[t];
 #pragma unroll
-        for (int cc = 0; cc < CPW; ++cc) {
-            float kv = 0.0f;
+                for (int k = 0; k < 3; ++k) acc += w[k] * st[k];
+                x[t] = __fdiv_rn(acc, 1.0f + expf(-acc));
+                st[0] = st[1]; st[1] = st[2]; st[2] = cur[t];
+                if (writes && a.write_all && rb0 + t < a.n_slots) {
 #pragma unroll
-            for (int r = 0; r < RPL; ++r) kv += s[cc][r] * kr[r];
-            kv = warp_sum(kv);
-            const float delta = (in.xv[cc] - g * kv) * beta;
-            float at = 0.0f;
-#pragma unroll
-            for (int r = 0; r < RPL; ++r) {
-                s[cc][r] = g * s[cc][r] + kr[r] * delta;
-                at += s[cc][r] * qr[r];
+                    for (int k = 0; k < 3; ++k) conv_out[((size_t)(rb0 + t) * C + ch) * 3 + k] = st[k];
+                }
             }
-            at = warp_sum(at);
-            if (lane == 0) a.core[row * vdim + vh * HD + col0 + cc] = at * oscale;
-            if (a.write_all && t < a.n_slots) {
+            if (warp < QK_WARPS) {                    // warp-uniform: q and k channels only
+                const float ss = warp_sum(x[t] * x[t]);
+                if (lane == 0) red[t][warp] = ss;
+            }
+        }
+        __syncthreads();
+        if (has) {
 #pragma unroll
-                for (int r = 0; r < RPL; ++r)
-                    state_seq[(size_t)t * ssz + ((size_t)vh * HD + col0 + cc) * HD + r * 32 + lane] = s[cc][r];
+            for (int t = 0; t < RB; ++t) {
+                if ((uint32_t)t >= nrows) continue;
+                float v = x[t];
+                if (is_qk) {
+                    const int g0 = tid < HD ? 0 : HD / 32;
+                    float tot = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < HD / 32; ++k) tot += red[t][g0 + k];
+                    v *= rsqrtf(tot + a.eps);
+                }
+                xs[t][tid] = v;
+            }
+        }
+        __syncthreads();
+        // delta rule on the block's rows
+#pragma unroll 1
+        for (uint32_t t = 0; t < nrows; ++t) {
+            const float g = gbs[t][0], beta = gbs[t][1];
+            float kr[RPL], qr[RPL];
+#pragma unroll
+            for (int r = 0; r < RPL; ++r) { qr[r] = xs[t][r * 32 + lane]; kr[r] = xs[t][HD + r * 32 + lane]; }
+#pragma unroll
+            for (int cc = 0; cc < CPW; ++cc) {
+                float kv = 0.0f;
+#pragma unroll
+                for (int r = 0; r < RPL; ++r) kv += s[cc][r] * kr[r];
+                kv = warp_sum(kv);
+                const float delta = (xs[t][2 * HD + warp * CPW + cc] - g * kv) * beta;
+                float at = 0.0f;
+#pragma unroll
+                for (int r = 0; r < RPL; ++r) {
+                    s[cc][r] = g * s[cc][r] + kr[r] * delta;
+                    at += s[cc][r] * qr[r];
+                }
+                at = warp_sum(at);
+                if (lane == 0) core_s[t][warp * CPW + cc] = at * oscale;
+                if (a.write_all && rb0 + t < a.n_slots) {
+#pragma unroll
+                    for (int r = 0; r < RPL; ++r)
+                        state_seq[(size_t)(rb0 + t) * ssz + ((size_t)vh * HD + col0 + cc) * HD + r * 32 + lane] = s[cc][r];
+                }
+            }
+        }
+        __syncthreads();
+        // this CTA's part of the head's sum of squares, pushed to every CTA of the cluster
+        if (blk == 0) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // all CTAs of the cluster run
+        if (warp == 0) {
+            float mine = 0.0f;
+#pragma unroll
+            for (int t = 0; t < RB; ++t) {
+                const float v = (uint32_t)t < nrows ? core_s[t][lane] : 0.0f;
+                const float ss = warp_sum(v * v);
+                if ((lane % RB) == (uint32_t)t) mine = ss;
+            }
+            if (lane < NCB * RB) {
+                uint32_t local = (uint32_t)__cvta_generic_to_shared(&cl_ss[par][crank][lane % RB]), remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(lane / RB));
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(mine) : "memory");
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        // RMSNorm * gain * SiLU(z), int8 quantisation: warp t takes row t, lane = column
+        if (warp < nrows) {
+            const uint32_t t = warp, col = vh * HD + cb * 32 + lane;
+            const size_t row = row0 + t;
+            float tot = 0.0f;
+#pragma unroll
+            for (int r = 0; r < NCB; ++r) tot += cl_ss[par][r][t];
+            const float o = core_s[t][lane] * rsqrtf(tot / (float)HD + a.eps) * nw * __fdiv_rn(zv, 1.0f + expf(-zv));
+            if (a.core_out) a.core_out[row * vdim + col] = o;
+            if (a.q8) {
+                float amax = fabsf(o);
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+                const float d_inv = (amax == 0.0f) ? 0.0f : __fdiv_rn(127.0f, amax);
+                a.q8[row * a.q_pitch + col] = (int8_t)((amax == 0.0f) ? 0 : __float2int_rn(__fmul_rn(o, d_inv)));
+                if (lane == 0) a.d[(size_t)(col / 32) * a.d_ld + row] = (amax == 0.0f) ? 0.0f : __fdiv_rn(1.0f, d_inv);
             }
         }
     }
     if (!a.write_all) {
+        if (has && writes) {
+#pragma unroll
+            for (int k = 0; k < 3; ++k) conv_out[(size_t)ch * 3 + k] = st[k];
+        }
 #pragma unroll
         for (int cc = 0; cc < CPW; ++cc)
 #pragma unroll
@@ -145,43 +211,23 @@ __global__ void __launch_bounds__(128) dn_delta_kernel(DnArgs a) {
     }
 }
 
-// grid (rows, nv), block HD.
 template <int HD>
-__global__ void __launch_bounds__(HD) dn_normgate_kernel(DnArgs a) {
-    QB_PDL_ENTER();
-    __shared__ float red[HD / 32];
-    const uint32_t row = blockIdx.x, vh = blockIdx.y, i = threadIdx.x, lane = i & 31;
-    const uint32_t C = 2 * a.nk * HD + a.nv * HD, vdim = a.nv * HD;
-    const float v = a.core[(size_t)row * vdim + vh * HD + i];
-    const float ss = warp_sum(v * v);
-    if (lane == 0) red[i >> 5] = ss;
-    __syncthreads();
-    float tot = 0.0f;
-#pragma unroll
-    for (int k = 0; k < HD / 32; ++k) tot += red[k];
-    const float z = qb_ldsum(a.proj, (size_t)row * a.proj_stride + C + vh * HD + i, a.proj_S, a.proj_pstride);
-    const float o = v * rsqrtf(tot / (float)HD + a.eps) * a.norm_w[i] * __fdiv_rn(z, 1.0f + expf(-z));
-    const uint32_t col = vh * HD + i;
-    if (a.core_out) a.core_out[(size_t)row * vdim + col] = o;
-    if (a.q8) {
-        float amax = fabsf(o);
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        const float d_inv = (amax == 0.0f) ? 0.0f : __fdiv_rn(127.0f, amax);
-        a.q8[(size_t)row * a.q_pitch + col] = (int8_t)((amax == 0.0f) ? 0 : __float2int_rn(__fmul_rn(o, d_inv)));
-        if (lane == 0) a.d[(size_t)(col / 32) * a.d_ld + row] = (amax == 0.0f) ? 0.0f : __fdiv_rn(1.0f, d_inv);
-    }
-}
-
-template <int HD>
-int launch_all(qb_ctx *ctx, const DnArgs &a) {
-    const uint32_t C = 2 * a.nk * HD + a.nv * HD;
-    QB_CUDA(qb_launch_pdl(ctx->stream, dn_conv_kernel<HD>, dim3(dim3(C / HD, a.n_seqs)), dim3(HD), (size_t)(0), a));
-    QB_LAUNCHED(ctx, "dn_conv_kernel");
-    QB_CUDA(qb_launch_pdl(ctx->stream, dn_delta_kernel<HD>, dim3(dim3(a.nv, HD / 8, a.n_seqs)), dim3(128), (size_t)(0), a));
-    QB_LAUNCHED(ctx, "dn_delta_kernel");
-    QB_CUDA(qb_launch_pdl(ctx->stream, dn_normgate_kernel<HD>, dim3(dim3(a.n_seqs * a.rows_per_seq, a.nv)), dim3(HD), (size_t)(0), a));
-    QB_LAUNCHED(ctx, "dn_normgate_kernel");
+int launch_fused(qb_ctx *ctx, const DnArgs &a) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(HD / 32, a.nv, a.n_seqs);
+    cfg.blockDim = dim3(512);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = HD / 32;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    QB_CUDA(cudaLaunchKernelEx(&cfg, dn_fused_kernel<HD>, a));
+    QB_LAUNCHED(ctx, "dn_fused_kernel");
     return QB_OK;
 }
 
@@ -191,7 +237,8 @@ int qb_launch_deltanet(qb_ctx *ctx, const DnArgs &a) {
     QB_REQUIRE(a.n_seqs > 0 && a.rows_per_seq > 0 && a.n_slots > 0, "deltanet: empty launch");
     QB_REQUIRE(!a.write_all || a.rows_per_seq <= a.n_slots, "deltanet: %u rows need %u checkpoint slots, have %u",
                a.rows_per_seq, a.rows_per_seq, a.n_slots);
-    if (a.hd == 128) return launch_all<128>(ctx, a);
-    if (a.hd == 64) return launch_all<64>(ctx, a);
+    QB_REQUIRE(a.conv_out && a.conv_out != a.conv, "deltanet: the new conv state needs a buffer of its own");
+    if (a.hd == 128) return launch_fused<128>(ctx, a);
+    if (a.hd == 64) return launch_fused<64>(ctx, a);
     return qb_fail(QB_ERR_UNSUPPORTED, "deltanet: head dim %u unsupported (64/128)", a.hd);
 }

@@ -164,6 +164,8 @@ struct qb_batch {
     uint32_t n_seqs = 0, max_ctx = 0, k = 0, page_size = 0, pages_per_seq = 0, rows_cap = 0, chunk = 0, logit_rows = 0;
     std::vector<__half *> kc, vc;          // per layer (attention layers only), + MTP layer at index n_layers
     std::vector<float *> state, conv;      // per layer (recurrent layers only): [n_seqs][k+1][...]
+    std::vector<float *> conv_alt;         // second conv-state buffer: a forward reads one and writes the other
+    int conv_par = 0;                      // which of the two holds the valid conv state (the same for all sequences)
     int32_t *page_table = nullptr;         // [n_seqs][pages_per_seq]
     // device control block (all int32)
     int32_t *ctl = nullptr;
@@ -175,7 +177,7 @@ struct qb_batch {
     int32_t *out_rec_host = nullptr;       // pinned mirror of out_rec
     // activations
     float *hid = nullptr;                  // [rows_cap + n_seqs][H]; rows rows_cap+s hold prev hidden of seq s
-    float *mtp_h = nullptr, *embd = nullptr, *act = nullptr, *xconv = nullptr, *core = nullptr, *parts = nullptr;
+    float *mtp_h = nullptr, *embd = nullptr, *act = nullptr, *parts = nullptr;
     float *logits = nullptr, *am_val = nullptr, *att_acc = nullptr, *att_ml = nullptr;
     int32_t *am_idx = nullptr;
     QBuf xq_h, xq_attn, xq_dn, xq_ffn, xq_cat;
@@ -214,7 +216,7 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
     const uint32_t H = c.n_embd, K1 = draft_k + 1, L = c.n_layers, rows = b->rows_cap;
     const size_t slots = (size_t)n_seqs * b->pages_per_seq * page_size;
     const uint32_t kvd = m->kvd();
-    b->kc.assign(L + 1, nullptr); b->vc.assign(L + 1, nullptr); b->state.assign(L, nullptr); b->conv.assign(L, nullptr);
+    b->kc.assign(L + 1, nullptr); b->vc.assign(L + 1, nullptr); b->state.assign(L, nullptr); b->conv.assign(L, nullptr); b->conv_alt.assign(L, nullptr);
     for (uint32_t il = 0; il <= L; ++il) {
         const bool attn = il == L ? c.mtp_layers == 1 : m->is_attn(il);
         if (attn) {
@@ -229,6 +231,8 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
             QB_CUDA(cudaMalloc(&b->conv[il], csz * sizeof(float)));
             QB_CUDA(cudaMemsetAsync(b->state[il], 0, ssz * sizeof(float), ctx->stream));
             QB_CUDA(cudaMemsetAsync(b->conv[il], 0, csz * sizeof(float), ctx->stream));
+            QB_CUDA(cudaMalloc(&b->conv_alt[il], csz * sizeof(float)));
+            QB_CUDA(cudaMemsetAsync(b->conv_alt[il], 0, csz * sizeof(float), ctx->stream));
         }
     }
     // page table: identity / reverse / seeded shuffle over the whole pool
@@ -276,8 +280,6 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
     QB_CUDA(cudaMalloc(&b->mtp_h, (size_t)rows * H * sizeof(float)));
     QB_CUDA(cudaMalloc(&b->embd, (size_t)rows * H * sizeof(float)));
     QB_CUDA(cudaMalloc(&b->act, (size_t)rows * act_cols * sizeof(float)));
-    QB_CUDA(cudaMalloc(&b->xconv, (size_t)rows * m->qkv_dim() * sizeof(float)));
-    QB_CUDA(cudaMalloc(&b->core, (size_t)rows * vdim * sizeof(float)));
     QB_CUDA(cudaMalloc(&b->logits, (size_t)b->logit_rows * V * sizeof(float)));
     QB_CUDA(cudaMalloc(&b->am_val, (size_t)b->logit_rows * QB_ARGMAX_BLOCKS * sizeof(float)));
     QB_CUDA(cudaMalloc(&b->am_idx, (size_t)b->logit_rows * QB_ARGMAX_BLOCKS * sizeof(int32_t)));
@@ -316,7 +318,8 @@ extern "C" void qb_batch_destroy(qb_ctx *ctx, qb_batch *b) {
     for (auto p : b->vc) if (p) cudaFree(p);
     for (auto p : b->state) if (p) cudaFree(p);
     for (auto p : b->conv) if (p) cudaFree(p);
-    void *ptrs[] = {b->page_table, b->ctl, b->stats, b->hid, b->mtp_h, b->embd, b->act, b->xconv, b->core, b->parts,
+    for (auto p : b->conv_alt) if (p) cudaFree(p);
+    void *ptrs[] = {b->page_table, b->ctl, b->stats, b->hid, b->mtp_h, b->embd, b->act, b->parts,
                     b->logits, b->am_val, b->am_idx, b->att_acc, b->att_ml, b->xq_h.q, b->xq_h.d, b->xq_attn.q,
                     b->xq_attn.d, b->xq_dn.q, b->xq_dn.d, b->xq_ffn.q, b->xq_ffn.d, b->xq_cat.q, b->xq_cat.d};
     for (void *p : ptrs) if (p) cudaFree(p);
@@ -558,9 +561,10 @@ static int deltanet_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t il
     d.conv_w = L.conv_w; d.ssm_a = L.ssm_a; d.dt_bias = L.dt_bias; d.norm_w = m->ones;
     d.nk = c.ssm_num_k_heads; d.nv = c.ssm_num_v_heads; d.hd = c.ssm_head_dim; d.eps = c.rms_eps;
     d.state = b->state[il] + (size_t)rs.seq0 * K1 * c.ssm_num_v_heads * c.ssm_head_dim * c.ssm_head_dim;
-    d.conv = b->conv[il] + (size_t)rs.seq0 * K1 * m->qkv_dim() * 3;
+    const size_t conv_off = (size_t)rs.seq0 * K1 * m->qkv_dim() * 3;
+    d.conv = (b->conv_par ? b->conv_alt[il] : b->conv[il]) + conv_off;
+    d.conv_out = (b->conv_par ? b->conv[il] : b->conv_alt[il]) + conv_off;
     d.n_slots = K1; d.slot_in = b->sel + rs.seq0; d.write_all = checkpoints ? 1 : 0;
-    d.xconv = b->xconv; d.core = b->core;
     d.q8 = b->xq_dn.q; d.q_pitch = b->xq_dn.K; d.d = b->xq_dn.d; d.d_ld = qb_act_ld(rows);
     QB_TRY(qb_launch_deltanet(ctx, d));
     uint32_t S = 1;
@@ -583,6 +587,19 @@ static int target_forward(qb_ctx *ctx, qb_batch *b, const int32_t *tokens_dev, c
         if (L.recurrent) QB_TRY(deltanet_block(ctx, b, L, il, h, rs, checkpoints, m->ones));
         else QB_TRY(attention_block(ctx, b, L, il, h, rs, false, m->ones));
         QB_TRY(ffn_block(ctx, b, L, h, rows, m->ones));   // the next norm is the next layer's attn_norm or output_norm
+    }
+    // the DeltaNet layers read the conv windows from one buffer and wrote the new ones to the other: a forward over
+    // every sequence just swaps the two; one over a subset copies its windows back so all sequences stay in one
+    if (rs.seq0 == 0 && rs.ns == b->n_seqs) {
+        b->conv_par ^= 1;
+    } else {
+        const size_t per_seq = (size_t)(b->k + 1) * m->qkv_dim() * 3;
+        for (uint32_t il = 0; il < c.n_layers; ++il) {
+            if (!m->layers[il].recurrent) continue;
+            float *rd = b->conv_par ? b->conv_alt[il] : b->conv[il], *wr = b->conv_par ? b->conv[il] : b->conv_alt[il];
+            QB_CUDA(cudaMemcpyAsync(rd + rs.seq0 * per_seq, wr + rs.seq0 * per_seq, rs.ns * per_seq * sizeof(float),
+                                    cudaMemcpyDeviceToDevice, ctx->stream));
+        }
     }
     b->last_logit_rows = 0;
     if (logits == 1) {

@@ -47,12 +47,17 @@ extern "C" int qb_deltanet_rows(qb_ctx *ctx, const float *proj_dev, uint32_t n_s
                "qb_deltanet_rows: null argument");
     const uint32_t rows = n_seqs * rows_per_seq, C = (2 * nk + nv) * hd, vdim = nv * hd;
     QB_REQUIRE(proj_stride >= C + vdim + 2 * nv, "qb_deltanet_rows: proj_stride %u too small", proj_stride);
+    // the kernel reads the conv windows from one buffer and writes the new ones to another: the old ones are
+    // copied to scratch first so the caller's buffer can be the output
+    const size_t conv_floats = (size_t)n_seqs * n_slots * C * 3;
     void *scr = nullptr;
-    QB_TRY(qb_ctx_scratch(ctx, ((size_t)rows * C + (size_t)rows * vdim) * sizeof(float), &scr));
+    QB_TRY(qb_ctx_scratch(ctx, conv_floats * sizeof(float), &scr));
+    float *conv_old = (float *)scr;
+    QB_CUDA(cudaMemcpyAsync(conv_old, conv_dev, conv_floats * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
     DnArgs d;
     d.proj = proj_dev; d.proj_stride = proj_stride; d.n_seqs = n_seqs; d.rows_per_seq = rows_per_seq;
     d.conv_w = conv_w; d.ssm_a = ssm_a; d.dt_bias = dt_bias; d.norm_w = norm_w; d.nk = nk; d.nv = nv; d.hd = hd; d.eps = eps;
-    d.state = state_dev; d.conv = conv_dev; d.n_slots = n_slots; d.slot_in = slot_in_dev; d.write_all = write_all;
-    d.xconv = (float *)scr; d.core = d.xconv + (size_t)rows * C; d.core_out = core_dev;
+    d.state = state_dev; d.conv = conv_old; d.conv_out = conv_dev; d.n_slots = n_slots; d.slot_in = slot_in_dev; d.write_all = write_all;
+    d.core_out = core_dev;
     return qb_launch_deltanet(ctx, d);
 }

@@ -443,7 +443,7 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
     QB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, NLD>, (const uint8_t *)w->rec, iq->second, id->second, K, w->rows, M, part, S,
-                               tiles, units, ctx->err_flag_dev, qb_timeline_slot(ctx, grid), push ? *push : QbGemmPush()));
+                               tiles, units, ctx->err_flag_dev, qb_timeline_slot(ctx, grid, (double)w->rows_pad * K / 32.0 * 34.0 + (double)M * K * 1.125 + (double)S * M * w->rows * 4.0), push ? *push : QbGemmPush()));
     if (grid_out) *grid_out = grid;
     QB_LAUNCHED(ctx, "gemm_tc_kernel");
     return QB_OK;

@@ -86,6 +86,7 @@ struct qb_ctx {
     unsigned long long *tl_dev = nullptr;  // device timeline slots
     uint32_t tl_cap = 0, tl_used = 0;
     std::vector<uint32_t> tl_grid;
+    std::vector<double> tl_bytes;          // algorithmic bytes of each recorded launch
     bool prof_on = false;
     std::vector<cudaEvent_t> prof_ev;      // pool, two per recorded launch
     size_t prof_used = 0;
@@ -100,7 +101,7 @@ void qb_trace_mark(qb_ctx *ctx, const char *name);
 // QB_TL_CTAS x 4 words; CTA b stores {entry, dependency wait passed, exit} in nanoseconds of the global
 // timer and its SM id.  Returns null when disabled or full.
 static const uint32_t QB_TL_CTAS = 320;
-unsigned long long *qb_timeline_slot(qb_ctx *ctx, uint32_t grid);
+unsigned long long *qb_timeline_slot(qb_ctx *ctx, uint32_t grid, double bytes);
 #ifdef __CUDACC__
 __device__ __forceinline__ unsigned long long qb_globaltimer() {
     unsigned long long t;
@@ -247,11 +248,10 @@ struct DnArgs {
     const float *conv_w = nullptr, *ssm_a = nullptr, *dt_bias = nullptr, *norm_w = nullptr;
     uint32_t nk = 0, nv = 0, hd = 0; float eps = 0.f;
     float *state = nullptr, *conv = nullptr;                 // [n_seqs][n_slots][...]
+    float *conv_out = nullptr;                               // new conv state (same layout), a buffer other than conv
     uint32_t n_slots = 0;
     const int32_t *slot_in = nullptr;                        // [n_seqs] device
     int write_all = 0;
-    float *xconv = nullptr;                                  // scratch [rows][qkv_dim]
-    float *core = nullptr;                                   // scratch/out [rows][nv*hd]
     int8_t *q8 = nullptr; uint32_t q_pitch = 0; float *d = nullptr; uint32_t d_ld = 0;   // quantised gated core
     float *core_out = nullptr;                               // optional fp32 gated core
 };
