@@ -341,7 +341,7 @@ def run_ours(args, rank, world, local_rank, dist):
         "data": "synthetic", "config": workload_config(args), "clocks": clocks,
         "e2e": {"value": agg[3] / (agg[1] * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": ns * k * 4, "d2h_bytes_per_step": ns * (k + 3) * 4,
                 "ms_per_step": agg[1] / K, "lossless_vs_greedy": bool(lossless)},
-        "gpu_launches": int(agg[4]),
+        "gpu_launches": int(agg[4]), "gpu_launches_before_timed_region": int(l0),
         "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel + gemm_dp4a_kernel (all Q8_0 projections of the step)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                      # DRAM bytes per launch: the ncu capture of this kernel on a 94.70 MB weight read 94.79 MB
