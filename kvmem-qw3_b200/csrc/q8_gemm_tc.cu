@@ -14,14 +14,13 @@
 // swizzle), all through one mbarrier pipeline; the kernel is an HBM streaming kernel until the
 // activation-row count reaches the hundreds.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (owns the TMEM allocation),
-// warps 2..5 = epilogue (TMEM lane quarter = warp % 4).  Every wait is bounded: when a wait runs out
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (owns the TMEM allocation), warps 2.. = epilogue
+// (TMEM lane quarter = warp % 4; four warps for the small tiles, eight from 32 activation rows on).  Every wait is bounded: when a wait runs out
 // the CTA raises the context's error flag, lets its copies land, frees its TMEM and returns.
 #include "qb_internal.h"
 
 namespace {
 
-constexpr int TC_THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -104,6 +103,14 @@ __device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, int32_t *r) {
         : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait, naming the 16 registers of an earlier (asynchronous) load as read-write operands: whatever
+// consumes them is then ordered after the wait by a data dependency, however far the load was issued ahead.
+__device__ __forceinline__ void tmem_ld_wait16(int32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :: "memory");
+}
 
 __host__ __device__ inline uint32_t tc_seg_begin(uint32_t s, uint32_t S, uint32_t nchunks) {
     return (uint32_t)(((uint64_t)s * nchunks) / S);
@@ -134,6 +141,12 @@ struct TcCfg {
     static constexpr int NST = NST_FIT > 8 ? 8 : NST_FIT;
     static constexpr int TOTAL = STAGE * NST + BAR_BYTES + 1024;   // + slack to align the base to 1024
     static constexpr int CH = NLD < 16 ? NLD : 16;               // columns per tcgen05.ld
+    // Epilogue warps: four for the small tiles (one per TMEM lane quarter); eight from MT = 32 on (two per
+    // quarter, each taking half of the activation columns): the drain + rescale of a large tile is bound by
+    // instruction issue and dependent latencies, which a second warp per scheduler hides.
+    static constexpr int EPI_WARPS = MT >= 32 ? 8 : 4;
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+    static constexpr int NC = NLD / (EPI_WARPS / 4);             // accumulator columns per epilogue thread
 };
 
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -144,7 +157,7 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
 // Persistent kernel: CTA b works on units b, b + gridDim.x, ...; a unit is (activation tile, K segment,
 // 128-row weight tile).  The TMA / MMA / TMEM pipeline keeps running across unit boundaries.
 template <int MT, int NLD>
-__global__ void __launch_bounds__(TC_THREADS)
+__global__ void __launch_bounds__((TcCfg<MT, NLD>::THREADS))
 gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensorMap map_xq,
                const __grid_constant__ CUtensorMap map_xd, uint32_t K, uint32_t N, uint32_t M, float *__restrict__ part,
                uint32_t S, uint32_t tiles, uint32_t units, int *err_flag, unsigned long long *tl,
@@ -167,11 +180,11 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < NST; ++i) {
             mbar_init(bar_full + 8 * i, 1);
-            mbar_init(bar_empty + 8 * i, 1 + 4);          // MMA commit + one lane of every epilogue warp
+            mbar_init(bar_empty + 8 * i, 1 + C::EPI_WARPS);   // MMA commit + one lane of every epilogue warp
         }
         for (uint32_t i = 0; i < NSLOT; ++i) {
             mbar_init(bar_tfull + 8 * i, 1);
-            mbar_init(bar_tempty + 8 * i, 4);
+            mbar_init(bar_tempty + 8 * i, C::EPI_WARPS);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -276,9 +289,9 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
         for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
             uint32_t tile, seg, m0, c_begin, n_it;
             decode(u, tile, seg, m0, c_begin, n_it);
-            float acc[NLD];
+            float acc[C::NC];
 #pragma unroll
-            for (int i = 0; i < NLD; ++i) acc[i] = 0.0f;
+            for (int i = 0; i < C::NC; ++i) acc[i] = 0.0f;
             if constexpr (NLD <= 16) {
                 // Small activation tiles (the HBM-bound regime): the scales of a stage are copied to registers
                 // as soon as the stage has landed and the stage is released at once, one stage ahead of the
@@ -325,31 +338,34 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
                     if (lane == 0) mbar_arrive(bar_tempty + 8 * slot);
                 }
             } else {
+                // Large activation tiles: this warp drains columns [c_base, c_base + NC) of its lane quarter.  The
+                // TMEM loads are software-pipelined: the next 16 columns are in flight while the current 16 are
+                // rescaled.
+                constexpr int NC = C::NC, NCH = NC / 16;                // 16-column chunks per 32-block
+                const uint32_t c_base = ((warp - 2) >> 2) * NC;
                 for (uint32_t it = 0; it < n_it && ok; ++it, ++git) {
                     const uint32_t st = git % NST, ph = (git / NST) & 1;
                     // warp-uniform results: the TMEM loads below are .aligned
                     if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * st, ph, abort_flag))) { ok = false; break; }
                     const uint8_t *stage = smem + (size_t)st * C::STAGE;
                     const __half *wd = reinterpret_cast<const __half *>(stage + QB_REC_Q_BYTES);
-                    const float *xd = reinterpret_cast<const float *>(stage + C::XD_OFF);
+                    const float *xd = reinterpret_cast<const float *>(stage + C::XD_OFF) + c_base;
                     for (int sp = 0; sp < C::SPS; ++sp, ++j) {
                         const uint32_t slot = j % NSLOT, sph = (j / NSLOT) & 1;
                         if (!__all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * slot, sph, abort_flag))) { ok = false; break; }
                         tc_fence_after();
+                        const uint32_t tbase = tmem_base + ((quarter * 32u) << 16) + slot * (C::KPS * MT) + c_base;
+                        int32_t v[2][16];
+                        tmem_ld<16>(tbase, v[0]);
 #pragma unroll
-                        for (int kl = 0; kl < C::KPS; ++kl) {
-                                const int kb = sp * C::KPS + kl;
+                        for (int q = 0; q < C::KPS * NCH; ++q) {
+                            const int kl = q / NCH, c0 = (q % NCH) * 16, kb = sp * C::KPS + kl;
+                            tmem_ld_wait16(v[q & 1]);
+                            if (q + 1 < C::KPS * NCH) tmem_ld<16>(tbase + ((q + 1) / NCH) * MT + ((q + 1) % NCH) * 16, v[(q + 1) & 1]);
                             const float dw = __half2float(wd[kb * 128 + r]);
-                            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + slot * (C::KPS * MT) + kl * MT;
 #pragma unroll
-                            for (int c0 = 0; c0 < NLD; c0 += C::CH) {
-                                int32_t v[C::CH];
-                                tmem_ld<C::CH>(taddr + c0, v);
-                                tmem_ld_wait();
-#pragma unroll
-                                for (int i = 0; i < C::CH; ++i)
-                                    acc[c0 + i] = __fmaf_rn(__fmul_rn(dw, xd[kb * MT + c0 + i]), (float)v[i], acc[c0 + i]);
-                            }
+                            for (int i = 0; i < 16; ++i)
+                                acc[c0 + i] = __fmaf_rn(__fmul_rn(dw, xd[kb * MT + c0 + i]), (float)v[q & 1][i], acc[c0 + i]);
                         }
                         tc_fence_before();
                         __syncwarp();
@@ -364,8 +380,8 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
             const uint32_t row = tile * 128 + r;
             if (ok && row < N) {
 #pragma unroll
-                for (int i = 0; i < NLD; ++i) {
-                    const uint32_t m = m0 + i;
+                for (int i = 0; i < C::NC; ++i) {
+                    const uint32_t m = m0 + (C::EPI_WARPS == 8 ? ((warp - 2) >> 2) * C::NC : 0u) + i;
                     if (m < M) {
                         const size_t o = ((size_t)seg * M + m) * N + row;
                         if (push.n == 0) part[o] = acc[i];
@@ -434,7 +450,7 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
     const size_t smem_bytes = C::TOTAL;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(TC_THREADS);
+    cfg.blockDim = dim3(C::THREADS);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attrs[1];
