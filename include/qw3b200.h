@@ -309,6 +309,9 @@ int qb_ipc_close(qb_ctx *ctx, void *dev_ptr);
 int qb_debug_timeline_enable(qb_ctx *ctx, uint32_t max_launches);
 int qb_debug_timeline_read(qb_ctx *ctx, uint64_t *out, uint32_t *grids, double *bytes, uint32_t max_launches,
                            uint32_t *n_out);
+/* Measured INT8 tensor-core peak: one CTA per SM issues iters x 4 tcgen05.mma.kind::i8 (128 x 256 x 32) on operands
+ * resident in shared memory; returns tera-ops per second (2 ops per multiply-add). */
+int qb_debug_int8_mma_peak(qb_ctx *ctx, uint32_t iters, double *tops_out);
 /* Number of kernels this library launched on the context since creation. */
 int64_t qb_launch_count(qb_ctx *ctx);
 

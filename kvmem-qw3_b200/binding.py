@@ -101,6 +101,7 @@ SIGNATURES = {
     "qb_ipc_export": (i32, [vp, vp, vp]),
     "qb_ipc_open": (i32, [vp, vp, C.POINTER(vp)]),
     "qb_ipc_close": (i32, [vp, vp]),
+    "qb_debug_int8_mma_peak": (i32, [vp, u32, C.POINTER(C.c_double)]),
     "qb_debug_timeline_enable": (i32, [vp, u32]),
     "qb_debug_timeline_read": (i32, [vp, vp, vp, vp, u32, C.POINTER(u32)]),
 }
@@ -242,6 +243,12 @@ class Context:
             n, c, t = ln.split("\t")
             out.append((n, int(c), float(t)))
         return out
+
+    def int8_mma_peak(self, iters=20000):
+        """Measured INT8 tensor-core peak in TOP/s (operands resident in shared memory)."""
+        t = C.c_double()
+        check(lib().qb_debug_int8_mma_peak(self.h, iters, C.byref(t)))
+        return t.value
 
     def timeline_enable(self, max_launches):
         check(lib().qb_debug_timeline_enable(self.h, max_launches))

@@ -110,6 +110,8 @@ def main():
         peak = float(json.load(open(p))["hbm_gbs"])
     rng = np.random.default_rng(5)
     e0, e1 = ctx.event(), ctx.event()
+    int8_peak = ctx.int8_mma_peak()
+    print(json.dumps({"int8_mma_peak_TOPs": round(int8_peak, 1), "how": "tcgen05.mma.kind::i8 128x256x32 back to back, operands in shared memory, one CTA per SM"}), flush=True)
     for shape in args.shapes.split(","):
         N, K = [int(v) for v in shape.split("x")]
         w = pkg.Weight.synth(ctx, 0x5EED, 77, N, K, 0.02)
@@ -142,7 +144,8 @@ def main():
                 nbytes = N * K / 32 * 34 + M * K * 1.125 + S * M * N * 4
                 print(json.dumps({"N": N, "K": K, "M": M, "ksplit": S, "impl": impl, "us": round(us, 2),
                                   "GBps": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peak, 3),
-                                  "TOPs": round(2.0 * M * N * K / us / 1e6, 2), "bit_identical_to_first_impl": same}), flush=True)
+                                  "TOPs": round(2.0 * M * N * K / us / 1e6, 2), "frac_int8_peak": round(2.0 * M * N * K / us / 1e6 / int8_peak, 4),
+                                  "bit_identical_to_first_impl": same}), flush=True)
             q.free(); d.free(); part.free()
         w.free()
     ctx.close()
