@@ -48,4 +48,35 @@ int ref_gated_delta_net(float *alpha, float *beta, const float *dt_bias, const f
                                                       T, nk, nv, hd, qkv_stride, gb_stride, out_stride, true, ckpt,
                                                       ckpt_count, 0));
 }
+
+// Device time of one launch of a reference GEMM kernel (kind 0 = mul_mat_vec_q8_0, 1 = mmq_q8_0, 2 = mmq_q8_0_medium):
+// median of `iters` launches, each after `flush` (a buffer larger than L2) has been rewritten, CUDA events on the
+// launching stream.  Returns -1 when the launcher declines the shape.
+int ref_time_gemm(int kind, const uint8_t *w, const void *y, float *dst, uint32_t rows, uint32_t cols, uint32_t batch,
+                  int iters, void *flush, size_t flush_bytes, float *us_out) {
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    float t[64];
+    if (iters > 64) iters = 64;
+    int n = 0;
+    for (int it = 0; it < iters + 2; ++it) {
+        if (flush) cudaMemsetAsync(flush, it & 0xff, flush_bytes, 0);
+        cudaEventRecord(e0, 0);
+        bool ok = kind == 0 ? qw3::ported::launch_mmvq_q8_0(w, y, dst, rows, cols, batch, rows, 0)
+                : kind == 1 ? qw3::ported::launch_mmq_q8_0(w, y, dst, rows, cols, batch, rows, 0)
+                            : qw3::ported::launch_mmq_q8_0_medium(w, y, dst, rows, cols, batch, rows, 0);
+        cudaEventRecord(e1, 0);
+        if (!ok) { cudaEventDestroy(e0); cudaEventDestroy(e1); return -1; }
+        if (cudaDeviceSynchronize() != cudaSuccess) { cudaEventDestroy(e0); cudaEventDestroy(e1); return (int)cudaGetLastError(); }
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (it >= 2) t[n++] = ms * 1e3f;
+    }
+    for (int i = 1; i < n; ++i) for (int j = i; j > 0 && t[j] < t[j - 1]; --j) { float x = t[j]; t[j] = t[j - 1]; t[j - 1] = x; }
+    *us_out = t[n / 2];
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return 0;
+}
 }
