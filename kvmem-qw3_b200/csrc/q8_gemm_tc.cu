@@ -112,6 +112,25 @@ __device__ __forceinline__ void tmem_ld_wait16(int32_t (&r)[16]) {
                  :: "memory");
 }
 
+// Two fp32 lanes per instruction (sm_100 packed arithmetic): each lane rounds exactly like the scalar operation.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 __host__ __device__ inline uint32_t tc_seg_begin(uint32_t s, uint32_t S, uint32_t nchunks) {
     return (uint32_t)(((uint64_t)s * nchunks) / S);
 }
@@ -141,10 +160,10 @@ struct TcCfg {
     static constexpr int NST = NST_FIT > 8 ? 8 : NST_FIT;
     static constexpr int TOTAL = STAGE * NST + BAR_BYTES + 1024;   // + slack to align the base to 1024
     static constexpr int CH = NLD < 16 ? NLD : 16;               // columns per tcgen05.ld
-    // Epilogue warps: four for the small tiles (one per TMEM lane quarter); eight from MT = 32 on (two per
-    // quarter, each taking half of the activation columns): the drain + rescale of a large tile is bound by
-    // instruction issue and dependent latencies, which a second warp per scheduler hides.
-    static constexpr int EPI_WARPS = MT >= 32 ? 8 : 4;
+    // Epilogue warps: four for the small tiles (one per TMEM lane quarter); eight from MT = 32 and sixteen at
+    // MT = 128 (two / four per quarter, each taking a slice of the activation columns): the drain + rescale of a
+    // large tile is bound by instruction issue and dependent latencies, which more warps per scheduler hide.
+    static constexpr int EPI_WARPS = MT >= 64 ? 16 : MT >= 32 ? 8 : 4;
     static constexpr int THREADS = 64 + 32 * EPI_WARPS;
     static constexpr int NC = NLD / (EPI_WARPS / 4);             // accumulator columns per epilogue thread
 };
@@ -343,6 +362,9 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
                 // rescaled.
                 constexpr int NC = C::NC, NCH = NC / 16;                // 16-column chunks per 32-block
                 const uint32_t c_base = ((warp - 2) >> 2) * NC;
+                f32x2 acc2[NC / 2];                                     // column pairs, packed arithmetic
+#pragma unroll
+                for (int i = 0; i < NC / 2; ++i) acc2[i] = pack2(0.0f, 0.0f);
                 for (uint32_t it = 0; it < n_it && ok; ++it, ++git) {
                     const uint32_t st = git % NST, ph = (git / NST) & 1;
                     // warp-uniform results: the TMEM loads below are .aligned
@@ -363,9 +385,11 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
                             tmem_ld_wait16(v[q & 1]);
                             if (q + 1 < C::KPS * NCH) tmem_ld<16>(tbase + ((q + 1) / NCH) * MT + ((q + 1) % NCH) * 16, v[(q + 1) & 1]);
                             const float dw = __half2float(wd[kb * 128 + r]);
+                            const f32x2 dw2 = pack2(dw, dw);
+                            const f32x2 *xd2 = reinterpret_cast<const f32x2 *>(xd + kb * MT + c0);
 #pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                acc[c0 + i] = __fmaf_rn(__fmul_rn(dw, xd[kb * MT + c0 + i]), (float)v[q & 1][i], acc[c0 + i]);
+                            for (int i = 0; i < 8; ++i)
+                                acc2[c0 / 2 + i] = fma2(mul2(dw2, xd2[i]), pack2((float)v[q & 1][2 * i], (float)v[q & 1][2 * i + 1]), acc2[c0 / 2 + i]);
                         }
                         tc_fence_before();
                         __syncwarp();
@@ -376,12 +400,14 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
                         if (lane == 0) mbar_arrive(bar_empty + 8 * st);
                     }
                 }
+#pragma unroll
+                for (int i = 0; i < NC / 2; ++i) unpack2(acc2[i], acc[2 * i], acc[2 * i + 1]);
             }
             const uint32_t row = tile * 128 + r;
             if (ok && row < N) {
 #pragma unroll
                 for (int i = 0; i < C::NC; ++i) {
-                    const uint32_t m = m0 + (C::EPI_WARPS == 8 ? ((warp - 2) >> 2) * C::NC : 0u) + i;
+                    const uint32_t m = m0 + (C::EPI_WARPS > 4 ? ((warp - 2) >> 2) * C::NC : 0u) + i;
                     if (m < M) {
                         const size_t o = ((size_t)seg * M + m) * N + row;
                         if (push.n == 0) part[o] = acc[i];
