@@ -21,8 +21,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // ---- one kernel for the whole layer -------------------------------------------------------------------------
-// grid (HD/32, nv, n_seqs), cluster (HD/32, 1, 1), block 512: the CTAs of a cluster share one v head, each owns 32
-// state columns (a warp 2 of them, lanes stripe the k dimension).  Rows are processed in blocks of 4:
+// grid (HD/COLS, nv, n_seqs), cluster (HD/COLS, 1, 1), block 512: the CTAs of a cluster share one v head, each owns
+// COLS = 32 or 64 state columns (a warp 2 or 4 of them, lanes stripe the k dimension).  Rows are processed in blocks of 4:
 //   conv + SiLU of the head's q and k channels (every CTA of the head repeats them: 2*HD cheap channels) and of
 //   its own 32 v channels, L2 norm of q and k, all in shared memory;
 //   the delta rule for the block's rows on the register-resident state (checkpoints written as it goes);
@@ -31,21 +31,21 @@ __device__ __forceinline__ float warp_sum(float v) {
 //   columns (= one quantisation block).
 // The q/k conv windows are read by several CTAs but written by one (v head < nk, column block 0), so the kernel
 // reads the conv state from conv and writes it to conv_out (a different buffer: the caller ping-pongs).
-template <int HD>
+template <int HD, int CPW>
 __global__ void __launch_bounds__(512, 2) dn_fused_kernel(DnArgs a) {
-    constexpr int NCB = HD / 32, RPL = HD / 32, CPW = 2, RB = 4, NCH = 2 * HD + 32;
+    constexpr int COLS = 16 * CPW, NCB = HD / COLS, NQB = COLS / 32, RPL = HD / 32, RB = 4, NCH = 2 * HD + COLS;
     constexpr int QK_WARPS = 2 * HD / 32;
     asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");     // "this CTA runs": awaited before the first push
     QB_PDL_ENTER();
     __shared__ float xs[RB][NCH];
     __shared__ float red[RB][8];
-    __shared__ float core_s[RB][32];
+    __shared__ float core_s[RB][COLS];
     __shared__ float gbs[RB][2];
-    __shared__ float cl_ss[2][NCB][RB];
+    __shared__ float cl_ss[2][HD / 32][RB];      // sums of squares per 32-column group of the head, by block parity
     const uint32_t cb = blockIdx.x, vh = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t slot = (uint32_t)a.slot_in[seq];        // requested now, first needed after the block inputs
     const uint32_t kh = vh % a.nk;                         // src/gated_delta_net.cu:105
     const uint32_t C = 2 * a.nk * HD + a.nv * HD, vdim = a.nv * HD, R = a.rows_per_seq;
-    const uint32_t slot = (uint32_t)a.slot_in[seq];
     const size_t ssz = (size_t)a.nv * HD * HD;
     float *state_seq = a.state + (size_t)seq * a.n_slots * ssz;
     const float *conv_in = a.conv + (size_t)seq * a.n_slots * C * 3;
@@ -53,46 +53,67 @@ __global__ void __launch_bounds__(512, 2) dn_fused_kernel(DnArgs a) {
 
     // thread tid < NCH convolves one channel: a q or k channel of head kh, or one of this CTA's 32 v channels
     const bool has = tid < NCH, is_qk = tid < 2 * HD;
-    const uint32_t ch = tid < HD ? kh * HD + tid : tid < 2 * HD ? a.nk * HD + kh * HD + (tid - HD) : 2 * a.nk * HD + vh * HD + cb * 32 + (tid - 2 * HD);
+    const uint32_t ch = tid < HD ? kh * HD + tid : tid < 2 * HD ? a.nk * HD + kh * HD + (tid - HD) : 2 * a.nk * HD + vh * HD + cb * COLS + (tid - 2 * HD);
     const bool writes = is_qk ? (vh < a.nk && cb == 0) : true;
-    float st[3] = {0.f, 0.f, 0.f}, w[4] = {0.f, 0.f, 0.f, 0.f};
-    if (has) {
+    const uint32_t col0 = cb * COLS + warp * CPW;
+    const uint32_t ng_t = warp % RB, ng_q = warp / RB;       // norm-gate role of this warp: row of the block, 32-column group
+
+    // The inputs of a row block (projection rows, gate inputs, z) do not depend on the state slot: they are
+    // requested first, and the next block's while the current one is processed.
+    struct BlockIn { float cur[RB]; float zv, graw; };
+    auto load_block = [&](uint32_t rb0) {
+        BlockIn in;
+        const uint32_t nrows = rb0 < R ? min((uint32_t)RB, R - rb0) : 0u;
+        const size_t row0 = (size_t)seq * R + rb0;
 #pragma unroll
-        for (int k = 0; k < 3; ++k) st[k] = conv_in[((size_t)slot * C + ch) * 3 + k];
+        for (int t = 0; t < RB; ++t) {
+            in.cur[t] = 0.0f;
+            if (has && (uint32_t)t < nrows) in.cur[t] = qb_ldsum(a.proj, (row0 + t) * a.proj_stride + ch, a.proj_S, a.proj_pstride);
+        }
+        in.zv = 0.0f;
+        if (ng_q < NQB && ng_t < nrows)
+            in.zv = qb_ldsum(a.proj, (row0 + ng_t) * a.proj_stride + C + vh * HD + cb * COLS + ng_q * 32 + lane, a.proj_S, a.proj_pstride);
+        in.graw = 0.0f;
+        if (warp == 15 && lane < 2 * nrows)      // (row, decay | write strength) of the block: lanes of the last warp
+            in.graw = qb_ldsum(a.proj, (row0 + (lane >> 1)) * a.proj_stride + C + vdim + (lane & 1) * a.nv + vh, a.proj_S, a.proj_pstride);
+        return in;
+    };
+    BlockIn nxt = load_block(0);
+    float w[4] = {0.f, 0.f, 0.f, 0.f};
+    if (has) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) w[k] = a.conv_w[(size_t)ch * 4 + k];
     }
-    // state columns of this warp
-    const uint32_t col0 = cb * 32 + warp * CPW;
+    const float oscale = rsqrtf((float)HD);
+    const float A = a.ssm_a[vh], bias = a.dt_bias[vh];
+    const float nw = ng_q < NQB ? a.norm_w[cb * COLS + ng_q * 32 + lane] : 0.0f;
+    uint32_t crank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+    // ... then everything that hangs on the slot: conv window and the warp's state columns
+    float st[3] = {0.f, 0.f, 0.f};
+    if (has) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) st[k] = conv_in[((size_t)slot * C + ch) * 3 + k];
+    }
     float s[CPW][RPL];
 #pragma unroll
     for (int cc = 0; cc < CPW; ++cc)
 #pragma unroll
         for (int r = 0; r < RPL; ++r)
             s[cc][r] = state_seq[(size_t)slot * ssz + ((size_t)vh * HD + col0 + cc) * HD + r * 32 + lane];
-    const float oscale = rsqrtf((float)HD);
-    const float A = a.ssm_a[vh], bias = a.dt_bias[vh];
-    const float nw = a.norm_w[cb * 32 + lane];
-    uint32_t crank;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
 
     for (uint32_t rb0 = 0, blk = 0; rb0 < R; rb0 += RB, ++blk) {
         const uint32_t nrows = min((uint32_t)RB, R - rb0), par = blk & 1;
         const size_t row0 = (size_t)seq * R + rb0;
-        // all loads of the block first
-        float cur[RB], zv = 0.0f;
+        const BlockIn in = nxt;
+        nxt = load_block(rb0 + RB);
+        const float zv = in.zv;
+        float cur[RB];
 #pragma unroll
-        for (int t = 0; t < RB; ++t) {
-            cur[t] = 0.0f;
-            if (has && (uint32_t)t < nrows) cur[t] = qb_ldsum(a.proj, (row0 + t) * a.proj_stride + ch, a.proj_S, a.proj_pstride);
-        }
-        if (warp < nrows) zv = qb_ldsum(a.proj, (row0 + warp) * a.proj_stride + C + vh * HD + cb * 32 + lane, a.proj_S, a.proj_pstride);
-        // decay and write strength of the block's rows: thread (t, which) of the last warp
-        if (warp == 15 && lane < 2 * nrows) {
-            const uint32_t t = lane >> 1, which = lane & 1;
-            const float raw = qb_ldsum(a.proj, (row0 + t) * a.proj_stride + C + vdim + which * a.nv + vh, a.proj_S, a.proj_pstride);
-            gbs[t][which] = which == 0 ? expf(log1pf(expf(raw + bias)) * A) : __fdiv_rn(1.0f, 1.0f + expf(-raw));
-        }
+        for (int t = 0; t < RB; ++t) cur[t] = in.cur[t];
+        // decay and write strength of the block's rows
+        if (warp == 15 && lane < 2 * nrows)
+            gbs[lane >> 1][lane & 1] = (lane & 1) == 0 ? expf(log1pf(expf(in.graw + bias)) * A) : __fdiv_rn(1.0f, 1.0f + expf(-in.graw));
         // conv + SiLU, conv-state checkpoints
         float x[RB];
 #pragma unroll
@@ -164,29 +185,34 @@ __global__ void __launch_bounds__(512, 2) dn_fused_kernel(DnArgs a) {
         // this CTA's part of the head's sum of squares, pushed to every CTA of the cluster
         if (blk == 0) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // all CTAs of the cluster run
         if (warp == 0) {
+            // one value per (32-column group of this CTA, row); the same grouping whatever COLS is, so the
+            // head's sum below adds the same numbers in the same order in both forms of the kernel
             float mine = 0.0f;
 #pragma unroll
-            for (int t = 0; t < RB; ++t) {
-                const float v = (uint32_t)t < nrows ? core_s[t][lane] : 0.0f;
-                const float ss = warp_sum(v * v);
-                if ((lane % RB) == (uint32_t)t) mine = ss;
-            }
-            if (lane < NCB * RB) {
-                uint32_t local = (uint32_t)__cvta_generic_to_shared(&cl_ss[par][crank][lane % RB]), remote;
-                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(lane / RB));
+            for (int q = 0; q < NQB; ++q)
+#pragma unroll
+                for (int t = 0; t < RB; ++t) {
+                    const float v = (uint32_t)t < nrows ? core_s[t][q * 32 + lane] : 0.0f;
+                    const float ss = warp_sum(v * v);
+                    if ((lane % (NQB * RB)) == (uint32_t)(q * RB + t)) mine = ss;
+                }
+            if (lane < NCB * NQB * RB) {
+                const uint32_t dest = lane / (NQB * RB), q = (lane / RB) % NQB, t = lane % RB;
+                uint32_t local = (uint32_t)__cvta_generic_to_shared(&cl_ss[par][crank * NQB + q][t]), remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(dest));
                 asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(mine) : "memory");
             }
         }
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-        // RMSNorm * gain * SiLU(z), int8 quantisation: warp t takes row t, lane = column
-        if (warp < nrows) {
-            const uint32_t t = warp, col = vh * HD + cb * 32 + lane;
+        // RMSNorm * gain * SiLU(z), int8 quantisation: a warp takes (row, 32-column group), lane = column
+        if (ng_q < NQB && ng_t < nrows) {
+            const uint32_t t = ng_t, col = vh * HD + cb * COLS + ng_q * 32 + lane;
             const size_t row = row0 + t;
             float tot = 0.0f;
 #pragma unroll
-            for (int r = 0; r < NCB; ++r) tot += cl_ss[par][r][t];
-            const float o = core_s[t][lane] * rsqrtf(tot / (float)HD + a.eps) * nw * __fdiv_rn(zv, 1.0f + expf(-zv));
+            for (int r = 0; r < HD / 32; ++r) tot += cl_ss[par][r][t];
+            const float o = core_s[t][ng_q * 32 + lane] * rsqrtf(tot / (float)HD + a.eps) * nw * __fdiv_rn(zv, 1.0f + expf(-zv));
             if (a.core_out) a.core_out[row * vdim + col] = o;
             if (a.q8) {
                 float amax = fabsf(o);
@@ -211,22 +237,22 @@ __global__ void __launch_bounds__(512, 2) dn_fused_kernel(DnArgs a) {
     }
 }
 
-template <int HD>
+template <int HD, int CPW>
 int launch_fused(qb_ctx *ctx, const DnArgs &a) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(HD / 32, a.nv, a.n_seqs);
+    cfg.gridDim = dim3(HD / (16 * CPW), a.nv, a.n_seqs);
     cfg.blockDim = dim3(512);
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     attr[1].id = cudaLaunchAttributeClusterDimension;
-    attr[1].val.clusterDim.x = HD / 32;
+    attr[1].val.clusterDim.x = HD / (16 * CPW);
     attr[1].val.clusterDim.y = 1;
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    QB_CUDA(cudaLaunchKernelEx(&cfg, dn_fused_kernel<HD>, a));
+    QB_CUDA(cudaLaunchKernelEx(&cfg, (dn_fused_kernel<HD, CPW>), a));
     QB_LAUNCHED(ctx, "dn_fused_kernel");
     return QB_OK;
 }
@@ -238,7 +264,10 @@ int qb_launch_deltanet(qb_ctx *ctx, const DnArgs &a) {
     QB_REQUIRE(!a.write_all || a.rows_per_seq <= a.n_slots, "deltanet: %u rows need %u checkpoint slots, have %u",
                a.rows_per_seq, a.rows_per_seq, a.n_slots);
     QB_REQUIRE(a.conv_out && a.conv_out != a.conv, "deltanet: the new conv state needs a buffer of its own");
-    if (a.hd == 128) return launch_fused<128>(ctx, a);
-    if (a.hd == 64) return launch_fused<64>(ctx, a);
+    // one request: 32 state columns per CTA (more CTAs, shortest critical path); several: 64 per CTA (the per-CTA
+    // work that does not depend on the column count — the head's q/k conv, the barriers — is paid half as often)
+    const bool wide = a.n_seqs > 2;
+    if (a.hd == 128) return wide ? launch_fused<128, 4>(ctx, a) : launch_fused<128, 2>(ctx, a);
+    if (a.hd == 64) return wide ? launch_fused<64, 4>(ctx, a) : launch_fused<64, 2>(ctx, a);
     return qb_fail(QB_ERR_UNSUPPORTED, "deltanet: head dim %u unsupported (64/128)", a.hd);
 }
