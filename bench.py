@@ -3,7 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 One "step" is one speculative step of one request: 3 chained MTP-head drafts, the 4-row target
-verification forward over all 64 layers, greedy acceptance and commit.  The workload is BASELINE
+verification forward over all 64 layers, greedy acceptance and commit.  The workload is benchmark
 configuration 2 (batch 1, prompt 2048 seeded uniform token ids in paged fp16 KV, page 16) in its
 forced-acceptance form: the verified drafts equal the true greedy continuation at a seeded 70% rate,
 because seeded random weights give the MTP head no natural acceptance.  The MTP-head drafts are still
@@ -158,7 +158,7 @@ def run_reference(args, rank):
 
 
 def workload_config(args):
-    return {"workload": "BASELINE config 2: 27B-class qwen35 shape (%d layers, hidden 5120, 24q/4kv x 256, DeltaNet 16k/48v x 128, "
+    return {"workload": "configuration 2: 27B-class qwen35 shape (%d layers, hidden 5120, 24q/4kv x 256, DeltaNet 16k/48v x 128, "
                         "FFN 17408, vocab 151936), Q8_0, MTP k=3, batch %d, prompt %d, forced drafts = greedy continuation at a "
                         "seeded 70%% rate" % (args.layers, args.seqs, args.prompt),
             "draft_k": K_DRAFT, "prompt_len": args.prompt, "requests_per_gpu": args.seqs, "page_size": 16, "kv_dtype": "fp16", "accept_rate_target": ACCEPT_RATE,

@@ -1,4 +1,4 @@
-"""Isolated verify-GEMM sweep (BASELINE configuration 5 on one GPU).
+"""Isolated verify-GEMM sweep (benchmark configuration 5 on one GPU).
 
 Q8_0 weights 5120x17408 and 17408x5120 (seeded), activations N(0,1) quantised per 32-block to int8,
 M in {1, 4, 16, 64, 128, 512}; both kernels (1 = CUDA-core dp4a streaming, 2 = tcgen05 INT8).  Each

@@ -79,7 +79,7 @@ def test_prefill_logits_and_greedy_stream_vs_oracle(qb, orc, ctx, tiny):
 
 
 def test_config1_mtp_k1_is_lossless(qb, orc, ctx, tiny):
-    """BASELINE config 1: prompt 64, decode 32, k=1: speculative stream == greedy stream exactly."""
+    """Configuration 1 (tiny model): prompt 64, decode 32, k=1: speculative stream == greedy stream exactly."""
     want = greedy_stream(qb, tiny["model"], tiny["prompt"], 32)[0][:32]
     b = qb.Batch(tiny["model"], 1, 256, 1)
     b.prefill(0, tiny["prompt"])
