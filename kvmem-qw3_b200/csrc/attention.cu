@@ -13,6 +13,8 @@
 // rows are in the launch.
 #include "qb_internal.h"
 
+#include <cstdlib>
+
 namespace {
 
 constexpr int ATT_THREADS = 256;
@@ -142,9 +144,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, con
     const uint32_t NQ = r_count * G;
     const int base_pos = seq_pos[seq] + (int)r_begin;            // position of the chunk's first row
     const int last_key = base_pos + (int)r_count - 1;            // highest key index any row here sees
-    const int k_begin = (int)(split * QB_ATTN_SPLIT);
+    const int k_begin = (int)(split * a.split_keys);
     if (k_begin > last_key) return;
-    const int k_end = min(k_begin + (int)QB_ATTN_SPLIT, last_key + 1);
+    const int k_end = min(k_begin + (int)a.split_keys, last_key + 1);
     const int n_tiles = (k_end - k_begin + TK - 1) / TK;
     const float scale = rsqrtf((float)HD);
     const int32_t *pt = a.page_table + (size_t)seq * a.pt_stride;
@@ -333,7 +335,7 @@ __global__ void attn_merge_kernel(AttnArgs a, const int32_t *__restrict__ seq_po
     __shared__ float red_m[8];
     const uint32_t row = blockIdx.x, head = blockIdx.y, i = threadIdx.x, hd = a.hd, lane = i & 31;
     const int pos = seq_pos[row / R] + (int)(row % R);
-    const uint32_t nsplit = ((uint32_t)pos + QB_ATTN_SPLIT) / QB_ATTN_SPLIT;
+    const uint32_t nsplit = ((uint32_t)pos + a.split_keys) / a.split_keys;
     const size_t p0 = ((size_t)row * a.n_heads + head) * max_splits;
     // block-wide maximum of the split maxima (all loads in flight together)
     float mx = -INFINITY;
@@ -393,7 +395,16 @@ int launch_split(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_
 
 }  // namespace
 
-static uint32_t max_splits_for(uint32_t max_pos) { return max_pos / QB_ATTN_SPLIT + 1; }
+// Keys per split: a fixed number (absolute boundaries), so a row's result never depends on the launch it is in.
+static uint32_t split_keys() {
+    static const uint32_t v = [] {
+        const char *e = getenv("QW3B200_ATTN_SPLIT");
+        const uint32_t n = e ? (uint32_t)atoi(e) : QB_ATTN_SPLIT;
+        return (n >= 64 && n % 64 == 0) ? n : QB_ATTN_SPLIT;
+    }();
+    return v;
+}
+static uint32_t max_splits_for(uint32_t max_pos) { return max_pos / split_keys() + 1; }
 
 size_t qb_attention_scratch_floats(uint32_t rows, uint32_t n_heads, uint32_t hd, uint32_t max_pos, size_t *ml_floats) {
     const size_t ms = max_splits_for(max_pos);
@@ -420,15 +431,17 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
     const uint32_t G = a.n_heads / a.n_kv;
     QB_REQUIRE(G * a.n_kv == a.n_heads && G <= 8, "attention: GQA group %u unsupported (<= 8)", G);
     const uint32_t ms = max_splits_for(a.max_pos);
+    AttnArgs aa = a;
+    aa.split_keys = split_keys();
     QB_REQUIRE(((uintptr_t)a.qkv & 7) == 0 && a.row_stride % 2 == 0, "attention: q rows must be 8-byte aligned");
     int st = QB_OK;
-    if (a.hd == 256) st = launch_split<256>(ctx, a, seq_pos, R, n_seqs, ms);
-    else if (a.hd == 128) st = launch_split<128>(ctx, a, seq_pos, R, n_seqs, ms);
-    else if (a.hd == 64) st = launch_split<64>(ctx, a, seq_pos, R, n_seqs, ms);
+    if (a.hd == 256) st = launch_split<256>(ctx, aa, seq_pos, R, n_seqs, ms);
+    else if (a.hd == 128) st = launch_split<128>(ctx, aa, seq_pos, R, n_seqs, ms);
+    else if (a.hd == 64) st = launch_split<64>(ctx, aa, seq_pos, R, n_seqs, ms);
     else return qb_fail(QB_ERR_UNSUPPORTED, "attention: head_dim %u unsupported", a.hd);
     QB_TRY(st);
     dim3 grid(a.rows, a.n_heads);
-    QB_CUDA(qb_launch_pdl(ctx->stream, attn_merge_kernel, dim3(grid), dim3(a.hd), (size_t)(0), a, seq_pos, R, ms, out, q8, q_pitch, d, d_ld));
+    QB_CUDA(qb_launch_pdl(ctx->stream, attn_merge_kernel, dim3(grid), dim3(a.hd), (size_t)(0), aa, seq_pos, R, ms, out, q8, q_pitch, d, d_ld));
     QB_LAUNCHED(ctx, "attn_merge_kernel");
     return QB_OK;
 }

@@ -232,6 +232,7 @@ struct AttnArgs {
     uint32_t max_pos = 0;            // upper bound of any row position (sizes the split grid)
     float *part_acc = nullptr, *part_ml = nullptr;   // split partials
     bool kv_only = false;            // prepare: skip the q heads
+    uint32_t split_keys = 0;         // keys per split (set by qb_attn_run)
 };
 int qb_attn_prepare(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t n_seqs);
 // split partials, then merge + gate; out fp32 [rows][n_heads*hd] and/or int8 (q8 [rows][q_pitch], d [.][d_ld]).

@@ -43,3 +43,14 @@ def test_oracle_is_not_reachable_from_the_product():
             if f.endswith((".py", ".cu", ".h", ".cuh", ".cpp")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in src.lower() or f == "binding.py" and False, (dirpath, f)
+
+
+def test_split_policy_of_library_and_oracle_agree(qb, orc):
+    """The number of K segments fixes the fp32 summation order of every projection: the library's policy (a host
+    function, no GPU needed) and the oracle's restatement must be the same function of the weight shape."""
+    L = qb.lib()
+    shapes = [(n, k) for n in (32, 96, 128, 256, 1024, 2048, 4096, 5120, 6144, 10240, 14336, 16480, 17408, 34816, 151936)
+              for k in (128, 256, 512, 2176, 4352, 5120, 6144, 8704, 10240, 17408)]
+    for n, k in shapes:
+        assert L.qb_ksplit_policy(n, k) == orc.ksplit_policy(n, k), (n, k)
+    assert L.qb_ksplit_policy(5120, 17408) == 7 and L.qb_ksplit_policy(16480, 5120) == 2 and L.qb_ksplit_policy(34816, 5120) == 1
