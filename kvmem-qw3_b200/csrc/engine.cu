@@ -209,7 +209,7 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
     qb_batch *b = new qb_batch();
     b->m = m; b->n_seqs = n_seqs; b->max_ctx = max_ctx; b->k = draft_k; b->page_size = page_size;
     b->pages_per_seq = (max_ctx + draft_k + 1 + page_size - 1) / page_size;
-    b->chunk = std::max(1u, env_u32("QW3B200_PREFILL_CHUNK", 64));
+    b->chunk = std::max(1u, env_u32("QW3B200_PREFILL_CHUNK", 128));
     b->logit_rows = n_seqs * (draft_k + 1);
     b->rows_cap = std::max(b->chunk, b->logit_rows);
     b->gemm_impl = (int)env_u32("QW3B200_GEMM_IMPL", 0);
