@@ -17,8 +17,6 @@
 
 namespace {
 
-constexpr int ATT_THREADS = 256;
-constexpr int ATT_WARPS = 8;
 constexpr int TK = 64;          // keys per tile
 constexpr int QR = 4;           // query rows per CTA
 
@@ -91,10 +89,10 @@ __global__ void qk_norm_rope_append_kernel(AttnArgs a, const int32_t *__restrict
 // GQA group).  Tensor-core math on fp16 operands with fp32 accumulation (mma.sync m16n8k16; the kernel streams
 // the cache once and is bound by HBM, not by the tensor pipe): S = Q K^T with Q (scaled, fp16) held in
 // registers as A fragments, P = exp(S - m) written to shared memory as fp16, O += P V with V read through
-// ldmatrix.trans.  Warp w = (h, j): query rows [16h, 16h+16), keys [16j, 16j+16) of the tile for S and
-// output dims [j*HD/4, (j+1)*HD/4) for O.  The running maximum of a row is shared by the four warps that hold
-// it (one exchange per tile through shared memory); each warp keeps its own partial row sum, added in warp
-// order at the end.  K/V tiles arrive through a 3-stage cp.async pipeline (zero-filled past the last key).
+// ldmatrix.trans.  Warp w = (h, j), j < JW (8 for head dims 128 / 256, 4 for 64): query rows [16h, 16h+16), keys
+// [j*64/JW, (j+1)*64/JW) of the tile for S and output dims [j*HD/JW, (j+1)*HD/JW) for O.  The running maximum of a
+// row is shared by the JW warps that hold it (one exchange per tile through shared memory); each warp keeps its
+// own partial row sum, added in warp order at the end.  K/V tiles arrive through a 3-stage cp.async pipeline (zero-filled past the last key).
 template <int HD>
 struct AttSmem {
     static constexpr int ROWB = HD * 2 + 16;                // bytes per key / query row (padded: conflict-free ldmatrix)
@@ -106,8 +104,8 @@ struct AttSmem {
     static constexpr int P_ROWB = TK * 2 + 16;
     static constexpr int P_OFF = Q_OFF + Q_BYTES;
     static constexpr int P_BYTES = 32 * P_ROWB;
-    static constexpr int RED_OFF = P_OFF + P_BYTES;         // float [4 warps j][32 rows]
-    static constexpr int TOTAL = RED_OFF + 4 * 32 * 4;
+    static constexpr int RED_OFF = P_OFF + P_BYTES;         // float [up to 8 warps j][32 rows]
+    static constexpr int TOTAL = RED_OFF + 8 * 32 * 4;
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -125,16 +123,19 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], u
 }
 
 // grid (max_splits, n_kv, n_seqs * ceil(R/QR)).
-template <int HD>
-__global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, const int32_t *__restrict__ seq_pos, uint32_t R,
+template <int HD, int JW>
+__global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const int32_t *__restrict__ seq_pos, uint32_t R,
                                                                  uint32_t max_splits) {
     QB_PDL_ENTER();
     using L = AttSmem<HD>;
+    constexpr int THREADS = 64 * JW, WARPS = 2 * JW;             // JW warps share a 16-query m-tile
+    constexpr int KW = TK / JW, NTS = KW / 8;                    // keys (8-key n-tiles) of a tile per warp
+    constexpr int DW = HD / JW;                                  // output dims per warp
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     float *red = reinterpret_cast<float *>(smem + L::RED_OFF);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t h = warp & 1, j = warp >> 1;                  // query m-tile, key / output-dim quarter
+    const uint32_t h = warp & 1, j = warp >> 1;                  // query m-tile, key / output-dim slice
     const uint32_t g4 = lane >> 2, t4 = lane & 3;                // accumulator row / column pair of this lane
     const uint32_t split = blockIdx.x, kvh = blockIdx.y;
     const uint32_t chunks = (R + QR - 1) / QR;
@@ -160,7 +161,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, con
     auto load_tile = [&](int tile, int slot) {
         uint8_t *ks = smem + slot * L::STAGE, *vs = ks + L::KV_TILE;
         constexpr int CH = HD * 2 / 16;                          // 16-byte chunks per key row
-        constexpr int RPP = ATT_THREADS / CH;                    // rows per pass
+        constexpr int RPP = THREADS / CH;                    // rows per pass
         const int p = tid % CH;
 #pragma unroll
         for (int t = tid / CH; t < TK; t += RPP) {
@@ -182,7 +183,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, con
     cp_async_commit();
 
     // stage the queries (scaled, fp16): query index qi = r_local * G + g, head = kvh*G + g; missing rows are zero
-    for (uint32_t qi = warp; qi < 32; qi += ATT_WARPS) {
+    for (uint32_t qi = warp; qi < 32; qi += WARPS) {
         const uint32_t rl = qi / G, gq = qi - rl * G;
         const float *src = a.qkv + ((size_t)seq * R + r_begin + rl) * a.row_stride + (size_t)(kvh * G + gq) * 2 * HD;
 #pragma unroll
@@ -201,7 +202,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, con
     for (int ks = 0; ks < HD / 16; ++ks)
         ldsm_x4(qf[ks], smem_base + L::Q_OFF + (h * 16 + (lane & 15)) * L::ROWB + (ks * 16 + (lane >> 4) * 8) * 2);
 
-    constexpr int NT_O = HD / 32;                                // 8-wide output tiles per warp (HD/4 dims)
+    constexpr int NT_O = DW / 8;                                 // 8-wide output tiles per warp
     float o[NT_O][4];
 #pragma unroll
     for (int n = 0; n < NT_O; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
@@ -220,24 +221,41 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, con
         if (tile + 2 < n_tiles) load_tile(tile + 2, (tile + 2) % L::NSTAGE);
         cp_async_commit();
         const uint32_t ks_base = smem_base + (tile % L::NSTAGE) * L::STAGE, vs_base = ks_base + L::KV_TILE;
-        const int key0 = k_begin + tile * TK + (int)j * 16;     // first key of this warp's 16
+        const int key0 = k_begin + tile * TK + (int)j * KW;     // first key of this warp's KW
 
-        // S = Q K^T for 16 queries x 16 keys
-        float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        if (active) {
-            const uint32_t kaddr = ks_base + (j * 16 + (lane & 7) + ((lane >> 4) << 3)) * L::ROWB + (((lane >> 3) & 1) * 8) * 2;
+        // S = Q K^T for 16 queries x KW keys
+        float sc[NTS][4];
 #pragma unroll
-            for (int ks = 0; ks < HD / 16; ++ks) {
-                uint32_t b[4];
-                ldsm_x4(b, kaddr + ks * 32);
-                mma_f16(sc[0], qf[ks], b[0], b[1]);
-                mma_f16(sc[1], qf[ks], b[2], b[3]);
+        for (int nt = 0; nt < NTS; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.0f; }
+        if (active) {
+            if constexpr (NTS == 2) {
+                const uint32_t kaddr = ks_base + (j * KW + (lane & 7) + ((lane >> 4) << 3)) * L::ROWB + (((lane >> 3) & 1) * 8) * 2;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    uint32_t b[4];
+                    ldsm_x4(b, kaddr + ks * 32);
+                    mma_f16(sc[0], qf[ks], b[0], b[1]);
+                    mma_f16(sc[1], qf[ks], b[2], b[3]);
+                }
+            } else {
+                // one 8-key n-tile: an x4 load covers two k-steps (d 0-7, 8-15, 16-23, 24-31)
+                const uint32_t kaddr = ks_base + (j * KW + (lane & 7)) * L::ROWB + ((lane >> 3) * 8) * 2;
+#pragma unroll
+                float s2[4] = {0.f, 0.f, 0.f, 0.f};               // second accumulator: halves the dependent chain
+                for (int ks = 0; ks < HD / 16; ks += 2) {
+                    uint32_t b[4];
+                    ldsm_x4(b, kaddr + ks * 32);
+                    mma_f16(sc[0], qf[ks], b[0], b[1]);
+                    mma_f16(s2, qf[ks + 1], b[2], b[3]);
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) sc[0][c] += s2[c];
             }
         }
         // causal mask + this warp's row maxima
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < NTS; ++nt)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int key = key0 + nt * 8 + (int)t4 * 2 + (c & 1), e = c >> 1;
@@ -252,42 +270,45 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, con
         }
         __syncthreads();
         float corr[2];
-        uint32_t pk[2][2];                                       // P as fp16 pairs: [nt][row e]
+        uint32_t pk[NTS][2];                                     // P as fp16 pairs: [nt][row e]
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
             const uint32_t r = h * 16 + g4 + 8 * e;
-            const float m_tile = fmaxf(fmaxf(red[r], red[32 + r]), fmaxf(red[64 + r], red[96 + r]));
+            float m_tile = red[r];
+#pragma unroll
+            for (int w = 1; w < JW; ++w) m_tile = fmaxf(m_tile, red[w * 32 + r]);
             const float m_new = fmaxf(m_run[e], m_tile);
-            float p[4] = {0.f, 0.f, 0.f, 0.f};
             corr[e] = 1.0f;
-            if (m_new != -INFINITY) {
-                corr[e] = expf(m_run[e] - m_new);
-                p[0] = expf(sc[0][2 * e] - m_new); p[1] = expf(sc[0][2 * e + 1] - m_new);
-                p[2] = expf(sc[1][2 * e] - m_new); p[3] = expf(sc[1][2 * e + 1] - m_new);
+            float psum = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < NTS; ++nt) {
+                float p0 = 0.0f, p1 = 0.0f;
+                if (m_new != -INFINITY) { p0 = expf(sc[nt][2 * e] - m_new); p1 = expf(sc[nt][2 * e + 1] - m_new); }
+                const __half2 hp = __floats2half2_rn(p0, p1);
+                // the row sum uses the rounded probabilities, the values the tensor cores multiply with V
+                const float2 fp = __half22float2(hp);
+                psum += fp.x + fp.y;
+                pk[nt][e] = *reinterpret_cast<const uint32_t *>(&hp);
             }
-            const __half2 h0 = __floats2half2_rn(p[0], p[1]), h1 = __floats2half2_rn(p[2], p[3]);
-            // the row sum uses the rounded probabilities, the values the tensor cores multiply with V
-            const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-            l_run[e] = l_run[e] * corr[e] + ((f0.x + f0.y) + (f1.x + f1.y));
+            if (m_new != -INFINITY) corr[e] = expf(m_run[e] - m_new);
+            l_run[e] = l_run[e] * corr[e] + psum;
             m_run[e] = m_new;
-            pk[0][e] = *reinterpret_cast<const uint32_t *>(&h0);
-            pk[1][e] = *reinterpret_cast<const uint32_t *>(&h1);
         }
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < NTS; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e)
-                *reinterpret_cast<uint32_t *>(smem + L::P_OFF + (h * 16 + g4 + 8 * e) * L::P_ROWB + (j * 16 + nt * 8 + t4 * 2) * 2) = pk[nt][e];
+                *reinterpret_cast<uint32_t *>(smem + L::P_OFF + (h * 16 + g4 + 8 * e) * L::P_ROWB + (j * KW + nt * 8 + t4 * 2) * 2) = pk[nt][e];
 #pragma unroll
         for (int n = 0; n < NT_O; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
         __syncthreads();
-        // O += P V for 16 queries x HD/4 dims over the tile's 64 keys
+        // O += P V for 16 queries x DW dims over the tile's 64 keys
         if (active) {
 #pragma unroll
             for (int kk = 0; kk < TK / 16; ++kk) {
                 uint32_t pa[4];
                 ldsm_x4(pa, smem_base + L::P_OFF + (h * 16 + (lane & 15)) * L::P_ROWB + (kk * 16 + (lane >> 4) * 8) * 2);
-                const uint32_t vaddr = vs_base + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * L::ROWB + (j * (HD / 4) + (lane >> 4) * 8) * 2;
+                const uint32_t vaddr = vs_base + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * L::ROWB + (j * DW + (lane >> 4) * 8) * 2;
 #pragma unroll
                 for (int n2 = 0; n2 < NT_O / 2; ++n2) {
                     uint32_t b[4];
@@ -316,12 +337,15 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(AttnArgs a, con
         const size_t row = (size_t)seq * R + r_begin + qi / G;
         const uint32_t head = kvh * G + qi % G;
         const size_t pidx = (row * a.n_heads + head) * max_splits + split;
-        float *dst = a.part_acc + pidx * HD + j * (HD / 4) + t4 * 2;
+        float *dst = a.part_acc + pidx * HD + j * DW + t4 * 2;
 #pragma unroll
         for (int n = 0; n < NT_O; ++n) *reinterpret_cast<float2 *>(dst + n * 8) = make_float2(o[n][2 * e], o[n][2 * e + 1]);
         if (j == 0 && t4 == 0) {
             a.part_ml[pidx * 2] = m_run[e];
-            a.part_ml[pidx * 2 + 1] = ((red[qi] + red[32 + qi]) + red[64 + qi]) + red[96 + qi];
+            float l = red[qi];
+#pragma unroll
+            for (int w = 1; w < JW; ++w) l += red[w * 32 + qi];
+            a.part_ml[pidx * 2 + 1] = l;
         }
     }
 }
@@ -379,16 +403,16 @@ __global__ void attn_merge_kernel(AttnArgs a, const int32_t *__restrict__ seq_po
     }
 }
 
-template <int HD>
+template <int HD, int JW>
 int launch_split(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t R, uint32_t n_seqs, uint32_t max_splits) {
     using L = AttSmem<HD>;
     static bool attr = false;
     if (!attr) {
-        QB_CUDA(cudaFuncSetAttribute(attn_split_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        QB_CUDA(cudaFuncSetAttribute((attn_split_kernel<HD, JW>), cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         attr = true;
     }
     dim3 grid(max_splits, a.n_kv, n_seqs * ((R + QR - 1) / QR));
-    QB_CUDA(qb_launch_pdl(ctx->stream, attn_split_kernel<HD>, dim3(grid), dim3(ATT_THREADS), (size_t)(L::TOTAL), a, seq_pos, R, max_splits));
+    QB_CUDA(qb_launch_pdl(ctx->stream, (attn_split_kernel<HD, JW>), dim3(grid), dim3(64 * JW), (size_t)(L::TOTAL), a, seq_pos, R, max_splits));
     QB_LAUNCHED(ctx, "attn_split_kernel");
     return QB_OK;
 }
@@ -435,9 +459,9 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
     aa.split_keys = split_keys();
     QB_REQUIRE(((uintptr_t)a.qkv & 7) == 0 && a.row_stride % 2 == 0, "attention: q rows must be 8-byte aligned");
     int st = QB_OK;
-    if (a.hd == 256) st = launch_split<256>(ctx, aa, seq_pos, R, n_seqs, ms);
-    else if (a.hd == 128) st = launch_split<128>(ctx, aa, seq_pos, R, n_seqs, ms);
-    else if (a.hd == 64) st = launch_split<64>(ctx, aa, seq_pos, R, n_seqs, ms);
+    if (a.hd == 256) st = launch_split<256, 8>(ctx, aa, seq_pos, R, n_seqs, ms);
+    else if (a.hd == 128) st = launch_split<128, 8>(ctx, aa, seq_pos, R, n_seqs, ms);
+    else if (a.hd == 64) st = launch_split<64, 4>(ctx, aa, seq_pos, R, n_seqs, ms);
     else return qb_fail(QB_ERR_UNSUPPORTED, "attention: head_dim %u unsupported", a.hd);
     QB_TRY(st);
     dim3 grid(a.rows, a.n_heads);
