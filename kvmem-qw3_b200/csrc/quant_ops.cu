@@ -89,6 +89,66 @@ __device__ __forceinline__ void st4(float *p, float4 v, bool vec) {
     else { p[0] = v.x; p[1] = v.y; p[2] = v.z; p[3] = v.w; }
 }
 
+// The two phases of one thread's 4 consecutive elements.
+struct NqRow {
+    const float *x, *parts;
+    size_t pstride;
+    bool vx, vp, vh;
+};
+__device__ __forceinline__ NqRow nq_row(const NormQuantArgs &a, uint32_t m, uint32_t vec) {
+    NqRow r;
+    const uint32_t src = a.row_map ? (uint32_t)a.row_map[m] : m;
+    r.x = a.x ? a.x + (size_t)src * a.x_stride : nullptr;
+    r.parts = a.parts ? a.parts + (size_t)m * a.part_ld : nullptr;
+    r.pstride = (size_t)a.M * a.part_ld;
+    r.vx = vec & 1; r.vp = vec & 2; r.vh = vec & 4;
+    return r;
+}
+// loads: x + split partials (segments ascending, then the residual), gains; returns the 4 values and adds their
+// squares to ss in element order
+__device__ __forceinline__ void nq_load(const NormQuantArgs &a, const NqRow &r, uint32_t i, float4 &v, float4 &g, float &ss) {
+    float4 xv = r.x ? ld4(r.x + i, r.vx) : make_float4(0.f, 0.f, 0.f, 0.f);
+    g = a.w ? ld4(a.w + i, true) : make_float4(1.f, 1.f, 1.f, 1.f);
+    if (a.S > 0) {
+        float4 q[8];  // all segment loads are issued before the first add (S <= 8)
+#pragma unroll
+        for (uint32_t s = 0; s < 8; ++s) q[s] = s < a.S ? ld4(r.parts + s * r.pstride + i, r.vp) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 y = q[0];
+#pragma unroll
+        for (uint32_t s = 1; s < 8; ++s)
+            if (s < a.S) { y.x += q[s].x; y.y += q[s].y; y.z += q[s].z; y.w += q[s].w; }
+        if (r.x) { xv.x += y.x; xv.y += y.y; xv.z += y.z; xv.w += y.w; } else xv = y;
+    }
+    v = xv;
+    ss = __fmaf_rn(xv.x, xv.x, ss); ss = __fmaf_rn(xv.y, xv.y, ss); ss = __fmaf_rn(xv.z, xv.z, ss); ss = __fmaf_rn(xv.w, xv.w, ss);
+}
+// residual stream out, normalise, quantise (8 lanes = one 32-block); b = block index, i = first element
+__device__ __forceinline__ void nq_finish(const NormQuantArgs &a, const NqRow &r, uint32_t m, uint32_t b, uint32_t i, uint32_t lane,
+                                          float4 t, float4 g, float scale) {
+    if (a.h_out) st4(a.h_out + (size_t)m * a.h_stride + i, t, r.vh);
+    if (a.w) {
+        t.x = __fmul_rn(__fmul_rn(t.x, scale), g.x); t.y = __fmul_rn(__fmul_rn(t.y, scale), g.y);
+        t.z = __fmul_rn(__fmul_rn(t.z, scale), g.z); t.w = __fmul_rn(__fmul_rn(t.w, scale), g.w);
+    }
+    if (a.normed_out) st4(a.normed_out + (size_t)m * a.n + i, t, true);
+    if (a.q) {
+        // arithmetic of quantize_mmq_q8_1_kernel (src/mmvq_q8.cu:694-721)
+        const uint32_t grp = 0xffu << (lane & 24);
+        float amax = fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w)));
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(grp, amax, o));
+        const float d_inv = (amax == 0.0f) ? 0.0f : __fdiv_rn(127.0f, amax);
+        uint32_t packed = 0;
+        if (amax != 0.0f) {
+            const int q0 = __float2int_rn(__fmul_rn(t.x, d_inv)), q1 = __float2int_rn(__fmul_rn(t.y, d_inv));
+            const int q2 = __float2int_rn(__fmul_rn(t.z, d_inv)), q3 = __float2int_rn(__fmul_rn(t.w, d_inv));
+            packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+        }
+        *reinterpret_cast<uint32_t *>(a.q + (size_t)m * a.q_pitch + a.q_col_off + i) = packed;
+        if ((lane & 7) == 0) a.d[(size_t)(a.d_kb_off + b) * a.d_ld + m] = (amax == 0.0f) ? 0.0f : __fdiv_rn(1.0f, d_inv);
+    }
+}
+
 template <int P>
 __global__ void __launch_bounds__(NQ_THREADS) norm_quant_kernel(NormQuantArgs a, uint32_t vec) {
     asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");   // "this CTA runs": awaited before the pushes
@@ -100,11 +160,7 @@ __global__ void __launch_bounds__(NQ_THREADS) norm_quant_kernel(NormQuantArgs a,
     const uint32_t m = blockIdx.x / NQ_CLUSTER, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t nblk = a.n / 32, per = (nblk + NQ_CLUSTER - 1) / NQ_CLUSTER;
     const uint32_t b0 = crank * per, b1 = min(nblk, b0 + per), sub = tid & 7;
-    const uint32_t src = a.row_map ? (uint32_t)a.row_map[m] : m;
-    const float *__restrict__ x = a.x ? a.x + (size_t)src * a.x_stride : nullptr;
-    const float *__restrict__ parts = a.parts ? a.parts + (size_t)m * a.part_ld : nullptr;
-    const size_t pstride = (size_t)a.M * a.part_ld;
-    const bool vx = vec & 1, vp = vec & 2, vh = vec & 4;
+    const NqRow r = nq_row(a, m, vec);
 
     float4 v[P], g[P];
     float ss = 0.0f;
@@ -113,23 +169,7 @@ __global__ void __launch_bounds__(NQ_THREADS) norm_quant_kernel(NormQuantArgs a,
         const uint32_t b = b0 + (tid >> 3) + 32 * p;
         v[p] = make_float4(0.f, 0.f, 0.f, 0.f);
         g[p] = make_float4(1.f, 1.f, 1.f, 1.f);
-        if (b < b1) {
-            const uint32_t i = b * 32 + sub * 4;
-            float4 xv = x ? ld4(x + i, vx) : make_float4(0.f, 0.f, 0.f, 0.f);
-            if (a.w) g[p] = ld4(a.w + i, true);
-            if (a.S > 0) {   // GEMM result first (segments ascending), then the residual
-                float4 q[8];  // all segment loads are issued before the first add (S <= 8)
-#pragma unroll
-                for (uint32_t s = 0; s < 8; ++s) q[s] = s < a.S ? ld4(parts + s * pstride + i, vp) : make_float4(0.f, 0.f, 0.f, 0.f);
-                float4 y = q[0];
-#pragma unroll
-                for (uint32_t s = 1; s < 8; ++s)
-                    if (s < a.S) { y.x += q[s].x; y.y += q[s].y; y.z += q[s].z; y.w += q[s].w; }
-                if (x) { xv.x += y.x; xv.y += y.y; xv.z += y.z; xv.w += y.w; } else xv = y;
-            }
-            v[p] = xv;
-            ss += xv.x * xv.x; ss += xv.y * xv.y; ss += xv.z * xv.z; ss += xv.w * xv.w;
-        }
+        if (b < b1) nq_load(a, r, b * 32 + sub * 4, v[p], g[p], ss);
     }
     float scale = 1.0f;
     if (a.w) {   // uniform over the cluster
@@ -155,30 +195,8 @@ __global__ void __launch_bounds__(NQ_THREADS) norm_quant_kernel(NormQuantArgs a,
 #pragma unroll
     for (int p = 0; p < P; ++p) {
         const uint32_t b = b0 + (tid >> 3) + 32 * p;
-        if (b >= b1) continue;          // whole 8-thread groups leave together; the shuffles below stay inside a group
-        const uint32_t i = b * 32 + sub * 4;
-        float4 t = v[p];
-        if (a.h_out) st4(a.h_out + (size_t)m * a.h_stride + i, t, vh);
-        if (a.w) {
-            t.x = t.x * scale * g[p].x; t.y = t.y * scale * g[p].y; t.z = t.z * scale * g[p].z; t.w = t.w * scale * g[p].w;
-        }
-        if (a.normed_out) st4(a.normed_out + (size_t)m * a.n + i, t, true);
-        if (a.q) {
-            // arithmetic of quantize_mmq_q8_1_kernel (src/mmvq_q8.cu:694-721)
-            const uint32_t grp = 0xffu << (lane & 24);
-            float amax = fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w)));
-#pragma unroll
-            for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(grp, amax, o));
-            const float d_inv = (amax == 0.0f) ? 0.0f : __fdiv_rn(127.0f, amax);
-            uint32_t packed = 0;
-            if (amax != 0.0f) {
-                const int q0 = __float2int_rn(__fmul_rn(t.x, d_inv)), q1 = __float2int_rn(__fmul_rn(t.y, d_inv));
-                const int q2 = __float2int_rn(__fmul_rn(t.z, d_inv)), q3 = __float2int_rn(__fmul_rn(t.w, d_inv));
-                packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
-            }
-            *reinterpret_cast<uint32_t *>(a.q + (size_t)m * a.q_pitch + a.q_col_off + i) = packed;
-            if (sub == 0) a.d[(size_t)(a.d_kb_off + b) * a.d_ld + m] = (amax == 0.0f) ? 0.0f : __fdiv_rn(1.0f, d_inv);
-        }
+        if (b >= b1) continue;          // whole 8-thread groups leave together; the shuffles stay inside a group
+        nq_finish(a, r, m, b, b * 32 + sub * 4, lane, v[p], g[p], scale);
     }
     if (!a.w) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // complete the opening arrive
 }
