@@ -136,9 +136,20 @@ CPU_SAMPLE_TEXT = ("one step per sample on a 4-layer slice (3 DeltaNet + 1 atten
                    "and MTP layer, ctx 8: 3 MTP drafts + 4-row verify; layer time scaled x16 to 64 layers")
 
 
+def all_host_threads():
+    """The CPU legs use every core the process may run on: the launcher of multi-rank runs exports
+    OMP_NUM_THREADS=1, which must not throttle the CPU baseline.  Call before the CPU library is loaded."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(n)
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
+    all_host_threads()
     pkg, O = entry.load_package(), entry.load_oracle()
     models, seqs = cpu_setup(O, pkg)
     for _ in range(args.warmup):
@@ -179,6 +190,8 @@ def peaks():
 
 def run_ours(args, rank, world, local_rank, dist):
     pkg = entry.load_package()
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        all_host_threads()
     O = entry.load_oracle() if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
     ctx = pkg.Context(local_rank)
     cfg = pkg.configs.qwen27b(args.layers)
