@@ -158,6 +158,15 @@ __global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const i
     const uint32_t psz = a.page_size;
     const bool pow2 = (psz & (psz - 1)) == 0;
     const int psh = __ffs((int)psz) - 1;
+    // first slot of every page the split touches, looked up once (the tile loop then reads shared memory only)
+    __shared__ int page_slot[64];
+    {
+        const uint32_t pg0 = pow2 ? (uint32_t)k_begin >> psh : (uint32_t)k_begin / psz;
+        const uint32_t pg1 = pow2 ? (uint32_t)(k_end - 1) >> psh : (uint32_t)(k_end - 1) / psz;
+        for (uint32_t i = tid; i <= pg1 - pg0 && i < 64; i += THREADS) page_slot[i] = pt[pg0 + i] * (int)psz;
+        __syncthreads();
+    }
+    const uint32_t pg_first = pow2 ? (uint32_t)k_begin >> psh : (uint32_t)k_begin / psz;
     auto load_tile = [&](int tile, int slot) {
         uint8_t *ks = smem + slot * L::STAGE, *vs = ks + L::KV_TILE;
         constexpr int CH = HD * 2 / 16;                          // 16-byte chunks per key row
@@ -171,7 +180,7 @@ __global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const i
             if (valid) {
                 const uint32_t pg = pow2 ? (uint32_t)key >> psh : (uint32_t)key / psz;
                 const uint32_t in_pg = (uint32_t)key - pg * psz;
-                off = (((size_t)pt[pg] * psz + in_pg) * a.n_kv + kvh) * HD;
+                off = ((size_t)(page_slot[pg - pg_first] + (int)in_pg) * a.n_kv + kvh) * HD;
             }
             cp_async16(ks + t * L::ROWB + p * 16, a.k_cache + off + p * 8, valid);
             cp_async16(vs + t * L::ROWB + p * 16, a.v_cache + off + p * 8, valid);
@@ -283,14 +292,14 @@ __global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const i
 #pragma unroll
             for (int nt = 0; nt < NTS; ++nt) {
                 float p0 = 0.0f, p1 = 0.0f;
-                if (m_new != -INFINITY) { p0 = expf(sc[nt][2 * e] - m_new); p1 = expf(sc[nt][2 * e + 1] - m_new); }
+                if (m_new != -INFINITY) { p0 = __expf(sc[nt][2 * e] - m_new); p1 = __expf(sc[nt][2 * e + 1] - m_new); }
                 const __half2 hp = __floats2half2_rn(p0, p1);
                 // the row sum uses the rounded probabilities, the values the tensor cores multiply with V
                 const float2 fp = __half22float2(hp);
                 psum += fp.x + fp.y;
                 pk[nt][e] = *reinterpret_cast<const uint32_t *>(&hp);
             }
-            if (m_new != -INFINITY) corr[e] = expf(m_run[e] - m_new);
+            if (m_new != -INFINITY) corr[e] = __expf(m_run[e] - m_new);
             l_run[e] = l_run[e] * corr[e] + psum;
             m_run[e] = m_new;
         }
@@ -457,6 +466,7 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
     const uint32_t ms = max_splits_for(a.max_pos);
     AttnArgs aa = a;
     aa.split_keys = split_keys();
+    QB_REQUIRE(aa.split_keys / a.page_size <= 64, "attention: a split of %u keys spans more than 64 pages of %u", aa.split_keys, a.page_size);
     QB_REQUIRE(((uintptr_t)a.qkv & 7) == 0 && a.row_stride % 2 == 0, "attention: q rows must be 8-byte aligned");
     int st = QB_OK;
     if (a.hd == 256) st = launch_split<256, 8>(ctx, aa, seq_pos, R, n_seqs, ms);
