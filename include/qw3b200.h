@@ -113,7 +113,7 @@ int qb_quantize_q8_1(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t K, ui
  * {float d4[4], int8 q[128]}, block index sb * M + row. */
 int qb_quantize_q8_1_mmq(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t K, uint32_t x_stride, void *out_dev);
 /* The engine's own planar form of the same arithmetic as q8_1_mmq: q_dev = int8 [M][K],
- * d_dev = float [K/32][M]. */
+ * d_dev = float [K/32][ld] with ld = M rounded up to a multiple of 4 (scale of block kb of row m at kb*ld + m). */
 int qb_quantize_act(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t K, uint32_t x_stride,
                     int8_t *q_dev, float *d_dev);
 
