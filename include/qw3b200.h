@@ -149,6 +149,18 @@ int qb_q8_0_matmul_noalloc(qb_ctx *ctx, const qb_weight *w, const float *x_dev, 
 int qb_q8_gemm_partials(qb_ctx *ctx, const qb_weight *w, const int8_t *q_dev, const float *d_dev, uint32_t M,
                         float *part_dev, uint32_t ksplit, int impl);
 
+/* The two FFN input tensors as ONE weight, rows interleaved in groups of 64 (tile t = gate rows [64t, 64t+64) then
+ * up rows [64t, 64t+64)): what weight_q8_0 (include/qw3/device_backend.hpp:215) does for ffn_gate and ffn_up, in
+ * the layout the fused kernel below needs. */
+int qb_weight_q8_0_gate_up(qb_ctx *ctx, const void *gate_blocks, const void *up_blocks, uint32_t n_ff, uint32_t cols,
+                           qb_weight **out);
+/* q8_0_matmul_silu_mul (include/qw3/device_backend.hpp:300-539): h = silu(W_gate x) * (W_up x) for M rows, left as
+ * the quantised input of the down projection: hq_dev = int8 [M][n_ff], hd_dev = float [n_ff/32][ld] (qb_quantize_act
+ * layout).  With M <= 16 and a one-segment weight the GEMM's epilogue does it in one launch; otherwise GEMM + a
+ * SwiGLU kernel.  mode: 0 = choose, 1 = always two launches, 2 = one launch or fail; all give the same bits. */
+int qb_q8_0_matmul_silu_mul_q8(qb_ctx *ctx, const qb_weight *gate_up, const float *x_dev, uint32_t M, uint32_t x_stride,
+                               int8_t *hq_dev, float *hd_dev, int mode);
+
 /* ---- element-wise / norm / rope / embedding --------------------------------------- */
 
 /* q8_get_rows_batch_kernel (src/kernels_cuda.cu:2075-2157): out[i][:] = dequant(row ids[i]). */

@@ -92,6 +92,8 @@ SIGNATURES = {
     "qb_trace_enable": (i32, [vp, i32]),
     "qb_trace_summary": (i32, [vp, C.c_char_p, sz]),
     "qb_launch_count": (C.c_int64, [vp]),
+    "qb_weight_q8_0_gate_up": (i32, [vp, vp, vp, u32, u32, C.POINTER(vp)]),
+    "qb_q8_0_matmul_silu_mul_q8": (i32, [vp, vp, vp, u32, u32, vp, vp, i32]),
     "qb_tp_recv_bytes": (sz, [u32, u32, u32, u32]),
     "qb_tp_group_create": (i32, [vp, u32, u32, C.POINTER(vp), u32, u32, u32, u32, C.POINTER(vp)]),
     "qb_tp_group_destroy": (i32, [vp, vp]),

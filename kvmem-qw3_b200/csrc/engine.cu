@@ -96,8 +96,10 @@ static int build_layer(qb_ctx *ctx, qb_model *m, LayerW &L, uint32_t il, bool re
         QB_TRY(upload_f32(ctx, dt, &L.dt_bias));
     }
     QB_TRY(qb_weight_alloc(ctx, 2 * c.n_ff, c.n_embd, &L.w_gate_up));
-    QB_TRY(qb_weight_fill_synth(ctx, L.w_gate_up, 0, c.n_ff, seed, tensor_id(il, T_FFN_GATE), sg));
-    QB_TRY(qb_weight_fill_synth(ctx, L.w_gate_up, c.n_ff, c.n_ff, seed, tensor_id(il, T_FFN_UP), sg));
+    // gate and up interleaved in groups of 64 rows: a 128-row tile holds both halves of 64 hidden indices
+    QB_REQUIRE(c.n_ff % 64 == 0, "model: FFN dimension %u is not a multiple of 64", c.n_ff);
+    QB_TRY(qb_weight_fill_synth(ctx, L.w_gate_up, 0, c.n_ff, seed, tensor_id(il, T_FFN_GATE), sg, 64));
+    QB_TRY(qb_weight_fill_synth(ctx, L.w_gate_up, 64, c.n_ff, seed, tensor_id(il, T_FFN_UP), sg, 64));
     QB_TRY(qb_weight_alloc(ctx, c.n_embd, c.n_ff, &L.w_down));
     QB_TRY(qb_weight_fill_synth(ctx, L.w_down, 0, c.n_embd, seed, tensor_id(il, T_FFN_DOWN), sg));
     m->weight_bytes += weight_bytes_of(L.w_in) + weight_bytes_of(L.w_out) + weight_bytes_of(L.w_gate_up) + weight_bytes_of(L.w_down);
@@ -541,8 +543,8 @@ static int attention_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t c
 
 static int ffn_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, float *h, uint32_t rows, const float *next_norm_w) {
     const qb_model_config &c = b->m->cfg;
-    QB_TRY(gemm_to(ctx, b, L.w_gate_up, b->xq_h, rows, b->act));
-    QB_TRY(qb_launch_swiglu_quant(ctx, b->act, 2 * c.n_ff, rows, c.n_ff, b->xq_ffn.q, b->xq_ffn.K, b->xq_ffn.d, qb_act_ld(rows)));
+    QB_TRY(qb_ffn_gate_up_swiglu(ctx, L.w_gate_up, b->xq_h.q, b->xq_h.d, rows, b->act, b->parts, b->parts_floats, b->xq_ffn.q, b->xq_ffn.K,
+                                 b->xq_ffn.d, qb_act_ld(rows), b->gemm_impl, 0));
     uint32_t S = 1;
     QB_TRY(gemm_parts(ctx, b, L.w_down, b->xq_ffn, rows, &S));
     return residual_norm_quant(ctx, b, h, rows, S, next_norm_w, b->xq_h);

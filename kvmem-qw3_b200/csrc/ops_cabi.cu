@@ -61,3 +61,22 @@ extern "C" int qb_deltanet_rows(qb_ctx *ctx, const float *proj_dev, uint32_t n_s
     d.core_out = core_dev;
     return qb_launch_deltanet(ctx, d);
 }
+
+// q8_0_matmul_silu_mul (include/qw3/device_backend.hpp:300-539) for the fused [gate; up] weight, leaving the result
+// as the quantised input of the down projection.
+extern "C" int qb_q8_0_matmul_silu_mul_q8(qb_ctx *ctx, const qb_weight *gate_up, const float *x_dev, uint32_t M, uint32_t x_stride,
+                                          int8_t *hq_dev, float *hd_dev, int mode) {
+    QB_REQUIRE(ctx && gate_up && x_dev && hq_dev && hd_dev && M > 0, "qb_q8_0_matmul_silu_mul_q8: bad arguments");
+    QB_REQUIRE(gate_up->rows % 128 == 0 && gate_up->cols % 128 == 0, "qb_q8_0_matmul_silu_mul_q8: weight must be whole 128 x 128 tiles");
+    const uint32_t K = gate_up->cols, N = gate_up->rows, F = N / 2, ld = qb_act_ld(M), S = qb_ksplit(N, K);
+    const size_t q_bytes = ((size_t)M * K + 255) & ~(size_t)255, d_bytes = ((size_t)(K / 32) * ld * 4 + 255) & ~(size_t)255;
+    const size_t act_floats = (size_t)S * M * N;
+    void *scr = nullptr;
+    QB_TRY(qb_ctx_scratch(ctx, q_bytes + d_bytes + act_floats * sizeof(float), &scr));
+    int8_t *xq = (int8_t *)scr;
+    float *xd = (float *)((uint8_t *)scr + q_bytes), *act = (float *)((uint8_t *)scr + q_bytes + d_bytes);
+    NormQuantArgs a;
+    a.x = x_dev; a.x_stride = x_stride; a.n = K; a.M = M; a.q = xq; a.q_pitch = K; a.d = xd; a.d_ld = ld;
+    QB_TRY(qb_launch_norm_quant(ctx, a));
+    return qb_ffn_gate_up_swiglu(ctx, gate_up, xq, xd, M, act, act, act_floats, hq_dev, F, hd_dev, ld, 0, mode);
+}

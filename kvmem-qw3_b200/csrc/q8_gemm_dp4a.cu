@@ -175,6 +175,25 @@ uint32_t qb_ksplit(uint32_t N, uint32_t K) {
 }
 extern "C" uint32_t qb_ksplit_policy(uint32_t N, uint32_t K) { return qb_ksplit(N, K); }
 
+int qb_ffn_gate_up_swiglu(qb_ctx *ctx, const qb_weight *w, const int8_t *xq, const float *xd, uint32_t M, float *act, float *parts,
+                          size_t parts_floats, int8_t *hq, uint32_t hq_pitch, float *hd, uint32_t hd_ld, int gemm_impl, int mode) {
+    const uint32_t F = w->rows / 2, S = qb_ksplit(w->rows, w->cols);
+    const bool can_fuse = M <= 16 && S == 1 && w->rows % 128 == 0 && w->cols / 128 > 8 && qb_gemm_tc_supported(w, M) && gemm_impl != 1;
+    QB_REQUIRE(mode != 2 || can_fuse, "gate/up + SwiGLU in one launch needs M <= 16, one K segment and K > 1024");
+    if (can_fuse && mode != 1) {
+        QbGemmSwiglu sw;
+        sw.q = hq; sw.d = hd; sw.q_pitch = hq_pitch; sw.d_ld = hd_ld;
+        return qb_launch_gemm_tc(ctx, w, xq, xd, M, nullptr, 1, nullptr, nullptr, &sw);
+    }
+    if (S == 1) {
+        QB_TRY(qb_launch_gemm(ctx, w, xq, xd, M, act, 1, gemm_impl));
+        return qb_launch_swiglu_quant(ctx, act, w->rows, M, F, hq, hq_pitch, hd, hd_ld, 1, 0, 64);
+    }
+    QB_REQUIRE((size_t)S * M * w->rows <= parts_floats, "split scratch too small");
+    QB_TRY(qb_launch_gemm(ctx, w, xq, xd, M, parts, S, gemm_impl));
+    return qb_launch_swiglu_quant(ctx, parts, w->rows, M, F, hq, hq_pitch, hd, hd_ld, S, (size_t)M * w->rows, 64);
+}
+
 int qb_launch_gemm_dp4a(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
                         uint32_t S) {
     QB_REQUIRE(M > 0 && S > 0 && S <= w->cols / 128, "gemm: bad M=%u or ksplit=%u", M, S);

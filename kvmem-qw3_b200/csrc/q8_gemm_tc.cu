@@ -156,9 +156,11 @@ struct TcCfg {
     static constexpr int TX_BYTES = (int)QB_REC_BYTES + B_BYTES + XD_BYTES;
     static constexpr int STAGE = (XD_OFF + XD_BYTES + 1023) / 1024 * 1024;
     static constexpr int BAR_BYTES = 1024;
-    static constexpr int NST_FIT = (232448 / CTAS_PER_SM - BAR_BYTES - 2048) / STAGE;
+    // fused SwiGLU (small tiles only): the up half of a tile's rows hands its sums to the gate half, two buffers
+    static constexpr int EX_BYTES = MT == 16 ? 2 * NLD * 64 * 4 : 0;
+    static constexpr int NST_FIT = (232448 / CTAS_PER_SM - BAR_BYTES - EX_BYTES - 2048) / STAGE;
     static constexpr int NST = NST_FIT > 8 ? 8 : NST_FIT;
-    static constexpr int TOTAL = STAGE * NST + BAR_BYTES + 1024;   // + slack to align the base to 1024
+    static constexpr int TOTAL = STAGE * NST + BAR_BYTES + EX_BYTES + 1024;   // + slack to align the base to 1024
     static constexpr int CH = NLD < 16 ? NLD : 16;               // columns per tcgen05.ld
     // Epilogue warps: four for the small tiles (one per TMEM lane quarter); eight from MT = 32 and sixteen at
     // MT = 128 (two / four per quarter, each taking a slice of the activation columns): the drain + rescale of a
@@ -180,7 +182,7 @@ __global__ void __launch_bounds__((TcCfg<MT, NLD>::THREADS))
 gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensorMap map_xq,
                const __grid_constant__ CUtensorMap map_xd, uint32_t K, uint32_t N, uint32_t M, float *__restrict__ part,
                uint32_t S, uint32_t tiles, uint32_t units, int *err_flag, unsigned long long *tl,
-               const __grid_constant__ QbGemmPush push) {
+               const __grid_constant__ QbGemmPush push, const QbGemmSwiglu swz) {
     using C = TcCfg<MT, NLD>;
     constexpr uint32_t NST = C::NST, NSLOT = C::NSLOT;
     extern __shared__ uint8_t smem_raw[];
@@ -191,6 +193,8 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
     const uint32_t bar_tfull = bar_empty + 8 * NST, bar_tempty = bar_tfull + 8 * NSLOT;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_mem + 8 * (2 * NST + 2 * NSLOT));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t bar_ex = smem_u32(bar_mem + 512);                  // two "up half stored" barriers (fused SwiGLU)
+    float *ex = reinterpret_cast<float *>(bar_mem + C::BAR_BYTES);    // [2][NLD][64]
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t nchunks = K / 128;
@@ -205,6 +209,8 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
             mbar_init(bar_tfull + 8 * i, 1);
             mbar_init(bar_tempty + 8 * i, C::EPI_WARPS);
         }
+        mbar_init(bar_ex, 2);
+        mbar_init(bar_ex + 8, 2);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -403,6 +409,35 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
 #pragma unroll
                 for (int i = 0; i < NC / 2; ++i) unpack2(acc2[i], acc[2 * i], acc[2 * i + 1]);
             }
+            if constexpr (MT == 16) {
+                if (swz.q != nullptr) {
+                    // fused SwiGLU: rows 64..127 of the tile are the up rows of the hidden indices whose gate rows are
+                    // rows 0..63: the up warps hand their sums over, the gate warps finish (a warp = one 32-block)
+                    const uint32_t n_unit = (u - blockIdx.x) / gridDim.x, buf = n_unit & 1, exph = (n_unit >> 1) & 1;
+                    float *exb = ex + buf * (NLD * 64);
+                    if (quarter >= 2) {
+                        if (ok) {
+#pragma unroll
+                            for (int i = 0; i < NLD; ++i) exb[i * 64 + (r - 64)] = acc[i];
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_ex + 8 * buf);          // arrives also when aborting: nobody waits in vain
+                    } else {
+                        if (!__all_sync(0xffffffffu, mbar_wait(bar_ex + 8 * buf, exph, abort_flag))) ok = false;
+                        if (ok) {
+                            const uint32_t hidx = tile * 64 + r;               // hidden index of this thread's gate row
+#pragma unroll
+                            for (int i = 0; i < NLD; ++i) {
+                                const uint32_t m = m0 + i;
+                                if (m < M)                                       // warp-uniform
+                                    quant_block_store(qb_swiglu(acc[i], exb[i * 64 + r]), (int)lane, swz.q + (size_t)m * swz.q_pitch + (hidx & ~31u),
+                                                      swz.d + (size_t)(hidx >> 5) * swz.d_ld + m);
+                            }
+                        }
+                    }
+                    continue;
+                }
+            }
             const uint32_t row = tile * 128 + r;
             if (ok && row < N) {
 #pragma unroll
@@ -449,7 +484,7 @@ std::map<MapKey, CUtensorMap> g_xq_maps, g_xd_maps;
 
 template <int MT, int NLD>
 int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S,
-              const QbGemmPush *push, uint32_t *grid_out) {
+              const QbGemmPush *push, uint32_t *grid_out, const QbGemmSwiglu *swiglu) {
     using C = TcCfg<MT, NLD>;
     static bool attr = false;
     if (!attr) {
@@ -485,7 +520,8 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
     QB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, NLD>, (const uint8_t *)w->rec, iq->second, id->second, K, w->rows, M, part, S,
-                               tiles, units, ctx->err_flag_dev, qb_timeline_slot(ctx, grid, (double)w->rows_pad * K / 32.0 * 34.0 + (double)M * K * 1.125 + (double)S * M * w->rows * 4.0), push ? *push : QbGemmPush()));
+                               tiles, units, ctx->err_flag_dev, qb_timeline_slot(ctx, grid, (double)w->rows_pad * K / 32.0 * 34.0 + (double)M * K * 1.125 + (double)S * M * w->rows * 4.0), push ? *push : QbGemmPush(),
+                               swiglu ? *swiglu : QbGemmSwiglu()));
     if (grid_out) *grid_out = grid;
     QB_LAUNCHED(ctx, "gemm_tc_kernel");
     return QB_OK;
@@ -498,13 +534,15 @@ bool qb_gemm_tc_supported(const qb_weight *w, uint32_t M) {
 }
 
 int qb_launch_gemm_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S,
-                      const QbGemmPush *push, uint32_t *grid_out) {
+                      const QbGemmPush *push, uint32_t *grid_out, const QbGemmSwiglu *swiglu) {
+    QB_REQUIRE(!swiglu || (M <= 16 && S == 1 && w->rows % 128 == 0 && w->cols / 128 > 8 && swiglu->q && swiglu->d),
+               "gemm: the fused SwiGLU needs M <= 16, one K segment, whole 128-row tiles and K > 1024");
     QB_REQUIRE(M > 0 && S > 0 && S <= w->cols / 128, "gemm: bad M=%u or ksplit=%u", M, S);
     QB_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)d & 15) == 0, "gemm: activation buffers must be 16-byte aligned");
-    if (M <= 4) return launch_tc<16, 4>(ctx, w, q, d, M, part, S, push, grid_out);
-    if (M <= 8) return launch_tc<16, 8>(ctx, w, q, d, M, part, S, push, grid_out);
-    if (M <= 16) return launch_tc<16, 16>(ctx, w, q, d, M, part, S, push, grid_out);
-    if (M <= 32) return launch_tc<32, 32>(ctx, w, q, d, M, part, S, push, grid_out);
-    if (M <= 64) return launch_tc<64, 64>(ctx, w, q, d, M, part, S, push, grid_out);
-    return launch_tc<128, 128>(ctx, w, q, d, M, part, S, push, grid_out);
+    if (M <= 4) return launch_tc<16, 4>(ctx, w, q, d, M, part, S, push, grid_out, swiglu);
+    if (M <= 8) return launch_tc<16, 8>(ctx, w, q, d, M, part, S, push, grid_out, swiglu);
+    if (M <= 16) return launch_tc<16, 16>(ctx, w, q, d, M, part, S, push, grid_out, swiglu);
+    if (M <= 32) return launch_tc<32, 32>(ctx, w, q, d, M, part, S, push, grid_out, swiglu);
+    if (M <= 64) return launch_tc<64, 64>(ctx, w, q, d, M, part, S, push, grid_out, swiglu);
+    return launch_tc<128, 128>(ctx, w, q, d, M, part, S, push, grid_out, swiglu);
 }

@@ -47,13 +47,22 @@ extern "C" void qb_weight_free(qb_ctx *ctx, qb_weight *w) {
 extern "C" uint32_t qb_weight_rows(const qb_weight *w) { return w->rows; }
 extern "C" uint32_t qb_weight_cols(const qb_weight *w) { return w->cols; }
 
+// Row of the device weight that holds row `row` of a tensor placed at row_off.  ileave = 0: row_off + row.
+// ileave = 64 (the two halves of a fused [gate; up] weight): the tensor's rows go to every other group of 64
+// rows, so each 128-row tile of the fused weight holds 64 gate rows (row_off 0) and the 64 up rows (row_off 64)
+// of the same hidden indices.
+__device__ __forceinline__ uint32_t q8_dest_row(uint32_t row_off, uint32_t row, uint32_t ileave) {
+    return ileave ? row_off + (row / ileave) * 2 * ileave + row % ileave : row_off + row;
+}
+
 // One thread per 32-block.
 __global__ void q8_synth_kernel(uint8_t *rec, uint32_t cols, uint32_t row_off, uint32_t rows,
-                                const float *__restrict__ table, uint64_t seed, uint32_t tensor_id, float sigma) {
+                                const float *__restrict__ table, uint64_t seed, uint32_t tensor_id, float sigma, uint32_t ileave) {
     const uint32_t nb = cols / 32;
     const uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= (uint64_t)rows * nb) return;
-    const uint32_t row = (uint32_t)(b / nb), kb = (uint32_t)(b % nb);
+    const uint32_t kb = (uint32_t)(b % nb);
+    const uint32_t row = q8_dest_row(0, (uint32_t)(b / nb), ileave);
     uint16_t dbits;
     __align__(16) int8_t qq[32];
     qs_synth_q8_0_block(table, seed, tensor_id, b, sigma, &dbits, qq);
@@ -63,25 +72,27 @@ __global__ void q8_synth_kernel(uint8_t *rec, uint32_t cols, uint32_t row_off, u
 }
 
 int qb_weight_fill_synth(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, uint64_t seed,
-                         uint32_t tensor_id, float sigma) {
-    QB_REQUIRE(row_off + rows <= w->rows_pad, "synth fill out of range");
+                         uint32_t tensor_id, float sigma, uint32_t ileave) {
+    QB_REQUIRE(ileave ? (rows % ileave == 0 && row_off + 2 * rows - ileave <= w->rows_pad) : row_off + rows <= w->rows_pad,
+               "synth fill out of range");
     const uint64_t nblocks = (uint64_t)rows * (w->cols / 32);
     const uint32_t threads = 128;
     const uint64_t grid = (nblocks + threads - 1) / threads;
     QB_REQUIRE(grid < (1ull << 31), "synth fill too large");
     q8_synth_kernel<<<(uint32_t)grid, threads, 0, ctx->stream>>>(w->rec, w->cols, row_off, rows, ctx->normal_table_dev, seed,
-                                                                tensor_id, sigma);
+                                                                tensor_id, sigma, ileave);
     QB_LAUNCHED(ctx, "q8_synth_kernel");
     return QB_OK;
 }
 
 // GGUF blocks (34 B, row-major block order) of `rows` rows -> device layout at row_off.
 __global__ void q8_repack_kernel(uint8_t *rec, uint32_t cols, uint32_t row_off, uint32_t rows,
-                                 const uint8_t *__restrict__ blocks) {
+                                 const uint8_t *__restrict__ blocks, uint32_t row0, uint32_t ileave) {
     const uint32_t nb = cols / 32;
     const uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= (uint64_t)rows * nb) return;
-    const uint32_t row = (uint32_t)(b / nb), kb = (uint32_t)(b % nb);
+    const uint32_t kb = (uint32_t)(b % nb);
+    const uint32_t row = q8_dest_row(0, row0 + (uint32_t)(b / nb), ileave);       // row0 = tensor row of the first staged row
     const uint16_t *src = reinterpret_cast<const uint16_t *>(blocks + b * 34);   // 2-byte aligned
     *reinterpret_cast<uint16_t *>(rec + qb_d_offset(cols, row_off + row, kb)) = src[0];
     uint16_t *lo = reinterpret_cast<uint16_t *>(rec + qb_q_offset(cols, row_off + row, kb * 32));
@@ -105,9 +116,10 @@ __global__ void q8_unpack_kernel(const uint8_t *rec, uint32_t cols, uint32_t row
 
 static const size_t STAGE_BYTES = (size_t)64 << 20;
 
-int qb_weight_fill_upload(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, const void *host_blocks) {
+int qb_weight_fill_upload(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, const void *host_blocks, uint32_t ileave) {
     QB_REQUIRE(host_blocks != nullptr, "weight upload: host pointer is null");
-    QB_REQUIRE(row_off + rows <= w->rows_pad, "weight upload out of range");
+    QB_REQUIRE(ileave ? (rows % ileave == 0 && row_off + 2 * rows - ileave <= w->rows_pad) : row_off + rows <= w->rows_pad,
+               "weight upload out of range");
     const size_t row_bytes = (size_t)(w->cols / 32) * 34;
     const uint32_t rows_per = (uint32_t)std::max<size_t>(1, STAGE_BYTES / row_bytes);
     void *stage = nullptr;
@@ -117,8 +129,8 @@ int qb_weight_fill_upload(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t 
         QB_CUDA(cudaMemcpyAsync(stage, (const uint8_t *)host_blocks + (size_t)r0 * row_bytes, (size_t)nr * row_bytes,
                                 cudaMemcpyHostToDevice, ctx->stream));
         const uint64_t nblocks = (uint64_t)nr * (w->cols / 32);
-        q8_repack_kernel<<<(uint32_t)((nblocks + 127) / 128), 128, 0, ctx->stream>>>(w->rec, w->cols, row_off + r0, nr,
-                                                                                     (const uint8_t *)stage);
+        q8_repack_kernel<<<(uint32_t)((nblocks + 127) / 128), 128, 0, ctx->stream>>>(w->rec, w->cols, row_off, nr,
+                                                                                     (const uint8_t *)stage, r0, ileave);
         QB_LAUNCHED(ctx, "q8_repack_kernel");
         QB_CUDA(cudaStreamSynchronize(ctx->stream));
     }
@@ -131,6 +143,21 @@ extern "C" int qb_weight_q8_0(qb_ctx *ctx, const void *host_blocks, uint32_t row
     qb_weight *w = nullptr;
     QB_TRY(qb_weight_alloc(ctx, rows, cols, &w));
     int s = qb_weight_fill_upload(ctx, w, 0, rows, host_blocks);
+    if (s != QB_OK) { qb_weight_free(ctx, w); return s; }
+    *out = w;
+    return QB_OK;
+}
+
+// Fused [gate; up] weight of an FFN from the two GGUF tensors, rows interleaved in groups of 64 (see q8_dest_row):
+// the layout the fused gate/up + SwiGLU kernel needs (a 128-row tile = 64 gate rows + the matching 64 up rows).
+extern "C" int qb_weight_q8_0_gate_up(qb_ctx *ctx, const void *gate_blocks, const void *up_blocks, uint32_t n_ff, uint32_t cols,
+                                      qb_weight **out) {
+    QB_REQUIRE(ctx && gate_blocks && up_blocks && out, "qb_weight_q8_0_gate_up: null argument");
+    QB_REQUIRE(n_ff % 64 == 0, "qb_weight_q8_0_gate_up: FFN dimension %u is not a multiple of 64", n_ff);
+    qb_weight *w = nullptr;
+    QB_TRY(qb_weight_alloc(ctx, 2 * n_ff, cols, &w));
+    int s = qb_weight_fill_upload(ctx, w, 0, n_ff, gate_blocks, 64);
+    if (s == QB_OK) s = qb_weight_fill_upload(ctx, w, 64, n_ff, up_blocks, 64);
     if (s != QB_OK) { qb_weight_free(ctx, w); return s; }
     *out = w;
     return QB_OK;

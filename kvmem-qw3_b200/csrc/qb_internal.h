@@ -138,8 +138,9 @@ __host__ __device__ inline size_t qb_d_offset(uint32_t cols, uint32_t row, uint3
 }
 int qb_weight_alloc(qb_ctx *ctx, uint32_t rows, uint32_t cols, qb_weight **out);
 int qb_weight_fill_synth(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, uint64_t seed,
-                         uint32_t tensor_id, float sigma);
-int qb_weight_fill_upload(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, const void *host_blocks);
+                         uint32_t tensor_id, float sigma, uint32_t ileave = 0);
+int qb_weight_fill_upload(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, const void *host_blocks,
+                          uint32_t ileave = 0);
 // rows [row_off, row_off+rows) of w as a weight of its own (row_off multiple of 128).
 int qb_weight_view(qb_ctx *ctx, const qb_weight *w, uint32_t row_off, uint32_t rows, qb_weight *out);
 
@@ -154,6 +155,30 @@ int qb_make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, uint32_t elem_byte
 static inline uint32_t qb_act_ld(uint32_t M) { return (M + 3u) & ~3u; }
 
 // x (+ optional residual / split partials) -> optional h_out -> optional RMSNorm -> int8 + scales.
+#ifdef __CUDACC__
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// One warp quantises one 32-block with the arithmetic of quantize_mmq_q8_1_kernel
+// (src/mmvq_q8.cu:694-721): d_inv = 127/amax, q = rint(x*d_inv), d = 1/d_inv.
+__device__ __forceinline__ void quant_block_store(float v, int lane, int8_t *q_blk, float *d_out) {
+    const float amax = warp_max(fabsf(v));
+    const float d_inv = (amax == 0.0f) ? 0.0f : __fdiv_rn(127.0f, amax);
+    const int qi = (amax == 0.0f) ? 0 : __float2int_rn(__fmul_rn(v, d_inv));
+    q_blk[lane] = (int8_t)qi;
+    if (lane == 0) *d_out = (amax == 0.0f) ? 0.0f : __fdiv_rn(1.0f, d_inv);
+}
+// silu(gate) * up (silu_mul_kernel src/kernels_cuda.cu:1894-1903)
+__device__ __forceinline__ float qb_swiglu(float g, float u) { return __fdiv_rn(g, 1.0f + expf(-g)) * u; }
+#endif
+
 // Sum of the S split partials of one GEMM output element, ascending (the order of the split reduction).
 __device__ __forceinline__ float qb_ldsum(const float *p, size_t idx, uint32_t S, size_t pstride) {
     const float p0 = p[idx];
@@ -187,7 +212,7 @@ int qb_launch_norm_quant(qb_ctx *ctx, const NormQuantArgs &a);
 // gate/up fp32 [M][2F] (gate cols [0,F), up cols [F,2F)) -> silu(gate)*up -> int8 + scales.  gu may hold S split
 // partials pstride floats apart (summed ascending on read).
 int qb_launch_swiglu_quant(qb_ctx *ctx, const float *gu, uint32_t gu_stride, uint32_t M, uint32_t F, int8_t *q,
-                           uint32_t q_pitch, float *d, uint32_t d_ld, uint32_t S = 1, size_t pstride = 0);
+                           uint32_t q_pitch, float *d, uint32_t d_ld, uint32_t S = 1, size_t pstride = 0, uint32_t ileave = 0);
 
 // ---- GEMM ----------------------------------------------------------------------------------
 // part[s][m][n] for s < S; activations q [M][K] pitch K, d [K/32][ld].
@@ -203,9 +228,23 @@ struct QbGemmPush {
     unsigned int *counter[8] = {};
     uint32_t n = 0;
 };
+// Optional fused SwiGLU of the tensor-core GEMM (M <= 16, one K segment, weight = [gate; up] interleaved in groups
+// of 64 rows): instead of the fp32 products the epilogue writes int8(silu(gate) * up) and its block scales, the
+// quantised input of the down projection.
+struct QbGemmSwiglu {
+    int8_t *q = nullptr;             // [M][q_pitch]
+    float *d = nullptr;              // [F/32][d_ld]
+    uint32_t q_pitch = 0, d_ld = 0;
+};
 int qb_launch_gemm_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
-                      uint32_t S, const QbGemmPush *push = nullptr, uint32_t *grid_out = nullptr);
+                      uint32_t S, const QbGemmPush *push = nullptr, uint32_t *grid_out = nullptr,
+                      const QbGemmSwiglu *swiglu = nullptr);
 bool qb_gemm_tc_supported(const qb_weight *w, uint32_t M);
+// hq/hd = quantise(silu(gate) * up) of x W^T for a fused, 64-row-interleaved [gate; up] weight.  Few rows and one K
+// segment: one launch (the GEMM epilogue does it); otherwise GEMM (into act, or split partials into parts) and the
+// SwiGLU kernel.  mode: 0 = as described, 1 = always two launches, 2 = one launch or fail.
+int qb_ffn_gate_up_swiglu(qb_ctx *ctx, const qb_weight *w, const int8_t *xq, const float *xd, uint32_t M, float *act, float *parts,
+                          size_t parts_floats, int8_t *hq, uint32_t hq_pitch, float *hd, uint32_t hd_ld, int gemm_impl, int mode);
 uint32_t qb_ksplit(uint32_t N, uint32_t K);
 // y[m][n] = sum_s part[s][m][n] (ascending s).
 int qb_launch_reduce_parts(qb_ctx *ctx, const float *part, uint32_t S, uint32_t M, uint32_t N, float *y,

@@ -1,27 +1,6 @@
 // Activation quantisers and the fused element-wise kernels around the Q8 GEMMs.
 #include "qb_internal.h"
 
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-
-// One warp quantises one 32-block with the arithmetic of quantize_mmq_q8_1_kernel
-// (src/mmvq_q8.cu:694-721): d_inv = 127/amax, q = rint(x*d_inv), d = 1/d_inv.
-__device__ __forceinline__ void quant_block_store(float v, int lane, int8_t *q_blk, float *d_out) {
-    const float amax = warp_max(fabsf(v));
-    const float d_inv = (amax == 0.0f) ? 0.0f : __fdiv_rn(127.0f, amax);
-    const int qi = (amax == 0.0f) ? 0 : __float2int_rn(__fmul_rn(v, d_inv));
-    q_blk[lane] = (int8_t)qi;
-    if (lane == 0) *d_out = (amax == 0.0f) ? 0.0f : __fdiv_rn(1.0f, d_inv);
-}
-
 // ---- reference-format quantisers (parity tests against the reference kernels) --------------
 
 // quantize_q8_1_kernel (src/mmvq_q8.cu:83-112): 36-byte blocks {half d, half sum, int8 q[32]}.
@@ -252,21 +231,25 @@ extern "C" int qb_rms_norm(qb_ctx *ctx, const float *x_dev, const float *w_dev, 
 }
 
 // silu(gate) * up -> int8 (silu_mul_kernel src/kernels_cuda.cu:1894-1903 fused with the quantiser).
+// ileave = 0: gate cols [0,F), up cols [F,2F); ileave = 64: the fused weight's interleaved order (hidden index c
+// has its gate at (c/64)*128 + c%64 and its up 64 further).
 __global__ void swiglu_quant_kernel(const float *__restrict__ gu, uint32_t gu_stride, uint32_t F, int8_t *q,
-                                    uint32_t q_pitch, float *d, uint32_t d_ld, uint32_t S, size_t pstride) {
+                                    uint32_t q_pitch, float *d, uint32_t d_ld, uint32_t S, size_t pstride, uint32_t ileave) {
     QB_PDL_ENTER();
     const uint32_t b = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32, m = blockIdx.y, lane = threadIdx.x & 31;
     if (b >= F / 32) return;
-    const float g = qb_ldsum(gu, (size_t)m * gu_stride + b * 32 + lane, S, pstride);
-    const float u = qb_ldsum(gu, (size_t)m * gu_stride + F + b * 32 + lane, S, pstride);
-    const float v = __fdiv_rn(g, 1.0f + expf(-g)) * u;
-    quant_block_store(v, lane, q + (size_t)m * q_pitch + b * 32, d + (size_t)b * d_ld + m);
+    const uint32_t c = b * 32 + lane;
+    const uint32_t gi = ileave ? (c / ileave) * 2 * ileave + c % ileave : c, ui = ileave ? gi + ileave : F + c;
+    const float g = qb_ldsum(gu, (size_t)m * gu_stride + gi, S, pstride);
+    const float u = qb_ldsum(gu, (size_t)m * gu_stride + ui, S, pstride);
+    quant_block_store(qb_swiglu(g, u), lane, q + (size_t)m * q_pitch + b * 32, d + (size_t)b * d_ld + m);
 }
 
 int qb_launch_swiglu_quant(qb_ctx *ctx, const float *gu, uint32_t gu_stride, uint32_t M, uint32_t F, int8_t *q,
-                           uint32_t q_pitch, float *d, uint32_t d_ld, uint32_t S, size_t pstride) {
+                           uint32_t q_pitch, float *d, uint32_t d_ld, uint32_t S, size_t pstride, uint32_t ileave) {
     dim3 grid((F / 32 + 7) / 8, M);
-    QB_CUDA(qb_launch_pdl(ctx->stream, swiglu_quant_kernel, dim3(grid), dim3(256), (size_t)(0), gu, gu_stride, F, q, q_pitch, d, d_ld, S, pstride));
+    QB_CUDA(qb_launch_pdl(ctx->stream, swiglu_quant_kernel, dim3(grid), dim3(256), (size_t)(0), gu, gu_stride, F, q, q_pitch, d, d_ld, S, pstride,
+                          ileave));
     QB_LAUNCHED(ctx, "swiglu_quant_kernel");
     return QB_OK;
 }
