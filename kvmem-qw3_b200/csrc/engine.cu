@@ -336,12 +336,22 @@ namespace {
 
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
 
+// Argmax of a row from its per-block partial results, by one warp (all lanes return it): largest value, lowest
+// index among equals (argmax_kernel src/kernels_cuda.cu:1765-1771).
 __device__ int final_argmax(const float *pval, const int32_t *pidx, uint32_t row) {
-    float bv = pval[(size_t)row * QB_ARGMAX_BLOCKS];
-    int bi = pidx[(size_t)row * QB_ARGMAX_BLOCKS];
-    for (uint32_t j = 1; j < QB_ARGMAX_BLOCKS; ++j) {
+    const uint32_t lane = threadIdx.x & 31;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (uint32_t j = lane; j < QB_ARGMAX_BLOCKS; j += 32) {
         const float v = pval[(size_t)row * QB_ARGMAX_BLOCKS + j];
         const int i = pidx[(size_t)row * QB_ARGMAX_BLOCKS + j];
+        if (better(v, i, bv, bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int i = __shfl_xor_sync(0xffffffffu, bi, o);
         if (better(v, i, bv, bi)) { bv = v; bi = i; }
     }
     return bi;
@@ -357,11 +367,13 @@ __global__ void prep_draft_kernel(const int32_t *cur, const int32_t *drafts, con
     seqpos[s] = pos[s] + (int)i;
 }
 
+// one warp per sequence
 __global__ void store_draft_kernel(const float *pval, const int32_t *pidx, uint32_t n_seqs, uint32_t k, uint32_t i, int32_t *drafts) {
     QB_PDL_ENTER();
-    const uint32_t s = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t s = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
     if (s >= n_seqs) return;
-    drafts[(size_t)s * k + i] = final_argmax(pval, pidx, s);
+    const int tok = final_argmax(pval, pidx, s);
+    if ((threadIdx.x & 31) == 0) drafts[(size_t)s * k + i] = tok;
 }
 
 __global__ void prep_verify_kernel(const int32_t *cur, const int32_t *drafts, uint32_t n_seqs, uint32_t k, int32_t *tok) {
@@ -393,11 +405,15 @@ __global__ void accept_commit_kernel(const float *pval, const int32_t *pidx, uin
                                      unsigned long long *stats) {
     QB_PDL_ENTER();
     __shared__ int s_acc;
+    __shared__ int am[8];
     const uint32_t s = blockIdx.x;
     const uint32_t K1 = k + 1;
+    if (threadIdx.x / 32 < K1) {                                    // warp r takes verify row r
+        const int t = final_argmax(pval, pidx, s * K1 + threadIdx.x / 32);
+        if ((threadIdx.x & 31) == 0) am[threadIdx.x / 32] = t;
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
-        int am[8];
-        for (uint32_t r = 0; r < K1; ++r) am[r] = final_argmax(pval, pidx, s * K1 + r);
         uint32_t a = 0;
         while (a < k && am[a] == drafts[(size_t)s * k + a]) ++a;
         int32_t *n_out = out_rec, *toks = out_rec + n_seqs, *opos = out_rec + n_seqs + (size_t)n_seqs * K1;
@@ -432,8 +448,9 @@ __global__ void greedy_commit_kernel(const float *pval, const int32_t *pidx, uin
     QB_PDL_ENTER();
     const uint32_t j = blockIdx.x, s = seq0 + j;
     if (j >= n) return;
+    int tok = 0;
+    if (threadIdx.x < 32) tok = final_argmax(pval, pidx, logit_row0 + j);
     if (threadIdx.x == 0) {
-        const int tok = final_argmax(pval, pidx, logit_row0 + j);
         int32_t *n_out = out_rec, *toks = out_rec + n_seqs, *opos = out_rec + n_seqs + (size_t)n_seqs * K1;
         toks[(size_t)s * K1] = tok;
         n_out[s] = 1;
@@ -729,7 +746,7 @@ extern "C" int qb_mtp_draft(qb_ctx *ctx, qb_batch *b) {
         // step 0 reads the target hidden of the last committed position, later steps the MTP hidden
         if (i == 0) QB_TRY(mtp_forward(ctx, b, b->tok_buf, b->hid, b->map_prevh, rs, false));
         else QB_TRY(mtp_forward(ctx, b, b->tok_buf, b->mtp_h, nullptr, rs, false));
-        QB_CUDA(qb_launch_pdl(ctx->stream, store_draft_kernel, dim3((ns + 127) / 128), dim3(128), (size_t)(0), b->am_val, b->am_idx, ns, k, i, b->drafts));
+        QB_CUDA(qb_launch_pdl(ctx->stream, store_draft_kernel, dim3((ns + 3) / 4), dim3(128), (size_t)(0), b->am_val, b->am_idx, ns, k, i, b->drafts));
         QB_LAUNCHED(ctx, "store_draft_kernel");
     }
     return QB_OK;
