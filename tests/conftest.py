@@ -62,3 +62,13 @@ def std_mt19937_uniform(rs, n, a, b):
 
 def tiny_ocfg(orc, qb):
     return orc.ModelConfig(**qb.configs.tiny().as_dict())
+
+
+@pytest.fixture(scope="session")
+def ref_attn():
+    """The reference's native decode attention (oracle/_ref/libqw3ref_attn.so, `make -C oracle ref-attn`), or None."""
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "_ref", "libqw3ref_attn.so")
+    if not os.path.exists(path):
+        return None
+    return ctypes.CDLL(path)
