@@ -56,3 +56,10 @@ def test_paged_attention_matches_reference_native_decode_kernel(qb, orc, ctx, re
     want = ref_out.download() * (1.0 / (1.0 + np.exp(-gate)))
     # fp16 operands on our side (q, p), fp32 q on the reference's: the bound of the oracle comparison
     assert np.allclose(got, want, rtol=2e-3, atol=1e-3), float(np.abs(got - want).max())
+    # and the CPU oracle's restatement of the same math (fp32 q and p, fp16 K/V) is pinned on the reference kernel
+    o_qkv = d_qkv.download()
+    okc, ovc = d_kc.download(), d_vc.download()
+    row_seq = np.zeros(R, np.int32)
+    row_pos = (base + np.arange(R)).astype(np.int32)
+    ours_cpu = orc.attention_paged_gated(o_qkv, n_heads, n_kv, hd, row_seq, row_pos, pt, page, okc, ovc)
+    assert np.allclose(ours_cpu, want, rtol=1e-4, atol=2e-5), float(np.abs(ours_cpu - want).max())
