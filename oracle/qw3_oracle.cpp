@@ -9,9 +9,10 @@
 // accumulation orders (mmvq, mmq) are pinned against the reference's own CUDA kernels compiled
 // from its sources (oracle/_ref, GPU tests) and against the procedures and closed forms of the
 // reference's tests (tests/mmq_parity.cu, tests/mixed_linear_parity.cu).  The gated-delta rule is
-// pinned against the reference's gated_delta_net.cu in the same way.  Attention, the MTP head
-// wiring and acceptance have no golden vectors in the reference ("parity unpinned" at unit level);
-// they follow the cited source lines.
+// pinned against the reference's gated_delta_net.cu in the same way, and the attention math against
+// the reference's native decode attention (fattn_vec_decode.cu, its own library under oracle/_ref).
+// The MTP head wiring and acceptance have no golden vectors in the reference ("parity unpinned" at
+// unit level); they follow the cited source lines.
 //
 // Every function cites the reference lines it follows (paths inside the kvmem-qw3 tree).
 
