@@ -11,6 +11,9 @@
 // reference's tests (tests/mmq_parity.cu, tests/mixed_linear_parity.cu).  The gated-delta rule is
 // pinned against the reference's gated_delta_net.cu in the same way, and the attention math against
 // the reference's native decode attention (fattn_vec_decode.cu, its own library under oracle/_ref).
+// RMSNorm, per-head norm + RoPE + KV append, gated attention, the whole recurrent layer core with its
+// checkpoints, argmax and embedding rows are pinned on the reference's CUDA DeviceBackend driven through
+// its public interface (kernels_cuda.cu built into oracle/_ref/libqw3ref_backend.so).
 // The MTP head wiring and acceptance have no golden vectors in the reference ("parity unpinned" at
 // unit level); they follow the cited source lines.
 //

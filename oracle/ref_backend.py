@@ -17,6 +17,9 @@ SIG = {
     "rb_destroy": (None, [vp]),
     "rb_name": (C.c_char_p, [vp]),
     "rb_sync": (i32, [vp]),
+    "rb_begin_capture": (i32, [vp]),
+    "rb_end_capture": (i32, [vp]),
+    "rb_replay_graph": (i32, [vp]),
     "rb_tensor": (vp, [vp, i32, u64]),
     "rb_tensor_free": (None, [vp]),
     "rb_tensor_elem_size": (u32, [vp]),
@@ -110,6 +113,26 @@ class RefBackend:
 
     def sync(self):
         self._check(self.L.rb_sync(self.h))
+
+    def time_us(self, op, reps=20, replays=10):
+        """Device time of one `op()` in microseconds: `reps` calls captured into the backend's CUDA graph, the graph
+        replayed `replays` times, wall clock around replay + synchronize (inputs stay where they are: warm L2)."""
+        import time
+        op()                                   # workspaces are allocated outside the capture
+        self.sync()
+        self._check(self.L.rb_begin_capture(self.h))
+        for _ in range(reps):
+            op()
+        self._check(self.L.rb_end_capture(self.h))
+        self._check(self.L.rb_replay_graph(self.h))
+        self.sync()
+        best = float("inf")
+        for _ in range(replays):
+            t0 = time.perf_counter()
+            self._check(self.L.rb_replay_graph(self.h))
+            self.sync()
+            best = min(best, time.perf_counter() - t0)
+        return best / reps * 1e6
 
     def release(self):
         self.sync()

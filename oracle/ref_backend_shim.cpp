@@ -41,6 +41,12 @@ void rb_destroy(void *b) { if (b) { B(b).end(); delete static_cast<DeviceBackend
 const char *rb_name(void *b) { return B(b).name(); }
 int rb_sync(void *b) { return st(B(b).synchronize()); }
 
+// CUDA-graph hooks of the backend (include/qw3/device_backend.hpp:96-116): the timing tests capture a run of
+// operator calls once and replay it, as the reference's decode loop does.
+int rb_begin_capture(void *b) { return B(b).begin_capture() ? 0 : fail("begin_capture refused"); }
+int rb_end_capture(void *b) { return st(B(b).end_capture()); }
+int rb_replay_graph(void *b) { return st(B(b).replay_graph()); }
+
 // kind: 0 = f32, 1 = f16, 2 = i32
 void *rb_tensor(void *b, int kind, uint64_t count) {
     try {
