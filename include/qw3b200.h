@@ -268,6 +268,11 @@ int qb_read_step_output(qb_ctx *ctx, qb_batch *b, int32_t *n_out_host, int32_t *
 int qb_batch_stats(qb_ctx *ctx, qb_batch *b, int64_t *out4);
 /* Position (committed tokens) of a sequence; reads a device counter (syncs). */
 int qb_seq_position(qb_ctx *ctx, qb_batch *b, uint32_t seq, int32_t *pos);
+/* Slot recycling of the continuous-batching loop (request retirement and admission,
+ * src/qwen_native_backend.cpp:6711-6866; page release of GlobalKvPagePool :1155-1265): sequence `seq` goes back to
+ * position 0 with zero DeltaNet / conv state, ready for qb_prefill of the next request.  The slot keeps its K/V pages.
+ * The other sequences of the batch are untouched. */
+int qb_seq_reset(qb_ctx *ctx, qb_batch *b, uint32_t seq);
 /* Test aids: logits of the last verify/greedy/prefill rows (float [rows][vocab]) and hidden rows. */
 int qb_debug_last_logits(qb_ctx *ctx, qb_batch *b, float *host_out, uint32_t max_rows, uint32_t *rows_out);
 /* Drafts of the last qb_mtp_draft / qb_mtp_force_drafts: int32 [n_seqs][k] (test aid, syncs). */

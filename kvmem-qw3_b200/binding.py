@@ -85,6 +85,7 @@ SIGNATURES = {
     "qb_read_step_output": (i32, [vp, vp, vp, vp]),
     "qb_batch_stats": (i32, [vp, vp, vp]),
     "qb_seq_position": (i32, [vp, vp, u32, C.POINTER(C.c_int32)]),
+    "qb_seq_reset": (i32, [vp, vp, u32]),
     "qb_debug_last_logits": (i32, [vp, vp, vp, u32, C.POINTER(u32)]),
     "qb_debug_last_drafts": (i32, [vp, vp, vp]),
     "qb_prof_enable": (i32, [vp, i32]),
@@ -388,7 +389,7 @@ class Batch:
     """Executor state of n_seqs requests (the QwenExecutor-side state of the reference)."""
 
     def __init__(self, model, n_seqs, max_ctx, k, page_size=16, page_order=0):
-        self.ctx, self.model, self.n_seqs, self.k = model.ctx, model, n_seqs, k
+        self.ctx, self.model, self.n_seqs, self.k, self.max_ctx = model.ctx, model, n_seqs, k, max_ctx
         h = vp()
         check(lib().qb_batch_create(self.ctx.h, model.h, n_seqs, max_ctx, k, page_size, page_order, C.byref(h)))
         self.h = h
@@ -436,6 +437,10 @@ class Batch:
         out = np.zeros(4, np.int64)
         check(lib().qb_batch_stats(self.ctx.h, self.h, _np_ptr(out)))
         return dict(steps=int(out[0]), drafted=int(out[1]), accepted=int(out[2]), emitted=int(out[3]))
+
+    def reset(self, seq):
+        """Retire the request in slot `seq`: position 0, zero recurrent state; prefill admits the next one."""
+        check(lib().qb_seq_reset(self.ctx.h, self.h, seq))
 
     def position(self, seq):
         p = C.c_int32()

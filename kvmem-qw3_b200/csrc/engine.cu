@@ -828,6 +828,27 @@ extern "C" int qb_seq_position(qb_ctx *ctx, qb_batch *b, uint32_t seq, int32_t *
     return QB_OK;
 }
 
+// Slot recycling of the continuous-batching loop: the retired request's recurrent state, conv windows, position and
+// previous hidden row go back to their initial values; the slot keeps its K/V pages (entries beyond the position are
+// never read, so they need no clearing).
+extern "C" int qb_seq_reset(qb_ctx *ctx, qb_batch *b, uint32_t seq) {
+    QB_REQUIRE(ctx && b && seq < b->n_seqs, "qb_seq_reset: bad arguments");
+    QB_CUDA(cudaSetDevice(ctx->device));
+    const qb_model_config &c = b->m->cfg;
+    const uint32_t K1 = b->k + 1;
+    const size_t ssz = (size_t)K1 * c.ssm_num_v_heads * c.ssm_head_dim * c.ssm_head_dim, csz = (size_t)K1 * b->m->qkv_dim() * 3;
+    for (uint32_t il = 0; il < c.n_layers; ++il) {
+        if (!b->state[il]) continue;
+        QB_CUDA(cudaMemsetAsync(b->state[il] + seq * ssz, 0, ssz * sizeof(float), ctx->stream));
+        QB_CUDA(cudaMemsetAsync(b->conv[il] + seq * csz, 0, csz * sizeof(float), ctx->stream));
+        QB_CUDA(cudaMemsetAsync(b->conv_alt[il] + seq * csz, 0, csz * sizeof(float), ctx->stream));
+    }
+    for (int32_t *p : {b->pos, b->sel, b->cur, b->prefix_pos}) QB_CUDA(cudaMemsetAsync(p + seq, 0, sizeof(int32_t), ctx->stream));
+    QB_CUDA(cudaMemsetAsync(b->hid + (size_t)(b->rows_cap + seq) * c.n_embd, 0, (size_t)c.n_embd * sizeof(float), ctx->stream));
+    b->host_pos[seq] = 0;
+    return QB_OK;
+}
+
 extern "C" int qb_debug_last_logits(qb_ctx *ctx, qb_batch *b, float *host_out, uint32_t max_rows, uint32_t *rows_out) {
     const uint32_t r = std::min(max_rows, b->last_logit_rows);
     if (r) QB_CUDA(cudaMemcpyAsync(host_out, b->logits, (size_t)r * b->m->cfg.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));

@@ -1,0 +1,109 @@
+"""Continuous-batching loop around the MTP step: request queue, admission into free sequence slots, retirement.
+
+The host side of the reference's continuous_batch_worker_loop (src/qwen_native_backend.cpp:6711-6866: pending queue,
+`max_active` slots, admission when a slot is free, retirement at EOS or at the token budget) over the fixed-slot batch of
+this library: a batch has `n_slots` sequences; a retired request's slot is recycled with Batch.reset (position 0, zero
+recurrent state) and the next pending request is prefilled into it while the others keep decoding.  Every step runs all
+slots (an idle slot decodes from its reset state and is reset again before it runs out of context); because a row's
+result never depends on which other rows share a launch, a request's tokens are the ones it would get alone.
+
+`engine` is anything with n_seqs, k, max_ctx, prefill(seq, tokens), mtp_step() or greedy_step(), read_output(), reset(seq):
+binding.Batch on the GPU, a fake in the CPU tests.
+"""
+import collections
+
+
+class Request:
+    def __init__(self, rid, prompt, max_new_tokens, arrival_step=0, eos=None):
+        self.rid, self.prompt, self.max_new_tokens = rid, list(prompt), int(max_new_tokens)
+        self.arrival_step, self.eos = int(arrival_step), eos
+        self.tokens = []            # emitted tokens (the first one comes from the prefill's last row)
+        self.admitted_step = self.finished_step = None
+        self.slot = None
+
+    def done(self):
+        return len(self.tokens) >= self.max_new_tokens or (self.eos is not None and self.eos in self.tokens)
+
+    def _trim(self):
+        if self.eos is not None and self.eos in self.tokens:
+            self.tokens = self.tokens[:self.tokens.index(self.eos) + 1]
+        self.tokens = self.tokens[:self.max_new_tokens]
+
+
+class SlotScheduler:
+    """FIFO admission into a fixed number of slots; free slots are reused last-freed-first (the LIFO order of the
+    reference's page pool, src/qwen_native_backend.cpp:1155-1265)."""
+
+    def __init__(self, n_slots):
+        self.free = list(range(n_slots - 1, -1, -1))     # pop() hands out slot 0 first
+        self.pending = collections.deque()
+        self.active = {}                                 # slot -> Request
+
+    def submit(self, req):
+        self.pending.append(req)
+
+    def admissible(self, step):
+        """Requests that can be admitted now: arrived, in arrival order, one per free slot."""
+        out = []
+        while self.pending and self.free and self.pending[0].arrival_step <= step:
+            req = self.pending.popleft()
+            req.slot = self.free.pop()
+            req.admitted_step = step
+            self.active[req.slot] = req
+            out.append(req)
+        return out
+
+    def retire(self, slot, step):
+        req = self.active.pop(slot)
+        req.finished_step = step
+        self.free.append(slot)
+        return req
+
+    def idle(self):
+        return not self.pending and not self.active
+
+
+def run(engine, requests, speculative=True, max_steps=1 << 30):
+    """Serve `requests` (a list of Request) to completion; returns them in completion order.
+    One loop iteration = admissions (a prefill each) + one decode step of the whole batch."""
+    sched = SlotScheduler(engine.n_seqs)
+    for r in sorted(requests, key=lambda r: (r.arrival_step, r.rid)):
+        sched.submit(r)
+    per_step = engine.k + 1 if speculative else 1
+    idle_pos = [0] * engine.n_seqs                       # upper bound of the position of slots that hold no request
+    finished, step = [], 0
+    while not sched.idle() and step < max_steps:
+        for req in sched.admissible(step):
+            if len(req.prompt) + req.max_new_tokens + per_step > engine.max_ctx:
+                raise ValueError("request %r does not fit max_ctx %d" % (req.rid, engine.max_ctx))
+            engine.reset(req.slot)
+            engine.prefill(req.slot, req.prompt)
+            req.tokens.extend(engine.read_output()[req.slot])      # the prefill's last row gives the first token
+            if req.done():
+                req._trim()
+                finished.append(sched.retire(req.slot, step))
+                idle_pos[req.slot] = len(req.prompt) + per_step
+        if not sched.active:                             # nothing to decode yet: wait for the next arrival
+            step += 1
+            continue
+        for s in range(engine.n_seqs):                   # idle slots must not run out of context
+            if s not in sched.active and idle_pos[s] + 2 * per_step >= engine.max_ctx:
+                engine.reset(s)
+                idle_pos[s] = 0
+        if speculative:
+            engine.mtp_step()
+        else:
+            engine.greedy_step()
+        out = engine.read_output()
+        step += 1
+        for s in range(engine.n_seqs):
+            req = sched.active.get(s)
+            if req is None:
+                idle_pos[s] += per_step
+                continue
+            req.tokens.extend(out[s])
+            if req.done():
+                req._trim()
+                finished.append(sched.retire(s, step))
+                idle_pos[s] = len(req.prompt) + len(req.tokens) + per_step
+    return finished
