@@ -261,6 +261,27 @@ int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b);
 /* draft + verify + accept_commit. */
 int qb_mtp_step(qb_ctx *ctx, qb_batch *b);
 
+/* Sampling-mode requests (temp > 0).  The reference copies the verifier's logits to the host and runs
+ * sampling_distribution (src/qwen_native_backend.cpp:282-370: softmax(logits / temp), then top-k, min-p and nucleus
+ * truncation, renormalised over the kept set) and speculative_accept_pointmass (:399-467: a greedy draft is accepted with
+ * probability p[draft]; a rejection draws from p with the draft removed and stops; a fully accepted chain draws a bonus
+ * token from the last row) there.  qb_sample_rows does the same per logits row on the device:
+ *   draft_dev[row] >= 0: accepted_dev[row] = (u_acc_dev[row] < p[draft]); token = draft if accepted, else the residual draw
+ *   with u_res_dev[row]; draft_dev == NULL or draft_dev[row] < 0: token = a draw from p with u_res_dev[row].
+ * Draws walk the nonzero entries in index order (sample_from, :373-383, std::discrete_distribution).  top_k <= 0, top_p
+ * outside (0,1) and min_p <= 0 switch the respective truncation off.  Ties at the truncation boundary are kept lowest index
+ * first.  Token penalties (:262-280) are not applied.  p_draft_dev / accepted_dev may be NULL. */
+int qb_sample_rows(qb_ctx *ctx, const float *logits_dev, uint32_t rows, uint32_t V, uint32_t stride, const int32_t *draft_dev,
+                   const double *u_acc_dev, const double *u_res_dev, float temp, float top_p, int32_t top_k, float min_p,
+                   int32_t *token_dev, int32_t *accepted_dev, float *p_draft_dev);
+/* The same decision for the rows of the last qb_mtp_verify, left where qb_mtp_accept_commit reads the row tokens: call
+ * between the two.  u_host: double [n_seqs][k+1], the caller's uniform draws in the order the reference consumes its
+ * generator: row i accepts with u[i], a rejection at row i draws with u[i+1], the bonus draw is u[k]; a step uses the
+ * first accepted + 1 of them. */
+int qb_mtp_sample_rows(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host);
+/* draft + verify + sample_rows + accept_commit. */
+int qb_mtp_step_sampled(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host);
+
 /* Host view of what the last step emitted: n_out[seq] tokens in tokens[seq*(k+1) ...]. Performs
  * the step's single device->host copy and a stream sync. */
 int qb_read_step_output(qb_ctx *ctx, qb_batch *b, int32_t *n_out_host, int32_t *tokens_host);

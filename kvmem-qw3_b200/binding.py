@@ -86,6 +86,9 @@ SIGNATURES = {
     "qb_batch_stats": (i32, [vp, vp, vp]),
     "qb_seq_position": (i32, [vp, vp, u32, C.POINTER(C.c_int32)]),
     "qb_seq_reset": (i32, [vp, vp, u32]),
+    "qb_sample_rows": (i32, [vp, vp, u32, u32, u32, vp, vp, vp, C.c_float, C.c_float, i32, C.c_float, vp, vp, vp]),
+    "qb_mtp_sample_rows": (i32, [vp, vp, C.c_float, C.c_float, i32, C.c_float, vp]),
+    "qb_mtp_step_sampled": (i32, [vp, vp, C.c_float, C.c_float, i32, C.c_float, vp]),
     "qb_debug_last_logits": (i32, [vp, vp, vp, u32, C.POINTER(u32)]),
     "qb_debug_last_drafts": (i32, [vp, vp, vp]),
     "qb_prof_enable": (i32, [vp, i32]),
@@ -427,6 +430,15 @@ class Batch:
 
     def mtp_step(self):
         check(lib().qb_mtp_step(self.ctx.h, self.h))
+
+    def mtp_step_sampled(self, u, temp, top_p=1.0, top_k=0, min_p=0.0):
+        """u: float64 [n_seqs][k+1] uniform draws (see qb_mtp_sample_rows)."""
+        u = np.ascontiguousarray(u, np.float64).reshape(self.n_seqs, self.k + 1)
+        check(lib().qb_mtp_step_sampled(self.ctx.h, self.h, temp, top_p, top_k, min_p, _np_ptr(u)))
+
+    def mtp_sample_rows(self, u, temp, top_p=1.0, top_k=0, min_p=0.0):
+        u = np.ascontiguousarray(u, np.float64).reshape(self.n_seqs, self.k + 1)
+        check(lib().qb_mtp_sample_rows(self.ctx.h, self.h, temp, top_p, top_k, min_p, _np_ptr(u)))
 
     def read_output(self):
         """Returns a list (per sequence) of the tokens the last step emitted."""

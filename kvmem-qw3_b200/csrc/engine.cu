@@ -187,6 +187,7 @@ struct qb_batch {
     std::vector<int32_t> host_pos;         // upper bound of pos per sequence
     uint32_t last_logit_rows = 0;
     int gemm_impl = 0;
+    double *samp_u = nullptr;              // [2][logit_rows]: acceptance draws, then residual draws (sampling mode)
 };
 
 static int alloc_qbuf(QBuf &b, uint32_t rows, uint32_t K) {
@@ -323,7 +324,7 @@ extern "C" void qb_batch_destroy(qb_ctx *ctx, qb_batch *b) {
     for (auto p : b->conv_alt) if (p) cudaFree(p);
     void *ptrs[] = {b->page_table, b->ctl, b->stats, b->hid, b->mtp_h, b->embd, b->act, b->parts,
                     b->logits, b->am_val, b->am_idx, b->att_acc, b->att_ml, b->xq_h.q, b->xq_h.d, b->xq_attn.q,
-                    b->xq_attn.d, b->xq_dn.q, b->xq_dn.d, b->xq_ffn.q, b->xq_ffn.d, b->xq_cat.q, b->xq_cat.d};
+                    b->xq_attn.d, b->xq_dn.q, b->xq_dn.d, b->xq_ffn.q, b->xq_ffn.d, b->xq_cat.q, b->xq_cat.d, b->samp_u};
     for (void *p : ptrs) if (p) cudaFree(p);
     if (b->out_rec_host) cudaFreeHost(b->out_rec_host);
     delete b;
@@ -795,6 +796,37 @@ extern "C" int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b) {
     QB_TRY(mtp_forward(ctx, b, b->prefix_tok, b->hid, b->map_prefix, rs, true));
     for (auto &p : b->host_pos) p += (int32_t)(k + 1);   // upper bound until the host reads the step record
     return QB_OK;
+}
+
+// Sampling-mode acceptance (speculative_accept_pointmass, src/qwen_native_backend.cpp:399-467): every verifier row takes
+// its decision on the device from the logits the verify forward left, and hands the commit kernel the decided token in
+// place of the row's argmax -- the draft itself when accepted, the residual draw when rejected, the bonus draw on the last
+// row -- so the longest-matching-prefix commit that follows is the reference's accept loop.  u_host: double [n_seqs][k+1],
+// the caller's uniform draws in the order its generator is consumed: row i accepts with u[i]; a rejection at row i draws
+// its residual with u[i+1]; the bonus draw is u[k].  A step consumes accepted + 1 of them.
+extern "C" int qb_mtp_sample_rows(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host) {
+    QB_REQUIRE(ctx && b && u_host && b->k > 0, "qb_mtp_sample_rows: needs draws and a batch with draft depth > 0");
+    QB_CUDA(cudaSetDevice(ctx->device));
+    const uint32_t ns = b->n_seqs, k = b->k, K1 = k + 1, rows = ns * K1;
+    if (!b->samp_u) QB_CUDA(cudaMalloc(&b->samp_u, 2 * (size_t)rows * sizeof(double)));
+    std::vector<double> u(2 * (size_t)rows, 0.0);
+    for (uint32_t s = 0; s < ns; ++s)
+        for (uint32_t i = 0; i < K1; ++i) {
+            u[(size_t)s * K1 + i] = u_host[(size_t)s * K1 + i];                                  // acceptance draw of row i
+            u[(size_t)rows + s * K1 + i] = u_host[(size_t)s * K1 + (i < k ? i + 1 : k)];          // residual / bonus draw
+        }
+    QB_CUDA(cudaMemcpyAsync(b->samp_u, u.data(), u.size() * sizeof(double), cudaMemcpyHostToDevice, ctx->stream));
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));       // the vector goes out of scope
+    const qb_model_config &c = b->m->cfg;
+    return qb_launch_sample_rows(ctx, b->logits, rows, c.vocab_size, c.vocab_size, b->drafts, K1, b->samp_u, b->samp_u + rows, temp, top_p,
+                                 top_k, min_p, nullptr, nullptr, nullptr, b->am_val, b->am_idx, QB_ARGMAX_BLOCKS);
+}
+
+extern "C" int qb_mtp_step_sampled(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host) {
+    QB_TRY(qb_mtp_draft(ctx, b));
+    QB_TRY(qb_mtp_verify(ctx, b));
+    QB_TRY(qb_mtp_sample_rows(ctx, b, temp, top_p, top_k, min_p, u_host));
+    return qb_mtp_accept_commit(ctx, b);
 }
 
 extern "C" int qb_mtp_step(qb_ctx *ctx, qb_batch *b) {

@@ -222,6 +222,18 @@ def argmax_rows(x):
     return out
 
 
+def sample_rows(logits, draft, u_acc, u_res, temp, top_p=1.0, top_k=0, min_p=0.0):
+    """Per row: (token, accepted, p[draft]) of the sampling-mode acceptance; draft entries < 0 mean a plain draw."""
+    x = _f32(logits)
+    rows, V = x.shape
+    d = np.ascontiguousarray(draft, np.int32)
+    ua, ur = np.ascontiguousarray(u_acc, np.float64), np.ascontiguousarray(u_res, np.float64)
+    tok, acc, pd = np.empty(rows, np.int32), np.empty(rows, np.int32), np.empty(rows, np.float32)
+    lib().orc_sample_rows(_p(x), C.c_uint32(rows), C.c_uint32(V), C.c_uint32(V), _p(d), _p(ua), _p(ur), C.c_float(temp),
+                          C.c_float(top_p), C.c_int32(top_k), C.c_float(min_p), _p(tok), _p(acc), _p(pd))
+    return tok, acc, pd
+
+
 def synth_prompt(seed, vocab, n):
     out = np.empty(n, np.int32)
     lib().orc_synth_prompt(C.c_uint64(seed), C.c_uint32(vocab), C.c_uint32(n), _p(out))

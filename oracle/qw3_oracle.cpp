@@ -783,6 +783,94 @@ void orc_deltanet_rows(const float *proj, uint32_t T, uint32_t proj_stride, cons
     if (!write_all) { memcpy(state, S.data(), ssz * 4); memcpy(conv, Cv.data(), csz * 4); }
 }
 
+
+// ---- sampling-mode acceptance ---------------------------------------------------------------
+// sampling_distribution (src/qwen_native_backend.cpp:282-370): softmax(logits / temp) with the denominator summed in
+// double, then top-k, min-p and nucleus truncation, each keeping a prefix of the descending order, renormalised over the
+// kept set.  The reference isolates a growing window with nth_element; sorting the whole row gives the same kept set.
+// Equal logits are ordered lowest index first here (the reference leaves their order to nth_element / sort).
+static void sampling_distribution(const float *logits, int n, float temp, float top_p, int top_k, float min_p,
+                                  std::vector<float> &out) {
+    out.assign((size_t)n, 0.0f);
+    const float inv_t = 1.0f / (temp > 0.0f ? temp : 1.0f);
+    float maxv = logits[0];
+    for (int i = 1; i < n; ++i) if (logits[i] > maxv) maxv = logits[i];
+    double sum = 0.0;
+    for (int i = 0; i < n; ++i) sum += std::exp((logits[i] - maxv) * inv_t);
+    const float norm = (float)(1.0 / (sum > 0.0 ? sum : 1.0));
+    auto prob_of = [&](int i) -> float { return std::exp((logits[i] - maxv) * inv_t) * norm; };
+    const bool need_sort = (top_k > 0 && top_k < n) || (top_p < 1.0f && top_p > 0.0f) || (min_p > 0.0f);
+    if (!need_sort) { for (int i = 0; i < n; ++i) out[i] = prob_of(i); return; }
+    std::vector<int> idx((size_t)n);
+    for (int i = 0; i < n; ++i) idx[i] = i;
+    std::stable_sort(idx.begin(), idx.end(), [&](int a, int b) { return logits[a] > logits[b]; });
+    size_t keep = (size_t)n;
+    if (top_k > 0 && (size_t)top_k < keep) keep = (size_t)top_k;
+    if (min_p > 0.0f && keep > 0) {
+        const float cutoff = prob_of(idx[0]) * min_p;
+        size_t k = 0;
+        while (k < keep && prob_of(idx[k]) >= cutoff) ++k;
+        keep = k;
+    }
+    if (top_p < 1.0f && top_p > 0.0f) {
+        double cum = 0.0;
+        size_t k = keep;
+        for (size_t i = 0; i < keep; ++i) { cum += prob_of(idx[i]); if (cum >= top_p) { k = i + 1; break; } }
+        keep = k;
+    }
+    double kept_sum = 0.0;
+    for (size_t i = 0; i < keep; ++i) kept_sum += prob_of(idx[i]);
+    if (kept_sum <= 0.0) { out[idx[0]] = 1.0f; return; }
+    const float kn = (float)(1.0 / kept_sum);
+    for (size_t i = 0; i < keep; ++i) out[idx[i]] = prob_of(idx[i]) * kn;
+}
+
+// sample_from (:373-383) with the draw given: std::discrete_distribution over the nonzero entries in index order, i.e.
+// weights divided by their sum, partial sums, the last forced to 1, first entry whose partial sum is >= u (libstdc++).
+static int32_t sample_from_u(const std::vector<float> &probs, double u) {
+    std::vector<double> w;
+    std::vector<int> idx;
+    for (int i = 0; i < (int)probs.size(); ++i) if (probs[i] > 0.0f) { w.push_back(probs[i]); idx.push_back(i); }
+    if (w.empty()) return -1;
+    if (w.size() < 2) return idx[0];
+    double s = 0.0;
+    for (double v : w) s += v;
+    double c = 0.0;
+    for (size_t j = 0; j < w.size(); ++j) {
+        c += w[j] / s;
+        if ((j + 1 == w.size() ? 1.0 : c) >= u) return idx[j];
+    }
+    return idx.back();
+}
+
+// One row of speculative_accept_pointmass (:399-467) without penalties: draft >= 0: accept with probability p[draft], on
+// rejection draw from p with the draft removed (the draft itself if nothing is left); draft < 0: a plain draw from p.
+void orc_sample_rows(const float *logits, uint32_t rows, uint32_t V, uint32_t stride, const int32_t *draft, const double *u_acc,
+                     const double *u_res, float temp, float top_p, int32_t top_k, float min_p, int32_t *token,
+                     int32_t *accepted, float *p_draft) {
+#pragma omp parallel for schedule(dynamic)
+    for (int64_t r = 0; r < (int64_t)rows; ++r) {
+        std::vector<float> p;
+        sampling_distribution(logits + (size_t)r * stride, (int)V, temp, top_p, top_k, min_p, p);
+        const int d = draft ? draft[r] : -1;
+        int acc = 0;
+        float pd = 0.0f;
+        int32_t tok = d;
+        if (d >= 0 && (uint32_t)d < V) {
+            pd = p[d];
+            acc = u_acc[r] < (double)pd ? 1 : 0;
+        }
+        if (!acc) {
+            if (d >= 0 && (uint32_t)d < V) p[d] = 0.0f;
+            const int32_t s = sample_from_u(p, u_res[r]);
+            tok = s >= 0 ? s : d;
+        }
+        token[r] = tok;
+        if (accepted) accepted[r] = acc;
+        if (p_draft) p_draft[r] = pd;
+    }
+}
+
 void orc_argmax_rows(const float *x, uint32_t M, uint32_t n, uint32_t stride, int32_t *out) {
     for (uint32_t m = 0; m < M; ++m) out[m] = argmax(x + (size_t)m * stride, n);
 }

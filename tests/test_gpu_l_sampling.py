@@ -1,0 +1,126 @@
+"""Sampling-mode speculative acceptance on the device (qb_sample_rows, qb_mtp_sample_rows) against the oracle's restatement
+of sampling_distribution + speculative_accept_pointmass (src/qwen_native_backend.cpp:282-467), same logits, same draws."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+PARAMS = [(1.0, 1.0, 0, 0.0), (0.7, 0.9, 0, 0.0), (0.5, 1.0, 5, 0.0), (1.3, 0.8, 50, 0.05), (0.2, 0.0, 0, 0.3), (1.0, 0.5, 1, 0.0),
+          (0.05, 0.95, 40, 0.0), (2.0, 0.999, 0, 0.0)]
+
+
+def gpu_sample(qb, ctx, x, draft, ua, ur, temp, top_p, top_k, min_p):
+    rows, V = x.shape
+    tok, acc, pd = ctx.empty((rows,), np.int32), ctx.empty((rows,), np.int32), ctx.empty((rows,), np.float32)
+    d = ctx.array(np.ascontiguousarray(draft, np.int32)) if draft is not None else None
+    a = ctx.array(np.ascontiguousarray(ua, np.float64)) if ua is not None else None
+    qb.binding.check(qb.lib().qb_sample_rows(ctx.h, ctx.array(x).ptr, rows, V, V, d.ptr if d else None, a.ptr if a else None,
+                                             ctx.array(np.ascontiguousarray(ur, np.float64)).ptr, temp, top_p, top_k, min_p,
+                                             tok.ptr, acc.ptr, pd.ptr))
+    ctx.sync()
+    return tok.download(), acc.download(), pd.download()
+
+
+@pytest.mark.parametrize("temp,top_p,top_k,min_p", PARAMS)
+@pytest.mark.parametrize("V", [3000, 151936])
+def test_sample_rows_vs_oracle(qb, orc, ctx, V, temp, top_p, top_k, min_p):
+    rng = np.random.default_rng(100 + V % 97 + int(temp * 10))
+    rows = 8
+    x = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    x[3, 100] = x[3, V - 5] = x[3].max() + 1                      # a tie at the top: lowest index first
+    x[5, :] = np.round(x[5, :] * 2) / 2                           # many ties everywhere
+    draft = np.where(np.arange(rows) % 3 == 2, -1, x.argmax(1)).astype(np.int32)
+    draft[4] = 7                                                  # a draft the target gives almost no mass
+    ua, ur = rng.random(rows), rng.random(rows)
+    ur[0], ur[1] = 0.0, 1.0 - 1e-12                               # ends of the inverse CDF
+    want = orc.sample_rows(x, draft, ua, ur, temp, top_p, top_k, min_p)
+    got = gpu_sample(qb, ctx, x, draft, ua, ur, temp, top_p, top_k, min_p)
+    assert np.allclose(got[2], want[2], rtol=2e-5, atol=1e-9), (got[2], want[2])
+    assert np.array_equal(got[1], want[1]), (got[1], want[1])
+    assert np.array_equal(got[0], want[0]), (got[0], want[0])
+
+
+def test_plain_sampling_rows_follow_the_distribution(qb, orc, ctx):
+    """No drafts: 4000 draws of one 50-token row reproduce its truncated distribution (chi-square-sized bound)."""
+    rng = np.random.default_rng(5)
+    V, n = 50, 4000
+    row = (rng.standard_normal(V) * 2).astype(np.float32)
+    x = np.tile(row, (n, 1))
+    ur = rng.random(n)
+    tok, _, _ = gpu_sample(qb, ctx, x, None, None, ur, 0.8, 0.9, 0, 0.0)
+    want, _, _ = orc.sample_rows(x[:1], np.array([-1], np.int32), np.zeros(1), ur[:1], 0.8, 0.9, 0, 0.0)
+    assert tok[0] == want[0]
+    e = np.exp((row - row.max()) / 0.8); p = e / e.sum()
+    order = np.argsort(-p); keep = order[:np.nonzero(np.cumsum(p[order]) >= 0.9)[0][0] + 1]
+    q = np.zeros(V); q[keep] = p[keep] / p[keep].sum()
+    freq = np.bincount(tok, minlength=V) / n
+    assert set(np.nonzero(freq)[0]) <= set(keep)
+    assert np.abs(freq - q).max() < 4 * np.sqrt(0.25 / n)
+
+
+@pytest.fixture(scope="module")
+def model(qb, ctx):
+    m = qb.Model(ctx, qb.configs.tiny(), qb.configs.MODEL_SEED)
+    yield m
+    m.close()
+
+
+def test_top_k_one_is_greedy(qb, orc, ctx, model):
+    """top_k = 1 makes the target a point mass at the argmax: whatever the draws, the sampled speculative stream is the greedy one."""
+    V = model.cfg.vocab_size
+    prompt = orc.synth_prompt(77, V, 48)
+    g = qb.Batch(model, 1, 256, 0)
+    g.prefill(0, prompt)
+    want = list(g.read_output()[0])
+    while len(want) < 24:
+        g.greedy_step()
+        want += g.read_output()[0]
+    g.close()
+    b = qb.Batch(model, 1, 256, 3)
+    b.prefill(0, prompt)
+    got = list(b.read_output()[0])
+    rng = np.random.default_rng(1)
+    while len(got) < 24:
+        b.mtp_step_sampled(rng.random((1, 4)), temp=0.9, top_k=1)
+        got += b.read_output()[0]
+    b.close()
+    assert got[:24] == want[:24]
+
+
+@pytest.mark.parametrize("temp,top_p,top_k", [(1.0, 1.0, 0), (0.6, 0.9, 20)])
+def test_sampled_step_matches_the_reference_accept_loop(qb, orc, ctx, model, temp, top_p, top_k):
+    """Each step: the verifier's logits and the drafts go through the oracle's accept loop with the same draws (row i accepts
+    with u[i], a rejection at row i draws with u[i+1], the bonus draw is u[k]); the step must emit exactly those tokens."""
+    V, k, ns = model.cfg.vocab_size, 3, 2
+    b = qb.Batch(model, ns, 256, k)
+    for s in range(ns):
+        b.prefill(s, orc.synth_prompt(80 + s, V, 30 + 7 * s))
+    rng = np.random.default_rng(3)
+    n_acc = 0
+    for step in range(12):
+        u = rng.random((ns, k + 1))
+        if step % 3 == 0:
+            u[:, 0] = 0.0                                        # force some acceptances of the first draft
+        b.mtp_draft()
+        b.mtp_verify()
+        logits = b.last_logits(ns * (k + 1)).reshape(ns, k + 1, V).copy()
+        drafts = b.last_drafts()
+        b.mtp_sample_rows(u, temp, top_p, top_k)
+        b.mtp_accept_commit()
+        out = b.read_output()
+        for s in range(ns):
+            want = []
+            for i in range(k + 1):
+                d = int(drafts[s, i]) if i < k else -1
+                tok, acc, _ = orc.sample_rows(logits[s, i:i + 1], np.array([d], np.int32), u[s, i:i + 1], u[s, min(i + 1, k):min(i + 1, k) + 1],
+                                              temp, top_p, top_k, 0.0)
+                want.append(int(tok[0]))
+                if d < 0 or not acc[0]:
+                    break
+                n_acc += 1
+            assert out[s] == want, (step, s, out[s], want)
+    if top_k == 0:
+        assert n_acc > 0          # untruncated: every draft has some mass, and u = 0 accepts it
+    b.close()

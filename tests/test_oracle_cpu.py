@@ -224,3 +224,60 @@ def test_golden_tiny_streams_and_losslessness(orc, qb):
         accepted += len(toks) - 1
         out += toks
     assert out[:28] == greedy[:28] and accepted > 0
+
+
+def _np_distribution(l, temp, top_p, top_k, min_p):
+    """Independent numpy statement of the sampling distribution (stable descending order)."""
+    n = len(l)
+    e = np.exp(((l - l.max()) * np.float32(1.0 / temp)).astype(np.float32)).astype(np.float32)
+    p = (e * np.float32(1.0 / e.astype(np.float64).sum())).astype(np.float32)
+    if not ((0 < top_k < n) or (0 < top_p < 1) or min_p > 0):
+        return p
+    order = np.argsort(-l.astype(np.float64), kind="stable")
+    keep = top_k if 0 < top_k < n else n
+    if min_p > 0:
+        keep = min(keep, int((p[order] >= p[order[0]] * np.float32(min_p)).sum()))
+    if 0 < top_p < 1:
+        cum = np.cumsum(p[order[:keep]].astype(np.float64))
+        hit = np.nonzero(cum >= np.float32(top_p))[0]
+        if len(hit):
+            keep = int(hit[0]) + 1
+    out = np.zeros(n, np.float32)
+    ks = p[order[:keep]].astype(np.float64).sum()
+    out[order[:keep]] = p[order[:keep]] * np.float32(1.0 / ks)
+    return out
+
+
+@pytest.mark.parametrize("temp,top_p,top_k,min_p", [(1.0, 1.0, 0, 0.0), (0.7, 0.9, 0, 0.0), (0.5, 1.0, 5, 0.0), (1.3, 0.8, 50, 0.05),
+                                                     (0.2, 0.0, 0, 0.3), (1.0, 0.5, 1, 0.0)])
+def test_sampling_acceptance_oracle(orc, temp, top_p, top_k, min_p):
+    """The oracle's sampling-mode acceptance against an independent numpy statement: p[draft], the accept decision, and the
+    inverse-CDF draw over the nonzero entries in index order."""
+    rng = np.random.default_rng(17)
+    rows, V = 12, 3000
+    x = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    x[3, 100] = x[3, 2000] = x[3].max() + 1          # a tie at the top
+    draft = np.where(np.arange(rows) % 3 == 2, -1, x.argmax(1)).astype(np.int32)
+    draft[4] = 7                                      # an unlikely draft
+    ua, ur = rng.random(rows), rng.random(rows)
+    tok, acc, pd = orc.sample_rows(x, draft, ua, ur, temp, top_p, top_k, min_p)
+    for r in range(rows):
+        p = _np_distribution(x[r], temp, top_p, top_k, min_p)
+        assert abs(p.astype(np.float64).sum() - 1) < 1e-4
+        d = int(draft[r])
+        if d >= 0:
+            assert np.isclose(pd[r], p[d], rtol=1e-5, atol=1e-9)
+            assert acc[r] == int(ua[r] < p[d])
+            if acc[r]:
+                assert tok[r] == d
+                continue
+            p[d] = 0
+        nz = np.nonzero(p > 0)[0]
+        if len(nz) == 0:
+            assert tok[r] == d
+            continue
+        cp = np.cumsum(p[nz].astype(np.float64) / p[nz].astype(np.float64).sum())
+        cp[-1] = 1.0
+        want = nz[np.searchsorted(cp, ur[r], side="left")]
+        assert tok[r] == want, (r, tok[r], want)
+        assert d < 0 or tok[r] != d
