@@ -2,23 +2,28 @@
 //
 // The reference pulls the verifier's logits to the host for non-greedy requests and runs
 // sampling_distribution + speculative_accept_pointmass there (src/qwen_native_backend.cpp:282-370, 399-467).
-// Here one CTA per logits row builds the same distribution in place -- softmax(logits / temp), then the top-k,
+// Here a cluster of 8 CTAs per logits row builds the same distribution -- softmax(logits / temp), then the top-k,
 // min-p and nucleus truncations, each a prefix of the descending order, renormalised over the kept set -- and
 // takes the row's decision: accept the (greedy, point-mass) draft with probability p[draft]; on rejection draw
 // from p with the draft removed; a row without a draft draws from p (the bonus token, or plain sampling).
 // The uniform draws come from the caller, in the order the reference's generator would be consumed.
 //
-// The kept set is found without sorting: the descending order is the order of a monotone 32-bit key of the
-// logit, and "the shortest prefix that reaches top_p or the count limit" is a bisection over that key with one
-// pass over the row per step (count and probability mass of the keys at or above the probe).  Ties at the
-// boundary key are taken lowest index first.
+// Every thread keeps its (at most 20) consecutive logits and their exponentials in registers, so the row is read
+// once.  The kept set is found without sorting: the descending order is the order of a monotone 32-bit key of the
+// logit, and "the shortest prefix that reaches top_p or the count limit" is a radix descent over that key, two
+// bits per pass: a 4-bin histogram (count and probability mass) of the elements under the current prefix, reduced
+// over the block and exchanged between the CTAs through distributed shared memory.  Ties at the boundary key are
+// taken lowest index first.
 #include "qb_internal.h"
 
 #include <cfloat>
 
 namespace {
 
-constexpr int ST = 1024;                      // threads per row
+constexpr int ST = 1024;                      // threads per CTA
+constexpr int CL = 8;                         // CTAs per row (one cluster)
+constexpr int EPT = 20;                       // elements per thread at most: rows up to CL * ST * EPT = 163840 logits
+constexpr int NB = 4;                         // histogram bins per pass (two key bits)
 
 struct SampleParams {
     float inv_t, top_p, min_p;
@@ -29,136 +34,233 @@ __device__ __forceinline__ uint32_t okey(float f) {      // ascending key order 
     const uint32_t b = __float_as_uint(f);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
-
-template <typename T, typename Op>
-__device__ T block_reduce(T v, Op op, T *scratch) {       // all threads get the result; scratch: 32 entries
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
-    __syncthreads();                                       // scratch may still be read from an earlier call
-    if (lane == 0) scratch[warp] = v;
-    __syncthreads();
-    T r = scratch[lane];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) r = op(r, __shfl_xor_sync(0xffffffffu, r, o));
-    return r;
-}
-
-struct OpSumD { __device__ double operator()(double a, double b) const { return a + b; } };
-struct OpSumU { __device__ unsigned long long operator()(unsigned long long a, unsigned long long b) const { return a + b; } };
-struct OpMaxF { __device__ float operator()(float a, float b) const { return fmaxf(a, b); } };
-struct OpMinI { __device__ int operator()(int a, int b) const { return a < b ? a : b; } };
-struct OpMaxI { __device__ int operator()(int a, int b) const { return a > b ? a : b; } };
-
-// exclusive prefix over the threads of the block (thread order) of a double and a count; totals returned too
-__device__ void block_exscan(double v, unsigned int c, double &ex_v, unsigned int &ex_c, double &tot_v, unsigned int &tot_c,
-                             double *sv, unsigned int *sc) {
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    double iv = v;
-    unsigned int ic = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const double nv = __shfl_up_sync(0xffffffffu, iv, o);
-        const unsigned int nc = __shfl_up_sync(0xffffffffu, ic, o);
-        if (lane >= (uint32_t)o) { iv += nv; ic += nc; }
-    }
-    __syncthreads();
-    if (lane == 31) { sv[warp] = iv; sc[warp] = ic; }
-    __syncthreads();
-    double wv = 0.0;
-    unsigned int wc = 0;
-    tot_v = 0.0; tot_c = 0;
-    for (uint32_t w = 0; w < ST / 32; ++w) {               // 32 entries, warp order = the summation order of a serial scan
-        if (w < warp) { wv += sv[w]; wc += sc[w]; }
-        tot_v += sv[w]; tot_c += sc[w];
-    }
-    ex_v = wv + (iv - v);
-    ex_c = wc + (ic - c);
-}
-
 __device__ __forceinline__ float key_to_float(uint32_t k) {
     return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
 
-// One CTA per row.  draft[row] < 0: no draft (bonus / plain sampling row).
+// Shared memory of a CTA: per-warp partials of a block reduction and the exchange area the CTAs of the cluster write
+// into (two buffers, used alternately: a CTA that is one exchange ahead never overwrites what a slower one still reads).
+struct Smem {
+    double wd[ST / 32][NB];
+    long long wi[ST / 32][NB];
+    double xd[2][CL][NB];
+    long long xi[2][CL][NB];
+};
+
+struct Comm {
+    Smem *sm;
+    uint32_t crank;
+    int par;
+};
+
+__device__ __forceinline__ void push_to_cluster(Comm &c, int j, double sd, long long si) {
+    const uint32_t ld = (uint32_t)__cvta_generic_to_shared(&c.sm->xd[c.par][c.crank][j]);
+    const uint32_t li = (uint32_t)__cvta_generic_to_shared(&c.sm->xi[c.par][c.crank][j]);
+    for (uint32_t r = 0; r < CL; ++r) {
+        uint32_t rd, ri;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rd) : "r"(ld), "r"(r));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ri) : "r"(li), "r"(r));
+        asm volatile("st.shared::cluster.f64 [%0], %1;" ::"r"(rd), "d"(sd) : "memory");
+        asm volatile("st.shared::cluster.s64 [%0], %1;" ::"r"(ri), "l"(si) : "memory");
+    }
+}
+__device__ __forceinline__ int cluster_turn(Comm &c) {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    const int buf = c.par;
+    c.par ^= 1;
+    return buf;
+}
+
+// Sum over the block of N (<= NB) doubles and N integers per thread (warp shuffles, then the 32 warp rows added in warp
+// order), handed to every CTA of the cluster: afterwards c.sm->xd[buf][rank][j] / xi[buf][rank][j] hold every CTA's sums.
+template <int N>
+__device__ int exchange(Comm &c, double (&d)[N], long long (&i)[N]) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            d[j] += __shfl_xor_sync(0xffffffffu, d[j], o);
+            i[j] += __shfl_xor_sync(0xffffffffu, i[j], o);
+        }
+    }
+    __syncthreads();                                       // the warp rows may still be read from the previous call
+    if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) { c.sm->wd[warp][j] = d[j]; c.sm->wi[warp][j] = i[j]; }
+    }
+    __syncthreads();
+    if (threadIdx.x < N) {
+        double sd = 0.0;
+        long long si = 0;
+        for (int w = 0; w < ST / 32; ++w) { sd += c.sm->wd[w][threadIdx.x]; si += c.sm->wi[w][threadIdx.x]; }
+        push_to_cluster(c, (int)threadIdx.x, sd, si);
+    }
+    return cluster_turn(c);
+}
+
+// one maximum (as a double) and one minimum (as an integer) per CTA, exchanged the same way; combined by the caller
+__device__ int exchange_minmax(Comm &c, double vmax, long long vmin) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        vmax = fmax(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+        const long long t = __shfl_xor_sync(0xffffffffu, vmin, o);
+        vmin = t < vmin ? t : vmin;
+    }
+    __syncthreads();
+    if (lane == 0) { c.sm->wd[warp][0] = vmax; c.sm->wi[warp][0] = vmin; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double sd = c.sm->wd[0][0];
+        long long si = c.sm->wi[0][0];
+        for (int w = 1; w < ST / 32; ++w) { sd = fmax(sd, c.sm->wd[w][0]); si = c.sm->wi[w][0] < si ? c.sm->wi[w][0] : si; }
+        push_to_cluster(c, 0, sd, si);
+    }
+    return cluster_turn(c);
+}
+
+// exclusive prefix of (v, n) over the threads of this CTA in thread order, and the CTA totals
+__device__ void block_exscan(Comm &c, double v, long long n, double &ex_v, long long &ex_n, double &tot_v, long long &tot_n) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    double iv = v;
+    long long in = n;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double nv = __shfl_up_sync(0xffffffffu, iv, o);
+        const long long nn = __shfl_up_sync(0xffffffffu, in, o);
+        if (lane >= (uint32_t)o) { iv += nv; in += nn; }
+    }
+    __syncthreads();
+    if (lane == 31) { c.sm->wd[warp][0] = iv; c.sm->wi[warp][0] = in; }
+    __syncthreads();
+    double wv = 0.0;
+    long long wn = 0;
+    tot_v = 0.0; tot_n = 0;
+    for (uint32_t w = 0; w < ST / 32; ++w) {
+        if (w < warp) { wv += c.sm->wd[w][0]; wn += c.sm->wi[w][0]; }
+        tot_v += c.sm->wd[w][0]; tot_n += c.sm->wi[w][0];
+    }
+    ex_v = wv + (iv - v);
+    ex_n = wn + (in - n);
+}
+
+// One cluster per row.  draft == nullptr or the row's draft < 0: no draft (bonus / plain sampling row).
+// K1 = 0: one draft entry per row; K1 > 0: rows are [sequence][K1] and drafts [sequence][K1 - 1], the last row of a
+// sequence has none.
 __global__ void __launch_bounds__(ST)
 sample_rows_kernel(const float *__restrict__ logits, uint32_t V, uint32_t stride, const int32_t *__restrict__ draft,
                    const double *__restrict__ u_acc, const double *__restrict__ u_res, SampleParams p, int32_t *token,
                    int32_t *accepted, float *p_draft, float *pval, int32_t *pidx, uint32_t nblk, uint32_t K1) {
-    __shared__ double s_d[32];
-    __shared__ unsigned long long s_u[32];
-    __shared__ float s_f[32];
-    __shared__ int s_i[32];
-    __shared__ unsigned int s_c[32];
+    __shared__ Smem sm;
     QB_PDL_ENTER();
-    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    Comm c;
+    c.sm = &sm; c.par = 0;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(c.crank));
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");     // every CTA of the cluster runs (its shared
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");       // memory exists) before anyone writes into it
+    const uint32_t row = blockIdx.x / CL, tid = threadIdx.x;
     const float *x = logits + (size_t)row * stride;
+    // this CTA's slice of the row, this thread's consecutive elements of it (index order = rank, thread, j)
+    const uint32_t VC = (V + CL - 1) / CL, s0 = min(V, c.crank * VC), s1 = min(V, s0 + VC);
+    const uint32_t ept = (VC + ST - 1) / ST, g0 = s0 + tid * ept;
+    const int nv = g0 >= s1 ? 0 : (int)min(ept, s1 - g0);
+    float l[EPT];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) l[j] = j < nv ? x[g0 + j] : -INFINITY;
 
-    // softmax(logits / temp): max, then the denominator in double (src/qwen_native_backend.cpp:296-303)
-    float mx = -INFINITY;
-    for (uint32_t i = tid; i < V; i += ST) mx = fmaxf(mx, x[i]);
-    mx = block_reduce(mx, OpMaxF(), s_f);
-    int top_idx = 0x7fffffff;
-    double sum = 0.0;
-    for (uint32_t i = tid; i < V; i += ST) {
-        const float l = x[i];
-        if (l == mx && (int)i < top_idx) top_idx = (int)i;
-        sum += (double)expf((l - mx) * p.inv_t);
+    // largest logit and its lowest index in one exchange: max of (key, ~index) as one integer
+    float mx;
+    int top_idx;
+    {
+        unsigned long long best = 0;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j)
+            if (j < nv) {
+                const unsigned long long pk = ((unsigned long long)okey(l[j]) << 32) | (uint32_t)~(g0 + j);
+                best = pk > best ? pk : best;
+            }
+        const int buf = exchange_minmax(c, 0.0, ~(long long)(best ^ 0x8000000000000000ull));
+        long long m = sm.xi[buf][0][0];
+        for (int r = 1; r < CL; ++r) m = sm.xi[buf][r][0] < m ? sm.xi[buf][r][0] : m;
+        const unsigned long long pk = (unsigned long long)(~m) ^ 0x8000000000000000ull;
+        mx = key_to_float((uint32_t)(pk >> 32));
+        top_idx = (int)(~(uint32_t)pk);
     }
-    sum = block_reduce(sum, OpSumD(), s_d);
-    top_idx = block_reduce(top_idx, OpMinI(), s_i);
-    const float norm = (float)(1.0 / (sum > 0.0 ? sum : 1.0));
-    auto prob = [&](float l) -> float { return expf((l - mx) * p.inv_t) * norm; };
+    // softmax denominator in double (src/qwen_native_backend.cpp:296-303)
+    float norm;
+    {
+        double d[1] = {0.0};
+        long long z[1] = {0};
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) if (j < nv) d[0] += (double)expf((l[j] - mx) * p.inv_t);
+        const int buf = exchange<1>(c, d, z);
+        double sum = 0.0;
+        for (int r = 0; r < CL; ++r) sum += sm.xd[buf][r][0];
+        norm = (float)(1.0 / (sum > 0.0 ? sum : 1.0));
+    }
+    auto prob = [&](float v) -> float { return expf((v - mx) * p.inv_t) * norm; };
 
     const bool use_k = p.top_k > 0 && (uint32_t)p.top_k < V, use_p = p.top_p < 1.0f && p.top_p > 0.0f, use_m = p.min_p > 0.0f;
     const bool trunc = use_k || use_p || use_m;
     uint32_t B = 0;                 // boundary key: keys above it are kept, r_ties of the n_ties equal to it
-    unsigned int r_ties = 0, n_ties = 0;
+    long long r_ties = 0, n_ties = 0;
     float kn = 1.0f;
     bool degenerate = false;
     if (trunc) {
-        unsigned long long L1 = use_k ? (unsigned long long)p.top_k : (unsigned long long)V;
+        long long L1 = use_k ? (long long)p.top_k : (long long)V;
         if (use_m) {                // min-p keeps the prefix whose probability is at least min_p times the top one (:333-338)
             const float cutoff = prob(mx) * p.min_p;
-            unsigned long long c = 0;
-            for (uint32_t i = tid; i < V; i += ST) c += prob(x[i]) >= cutoff ? 1u : 0u;
-            c = block_reduce(c, OpSumU(), s_u);
-            L1 = c < L1 ? c : L1;
+            double z[1] = {0.0};
+            long long n[1] = {0};
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) if (j < nv && prob(l[j]) >= cutoff) ++n[0];
+            const int buf = exchange<1>(c, z, n);
+            long long cnt = 0;
+            for (int r = 0; r < CL; ++r) cnt += sm.xi[buf][r][0];
+            L1 = cnt < L1 ? cnt : L1;
         }
         if (L1 == 0) {
             degenerate = true;
         } else {
-            // largest key t such that the elements with key >= t already hit the count limit or the nucleus mass
-            uint32_t lo = 0, hi = 0xffffffffu;
-            while (lo < hi) {
-                const uint32_t mid = lo + (uint32_t)(((unsigned long long)(hi - lo) + 1) >> 1);
-                unsigned long long c = 0;
-                double m = 0.0;
-                for (uint32_t i = tid; i < V; i += ST) {
-                    const float l = x[i];
-                    if (okey(l) >= mid) { ++c; if (use_p) m += (double)prob(l); }
-                }
-                c = block_reduce(c, OpSumU(), s_u);
-                bool ok = c >= L1;
-                if (use_p && !ok) { m = block_reduce(m, OpSumD(), s_d); ok = m >= (double)p.top_p; }
-                if (ok) lo = mid; else hi = mid - 1;
-            }
-            B = lo;
-            unsigned long long c_above = 0, c_eq = 0;
+            // radix descent from the top key bits: the bin (walking down from the highest) in which the elements seen so
+            // far first hit the count limit or the nucleus mass holds the boundary key
+            long long c_above = 0;
             double m_above = 0.0;
-            for (uint32_t i = tid; i < V; i += ST) {
-                const float l = x[i];
-                const uint32_t k = okey(l);
-                if (k > B) { ++c_above; m_above += (double)prob(l); }
-                else if (k == B) ++c_eq;
+            uint32_t pre = 0;
+            for (int sh = 30; sh >= 0; sh -= 2) {
+                double hm[NB] = {0.0, 0.0, 0.0, 0.0};
+                long long hc[NB] = {0, 0, 0, 0};
+#pragma unroll
+                for (int j = 0; j < EPT; ++j) {
+                    const uint32_t k = okey(l[j]);
+                    if (j < nv && (sh == 30 || (k >> (sh + 2)) == pre)) {
+                        const uint32_t b = (k >> sh) & 3u;
+                        const double pm = (double)prob(l[j]);
+#pragma unroll
+                        for (int q = 0; q < NB; ++q) { hc[q] += b == (uint32_t)q ? 1 : 0; hm[q] += b == (uint32_t)q ? pm : 0.0; }
+                    }
+                }
+                const int buf = exchange<NB>(c, hm, hc);
+                long long cc = 0;
+                double mc = 0.0;
+                int chosen = 0;
+                for (int q = NB - 1; q >= 0; --q) {
+                    long long tc = 0;
+                    double tm = 0.0;
+                    for (int r = 0; r < CL; ++r) { tc += sm.xi[buf][r][q]; tm += sm.xd[buf][r][q]; }
+                    const bool ok = c_above + cc + tc >= L1 || (use_p && m_above + mc + tm >= (double)p.top_p);
+                    if (ok || q == 0) { chosen = q; n_ties = tc; break; }
+                    cc += tc; mc += tm;
+                }
+                c_above += cc; m_above += mc;
+                pre = (pre << 2) | (uint32_t)chosen;
             }
-            c_above = block_reduce(c_above, OpSumU(), s_u);
-            c_eq = block_reduce(c_eq, OpSumU(), s_u);
-            m_above = block_reduce(m_above, OpSumD(), s_d);
-            n_ties = (unsigned int)c_eq;
+            B = pre;
             const float pB = prob(key_to_float(B));
             double cum = m_above;
-            unsigned int j = 0;
+            long long j = 0;
             while (j < n_ties) {     // ties enter one at a time, as the sorted walk of the reference does (:340-348)
                 ++j;
                 cum += (double)pB;
@@ -171,88 +273,105 @@ sample_rows_kernel(const float *__restrict__ logits, uint32_t V, uint32_t stride
         }
     }
     const bool rank_ties = trunc && !degenerate && r_ties < n_ties;
-    // probability of element i of the final distribution; tie_rank only matters when rank_ties
-    auto out_of = [&](uint32_t i, float l, unsigned int tie_rank) -> float {
+    // probability of element i (logit v) of the final distribution; tie_rank only matters when rank_ties
+    auto out_of = [&](uint32_t i, float v, long long tie_rank) -> float {
         if (degenerate) return (int)i == top_idx ? 1.0f : 0.0f;
-        if (!trunc) return prob(l);
-        const uint32_t k = okey(l);
-        if (k > B || (k == B && (!rank_ties || tie_rank < r_ties))) return prob(l) * kn;
+        if (!trunc) return prob(v);
+        const uint32_t k = okey(v);
+        if (k > B || (k == B && (!rank_ties || tie_rank < r_ties))) return prob(v) * kn;
         return 0.0f;
     };
-    // contiguous chunk of this thread (index order = the order sample_from walks the nonzero entries, :373-383)
-    const uint32_t CH = (V + ST - 1) / ST, i0 = tid * CH, i1 = (i0 + CH < V) ? i0 + CH : V;
-    unsigned int tie_ex = 0;
+    // ranks of the boundary ties in index order: this thread's first tie rank, and the rank of the draft
+    const int d = !draft ? -1 : K1 == 0 ? draft[row] : (row % K1 + 1 < K1 ? draft[(row / K1) * (K1 - 1) + row % K1] : -1);
+    const bool has_d = d >= 0 && (uint32_t)d < V;
+    long long tie_ex = 0, d_rank = 0;
     if (rank_ties) {
-        unsigned int c = 0;
-        for (uint32_t i = i0; i < i1; ++i) c += okey(x[i]) == B ? 1u : 0u;
-        double dv, dt;
-        unsigned int tot;
-        block_exscan(0.0, c, dv, tie_ex, dt, tot, s_d, s_c);
+        double z[2] = {0.0, 0.0};
+        long long n[2] = {0, 0};
+#pragma unroll
+        for (int j = 0; j < EPT; ++j)
+            if (j < nv && okey(l[j]) == B) { ++n[0]; if (has_d && g0 + j < (uint32_t)d) ++n[1]; }
+        double ev, tv;
+        long long tn;
+        block_exscan(c, 0.0, n[0], ev, tie_ex, tv, tn);
+        const int buf = exchange<2>(c, z, n);
+        for (uint32_t r = 0; r < CL; ++r) {
+            if (r < c.crank) tie_ex += sm.xi[buf][r][0];
+            d_rank += sm.xi[buf][r][1];
+        }
     }
     // accept the draft with probability p[draft] (:436-443)
-    // K1 = 0: one draft entry per row; K1 > 0: rows are [sequence][K1] and drafts [sequence][K1 - 1], the last row of a
-    // sequence has none
-    const int d = !draft ? -1 : K1 == 0 ? draft[row] : (row % K1 + 1 < K1 ? draft[(row / K1) * (K1 - 1) + row % K1] : -1);
     int acc = 0;
     float pd = 0.0f;
-    if (d >= 0 && (uint32_t)d < V) {
-        unsigned int rk = 0;
-        if (rank_ties && okey(x[d]) == B) {                 // rank of the draft among the boundary ties
-            unsigned long long c = 0;
-            for (uint32_t i = tid; i < (uint32_t)d; i += ST) c += okey(x[i]) == B ? 1u : 0u;
-            rk = (unsigned int)block_reduce(c, OpSumU(), s_u);
-        }
-        pd = out_of((uint32_t)d, x[d], rk);
+    if (has_d) {
+        pd = out_of((uint32_t)d, x[d], d_rank);
         acc = u_acc[row] < (double)pd ? 1 : 0;
     }
     int tok = d;
     if (!acc) {
         // draw from the distribution with the rejected draft removed: inverse CDF over the nonzero entries in index
         // order, cumulative sums of weight / total, the last one forced to 1 (std::discrete_distribution)
-        double wsum = 0.0;
-        unsigned int tr = tie_ex;
-        for (uint32_t i = i0; i < i1; ++i) {
-            const float l = x[i];
-            const bool tie = rank_ties && okey(l) == B;
-            if ((int)i != d) wsum += (double)out_of(i, l, tr);
-            if (tie) ++tr;
+        double w[1] = {0.0};
+        long long z[1] = {0};
+        {
+            long long tr = tie_ex;
+#pragma unroll
+            for (int j = 0; j < EPT; ++j)
+                if (j < nv) {
+                    const bool tie = rank_ties && okey(l[j]) == B;
+                    if ((int)(g0 + j) != d) w[0] += (double)out_of(g0 + j, l[j], tr);
+                    if (tie) ++tr;
+                }
         }
-        double ex, total;
-        unsigned int ec, tc;
-        block_exscan(wsum, 0u, ex, ec, total, tc, s_d, s_c);
-        int cand = 0x7fffffff, last_nz = -1;
+        double ex, tv;
+        long long en, tn;
+        block_exscan(c, w[0], 0, ex, en, tv, tn);
+        int buf = exchange<1>(c, w, z);
+        double total = 0.0, off = 0.0;
+        for (uint32_t r = 0; r < CL; ++r) {
+            if (r < c.crank) off += sm.xd[buf][r][0];
+            total += sm.xd[buf][r][0];
+        }
+        long long cand = 0x7fffffff;
+        double last_nz = -1.0;
         if (total > 0.0) {
             const double u = u_res[row];
-            double run = ex;
-            tr = tie_ex;
-            for (uint32_t i = i0; i < i1; ++i) {
-                const float l = x[i];
-                const bool tie = rank_ties && okey(l) == B;
-                const float w = (int)i != d ? out_of(i, l, tr) : 0.0f;
-                if (tie) ++tr;
-                if (w > 0.0f) {
-                    run += (double)w;
-                    last_nz = (int)i;
-                    if (cand == 0x7fffffff && run / total >= u) cand = (int)i;
+            double run = off + ex;
+            long long tr = tie_ex;
+#pragma unroll
+            for (int j = 0; j < EPT; ++j)
+                if (j < nv) {
+                    const bool tie = rank_ties && okey(l[j]) == B;
+                    const float wj = (int)(g0 + j) != d ? out_of(g0 + j, l[j], tr) : 0.0f;
+                    if (tie) ++tr;
+                    if (wj > 0.0f) {
+                        run += (double)wj;
+                        last_nz = (double)(g0 + j);
+                        if (cand == 0x7fffffff && run / total >= u) cand = (long long)(g0 + j);
+                    }
                 }
-            }
         }
-        cand = block_reduce(cand, OpMinI(), s_i);
-        last_nz = block_reduce(last_nz, OpMaxI(), s_i);
-        if (cand != 0x7fffffff) tok = cand;
-        else if (last_nz >= 0) tok = last_nz;
+        buf = exchange_minmax(c, last_nz, cand);
+        for (uint32_t r = 0; r < CL; ++r) {
+            cand = sm.xi[buf][r][0] < cand ? sm.xi[buf][r][0] : cand;
+            last_nz = fmax(last_nz, sm.xd[buf][r][0]);
+        }
+        if (cand != 0x7fffffff) tok = (int)cand;
+        else if (last_nz >= 0.0) tok = (int)last_nz;
         else if (d < 0) tok = top_idx;                      // cannot happen for a proper distribution
     }
-    if (tid == 0) {
-        if (token) token[row] = tok;
-        if (accepted) accepted[row] = acc;
-        if (p_draft) p_draft[row] = pd;
-    }
-    if (pval)                                               // the row's "argmax" for the commit kernel: the decided token
-        for (uint32_t j = tid; j < nblk; j += ST) {
-            pval[(size_t)row * nblk + j] = j == 0 ? INFINITY : -INFINITY;
-            pidx[(size_t)row * nblk + j] = j == 0 ? tok : 0x7fffffff;
+    if (c.crank == 0) {
+        if (tid == 0) {
+            if (token) token[row] = tok;
+            if (accepted) accepted[row] = acc;
+            if (p_draft) p_draft[row] = pd;
         }
+        if (pval)                                           // the row's "argmax" for the commit kernel: the decided token
+            for (uint32_t j = tid; j < nblk; j += ST) {
+                pval[(size_t)row * nblk + j] = j == 0 ? INFINITY : -INFINITY;
+                pidx[(size_t)row * nblk + j] = j == 0 ? tok : 0x7fffffff;
+            }
+    }
 }
 
 }  // namespace
@@ -265,8 +384,22 @@ int qb_launch_sample_rows(qb_ctx *ctx, const float *logits, uint32_t rows, uint3
     QB_REQUIRE(rows > 0 && V > 0 && u_res != nullptr, "qb_launch_sample_rows: bad arguments");
     SampleParams p;
     p.inv_t = 1.0f / temp; p.top_p = top_p; p.min_p = min_p; p.top_k = top_k;
-    QB_CUDA(qb_launch_pdl(ctx->stream, sample_rows_kernel, dim3(rows), dim3(ST), (size_t)0, logits, V, stride, draft, u_acc, u_res, p,
-                          token, accepted, p_draft, pval, pidx, nblk, K1));
+    QB_REQUIRE(V <= (uint32_t)(CL * ST * EPT), "sampling: rows of %u logits exceed the kernel's %d", V, CL * ST * EPT);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * CL);
+    cfg.blockDim = dim3(ST);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = CL;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    QB_CUDA(cudaLaunchKernelEx(&cfg, sample_rows_kernel, logits, V, stride, draft, u_acc, u_res, p, token, accepted, p_draft, pval,
+                               pidx, nblk, K1));
     QB_LAUNCHED(ctx, "sample_rows_kernel");
     return QB_OK;
 }
