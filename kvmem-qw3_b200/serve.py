@@ -63,14 +63,36 @@ class SlotScheduler:
         return not self.pending and not self.active
 
 
-def run(engine, requests, speculative=True, max_steps=1 << 30):
+class DrawQueue:
+    """Uniform draws of one request in the order the reference consumes its generator (one std::mt19937_64 per request,
+    src/qwen_native_backend.cpp:399-467): a sampled step is handed k+1 draws and uses the first accepted + 1 of them; the
+    rest stay at the head of the queue for the next step."""
+
+    def __init__(self, rng, width):
+        self.rng, self.width, self.buf = rng, width, []
+
+    def peek(self):
+        while len(self.buf) < self.width:
+            self.buf.append(float(self.rng.random()))
+        return self.buf[:self.width]
+
+    def consume(self, n):
+        del self.buf[:n]
+
+
+def run(engine, requests, speculative=True, max_steps=1 << 30, sampling=None, rng_of=None):
     """Serve `requests` (a list of Request) to completion; returns them in completion order.
-    One loop iteration = admissions (a prefill each) + one decode step of the whole batch."""
+    One loop iteration = admissions (a prefill each) + one decode step of the whole batch.
+    sampling: None (greedy) or dict(temp=, top_p=, top_k=, min_p=) for engine.mtp_step_sampled; rng_of(request) gives the
+    request's generator (anything with .random() -> float in [0, 1))."""
     sched = SlotScheduler(engine.n_seqs)
     for r in sorted(requests, key=lambda r: (r.arrival_step, r.rid)):
         sched.submit(r)
     per_step = engine.k + 1 if speculative else 1
     idle_pos = [0] * engine.n_seqs                       # upper bound of the position of slots that hold no request
+    if sampling is not None and not speculative:
+        raise ValueError("sampled decode runs through the speculative step")
+    draws = {}                                           # slot -> DrawQueue of the request it holds
     finished, step = [], 0
     while not sched.idle() and step < max_steps:
         for req in sched.admissible(step):
@@ -78,6 +100,8 @@ def run(engine, requests, speculative=True, max_steps=1 << 30):
                 raise ValueError("request %r does not fit max_ctx %d" % (req.rid, engine.max_ctx))
             engine.reset(req.slot)
             engine.prefill(req.slot, req.prompt)
+            if sampling is not None:
+                draws[req.slot] = DrawQueue(rng_of(req), per_step)
             req.tokens.extend(engine.read_output()[req.slot])      # the prefill's last row gives the first token
             if req.done():
                 req._trim()
@@ -90,7 +114,10 @@ def run(engine, requests, speculative=True, max_steps=1 << 30):
             if s not in sched.active and idle_pos[s] + 2 * per_step >= engine.max_ctx:
                 engine.reset(s)
                 idle_pos[s] = 0
-        if speculative:
+        if sampling is not None:
+            u = [draws[s].peek() if s in sched.active else [0.5] * per_step for s in range(engine.n_seqs)]
+            engine.mtp_step_sampled(u, **sampling)
+        elif speculative:
             engine.mtp_step()
         else:
             engine.greedy_step()
@@ -102,6 +129,8 @@ def run(engine, requests, speculative=True, max_steps=1 << 30):
                 idle_pos[s] += per_step
                 continue
             req.tokens.extend(out[s])
+            if sampling is not None:
+                draws[s].consume(len(out[s]))            # accepted + 1 draws were used
             if req.done():
                 req._trim()
                 finished.append(sched.retire(s, step))

@@ -70,3 +70,28 @@ def test_idle_slot_survives_a_long_run(qb, orc, ctx, model):
     b.close()
     want = alone(qb, model, p, 70, 1)
     assert done[0].tokens == want and done[1].tokens == want
+
+
+def test_sampled_serving_reproduces_each_request_alone(qb, orc, ctx, model):
+    """Sampling mode through the loop: a request with its own generator gets the same tokens in a shared batch with delayed
+    admission as alone in a one-slot batch (decisions depend only on the request's logits and its own draws)."""
+    V = model.cfg.vocab_size
+    samp = dict(temp=0.9, top_p=0.95, top_k=40, min_p=0.0)
+    spec = [(30, 14, 0), (12, 20, 0), (21, 10, 2), (9, 16, 5)]
+    mk = lambda: [qb.serve.Request(i, orc.synth_prompt(400 + i, V, n), new, arrival_step=a) for i, (n, new, a) in enumerate(spec)]
+    rng_of = lambda r: np.random.default_rng(1000 + r.rid)
+    b = qb.Batch(model, 2, 256, 1)
+    together = {r.rid: r.tokens for r in qb.serve.run(b, mk(), sampling=samp, rng_of=rng_of)}
+    b.close()
+    for req in mk():
+        b1 = qb.Batch(model, 1, 256, 1)
+        req.arrival_step = 0
+        solo = qb.serve.run(b1, [req], sampling=samp, rng_of=rng_of)[0].tokens
+        b1.close()
+        assert together[req.rid] == solo, req.rid
+    # and top_k = 1 collapses to the greedy stream whatever the draws
+    b = qb.Batch(model, 2, 256, 1)
+    done = qb.serve.run(b, mk(), sampling=dict(temp=0.7, top_p=1.0, top_k=1, min_p=0.0), rng_of=rng_of)
+    b.close()
+    for r in done:
+        assert r.tokens == alone(qb, model, r.prompt, r.max_new_tokens, 1), r.rid

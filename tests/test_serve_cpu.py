@@ -113,3 +113,48 @@ def test_request_that_cannot_fit_is_refused():
     serve = entry.load_package().serve
     with pytest.raises(ValueError):
         serve.run(FakeEngine(1, 3, 32), [serve.Request(0, list(range(20)), 20)])
+
+
+def test_sampled_serving_hands_each_request_its_draws_in_order():
+    """A sampled step gets k+1 draws per slot and consumes as many as it emitted tokens; the rest lead the next step."""
+    serve = entry.load_package().serve
+
+    class Counter:
+        def __init__(self, base):
+            self.n = base
+
+        def random(self):
+            self.n += 1
+            return self.n / 1000.0
+
+    class Eng(FakeEngine):
+        def __init__(self, *a):
+            super().__init__(*a)
+            self.seen = []
+
+        def mtp_step_sampled(self, u, **kw):
+            assert kw == dict(temp=0.8, top_p=0.9, top_k=0, min_p=0.0)
+            self.seen.append([list(r) for r in u])
+            self.mtp_step()
+
+    eng = Eng(2, 3, 256)
+    reqs = [serve.Request(0, [1, 2], 9), serve.Request(1, [3], 7, arrival_step=2)]
+    done = serve.run(eng, reqs, sampling=dict(temp=0.8, top_p=0.9, top_k=0, min_p=0.0), rng_of=lambda r: Counter(100 * r.rid))
+    assert {r.rid: r.tokens for r in done} == {0: stream([1, 2], 9), 1: stream([3], 7)}
+    used, emitted, budget = {0: [], 1: []}, {0: 1, 1: 1}, {0: 9, 1: 7}      # the prefill gave each its first token
+    # replay: what each step consumed is the head of what it was handed, and the heads chain into 1, 2, 3, ... per request
+    eng2 = FakeEngine(2, 3, 256)
+    eng2.prefill(0, [1, 2])
+    for step, u in enumerate(eng.seen):
+        if step == 2:
+            eng2.reset(1)
+            eng2.prefill(1, [3])
+        eng2.mtp_step()
+        out = eng2.read_output()
+        for s in (0, 1):
+            if eng2.prompt[s] is not None and emitted[s] < budget[s]:
+                used[s] += u[s][:len(out[s])]
+                emitted[s] += len(out[s])
+    for s, base in ((0, 0), (1, 100)):
+        got = [round(v * 1000) for v in used[s]]
+        assert len(got) >= budget[s] - 1 and got == list(range(base + 1, base + 1 + len(got)))
