@@ -270,7 +270,7 @@ int qb_mtp_step(qb_ctx *ctx, qb_batch *b);
  *   with u_res_dev[row]; draft_dev == NULL or draft_dev[row] < 0: token = a draw from p with u_res_dev[row].
  * Draws walk the nonzero entries in index order (sample_from, :373-383, std::discrete_distribution).  top_k <= 0, top_p
  * outside (0,1) and min_p <= 0 switch the respective truncation off.  Ties at the truncation boundary are kept lowest index
- * first.  Token penalties (:262-280) are not applied.  p_draft_dev / accepted_dev may be NULL. */
+ * first.  Token penalties are applied by the batch-level form below only.  p_draft_dev / accepted_dev may be NULL. */
 int qb_sample_rows(qb_ctx *ctx, const float *logits_dev, uint32_t rows, uint32_t V, uint32_t stride, const int32_t *draft_dev,
                    const double *u_acc_dev, const double *u_res_dev, float temp, float top_p, int32_t top_k, float min_p,
                    int32_t *token_dev, int32_t *accepted_dev, float *p_draft_dev);
@@ -279,6 +279,12 @@ int qb_sample_rows(qb_ctx *ctx, const float *logits_dev, uint32_t rows, uint32_t
  * generator: row i accepts with u[i], a rejection at row i draws with u[i+1], the bonus draw is u[k]; a step uses the
  * first accepted + 1 of them. */
 int qb_mtp_sample_rows(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host);
+/* Token penalties of sampling requests (apply_token_penalties, src/qwen_native_backend.cpp:262-280: a seen token's logit is
+ * divided by repetition when >= 0, multiplied when < 0, then lowered by presence): from this call on the batch records the
+ * prompt and emitted tokens of every sequence, and qb_mtp_sample_rows penalises their logits and, on row i, those of the
+ * step's drafts 0..i-1 (the running prefix of the accept loop, :432-447).  Call before the prefill of the requests it
+ * should cover; qb_seq_reset clears a sequence's record.  presence = 0 and repetition = 1 switch the penalties off. */
+int qb_batch_set_penalties(qb_ctx *ctx, qb_batch *b, float presence, float repetition);
 /* draft + verify + sample_rows + accept_commit. */
 int qb_mtp_step_sampled(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host);
 

@@ -86,6 +86,7 @@ SIGNATURES = {
     "qb_batch_stats": (i32, [vp, vp, vp]),
     "qb_seq_position": (i32, [vp, vp, u32, C.POINTER(C.c_int32)]),
     "qb_seq_reset": (i32, [vp, vp, u32]),
+    "qb_batch_set_penalties": (i32, [vp, vp, C.c_float, C.c_float]),
     "qb_sample_rows": (i32, [vp, vp, u32, u32, u32, vp, vp, vp, C.c_float, C.c_float, i32, C.c_float, vp, vp, vp]),
     "qb_mtp_sample_rows": (i32, [vp, vp, C.c_float, C.c_float, i32, C.c_float, vp]),
     "qb_mtp_step_sampled": (i32, [vp, vp, C.c_float, C.c_float, i32, C.c_float, vp]),
@@ -430,6 +431,9 @@ class Batch:
 
     def mtp_step(self):
         check(lib().qb_mtp_step(self.ctx.h, self.h))
+
+    def set_penalties(self, presence=0.0, repetition=1.0):
+        check(lib().qb_batch_set_penalties(self.ctx.h, self.h, presence, repetition))
 
     def mtp_step_sampled(self, u, temp, top_p=1.0, top_k=0, min_p=0.0):
         """u: float64 [n_seqs][k+1] uniform draws (see qb_mtp_sample_rows)."""

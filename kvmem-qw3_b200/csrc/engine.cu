@@ -188,6 +188,9 @@ struct qb_batch {
     uint32_t last_logit_rows = 0;
     int gemm_impl = 0;
     double *samp_u = nullptr;              // [2][logit_rows]: acceptance draws, then residual draws (sampling mode)
+    uint32_t *seen = nullptr;              // [n_seqs][seen_words] bitmap of prompt + emitted tokens (token penalties), or null
+    uint32_t seen_words = 0;
+    float pen_presence = 0.0f, pen_repetition = 1.0f;
 };
 
 static int alloc_qbuf(QBuf &b, uint32_t rows, uint32_t K) {
@@ -324,7 +327,7 @@ extern "C" void qb_batch_destroy(qb_ctx *ctx, qb_batch *b) {
     for (auto p : b->conv_alt) if (p) cudaFree(p);
     void *ptrs[] = {b->page_table, b->ctl, b->stats, b->hid, b->mtp_h, b->embd, b->act, b->parts,
                     b->logits, b->am_val, b->am_idx, b->att_acc, b->att_ml, b->xq_h.q, b->xq_h.d, b->xq_attn.q,
-                    b->xq_attn.d, b->xq_dn.q, b->xq_dn.d, b->xq_ffn.q, b->xq_ffn.d, b->xq_cat.q, b->xq_cat.d, b->samp_u};
+                    b->xq_attn.d, b->xq_dn.q, b->xq_dn.d, b->xq_ffn.q, b->xq_ffn.d, b->xq_cat.q, b->xq_cat.d, b->samp_u, b->seen};
     for (void *p : ptrs) if (p) cudaFree(p);
     if (b->out_rec_host) cudaFreeHost(b->out_rec_host);
     delete b;
@@ -464,6 +467,26 @@ __global__ void greedy_commit_kernel(const float *pval, const int32_t *pidx, uin
     const float *src = hid + (size_t)(hid_row0 + j * hid_row_stride) * H;
     float *dst = hid + (size_t)(rows_cap + s) * H;
     for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+}
+
+// Token-penalty bookkeeping (the `seen` map of the reference's generate loops, src/qwen_native_backend.cpp:15396, 15712):
+// bits of the prompt tokens of a chunk, and of the tokens the last commit emitted.
+__global__ void mark_seen_tokens_kernel(const int32_t *toks, uint32_t n, uint32_t *seen_row, uint32_t V) {
+    QB_PDL_ENTER();
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && (uint32_t)toks[i] < V) atomicOr(seen_row + ((uint32_t)toks[i] >> 5), 1u << (toks[i] & 31));
+}
+__global__ void mark_seen_record_kernel(const int32_t *out_rec, uint32_t n_seqs, uint32_t K1, uint32_t seq0, uint32_t ns, uint32_t *seen,
+                                        uint32_t words, uint32_t V) {
+    QB_PDL_ENTER();
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= ns * K1) return;
+    const uint32_t s = seq0 + idx / K1, i = idx % K1;
+    const int32_t *n_out = out_rec, *toks = out_rec + n_seqs;
+    if ((int)i < n_out[s]) {
+        const uint32_t t = (uint32_t)toks[(size_t)s * K1 + i];
+        if (t < V) atomicOr(seen + (size_t)s * words + (t >> 5), 1u << (t & 31));
+    }
 }
 
 __global__ void advance_kernel(int32_t *pos, int32_t *sel, uint32_t s, int32_t adv, uint32_t rows_cap, uint32_t H, uint32_t last_row, float *hid) {
@@ -671,6 +694,31 @@ static uint32_t max_host_pos(const qb_batch *b) {
     return (uint32_t)mx;
 }
 
+static int mark_seen_record(qb_ctx *ctx, qb_batch *b, uint32_t seq0, uint32_t ns) {
+    if (!b->seen) return QB_OK;
+    const uint32_t K1 = b->k + 1;
+    QB_CUDA(qb_launch_pdl(ctx->stream, mark_seen_record_kernel, dim3((ns * K1 + 127) / 128), dim3(128), (size_t)0, b->out_rec, b->n_seqs, K1, seq0, ns,
+                          b->seen, b->seen_words, b->m->cfg.vocab_size));
+    QB_LAUNCHED(ctx, "mark_seen_record_kernel");
+    return QB_OK;
+}
+
+// Token penalties of sampling requests (presence_penalty / repetition_penalty of the reference's sampler): from this call on
+// the batch records the prompt and emitted tokens of every sequence, and qb_mtp_sample_rows penalises their logits.  Call
+// before the prefill of the requests it should cover.  presence = 0 and repetition = 1 switch the penalties off again.
+extern "C" int qb_batch_set_penalties(qb_ctx *ctx, qb_batch *b, float presence, float repetition) {
+    QB_REQUIRE(ctx && b, "qb_batch_set_penalties: null argument");
+    QB_CUDA(cudaSetDevice(ctx->device));
+    if (!b->seen) {
+        b->seen_words = (b->m->cfg.vocab_size + 31) / 32;
+        QB_CUDA(cudaMalloc(&b->seen, (size_t)b->n_seqs * b->seen_words * sizeof(uint32_t)));
+        QB_CUDA(cudaMemsetAsync(b->seen, 0, (size_t)b->n_seqs * b->seen_words * sizeof(uint32_t), ctx->stream));
+    }
+    b->pen_presence = presence;
+    b->pen_repetition = repetition;
+    return QB_OK;
+}
+
 extern "C" int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n) {
     QB_REQUIRE(ctx && b && tokens_host && n > 0 && seq < b->n_seqs, "qb_prefill: bad arguments");
     QB_REQUIRE((uint32_t)b->host_pos[seq] + n + b->k + 1 <= b->max_ctx + b->k + 1 && (uint32_t)b->host_pos[seq] + n <= b->max_ctx,
@@ -684,6 +732,11 @@ extern "C" int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t 
         const bool last = off + M == n;
         const uint32_t p0 = (uint32_t)b->host_pos[seq];
         QB_CUDA(cudaMemcpyAsync(b->tok_buf, tokens_host + off, M * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        if (b->seen) {
+            QB_CUDA(qb_launch_pdl(ctx->stream, mark_seen_tokens_kernel, dim3((M + 127) / 128), dim3(128), (size_t)0, b->tok_buf, M,
+                                  b->seen + (size_t)seq * b->seen_words, c.vocab_size));
+            QB_LAUNCHED(ctx, "mark_seen_tokens_kernel");
+        }
         RowSet rs;
         rs.seq0 = seq; rs.ns = 1; rs.R = M; rs.seq_pos = b->pos + seq; rs.max_pos = p0 + M;
         QB_TRY(target_forward(ctx, b, b->tok_buf, rs, false, last ? 2 : 0));
@@ -700,6 +753,7 @@ extern "C" int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t 
                                                            b->pos, b->sel, b->cur, (int32_t)M, b->out_rec, b->n_seqs, b->hid,
                                                            (unsigned long long *)b->stats));
             QB_LAUNCHED(ctx, "greedy_commit_kernel");
+            QB_TRY(mark_seen_record(ctx, b, seq, 1));
         } else {
             QB_CUDA(qb_launch_pdl(ctx->stream, advance_kernel, dim3(1), dim3(256), (size_t)(0), b->pos, b->sel, seq, (int32_t)M, b->rows_cap, c.n_embd, M - 1, b->hid));
             QB_LAUNCHED(ctx, "advance_kernel");
@@ -730,6 +784,7 @@ extern "C" int qb_decode_greedy_step(qb_ctx *ctx, qb_batch *b) {
                                                            c.n_embd, b->pos, b->sel, b->cur, 1, b->out_rec, b->n_seqs, b->hid,
                                                            (unsigned long long *)b->stats));
     QB_LAUNCHED(ctx, "greedy_commit_kernel");
+    QB_TRY(mark_seen_record(ctx, b, 0, b->n_seqs));
     for (auto &p : b->host_pos) p += 1;
     return QB_OK;
 }
@@ -789,6 +844,7 @@ extern "C" int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b) {
                                                     b->prefix_pos, b->prefix_tok, b->out_rec, ns, b->hid,
                                                     (unsigned long long *)b->stats));
     QB_LAUNCHED(ctx, "accept_commit_kernel");
+    QB_TRY(mark_seen_record(ctx, b, 0, ns));
     // MTP-layer K/V of positions old_pos+1 .. old_pos+k from (draft_i, target hidden of row i-1); the
     // rows beyond the accepted prefix land past the committed length and are overwritten later.
     RowSet rs;
@@ -819,7 +875,8 @@ extern "C" int qb_mtp_sample_rows(qb_ctx *ctx, qb_batch *b, float temp, float to
     QB_CUDA(cudaStreamSynchronize(ctx->stream));       // the vector goes out of scope
     const qb_model_config &c = b->m->cfg;
     return qb_launch_sample_rows(ctx, b->logits, rows, c.vocab_size, c.vocab_size, b->drafts, K1, b->samp_u, b->samp_u + rows, temp, top_p,
-                                 top_k, min_p, nullptr, nullptr, nullptr, b->am_val, b->am_idx, QB_ARGMAX_BLOCKS);
+                                 top_k, min_p, nullptr, nullptr, nullptr, b->am_val, b->am_idx, QB_ARGMAX_BLOCKS, b->pen_presence, b->pen_repetition,
+                                 b->seen, b->seen_words);
 }
 
 extern "C" int qb_mtp_step_sampled(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host) {
@@ -877,6 +934,7 @@ extern "C" int qb_seq_reset(qb_ctx *ctx, qb_batch *b, uint32_t seq) {
     }
     for (int32_t *p : {b->pos, b->sel, b->cur, b->prefix_pos}) QB_CUDA(cudaMemsetAsync(p + seq, 0, sizeof(int32_t), ctx->stream));
     QB_CUDA(cudaMemsetAsync(b->hid + (size_t)(b->rows_cap + seq) * c.n_embd, 0, (size_t)c.n_embd * sizeof(float), ctx->stream));
+    if (b->seen) QB_CUDA(cudaMemsetAsync(b->seen + (size_t)seq * b->seen_words, 0, (size_t)b->seen_words * sizeof(uint32_t), ctx->stream));
     b->host_pos[seq] = 0;
     return QB_OK;
 }

@@ -28,6 +28,9 @@ constexpr int NB = 4;                         // histogram bins per pass (two ke
 struct SampleParams {
     float inv_t, top_p, min_p;
     int top_k;
+    float presence, repetition;               // token penalties (0 / 1 = off)
+    const uint32_t *seen;                     // bitmap [sequence][seen_words] of the tokens a request has seen, or null
+    uint32_t seen_words;
 };
 
 __device__ __forceinline__ uint32_t okey(float f) {      // ascending key order == ascending float order
@@ -166,9 +169,22 @@ sample_rows_kernel(const float *__restrict__ logits, uint32_t V, uint32_t stride
     const uint32_t VC = (V + CL - 1) / CL, s0 = min(V, c.crank * VC), s1 = min(V, s0 + VC);
     const uint32_t ept = (VC + ST - 1) / ST, g0 = s0 + tid * ept;
     const int nv = g0 >= s1 ? 0 : (int)min(ept, s1 - g0);
+    // token penalties (apply_token_penalties, src/qwen_native_backend.cpp:262-280) against the request's seen tokens and
+    // the drafts of the earlier rows of this step (the running prefix of the accept loop, :432-447)
+    const uint32_t seq = K1 ? row / K1 : row, n_prior = K1 ? row % K1 : 0;
+    const bool pen_rep = p.repetition > 0.0f && p.repetition != 1.0f, pen_pres = p.presence != 0.0f;
+    auto penalised = [&](uint32_t idx, float v) -> float {
+        if (!(pen_rep || pen_pres)) return v;
+        bool sn = p.seen && ((p.seen[(size_t)seq * p.seen_words + (idx >> 5)] >> (idx & 31)) & 1u);
+        for (uint32_t q = 0; q < n_prior && !sn; ++q) sn = draft && (uint32_t)draft[(size_t)seq * (K1 - 1) + q] == idx;
+        if (!sn) return v;
+        if (pen_rep) v = v >= 0.0f ? v / p.repetition : v * p.repetition;
+        if (pen_pres) v -= p.presence;
+        return v;
+    };
     float l[EPT];
 #pragma unroll
-    for (int j = 0; j < EPT; ++j) l[j] = j < nv ? x[g0 + j] : -INFINITY;
+    for (int j = 0; j < EPT; ++j) l[j] = j < nv ? penalised(g0 + j, x[g0 + j]) : -INFINITY;
 
     // largest logit and its lowest index in one exchange: max of (key, ~index) as one integer
     float mx;
@@ -304,7 +320,7 @@ sample_rows_kernel(const float *__restrict__ logits, uint32_t V, uint32_t stride
     int acc = 0;
     float pd = 0.0f;
     if (has_d) {
-        pd = out_of((uint32_t)d, x[d], d_rank);
+        pd = out_of((uint32_t)d, penalised((uint32_t)d, x[d]), d_rank);
         acc = u_acc[row] < (double)pd ? 1 : 0;
     }
     int tok = d;
@@ -379,11 +395,12 @@ sample_rows_kernel(const float *__restrict__ logits, uint32_t V, uint32_t stride
 int qb_launch_sample_rows(qb_ctx *ctx, const float *logits, uint32_t rows, uint32_t V, uint32_t stride, const int32_t *draft,
                           uint32_t K1, const double *u_acc, const double *u_res, float temp, float top_p, int32_t top_k,
                           float min_p, int32_t *token, int32_t *accepted, float *p_draft, float *pval, int32_t *pidx,
-                          uint32_t nblk) {
+                          uint32_t nblk, float presence, float repetition, const uint32_t *seen, uint32_t seen_words) {
     QB_REQUIRE(temp > 0.0f, "sampling needs temp > 0 (temp <= 0 is the argmax path)");
     QB_REQUIRE(rows > 0 && V > 0 && u_res != nullptr, "qb_launch_sample_rows: bad arguments");
     SampleParams p;
     p.inv_t = 1.0f / temp; p.top_p = top_p; p.min_p = min_p; p.top_k = top_k;
+    p.presence = presence; p.repetition = repetition; p.seen = seen; p.seen_words = seen_words;
     QB_REQUIRE(V <= (uint32_t)(CL * ST * EPT), "sampling: rows of %u logits exceed the kernel's %d", V, CL * ST * EPT);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(rows * CL);
@@ -411,5 +428,5 @@ extern "C" int qb_sample_rows(qb_ctx *ctx, const float *logits_dev, uint32_t row
     QB_REQUIRE(draft_dev == nullptr || u_acc_dev != nullptr, "qb_sample_rows: drafts need acceptance draws");
     QB_CUDA(cudaSetDevice(ctx->device));
     return qb_launch_sample_rows(ctx, logits_dev, rows, V, stride, draft_dev, 0, u_acc_dev, u_res_dev, temp, top_p, top_k, min_p,
-                                 token_dev, accepted_dev, p_draft_dev, nullptr, nullptr, 0);
+                                 token_dev, accepted_dev, p_draft_dev, nullptr, nullptr, 0, 0.0f, 1.0f, nullptr, 0);
 }

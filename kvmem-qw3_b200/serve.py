@@ -83,7 +83,8 @@ class DrawQueue:
 def run(engine, requests, speculative=True, max_steps=1 << 30, sampling=None, rng_of=None):
     """Serve `requests` (a list of Request) to completion; returns them in completion order.
     One loop iteration = admissions (a prefill each) + one decode step of the whole batch.
-    sampling: None (greedy) or dict(temp=, top_p=, top_k=, min_p=) for engine.mtp_step_sampled; rng_of(request) gives the
+    sampling: None (greedy) or dict(temp=, top_p=, top_k=, min_p=[, presence=, repetition=]) for engine.mtp_step_sampled (the
+    penalties go to engine.set_penalties); rng_of(request) gives the
     request's generator (anything with .random() -> float in [0, 1))."""
     sched = SlotScheduler(engine.n_seqs)
     for r in sorted(requests, key=lambda r: (r.arrival_step, r.rid)):
@@ -93,6 +94,11 @@ def run(engine, requests, speculative=True, max_steps=1 << 30, sampling=None, rn
     if sampling is not None and not speculative:
         raise ValueError("sampled decode runs through the speculative step")
     draws = {}                                           # slot -> DrawQueue of the request it holds
+    if sampling is not None:
+        sampling = dict(sampling)
+        presence, repetition = sampling.pop("presence", 0.0), sampling.pop("repetition", 1.0)
+        if presence != 0.0 or repetition != 1.0:
+            engine.set_penalties(presence, repetition)   # before any prefill: the prompts count as seen tokens
     finished, step = [], 0
     while not sched.idle() and step < max_steps:
         for req in sched.admissible(step):

@@ -124,3 +124,70 @@ def test_sampled_step_matches_the_reference_accept_loop(qb, orc, ctx, model, tem
     if top_k == 0:
         assert n_acc > 0          # untruncated: every draft has some mass, and u = 0 accepts it
     b.close()
+
+
+def test_token_penalties_follow_the_running_prefix(qb, orc, ctx, model):
+    """presence / repetition penalties: row i of a step is penalised on the request's prompt and emitted tokens plus the
+    step's drafts 0..i-1 (apply_token_penalties against the running prefix of the accept loop)."""
+    V, k, ns = model.cfg.vocab_size, 3, 2
+    pres, rep = 0.7, 1.3
+    temp, top_p, top_k = 0.8, 0.95, 0
+    b = qb.Batch(model, ns, 256, k)
+    b.set_penalties(pres, rep)
+    seen = []
+    for s in range(ns):
+        prompt = orc.synth_prompt(90 + s, V, 25 + 9 * s)
+        b.prefill(s, prompt)
+        seen.append(set(int(t) for t in prompt) | set(b.read_output()[s]))
+    rng = np.random.default_rng(4)
+
+    def penalise(row, toks):
+        row = row.copy()
+        idx = np.array(sorted(toks), np.int64)
+        v = row[idx]
+        v = np.where(v >= 0, v / np.float32(rep), v * np.float32(rep)).astype(np.float32) - np.float32(pres)
+        row[idx] = v
+        return row
+
+    changed = 0
+    for step in range(10):
+        u = rng.random((ns, k + 1))
+        if step % 2 == 0:
+            u[:, 0] = 0.0
+        b.mtp_draft()
+        b.mtp_verify()
+        logits = b.last_logits(ns * (k + 1)).reshape(ns, k + 1, V).copy()
+        drafts = b.last_drafts()
+        b.mtp_sample_rows(u, temp, top_p, top_k)
+        b.mtp_accept_commit()
+        out = b.read_output()
+        for s in range(ns):
+            want, ctxset = [], set(seen[s])
+            for i in range(k + 1):
+                d = int(drafts[s, i]) if i < k else -1
+                row = penalise(logits[s, i], ctxset)
+                ui = min(i + 1, k)
+                tok, acc, _ = orc.sample_rows(row[None], np.array([d], np.int32), u[s, i:i + 1], u[s, ui:ui + 1], temp, top_p, top_k, 0.0)
+                plain, _, _ = orc.sample_rows(logits[s, i][None], np.array([d], np.int32), u[s, i:i + 1], u[s, ui:ui + 1], temp, top_p, top_k, 0.0)
+                changed += int(plain[0] != tok[0])
+                want.append(int(tok[0]))
+                if d < 0 or not acc[0]:
+                    break
+                ctxset.add(d)
+            assert out[s] == want, (step, s, out[s], want)
+            seen[s] |= set(out[s])
+    assert changed > 0            # the penalties did change decisions in this run
+    # a recycled slot starts with an empty record
+    b.reset(0)
+    p2 = orc.synth_prompt(95, V, 11)
+    b.prefill(0, p2)
+    seen0 = set(int(t) for t in p2) | set(b.read_output()[0])
+    u = rng.random((ns, k + 1))
+    b.mtp_draft(); b.mtp_verify()
+    logits = b.last_logits(ns * (k + 1)).reshape(ns, k + 1, V).copy()
+    drafts = b.last_drafts()
+    b.mtp_sample_rows(u, temp, top_p, top_k); b.mtp_accept_commit()
+    d = int(drafts[0, 0])
+    tok, acc, _ = orc.sample_rows(penalise(logits[0, 0], seen0)[None], np.array([d], np.int32), u[0, 0:1], u[0, 1:2], temp, top_p, top_k, 0.0)
+    assert b.read_output()[0][0] == int(tok[0])
+    b.close()
