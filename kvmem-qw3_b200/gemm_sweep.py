@@ -14,6 +14,8 @@ into the down GEMM's epilogue) with the FFN dimension split over the ranks of th
         kvmem-qw3_b200/gemm_sweep.py --tp [--rows 4,16,64,128,512]
 
 One JSON line per M on rank 0: the time is the max over ranks of the CUDA-event time of one FFN (cold L2).
+With --nccl-baseline every M is also timed in the unfused form: the same two GEMMs on the rank's shard, its own
+sum over the K segments, then torch.distributed.all_reduce (NCCL) of the [M, 5120] result on the same stream.
 """
 import argparse
 import ctypes as C
@@ -50,9 +52,42 @@ def tp_sweep(args):
         group, opened = groups[0], []
     rng = np.random.default_rng(5)
     e0, e1 = ctx.event(), ctx.event()
+    nccl = None
+    if args.nccl_baseline and dist is not None:
+        import torch
+        nccl = dist.new_group(backend="nccl")
+        ext = torch.cuda.ExternalStream(int(pkg.lib().qb_stream(ctx.h)))
+        solo_groups, solo_area = pkg.tp.local_groups(ctx, 1, max(Ms), H, f, H)      # the rank's shard alone: GEMMs + own sum
+
+        class Raw:                                  # a device buffer of the library as a torch tensor (no copy)
+            def __init__(self, arr):
+                self.__cuda_array_interface__ = {"shape": arr.shape, "typestr": "<f4", "data": (int(arr.ptr.value), False), "version": 2}
     for M in Ms:
         x = ctx.array(rng.standard_normal((M, H)).astype(np.float32))
         y = ctx.empty((M, H), np.float32)
+        base_us = None
+        if nccl is not None:
+            import torch
+            yb = ctx.empty((M, H), np.float32)
+            yt = torch.as_tensor(Raw(yb), device="cuda:%d" % local)
+            bt = []
+            with torch.cuda.stream(ext):
+                for it in range(args.iters + 3):
+                    if not args.no_flush:
+                        ctx.flush_l2()
+                    ctx.sync()
+                    dist.barrier()
+                    ctx.record(e0)
+                    solo_groups[0].ffn(w_gu, w_dn, x, M, yb)
+                    dist.all_reduce(yt, group=nccl)
+                    ctx.record(e1)
+                    ctx.sync()
+                    torch.cuda.synchronize()
+                    if it >= 3:
+                        bt.append(ctx.elapsed_ms(e0, e1))
+            t = torch.tensor([float(np.median(bt)) * 1e3], dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            base_us = float(t[0])
         times = []
         for it in range(args.iters + 3):
             if not args.no_flush:
@@ -76,11 +111,14 @@ def tp_sweep(args):
             wbytes = (2 * f * H + H * f) / 32 * 34
             print(json.dumps({"tp": world, "M": M, "ffn_us": round(us, 2), "weight_MB_per_rank": round(wbytes / 1e6, 1),
                               "GBps_per_rank": round(wbytes / us / 1e3, 1), "allreduce_bytes": M * H * 4,
+                              "unfused_gemms_plus_nccl_allreduce_us": None if base_us is None else round(base_us, 2),
                               "TOPs_total": round(2.0 * M * 3 * F * H / us / 1e6, 2)}), flush=True)
     ctx.sync()
     if dist is not None:
         dist.barrier()                  # nobody unmaps a receive area a peer may still write
     group.close()
+    if nccl is not None:
+        solo_groups[0].close()
     pkg.tp.ipc_release(ctx, opened)
     w_gu.free(); w_dn.free()
     if dist is not None:
@@ -98,6 +136,7 @@ def main():
     ap.add_argument("--ksplit", type=int, default=0)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--tp", action="store_true", help="tensor-parallel FFN pair over the ranks of this launch")
+    ap.add_argument("--nccl-baseline", action="store_true", help="with --tp: also time the unfused form (GEMMs, then an NCCL all-reduce)")
     args = ap.parse_args()
     if args.tp:
         return tp_sweep(args)
