@@ -300,6 +300,14 @@ int qb_seq_position(qb_ctx *ctx, qb_batch *b, uint32_t seq, int32_t *pos);
  * position 0 with zero DeltaNet / conv state, ready for qb_prefill of the next request.  The slot keeps its K/V pages.
  * The other sequences of the batch are untouched. */
 int qb_seq_reset(qb_ctx *ctx, qb_batch *b, uint32_t seq);
+/* The decode steps (greedy, draft, verify, sample, accept) run the sequences [0, n); the others keep their state untouched
+ * and may be prefilled meanwhile.  A continuous-batching loop keeps its live requests in the first slots: empty slots and
+ * requests still being ingested then cost nothing (the reference's worker loop likewise decodes its `active` list only,
+ * src/qwen_native_backend.cpp:6711-6866).  A new batch has n = n_seqs. */
+int qb_batch_set_active(qb_ctx *ctx, qb_batch *b, uint32_t n);
+/* Exchange the contents of two sequence slots (page-table rows, DeltaNet state and conv windows, position, current
+ * token, previous hidden row, seen-token record). */
+int qb_seq_swap(qb_ctx *ctx, qb_batch *b, uint32_t s1, uint32_t s2);
 /* Test aids: logits of the last verify/greedy/prefill rows (float [rows][vocab]) and hidden rows. */
 int qb_debug_last_logits(qb_ctx *ctx, qb_batch *b, float *host_out, uint32_t max_rows, uint32_t *rows_out);
 /* Drafts of the last qb_mtp_draft / qb_mtp_force_drafts: int32 [n_seqs][k] (test aid, syncs). */

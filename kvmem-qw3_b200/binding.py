@@ -86,6 +86,8 @@ SIGNATURES = {
     "qb_batch_stats": (i32, [vp, vp, vp]),
     "qb_seq_position": (i32, [vp, vp, u32, C.POINTER(C.c_int32)]),
     "qb_seq_reset": (i32, [vp, vp, u32]),
+    "qb_batch_set_active": (i32, [vp, vp, u32]),
+    "qb_seq_swap": (i32, [vp, vp, u32, u32]),
     "qb_batch_set_penalties": (i32, [vp, vp, C.c_float, C.c_float]),
     "qb_sample_rows": (i32, [vp, vp, u32, u32, u32, vp, vp, vp, C.c_float, C.c_float, i32, C.c_float, vp, vp, vp]),
     "qb_mtp_sample_rows": (i32, [vp, vp, C.c_float, C.c_float, i32, C.c_float, vp]),
@@ -394,6 +396,7 @@ class Batch:
 
     def __init__(self, model, n_seqs, max_ctx, k, page_size=16, page_order=0):
         self.ctx, self.model, self.n_seqs, self.k, self.max_ctx = model.ctx, model, n_seqs, k, max_ctx
+        self.n_active = n_seqs
         h = vp()
         check(lib().qb_batch_create(self.ctx.h, model.h, n_seqs, max_ctx, k, page_size, page_order, C.byref(h)))
         self.h = h
@@ -457,6 +460,14 @@ class Batch:
     def reset(self, seq):
         """Retire the request in slot `seq`: position 0, zero recurrent state; prefill admits the next one."""
         check(lib().qb_seq_reset(self.ctx.h, self.h, seq))
+
+    def set_active(self, n):
+        """The decode steps run the sequences [0, n)."""
+        check(lib().qb_batch_set_active(self.ctx.h, self.h, n))
+        self.n_active = n
+
+    def swap(self, s1, s2):
+        check(lib().qb_seq_swap(self.ctx.h, self.h, s1, s2))
 
     def position(self, seq):
         p = C.c_int32()

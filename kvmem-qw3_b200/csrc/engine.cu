@@ -164,6 +164,7 @@ struct QBuf {   // quantised activation buffer for one K
 struct qb_batch {
     qb_model *m = nullptr;
     uint32_t n_seqs = 0, max_ctx = 0, k = 0, page_size = 0, pages_per_seq = 0, rows_cap = 0, chunk = 0, logit_rows = 0;
+    uint32_t n_active = 0;                 // the decode steps run sequences [0, n_active); the rest keep their state untouched
     std::vector<__half *> kc, vc;          // per layer (attention layers only), + MTP layer at index n_layers
     std::vector<float *> state, conv;      // per layer (recurrent layers only): [n_seqs][k+1][...]
     std::vector<float *> conv_alt;         // second conv-state buffer: a forward reads one and writes the other
@@ -191,6 +192,8 @@ struct qb_batch {
     uint32_t *seen = nullptr;              // [n_seqs][seen_words] bitmap of prompt + emitted tokens (token penalties), or null
     uint32_t seen_words = 0;
     float pen_presence = 0.0f, pen_repetition = 1.0f;
+    void *swap_tmp = nullptr;              // one sequence's largest per-layer state block (qb_seq_swap)
+    size_t swap_bytes = 0;
 };
 
 static int alloc_qbuf(QBuf &b, uint32_t rows, uint32_t K) {
@@ -213,7 +216,7 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
     QB_CUDA(cudaSetDevice(ctx->device));
     const qb_model_config &c = m->cfg;
     qb_batch *b = new qb_batch();
-    b->m = m; b->n_seqs = n_seqs; b->max_ctx = max_ctx; b->k = draft_k; b->page_size = page_size;
+    b->m = m; b->n_seqs = n_seqs; b->n_active = n_seqs; b->max_ctx = max_ctx; b->k = draft_k; b->page_size = page_size;
     b->pages_per_seq = (max_ctx + draft_k + 1 + page_size - 1) / page_size;
     b->chunk = std::max(1u, env_u32("QW3B200_PREFILL_CHUNK", 128));
     b->logit_rows = n_seqs * (draft_k + 1);
@@ -327,7 +330,7 @@ extern "C" void qb_batch_destroy(qb_ctx *ctx, qb_batch *b) {
     for (auto p : b->conv_alt) if (p) cudaFree(p);
     void *ptrs[] = {b->page_table, b->ctl, b->stats, b->hid, b->mtp_h, b->embd, b->act, b->parts,
                     b->logits, b->am_val, b->am_idx, b->att_acc, b->att_ml, b->xq_h.q, b->xq_h.d, b->xq_attn.q,
-                    b->xq_attn.d, b->xq_dn.q, b->xq_dn.d, b->xq_ffn.q, b->xq_ffn.d, b->xq_cat.q, b->xq_cat.d, b->samp_u, b->seen};
+                    b->xq_attn.d, b->xq_dn.q, b->xq_dn.d, b->xq_ffn.q, b->xq_ffn.d, b->xq_cat.q, b->xq_cat.d, b->samp_u, b->seen, b->swap_tmp};
     for (void *p : ptrs) if (p) cudaFree(p);
     if (b->out_rec_host) cudaFreeHost(b->out_rec_host);
     delete b;
@@ -486,6 +489,14 @@ __global__ void mark_seen_record_kernel(const int32_t *out_rec, uint32_t n_seqs,
     if ((int)i < n_out[s]) {
         const uint32_t t = (uint32_t)toks[(size_t)s * K1 + i];
         if (t < V) atomicOr(seen + (size_t)s * words + (t >> 5), 1u << (t & 31));
+    }
+}
+
+__global__ void swap_ctl_kernel(int32_t *pos, int32_t *sel, int32_t *cur, int32_t *prefix_pos, uint32_t a, uint32_t b) {
+    QB_PDL_ENTER();
+    if (threadIdx.x == 0) {
+        int32_t *arr[4] = {pos, sel, cur, prefix_pos};
+        for (int i = 0; i < 4; ++i) { const int32_t t = arr[i][a]; arr[i][a] = arr[i][b]; arr[i][b] = t; }
     }
 }
 
@@ -690,8 +701,11 @@ static int mtp_forward(qb_ctx *ctx, qb_batch *b, const int32_t *tokens_dev, cons
 
 static uint32_t max_host_pos(const qb_batch *b) {
     int32_t mx = 0;
-    for (int32_t p : b->host_pos) mx = std::max(mx, p);
+    for (uint32_t s = 0; s < b->n_active; ++s) mx = std::max(mx, b->host_pos[s]);
     return (uint32_t)mx;
+}
+static void advance_host_pos(qb_batch *b, int32_t by) {
+    for (uint32_t s = 0; s < b->n_active; ++s) b->host_pos[s] += by;
 }
 
 static int mark_seen_record(qb_ctx *ctx, qb_batch *b, uint32_t seq0, uint32_t ns) {
@@ -765,7 +779,8 @@ extern "C" int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t 
 }
 
 static int check_room(qb_batch *b, uint32_t need) {
-    for (uint32_t s = 0; s < b->n_seqs; ++s)
+    if (b->n_active == 0) return qb_fail(QB_ERR_INVALID, "no active sequence");
+    for (uint32_t s = 0; s < b->n_active; ++s)
         if ((uint32_t)b->host_pos[s] + need > b->max_ctx + b->k + 1 || (uint32_t)b->host_pos[s] >= b->max_ctx)
             return qb_fail(QB_ERR_CAPACITY, "sequence %u at position %d has no room for %u more positions (max_ctx %u)", s,
                            b->host_pos[s], need, b->max_ctx);
@@ -778,14 +793,14 @@ extern "C" int qb_decode_greedy_step(qb_ctx *ctx, qb_batch *b) {
     QB_CUDA(cudaSetDevice(ctx->device));
     const qb_model_config &c = b->m->cfg;
     RowSet rs;
-    rs.seq0 = 0; rs.ns = b->n_seqs; rs.R = 1; rs.seq_pos = b->pos; rs.max_pos = max_host_pos(b) + 1;
+    rs.seq0 = 0; rs.ns = b->n_active; rs.R = 1; rs.seq_pos = b->pos; rs.max_pos = max_host_pos(b) + 1;
     QB_TRY(target_forward(ctx, b, b->cur, rs, false, 1));
-    QB_CUDA(qb_launch_pdl(ctx->stream, greedy_commit_kernel, dim3(b->n_seqs), dim3(256), (size_t)(0), b->am_val, b->am_idx, 0, 0, 1, 0, b->n_seqs, b->k + 1, b->rows_cap,
+    QB_CUDA(qb_launch_pdl(ctx->stream, greedy_commit_kernel, dim3(b->n_active), dim3(256), (size_t)(0), b->am_val, b->am_idx, 0, 0, 1, 0, b->n_active, b->k + 1, b->rows_cap,
                                                            c.n_embd, b->pos, b->sel, b->cur, 1, b->out_rec, b->n_seqs, b->hid,
                                                            (unsigned long long *)b->stats));
     QB_LAUNCHED(ctx, "greedy_commit_kernel");
-    QB_TRY(mark_seen_record(ctx, b, 0, b->n_seqs));
-    for (auto &p : b->host_pos) p += 1;
+    QB_TRY(mark_seen_record(ctx, b, 0, b->n_active));
+    advance_host_pos(b, 1);
     return QB_OK;
 }
 
@@ -793,7 +808,7 @@ extern "C" int qb_mtp_draft(qb_ctx *ctx, qb_batch *b) {
     QB_REQUIRE(ctx && b && b->k > 0, "qb_mtp_draft: needs a batch with draft depth > 0");
     QB_TRY(check_room(b, b->k + 1));
     QB_CUDA(cudaSetDevice(ctx->device));
-    const uint32_t ns = b->n_seqs, k = b->k;
+    const uint32_t ns = b->n_active, k = b->k;
     for (uint32_t i = 0; i < k; ++i) {
         QB_CUDA(qb_launch_pdl(ctx->stream, prep_draft_kernel, dim3((ns + 127) / 128), dim3(128), (size_t)(0), b->cur, b->drafts, b->pos, ns, k, i, b->tok_buf, b->seqpos_buf));
         QB_LAUNCHED(ctx, "prep_draft_kernel");
@@ -810,8 +825,8 @@ extern "C" int qb_mtp_draft(qb_ctx *ctx, qb_batch *b) {
 
 extern "C" int qb_mtp_force_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *forced_dev, uint32_t stride) {
     QB_REQUIRE(ctx && b && forced_dev && b->k > 0, "qb_mtp_force_drafts: bad arguments");
-    const uint32_t n = b->n_seqs * b->k;
-    QB_CUDA(qb_launch_pdl(ctx->stream, force_drafts_kernel, dim3((n + 127) / 128), dim3(128), (size_t)0, b->drafts, b->pos, b->n_seqs,
+    const uint32_t n = b->n_active * b->k;
+    QB_CUDA(qb_launch_pdl(ctx->stream, force_drafts_kernel, dim3((n + 127) / 128), dim3(128), (size_t)0, b->drafts, b->pos, b->n_active,
                           b->k, forced_dev, stride));
     QB_LAUNCHED(ctx, "force_drafts_kernel");
     return QB_OK;
@@ -819,7 +834,7 @@ extern "C" int qb_mtp_force_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *forc
 
 extern "C" int qb_mtp_set_drafts(qb_ctx *ctx, qb_batch *b, const int32_t *drafts_host) {
     QB_REQUIRE(ctx && b && drafts_host && b->k > 0, "qb_mtp_set_drafts: bad arguments");
-    QB_CUDA(cudaMemcpyAsync(b->drafts, drafts_host, (size_t)b->n_seqs * b->k * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+    QB_CUDA(cudaMemcpyAsync(b->drafts, drafts_host, (size_t)b->n_active * b->k * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
     return QB_OK;
 }
 
@@ -827,7 +842,7 @@ extern "C" int qb_mtp_verify(qb_ctx *ctx, qb_batch *b) {
     QB_REQUIRE(ctx && b && b->k > 0, "qb_mtp_verify: needs a batch with draft depth > 0");
     QB_TRY(check_room(b, b->k + 1));
     QB_CUDA(cudaSetDevice(ctx->device));
-    const uint32_t ns = b->n_seqs, K1 = b->k + 1;
+    const uint32_t ns = b->n_active, K1 = b->k + 1;
     QB_CUDA(qb_launch_pdl(ctx->stream, prep_verify_kernel, dim3((ns * K1 + 127) / 128), dim3(128), (size_t)(0), b->cur, b->drafts, ns, b->k, b->tok_buf));
     QB_LAUNCHED(ctx, "prep_verify_kernel");
     RowSet rs;
@@ -839,9 +854,9 @@ extern "C" int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b) {
     QB_REQUIRE(ctx && b && b->k > 0, "qb_mtp_accept_commit: needs a batch with draft depth > 0");
     QB_CUDA(cudaSetDevice(ctx->device));
     const qb_model_config &c = b->m->cfg;
-    const uint32_t ns = b->n_seqs, k = b->k;
+    const uint32_t ns = b->n_active, k = b->k;
     QB_CUDA(qb_launch_pdl(ctx->stream, accept_commit_kernel, dim3(ns), dim3(256), (size_t)(0), b->am_val, b->am_idx, k, b->rows_cap, c.n_embd, b->pos, b->sel, b->cur, b->drafts,
-                                                    b->prefix_pos, b->prefix_tok, b->out_rec, ns, b->hid,
+                                                    b->prefix_pos, b->prefix_tok, b->out_rec, b->n_seqs, b->hid,
                                                     (unsigned long long *)b->stats));
     QB_LAUNCHED(ctx, "accept_commit_kernel");
     QB_TRY(mark_seen_record(ctx, b, 0, ns));
@@ -850,7 +865,7 @@ extern "C" int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b) {
     RowSet rs;
     rs.seq0 = 0; rs.ns = ns; rs.R = k; rs.seq_pos = b->prefix_pos; rs.max_pos = max_host_pos(b) + k + 1;
     QB_TRY(mtp_forward(ctx, b, b->prefix_tok, b->hid, b->map_prefix, rs, true));
-    for (auto &p : b->host_pos) p += (int32_t)(k + 1);   // upper bound until the host reads the step record
+    advance_host_pos(b, (int32_t)(k + 1));               // upper bound until the host reads the step record
     return QB_OK;
 }
 
@@ -863,8 +878,8 @@ extern "C" int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b) {
 extern "C" int qb_mtp_sample_rows(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host) {
     QB_REQUIRE(ctx && b && u_host && b->k > 0, "qb_mtp_sample_rows: needs draws and a batch with draft depth > 0");
     QB_CUDA(cudaSetDevice(ctx->device));
-    const uint32_t ns = b->n_seqs, k = b->k, K1 = k + 1, rows = ns * K1;
-    if (!b->samp_u) QB_CUDA(cudaMalloc(&b->samp_u, 2 * (size_t)rows * sizeof(double)));
+    const uint32_t ns = b->n_active, k = b->k, K1 = k + 1, rows = ns * K1;
+    if (!b->samp_u) QB_CUDA(cudaMalloc(&b->samp_u, 2 * (size_t)b->n_seqs * K1 * sizeof(double)));
     std::vector<double> u(2 * (size_t)rows, 0.0);
     for (uint32_t s = 0; s < ns; ++s)
         for (uint32_t i = 0; i < K1; ++i) {
@@ -936,6 +951,53 @@ extern "C" int qb_seq_reset(qb_ctx *ctx, qb_batch *b, uint32_t seq) {
     QB_CUDA(cudaMemsetAsync(b->hid + (size_t)(b->rows_cap + seq) * c.n_embd, 0, (size_t)c.n_embd * sizeof(float), ctx->stream));
     if (b->seen) QB_CUDA(cudaMemsetAsync(b->seen + (size_t)seq * b->seen_words, 0, (size_t)b->seen_words * sizeof(uint32_t), ctx->stream));
     b->host_pos[seq] = 0;
+    return QB_OK;
+}
+
+// The decode steps run the sequences [0, n): a continuous-batching loop keeps its live requests in the first slots
+// (qb_seq_swap moves one) so that empty slots and requests still being prefilled cost nothing.
+extern "C" int qb_batch_set_active(qb_ctx *ctx, qb_batch *b, uint32_t n) {
+    QB_REQUIRE(ctx && b && n <= b->n_seqs, "qb_batch_set_active: bad arguments");
+    b->n_active = n;
+    return QB_OK;
+}
+
+// Exchange everything two sequence slots hold: K/V pages (their page-table rows), DeltaNet state and conv windows of
+// every layer, position, selected checkpoint, current token, previous hidden row, seen-token record.
+extern "C" int qb_seq_swap(qb_ctx *ctx, qb_batch *b, uint32_t s1, uint32_t s2) {
+    QB_REQUIRE(ctx && b && s1 < b->n_seqs && s2 < b->n_seqs, "qb_seq_swap: bad arguments");
+    if (s1 == s2) return QB_OK;
+    QB_CUDA(cudaSetDevice(ctx->device));
+    const qb_model_config &c = b->m->cfg;
+    const uint32_t K1 = b->k + 1;
+    const size_t ssz = (size_t)K1 * c.ssm_num_v_heads * c.ssm_head_dim * c.ssm_head_dim * sizeof(float);
+    const size_t csz = (size_t)K1 * b->m->qkv_dim() * 3 * sizeof(float);
+    const size_t need = std::max({ssz, csz, (size_t)c.n_embd * sizeof(float), (size_t)b->pages_per_seq * sizeof(int32_t),
+                                  (size_t)b->seen_words * sizeof(uint32_t)});
+    if (b->swap_bytes < need) {
+        if (b->swap_tmp) { QB_CUDA(cudaStreamSynchronize(ctx->stream)); QB_CUDA(cudaFree(b->swap_tmp)); b->swap_tmp = nullptr; }
+        QB_CUDA(cudaMalloc(&b->swap_tmp, need));
+        b->swap_bytes = need;
+    }
+    auto swap_block = [&](void *base, size_t bytes) -> int {
+        char *a = (char *)base + (size_t)s1 * bytes, *d = (char *)base + (size_t)s2 * bytes;
+        QB_CUDA(cudaMemcpyAsync(b->swap_tmp, a, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        QB_CUDA(cudaMemcpyAsync(a, d, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        QB_CUDA(cudaMemcpyAsync(d, b->swap_tmp, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        return QB_OK;
+    };
+    for (uint32_t il = 0; il < c.n_layers; ++il) {
+        if (!b->state[il]) continue;
+        QB_TRY(swap_block(b->state[il], ssz));
+        QB_TRY(swap_block(b->conv[il], csz));
+        QB_TRY(swap_block(b->conv_alt[il], csz));
+    }
+    QB_TRY(swap_block(b->page_table, (size_t)b->pages_per_seq * sizeof(int32_t)));
+    QB_TRY(swap_block(b->hid + (size_t)b->rows_cap * c.n_embd, (size_t)c.n_embd * sizeof(float)));
+    if (b->seen) QB_TRY(swap_block(b->seen, (size_t)b->seen_words * sizeof(uint32_t)));
+    QB_CUDA(qb_launch_pdl(ctx->stream, swap_ctl_kernel, dim3(1), dim3(32), (size_t)0, b->pos, b->sel, b->cur, b->prefix_pos, s1, s2));
+    QB_LAUNCHED(ctx, "swap_ctl_kernel");
+    std::swap(b->host_pos[s1], b->host_pos[s2]);
     return QB_OK;
 }
 

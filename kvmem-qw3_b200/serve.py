@@ -80,6 +80,96 @@ class DrawQueue:
         del self.buf[:n]
 
 
+def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=None, rng_of=None, prefill_chunk=0):
+    """The loop for engines with set_active(n) and swap(s1, s2): live requests are kept in slots [0, n_live) and only those
+    are decoded; a retiring request's slot is filled by the last live one (swap), a new request is ingested in a slot
+    beyond the live range -- `prefill_chunk` tokens per iteration when that is set, so decoding goes on meanwhile -- and
+    swapped to the end of the live range when its prompt is in."""
+    pending = collections.deque(sorted(requests, key=lambda r: (r.arrival_step, r.rid)))
+    per_step = engine.k + 1 if speculative else 1
+    if sampling is not None:
+        if not speculative:
+            raise ValueError("sampled decode runs through the speculative step")
+        sampling = dict(sampling)
+        presence, repetition = sampling.pop("presence", 0.0), sampling.pop("repetition", 1.0)
+        if presence != 0.0 or repetition != 1.0:
+            engine.set_penalties(presence, repetition)
+    live = []                                            # live[s] = request in slot s
+    ingest = {}                                          # slot -> [request, tokens ingested]
+    draws = {}                                           # rid -> DrawQueue
+    finished, step = [], 0
+    engine.set_active(0)
+
+    def retire(s):
+        req = live[s]
+        req.finished_step = step
+        req._trim()
+        finished.append(req)
+        last = len(live) - 1
+        if s != last:
+            engine.swap(s, last)
+            live[s] = live[last]
+            live[s].slot = s
+        live.pop()
+        engine.set_active(len(live))
+
+    while (pending or live or ingest) and step < max_steps:
+        # admission: a free slot beyond the live range per arrived request
+        while pending and pending[0].arrival_step <= step and len(live) + len(ingest) < engine.n_seqs:
+            req = pending.popleft()
+            if len(req.prompt) + req.max_new_tokens + per_step > engine.max_ctx:
+                raise ValueError("request %r does not fit max_ctx %d" % (req.rid, engine.max_ctx))
+            slot = next(s for s in range(len(live), engine.n_seqs) if s not in ingest)
+            engine.reset(slot)
+            req.slot, req.admitted_step = slot, step
+            ingest[slot] = [req, 0]
+        # ingestion: one chunk per request and iteration (the whole prompt when prefill_chunk is 0)
+        for slot in sorted(ingest):
+            if slot not in ingest:                                 # moved by a swap earlier in this iteration
+                continue
+            req, done_n = ingest[slot]
+            n = len(req.prompt) - done_n if not prefill_chunk else min(prefill_chunk, len(req.prompt) - done_n)
+            engine.prefill(slot, req.prompt[done_n:done_n + n])
+            ingest[slot][1] = done_n + n
+            if ingest[slot][1] < len(req.prompt):
+                continue
+            req.tokens.extend(engine.read_output()[slot])          # the prefill's last row gives the first token
+            del ingest[slot]
+            target = len(live)
+            if slot != target:                                     # to the end of the live range
+                engine.swap(slot, target)
+                if target in ingest:
+                    ingest[slot] = ingest.pop(target)
+                    ingest[slot][0].slot = slot
+            req.slot = target
+            live.append(req)
+            engine.set_active(len(live))
+            if sampling is not None:
+                draws[req.rid] = DrawQueue(rng_of(req), per_step)
+            if req.done():
+                retire(target)
+        if not live:
+            step += 1
+            continue
+        if sampling is not None:
+            u = [draws[live[s].rid].peek() if s < len(live) else [0.5] * per_step for s in range(engine.n_seqs)]
+            engine.mtp_step_sampled(u, **sampling)
+        elif speculative:
+            engine.mtp_step()
+        else:
+            engine.greedy_step()
+        out = engine.read_output()
+        step += 1
+        for s in range(len(live) - 1, -1, -1):           # from the end: retiring swaps the last live request in
+            req = live[s]
+            req.tokens.extend(out[s])
+            if sampling is not None:
+                draws[req.rid].consume(len(out[s]))
+            if req.done():
+                retire(s)
+    return finished
+
+
 def run(engine, requests, speculative=True, max_steps=1 << 30, sampling=None, rng_of=None):
     """Serve `requests` (a list of Request) to completion; returns them in completion order.
     One loop iteration = admissions (a prefill each) + one decode step of the whole batch.

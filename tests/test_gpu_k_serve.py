@@ -95,3 +95,69 @@ def test_sampled_serving_reproduces_each_request_alone(qb, orc, ctx, model):
     b.close()
     for r in done:
         assert r.tokens == alone(qb, model, r.prompt, r.max_new_tokens, 1), r.rid
+
+
+def test_swap_and_active_prefix(qb, orc, ctx, model):
+    """Three requests in a 3-slot batch; after some steps slots 0 and 2 are exchanged and only the first two slots stay
+    active: the exchanged requests continue their own streams, the parked one resumes unchanged later."""
+    V = model.cfg.vocab_size
+    prompts = [orc.synth_prompt(500 + i, V, n) for i, n in enumerate([30, 12, 21])]
+    want = [alone(qb, model, p, 40, 1) for p in prompts]
+    b = qb.Batch(model, 3, 256, 1)
+    outs = []
+    for s, p in enumerate(prompts):
+        b.prefill(s, p)
+        outs.append(list(b.read_output()[s]))
+    for _ in range(5):
+        b.mtp_step()
+        for s, t in enumerate(b.read_output()):
+            outs[s] += t
+    b.swap(0, 2)
+    outs[0], outs[2] = outs[2], outs[0]
+    want[0], want[2] = want[2], want[0]
+    b.set_active(2)
+    for _ in range(6):
+        b.mtp_step()
+        o = b.read_output()
+        for s in range(2):
+            outs[s] += o[s]
+    parked = len(outs[2])
+    b.set_active(3)
+    while min(len(o) for o in outs) < 40:
+        b.mtp_step()
+        for s, t in enumerate(b.read_output()):
+            outs[s] += t
+    for s in range(3):
+        assert outs[s][:40] == want[s], s
+    assert parked < 40
+    b.close()
+
+
+@pytest.mark.parametrize("k,slots,chunk", [(1, 2, 0), (1, 3, 8), (0, 2, 5)])
+def test_compacting_loop_matches_solo_streams(qb, orc, ctx, model, k, slots, chunk):
+    V = model.cfg.vocab_size
+    spec = [(64, 12, 0), (17, 30, 0), (40, 9, 0), (5, 20, 3), (33, 14, 25), (8, 1, 26), (29, 11, 27)]
+    reqs = [qb.serve.Request(i, orc.synth_prompt(600 + i, V, n), new, arrival_step=a) for i, (n, new, a) in enumerate(spec)]
+    b = qb.Batch(model, slots, 256, k)
+    done = qb.serve.run_compact(b, reqs, speculative=k > 0, prefill_chunk=chunk)
+    b.close()
+    assert sorted(r.rid for r in done) == list(range(len(spec)))
+    for r in done:
+        assert r.tokens == alone(qb, model, r.prompt, r.max_new_tokens, k), r.rid
+
+
+def test_compacting_loop_sampled_with_penalties(qb, orc, ctx, model):
+    V = model.cfg.vocab_size
+    samp = dict(temp=0.9, top_p=0.95, top_k=40, min_p=0.0, presence=0.5, repetition=1.2)
+    spec = [(30, 14, 0), (12, 20, 0), (21, 10, 2), (9, 16, 5)]
+    mk = lambda: [qb.serve.Request(i, orc.synth_prompt(700 + i, V, n), new, arrival_step=a) for i, (n, new, a) in enumerate(spec)]
+    rng_of = lambda r: np.random.default_rng(2000 + r.rid)
+    b = qb.Batch(model, 2, 256, 1)
+    together = {r.rid: r.tokens for r in qb.serve.run_compact(b, mk(), sampling=samp, rng_of=rng_of, prefill_chunk=7)}
+    b.close()
+    for req in mk():
+        b1 = qb.Batch(model, 1, 256, 1)
+        req.arrival_step = 0
+        solo = qb.serve.run_compact(b1, [req], sampling=samp, rng_of=rng_of)[0].tokens
+        b1.close()
+        assert together[req.rid] == solo, req.rid

@@ -8,7 +8,8 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 PARAMS = [(1.0, 1.0, 0, 0.0), (0.7, 0.9, 0, 0.0), (0.5, 1.0, 5, 0.0), (1.3, 0.8, 50, 0.05), (0.2, 0.0, 0, 0.3), (1.0, 0.5, 1, 0.0),
-          (0.05, 0.95, 40, 0.0), (2.0, 0.999, 0, 0.0)]
+          (0.05, 0.95, 40, 0.0), (2.0, 0.999, 0, 0.0),
+          (1.0, 1e-6, 0, 0.0), (1.0, 1.0, 0, 1.5), (1.0, 1.0, 10**9, 0.0), (1.0, 0.3, 3, 0.9)]      # one-token nucleus, min_p above 1 (collapses to the top token), top_k beyond the vocabulary
 
 
 def gpu_sample(qb, ctx, x, draft, ua, ur, temp, top_p, top_k, min_p):

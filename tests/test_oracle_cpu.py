@@ -249,7 +249,7 @@ def _np_distribution(l, temp, top_p, top_k, min_p):
 
 
 @pytest.mark.parametrize("temp,top_p,top_k,min_p", [(1.0, 1.0, 0, 0.0), (0.7, 0.9, 0, 0.0), (0.5, 1.0, 5, 0.0), (1.3, 0.8, 50, 0.05),
-                                                     (0.2, 0.0, 0, 0.3), (1.0, 0.5, 1, 0.0)])
+                                                     (0.2, 0.0, 0, 0.3), (1.0, 0.5, 1, 0.0), (1.0, 1e-6, 0, 0.0), (1.0, 1.0, 10**9, 0.0)])
 def test_sampling_acceptance_oracle(orc, temp, top_p, top_k, min_p):
     """The oracle's sampling-mode acceptance against an independent numpy statement: p[draft], the accept decision, and the
     inverse-CDF draw over the nonzero entries in index order."""

@@ -158,3 +158,88 @@ def test_sampled_serving_hands_each_request_its_draws_in_order():
     for s, base in ((0, 0), (1, 100)):
         got = [round(v * 1000) for v in used[s]]
         assert len(got) >= budget[s] - 1 and got == list(range(base + 1, base + 1 + len(got)))
+
+
+class CompactEngine(FakeEngine):
+    """FakeEngine with the active-prefix count, slot swap and appending prefill of binding.Batch."""
+
+    def __init__(self, *a):
+        super().__init__(*a)
+        self.n_active = self.n_seqs
+        self.stepped = 0                                  # sequence-steps actually computed
+
+    def set_active(self, n):
+        assert 0 <= n <= self.n_seqs
+        self.n_active = n
+
+    def swap(self, a, b):
+        for arr in (self.prompt, self.emitted, self.pos, self.out):
+            arr[a], arr[b] = arr[b], arr[a]
+
+    def prefill(self, s, tokens):
+        assert s >= self.n_active, "prefill into a slot the decode steps are running"
+        self.prompt[s] = (self.prompt[s] or []) + list(tokens)
+        self.pos[s] += len(tokens)
+        self.out[s] = stream(self.prompt[s], 1)
+        self.emitted[s] = 1
+
+    def _step(self, width):
+        self.steps += 1
+        for s in range(self.n_active):
+            assert self.prompt[s] is not None, "an empty slot inside the active range"
+            n = 1 + (self.steps + s) % width
+            assert self.pos[s] < self.max_ctx
+            self.pos[s] += n
+            full = stream(self.prompt[s], self.emitted[s] + n)
+            self.out[s] = full[self.emitted[s]:]
+            self.emitted[s] += n
+            self.stepped += 1
+
+
+import pytest as _pytest
+
+
+@_pytest.mark.parametrize("chunk", [0, 3])
+def test_compacting_loop_keeps_live_requests_in_the_first_slots(chunk):
+    serve = entry.load_package().serve
+    eng = CompactEngine(3, 3, 512)
+    spec = [(5, 9, 0), (11, 30, 0), (2, 4, 0), (7, 12, 1), (9, 6, 2), (4, 1, 3), (13, 20, 40)]
+    reqs = [serve.Request(i, list(range(i, i + n)), new, arrival_step=a) for i, (n, new, a) in enumerate(spec)]
+    done = serve.run_compact(eng, reqs, prefill_chunk=chunk)
+    assert sorted(r.rid for r in done) == list(range(len(spec)))
+    for r in done:
+        assert r.tokens == stream(r.prompt, r.max_new_tokens), r.rid
+    assert eng.n_active == 0
+    # no sequence-step was spent on an empty slot: the steps computed are bounded by what the requests needed
+    assert eng.stepped <= sum(new for _, new, _ in spec)
+
+
+def test_compacting_loop_sampled_draws_follow_the_request_through_swaps():
+    serve = entry.load_package().serve
+
+    class Eng(CompactEngine):
+        def __init__(self, *a):
+            super().__init__(*a)
+            self.first = {}
+
+        def mtp_step_sampled(self, u, **kw):
+            for s in range(self.n_active):
+                key = tuple(self.prompt[s])
+                self.first.setdefault(key, []).append(u[s][0])
+            self.mtp_step()
+
+    class Counter:
+        def __init__(self, base):
+            self.n = base
+
+        def random(self):
+            self.n += 1
+            return float(self.n)
+
+    eng = Eng(2, 1, 256)
+    reqs = [serve.Request(i, [i + 1], new, arrival_step=0) for i, new in enumerate([3, 12, 7])]
+    done = serve.run_compact(eng, reqs, sampling=dict(temp=1.0, top_p=1.0, top_k=0, min_p=0.0), rng_of=lambda r: Counter(1000 * r.rid))
+    assert {r.rid: r.tokens for r in done} == {i: stream([i + 1], new) for i, new in enumerate([3, 12, 7])}
+    for i in range(3):
+        heads = eng.first[(i + 1,)]
+        assert heads[0] == 1000 * i + 1 and all(b > a for a, b in zip(heads, heads[1:])) and all(1000 * i < h < 1000 * (i + 1) for h in heads)
