@@ -492,11 +492,14 @@ __global__ void mark_seen_record_kernel(const int32_t *out_rec, uint32_t n_seqs,
     }
 }
 
-__global__ void swap_ctl_kernel(int32_t *pos, int32_t *sel, int32_t *cur, int32_t *prefix_pos, uint32_t a, uint32_t b) {
+__global__ void swap_ctl_kernel(int32_t *pos, int32_t *sel, int32_t *cur, int32_t *prefix_pos, int32_t *out_rec, uint32_t n_seqs, uint32_t K1,
+                                uint32_t a, uint32_t b) {
     QB_PDL_ENTER();
     if (threadIdx.x == 0) {
-        int32_t *arr[4] = {pos, sel, cur, prefix_pos};
-        for (int i = 0; i < 4; ++i) { const int32_t t = arr[i][a]; arr[i][a] = arr[i][b]; arr[i][b] = t; }
+        int32_t *n_out = out_rec, *toks = out_rec + n_seqs, *opos = out_rec + n_seqs + (size_t)n_seqs * K1;
+        int32_t *arr[6] = {pos, sel, cur, prefix_pos, n_out, opos};      // the step record follows its sequence
+        for (int i = 0; i < 6; ++i) { const int32_t t = arr[i][a]; arr[i][a] = arr[i][b]; arr[i][b] = t; }
+        for (uint32_t i = 0; i < K1; ++i) { const int32_t t = toks[(size_t)a * K1 + i]; toks[(size_t)a * K1 + i] = toks[(size_t)b * K1 + i]; toks[(size_t)b * K1 + i] = t; }
     }
 }
 
@@ -947,7 +950,9 @@ extern "C" int qb_seq_reset(qb_ctx *ctx, qb_batch *b, uint32_t seq) {
         QB_CUDA(cudaMemsetAsync(b->conv[il] + seq * csz, 0, csz * sizeof(float), ctx->stream));
         QB_CUDA(cudaMemsetAsync(b->conv_alt[il] + seq * csz, 0, csz * sizeof(float), ctx->stream));
     }
-    for (int32_t *p : {b->pos, b->sel, b->cur, b->prefix_pos}) QB_CUDA(cudaMemsetAsync(p + seq, 0, sizeof(int32_t), ctx->stream));
+    // the step record of the slot too: the host's position mirror is refreshed from it (qb_read_step_output)
+    for (int32_t *p : {b->pos, b->sel, b->cur, b->prefix_pos, b->out_rec, b->out_rec + b->n_seqs + (size_t)b->n_seqs * K1})
+        QB_CUDA(cudaMemsetAsync(p + seq, 0, sizeof(int32_t), ctx->stream));
     QB_CUDA(cudaMemsetAsync(b->hid + (size_t)(b->rows_cap + seq) * c.n_embd, 0, (size_t)c.n_embd * sizeof(float), ctx->stream));
     if (b->seen) QB_CUDA(cudaMemsetAsync(b->seen + (size_t)seq * b->seen_words, 0, (size_t)b->seen_words * sizeof(uint32_t), ctx->stream));
     b->host_pos[seq] = 0;
@@ -995,7 +1000,7 @@ extern "C" int qb_seq_swap(qb_ctx *ctx, qb_batch *b, uint32_t s1, uint32_t s2) {
     QB_TRY(swap_block(b->page_table, (size_t)b->pages_per_seq * sizeof(int32_t)));
     QB_TRY(swap_block(b->hid + (size_t)b->rows_cap * c.n_embd, (size_t)c.n_embd * sizeof(float)));
     if (b->seen) QB_TRY(swap_block(b->seen, (size_t)b->seen_words * sizeof(uint32_t)));
-    QB_CUDA(qb_launch_pdl(ctx->stream, swap_ctl_kernel, dim3(1), dim3(32), (size_t)0, b->pos, b->sel, b->cur, b->prefix_pos, s1, s2));
+    QB_CUDA(qb_launch_pdl(ctx->stream, swap_ctl_kernel, dim3(1), dim3(32), (size_t)0, b->pos, b->sel, b->cur, b->prefix_pos, b->out_rec, b->n_seqs, K1, s1, s2));
     QB_LAUNCHED(ctx, "swap_ctl_kernel");
     std::swap(b->host_pos[s1], b->host_pos[s2]);
     return QB_OK;

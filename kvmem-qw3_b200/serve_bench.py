@@ -1,7 +1,7 @@
 """Throughput of the continuous-batching loop (serve.py) on one GPU: seeded synthetic requests of the 27B shape admitted
 into `--slots` sequence slots as they arrive; wall clock over the whole run (prefills included), one JSON line.
 
-    python kvmem-qw3_b200/serve_bench.py [--slots 8] [--requests 24] [--prompt 512] [--new 96] [--gap 2] [--tiny]
+    python kvmem-qw3_b200/serve_bench.py [--slots 8] [--requests 24] [--prompt 512] [--new 96] [--gap 2] [--chunk 0] [--fixed-slots] [--tiny]
 """
 import argparse
 import json
@@ -22,6 +22,8 @@ def main():
     ap.add_argument("--gap", type=int, default=2, help="a new request arrives every GAP decode steps")
     ap.add_argument("--k", type=int, default=3)
     ap.add_argument("--tiny", action="store_true")
+    ap.add_argument("--fixed-slots", action="store_true", help="the loop that steps every slot (serve.run) instead of the compacting one")
+    ap.add_argument("--chunk", type=int, default=0, help="compacting loop: prompt tokens ingested per iteration (0 = whole prompt)")
     args = ap.parse_args()
     pkg = entry.load_package()
     ctx = pkg.Context(0)
@@ -37,13 +39,16 @@ def main():
     batch = pkg.Batch(model, args.slots, args.prompt + args.new + 4 * (args.k + 1) + 64, args.k)
     ctx.sync()
     t0 = time.perf_counter()
-    done = pkg.serve.run(batch, reqs, speculative=args.k > 0)
+    if args.fixed_slots:
+        done = pkg.serve.run(batch, reqs, speculative=args.k > 0)
+    else:
+        done = pkg.serve.run_compact(batch, reqs, speculative=args.k > 0, prefill_chunk=args.chunk)
     ctx.sync()
     wall = time.perf_counter() - t0
     st = batch.stats()
     emitted = sum(len(r.tokens) for r in done)
     prompt_tokens = sum(len(r.prompt) for r in done)
-    print(json.dumps({"slots": args.slots, "requests": len(done), "prompt_tokens": prompt_tokens, "emitted_tokens": emitted,
+    print(json.dumps({"loop": "fixed slots" if args.fixed_slots else "compacting, chunk %d" % args.chunk, "slots": args.slots, "requests": len(done), "prompt_tokens": prompt_tokens, "emitted_tokens": emitted,
                       "wall_s": round(wall, 3), "emitted_tok_per_s": round(emitted / wall, 1),
                       "sequence_steps": st["steps"], "accepted_drafts": st["accepted"], "last_finish_step": max(r.finished_step for r in done),
                       "mean_queue_steps": round(float(np.mean([r.admitted_step - r.arrival_step for r in done])), 2),

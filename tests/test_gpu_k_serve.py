@@ -161,3 +161,16 @@ def test_compacting_loop_sampled_with_penalties(qb, orc, ctx, model):
         solo = qb.serve.run_compact(b1, [req], sampling=samp, rng_of=rng_of)[0].tokens
         b1.close()
         assert together[req.rid] == solo, req.rid
+
+
+def test_reset_then_read_keeps_the_slot_at_position_zero(qb, orc, ctx, model):
+    """A recycled slot stays at position 0 for the host as well, whatever step records are read before its prefill."""
+    V = model.cfg.vocab_size
+    b = qb.Batch(model, 2, 128, 1)
+    b.prefill(0, orc.synth_prompt(1, V, 90)); b.prefill(1, orc.synth_prompt(2, V, 70))
+    b.mtp_step(); b.read_output()
+    b.reset(1)
+    b.read_output()                                      # refreshes the host's position mirror from the records
+    b.prefill(1, orc.synth_prompt(3, V, 100))            # would not fit behind the old request's 70 tokens
+    assert b.position(1) == 100
+    b.close()
