@@ -31,9 +31,13 @@ __device__ __forceinline__ float warp_sum(float v) {
 //   columns (= one quantisation block).
 // The q/k conv windows are read by several CTAs but written by one (v head < nk, column block 0), so the kernel
 // reads the conv state from conv and writes it to conv_out (a different buffer: the caller ping-pongs).
-template <int HD, int CPW>
-__global__ void __launch_bounds__(512, 2) dn_fused_kernel(DnArgs a) {
-    constexpr int COLS = 16 * CPW, NCB = HD / COLS, NQB = COLS / 32, RPL = HD / 32, RB = 4, NCH = 2 * HD + COLS;
+// RB = rows per block (one conv / norm phase, one exchange of the head's sums of squares and one norm-gate phase per
+// block): 4 for the decode and verify steps, 8 for prompt ingestion, where the per-block costs dominate.  A row's
+// arithmetic does not depend on RB.
+template <int HD, int CPW, int RB, int MINB>
+__global__ void __launch_bounds__(512, MINB) dn_fused_kernel(DnArgs a) {
+    constexpr int COLS = 16 * CPW, NCB = HD / COLS, NQB = COLS / 32, RPL = HD / 32, NCH = 2 * HD + COLS;
+    static_assert(NCB * NQB * RB <= 32 && NQB * RB <= 16 && 2 * RB <= 32, "row block too large for the warp role mapping");
     constexpr int QK_WARPS = 2 * HD / 32;
     asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");     // "this CTA runs": awaited before the first push
     QB_PDL_ENTER();
@@ -237,7 +241,7 @@ __global__ void __launch_bounds__(512, 2) dn_fused_kernel(DnArgs a) {
     }
 }
 
-template <int HD, int CPW>
+template <int HD, int CPW, int RB, int MINB>
 int launch_fused(qb_ctx *ctx, const DnArgs &a) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(HD / (16 * CPW), a.nv, a.n_seqs);
@@ -252,7 +256,7 @@ int launch_fused(qb_ctx *ctx, const DnArgs &a) {
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    QB_CUDA(cudaLaunchKernelEx(&cfg, (dn_fused_kernel<HD, CPW>), a));
+    QB_CUDA(cudaLaunchKernelEx(&cfg, (dn_fused_kernel<HD, CPW, RB, MINB>), a));
     QB_LAUNCHED(ctx, "dn_fused_kernel");
     return QB_OK;
 }
@@ -266,8 +270,9 @@ int qb_launch_deltanet(qb_ctx *ctx, const DnArgs &a) {
     QB_REQUIRE(a.conv_out && a.conv_out != a.conv, "deltanet: the new conv state needs a buffer of its own");
     // one request: 32 state columns per CTA (more CTAs, shortest critical path); several: 64 per CTA (the per-CTA
     // work that does not depend on the column count — the head's q/k conv, the barriers — is paid half as often)
-    const bool wide = a.n_seqs > 2;
-    if (a.hd == 128) return wide ? launch_fused<128, 4>(ctx, a) : launch_fused<128, 2>(ctx, a);
-    if (a.hd == 64) return wide ? launch_fused<64, 4>(ctx, a) : launch_fused<64, 2>(ctx, a);
+    // prompt ingestion (many rows per sequence): 64 columns per CTA and 8-row blocks
+    const bool wide = a.n_seqs > 2, many = a.rows_per_seq >= 16;
+    if (a.hd == 128) return many ? launch_fused<128, 4, 8, 1>(ctx, a) : wide ? launch_fused<128, 4, 4, 2>(ctx, a) : launch_fused<128, 2, 4, 2>(ctx, a);
+    if (a.hd == 64) return many ? launch_fused<64, 4, 8, 1>(ctx, a) : wide ? launch_fused<64, 4, 4, 2>(ctx, a) : launch_fused<64, 2, 4, 2>(ctx, a);
     return qb_fail(QB_ERR_UNSUPPORTED, "deltanet: head dim %u unsupported (64/128)", a.hd);
 }
