@@ -65,21 +65,55 @@ __global__ void __launch_bounds__(512, MINB) dn_fused_kernel(DnArgs a) {
     // The inputs of a row block (projection rows, gate inputs, z) do not depend on the state slot: they are
     // requested first, and the next block's while the current one is processed.
     struct BlockIn { float cur[RB]; float zv, graw; };
+    // Ingestion form: every load of a block is issued before the first add (a load-add-load-add chain exposes one memory
+    // latency per row); each element still adds its K-segment partials in ascending order.
     auto load_block = [&](uint32_t rb0) {
         BlockIn in;
         const uint32_t nrows = rb0 < R ? min((uint32_t)RB, R - rb0) : 0u;
         const size_t row0 = (size_t)seq * R + rb0;
+        if constexpr (RB <= 4) {
+            // the step forms (64 registers per thread): element by element
+#pragma unroll
+            for (int t = 0; t < RB; ++t) {
+                in.cur[t] = 0.0f;
+                if (has && (uint32_t)t < nrows) in.cur[t] = qb_ldsum(a.proj, (row0 + t) * a.proj_stride + ch, a.proj_S, a.proj_pstride);
+            }
+            in.zv = 0.0f;
+            if (ng_q < NQB && ng_t < nrows)
+                in.zv = qb_ldsum(a.proj, (row0 + ng_t) * a.proj_stride + C + vh * HD + cb * COLS + ng_q * 32 + lane, a.proj_S, a.proj_pstride);
+            in.graw = 0.0f;
+            if (warp == 15 && lane < 2 * nrows)      // (row, decay | write strength) of the block: lanes of the last warp
+                in.graw = qb_ldsum(a.proj, (row0 + (lane >> 1)) * a.proj_stride + C + vdim + (lane & 1) * a.nv + vh, a.proj_S, a.proj_pstride);
+            return in;
+        }
+        const uint32_t S = a.proj_S;
+        const bool two = S > 1;
+        const bool hz = ng_q < NQB && ng_t < nrows, hg = warp == 15 && lane < 2 * nrows;
+        const size_t iz = (row0 + ng_t) * a.proj_stride + C + vh * HD + cb * COLS + ng_q * 32 + lane;
+        const size_t ig = (row0 + (lane >> 1)) * a.proj_stride + C + vdim + (lane & 1) * a.nv + vh;
+        float p0[RB], p1[RB];
 #pragma unroll
         for (int t = 0; t < RB; ++t) {
-            in.cur[t] = 0.0f;
-            if (has && (uint32_t)t < nrows) in.cur[t] = qb_ldsum(a.proj, (row0 + t) * a.proj_stride + ch, a.proj_S, a.proj_pstride);
+            const bool on = has && (uint32_t)t < nrows;
+            p0[t] = on ? a.proj[(row0 + t) * a.proj_stride + ch] : 0.0f;
+            p1[t] = on && two ? a.proj[(row0 + t) * a.proj_stride + ch + a.proj_pstride] : 0.0f;
         }
-        in.zv = 0.0f;
-        if (ng_q < NQB && ng_t < nrows)
-            in.zv = qb_ldsum(a.proj, (row0 + ng_t) * a.proj_stride + C + vh * HD + cb * COLS + ng_q * 32 + lane, a.proj_S, a.proj_pstride);
-        in.graw = 0.0f;
-        if (warp == 15 && lane < 2 * nrows)      // (row, decay | write strength) of the block: lanes of the last warp
-            in.graw = qb_ldsum(a.proj, (row0 + (lane >> 1)) * a.proj_stride + C + vdim + (lane & 1) * a.nv + vh, a.proj_S, a.proj_pstride);
+        const float z0 = hz ? a.proj[iz] : 0.0f, z1 = hz && two ? a.proj[iz + a.proj_pstride] : 0.0f;
+        const float g0 = hg ? a.proj[ig] : 0.0f, g1 = hg && two ? a.proj[ig + a.proj_pstride] : 0.0f;
+#pragma unroll
+        for (int t = 0; t < RB; ++t) in.cur[t] = two ? p0[t] + p1[t] : p0[t];
+        in.zv = two ? z0 + z1 : z0;
+        in.graw = two ? g0 + g1 : g0;
+        for (uint32_t sg = 2; sg < S; ++sg) {                 // further segments: again all loads, then the adds
+            const size_t off = (size_t)sg * a.proj_pstride;
+#pragma unroll
+            for (int t = 0; t < RB; ++t) p0[t] = has && (uint32_t)t < nrows ? a.proj[(row0 + t) * a.proj_stride + ch + off] : 0.0f;
+            const float zs = hz ? a.proj[iz + off] : 0.0f, gs = hg ? a.proj[ig + off] : 0.0f;
+#pragma unroll
+            for (int t = 0; t < RB; ++t) in.cur[t] += p0[t];
+            in.zv += zs;
+            in.graw += gs;
+        }
         return in;
     };
     BlockIn nxt = load_block(0);
