@@ -73,10 +73,22 @@ __global__ void __launch_bounds__(512, MINB) dn_fused_kernel(DnArgs a) {
         const size_t row0 = (size_t)seq * R + rb0;
         if constexpr (RB <= 4) {
             // the step forms (64 registers per thread): element by element
+            if (a.proj_S == 2) {                      // the usual split of the input projection: both partials of every row first
+                float p1[RB];
 #pragma unroll
-            for (int t = 0; t < RB; ++t) {
-                in.cur[t] = 0.0f;
-                if (has && (uint32_t)t < nrows) in.cur[t] = qb_ldsum(a.proj, (row0 + t) * a.proj_stride + ch, a.proj_S, a.proj_pstride);
+                for (int t = 0; t < RB; ++t) {
+                    const bool on = has && (uint32_t)t < nrows;
+                    in.cur[t] = on ? a.proj[(row0 + t) * a.proj_stride + ch] : 0.0f;
+                    p1[t] = on ? a.proj[(row0 + t) * a.proj_stride + ch + a.proj_pstride] : 0.0f;
+                }
+#pragma unroll
+                for (int t = 0; t < RB; ++t) in.cur[t] += p1[t];
+            } else {
+#pragma unroll
+                for (int t = 0; t < RB; ++t) {
+                    in.cur[t] = 0.0f;
+                    if (has && (uint32_t)t < nrows) in.cur[t] = qb_ldsum(a.proj, (row0 + t) * a.proj_stride + ch, a.proj_S, a.proj_pstride);
+                }
             }
             in.zv = 0.0f;
             if (ng_q < NQB && ng_t < nrows)
