@@ -219,6 +219,34 @@ int qb_argmax_rows(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t n, uint
  * GGUF file: every Q8_0 tensor ~ quantise(N(0, sigma^2)), norm gains 1, DeltaNet fp32 tensors from
  * the same seed (recipe in qw3b200_synth.h and the engine source). */
 int  qb_model_create_synth(qb_ctx *ctx, const qb_model_config *cfg, uint64_t seed, qb_model **out);
+/* One named tensor of a checkpoint on the host.  Names are the GGUF names the reference binds
+ * (src/qwen_native.cpp:147-190, MTP block :271-298): token_embd.weight, output_norm.weight, output.weight,
+ * blk.<i>.attn_norm.weight, blk.<i>.ffn_norm.weight (or post_attention_norm.weight), attention layers
+ * attn_q / attn_k / attn_v / attn_output / attn_q_norm / attn_k_norm, DeltaNet layers attn_qkv / attn_gate /
+ * ssm_alpha / ssm_beta / ssm_out (.weight), ssm_conv1d.weight, ssm_a, ssm_dt.bias, ssm_norm.weight, every layer
+ * ffn_gate / ffn_up / ffn_down (.weight); the MTP layer is block n_layers with nextn.eh_proj / nextn.enorm /
+ * nextn.hnorm and the optional nextn.embed_tokens / nextn.shared_head_head / nextn.shared_head_norm.
+ * type is the GGUF tensor type: the two the reference maps from a GGUF file (src/model_source.cpp:120-121).
+ * cols = dims[0] (input features), rows = product of the other dims (src/qwen_weights.cpp:12-22). */
+#define QB_TENSOR_F32 0u     /* data = float [rows * cols] */
+#define QB_TENSOR_Q8_0 8u    /* data = rows x (cols / 32) blocks of 34 bytes [fp16 d | int8 q[32]] */
+typedef struct qb_tensor_desc {
+    const char *name;
+    uint32_t    type;
+    uint64_t    rows, cols;
+    const void *data;
+} qb_tensor_desc;
+/* QwenNativeModel tensor binding + QwenWeights upload (src/qwen_native.cpp:147-190, 271-298;
+ * src/qwen_weights.cpp:170-208) from the caller's tensors: every projection Q8_0, every norm gain and the small
+ * DeltaNet tensors F32.  The host pointers are not retained.  A missing or mis-shaped tensor fails with its name. */
+int  qb_model_create(qb_ctx *ctx, const qb_model_config *cfg, const qb_tensor_desc *tensors, size_t n_tensors, qb_model **out);
+/* GgufFile + QwenConfig + the binding above (src/gguf.cpp:216-278, src/qwen_config.cpp:53-108): maps a GGUF v3
+ * file, reads the qwen35.* hyper-parameters (vocab_size = length of tokenizer.ggml.tokens) and uploads the tensors.
+ * cfg_out (may be NULL) receives the configuration read. */
+int  qb_model_load_gguf(qb_ctx *ctx, const char *path, qb_model **out, qb_model_config *cfg_out);
+/* The parsing half alone (no device needed): configuration, number of F32 / Q8_0 tensors and their bytes. */
+int  qb_gguf_read_config(const char *path, qb_model_config *cfg_out, uint64_t *n_tensors_out, uint64_t *tensor_bytes_out);
+const qb_model_config *qb_model_get_config(const qb_model *m);
 void qb_model_destroy(qb_ctx *ctx, qb_model *m);
 size_t qb_model_weight_bytes(const qb_model *m);
 
@@ -234,6 +262,16 @@ void qb_batch_destroy(qb_ctx *ctx, qb_batch *b);
  * 22543-22815): ingest `n` prompt tokens of sequence `seq` (chunked), leave next token = argmax of
  * the last row. */
 int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n);
+/* A part of a prompt that is not its end (the chunked ingestion of a continuous-batching loop, ContinuousPrefillBatch,
+ * src/qwen_native_backend.cpp:4482-4530): K/V, recurrent state and MTP prefix advance; no LM head, no token is chosen,
+ * nothing is counted as emitted or recorded as seen beyond the prompt tokens.  Finish with qb_prefill(_sampled). */
+int qb_prefill_chunk(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n);
+/* Sampling parameters of a request (GenerationOptions, include/qw3/qw3.hpp:222-230). */
+typedef struct qb_sampling { float temp, top_p; int32_t top_k; float min_p; } qb_sampling;
+/* The end of a sampled request's prompt: as qb_prefill, but the first token is drawn from the last row's logits with
+ * the request's first uniform draw u (pick_from_last_logits, src/qwen_native_backend.cpp:15399-15428: token penalties
+ * against the prompt when qb_batch_set_penalties is on, then sample_token). */
+int qb_prefill_sampled(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n, const qb_sampling *samp, double u);
 
 /* forward_one_token + argmax (src/qwen_executor.cpp:5446-5816): one non-speculative greedy step
  * for every sequence.  Emits one token per sequence. */
@@ -260,6 +298,12 @@ int qb_mtp_verify(qb_ctx *ctx, qb_batch *b);
 int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b);
 /* draft + verify + accept_commit. */
 int qb_mtp_step(qb_ctx *ctx, qb_batch *b);
+/* Chain policy of the speculative loop: limits_host[seq] = draft depth from the next step on, the reference's
+ * min(chain, tokens still wanted) (MtpAdaptivePolicy::draft_limit, src/qwen_native_backend.cpp:1625-1628; 0 makes the
+ * step a plain one, the empty-chain case of :15829-15848; NULL = depth k everywhere); eos_token = the token that ends a
+ * chain when drafted (:15817-15821; -1 = none, the reference's ignore_eos).  The counters of qb_batch_stats count the
+ * drafts of the cut chain, as the reference's mtp_spec_summary does. */
+int qb_batch_set_draft_policy(qb_ctx *ctx, qb_batch *b, const int32_t *limits_host, int32_t eos_token);
 
 /* Sampling-mode requests (temp > 0).  The reference copies the verifier's logits to the host and runs
  * sampling_distribution (src/qwen_native_backend.cpp:282-370: softmax(logits / temp), then top-k, min-p and nucleus
@@ -276,8 +320,8 @@ int qb_sample_rows(qb_ctx *ctx, const float *logits_dev, uint32_t rows, uint32_t
                    int32_t *token_dev, int32_t *accepted_dev, float *p_draft_dev);
 /* The same decision for the rows of the last qb_mtp_verify, left where qb_mtp_accept_commit reads the row tokens: call
  * between the two.  u_host: double [n_seqs][k+1], the caller's uniform draws in the order the reference consumes its
- * generator: row i accepts with u[i], a rejection at row i draws with u[i+1], the bonus draw is u[k]; a step uses the
- * first accepted + 1 of them. */
+ * generator: row i accepts with u[i], a rejection at row i draws with u[i+1], the bonus draw is u[k]; a step that
+ * rejects after a acceptances uses the first a + 2 of them, a fully accepted chain all k + 1. */
 int qb_mtp_sample_rows(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host);
 /* Token penalties of sampling requests (apply_token_penalties, src/qwen_native_backend.cpp:262-280: a seen token's logit is
  * divided by repetition when >= 0, multiplied when < 0, then lowered by presence): from this call on the batch records the
@@ -361,9 +405,6 @@ int qb_ipc_close(qb_ctx *ctx, void *dev_ptr);
 int qb_debug_timeline_enable(qb_ctx *ctx, uint32_t max_launches);
 int qb_debug_timeline_read(qb_ctx *ctx, uint64_t *out, uint32_t *grids, double *bytes, uint32_t max_launches,
                            uint32_t *n_out);
-/* Measured INT8 tensor-core peak: one CTA per SM issues iters x 4 tcgen05.mma.kind::i8 (128 x 256 x 32) on operands
- * resident in shared memory; returns tera-ops per second (2 ops per multiply-add). */
-int qb_debug_int8_mma_peak(qb_ctx *ctx, uint32_t iters, double *tops_out);
 /* Number of kernels this library launched on the context since creation. */
 int64_t qb_launch_count(qb_ctx *ctx);
 

@@ -28,6 +28,16 @@ class ModelConfig(C.Structure):
         return {n: getattr(self, n) for n, _ in self._fields_}
 
 
+class Sampling(C.Structure):
+    """qb_sampling (include/qw3b200.h)."""
+    _fields_ = [("temp", f32), ("top_p", f32), ("top_k", C.c_int32), ("min_p", f32)]
+
+
+class TensorDesc(C.Structure):
+    """qb_tensor_desc (include/qw3b200.h): one named host tensor of a checkpoint, GGUF type 0 (F32) or 8 (Q8_0)."""
+    _fields_ = [("name", C.c_char_p), ("type", u32), ("rows", u64), ("cols", u64), ("data", vp)]
+
+
 # name -> (restype, argtypes); every symbol include/qw3b200.h declares
 SIGNATURES = {
     "qb_create": (i32, [i32, C.POINTER(vp)]),
@@ -70,11 +80,17 @@ SIGNATURES = {
     "qb_deltanet_rows": (i32, [vp, vp, u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, f32, vp, vp, u32, vp, i32, vp]),
     "qb_argmax_rows": (i32, [vp, vp, u32, u32, u32, vp]),
     "qb_model_create_synth": (i32, [vp, C.POINTER(ModelConfig), u64, C.POINTER(vp)]),
+    "qb_model_create": (i32, [vp, C.POINTER(ModelConfig), C.POINTER(TensorDesc), sz, C.POINTER(vp)]),
+    "qb_model_load_gguf": (i32, [vp, C.c_char_p, C.POINTER(vp), C.POINTER(ModelConfig)]),
+    "qb_gguf_read_config": (i32, [C.c_char_p, C.POINTER(ModelConfig), C.POINTER(u64), C.POINTER(u64)]),
+    "qb_model_get_config": (C.POINTER(ModelConfig), [vp]),
     "qb_model_destroy": (None, [vp, vp]),
     "qb_model_weight_bytes": (sz, [vp]),
     "qb_batch_create": (i32, [vp, vp, u32, u32, u32, u32, i32, C.POINTER(vp)]),
     "qb_batch_destroy": (None, [vp, vp]),
     "qb_prefill": (i32, [vp, vp, u32, vp, u32]),
+    "qb_prefill_chunk": (i32, [vp, vp, u32, vp, u32]),
+    "qb_prefill_sampled": (i32, [vp, vp, u32, vp, u32, C.POINTER(Sampling), C.c_double]),
     "qb_decode_greedy_step": (i32, [vp, vp]),
     "qb_mtp_draft": (i32, [vp, vp]),
     "qb_mtp_force_drafts": (i32, [vp, vp, vp, u32]),
@@ -82,6 +98,7 @@ SIGNATURES = {
     "qb_mtp_verify": (i32, [vp, vp]),
     "qb_mtp_accept_commit": (i32, [vp, vp]),
     "qb_mtp_step": (i32, [vp, vp]),
+    "qb_batch_set_draft_policy": (i32, [vp, vp, vp, i32]),
     "qb_read_step_output": (i32, [vp, vp, vp, vp]),
     "qb_batch_stats": (i32, [vp, vp, vp]),
     "qb_seq_position": (i32, [vp, vp, u32, C.POINTER(C.c_int32)]),
@@ -110,7 +127,6 @@ SIGNATURES = {
     "qb_ipc_export": (i32, [vp, vp, vp]),
     "qb_ipc_open": (i32, [vp, vp, C.POINTER(vp)]),
     "qb_ipc_close": (i32, [vp, vp]),
-    "qb_debug_int8_mma_peak": (i32, [vp, u32, C.POINTER(C.c_double)]),
     "qb_debug_timeline_enable": (i32, [vp, u32]),
     "qb_debug_timeline_read": (i32, [vp, vp, vp, vp, u32, C.POINTER(u32)]),
 }
@@ -253,12 +269,6 @@ class Context:
             out.append((n, int(c), float(t)))
         return out
 
-    def int8_mma_peak(self, iters=20000):
-        """Measured INT8 tensor-core peak in TOP/s (operands resident in shared memory)."""
-        t = C.c_double()
-        check(lib().qb_debug_int8_mma_peak(self.h, iters, C.byref(t)))
-        return t.value
-
     def timeline_enable(self, max_launches):
         check(lib().qb_debug_timeline_enable(self.h, max_launches))
 
@@ -374,12 +384,60 @@ def matmul(ctx, w, x, ksplit=0, impl=0):
     return yd.download()
 
 
+def gguf_read_config(path):
+    """(ModelConfig, number of F32 / Q8_0 tensors, their bytes) of a GGUF v3 qwen35 checkpoint; needs no GPU."""
+    cfg, n, b = ModelConfig(), u64(), u64()
+    check(lib().qb_gguf_read_config(os.fsencode(path), C.byref(cfg), C.byref(n), C.byref(b)))
+    return cfg, n.value, b.value
+
+
+def tensor_descs(tensors):
+    """tensors: {name: numpy array}; float32 arrays are F32 tensors (any shape, cols = last axis), uint8 arrays of
+    shape [rows][cols/32*34] are Q8_0 block rows.  Returns (ctypes array, keep-alive list)."""
+    keep, descs = [], (TensorDesc * len(tensors))()
+    for i, (name, a) in enumerate(tensors.items()):
+        a = np.ascontiguousarray(a)
+        keep.append(a)
+        if a.dtype == np.uint8:
+            assert a.ndim == 2 and a.shape[1] % 34 == 0, name
+            rows, cols, typ = a.shape[0], a.shape[1] // 34 * 32, 8
+        else:
+            assert a.dtype == np.float32, name
+            cols = a.shape[-1]
+            rows, typ = a.size // cols, 0
+        nb = name.encode()
+        keep.append(nb)
+        descs[i] = TensorDesc(nb, typ, rows, cols, a.ctypes.data)
+    return descs, keep
+
+
 class Model:
     def __init__(self, ctx, cfg, seed):
         self.ctx, self.cfg = ctx, cfg
         h = vp()
         check(lib().qb_model_create_synth(ctx.h, C.byref(cfg), seed, C.byref(h)))
         self.h = h
+
+    @classmethod
+    def from_tensors(cls, ctx, cfg, tensors):
+        """Model from the caller's host tensors ({GGUF tensor name: numpy array}, see tensor_descs)."""
+        self = cls.__new__(cls)
+        self.ctx, self.cfg = ctx, cfg
+        descs, keep = tensor_descs(tensors)
+        h = vp()
+        check(lib().qb_model_create(ctx.h, C.byref(cfg), descs, len(tensors), C.byref(h)))
+        del keep
+        self.h = h
+        return self
+
+    @classmethod
+    def from_gguf(cls, ctx, path):
+        self = cls.__new__(cls)
+        self.ctx = ctx
+        h, cfg = vp(), ModelConfig()
+        check(lib().qb_model_load_gguf(ctx.h, os.fsencode(path), C.byref(h), C.byref(cfg)))
+        self.h, self.cfg = h, cfg
+        return self
 
     @property
     def weight_bytes(self):
@@ -408,9 +466,17 @@ class Batch:
             lib().qb_batch_destroy(self.ctx.h, self.h)
             self.h = None
 
-    def prefill(self, seq, tokens):
+    def prefill(self, seq, tokens, more=False):
+        """Ingests prompt tokens of sequence `seq`; more=True: the prompt continues in a later call (no token is chosen)."""
         t = np.ascontiguousarray(tokens, np.int32)
-        check(lib().qb_prefill(self.ctx.h, self.h, seq, _np_ptr(t), len(t)))
+        fn = lib().qb_prefill_chunk if more else lib().qb_prefill
+        check(fn(self.ctx.h, self.h, seq, _np_ptr(t), len(t)))
+
+    def prefill_sampled(self, seq, tokens, u, temp, top_p=1.0, top_k=0, min_p=0.0):
+        """The end of a sampled request's prompt: the first token is drawn with the uniform draw u."""
+        t = np.ascontiguousarray(tokens, np.int32)
+        sp = Sampling(temp, top_p, top_k, min_p)
+        check(lib().qb_prefill_sampled(self.ctx.h, self.h, seq, _np_ptr(t), len(t), C.byref(sp), float(u)))
 
     def greedy_step(self):
         check(lib().qb_decode_greedy_step(self.ctx.h, self.h))
@@ -434,6 +500,11 @@ class Batch:
 
     def mtp_step(self):
         check(lib().qb_mtp_step(self.ctx.h, self.h))
+
+    def set_draft_policy(self, limits=None, eos_token=-1):
+        """limits: per-sequence draft depth of the next steps (None = k everywhere); eos_token ends a chain when drafted."""
+        lim = None if limits is None else np.ascontiguousarray(limits, np.int32)
+        check(lib().qb_batch_set_draft_policy(self.ctx.h, self.h, _np_ptr(lim) if lim is not None else None, int(eos_token)))
 
     def set_penalties(self, presence=0.0, repetition=1.0):
         check(lib().qb_batch_set_penalties(self.ctx.h, self.h, presence, repetition))

@@ -12,6 +12,8 @@
 // synchronisation; the host reads back one small record per step.
 #include "qb_internal.h"
 
+#include <string>
+
 namespace {
 
 enum TensorKind : uint32_t {
@@ -32,6 +34,8 @@ struct LayerW {
     qb_weight *w_down = nullptr;
     qb_weight w_kv;                  // view of the k and v rows of w_in (attention layers)
     float *conv_w = nullptr, *ssm_a = nullptr, *dt_bias = nullptr;
+    // RMSNorm gains (attn_norm, ffn_norm / post_attention_norm, attn_q_norm, attn_k_norm, ssm_norm)
+    const float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr, *ssm_norm = nullptr;
 };
 
 }  // namespace
@@ -40,7 +44,12 @@ struct qb_model {
     qb_model_config cfg;
     std::vector<LayerW> layers;      // n_layers (+ the MTP layer last)
     qb_weight *token_embd = nullptr, *output = nullptr, *eh_proj = nullptr;
+    // MTP head: embedding table and LM head (nextn.embed_tokens / nextn.shared_head_head, else the target's)
+    qb_weight *mtp_embd = nullptr, *mtp_head = nullptr;
+    bool output_tied = false;        // no output.weight: the LM head is token_embd
     float *ones = nullptr;           // every RMSNorm gain of the seeded model is 1.0
+    const float *output_norm = nullptr, *enorm = nullptr, *hnorm = nullptr, *shared_head_norm = nullptr;
+    std::vector<float *> owned_f32;  // fp32 tensors uploaded for this model
     float *inv_freq = nullptr;
     size_t weight_bytes = 0;
     uint32_t inner() const { return cfg.n_heads * cfg.head_dim; }
@@ -106,50 +115,260 @@ static int build_layer(qb_ctx *ctx, qb_model *m, LayerW &L, uint32_t il, bool re
     return QB_OK;
 }
 
-extern "C" int qb_model_create_synth(qb_ctx *ctx, const qb_model_config *cfg, uint64_t seed, qb_model **out) {
-    QB_REQUIRE(ctx && cfg && out, "qb_model_create_synth: null argument");
-    const qb_model_config &c = *cfg;
-    QB_REQUIRE(c.n_embd % 128 == 0 && c.n_ff % 128 == 0, "n_embd and n_ff must be multiples of 128");
+extern "C" void qb_model_destroy(qb_ctx *ctx, qb_model *m);
+static void link_prefetch_chain(qb_model *m);
+
+// Shape checks shared by every model constructor, the all-ones gain vector and the RoPE frequencies.
+static int model_begin(qb_ctx *ctx, const qb_model_config &c, qb_model **out) {
+    QB_REQUIRE(c.n_layers > 0 && c.n_embd % 128 == 0 && c.n_ff % 128 == 0, "n_embd and n_ff must be multiples of 128");
     QB_REQUIRE(c.head_dim == 64 || c.head_dim == 128 || c.head_dim == 256, "head_dim must be 64, 128 or 256");
     QB_REQUIRE(c.ssm_head_dim == 64 || c.ssm_head_dim == 128, "ssm_head_dim must be 64 or 128");
     QB_REQUIRE(c.ssm_conv_kernel == 4, "ssm_conv_kernel must be 4");
-    QB_REQUIRE(c.n_heads % c.n_kv_heads == 0 && c.n_heads / c.n_kv_heads <= 8, "GQA group must divide and be <= 8");
+    QB_REQUIRE(c.n_kv_heads > 0 && c.n_heads % c.n_kv_heads == 0 && c.n_heads / c.n_kv_heads <= 8, "GQA group must divide and be <= 8");
     QB_REQUIRE((c.n_heads * c.head_dim) % 128 == 0 && (c.ssm_num_v_heads * c.ssm_head_dim) % 128 == 0, "inner dims must be multiples of 128");
     QB_REQUIRE(c.mtp_layers <= 1, "at most one MTP layer");
+    QB_REQUIRE(c.rope_dim >= 2 && c.rope_dim % 2 == 0 && c.rope_dim <= c.head_dim, "rope_dim must be even and <= head_dim");
+    QB_REQUIRE(c.vocab_size > 0, "vocab_size must be positive");
     QB_CUDA(cudaSetDevice(ctx->device));
     qb_model *m = new qb_model();
     m->cfg = c;
+    *out = m;
     std::vector<float> ones(std::max({c.n_embd, c.head_dim, c.ssm_head_dim}), 1.0f);
     QB_TRY(upload_f32(ctx, ones, &m->ones));
     std::vector<float> invf(c.rope_dim / 2);
     for (uint32_t i = 0; i < c.rope_dim / 2; ++i) invf[i] = (float)std::pow((double)c.rope_theta, -2.0 * (double)i / (double)c.rope_dim);
     QB_TRY(upload_f32(ctx, invf, &m->inv_freq));
     m->layers.resize(c.n_layers + (c.mtp_layers ? 1 : 0));
-    for (uint32_t il = 0; il < c.n_layers; ++il) QB_TRY(build_layer(ctx, m, m->layers[il], il, !m->is_attn(il), seed));
-    if (c.mtp_layers) {
-        QB_TRY(build_layer(ctx, m, m->layers[c.n_layers], c.n_layers, false, seed));
-        QB_TRY(qb_weight_q8_0_synth(ctx, seed, tensor_id(c.n_layers, T_EH_PROJ), c.n_embd, 2 * c.n_embd, c.weight_sigma, &m->eh_proj));
-        m->weight_bytes += weight_bytes_of(m->eh_proj);
-    }
-    QB_TRY(qb_weight_q8_0_synth(ctx, seed, tensor_id(0xFFFF, T_TOKEN_EMBD), c.vocab_size, c.n_embd, c.weight_sigma, &m->token_embd));
-    QB_TRY(qb_weight_q8_0_synth(ctx, seed, tensor_id(0xFFFF, T_OUTPUT), c.vocab_size, c.n_embd, c.weight_sigma, &m->output));
-    m->weight_bytes += weight_bytes_of(m->token_embd) + weight_bytes_of(m->output);
-    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return QB_OK;
+}
+
+extern "C" int qb_model_create_synth(qb_ctx *ctx, const qb_model_config *cfg, uint64_t seed, qb_model **out) {
+    QB_REQUIRE(ctx && cfg && out, "qb_model_create_synth: null argument");
+    const qb_model_config &c = *cfg;
+    qb_model *m = nullptr;
+    int st = model_begin(ctx, c, &m);
+    if (st != QB_OK) { qb_model_destroy(ctx, m); return st; }
+    auto body = [&]() -> int {
+        for (uint32_t il = 0; il < c.n_layers; ++il) QB_TRY(build_layer(ctx, m, m->layers[il], il, !m->is_attn(il), seed));
+        if (c.mtp_layers) {
+            QB_TRY(build_layer(ctx, m, m->layers[c.n_layers], c.n_layers, false, seed));
+            QB_TRY(qb_weight_q8_0_synth(ctx, seed, tensor_id(c.n_layers, T_EH_PROJ), c.n_embd, 2 * c.n_embd, c.weight_sigma, &m->eh_proj));
+            m->weight_bytes += weight_bytes_of(m->eh_proj);
+        }
+        QB_TRY(qb_weight_q8_0_synth(ctx, seed, tensor_id(0xFFFF, T_TOKEN_EMBD), c.vocab_size, c.n_embd, c.weight_sigma, &m->token_embd));
+        QB_TRY(qb_weight_q8_0_synth(ctx, seed, tensor_id(0xFFFF, T_OUTPUT), c.vocab_size, c.n_embd, c.weight_sigma, &m->output));
+        m->weight_bytes += weight_bytes_of(m->token_embd) + weight_bytes_of(m->output);
+        // every RMSNorm gain of the seeded model is 1.0; the MTP head shares the target's embedding and LM head
+        for (LayerW &L : m->layers) L.attn_norm = L.ffn_norm = L.q_norm = L.k_norm = L.ssm_norm = m->ones;
+        m->output_norm = m->enorm = m->hnorm = m->shared_head_norm = m->ones;
+        m->mtp_embd = m->token_embd;
+        m->mtp_head = m->output;
+        link_prefetch_chain(m);
+        QB_CUDA(cudaStreamSynchronize(ctx->stream));
+        return QB_OK;
+    };
+    st = body();
+    if (st != QB_OK) { qb_model_destroy(ctx, m); return st; }
     *out = m;
     return QB_OK;
 }
 
+// ---- a model from the caller's tensors (the GGUF tensor set of src/qwen_native.cpp:147-190, 271-298) ----
+namespace {
+struct TensorTable {
+    const qb_tensor_desc *t; size_t n;
+    const qb_tensor_desc *find(const std::string &name) const {
+        for (size_t i = 0; i < n; ++i) if (t[i].name && name == t[i].name) return &t[i];
+        return nullptr;
+    }
+};
+std::string blk(uint32_t il, const char *name) { return "blk." + std::to_string(il) + "." + name; }
+}  // namespace
+
+static int need_q8(const TensorTable &tt, const std::string &name, uint32_t rows, uint32_t cols, const qb_tensor_desc **out) {
+    const qb_tensor_desc *d = tt.find(name);
+    if (!d) return qb_fail(QB_ERR_INVALID, "model: tensor %s is missing", name.c_str());
+    if (d->type != QB_TENSOR_Q8_0)
+        return qb_fail(QB_ERR_UNSUPPORTED, "model: tensor %s has type %u; this path takes Q8_0 (type 8) matrices only", name.c_str(), d->type);
+    if (d->rows != rows || d->cols != cols || !d->data)
+        return qb_fail(QB_ERR_INVALID, "model: tensor %s is %llu x %llu, expected %u x %u", name.c_str(), (unsigned long long)d->rows,
+                       (unsigned long long)d->cols, rows, cols);
+    *out = d;
+    return QB_OK;
+}
+static int need_f32(qb_ctx *ctx, qb_model *m, const TensorTable &tt, const std::string &name, const std::string &alt, uint64_t count,
+                    const float **out) {
+    const qb_tensor_desc *d = tt.find(name);
+    if (!d && !alt.empty()) d = tt.find(alt);
+    if (!d) return qb_fail(QB_ERR_INVALID, "model: tensor %s is missing", name.c_str());
+    if (d->type != QB_TENSOR_F32 || !d->data) return qb_fail(QB_ERR_UNSUPPORTED, "model: tensor %s must be F32 (type 0)", name.c_str());
+    if (d->rows * d->cols != count)
+        return qb_fail(QB_ERR_INVALID, "model: tensor %s has %llu elements, expected %llu", name.c_str(),
+                       (unsigned long long)(d->rows * d->cols), (unsigned long long)count);
+    float *dev = nullptr;
+    QB_CUDA(cudaMalloc(&dev, count * sizeof(float)));
+    m->owned_f32.push_back(dev);
+    QB_CUDA(cudaMemcpyAsync(dev, d->data, count * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    *out = dev;
+    return QB_OK;
+}
+
+static int bind_layer(qb_ctx *ctx, qb_model *m, const TensorTable &tt, LayerW &L, uint32_t il, bool recurrent) {
+    const qb_model_config &c = m->cfg;
+    const uint32_t H = c.n_embd;
+    const qb_tensor_desc *d = nullptr;
+    L.recurrent = recurrent;
+    QB_TRY(need_f32(ctx, m, tt, blk(il, "attn_norm.weight"), "", H, &L.attn_norm));
+    QB_TRY(need_f32(ctx, m, tt, blk(il, "ffn_norm.weight"), blk(il, "post_attention_norm.weight"), H, &L.ffn_norm));
+    if (!recurrent) {
+        const uint32_t inner = m->inner(), kvd = m->kvd();
+        QB_REQUIRE((2 * inner) % 128 == 0, "attention q rows %u not a multiple of 128", 2 * inner);
+        QB_TRY(qb_weight_alloc(ctx, m->attn_in(), H, &L.w_in));
+        QB_TRY(need_q8(tt, blk(il, "attn_q.weight"), 2 * inner, H, &d));
+        QB_TRY(qb_weight_fill_upload(ctx, L.w_in, 0, 2 * inner, d->data));
+        QB_TRY(need_q8(tt, blk(il, "attn_k.weight"), kvd, H, &d));
+        QB_TRY(qb_weight_fill_upload(ctx, L.w_in, 2 * inner, kvd, d->data));
+        QB_TRY(need_q8(tt, blk(il, "attn_v.weight"), kvd, H, &d));
+        QB_TRY(qb_weight_fill_upload(ctx, L.w_in, 2 * inner + kvd, kvd, d->data));
+        QB_TRY(qb_weight_view(ctx, L.w_in, 2 * inner, 2 * kvd, &L.w_kv));
+        QB_TRY(need_q8(tt, blk(il, "attn_output.weight"), H, inner, &d));
+        QB_TRY(qb_weight_q8_0(ctx, d->data, H, inner, &L.w_out));
+        QB_TRY(need_f32(ctx, m, tt, blk(il, "attn_q_norm.weight"), "", c.head_dim, &L.q_norm));
+        QB_TRY(need_f32(ctx, m, tt, blk(il, "attn_k_norm.weight"), "", c.head_dim, &L.k_norm));
+    } else {
+        const uint32_t C = m->qkv_dim(), vdim = m->vdim(), nv = c.ssm_num_v_heads;
+        QB_TRY(qb_weight_alloc(ctx, m->dn_in(), H, &L.w_in));
+        QB_TRY(need_q8(tt, blk(il, "attn_qkv.weight"), C, H, &d));
+        QB_TRY(qb_weight_fill_upload(ctx, L.w_in, 0, C, d->data));
+        QB_TRY(need_q8(tt, blk(il, "attn_gate.weight"), vdim, H, &d));
+        QB_TRY(qb_weight_fill_upload(ctx, L.w_in, C, vdim, d->data));
+        QB_TRY(need_q8(tt, blk(il, "ssm_alpha.weight"), nv, H, &d));
+        QB_TRY(qb_weight_fill_upload(ctx, L.w_in, C + vdim, nv, d->data));
+        QB_TRY(need_q8(tt, blk(il, "ssm_beta.weight"), nv, H, &d));
+        QB_TRY(qb_weight_fill_upload(ctx, L.w_in, C + vdim + nv, nv, d->data));
+        QB_TRY(need_q8(tt, blk(il, "ssm_out.weight"), H, vdim, &d));
+        QB_TRY(qb_weight_q8_0(ctx, d->data, H, vdim, &L.w_out));
+        const float *p = nullptr;
+        QB_TRY(need_f32(ctx, m, tt, blk(il, "ssm_conv1d.weight"), "", (uint64_t)C * c.ssm_conv_kernel, &p)); L.conv_w = const_cast<float *>(p);
+        QB_TRY(need_f32(ctx, m, tt, blk(il, "ssm_a"), "", nv, &p)); L.ssm_a = const_cast<float *>(p);
+        QB_TRY(need_f32(ctx, m, tt, blk(il, "ssm_dt.bias"), "", nv, &p)); L.dt_bias = const_cast<float *>(p);
+        QB_TRY(need_f32(ctx, m, tt, blk(il, "ssm_norm.weight"), "", c.ssm_head_dim, &L.ssm_norm));
+    }
+    const qb_tensor_desc *g = nullptr, *u = nullptr;
+    QB_REQUIRE(c.n_ff % 64 == 0, "model: FFN dimension %u is not a multiple of 64", c.n_ff);
+    QB_TRY(need_q8(tt, blk(il, "ffn_gate.weight"), c.n_ff, H, &g));
+    QB_TRY(need_q8(tt, blk(il, "ffn_up.weight"), c.n_ff, H, &u));
+    QB_TRY(qb_weight_q8_0_gate_up(ctx, g->data, u->data, c.n_ff, H, &L.w_gate_up));
+    QB_TRY(need_q8(tt, blk(il, "ffn_down.weight"), H, c.n_ff, &d));
+    QB_TRY(qb_weight_q8_0(ctx, d->data, H, c.n_ff, &L.w_down));
+    m->weight_bytes += weight_bytes_of(L.w_in) + weight_bytes_of(L.w_out) + weight_bytes_of(L.w_gate_up) + weight_bytes_of(L.w_down);
+    return QB_OK;
+}
+
+// QwenNativeModel's tensor binding (src/qwen_native.cpp:147-190; MTP block :271-298) and QwenWeights' upload
+// (src/qwen_weights.cpp:170-208) from the caller's host tensors.  A layer is full attention when its attn_q.weight
+// exists (the reference's rule), which must agree with full_attention_interval.  output.weight falls back to
+// token_embd.weight; the MTP head's embedding, LM head and final norm fall back to the target's.
+extern "C" int qb_model_create(qb_ctx *ctx, const qb_model_config *cfg, const qb_tensor_desc *tensors, size_t n_tensors, qb_model **out) {
+    QB_REQUIRE(ctx && cfg && tensors && out, "qb_model_create: null argument");
+    const qb_model_config &c = *cfg;
+    qb_model *m = nullptr;
+    int st = model_begin(ctx, c, &m);
+    if (st != QB_OK) { qb_model_destroy(ctx, m); return st; }
+    const TensorTable tt{tensors, n_tensors};
+    auto body = [&]() -> int {
+        const uint32_t H = c.n_embd, V = c.vocab_size;
+        const qb_tensor_desc *d = nullptr;
+        for (uint32_t il = 0; il < c.n_layers; ++il) {
+            const bool has_q = tt.find(blk(il, "attn_q.weight")) != nullptr;
+            QB_REQUIRE(has_q == m->is_attn(il), "model: layer %u %s attn_q.weight but full_attention_interval = %u says otherwise", il,
+                       has_q ? "has" : "lacks", c.full_attention_interval);
+            QB_TRY(bind_layer(ctx, m, tt, m->layers[il], il, !has_q));
+        }
+        QB_TRY(need_q8(tt, "token_embd.weight", V, H, &d));
+        QB_TRY(qb_weight_q8_0(ctx, d->data, V, H, &m->token_embd));
+        m->weight_bytes += weight_bytes_of(m->token_embd);
+        if (tt.find("output.weight")) {
+            QB_TRY(need_q8(tt, "output.weight", V, H, &d));
+            QB_TRY(qb_weight_q8_0(ctx, d->data, V, H, &m->output));
+            m->weight_bytes += weight_bytes_of(m->output);
+        } else {
+            m->output = m->token_embd;
+            m->output_tied = true;
+        }
+        QB_TRY(need_f32(ctx, m, tt, "output_norm.weight", "", H, &m->output_norm));
+        m->mtp_embd = m->token_embd; m->mtp_head = m->output; m->shared_head_norm = m->output_norm;
+        m->enorm = m->hnorm = m->ones;
+        if (c.mtp_layers) {
+            const uint32_t il = c.n_layers;
+            QB_TRY(bind_layer(ctx, m, tt, m->layers[il], il, false));
+            QB_TRY(need_q8(tt, blk(il, "nextn.eh_proj.weight"), H, 2 * H, &d));
+            QB_TRY(qb_weight_q8_0(ctx, d->data, H, 2 * H, &m->eh_proj));
+            m->weight_bytes += weight_bytes_of(m->eh_proj);
+            QB_TRY(need_f32(ctx, m, tt, blk(il, "nextn.enorm.weight"), "", H, &m->enorm));
+            QB_TRY(need_f32(ctx, m, tt, blk(il, "nextn.hnorm.weight"), "", H, &m->hnorm));
+            if (tt.find(blk(il, "nextn.shared_head_norm.weight")))
+                QB_TRY(need_f32(ctx, m, tt, blk(il, "nextn.shared_head_norm.weight"), "", H, &m->shared_head_norm));
+            if (tt.find(blk(il, "nextn.embed_tokens.weight"))) {
+                QB_TRY(need_q8(tt, blk(il, "nextn.embed_tokens.weight"), V, H, &d));
+                QB_TRY(qb_weight_q8_0(ctx, d->data, V, H, &m->mtp_embd));
+                m->weight_bytes += weight_bytes_of(m->mtp_embd);
+            }
+            if (tt.find(blk(il, "nextn.shared_head_head.weight"))) {
+                QB_TRY(need_q8(tt, blk(il, "nextn.shared_head_head.weight"), V, H, &d));
+                QB_TRY(qb_weight_q8_0(ctx, d->data, V, H, &m->mtp_head));
+                m->weight_bytes += weight_bytes_of(m->mtp_head);
+            }
+        }
+        link_prefetch_chain(m);
+        QB_CUDA(cudaStreamSynchronize(ctx->stream));     // the caller's host tensors may go away after the call
+        return QB_OK;
+    };
+    st = body();
+    if (st != QB_OK) { qb_model_destroy(ctx, m); return st; }
+    *out = m;
+    return QB_OK;
+}
+
+// Order in which a forward pass streams the weights (qb_weight::pf_next): in, out, gate/up, down of every layer, then
+// the LM head; the MTP head: eh_proj, its layer, its LM head, and back to eh_proj for the next draft.
+static void link_prefetch_chain(qb_model *m) {
+    const uint32_t n = m->cfg.n_layers;
+    for (uint32_t il = 0; il < n; ++il) {
+        LayerW &L = m->layers[il];
+        L.w_in->pf_next = L.w_out; L.w_out->pf_next = L.w_gate_up; L.w_gate_up->pf_next = L.w_down;
+        L.w_down->pf_next = il + 1 < n ? m->layers[il + 1].w_in : m->output;
+    }
+    if (m->cfg.mtp_layers && m->eh_proj) {
+        LayerW &L = m->layers[n];
+        m->eh_proj->pf_next = L.w_in; L.w_in->pf_next = L.w_out; L.w_out->pf_next = L.w_gate_up; L.w_gate_up->pf_next = L.w_down;
+        L.w_down->pf_next = m->mtp_head;
+        m->mtp_head->pf_next = m->eh_proj;
+        if (m->output != m->mtp_head) m->output->pf_next = m->eh_proj;
+    }
+}
+
+extern "C" const qb_model_config *qb_model_get_config(const qb_model *m) { return m ? &m->cfg : nullptr; }
+
 extern "C" void qb_model_destroy(qb_ctx *ctx, qb_model *m) {
     if (!m) return;
     cudaStreamSynchronize(ctx->stream);
+    std::vector<const float *> owned(m->owned_f32.begin(), m->owned_f32.end());
+    auto is_owned = [&](const float *p) { return std::find(owned.begin(), owned.end(), p) != owned.end(); };
     for (LayerW &L : m->layers) {
         qb_weight_free(ctx, L.w_in); qb_weight_free(ctx, L.w_out); qb_weight_free(ctx, L.w_gate_up); qb_weight_free(ctx, L.w_down);
-        if (L.conv_w) cudaFree(L.conv_w);
-        if (L.ssm_a) cudaFree(L.ssm_a);
-        if (L.dt_bias) cudaFree(L.dt_bias);
+        // the seeded constructor allocates these three itself; qb_model_create keeps them in owned_f32
+        if (L.conv_w && !is_owned(L.conv_w)) cudaFree(L.conv_w);
+        if (L.ssm_a && !is_owned(L.ssm_a)) cudaFree(L.ssm_a);
+        if (L.dt_bias && !is_owned(L.dt_bias)) cudaFree(L.dt_bias);
     }
-    qb_weight_free(ctx, m->token_embd); qb_weight_free(ctx, m->output); qb_weight_free(ctx, m->eh_proj);
-    cudaFree(m->ones); cudaFree(m->inv_freq);
+    if (m->mtp_embd && m->mtp_embd != m->token_embd) qb_weight_free(ctx, m->mtp_embd);
+    if (m->mtp_head && m->mtp_head != m->output) qb_weight_free(ctx, m->mtp_head);
+    if (!m->output_tied) qb_weight_free(ctx, m->output);
+    qb_weight_free(ctx, m->token_embd); qb_weight_free(ctx, m->eh_proj);
+    for (float *p : m->owned_f32) cudaFree(p);
+    if (m->ones) cudaFree(m->ones);
+    if (m->inv_freq) cudaFree(m->inv_freq);
     delete m;
 }
 extern "C" size_t qb_model_weight_bytes(const qb_model *m) { return m->weight_bytes; }
@@ -192,6 +411,12 @@ struct qb_batch {
     uint32_t *seen = nullptr;              // [n_seqs][seen_words] bitmap of prompt + emitted tokens (token penalties), or null
     uint32_t seen_words = 0;
     float pen_presence = 0.0f, pen_repetition = 1.0f;
+    int32_t *tok_stage = nullptr;          // pinned staging of the prompt tokens being ingested
+    uint32_t tok_stage_cap = 0;
+    double *first_draw_stage = nullptr;    // pinned: the first-token draw of a sampled request per sequence
+    int32_t *limit = nullptr;              // [n_seqs] device: draft depth of the next step per sequence (<= k)
+    int32_t *limit_host = nullptr;         // pinned staging of the same
+    int32_t eos_token = -1;                // a draft equal to it ends the chain (-1: none)
     void *swap_tmp = nullptr;              // one sequence's largest per-layer state block (qb_seq_swap)
     size_t swap_bytes = 0;
 };
@@ -258,7 +483,7 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
     }
     // control block
     {
-        const size_t n = (size_t)n_seqs * (16 + 4 * K1) + 4 * (size_t)rows + 256;
+        const size_t n = (size_t)n_seqs * (17 + 4 * K1) + 4 * (size_t)rows + 256;
         QB_CUDA(cudaMalloc(&b->ctl, n * sizeof(int32_t)));
         QB_CUDA(cudaMemsetAsync(b->ctl, 0, n * sizeof(int32_t), ctx->stream));
         int32_t *p = b->ctl;
@@ -269,6 +494,7 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
         b->prefix_tok = take((size_t)n_seqs * std::max(1u, draft_k));
         b->out_rec = take((size_t)n_seqs * (K1 + 2));
         b->map_prevh = take(n_seqs); b->map_prefix = take((size_t)n_seqs * K1); b->map_chunk = take(rows); b->map_last = take(n_seqs);
+        b->limit = take(n_seqs);
         std::vector<int32_t> prevh(n_seqs), mp((size_t)n_seqs * std::max(1u, draft_k));
         for (uint32_t s = 0; s < n_seqs; ++s) prevh[s] = (int32_t)(rows + s);
         for (uint32_t s = 0; s < n_seqs; ++s)
@@ -280,6 +506,10 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
         QB_CUDA(cudaMalloc(&b->stats, 4 * sizeof(long long)));
         QB_CUDA(cudaMemsetAsync(b->stats, 0, 4 * sizeof(long long), ctx->stream));
         QB_CUDA(cudaHostAlloc(&b->out_rec_host, (size_t)n_seqs * (K1 + 2) * sizeof(int32_t), cudaHostAllocDefault));
+        QB_CUDA(cudaHostAlloc(&b->limit_host, (size_t)n_seqs * sizeof(int32_t), cudaHostAllocDefault));
+        for (uint32_t s = 0; s < n_seqs; ++s) b->limit_host[s] = (int32_t)draft_k;
+        QB_CUDA(cudaMemcpyAsync(b->limit, b->limit_host, n_seqs * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        QB_CUDA(cudaStreamSynchronize(ctx->stream));
     }
     // activations
     const uint32_t inner = m->inner(), vdim = m->vdim(), F = c.n_ff, V = c.vocab_size;
@@ -333,6 +563,9 @@ extern "C" void qb_batch_destroy(qb_ctx *ctx, qb_batch *b) {
                     b->xq_attn.d, b->xq_dn.q, b->xq_dn.d, b->xq_ffn.q, b->xq_ffn.d, b->xq_cat.q, b->xq_cat.d, b->samp_u, b->seen, b->swap_tmp};
     for (void *p : ptrs) if (p) cudaFree(p);
     if (b->out_rec_host) cudaFreeHost(b->out_rec_host);
+    if (b->limit_host) cudaFreeHost(b->limit_host);
+    if (b->tok_stage) cudaFreeHost(b->tok_stage);
+    if (b->first_draw_stage) cudaFreeHost(b->first_draw_stage);
     delete b;
 }
 
@@ -409,7 +642,7 @@ __global__ void force_drafts_kernel(int32_t *drafts, const int32_t *pos, uint32_
 __global__ void accept_commit_kernel(const float *pval, const int32_t *pidx, uint32_t k, uint32_t rows_cap, uint32_t H,
                                      int32_t *pos, int32_t *sel, int32_t *cur, const int32_t *drafts, int32_t *prefix_pos,
                                      int32_t *prefix_tok, int32_t *out_rec, uint32_t n_seqs, float *hid,
-                                     unsigned long long *stats) {
+                                     unsigned long long *stats, const int32_t *limit, int32_t eos) {
     QB_PDL_ENTER();
     __shared__ int s_acc;
     __shared__ int am[8];
@@ -421,8 +654,15 @@ __global__ void accept_commit_kernel(const float *pval, const int32_t *pidx, uin
     }
     __syncthreads();
     if (threadIdx.x == 0) {
+        // chain length of this step: the caller's depth limit (min(k, tokens still wanted), MtpAdaptivePolicy::draft_limit,
+        // src/qwen_native_backend.cpp:1625-1628) cut before the first draft equal to the end-of-sequence token
+        // (:15817-15821); a chain of length 0 is one plain step (:15829-15848)
+        uint32_t kk = min(k, (uint32_t)max(limit[s], 0));
+        if (eos >= 0)
+            for (uint32_t i = 0; i < kk; ++i)
+                if (drafts[(size_t)s * k + i] == eos) { kk = i; break; }
         uint32_t a = 0;
-        while (a < k && am[a] == drafts[(size_t)s * k + a]) ++a;
+        while (a < kk && am[a] == drafts[(size_t)s * k + a]) ++a;
         int32_t *n_out = out_rec, *toks = out_rec + n_seqs, *opos = out_rec + n_seqs + (size_t)n_seqs * K1;
         for (uint32_t i = 0; i < a; ++i) toks[(size_t)s * K1 + i] = drafts[(size_t)s * k + i];
         toks[(size_t)s * K1 + a] = am[a];
@@ -436,7 +676,7 @@ __global__ void accept_commit_kernel(const float *pval, const int32_t *pidx, uin
         cur[s] = am[a];
         s_acc = (int)a;
         atomicAdd(&stats[0], 1ull);
-        atomicAdd(&stats[1], (unsigned long long)k);
+        atomicAdd(&stats[1], (unsigned long long)kk);
         atomicAdd(&stats[2], (unsigned long long)a);
         atomicAdd(&stats[3], (unsigned long long)(a + 1));
     }
@@ -492,15 +732,22 @@ __global__ void mark_seen_record_kernel(const int32_t *out_rec, uint32_t n_seqs,
     }
 }
 
-__global__ void swap_ctl_kernel(int32_t *pos, int32_t *sel, int32_t *cur, int32_t *prefix_pos, int32_t *out_rec, uint32_t n_seqs, uint32_t K1,
-                                uint32_t a, uint32_t b) {
+__global__ void swap_ctl_kernel(int32_t *pos, int32_t *sel, int32_t *cur, int32_t *prefix_pos, int32_t *out_rec, int32_t *limit, uint32_t n_seqs,
+                                uint32_t K1, uint32_t a, uint32_t b) {
     QB_PDL_ENTER();
     if (threadIdx.x == 0) {
         int32_t *n_out = out_rec, *toks = out_rec + n_seqs, *opos = out_rec + n_seqs + (size_t)n_seqs * K1;
-        int32_t *arr[6] = {pos, sel, cur, prefix_pos, n_out, opos};      // the step record follows its sequence
-        for (int i = 0; i < 6; ++i) { const int32_t t = arr[i][a]; arr[i][a] = arr[i][b]; arr[i][b] = t; }
+        int32_t *arr[7] = {pos, sel, cur, prefix_pos, n_out, opos, limit};      // the step record follows its sequence
+        for (int i = 0; i < 7; ++i) { const int32_t t = arr[i][a]; arr[i][a] = arr[i][b]; arr[i][b] = t; }
         for (uint32_t i = 0; i < K1; ++i) { const int32_t t = toks[(size_t)a * K1 + i]; toks[(size_t)a * K1 + i] = toks[(size_t)b * K1 + i]; toks[(size_t)b * K1 + i] = t; }
     }
+}
+
+// map[0] = the row that holds the previous chunk's last hidden, map[r] = r - 1 (prefill: hidden row feeding MTP row r)
+__global__ void chunk_map_kernel(int32_t *map, uint32_t M, int32_t prev_row) {
+    QB_PDL_ENTER();
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < M) map[r] = r == 0 ? prev_row : (int32_t)r - 1;
 }
 
 __global__ void advance_kernel(int32_t *pos, int32_t *sel, uint32_t s, int32_t adv, uint32_t rows_cap, uint32_t H, uint32_t last_row, float *hid) {
@@ -573,7 +820,7 @@ static int attention_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t c
     const uint32_t rows = rs.rows();
     AttnArgs a;
     a.rows = rows; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.hd = c.head_dim; a.rope_dim = c.rope_dim; a.eps = c.rms_eps;
-    a.q_norm_w = m->ones; a.k_norm_w = m->ones; a.inv_freq = m->inv_freq;
+    a.q_norm_w = L.q_norm; a.k_norm_w = L.k_norm; a.inv_freq = m->inv_freq;
     a.page_table = b->page_table + (size_t)rs.seq0 * b->pages_per_seq; a.pt_stride = b->pages_per_seq; a.page_size = b->page_size;
     a.k_cache = b->kc[cache_idx]; a.v_cache = b->vc[cache_idx];
     a.max_pos = rs.max_pos; a.part_acc = b->att_acc; a.part_ml = b->att_ml; a.kv_only = kv_only;
@@ -615,7 +862,7 @@ static int deltanet_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t il
     DnArgs d;
     d.proj = b->parts; d.proj_stride = m->dn_in(); d.proj_S = S_in; d.proj_pstride = (size_t)rows * m->dn_in();
     d.n_seqs = rs.ns; d.rows_per_seq = rs.R;
-    d.conv_w = L.conv_w; d.ssm_a = L.ssm_a; d.dt_bias = L.dt_bias; d.norm_w = m->ones;
+    d.conv_w = L.conv_w; d.ssm_a = L.ssm_a; d.dt_bias = L.dt_bias; d.norm_w = L.ssm_norm;
     d.nk = c.ssm_num_k_heads; d.nv = c.ssm_num_v_heads; d.hd = c.ssm_head_dim; d.eps = c.rms_eps;
     d.state = b->state[il] + (size_t)rs.seq0 * K1 * c.ssm_num_v_heads * c.ssm_head_dim * c.ssm_head_dim;
     const size_t conv_off = (size_t)rs.seq0 * K1 * m->qkv_dim() * 3;
@@ -638,12 +885,13 @@ static int target_forward(qb_ctx *ctx, qb_batch *b, const int32_t *tokens_dev, c
     QB_REQUIRE(rows <= b->rows_cap, "forward: %u rows exceed capacity %u", rows, b->rows_cap);
     float *h = b->hid;
     QB_TRY(qb_launch_get_rows(ctx, m->token_embd, tokens_dev, rows, h, c.n_embd));
-    QB_TRY(plain_norm_quant(ctx, b, h, nullptr, rows, m->ones, b->xq_h));
+    QB_TRY(plain_norm_quant(ctx, b, h, nullptr, rows, m->layers[0].attn_norm, b->xq_h));
     for (uint32_t il = 0; il < c.n_layers; ++il) {
         const LayerW &L = m->layers[il];
-        if (L.recurrent) QB_TRY(deltanet_block(ctx, b, L, il, h, rs, checkpoints, m->ones));
-        else QB_TRY(attention_block(ctx, b, L, il, h, rs, false, m->ones));
-        QB_TRY(ffn_block(ctx, b, L, h, rows, m->ones));   // the next norm is the next layer's attn_norm or output_norm
+        if (L.recurrent) QB_TRY(deltanet_block(ctx, b, L, il, h, rs, checkpoints, L.ffn_norm));
+        else QB_TRY(attention_block(ctx, b, L, il, h, rs, false, L.ffn_norm));
+        // the norm fused behind the FFN is the next layer's attn_norm, or output_norm after the last layer
+        QB_TRY(ffn_block(ctx, b, L, h, rows, il + 1 < c.n_layers ? m->layers[il + 1].attn_norm : m->output_norm));
     }
     // the DeltaNet layers read the conv windows from one buffer and wrote the new ones to the other: a forward over
     // every sequence just swaps the two; one over a subset copies its windows back so all sequences stay in one
@@ -669,7 +917,7 @@ static int target_forward(qb_ctx *ctx, qb_batch *b, const int32_t *tokens_dev, c
         std::vector<int32_t> map(rs.ns);
         for (uint32_t s = 0; s < rs.ns; ++s) map[s] = (int32_t)(s * rs.R + rs.R - 1);
         QB_CUDA(cudaMemcpyAsync(b->map_last, map.data(), rs.ns * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
-        QB_TRY(plain_norm_quant(ctx, b, h, b->map_last, rs.ns, m->ones, b->xq_h));
+        QB_TRY(plain_norm_quant(ctx, b, h, b->map_last, rs.ns, m->output_norm, b->xq_h));
         QB_TRY(gemm_to(ctx, b, m->output, b->xq_h, rs.ns, b->logits));
         QB_TRY(qb_launch_argmax_partial(ctx, b->logits, rs.ns, c.vocab_size, c.vocab_size, b->am_val, b->am_idx, QB_ARGMAX_BLOCKS));
         b->last_logit_rows = rs.ns;
@@ -686,17 +934,17 @@ static int mtp_forward(qb_ctx *ctx, qb_batch *b, const int32_t *tokens_dev, cons
     const qb_model_config &c = m->cfg;
     const uint32_t rows = rs.rows(), H = c.n_embd;
     const LayerW &L = m->layers[c.n_layers];
-    QB_TRY(qb_launch_get_rows(ctx, m->token_embd, tokens_dev, rows, b->embd, H));
-    QB_TRY(plain_norm_quant(ctx, b, b->embd, nullptr, rows, m->ones, b->xq_cat, 0));      // enorm
-    QB_TRY(plain_norm_quant(ctx, b, hsrc, hmap, rows, m->ones, b->xq_cat, H));             // hnorm
+    QB_TRY(qb_launch_get_rows(ctx, m->mtp_embd, tokens_dev, rows, b->embd, H));
+    QB_TRY(plain_norm_quant(ctx, b, b->embd, nullptr, rows, m->enorm, b->xq_cat, 0));     // enorm
+    QB_TRY(plain_norm_quant(ctx, b, hsrc, hmap, rows, m->hnorm, b->xq_cat, H));            // hnorm
     uint32_t S = 1;
     QB_TRY(gemm_parts(ctx, b, m->eh_proj, b->xq_cat, rows, &S));
-    QB_TRY(residual_norm_quant(ctx, b, b->mtp_h, rows, S, m->ones, b->xq_h, 0, /*add_x=*/false));
-    QB_TRY(attention_block(ctx, b, L, c.n_layers, b->mtp_h, rs, kv_only, m->ones));
+    QB_TRY(residual_norm_quant(ctx, b, b->mtp_h, rows, S, L.attn_norm, b->xq_h, 0, /*add_x=*/false));
+    QB_TRY(attention_block(ctx, b, L, c.n_layers, b->mtp_h, rs, kv_only, L.ffn_norm));
     if (kv_only) return QB_OK;
-    QB_TRY(ffn_block(ctx, b, L, b->mtp_h, rows, m->ones));   // next norm = shared_head_norm
+    QB_TRY(ffn_block(ctx, b, L, b->mtp_h, rows, m->shared_head_norm));
     QB_REQUIRE(rows <= b->logit_rows, "MTP logits rows exceed capacity");
-    QB_TRY(gemm_to(ctx, b, m->output, b->xq_h, rows, b->logits));
+    QB_TRY(gemm_to(ctx, b, m->mtp_head, b->xq_h, rows, b->logits));
     QB_TRY(qb_launch_argmax_partial(ctx, b->logits, rows, c.vocab_size, c.vocab_size, b->am_val, b->am_idx, QB_ARGMAX_BLOCKS));
     b->last_logit_rows = rows;
     return QB_OK;
@@ -736,19 +984,34 @@ extern "C" int qb_batch_set_penalties(qb_ctx *ctx, qb_batch *b, float presence, 
     return QB_OK;
 }
 
-extern "C" int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n) {
+// Prompt ingestion of one sequence in chunks.  more_follows: the prompt continues in a later call, so the last row needs
+// no logits, no token is committed, nothing is counted as emitted or seen beyond the prompt tokens themselves.  samp
+// (temp > 0): the first token is drawn from the last row (pick_from_last_logits, src/qwen_native_backend.cpp:15399-15428:
+// penalties against the prompt, then sample_token with the request's first draw) instead of its argmax.
+static int prefill_impl(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n, bool more_follows,
+                        const qb_sampling *samp) {
     QB_REQUIRE(ctx && b && tokens_host && n > 0 && seq < b->n_seqs, "qb_prefill: bad arguments");
-    QB_REQUIRE((uint32_t)b->host_pos[seq] + n + b->k + 1 <= b->max_ctx + b->k + 1 && (uint32_t)b->host_pos[seq] + n <= b->max_ctx,
-               "qb_prefill: %u tokens at position %d exceed max_ctx %u", n, b->host_pos[seq], b->max_ctx);
+    QB_REQUIRE((uint32_t)b->host_pos[seq] + n <= b->max_ctx, "qb_prefill: %u tokens at position %d exceed max_ctx %u", n, b->host_pos[seq],
+               b->max_ctx);
+    QB_REQUIRE(!samp || samp->temp > 0.0f, "qb_prefill_sampled: temp must be > 0 (temp <= 0 is the greedy qb_prefill)");
     QB_CUDA(cudaSetDevice(ctx->device));
     qb_model *m = b->m;
     const qb_model_config &c = m->cfg;
     const uint32_t K1 = b->k + 1;
+    // pinned staging for the chunk's tokens: the copies are asynchronous and the caller's array may go away
+    if (b->tok_stage_cap < n) {
+        if (b->tok_stage) { QB_CUDA(cudaStreamSynchronize(ctx->stream)); QB_CUDA(cudaFreeHost(b->tok_stage)); b->tok_stage = nullptr; }
+        QB_CUDA(cudaHostAlloc(&b->tok_stage, (size_t)n * sizeof(int32_t), cudaHostAllocDefault));
+        b->tok_stage_cap = n;
+    } else {
+        QB_CUDA(cudaStreamSynchronize(ctx->stream));     // an earlier call's copies out of the staging area are done
+    }
+    memcpy(b->tok_stage, tokens_host, (size_t)n * sizeof(int32_t));
     for (uint32_t off = 0; off < n; off += b->chunk) {
         const uint32_t M = std::min(b->chunk, n - off);
-        const bool last = off + M == n;
+        const bool last = off + M == n && !more_follows;
         const uint32_t p0 = (uint32_t)b->host_pos[seq];
-        QB_CUDA(cudaMemcpyAsync(b->tok_buf, tokens_host + off, M * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        QB_CUDA(cudaMemcpyAsync(b->tok_buf, b->tok_stage + off, M * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
         if (b->seen) {
             QB_CUDA(qb_launch_pdl(ctx->stream, mark_seen_tokens_kernel, dim3((M + 127) / 128), dim3(128), (size_t)0, b->tok_buf, M,
                                   b->seen + (size_t)seq * b->seen_words, c.vocab_size));
@@ -758,14 +1021,23 @@ extern "C" int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t 
         rs.seq0 = seq; rs.ns = 1; rs.R = M; rs.seq_pos = b->pos + seq; rs.max_pos = p0 + M;
         QB_TRY(target_forward(ctx, b, b->tok_buf, rs, false, last ? 2 : 0));
         if (c.mtp_layers && b->k > 0) {
-            std::vector<int32_t> map(M);
-            map[0] = (int32_t)(b->rows_cap + seq);
-            for (uint32_t r = 1; r < M; ++r) map[r] = (int32_t)(r - 1);
-            QB_CUDA(cudaMemcpyAsync(b->map_chunk, map.data(), M * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
-            QB_CUDA(cudaStreamSynchronize(ctx->stream));   // map / token vectors go out of scope
+            // MTP-layer K/V of the chunk: row r pairs token r with the target hidden of row r-1 (row 0: the previous chunk's
+            // last hidden, kept behind the chunk rows)
+            QB_CUDA(qb_launch_pdl(ctx->stream, chunk_map_kernel, dim3((M + 127) / 128), dim3(128), (size_t)0, b->map_chunk, M,
+                                  (int32_t)(b->rows_cap + seq)));
+            QB_LAUNCHED(ctx, "chunk_map_kernel");
+            // the MTP pass overwrites the logits' argmax partials only in full mode; kv_only leaves them alone
             QB_TRY(mtp_forward(ctx, b, b->tok_buf, b->hid, b->map_chunk, rs, true));
         }
         if (last) {
+            if (samp) {
+                if (!b->samp_u) QB_CUDA(cudaMalloc(&b->samp_u, 2 * (size_t)b->n_seqs * K1 * sizeof(double)));
+                QB_CUDA(cudaMemcpyAsync(b->samp_u, &b->first_draw_stage[seq], sizeof(double), cudaMemcpyHostToDevice, ctx->stream));
+                QB_TRY(qb_launch_sample_rows(ctx, b->logits, 1, c.vocab_size, c.vocab_size, nullptr, 0, b->samp_u, b->samp_u, samp->temp,
+                                             samp->top_p, samp->top_k, samp->min_p, nullptr, nullptr, nullptr, b->am_val, b->am_idx,
+                                             QB_ARGMAX_BLOCKS, b->pen_presence, b->pen_repetition,
+                                             b->seen ? b->seen + (size_t)seq * b->seen_words : nullptr, b->seen_words));
+            }
             QB_CUDA(qb_launch_pdl(ctx->stream, greedy_commit_kernel, dim3(1), dim3(256), (size_t)(0), b->am_val, b->am_idx, 0, M - 1, 0, seq, 1, K1, b->rows_cap, c.n_embd,
                                                            b->pos, b->sel, b->cur, (int32_t)M, b->out_rec, b->n_seqs, b->hid,
                                                            (unsigned long long *)b->stats));
@@ -776,9 +1048,27 @@ extern "C" int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t 
             QB_LAUNCHED(ctx, "advance_kernel");
         }
         b->host_pos[seq] += (int32_t)M;
-        QB_CUDA(cudaStreamSynchronize(ctx->stream));
     }
     return QB_OK;
+}
+
+extern "C" int qb_prefill(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n) {
+    return prefill_impl(ctx, b, seq, tokens_host, n, false, nullptr);
+}
+
+// A part of a prompt that is not its end: K/V, recurrent state and the MTP prefix advance, no token is chosen.
+extern "C" int qb_prefill_chunk(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n) {
+    return prefill_impl(ctx, b, seq, tokens_host, n, true, nullptr);
+}
+
+// The end of a sampled request's prompt: the first token is drawn with the request's first uniform draw u.
+extern "C" int qb_prefill_sampled(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n, const qb_sampling *samp,
+                                  double u) {
+    QB_REQUIRE(b && samp && seq < b->n_seqs, "qb_prefill_sampled: bad arguments");
+    if (!b->first_draw_stage) QB_CUDA(cudaHostAlloc(&b->first_draw_stage, (size_t)b->n_seqs * sizeof(double), cudaHostAllocDefault));
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    b->first_draw_stage[seq] = u;
+    return prefill_impl(ctx, b, seq, tokens_host, n, false, samp);
 }
 
 static int check_room(qb_batch *b, uint32_t need) {
@@ -860,7 +1150,7 @@ extern "C" int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b) {
     const uint32_t ns = b->n_active, k = b->k;
     QB_CUDA(qb_launch_pdl(ctx->stream, accept_commit_kernel, dim3(ns), dim3(256), (size_t)(0), b->am_val, b->am_idx, k, b->rows_cap, c.n_embd, b->pos, b->sel, b->cur, b->drafts,
                                                     b->prefix_pos, b->prefix_tok, b->out_rec, b->n_seqs, b->hid,
-                                                    (unsigned long long *)b->stats));
+                                                    (unsigned long long *)b->stats, (const int32_t *)b->limit, b->eos_token));
     QB_LAUNCHED(ctx, "accept_commit_kernel");
     QB_TRY(mark_seen_record(ctx, b, 0, ns));
     // MTP-layer K/V of positions old_pos+1 .. old_pos+k from (draft_i, target hidden of row i-1); the
@@ -872,12 +1162,26 @@ extern "C" int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b) {
     return QB_OK;
 }
 
+// Chain policy of the speculative loop (src/qwen_native_backend.cpp:1625-1628, 15817-15848): limits_host[s] = draft depth of
+// sequence s from the next step on (the reference passes min(k, tokens still wanted), at least 1; 0 here makes the step
+// a plain one), eos_token = the token that ends a chain when drafted (-1: none, the reference's ignore_eos).  NULL limits
+// restore depth k everywhere.  The verify forward still runs k+1 rows; the cut-off drafts are simply not compared.
+extern "C" int qb_batch_set_draft_policy(qb_ctx *ctx, qb_batch *b, const int32_t *limits_host, int32_t eos_token) {
+    QB_REQUIRE(ctx && b, "qb_batch_set_draft_policy: null argument");
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));        // the staging buffer may still be read by an earlier copy
+    for (uint32_t s = 0; s < b->n_seqs; ++s) b->limit_host[s] = limits_host ? std::min<int32_t>(std::max<int32_t>(limits_host[s], 0), (int32_t)b->k) : (int32_t)b->k;
+    QB_CUDA(cudaMemcpyAsync(b->limit, b->limit_host, b->n_seqs * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+    b->eos_token = eos_token;
+    return QB_OK;
+}
+
 // Sampling-mode acceptance (speculative_accept_pointmass, src/qwen_native_backend.cpp:399-467): every verifier row takes
 // its decision on the device from the logits the verify forward left, and hands the commit kernel the decided token in
 // place of the row's argmax -- the draft itself when accepted, the residual draw when rejected, the bonus draw on the last
 // row -- so the longest-matching-prefix commit that follows is the reference's accept loop.  u_host: double [n_seqs][k+1],
 // the caller's uniform draws in the order its generator is consumed: row i accepts with u[i]; a rejection at row i draws
-// its residual with u[i+1]; the bonus draw is u[k].  A step consumes accepted + 1 of them.
+// its residual with u[i+1]; the bonus draw is u[k].  A step that rejects after `a` acceptances consumes a + 2 of them
+// (a + 1 acceptance tests and the residual draw), a fully accepted chain all k + 1.
 extern "C" int qb_mtp_sample_rows(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host) {
     QB_REQUIRE(ctx && b && u_host && b->k > 0, "qb_mtp_sample_rows: needs draws and a batch with draft depth > 0");
     QB_CUDA(cudaSetDevice(ctx->device));
@@ -1000,7 +1304,7 @@ extern "C" int qb_seq_swap(qb_ctx *ctx, qb_batch *b, uint32_t s1, uint32_t s2) {
     QB_TRY(swap_block(b->page_table, (size_t)b->pages_per_seq * sizeof(int32_t)));
     QB_TRY(swap_block(b->hid + (size_t)b->rows_cap * c.n_embd, (size_t)c.n_embd * sizeof(float)));
     if (b->seen) QB_TRY(swap_block(b->seen, (size_t)b->seen_words * sizeof(uint32_t)));
-    QB_CUDA(qb_launch_pdl(ctx->stream, swap_ctl_kernel, dim3(1), dim3(32), (size_t)0, b->pos, b->sel, b->cur, b->prefix_pos, b->out_rec, b->n_seqs, K1, s1, s2));
+    QB_CUDA(qb_launch_pdl(ctx->stream, swap_ctl_kernel, dim3(1), dim3(32), (size_t)0, b->pos, b->sel, b->cur, b->prefix_pos, b->out_rec, b->limit, b->n_seqs, K1, s1, s2));
     QB_LAUNCHED(ctx, "swap_ctl_kernel");
     std::swap(b->host_pos[s1], b->host_pos[s2]);
     return QB_OK;

@@ -182,7 +182,7 @@ __global__ void __launch_bounds__((TcCfg<MT, NLD>::THREADS))
 gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensorMap map_xq,
                const __grid_constant__ CUtensorMap map_xd, uint32_t K, uint32_t N, uint32_t M, float *__restrict__ part,
                uint32_t S, uint32_t tiles, uint32_t units, int *err_flag, unsigned long long *tl,
-               const __grid_constant__ QbGemmPush push, const QbGemmSwiglu swz) {
+               const __grid_constant__ QbGemmPush push, const QbGemmSwiglu swz, const QbGemmPrefetch pf) {
     using C = TcCfg<MT, NLD>;
     constexpr uint32_t NST = C::NST, NSLOT = C::NSLOT;
     extern __shared__ uint8_t smem_raw[];
@@ -274,6 +274,22 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
                 if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) break;
                 load_w(c, st);
                 load_x(c, st);
+            }
+            // Every load of this CTA is requested.  While the last stages land and the kernels between this GEMM and
+            // the next one run, ask the L2 for the first records each CTA of the next GEMM will read.
+            if (pf.count && !*abort_flag) {
+                const uint32_t per_m = pf.tiles * pf.S;
+                for (uint32_t bb = blockIdx.x; bb < pf.grid; bb += gridDim.x) {
+                    uint32_t done = 0;
+                    for (uint32_t u = bb; u < pf.units && done < pf.count; u += pf.grid) {
+                        const uint32_t rem = u % per_m, seg = rem / pf.tiles, tile = rem % pf.tiles;
+                        const uint32_t cb = tc_seg_begin(seg, pf.S, pf.nchunks), n_it = tc_seg_begin(seg + 1, pf.S, pf.nchunks) - cb;
+                        for (uint32_t it = 0; it < n_it && done < pf.count; ++it, ++done) {
+                            const uint8_t *src = pf.rec + ((size_t)tile * pf.nchunks + cb + it) * QB_REC_BYTES;
+                            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(QB_REC_BYTES) : "memory");
+                        }
+                    }
+                }
             }
         }
     } else if (warp == 1) {
@@ -508,6 +524,20 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
     const uint32_t tiles = w->rows_pad / 128;
     const uint32_t units = tiles * S * ((M + MT - 1) / MT);
     const uint32_t grid = std::min<uint32_t>(units, (uint32_t)ctx->sm_count * C::CTAS_PER_SM);
+    // L2 prefetch of the next weight's head (QW3B200_L2PF = records per CTA of the next launch, 0 = off): the next
+    // launch is assumed to run the same number of activation rows, which is what a forward pass does
+    static const uint32_t pf_count = []() {
+        const char *e = getenv("QW3B200_L2PF");
+        return (e && *e) ? (uint32_t)strtoul(e, nullptr, 10) : 0u;
+    }();
+    QbGemmPrefetch pf;
+    if (pf_count && w->pf_next && w->pf_next->rec && !push) {
+        const qb_weight *nx = w->pf_next;
+        pf.rec = nx->rec; pf.nchunks = nx->cols / 128; pf.tiles = nx->rows_pad / 128; pf.S = qb_ksplit(nx->rows, nx->cols);
+        pf.units = pf.tiles * pf.S * ((M + MT - 1) / MT);
+        pf.grid = std::min<uint32_t>(pf.units, (uint32_t)ctx->sm_count * C::CTAS_PER_SM);
+        pf.count = pf_count;
+    }
     const size_t smem_bytes = C::TOTAL;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -521,7 +551,7 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
     cfg.numAttrs = 1;
     QB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, NLD>, (const uint8_t *)w->rec, iq->second, id->second, K, w->rows, M, part, S,
                                tiles, units, ctx->err_flag_dev, qb_timeline_slot(ctx, grid, (double)w->rows_pad * K / 32.0 * 34.0 + (double)M * K * 1.125 + (double)S * M * w->rows * 4.0), push ? *push : QbGemmPush(),
-                               swiglu ? *swiglu : QbGemmSwiglu()));
+                               swiglu ? *swiglu : QbGemmSwiglu(), pf));
     if (grid_out) *grid_out = grid;
     QB_LAUNCHED(ctx, "gemm_tc_kernel");
     return QB_OK;

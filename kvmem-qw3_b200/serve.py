@@ -7,7 +7,8 @@ recurrent state) and the next pending request is prefilled into it while the oth
 slots (an idle slot decodes from its reset state and is reset again before it runs out of context); because a row's
 result never depends on which other rows share a launch, a request's tokens are the ones it would get alone.
 
-`engine` is anything with n_seqs, k, max_ctx, prefill(seq, tokens), mtp_step() or greedy_step(), read_output(), reset(seq):
+`engine` is anything with n_seqs, k, max_ctx, prefill(seq, tokens, more=False), prefill_sampled(seq, tokens, u, **sampling),
+mtp_step() / mtp_step_sampled(u, **sampling) or greedy_step(), read_output(), reset(seq):
 binding.Batch on the GPU, a fake in the CPU tests.
 """
 import collections
@@ -65,8 +66,9 @@ class SlotScheduler:
 
 class DrawQueue:
     """Uniform draws of one request in the order the reference consumes its generator (one std::mt19937_64 per request,
-    src/qwen_native_backend.cpp:399-467): a sampled step is handed k+1 draws and uses the first accepted + 1 of them; the
-    rest stay at the head of the queue for the next step."""
+    src/qwen_native_backend.cpp:399-467): the first draw picks the token after the prompt (pick_from_last_logits,
+    :15399-15428); a sampled step is handed k+1 draws; one that rejects after a acceptances has used a + 2 of them (a + 1
+    acceptance tests and the residual draw), a fully accepted chain all k + 1; the rest stay at the head of the queue."""
 
     def __init__(self, rng, width):
         self.rng, self.width, self.buf = rng, width, []
@@ -78,6 +80,15 @@ class DrawQueue:
 
     def consume(self, n):
         del self.buf[:n]
+
+    def consume_step(self, n_out):
+        """Draws used by a speculative step that emitted n_out tokens (accepted drafts + the residual or bonus token)."""
+        self.consume(self.width if n_out >= self.width else n_out + 1)
+
+    def take(self):
+        v = self.peek()[0]
+        self.consume(1)
+        return v
 
 
 def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=None, rng_of=None, prefill_chunk=0):
@@ -129,9 +140,16 @@ def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=
                 continue
             req, done_n = ingest[slot]
             n = len(req.prompt) - done_n if not prefill_chunk else min(prefill_chunk, len(req.prompt) - done_n)
-            engine.prefill(slot, req.prompt[done_n:done_n + n])
+            final = done_n + n == len(req.prompt)
+            if not final:
+                engine.prefill(slot, req.prompt[done_n:done_n + n], more=True)     # no token is chosen, nothing counted
+            elif sampling is not None:
+                draws[req.rid] = DrawQueue(rng_of(req), per_step)
+                engine.prefill_sampled(slot, req.prompt[done_n:], draws[req.rid].take(), **sampling)
+            else:
+                engine.prefill(slot, req.prompt[done_n:])
             ingest[slot][1] = done_n + n
-            if ingest[slot][1] < len(req.prompt):
+            if not final:
                 continue
             req.tokens.extend(engine.read_output()[slot])          # the prefill's last row gives the first token
             del ingest[slot]
@@ -144,8 +162,6 @@ def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=
             req.slot = target
             live.append(req)
             engine.set_active(len(live))
-            if sampling is not None:
-                draws[req.rid] = DrawQueue(rng_of(req), per_step)
             if req.done():
                 retire(target)
         if not live:
@@ -164,7 +180,7 @@ def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=
             req = live[s]
             req.tokens.extend(out[s])
             if sampling is not None:
-                draws[req.rid].consume(len(out[s]))
+                draws[req.rid].consume_step(len(out[s]))
             if req.done():
                 retire(s)
     return finished
@@ -195,9 +211,11 @@ def run(engine, requests, speculative=True, max_steps=1 << 30, sampling=None, rn
             if len(req.prompt) + req.max_new_tokens + per_step > engine.max_ctx:
                 raise ValueError("request %r does not fit max_ctx %d" % (req.rid, engine.max_ctx))
             engine.reset(req.slot)
-            engine.prefill(req.slot, req.prompt)
             if sampling is not None:
                 draws[req.slot] = DrawQueue(rng_of(req), per_step)
+                engine.prefill_sampled(req.slot, req.prompt, draws[req.slot].take(), **sampling)
+            else:
+                engine.prefill(req.slot, req.prompt)
             req.tokens.extend(engine.read_output()[req.slot])      # the prefill's last row gives the first token
             if req.done():
                 req._trim()
@@ -226,7 +244,7 @@ def run(engine, requests, speculative=True, max_steps=1 << 30, sampling=None, rn
                 continue
             req.tokens.extend(out[s])
             if sampling is not None:
-                draws[s].consume(len(out[s]))            # accepted + 1 draws were used
+                draws[s].consume_step(len(out[s]))
             if req.done():
                 req._trim()
                 finished.append(sched.retire(s, step))

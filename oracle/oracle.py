@@ -26,6 +26,11 @@ class ModelConfig(C.Structure):
     ]
 
 
+class TensorDesc(C.Structure):
+    """Mirror of qb_tensor_desc (include/qw3b200.h)."""
+    _fields_ = [("name", C.c_char_p), ("type", C.c_uint32), ("rows", C.c_uint64), ("cols", C.c_uint64), ("data", C.c_void_p)]
+
+
 def build(force=False):
     so = os.path.join(_HERE, "libqw3oracle.so")
     src = os.path.join(_HERE, "qw3_oracle.cpp")
@@ -39,6 +44,7 @@ def lib():
     if _LIB is None:
         _LIB = C.CDLL(build())
         _LIB.orc_model_create.restype = C.c_void_p
+        _LIB.orc_model_create_tensors.restype = C.c_void_p
         _LIB.orc_seq_create.restype = C.c_void_p
         _LIB.orc_ksplit_policy.restype = C.c_uint32
         _LIB.orc_last_logits.restype = C.c_uint32
@@ -240,6 +246,12 @@ def synth_prompt(seed, vocab, n):
     return out
 
 
+def rand_u32(seed, stream, n, i0=0):
+    out = np.empty(n, np.uint32)
+    lib().orc_rand_u32(C.c_uint64(seed), C.c_uint32(stream), C.c_uint64(i0), C.c_uint64(n), _p(out))
+    return out
+
+
 def num_threads():
     return int(lib().orc_num_threads())
 
@@ -248,6 +260,30 @@ class Model:
     def __init__(self, cfg, seed, max_layers=-1):
         self.cfg = cfg
         self.h = C.c_void_p(lib().orc_model_create(C.byref(cfg), C.c_uint64(seed), C.c_int32(max_layers)))
+
+    @classmethod
+    def from_tensors(cls, cfg, tensors):
+        """Model from named host tensors ({GGUF name: array}: uint8 [rows][cols/32*34] = Q8_0, float32 = F32)."""
+        self = cls.__new__(cls)
+        self.cfg = cfg
+        keep, descs = [], (TensorDesc * len(tensors))()
+        for i, (name, a) in enumerate(tensors.items()):
+            a = np.ascontiguousarray(a)
+            nb = name.encode()
+            keep += [a, nb]
+            if a.dtype == np.uint8:
+                descs[i] = TensorDesc(nb, 8, a.shape[0], a.shape[1] // 34 * 32, a.ctypes.data)
+            else:
+                assert a.dtype == np.float32, name
+                descs[i] = TensorDesc(nb, 0, a.size // a.shape[-1], a.shape[-1], a.ctypes.data)
+        self.h = C.c_void_p(lib().orc_model_create_tensors(C.byref(cfg), descs, C.c_size_t(len(tensors))))
+        if not self.h:
+            raise RuntimeError("oracle: a tensor of the model is missing or mis-shaped (see stderr)")
+        return self
+
+    def nudge_attn_norm(self, layer=0, ulps=1):
+        """Moves every attn_norm gain of `layer` by `ulps` units in the last place (noise-floor measurements)."""
+        lib().orc_model_nudge_attn_norm(self.h, C.c_uint32(layer), C.c_int32(ulps))
 
     def close(self):
         if self.h:

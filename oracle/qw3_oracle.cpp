@@ -25,6 +25,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <string>
 #include <vector>
 #ifdef _OPENMP
 #include <omp.h>
@@ -316,14 +317,22 @@ struct Layer {
     Q8 attn_q, attn_k, attn_v, attn_out, ffn_gate, ffn_up, ffn_down;
     Q8 ssm_qkv, ssm_z, ssm_alpha, ssm_beta, ssm_out;
     std::vector<float> conv_w, ssm_a, dt_bias;
+    // RMSNorm gains (src/qwen_native.cpp:160-186): attn_norm, ffn_norm / post_attention_norm, attn_q_norm, attn_k_norm, ssm_norm
+    std::vector<float> attn_norm, ffn_norm, q_norm, k_norm, ssm_norm;
 };
 
 struct Model {
     qb_model_config cfg;
     std::vector<Layer> layers;   // n_layers (+1 MTP layer at the end if cfg.mtp_layers)
     Q8 token_embd, output, eh_proj;
-    std::vector<float> ones;     // all RMSNorm gains are 1.0
+    // MTP head: its own embedding table / LM head when the checkpoint has them, else the target's
+    // (src/qwen_native.cpp:288-298); empty = shared
+    Q8 mtp_embd, mtp_head;
+    std::vector<float> output_norm, enorm, hnorm, shared_head_norm;
+    std::vector<float> ones;     // gains of the seeded model are 1.0
     std::vector<float> inv_freq;
+    const Q8 &mtp_embedding() const { return mtp_embd.rows ? mtp_embd : token_embd; }
+    const Q8 &mtp_lm_head() const { return mtp_head.rows ? mtp_head : output; }
     DnShape dn() const { return {cfg.ssm_num_k_heads, cfg.ssm_num_v_heads, cfg.ssm_head_dim, cfg.ssm_conv_kernel}; }
     bool is_attn(uint32_t i) const { return cfg.full_attention_interval && ((i + 1) % cfg.full_attention_interval) == 0; }
 };
@@ -384,7 +393,7 @@ struct Seq {
 void ffn_rows(const Model &m, const Layer &L, float *h, uint32_t M) {
     const uint32_t H = m.cfg.n_embd, F = m.cfg.n_ff;
     std::vector<float> n((size_t)M * H), g((size_t)M * F), u((size_t)M * F), dn((size_t)M * H);
-    for (uint32_t r = 0; r < M; ++r) rms_norm(h + (size_t)r * H, m.ones.data(), H, m.cfg.rms_eps, &n[(size_t)r * H]);
+    for (uint32_t r = 0; r < M; ++r) rms_norm(h + (size_t)r * H, L.ffn_norm.data(), H, m.cfg.rms_eps, &n[(size_t)r * H]);
     linear(L.ffn_gate, 2 * F, n.data(), M, H, g.data(), F);
     linear(L.ffn_up, 2 * F, n.data(), M, H, u.data(), F);
     for (size_t i = 0; i < g.size(); ++i) g[i] = siluf_(g[i]) * u[i];
@@ -400,7 +409,7 @@ void attn_rows(const Model &m, const Layer &L, float *h, uint32_t M, int base,
     const uint32_t H = c.n_embd, hd = c.head_dim, inner = c.n_heads * hd, kvd = c.n_kv_heads * hd;
     const uint32_t fused = 2 * inner + 2 * kvd;
     std::vector<float> n((size_t)M * H), q((size_t)M * 2 * inner), k((size_t)M * kvd), v((size_t)M * kvd);
-    for (uint32_t r = 0; r < M; ++r) rms_norm(h + (size_t)r * H, m.ones.data(), H, c.rms_eps, &n[(size_t)r * H]);
+    for (uint32_t r = 0; r < M; ++r) rms_norm(h + (size_t)r * H, L.attn_norm.data(), H, c.rms_eps, &n[(size_t)r * H]);
     if (!kv_only) linear(L.attn_q, fused, n.data(), M, H, q.data(), 2 * inner);
     linear(L.attn_k, fused, n.data(), M, H, k.data(), kvd);
     linear(L.attn_v, fused, n.data(), M, H, v.data(), kvd);
@@ -408,7 +417,7 @@ void attn_rows(const Model &m, const Layer &L, float *h, uint32_t M, int base,
     for (uint32_t r = 0; r < M; ++r) {
         for (uint32_t hh = 0; hh < c.n_kv_heads; ++hh) {
             float *kp = &k[(size_t)r * kvd + hh * hd];
-            head_norm(kp, m.ones.data(), hd, c.rms_eps);
+            head_norm(kp, L.k_norm.data(), hd, c.rms_eps);
             rope_partial(kp, c.rope_dim, base + (int)r, m.inv_freq.data());
         }
         for (uint32_t i = 0; i < kvd; ++i) {   // kv_append_*_f16 (src/kernels_cuda.cu:8921-8969)
@@ -422,7 +431,7 @@ void attn_rows(const Model &m, const Layer &L, float *h, uint32_t M, int base,
     for (int64_t r = 0; r < (int64_t)M; ++r) {
         float *qr = &q[(size_t)r * 2 * inner];
         for (uint32_t hh = 0; hh < c.n_heads; ++hh) {
-            head_norm(qr + (size_t)hh * 2 * hd, m.ones.data(), hd, c.rms_eps);
+            head_norm(qr + (size_t)hh * 2 * hd, L.q_norm.data(), hd, c.rms_eps);
             rope_partial(qr + (size_t)hh * 2 * hd, c.rope_dim, base + (int)r, m.inv_freq.data());
         }
         attention_row(qr, c.n_heads, c.n_kv_heads, hd, (uint32_t)(base + r + 1), kc.data(), vc.data(),
@@ -444,14 +453,14 @@ void dn_rows(const Model &m, const Layer &L, float *h, uint32_t M, std::vector<f
     const uint32_t fused = C + vdim + 2 * d.nv;
     std::vector<float> n((size_t)M * H), proj((size_t)M * C), z((size_t)M * vdim), al((size_t)M * d.nv),
         be((size_t)M * d.nv), core((size_t)M * vdim), o((size_t)M * H);
-    for (uint32_t r = 0; r < M; ++r) rms_norm(h + (size_t)r * H, m.ones.data(), H, c.rms_eps, &n[(size_t)r * H]);
+    for (uint32_t r = 0; r < M; ++r) rms_norm(h + (size_t)r * H, L.attn_norm.data(), H, c.rms_eps, &n[(size_t)r * H]);
     linear(L.ssm_qkv, fused, n.data(), M, H, proj.data(), C);
     linear(L.ssm_z, fused, n.data(), M, H, z.data(), vdim);
     linear(L.ssm_alpha, fused, n.data(), M, H, al.data(), d.nv);
     linear(L.ssm_beta, fused, n.data(), M, H, be.data(), d.nv);
     for (uint32_t r = 0; r < M; ++r) {
         deltanet_row(d, &proj[(size_t)r * C], &z[(size_t)r * vdim], &al[(size_t)r * d.nv], &be[(size_t)r * d.nv],
-                     L.conv_w.data(), L.ssm_a.data(), L.dt_bias.data(), m.ones.data(), c.rms_eps,
+                     L.conv_w.data(), L.ssm_a.data(), L.dt_bias.data(), L.ssm_norm.data(), c.rms_eps,
                      state.data(), conv.data(), &core[(size_t)r * vdim]);
         if (ck_state) { (*ck_state)[r] = state; (*ck_conv)[r] = conv; }
     }
@@ -495,7 +504,7 @@ void target_forward(Seq &s, const int *tokens, uint32_t M, int base, std::vector
         const uint32_t R = M - logits_from;
         std::vector<float> n((size_t)R * H);
         for (uint32_t r = 0; r < R; ++r)
-            rms_norm(&hidden[(size_t)(logits_from + r) * H], m.ones.data(), H, m.cfg.rms_eps, &n[(size_t)r * H]);
+            rms_norm(&hidden[(size_t)(logits_from + r) * H], m.output_norm.data(), H, m.cfg.rms_eps, &n[(size_t)r * H]);
         logits->assign((size_t)R * V, 0.0f);
         linear(m.output, V, n.data(), R, H, logits->data(), V);
     }
@@ -510,10 +519,10 @@ void mtp_rows(Seq &s, const int *tokens, const float *hprev, uint32_t M, int bas
     const uint32_t H = m.cfg.n_embd, V = m.cfg.vocab_size;
     const Layer &L = m.layers[m.cfg.n_layers];
     std::vector<float> e((size_t)M * H), cat((size_t)M * 2 * H), hh((size_t)M * H);
-    embed_rows(m.token_embd, tokens, M, e.data());
+    embed_rows(m.mtp_embedding(), tokens, M, e.data());
     for (uint32_t r = 0; r < M; ++r) {
-        rms_norm(&e[(size_t)r * H], m.ones.data(), H, m.cfg.rms_eps, &cat[(size_t)r * 2 * H]);            // enorm
-        rms_norm(hprev + (size_t)r * H, m.ones.data(), H, m.cfg.rms_eps, &cat[(size_t)r * 2 * H + H]);    // hnorm
+        rms_norm(&e[(size_t)r * H], m.enorm.data(), H, m.cfg.rms_eps, &cat[(size_t)r * 2 * H]);            // enorm
+        rms_norm(hprev + (size_t)r * H, m.hnorm.data(), H, m.cfg.rms_eps, &cat[(size_t)r * 2 * H + H]);    // hnorm
     }
     linear(m.eh_proj, H, cat.data(), M, 2 * H, hh.data(), H);
     attn_rows(m, L, hh.data(), M, base, s.mtp_k, s.mtp_v, kv_only);
@@ -521,9 +530,9 @@ void mtp_rows(Seq &s, const int *tokens, const float *hprev, uint32_t M, int bas
     ffn_rows(m, L, hh.data(), M);
     if (logits) {
         std::vector<float> n((size_t)M * H);
-        for (uint32_t r = 0; r < M; ++r) rms_norm(&hh[(size_t)r * H], m.ones.data(), H, m.cfg.rms_eps, &n[(size_t)r * H]);
+        for (uint32_t r = 0; r < M; ++r) rms_norm(&hh[(size_t)r * H], m.shared_head_norm.data(), H, m.cfg.rms_eps, &n[(size_t)r * H]);
         logits->assign((size_t)M * V, 0.0f);
-        linear(m.output, V, n.data(), M, H, logits->data(), V);
+        linear(m.mtp_lm_head(), V, n.data(), M, H, logits->data(), V);
     }
     if (mtp_h_out) *mtp_h_out = hh;
 }
@@ -894,9 +903,91 @@ void *orc_model_create(const qb_model_config *cfg, uint64_t seed, int32_t max_la
     }
     q8_synth(seed, tid(0xFFFF, T_TOKEN_EMBD), c.vocab_size, c.n_embd, c.weight_sigma, m->token_embd);
     q8_synth(seed, tid(0xFFFF, T_OUTPUT), c.vocab_size, c.n_embd, c.weight_sigma, m->output);
+    for (Layer &L : m->layers) {
+        L.attn_norm.assign(c.n_embd, 1.0f); L.ffn_norm.assign(c.n_embd, 1.0f);
+        L.q_norm.assign(c.head_dim, 1.0f); L.k_norm.assign(c.head_dim, 1.0f); L.ssm_norm.assign(c.ssm_head_dim, 1.0f);
+    }
+    m->output_norm.assign(c.n_embd, 1.0f); m->enorm = m->hnorm = m->shared_head_norm = m->output_norm;
+    return m;
+}
+
+// A model from named host tensors (the GGUF tensor set the reference binds, src/qwen_native.cpp:147-190 and
+// :271-298; same descriptor as the product's qb_model_create).  Returns null when a tensor is missing or mis-shaped.
+void *orc_model_create_tensors(const qb_model_config *cfg, const qb_tensor_desc *t, size_t n) {
+    auto find = [&](const std::string &name) -> const qb_tensor_desc * {
+        for (size_t i = 0; i < n; ++i) if (name == t[i].name) return &t[i];
+        return nullptr;
+    };
+    bool ok = true;
+    auto q8 = [&](const std::string &name, uint32_t rows, uint32_t cols, Q8 &w) {
+        const qb_tensor_desc *d = find(name);
+        if (!d || d->type != QB_TENSOR_Q8_0 || d->rows != rows || d->cols != cols) { fprintf(stderr, "oracle: bad tensor %s\n", name.c_str()); ok = false; return; }
+        q8_from_blocks((const uint8_t *)d->data, rows, cols, w);
+    };
+    auto f32 = [&](const std::string &name, size_t count, std::vector<float> &v, const std::string &alt = "") {
+        const qb_tensor_desc *d = find(name);
+        if (!d && !alt.empty()) d = find(alt);
+        if (!d || d->type != QB_TENSOR_F32 || d->rows * d->cols != count) { fprintf(stderr, "oracle: bad tensor %s\n", name.c_str()); ok = false; return; }
+        v.assign((const float *)d->data, (const float *)d->data + count);
+    };
+    Model *m = new Model();
+    m->cfg = *cfg;
+    const auto &c = m->cfg;
+    const uint32_t H = c.n_embd, V = c.vocab_size;
+    m->ones.assign(std::max({c.n_embd, c.head_dim, c.ssm_head_dim}), 1.0f);
+    make_inv_freq(c.rope_dim, c.rope_theta, m->inv_freq);
+    m->layers.resize(c.n_layers + (c.mtp_layers ? 1 : 0));
+    auto bind = [&](Layer &L, uint32_t il, bool recurrent) {
+        const std::string b = "blk." + std::to_string(il) + ".";
+        L.recurrent = recurrent;
+        f32(b + "attn_norm.weight", H, L.attn_norm);
+        f32(b + "ffn_norm.weight", H, L.ffn_norm, b + "post_attention_norm.weight");
+        if (!recurrent) {
+            const uint32_t inner = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim;
+            q8(b + "attn_q.weight", 2 * inner, H, L.attn_q); q8(b + "attn_k.weight", kvd, H, L.attn_k);
+            q8(b + "attn_v.weight", kvd, H, L.attn_v); q8(b + "attn_output.weight", H, inner, L.attn_out);
+            f32(b + "attn_q_norm.weight", c.head_dim, L.q_norm); f32(b + "attn_k_norm.weight", c.head_dim, L.k_norm);
+        } else {
+            const DnShape d = m->dn();
+            const uint32_t vdim = d.nv * d.hd;
+            q8(b + "attn_qkv.weight", d.qkv_dim(), H, L.ssm_qkv); q8(b + "attn_gate.weight", vdim, H, L.ssm_z);
+            q8(b + "ssm_alpha.weight", d.nv, H, L.ssm_alpha); q8(b + "ssm_beta.weight", d.nv, H, L.ssm_beta);
+            q8(b + "ssm_out.weight", H, vdim, L.ssm_out);
+            f32(b + "ssm_conv1d.weight", (size_t)d.qkv_dim() * d.conv_k, L.conv_w);
+            f32(b + "ssm_a", d.nv, L.ssm_a); f32(b + "ssm_dt.bias", d.nv, L.dt_bias); f32(b + "ssm_norm.weight", d.hd, L.ssm_norm);
+        }
+        q8(b + "ffn_gate.weight", c.n_ff, H, L.ffn_gate); q8(b + "ffn_up.weight", c.n_ff, H, L.ffn_up);
+        q8(b + "ffn_down.weight", H, c.n_ff, L.ffn_down);
+    };
+    for (uint32_t il = 0; il < c.n_layers; ++il) bind(m->layers[il], il, find("blk." + std::to_string(il) + ".attn_q.weight") == nullptr);
+    q8("token_embd.weight", V, H, m->token_embd);
+    if (find("output.weight")) q8("output.weight", V, H, m->output); else m->output = m->token_embd;
+    f32("output_norm.weight", H, m->output_norm);
+    m->enorm = m->hnorm = m->ones; m->enorm.resize(H); m->hnorm.resize(H);
+    m->shared_head_norm = m->output_norm;
+    if (c.mtp_layers) {
+        const uint32_t il = c.n_layers;
+        const std::string b = "blk." + std::to_string(il) + ".nextn.";
+        bind(m->layers[il], il, false);
+        q8(b + "eh_proj.weight", H, 2 * H, m->eh_proj);
+        f32(b + "enorm.weight", H, m->enorm); f32(b + "hnorm.weight", H, m->hnorm);
+        if (find(b + "shared_head_norm.weight")) f32(b + "shared_head_norm.weight", H, m->shared_head_norm);
+        if (find(b + "embed_tokens.weight")) q8(b + "embed_tokens.weight", V, H, m->mtp_embd);
+        if (find(b + "shared_head_head.weight")) q8(b + "shared_head_head.weight", V, H, m->mtp_head);
+    }
+    if (!ok) { delete m; return nullptr; }
     return m;
 }
 void orc_model_destroy(void *mp) { delete (Model *)mp; }
+// Moves every gain of one layer's attn_norm by `ulps` units in the last place: the smallest change an equally valid
+// fp32 implementation could make.  The tests measure how far the logits move under it (the int8 re-quantisation of
+// the activations before every projection turns it into rounding flips), i.e. the noise floor of the model itself.
+void orc_model_nudge_attn_norm(void *mp, uint32_t layer, int32_t ulps) {
+    Model *m = (Model *)mp;
+    if (layer >= m->layers.size()) return;
+    for (float &g : m->layers[layer].attn_norm)
+        for (int32_t i = 0; i < (ulps < 0 ? -ulps : ulps); ++i) g = std::nextafterf(g, ulps > 0 ? 2.0f * g + 1.0f : -1.0f);
+}
 
 void *orc_seq_create(void *mp, uint32_t max_ctx) {
     const Model *m = (const Model *)mp;
@@ -1031,6 +1122,12 @@ void orc_forward_rows(void *sp, const int32_t *tokens, uint32_t M, float *logits
 // Seeded prompt: uniform token ids in [0, vocab).
 void orc_synth_prompt(uint64_t seed, uint32_t vocab, uint32_t n, int32_t *out) {
     for (uint32_t i = 0; i < n; ++i) out[i] = (int32_t)(qs_rand_u32(seed, 0x7011u, i) % vocab);
+}
+
+// Raw draws of the seeded generator (stream = tensor id): lets the test-side checkpoint writer rebuild the small fp32
+// tensors of the seeded model (ssm_a, dt_bias, conv1d) with the recipe of build_layer.
+void orc_rand_u32(uint64_t seed, uint32_t stream, uint64_t i0, uint64_t n, uint32_t *out) {
+    for (uint64_t i = 0; i < n; ++i) out[i] = qs_rand_u32(seed, stream, i0 + i);
 }
 
 int orc_num_threads() {

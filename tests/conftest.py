@@ -72,3 +72,42 @@ def ref_attn():
     if not os.path.exists(path):
         return None
     return ctypes.CDLL(path)
+
+
+def rel_err(got, want):
+    """max |got - want| / max |want|: the relative logit error the step is specified in."""
+    return float(np.abs(got - want).max() / np.abs(want).max())
+
+
+def top2_margin(lg):
+    top = np.sort(lg)[-2:]
+    return float((top[1] - top[0]) / np.abs(lg).max())
+
+
+def greedy_noise_floor(orc, omodel, prompt, steps, chunk=0, max_ctx=None):
+    """Noise floor of a model under the smallest change an equally valid fp32 implementation could make: the logits of
+    `steps` teacher-forced greedy steps with every attn_norm gain of layer 0 moved by one unit in the last place,
+    against the unmoved model.  Returns the per-step max-relative logit differences.  The network re-quantises its
+    activations to int8 before every projection, so the move flips rounding decisions and the difference is the
+    rounding noise itself."""
+    max_ctx = max_ctx or len(prompt) + steps + 8
+    a = orc.Seq(omodel, max_ctx)
+    a.prefill(prompt, chunk)
+    base, toks = [a.last_logits(1)[0].copy()], [a.cur_token]
+    for _ in range(steps - 1):
+        a.greedy_step()
+        base.append(a.last_logits(1)[0].copy())
+        toks.append(a.cur_token)
+    omodel.nudge_attn_norm(0, 1)
+    try:
+        b = orc.Seq(omodel, max_ctx)
+        b.prefill(prompt, chunk)
+        errs = []
+        for i in range(steps):
+            if i:
+                b.greedy_step()
+            errs.append(rel_err(b.last_logits(1)[0], base[i]))
+            b.set_cur_token(toks[i])
+    finally:
+        omodel.nudge_attn_norm(0, -1)
+    return errs

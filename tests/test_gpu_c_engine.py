@@ -3,19 +3,19 @@
 import numpy as np
 import pytest
 
-from conftest import tiny_ocfg
+from conftest import greedy_noise_floor, tiny_ocfg
 
 pytestmark = pytest.mark.gpu
 
 LOGIT_TOL = 1e-2     # max |gpu - oracle| / max |oracle|, the bound the step is specified to
 # The network re-quantises its activations to int8 before every projection.  Two fp32 implementations
 # that differ in the last bit somewhere (device rsqrt/exp, reduction order) take different rounding
-# decisions from then on, so their logits differ at the level of the int8 rounding noise itself
-# (about 0.6% of the logit range on this 256-wide model, measured, with single steps up to about twice
-# that).  Over a run of single-row steps the mean stays inside LOGIT_TOL and every step inside ROW_CAP;
-# in the 4-row verify block the later rows also consume the earlier rows' freshly written K/V and DeltaNet
-# state, so the first row must meet LOGIT_TOL and every row ROW_CAP.
-ROW_CAP = 2e-2
+# decisions from then on, so their logits differ at the level of the int8 rounding noise itself.  The
+# tests therefore measure that level on the oracle (greedy_noise_floor: the oracle against itself with one
+# norm gain vector moved by one unit in the last place; about 1.6 % worst step, 1 % mean on this 256-wide
+# model) and require: mean over a run and the first step inside LOGIT_TOL, and every step and verify row
+# inside max(LOGIT_TOL, measured floor): a step may not differ from the oracle by more than the oracle
+# differs from its own one-ulp neighbour.
 
 
 @pytest.fixture(scope="module")
@@ -24,7 +24,9 @@ def tiny(qb, orc, ctx):
     model = qb.Model(ctx, cfg, qb.configs.MODEL_SEED)
     omodel = orc.Model(tiny_ocfg(orc, qb), qb.configs.MODEL_SEED)
     prompt = orc.synth_prompt(qb.configs.PROMPT_SEED + 1, cfg.vocab_size, 64)
-    yield dict(cfg=cfg, model=model, omodel=omodel, prompt=prompt)
+    floor = greedy_noise_floor(orc, omodel, prompt, 32, 64)
+    print("tiny model noise floor (one-ulp nudge): max %.3g mean %.3g" % (max(floor), float(np.mean(floor))))
+    yield dict(cfg=cfg, model=model, omodel=omodel, prompt=prompt, row_cap=max(LOGIT_TOL, max(floor)))
     model.close()
 
 
@@ -51,7 +53,7 @@ def margin(lg):
 
 
 def test_prefill_logits_and_greedy_stream_vs_oracle(qb, orc, ctx, tiny):
-    """Logits within LOGIT_TOL of the oracle on average and ROW_CAP at every step; the token agrees wherever the oracle's
+    """Logits within LOGIT_TOL of the oracle on average and within the measured noise floor at every step; the token agrees wherever the oracle's
     top-2 margin exceeds the tolerance (on a near-tie the oracle is steered to the GPU's token so
     both keep decoding the same sequence)."""
     b = qb.Batch(tiny["model"], 1, 256, 1)
@@ -66,12 +68,12 @@ def test_prefill_logits_and_greedy_stream_vs_oracle(qb, orc, ctx, tiny):
         tok = b.read_output()[0][0]
         lg, want_lg = b.last_logits(1)[0], s.last_logits(1)[0]
         errs.append(rel_err(lg, want_lg))
-        assert errs[-1] < ROW_CAP, (step, errs)
+        assert errs[-1] < tiny["row_cap"], (step, errs, tiny["row_cap"])
         if tok != s.cur_token:
             assert margin(want_lg) < 2 * LOGIT_TOL, (step, tok, s.cur_token)
             near_ties += 1
             s.set_cur_token(tok)
-    print("greedy logit rel err: max %.3g mean %.3g, near ties %d" % (max(errs), float(np.mean(errs)), near_ties))
+    print("greedy logit rel err: max %.3g mean %.3g (cap %.3g), near ties %d" % (max(errs), float(np.mean(errs)), tiny["row_cap"], near_ties))
     assert float(np.mean(errs)) < LOGIT_TOL and errs[0] < LOGIT_TOL, errs
     assert near_ties <= 3
     assert b.position(0) == 64 + 31
@@ -112,7 +114,7 @@ def test_mtp_step_pieces_match_oracle(qb, orc, ctx, tiny):
         otoks, _, orows = s.mtp_step(3, drafts)
         olg = s.last_logits(4)
         per_row = [rel_err(lg[r], olg[r]) for r in range(4)]
-        assert per_row[0] < LOGIT_TOL and max(per_row) < ROW_CAP, (step, per_row)
+        assert per_row[0] < LOGIT_TOL and max(per_row) < tiny["row_cap"], (step, per_row, tiny["row_cap"])
         rows = np.argmax(lg, 1).tolist()
         for r in range(4):
             assert rows[r] == orows[r] or margin(olg[r]) < 2 * LOGIT_TOL

@@ -192,3 +192,77 @@ def test_token_penalties_follow_the_running_prefix(qb, orc, ctx, model):
     tok, acc, _ = orc.sample_rows(penalise(logits[0, 0], seen0)[None], np.array([d], np.int32), u[0, 0:1], u[0, 1:2], temp, top_p, top_k, 0.0)
     assert b.read_output()[0][0] == int(tok[0])
     b.close()
+
+
+@pytest.mark.parametrize("penalties", [False, True])
+def test_sampled_stream_replays_through_one_continuous_generator(qb, orc, ctx, model, penalties):
+    """A whole sampled request, first token included, against the reference's generator order: ONE generator per request;
+    the first draw picks the token after the prompt (pick_from_last_logits), then every step draws one uniform per
+    acceptance test and one for the residual or bonus token (speculative_accept_pointmass).  The host loop hands the
+    step k+1 draws from a DrawQueue and returns the unused ones; the replay below consumes a fresh copy of the same
+    generator strictly in sequence through the oracle's sampler and must produce the same tokens."""
+    V, k = model.cfg.vocab_size, 3
+    temp, top_p, top_k, pres, rep = 0.9, 0.95, 0, 0.6, 1.25
+    prompt = orc.synth_prompt(321, V, 37)
+    b = qb.Batch(model, 1, 256, k)
+    if penalties:
+        b.set_penalties(pres, rep)
+    dq = qb.serve.DrawQueue(np.random.default_rng(77), k + 1)
+    replay = np.random.default_rng(77)
+
+    def penalise(row, toks):
+        if not penalties:
+            return row
+        row = row.copy()
+        idx = np.array(sorted(toks), np.int64)
+        v = row[idx]
+        row[idx] = np.where(v >= 0, v / np.float32(rep), v * np.float32(rep)).astype(np.float32) - np.float32(pres)
+        return row
+
+    one = lambda: np.array([replay.random()], np.float64)
+    # chunked ingestion: the parts of the prompt that are not its end choose no token and count nothing
+    b.prefill(0, prompt[:16], more=True)
+    b.prefill(0, prompt[16:30], more=True)
+    assert b.stats()["emitted"] == 0
+    b.prefill_sampled(0, prompt[30:], dq.take(), temp, top_p, top_k)
+    first = b.read_output()[0]
+    seen = set(int(t) for t in prompt)
+    tok, _, _ = orc.sample_rows(penalise(b.last_logits(1)[0], seen)[None], np.array([-1], np.int32), np.zeros(1), one(), temp, top_p, top_k, 0.0)
+    assert first == [int(tok[0])]
+    assert b.stats()["emitted"] == 1
+    seen |= set(first)
+    emitted, rejected, full = list(first), 0, 0
+    for step in range(14):
+        u = np.array([dq.peek()], np.float64)
+        b.mtp_draft()
+        b.mtp_verify()
+        logits = b.last_logits(k + 1).copy()
+        drafts = b.last_drafts()[0]
+        b.mtp_sample_rows(u, temp, top_p, top_k)
+        b.mtp_accept_commit()
+        out = b.read_output()[0]
+        dq.consume_step(len(out))
+        # the reference's loop on the continuous generator
+        want, ctxset = [], set(seen)
+        for i in range(k + 1):
+            d = int(drafts[i]) if i < k else -1
+            row = penalise(logits[i], ctxset)
+            if d >= 0:
+                ua = one()
+                _, acc, _ = orc.sample_rows(row[None], np.array([d], np.int32), ua, ua, temp, top_p, top_k, 0.0)
+                if acc[0]:
+                    want.append(d)
+                    ctxset.add(d)
+                    continue
+                t, _, _ = orc.sample_rows(row[None], np.array([d], np.int32), np.array([2.0]), one(), temp, top_p, top_k, 0.0)   # rejected: residual draw
+                want.append(int(t[0]))
+                rejected += 1
+                break
+            t, _, _ = orc.sample_rows(row[None], np.array([-1], np.int32), np.zeros(1), one(), temp, top_p, top_k, 0.0)               # bonus draw
+            want.append(int(t[0]))
+            full += 1
+        assert out == want, (step, out, want)
+        seen |= set(out)
+        emitted += out
+    assert rejected > 0
+    b.close()

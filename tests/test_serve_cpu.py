@@ -32,12 +32,18 @@ class FakeEngine:
         self.prompt[s], self.emitted[s], self.pos[s] = None, 0, 0
         self.resets.append(s)
 
-    def prefill(self, s, tokens):
+    def prefill(self, s, tokens, more=False):
         assert self.pos[s] == 0, "prefill into a slot that was not reset"
+        assert not more, "the fixed-slot loop ingests whole prompts"
         self.prompt[s] = list(tokens)
         self.pos[s] = len(tokens)
         self.out[s] = stream(self.prompt[s], 1)
         self.emitted[s] = 1
+
+    def prefill_sampled(self, s, tokens, u, **kw):
+        self.first_draws = getattr(self, "first_draws", {})
+        self.first_draws[tuple(tokens)] = u
+        self.prefill(s, tokens)
 
     def _step(self, width):
         self.steps += 1
@@ -116,7 +122,9 @@ def test_request_that_cannot_fit_is_refused():
 
 
 def test_sampled_serving_hands_each_request_its_draws_in_order():
-    """A sampled step gets k+1 draws per slot and consumes as many as it emitted tokens; the rest lead the next step."""
+    """The first draw of a request picks the token after its prompt; a sampled step gets k+1 draws per slot and consumes
+    n_out + 1 of them when it rejected (n_out - 1 acceptance tests that passed, the one that failed and the residual draw),
+    all k + 1 when the whole chain was accepted; the rest lead the next step."""
     serve = entry.load_package().serve
 
     class Counter:
@@ -153,11 +161,13 @@ def test_sampled_serving_hands_each_request_its_draws_in_order():
         out = eng2.read_output()
         for s in (0, 1):
             if eng2.prompt[s] is not None and emitted[s] < budget[s]:
-                used[s] += u[s][:len(out[s])]
-                emitted[s] += len(out[s])
+                n = len(out[s])
+                used[s] += u[s][:4 if n == 4 else n + 1]
+                emitted[s] += n
+    assert eng.first_draws == {(1, 2): 0.001, (3,): 0.101}
     for s, base in ((0, 0), (1, 100)):
         got = [round(v * 1000) for v in used[s]]
-        assert len(got) >= budget[s] - 1 and got == list(range(base + 1, base + 1 + len(got)))
+        assert len(got) >= budget[s] - 1 and got == list(range(base + 2, base + 2 + len(got)))
 
 
 class CompactEngine(FakeEngine):
@@ -176,12 +186,20 @@ class CompactEngine(FakeEngine):
         for arr in (self.prompt, self.emitted, self.pos, self.out):
             arr[a], arr[b] = arr[b], arr[a]
 
-    def prefill(self, s, tokens):
+    def prefill(self, s, tokens, more=False):
         assert s >= self.n_active, "prefill into a slot the decode steps are running"
         self.prompt[s] = (self.prompt[s] or []) + list(tokens)
         self.pos[s] += len(tokens)
+        if more:                                          # a part of the prompt: no token is chosen
+            self.out[s], self.emitted[s] = [], 0
+            return
+        assert self.emitted[s] == 0, "a token was chosen before the prompt was complete"
         self.out[s] = stream(self.prompt[s], 1)
         self.emitted[s] = 1
+
+    def reset(self, s):
+        super().reset(s)
+        self.emitted[s] = 0
 
     def _step(self, width):
         self.steps += 1
@@ -242,4 +260,5 @@ def test_compacting_loop_sampled_draws_follow_the_request_through_swaps():
     assert {r.rid: r.tokens for r in done} == {i: stream([i + 1], new) for i, new in enumerate([3, 12, 7])}
     for i in range(3):
         heads = eng.first[(i + 1,)]
-        assert heads[0] == 1000 * i + 1 and all(b > a for a, b in zip(heads, heads[1:])) and all(1000 * i < h < 1000 * (i + 1) for h in heads)
+        assert eng.first_draws[(i + 1,)] == 1000 * i + 1        # the request's first draw picked its first token
+        assert heads[0] == 1000 * i + 2 and all(b > a for a, b in zip(heads, heads[1:])) and all(1000 * i < h < 1000 * (i + 1) for h in heads)
