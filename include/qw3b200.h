@@ -352,6 +352,14 @@ int qb_batch_set_active(qb_ctx *ctx, qb_batch *b, uint32_t n);
 /* Exchange the contents of two sequence slots (page-table rows, DeltaNet state and conv windows, position, current
  * token, previous hidden row, seen-token record). */
 int qb_seq_swap(qb_ctx *ctx, qb_batch *b, uint32_t s1, uint32_t s2);
+/* StateSnapshot / capture_state / restore_state (src/qwen_executor.cpp:7285-7411): a snapshot holds what a later restore
+ * needs to continue every sequence of the batch from this point (positions, selected checkpoint slots, current tokens,
+ * previous hidden rows, every DeltaNet state slot and conv window, the seen-token record); the K/V caches are not copied
+ * (entries at or beyond a position are never read, entries below it never rewritten).  Restore into the same batch. */
+typedef struct qb_snapshot qb_snapshot;
+int  qb_batch_snapshot(qb_ctx *ctx, qb_batch *b, qb_snapshot **out);
+int  qb_batch_restore(qb_ctx *ctx, qb_batch *b, const qb_snapshot *snap);
+void qb_snapshot_free(qb_ctx *ctx, qb_snapshot *snap);
 /* Test aids: logits of the last verify/greedy/prefill rows (float [rows][vocab]) and hidden rows. */
 int qb_debug_last_logits(qb_ctx *ctx, qb_batch *b, float *host_out, uint32_t max_rows, uint32_t *rows_out);
 /* Drafts of the last qb_mtp_draft / qb_mtp_force_drafts: int32 [n_seqs][k] (test aid, syncs). */

@@ -109,6 +109,9 @@ SIGNATURES = {
     "qb_sample_rows": (i32, [vp, vp, u32, u32, u32, vp, vp, vp, C.c_float, C.c_float, i32, C.c_float, vp, vp, vp]),
     "qb_mtp_sample_rows": (i32, [vp, vp, C.c_float, C.c_float, i32, C.c_float, vp]),
     "qb_mtp_step_sampled": (i32, [vp, vp, C.c_float, C.c_float, i32, C.c_float, vp]),
+    "qb_batch_snapshot": (i32, [vp, vp, C.POINTER(vp)]),
+    "qb_batch_restore": (i32, [vp, vp, vp]),
+    "qb_snapshot_free": (None, [vp, vp]),
     "qb_debug_last_logits": (i32, [vp, vp, vp, u32, C.POINTER(u32)]),
     "qb_debug_last_drafts": (i32, [vp, vp, vp]),
     "qb_prof_enable": (i32, [vp, i32]),
@@ -539,6 +542,18 @@ class Batch:
 
     def swap(self, s1, s2):
         check(lib().qb_seq_swap(self.ctx.h, self.h, s1, s2))
+
+    def snapshot(self):
+        """Opaque snapshot of every sequence's state (see qb_batch_snapshot); free with free_snapshot."""
+        h = vp()
+        check(lib().qb_batch_snapshot(self.ctx.h, self.h, C.byref(h)))
+        return h
+
+    def restore(self, snap):
+        check(lib().qb_batch_restore(self.ctx.h, self.h, snap))
+
+    def free_snapshot(self, snap):
+        lib().qb_snapshot_free(self.ctx.h, snap)
 
     def position(self, seq):
         p = C.c_int32()

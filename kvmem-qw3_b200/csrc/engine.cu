@@ -421,6 +421,8 @@ struct qb_batch {
     size_t swap_bytes = 0;
 };
 
+static size_t ctl_count(const qb_batch *b);
+
 static int alloc_qbuf(QBuf &b, uint32_t rows, uint32_t K) {
     b.K = K;
     QB_CUDA(cudaMalloc(&b.q, (size_t)rows * K));
@@ -483,7 +485,8 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
     }
     // control block
     {
-        const size_t n = (size_t)n_seqs * (17 + 4 * K1) + 4 * (size_t)rows + 256;
+        b->rows_cap = rows;
+        const size_t n = ctl_count(b);
         QB_CUDA(cudaMalloc(&b->ctl, n * sizeof(int32_t)));
         QB_CUDA(cudaMemsetAsync(b->ctl, 0, n * sizeof(int32_t), ctx->stream));
         int32_t *p = b->ctl;
@@ -1308,6 +1311,80 @@ extern "C" int qb_seq_swap(qb_ctx *ctx, qb_batch *b, uint32_t s1, uint32_t s2) {
     QB_LAUNCHED(ctx, "swap_ctl_kernel");
     std::swap(b->host_pos[s1], b->host_pos[s2]);
     return QB_OK;
+}
+
+// ---- state snapshots (StateSnapshot / capture_state / restore_state, src/qwen_executor.cpp:7285-7411) ----------------
+// Everything a later restore needs to continue every sequence from this point: the control block (positions, selected
+// checkpoint slots, current tokens, step records), the previous hidden rows, every DeltaNet state slot and conv window,
+// the seen-token record.  The K/V caches are not copied: entries at or beyond a sequence's position are never read, and
+// entries below it are never rewritten.
+struct qb_snapshot {
+    std::vector<void *> bufs;
+    std::vector<int32_t> host_pos;
+    int conv_par = 0;
+    uint32_t n_active = 0;
+    size_t ctl_ints = 0;
+};
+
+static size_t ctl_count(const qb_batch *b) {
+    return (size_t)b->n_seqs * (17 + 4 * (b->k + 1)) + 4 * (size_t)b->rows_cap + 256;
+}
+
+template <typename F>
+static int for_each_state_block(qb_batch *b, F f) {
+    const qb_model_config &c = b->m->cfg;
+    const uint32_t K1 = b->k + 1;
+    const size_t ssz = (size_t)b->n_seqs * K1 * c.ssm_num_v_heads * c.ssm_head_dim * c.ssm_head_dim * sizeof(float);
+    const size_t csz = (size_t)b->n_seqs * K1 * b->m->qkv_dim() * 3 * sizeof(float);
+    QB_TRY(f((void *)b->ctl, ctl_count(b) * sizeof(int32_t)));
+    QB_TRY(f((void *)(b->hid + (size_t)b->rows_cap * c.n_embd), (size_t)b->n_seqs * c.n_embd * sizeof(float)));
+    QB_TRY(f((void *)b->stats, 4 * sizeof(long long)));
+    QB_TRY(f((void *)b->page_table, (size_t)b->n_seqs * b->pages_per_seq * sizeof(int32_t)));      // qb_seq_swap exchanges rows
+    for (uint32_t il = 0; il < c.n_layers; ++il) {
+        if (!b->state[il]) continue;
+        QB_TRY(f((void *)b->state[il], ssz));
+        QB_TRY(f((void *)b->conv[il], csz));
+        QB_TRY(f((void *)b->conv_alt[il], csz));
+    }
+    if (b->seen) QB_TRY(f((void *)b->seen, (size_t)b->n_seqs * b->seen_words * sizeof(uint32_t)));
+    return QB_OK;
+}
+
+extern "C" int qb_batch_snapshot(qb_ctx *ctx, qb_batch *b, qb_snapshot **out) {
+    QB_REQUIRE(ctx && b && out, "qb_batch_snapshot: null argument");
+    QB_CUDA(cudaSetDevice(ctx->device));
+    qb_snapshot *sn = new qb_snapshot();
+    int st = for_each_state_block(b, [&](void *src, size_t bytes) -> int {
+        void *dst = nullptr;
+        QB_CUDA(cudaMalloc(&dst, bytes));
+        sn->bufs.push_back(dst);
+        QB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        return QB_OK;
+    });
+    if (st != QB_OK) { for (void *p : sn->bufs) cudaFree(p); delete sn; return st; }
+    sn->host_pos = b->host_pos; sn->conv_par = b->conv_par; sn->n_active = b->n_active; sn->ctl_ints = ctl_count(b);
+    *out = sn;
+    return QB_OK;
+}
+
+extern "C" int qb_batch_restore(qb_ctx *ctx, qb_batch *b, const qb_snapshot *sn) {
+    QB_REQUIRE(ctx && b && sn && sn->ctl_ints == ctl_count(b) && sn->host_pos.size() == b->n_seqs, "qb_batch_restore: the snapshot is not of this batch");
+    QB_CUDA(cudaSetDevice(ctx->device));
+    size_t i = 0;
+    QB_TRY(for_each_state_block(b, [&](void *dst, size_t bytes) -> int {
+        QB_REQUIRE(i < sn->bufs.size(), "qb_batch_restore: the batch gained state since the snapshot");
+        QB_CUDA(cudaMemcpyAsync(dst, sn->bufs[i++], bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        return QB_OK;
+    }));
+    b->host_pos = sn->host_pos; b->conv_par = sn->conv_par; b->n_active = sn->n_active;
+    return QB_OK;
+}
+
+extern "C" void qb_snapshot_free(qb_ctx *ctx, qb_snapshot *sn) {
+    if (!sn) return;
+    cudaStreamSynchronize(ctx->stream);
+    for (void *p : sn->bufs) cudaFree(p);
+    delete sn;
 }
 
 extern "C" int qb_debug_last_logits(qb_ctx *ctx, qb_batch *b, float *host_out, uint32_t max_rows, uint32_t *rows_out) {

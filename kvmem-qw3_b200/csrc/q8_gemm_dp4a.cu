@@ -12,6 +12,9 @@
 // warp broadcasts.
 #include "qb_internal.h"
 
+int qb_prof_begin(qb_ctx *ctx);
+int qb_prof_end(qb_ctx *ctx, double bytes);
+
 namespace {
 
 constexpr int TILE_N = 128;
@@ -183,7 +186,12 @@ int qb_ffn_gate_up_swiglu(qb_ctx *ctx, const qb_weight *w, const int8_t *xq, con
     if (can_fuse && mode != 1) {
         QbGemmSwiglu sw;
         sw.q = hq; sw.d = hd; sw.q_pitch = hq_pitch; sw.d_ld = hd_ld;
-        return qb_launch_gemm_tc(ctx, w, xq, xd, M, nullptr, 1, nullptr, nullptr, &sw);
+        if (!ctx->prof_on) return qb_launch_gemm_tc(ctx, w, xq, xd, M, nullptr, 1, nullptr, nullptr, &sw);
+        QB_TRY(qb_prof_begin(ctx));
+        const int st = qb_launch_gemm_tc(ctx, w, xq, xd, M, nullptr, 1, nullptr, nullptr, &sw);
+        // weight once, int8 activations + scales in, int8 hidden + scales out (no fp32 partials leave the kernel)
+        QB_TRY(qb_prof_end(ctx, (double)w->rows * w->cols / 32.0 * 34.0 + (double)M * w->cols * 1.125 + (double)M * F * 1.125));
+        return st;
     }
     if (S == 1) {
         QB_TRY(qb_launch_gemm(ctx, w, xq, xd, M, act, 1, gemm_impl));
@@ -211,9 +219,8 @@ static double gemm_bytes(const qb_weight *w, uint32_t M, uint32_t S) {
     return (double)w->rows * w->cols / 32.0 * 34.0 + (double)M * w->cols * 1.125 + (double)S * M * w->rows * 4.0;
 }
 
-int qb_launch_gemm(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
-                   uint32_t S, int impl) {
-    if (!ctx->prof_on) return gemm_dispatch(ctx, w, q, d, M, part, S, impl);
+// Per-launch timing of the GEMM kernels (qb_prof_*): an event pair around the launch and its algorithmic bytes.
+int qb_prof_begin(qb_ctx *ctx) {
     if (ctx->prof_used + 2 > ctx->prof_ev.size()) {
         for (int i = 0; i < 256; ++i) {
             cudaEvent_t e;
@@ -222,10 +229,21 @@ int qb_launch_gemm(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float
         }
     }
     QB_CUDA(cudaEventRecord(ctx->prof_ev[ctx->prof_used], ctx->stream));
-    const int st = gemm_dispatch(ctx, w, q, d, M, part, S, impl);
+    return QB_OK;
+}
+int qb_prof_end(qb_ctx *ctx, double bytes) {
     QB_CUDA(cudaEventRecord(ctx->prof_ev[ctx->prof_used + 1], ctx->stream));
     ctx->prof_used += 2;
-    ctx->prof_bytes.push_back(gemm_bytes(w, M, S));
+    ctx->prof_bytes.push_back(bytes);
+    return QB_OK;
+}
+
+int qb_launch_gemm(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part,
+                   uint32_t S, int impl) {
+    if (!ctx->prof_on) return gemm_dispatch(ctx, w, q, d, M, part, S, impl);
+    QB_TRY(qb_prof_begin(ctx));
+    const int st = gemm_dispatch(ctx, w, q, d, M, part, S, impl);
+    QB_TRY(qb_prof_end(ctx, gemm_bytes(w, M, S)));
     return st;
 }
 
