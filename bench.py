@@ -279,7 +279,9 @@ class SpecRun:
         self.ns, self.plen = len(prompts), [len(p) for p in prompts]
         self.sched = accept_schedule(n_steps, warmup, k)
         n_tok = int((self.sched + 1).sum()) + k + 4
-        self.max_ctx = max(self.plen) + n_tok + 16
+        # room for every step at its upper bound: a device-resident loop does not read the step records, and the host's
+        # position mirror then advances by k + 1 per step
+        self.max_ctx = max(self.plen) + max(n_tok, (n_steps + 2) * (k + 1)) + 16
         self.stride = self.max_ctx + 8
         e0, e1 = ctx.event(), ctx.event()
         self.b = pkg.Batch(model, self.ns, self.max_ctx, k)

@@ -210,8 +210,63 @@ int qb_deltanet_rows(qb_ctx *ctx, const float *proj_dev, uint32_t n_seqs, uint32
                      float *state_dev, float *conv_dev, uint32_t n_slots, const int32_t *slot_in_dev, int write_all,
                      float *core_dev);
 
+/* recurrent_batch / recurrent_single_token with the interface's own tensors (device_backend.hpp:665-800): `batch`
+ * consecutive tokens of one sequence; proj / gate / alpha / beta are separate row-major tensors with their own strides;
+ * state = float [nv][hd][hd] and conv_state = float [qkv_dim][3] are updated to the values after the last token; with
+ * ckpt_count > 0 the state and conv window after token t < ckpt_count also go to state_ckpt[t] / conv_ckpt[t]
+ * (src/gated_delta_net.cu:165-176, src/kernels_cuda.cu:3682-3691).  core = float [batch][core_stride]. */
+int qb_recurrent_batch(qb_ctx *ctx, float *core, uint32_t core_stride, float *state, float *conv_state, const float *proj,
+                       uint32_t proj_stride, const float *gate, uint32_t gate_stride, const float *alpha, uint32_t alpha_stride,
+                       const float *beta, uint32_t beta_stride, const float *conv_w, const float *ssm_a, const float *dt_bias,
+                       const float *ssm_norm, uint32_t batch, uint32_t nk, uint32_t nv, uint32_t hd, float eps, float *state_ckpt,
+                       float *conv_ckpt, uint32_t ckpt_count);
+
 /* argmax_batch (src/kernels_cuda.cu:1765-1888, :20814): lowest index wins ties.  out_dev = int32 [M]. */
 int qb_argmax_rows(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t n, uint32_t stride, int32_t *out_dev);
+/* argmax / argmax_to_buffer / copy_argmax_buffer_to_host (include/qw3/device_backend.hpp:2456-2497): token and logit
+ * of row m go to tok_dev[out_offset + m] / val_dev[out_offset + m] (a DeviceArgmaxBuffer is the pair of arrays). */
+int qb_argmax_rows_val(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t n, uint32_t stride, int32_t *tok_dev, float *val_dev,
+                       uint32_t out_offset);
+
+/* ---- the operators the executor calls one by one -----------------------------------------------------------------
+ * The fused step launches none of these (norms, RoPE, K/V append and gating live inside its attention / DeltaNet /
+ * norm kernels); a DeviceBackend subclass over this library needs them to answer every virtual. */
+/* add, add_n (include/qw3/device_backend.hpp:639-647), mul (:649), silu (:648), silu_mul / silu_mul_n (:650-664;
+ * silu_mul_kernel src/kernels_cuda.cu:1894-1903).  out may alias an input. */
+int qb_add(qb_ctx *ctx, float *out, const float *a, const float *b, uint64_t n);
+int qb_mul(qb_ctx *ctx, float *out, const float *a, const float *b, uint64_t n);
+int qb_silu(qb_ctx *ctx, float *out, const float *x, uint64_t n);
+int qb_silu_mul(qb_ctx *ctx, float *out, const float *gate, const float *up, uint64_t n);
+/* rmsnorm_per_head / rmsnorm_per_head_batch (device_backend.hpp:948-974; src/kernels_cuda.cu:4622-4645): in place,
+ * unit u of row b at x + b*batch_stride + u*per_unit_stride, head_dim elements, one gain vector for all units. */
+int qb_rmsnorm_per_head(qb_ctx *ctx, float *x, const float *w, uint32_t batch, uint32_t batch_stride, uint32_t n_units,
+                        uint32_t per_unit_stride, uint32_t head_dim, float eps);
+/* rope_partial / rope_partial_batch / rope_partial_batch_positions (device_backend.hpp:975-1044; src/kernels_cuda.cu:
+ * 4697-4719, 4779-4799): rotates the first rope_dim elements of every unit, pairs (i, i + rope_dim/2); row b is at
+ * position base_pos + b, or positions_dev[b] when that is given. */
+int qb_rope_partial(qb_ctx *ctx, float *x, uint32_t batch, uint32_t batch_stride, uint32_t n_units, uint32_t per_unit_stride,
+                    uint32_t rope_dim, uint32_t base_pos, const int32_t *positions_dev, float theta);
+/* kv_append / kv_append_batch (device_backend.hpp:1047-1089; src/kernels_cuda.cu:8921-8949) when page_indices_dev is
+ * NULL, kv_append_batch_paged_device (:1090-1119, :8950-8969) otherwise: row b (per_pos_size floats) goes as fp16 to
+ * slot base_pos + b, or page_indices[pos / page_size] * page_size + pos % page_size. */
+int qb_kv_append(qb_ctx *ctx, void *cache_f16, const float *src, uint32_t base_pos, uint32_t per_pos_size, uint32_t batch,
+                 const int32_t *page_indices_dev, uint32_t n_pages, uint32_t page_size);
+/* apply_attn_gate / apply_attn_gate_batch (device_backend.hpp:2218-2262; src/kernels_cuda.cu:9448-9465):
+ * out[b][h][d] *= sigmoid(q[b*batch_stride_q + h*q_stride + head_dim + d]). */
+int qb_apply_attn_gate(qb_ctx *ctx, float *out, const float *q, uint32_t q_stride, uint32_t batch, uint32_t batch_stride_q,
+                       uint32_t batch_stride_out, uint32_t n_heads, uint32_t head_dim);
+/* attention_decode (device_backend.hpp:2204-2217): qb_attention_paged_gated without the output gate. */
+int qb_attention_paged(qb_ctx *ctx, const float *qkv_dev, uint32_t rows, uint32_t row_stride,
+                       uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                       const int32_t *seq_pos_dev, uint32_t n_seqs,
+                       const int32_t *page_table_dev, uint32_t page_table_stride, uint32_t page_size,
+                       const void *k_cache_dev, const void *v_cache_dev, uint32_t max_pos,
+                       float *out_dev);
+/* pack_mtp_prefix_hinputs (device_backend.hpp:2646-2660): dst[0] = first_h, dst[1..batch-1] = h_batch[0..batch-2], rows of
+ * h_stride floats.  pack_mtp_concat (:2662-2695): dst[row] = [left[row][0:width] | right[row][0:width]]. */
+int qb_pack_mtp_prefix_hinputs(qb_ctx *ctx, float *dst, const float *first_h, const float *h_batch, uint32_t batch, uint32_t h_stride);
+int qb_pack_mtp_concat(qb_ctx *ctx, float *dst, const float *left, const float *right, uint32_t batch, uint32_t left_stride,
+                       uint32_t right_stride, uint32_t concat_stride, uint32_t width);
 
 /* ---- model / sequences / the MTP step --------------------------------------------- */
 

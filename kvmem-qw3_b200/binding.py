@@ -78,7 +78,20 @@ SIGNATURES = {
     "qb_qk_norm_rope_append": (i32, [vp, vp, u32, u32, vp, vp, vp, u32, u32, u32, u32, f32, vp, u32, vp, u32, u32, vp, vp]),
     "qb_attention_paged_gated": (i32, [vp, vp, u32, u32, u32, u32, u32, vp, u32, vp, u32, u32, vp, vp, u32, vp]),
     "qb_deltanet_rows": (i32, [vp, vp, u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, f32, vp, vp, u32, vp, i32, vp]),
+    "qb_recurrent_batch": (i32, [vp, vp, u32, vp, vp, vp, u32, vp, u32, vp, u32, vp, u32, vp, vp, vp, vp, u32, u32, u32, u32, f32, vp, vp, u32]),
     "qb_argmax_rows": (i32, [vp, vp, u32, u32, u32, vp]),
+    "qb_argmax_rows_val": (i32, [vp, vp, u32, u32, u32, vp, vp, u32]),
+    "qb_add": (i32, [vp, vp, vp, vp, u64]),
+    "qb_mul": (i32, [vp, vp, vp, vp, u64]),
+    "qb_silu": (i32, [vp, vp, vp, u64]),
+    "qb_silu_mul": (i32, [vp, vp, vp, vp, u64]),
+    "qb_rmsnorm_per_head": (i32, [vp, vp, vp, u32, u32, u32, u32, u32, f32]),
+    "qb_rope_partial": (i32, [vp, vp, u32, u32, u32, u32, u32, u32, vp, f32]),
+    "qb_kv_append": (i32, [vp, vp, vp, u32, u32, u32, vp, u32, u32]),
+    "qb_apply_attn_gate": (i32, [vp, vp, vp, u32, u32, u32, u32, u32, u32]),
+    "qb_attention_paged": (i32, [vp, vp, u32, u32, u32, u32, u32, vp, u32, vp, u32, u32, vp, vp, u32, vp]),
+    "qb_pack_mtp_prefix_hinputs": (i32, [vp, vp, vp, vp, u32, u32]),
+    "qb_pack_mtp_concat": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32]),
     "qb_model_create_synth": (i32, [vp, C.POINTER(ModelConfig), u64, C.POINTER(vp)]),
     "qb_model_create": (i32, [vp, C.POINTER(ModelConfig), C.POINTER(TensorDesc), sz, C.POINTER(vp)]),
     "qb_model_load_gguf": (i32, [vp, C.c_char_p, C.POINTER(vp), C.POINTER(ModelConfig)]),

@@ -398,8 +398,11 @@ __global__ void attn_merge_kernel(AttnArgs a, const int32_t *__restrict__ seq_po
         }
         for (; s < cnt; ++s) { num = fmaf(acc[(size_t)s * hd], wsplit[s], num); den = fmaf(ml[s * 2], wsplit[s], den); }
     }
-    const float gate = qb_ldsum(a.qkv, (size_t)row * a.row_stride + (size_t)head * 2 * hd + hd + i, a.in_S, a.in_pstride);
-    const float o = __fdiv_rn(num, den) * __fdiv_rn(1.0f, 1.0f + expf(-gate));
+    float o = __fdiv_rn(num, den);
+    if (!a.no_gate) {
+        const float gate = qb_ldsum(a.qkv, (size_t)row * a.row_stride + (size_t)head * 2 * hd + hd + i, a.in_S, a.in_pstride);
+        o *= __fdiv_rn(1.0f, 1.0f + expf(-gate));
+    }
     const uint32_t col = head * hd + i;
     if (out) out[(size_t)row * a.n_heads * hd + col] = o;
     if (q8) {

@@ -51,6 +51,7 @@ extern "C" void qb_destroy(qb_ctx *ctx) {
     if (ctx->flush_buf) cudaFree(ctx->flush_buf);
     if (ctx->err_flag_dev) cudaFree(ctx->err_flag_dev);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->scratch2) cudaFree(ctx->scratch2);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -81,6 +82,20 @@ int qb_ctx_scratch(qb_ctx *ctx, size_t bytes, void **out) {
         ctx->scratch_bytes = want;
     }
     *out = ctx->scratch;
+    return QB_OK;
+}
+
+int qb_ctx_scratch2(qb_ctx *ctx, size_t bytes, void **out) {
+    if (bytes > ctx->scratch2_bytes) {
+        QB_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (ctx->scratch2) QB_CUDA(cudaFree(ctx->scratch2));
+        ctx->scratch2 = nullptr;
+        ctx->scratch2_bytes = 0;
+        const size_t want = bytes + (bytes >> 2) + (1u << 20);
+        QB_CUDA(cudaMalloc(&ctx->scratch2, want));
+        ctx->scratch2_bytes = want;
+    }
+    *out = ctx->scratch2;
     return QB_OK;
 }
 

@@ -337,11 +337,13 @@ static void link_prefetch_chain(qb_model *m) {
     for (uint32_t il = 0; il < n; ++il) {
         LayerW &L = m->layers[il];
         L.w_in->pf_next = L.w_out; L.w_out->pf_next = L.w_gate_up; L.w_gate_up->pf_next = L.w_down;
+        L.w_out->pf_wait = true;
         L.w_down->pf_next = il + 1 < n ? m->layers[il + 1].w_in : m->output;
     }
     if (m->cfg.mtp_layers && m->eh_proj) {
         LayerW &L = m->layers[n];
         m->eh_proj->pf_next = L.w_in; L.w_in->pf_next = L.w_out; L.w_out->pf_next = L.w_gate_up; L.w_gate_up->pf_next = L.w_down;
+        L.w_out->pf_wait = true;
         L.w_down->pf_next = m->mtp_head;
         m->mtp_head->pf_next = m->eh_proj;
         if (m->output != m->mtp_head) m->output->pf_next = m->eh_proj;

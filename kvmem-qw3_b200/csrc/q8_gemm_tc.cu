@@ -265,19 +265,10 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
             Cursor head = start(blockIdx.x), c = head;
             uint32_t npre = 0;
             for (; npre < NST && c.valid; ++npre, next(c)) load_w(c, npre);
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            if (tl) tl[blockIdx.x * 4 + 1] = qb_globaltimer();
-            c = head;
-            for (uint32_t g = 0; g < npre; ++g, next(c)) load_x(c, g);
-            for (uint32_t git = npre; c.valid; ++git, next(c)) {
-                const uint32_t st = git % NST, ph = (git / NST) & 1;
-                if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) break;
-                load_w(c, st);
-                load_x(c, st);
-            }
-            // Every load of this CTA is requested.  While the last stages land and the kernels between this GEMM and
-            // the next one run, ask the L2 for the first records each CTA of the next GEMM will read.
-            if (pf.count && !*abort_flag) {
+            // This GEMM waits for a slow predecessor (the DeltaNet or attention kernels) with its first stages already
+            // requested: meanwhile HBM would idle, so ask the L2 for the first records every CTA of the NEXT GEMM
+            // will read (a weight several times the size of this one).
+            if (pf.count) {
                 const uint32_t per_m = pf.tiles * pf.S;
                 for (uint32_t bb = blockIdx.x; bb < pf.grid; bb += gridDim.x) {
                     uint32_t done = 0;
@@ -290,6 +281,16 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
                         }
                     }
                 }
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (tl) tl[blockIdx.x * 4 + 1] = qb_globaltimer();
+            c = head;
+            for (uint32_t g = 0; g < npre; ++g, next(c)) load_x(c, g);
+            for (uint32_t git = npre; c.valid; ++git, next(c)) {
+                const uint32_t st = git % NST, ph = (git / NST) & 1;
+                if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) break;
+                load_w(c, st);
+                load_x(c, st);
             }
         }
     } else if (warp == 1) {
@@ -524,14 +525,15 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
     const uint32_t tiles = w->rows_pad / 128;
     const uint32_t units = tiles * S * ((M + MT - 1) / MT);
     const uint32_t grid = std::min<uint32_t>(units, (uint32_t)ctx->sm_count * C::CTAS_PER_SM);
-    // L2 prefetch of the next weight's head (QW3B200_L2PF = records per CTA of the next launch, 0 = off): the next
-    // launch is assumed to run the same number of activation rows, which is what a forward pass does
+    // L2 prefetch of the next weight's head while this launch waits for a slow predecessor (QW3B200_L2PF = records per
+    // CTA of the next launch, 0 = off; only weights flagged pf_wait): the next launch is assumed to run the same
+    // number of activation rows, which is what a forward pass does
     static const uint32_t pf_count = []() {
         const char *e = getenv("QW3B200_L2PF");
         return (e && *e) ? (uint32_t)strtoul(e, nullptr, 10) : 0u;
     }();
     QbGemmPrefetch pf;
-    if (pf_count && w->pf_next && w->pf_next->rec && !push) {
+    if (pf_count && w->pf_wait && w->pf_next && w->pf_next->rec && !push) {
         const qb_weight *nx = w->pf_next;
         pf.rec = nx->rec; pf.nchunks = nx->cols / 128; pf.tiles = nx->rows_pad / 128; pf.S = qb_ksplit(nx->rows, nx->cols);
         pf.units = pf.tiles * pf.S * ((M + MT - 1) / MT);

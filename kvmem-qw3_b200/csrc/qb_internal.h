@@ -94,8 +94,11 @@ struct qb_ctx {
     // scratch of the op-level entry points (grown on demand)
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
+    void *scratch2 = nullptr;              // second area for entry points that call another scratch user
+    size_t scratch2_bytes = 0;
 };
 int qb_ctx_scratch(qb_ctx *ctx, size_t bytes, void **out);
+int qb_ctx_scratch2(qb_ctx *ctx, size_t bytes, void **out);
 void qb_trace_mark(qb_ctx *ctx, const char *name);
 // Device timeline (qb_debug_timeline_*): while enabled every tensor-core GEMM launch gets a slot of
 // QB_TL_CTAS x 4 words; CTA b stores {entry, dependency wait passed, exit} in nanoseconds of the global
@@ -124,10 +127,11 @@ struct qb_weight {
     uint32_t rows = 0, cols = 0, rows_pad = 0;
     uint8_t *rec = nullptr;
     bool owns = false;
-    // The weight the step streams after this one (set by the model constructors): the tensor-core GEMM asks the L2
-    // for the head of it while its own last stages are still landing, so HBM keeps streaming through the small
-    // kernels that run between two GEMMs.
+    // The weight the step streams after this one, and whether this one's launches wait for a slow predecessor (the
+    // out-projection behind the DeltaNet / attention kernels): such a launch asks the L2 for the head of the next
+    // weight while it waits, so HBM keeps streaming.  Set by the model constructors.
     const qb_weight *pf_next = nullptr;
+    bool pf_wait = false;
 };
 __host__ __device__ inline size_t qb_rec_offset(uint32_t cols, uint32_t row, uint32_t chunk) {
     return ((size_t)(row >> 7) * (cols >> 7) + chunk) * QB_REC_BYTES;
@@ -284,6 +288,7 @@ struct AttnArgs {
     uint32_t max_pos = 0;            // upper bound of any row position (sizes the split grid)
     float *part_acc = nullptr, *part_ml = nullptr;   // split partials
     bool kv_only = false;            // prepare: skip the q heads
+    bool no_gate = false;            // merge: leave the output ungated (attention_decode + a separate apply_attn_gate)
     uint32_t split_keys = 0;         // keys per split (set by qb_attn_run)
 };
 int qb_attn_prepare(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t n_seqs);

@@ -327,6 +327,40 @@ __global__ void argmax_final_kernel(const float *pval, const int32_t *pidx, uint
     out[m] = bi;
 }
 
+// Same reduction, leaving the winning value beside the index (DeviceArgmax {token, logit}).
+__global__ void argmax_final_val_kernel(const float *pval, const int32_t *pidx, uint32_t nblk, int32_t *out, float *out_val, uint32_t out_off) {
+    const uint32_t m = blockIdx.x, lane = threadIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (uint32_t j = lane; j < nblk; j += 32) {
+        const float v = pval[(size_t)m * nblk + j];
+        const int i = pidx[(size_t)m * nblk + j];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int i = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+    if (lane == 0) { out[out_off + m] = bi; out_val[out_off + m] = bv; }
+}
+
+// argmax_to_buffer / argmax_batch with logits (include/qw3/device_backend.hpp:2456-2497): token and value of row m go to
+// tok_dev[out_offset + m], val_dev[out_offset + m].
+extern "C" int qb_argmax_rows_val(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t n, uint32_t stride, int32_t *tok_dev, float *val_dev,
+                                  uint32_t out_offset) {
+    QB_REQUIRE(ctx && x_dev && tok_dev && val_dev && M > 0 && n > 0, "qb_argmax_rows_val: bad arguments");
+    void *scr = nullptr;
+    const uint32_t nblk = QB_ARGMAX_BLOCKS;
+    QB_TRY(qb_ctx_scratch(ctx, (size_t)M * nblk * 8, &scr));
+    float *pval = (float *)scr;
+    int32_t *pidx = (int32_t *)(pval + (size_t)M * nblk);
+    QB_TRY(qb_launch_argmax_partial(ctx, x_dev, M, n, stride, pval, pidx, nblk));
+    argmax_final_val_kernel<<<M, 32, 0, ctx->stream>>>(pval, pidx, nblk, tok_dev, val_dev, out_offset);
+    QB_LAUNCHED(ctx, "argmax_final_val_kernel");
+    return QB_OK;
+}
+
 extern "C" int qb_argmax_rows(qb_ctx *ctx, const float *x_dev, uint32_t M, uint32_t n, uint32_t stride, int32_t *out_dev) {
     QB_REQUIRE(ctx && x_dev && out_dev && M > 0 && n > 0, "qb_argmax_rows: bad arguments");
     void *scr = nullptr;

@@ -8,6 +8,8 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 PATH = os.path.join(HERE, "_ref", "libqw3ref_backend.so")
+# the product's DeviceBackend subclass (kvmem-qw3_b200/shim/b200_device_backend.cpp) behind the same C driver
+B200_PATH = os.path.join(HERE, "_ref", "libqw3b200_backend.so")
 
 vp, u32, u64, f32, i32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_float, C.c_int
 
@@ -41,6 +43,14 @@ SIG = {
     "rb_q8_0_get_rows_batch": (i32, [vp, vp, vp, vp, u32]),
     "rb_silu_mul_n": (i32, [vp, vp, vp, vp, u64]),
     "rb_add_n": (i32, [vp, vp, vp, vp, u64]),
+    "rb_kv_append_batch_paged_device": (i32, [vp, vp, vp, u32, u32, u32, vp, u32, u32]),
+    "rb_attention_decode_batch_paged_gated_device": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, u32, u32, f32]),
+    "rb_q8_0_matvec": (i32, [vp, vp, vp, vp]),
+    "rb_q8_0_matvec_add": (i32, [vp, vp, vp, vp]),
+    "rb_argmax_to_buffer_roundtrip": (i32, [vp, vp, u32, u32, vp, vp]),
+    "rb_pack_mtp_concat": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32]),
+    "rb_pack_mtp_prefix_hinputs": (i32, [vp, vp, vp, vp, u32, u32]),
+    "rb_rms_norm_q8_0_matmul_fanout2": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, vp, vp, u32, u32, f32]),
 }
 
 
@@ -55,10 +65,12 @@ class RefError(RuntimeError):
 class RefBackend:
     """One reference backend instance (its own stream, cuBLAS handle and allocations)."""
 
-    def __init__(self, linear=1):
-        self.L = C.CDLL(PATH)
+    def __init__(self, linear=1, path=PATH):
+        self.L = C.CDLL(path)
         for name, (res, args) in SIG.items():
-            fn = getattr(self.L, name)
+            fn = getattr(self.L, name, None)
+            if fn is None:                       # a library built from an older driver source
+                continue
             fn.restype, fn.argtypes = res, args
         self.h = self.L.rb_create(linear)
         if not self.h:

@@ -126,5 +126,40 @@ int rb_silu_mul_n(void *b, void *out, void *gate, void *up, uint64_t count) {
     return st(B(b).silu_mul_n(T(out), T(gate), T(up), count));
 }
 int rb_add_n(void *b, void *out, void *a, void *c, uint64_t count) { return st(B(b).add_n(T(out), T(a), T(c), count)); }
+int rb_kv_append_batch_paged_device(void *b, void *cache, void *src, uint32_t base_pos, uint32_t per_pos_size, uint32_t batch, void *pages,
+                                    uint32_t n_pages, uint32_t page_size) {
+    return st(B(b).kv_append_batch_paged_device(T(cache), T(src), base_pos, per_pos_size, batch, T(pages), n_pages, page_size));
+}
+int rb_attention_decode_batch_paged_gated_device(void *b, void *out, void *q, uint32_t q_stride, void *k_cache, void *v_cache, void *pages,
+                                                 uint32_t n_pages, uint32_t page_size, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                                                 uint32_t base_seq_len, uint32_t batch, uint32_t q_batch_stride, uint32_t out_batch_stride, float scale) {
+    return st(B(b).attention_decode_batch_paged_gated_device(T(out), T(q), q_stride, T(k_cache), T(v_cache), T(pages), n_pages, page_size, n_heads,
+                                                             n_kv_heads, head_dim, base_seq_len, batch, q_batch_stride, out_batch_stride, scale));
+}
+int rb_q8_0_matvec(void *b, void *out, void *w, void *x) { return st(B(b).q8_0_matvec(T(out), W(w), T(x))); }
+int rb_q8_0_matvec_add(void *b, void *accum, void *w, void *x) { return st(B(b).q8_0_matvec_add(T(accum), W(w), T(x))); }
+int rb_argmax_to_buffer_roundtrip(void *b, void *x, uint32_t slots, uint32_t index, int32_t *token, float *logit) {
+    try {
+        auto buf = B(b).argmax_buffer(slots);
+        if (int r = st(B(b).argmax_to_buffer(T(x), *buf, index))) return r;
+        std::vector<DeviceArgmax> host(slots);
+        if (int r = st(B(b).copy_argmax_buffer_to_host(*buf, host.data(), slots))) return r;
+        *token = host[index].token; *logit = host[index].logit;
+        return 0;
+    } catch (const std::exception &e) { return fail(e.what()); }
+}
+int rb_pack_mtp_concat(void *b, void *dst, void *left, void *right, uint32_t batch, uint32_t ls, uint32_t rs, uint32_t cs, uint32_t width) {
+    return st(B(b).pack_mtp_concat(T(dst), T(left), T(right), batch, ls, rs, cs, width));
+}
+int rb_pack_mtp_prefix_hinputs(void *b, void *dst, void *first_h, void *h_batch, uint32_t batch, uint32_t h_stride) {
+    return st(B(b).pack_mtp_prefix_hinputs(T(dst), T(first_h), T(h_batch), batch, h_stride));
+}
+int rb_rms_norm_q8_0_matmul_fanout2(void *b, void *normalized, void *out0, void *out1, void *w0, void *w1, uint32_t os0, uint32_t os1, void *x,
+                                    void *norm_w, uint32_t batch, uint32_t in_stride, float eps) {
+    DeviceTensor *outs[2] = {&T(out0), &T(out1)};
+    const DeviceWeight *ws[2] = {&W(w0), &W(w1)};
+    const uint32_t strides[2] = {os0, os1};
+    return st(B(b).rms_norm_q8_0_matmul_fanout(T(normalized), outs, ws, strides, 2, T(x), W(norm_w), batch, in_stride, eps));
+}
 
 }  // extern "C"

@@ -84,6 +84,13 @@ def top2_margin(lg):
     return float((top[1] - top[0]) / np.abs(lg).max())
 
 
+def noise_cap(floor, tol=1e-2, slack=1.5):
+    """Bound for a max-relative logit error given the measured one-ulp noise floor of the model: the specified
+    tolerance, or `slack` x the largest floor sample where the model's own rounding noise is above it (the floor is a
+    maximum over a few steps of a heavy-tailed quantity; an error in the wiring moves logits by tens of percent)."""
+    return max(tol, slack * max(floor))
+
+
 def greedy_noise_floor(orc, omodel, prompt, steps, chunk=0, max_ctx=None):
     """Noise floor of a model under the smallest change an equally valid fp32 implementation could make: the logits of
     `steps` teacher-forced greedy steps with every attn_norm gain of layer 0 moved by one unit in the last place,

@@ -69,7 +69,7 @@ def test_model_with_gains_matches_oracle_and_gguf_path(qb, orc, ctx, G, tmp_path
         olg = s.last_logits(4)
         per_row = [rel_err(lg[step + 1][r], olg[r]) for r in range(4)]
         worst = max(worst, max(per_row))
-        assert per_row[0] < 1e-2 and max(per_row) < 2.5e-2, (step, per_row)     # later rows: inside the model's one-ulp noise floor
+        assert per_row[0] < 1e-2 and max(per_row) < 2.5e-2, (step, per_row)     # later rows: inside the tiny model's one-ulp noise band (1.6 % measured)
         rows = np.argmax(lg[step + 1], 1).tolist()
         if rows != orows:
             assert all(rows[r] == orows[r] or top2_margin(olg[r]) < 2e-2 for r in range(4))
