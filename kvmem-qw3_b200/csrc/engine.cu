@@ -116,7 +116,6 @@ static int build_layer(qb_ctx *ctx, qb_model *m, LayerW &L, uint32_t il, bool re
 }
 
 extern "C" void qb_model_destroy(qb_ctx *ctx, qb_model *m);
-static void link_prefetch_chain(qb_model *m);
 
 // Shape checks shared by every model constructor, the all-ones gain vector and the RoPE frequencies.
 static int model_begin(qb_ctx *ctx, const qb_model_config &c, qb_model **out) {
@@ -163,7 +162,6 @@ extern "C" int qb_model_create_synth(qb_ctx *ctx, const qb_model_config *cfg, ui
         m->output_norm = m->enorm = m->hnorm = m->shared_head_norm = m->ones;
         m->mtp_embd = m->token_embd;
         m->mtp_head = m->output;
-        link_prefetch_chain(m);
         QB_CUDA(cudaStreamSynchronize(ctx->stream));
         return QB_OK;
     };
@@ -320,7 +318,6 @@ extern "C" int qb_model_create(qb_ctx *ctx, const qb_model_config *cfg, const qb
                 m->weight_bytes += weight_bytes_of(m->mtp_head);
             }
         }
-        link_prefetch_chain(m);
         QB_CUDA(cudaStreamSynchronize(ctx->stream));     // the caller's host tensors may go away after the call
         return QB_OK;
     };
@@ -328,26 +325,6 @@ extern "C" int qb_model_create(qb_ctx *ctx, const qb_model_config *cfg, const qb
     if (st != QB_OK) { qb_model_destroy(ctx, m); return st; }
     *out = m;
     return QB_OK;
-}
-
-// Order in which a forward pass streams the weights (qb_weight::pf_next): in, out, gate/up, down of every layer, then
-// the LM head; the MTP head: eh_proj, its layer, its LM head, and back to eh_proj for the next draft.
-static void link_prefetch_chain(qb_model *m) {
-    const uint32_t n = m->cfg.n_layers;
-    for (uint32_t il = 0; il < n; ++il) {
-        LayerW &L = m->layers[il];
-        L.w_in->pf_next = L.w_out; L.w_out->pf_next = L.w_gate_up; L.w_gate_up->pf_next = L.w_down;
-        L.w_out->pf_wait = true;
-        L.w_down->pf_next = il + 1 < n ? m->layers[il + 1].w_in : m->output;
-    }
-    if (m->cfg.mtp_layers && m->eh_proj) {
-        LayerW &L = m->layers[n];
-        m->eh_proj->pf_next = L.w_in; L.w_in->pf_next = L.w_out; L.w_out->pf_next = L.w_gate_up; L.w_gate_up->pf_next = L.w_down;
-        L.w_out->pf_wait = true;
-        L.w_down->pf_next = m->mtp_head;
-        m->mtp_head->pf_next = m->eh_proj;
-        if (m->output != m->mtp_head) m->output->pf_next = m->eh_proj;
-    }
 }
 
 extern "C" const qb_model_config *qb_model_get_config(const qb_model *m) { return m ? &m->cfg : nullptr; }

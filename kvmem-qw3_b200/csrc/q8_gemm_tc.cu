@@ -18,122 +18,10 @@
 // (TMEM lane quarter = warp % 4; four warps for the small tiles, eight from 32 activation rows on).  Every wait is bounded: when a wait runs out
 // the CTA raises the context's error flag, lets its copies land, frees its TMEM and returns.
 #include "qb_internal.h"
+#include "tc_common.cuh"
 
 namespace {
-
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Bounded wait; returns false when the CTA is aborting.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if (*abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// D[tmem] = A[smem] * B[smem], int8 x int8 -> int32, no accumulation into D.
-__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
-}
-
-// K-major operand tile with 128-byte rows and the 128-byte swizzle: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    uint64_t d = (uint64_t)((addr >> 4) & 0x3FFFu);
-    d |= (uint64_t)1 << 16;                  // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024u >> 4) << 32;       // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                  // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
-    return d;
-}
-
-template <int N>
-__device__ __forceinline__ void tmem_ld(uint32_t taddr, int32_t *r);
-template <>
-__device__ __forceinline__ void tmem_ld<4>(uint32_t taddr, int32_t *r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr));
-}
-template <>
-__device__ __forceinline__ void tmem_ld<8>(uint32_t taddr, int32_t *r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr));
-}
-template <>
-__device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, int32_t *r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// The same wait, naming the 16 registers of an earlier (asynchronous) load as read-write operands: whatever
-// consumes them is then ordered after the wait by a data dependency, however far the load was issued ahead.
-__device__ __forceinline__ void tmem_ld_wait16(int32_t (&r)[16]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
-                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
-                 :: "memory");
-}
-
-// Two fp32 lanes per instruction (sm_100 packed arithmetic): each lane rounds exactly like the scalar operation.
-typedef unsigned long long f32x2;
-__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
-    f32x2 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
-    f32x2 d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-    f32x2 d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-
-__host__ __device__ inline uint32_t tc_seg_begin(uint32_t s, uint32_t S, uint32_t nchunks) {
-    return (uint32_t)(((uint64_t)s * nchunks) / S);
-}
+using namespace qbtc;
 
 // MT = activation rows per tile (MMA N).  NLD = accumulator columns the epilogue reads (<= MT).
 // A pipeline stage holds one weight record (17 KB, one bulk copy, already the swizzled operand image
@@ -170,11 +58,6 @@ struct TcCfg {
     static constexpr int NC = NLD / (EPI_WARPS / 4);             // accumulator columns per epilogue thread
 };
 
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-
 // Persistent kernel: CTA b works on units b, b + gridDim.x, ...; a unit is (activation tile, K segment,
 // 128-row weight tile).  The TMA / MMA / TMEM pipeline keeps running across unit boundaries.
 template <int MT, int NLD>
@@ -182,7 +65,7 @@ __global__ void __launch_bounds__((TcCfg<MT, NLD>::THREADS))
 gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensorMap map_xq,
                const __grid_constant__ CUtensorMap map_xd, uint32_t K, uint32_t N, uint32_t M, float *__restrict__ part,
                uint32_t S, uint32_t tiles, uint32_t units, int *err_flag, unsigned long long *tl,
-               const __grid_constant__ QbGemmPush push, const QbGemmSwiglu swz, const QbGemmPrefetch pf) {
+               const __grid_constant__ QbGemmPush push, const QbGemmSwiglu swz) {
     using C = TcCfg<MT, NLD>;
     constexpr uint32_t NST = C::NST, NSLOT = C::NSLOT;
     extern __shared__ uint8_t smem_raw[];
@@ -265,23 +148,6 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
             Cursor head = start(blockIdx.x), c = head;
             uint32_t npre = 0;
             for (; npre < NST && c.valid; ++npre, next(c)) load_w(c, npre);
-            // This GEMM waits for a slow predecessor (the DeltaNet or attention kernels) with its first stages already
-            // requested: meanwhile HBM would idle, so ask the L2 for the first records every CTA of the NEXT GEMM
-            // will read (a weight several times the size of this one).
-            if (pf.count) {
-                const uint32_t per_m = pf.tiles * pf.S;
-                for (uint32_t bb = blockIdx.x; bb < pf.grid; bb += gridDim.x) {
-                    uint32_t done = 0;
-                    for (uint32_t u = bb; u < pf.units && done < pf.count; u += pf.grid) {
-                        const uint32_t rem = u % per_m, seg = rem / pf.tiles, tile = rem % pf.tiles;
-                        const uint32_t cb = tc_seg_begin(seg, pf.S, pf.nchunks), n_it = tc_seg_begin(seg + 1, pf.S, pf.nchunks) - cb;
-                        for (uint32_t it = 0; it < n_it && done < pf.count; ++it, ++done) {
-                            const uint8_t *src = pf.rec + ((size_t)tile * pf.nchunks + cb + it) * QB_REC_BYTES;
-                            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(QB_REC_BYTES) : "memory");
-                        }
-                    }
-                }
-            }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             if (tl) tl[blockIdx.x * 4 + 1] = qb_globaltimer();
             c = head;
@@ -525,21 +391,6 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
     const uint32_t tiles = w->rows_pad / 128;
     const uint32_t units = tiles * S * ((M + MT - 1) / MT);
     const uint32_t grid = std::min<uint32_t>(units, (uint32_t)ctx->sm_count * C::CTAS_PER_SM);
-    // L2 prefetch of the next weight's head while this launch waits for a slow predecessor (QW3B200_L2PF = records per
-    // CTA of the next launch, 0 = off; only weights flagged pf_wait): the next launch is assumed to run the same
-    // number of activation rows, which is what a forward pass does
-    static const uint32_t pf_count = []() {
-        const char *e = getenv("QW3B200_L2PF");
-        return (e && *e) ? (uint32_t)strtoul(e, nullptr, 10) : 0u;
-    }();
-    QbGemmPrefetch pf;
-    if (pf_count && w->pf_wait && w->pf_next && w->pf_next->rec && !push) {
-        const qb_weight *nx = w->pf_next;
-        pf.rec = nx->rec; pf.nchunks = nx->cols / 128; pf.tiles = nx->rows_pad / 128; pf.S = qb_ksplit(nx->rows, nx->cols);
-        pf.units = pf.tiles * pf.S * ((M + MT - 1) / MT);
-        pf.grid = std::min<uint32_t>(pf.units, (uint32_t)ctx->sm_count * C::CTAS_PER_SM);
-        pf.count = pf_count;
-    }
     const size_t smem_bytes = C::TOTAL;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -553,7 +404,7 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
     cfg.numAttrs = 1;
     QB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, NLD>, (const uint8_t *)w->rec, iq->second, id->second, K, w->rows, M, part, S,
                                tiles, units, ctx->err_flag_dev, qb_timeline_slot(ctx, grid, (double)w->rows_pad * K / 32.0 * 34.0 + (double)M * K * 1.125 + (double)S * M * w->rows * 4.0), push ? *push : QbGemmPush(),
-                               swiglu ? *swiglu : QbGemmSwiglu(), pf));
+                               swiglu ? *swiglu : QbGemmSwiglu()));
     if (grid_out) *grid_out = grid;
     QB_LAUNCHED(ctx, "gemm_tc_kernel");
     return QB_OK;

@@ -127,11 +127,6 @@ struct qb_weight {
     uint32_t rows = 0, cols = 0, rows_pad = 0;
     uint8_t *rec = nullptr;
     bool owns = false;
-    // The weight the step streams after this one, and whether this one's launches wait for a slow predecessor (the
-    // out-projection behind the DeltaNet / attention kernels): such a launch asks the L2 for the head of the next
-    // weight while it waits, so HBM keeps streaming.  Set by the model constructors.
-    const qb_weight *pf_next = nullptr;
-    bool pf_wait = false;
 };
 __host__ __device__ inline size_t qb_rec_offset(uint32_t cols, uint32_t row, uint32_t chunk) {
     return ((size_t)(row >> 7) * (cols >> 7) + chunk) * QB_REC_BYTES;
@@ -239,11 +234,6 @@ struct QbGemmPush {
 // Optional fused SwiGLU of the tensor-core GEMM (M <= 16, one K segment, weight = [gate; up] interleaved in groups
 // of 64 rows): instead of the fp32 products the epilogue writes int8(silu(gate) * up) and its block scales, the
 // quantised input of the down projection.
-// L2 prefetch of the next launch's first records (see qb_weight::pf_next): the unit decomposition of that launch.
-struct QbGemmPrefetch {
-    const uint8_t *rec = nullptr;
-    uint32_t nchunks = 0, tiles = 0, S = 0, units = 0, grid = 0, count = 0;   // count = records per CTA of the next launch
-};
 struct QbGemmSwiglu {
     int8_t *q = nullptr;             // [M][q_pitch]
     float *d = nullptr;              // [F/32][d_ld]

@@ -209,7 +209,13 @@ def test_fused_norm_fanout_and_ffn_input(orc, backends):
         except RB.RefError:
             fan = None                       # the executor takes its unfused fallback when a backend declines
         th = be.empty(M * F)
-        be.call("q8_0_matmul_silu_mul", th, W0, W1, be.tensor(x), M, H, F)
+        try:
+            be.call("q8_0_matmul_silu_mul", th, W0, W1, be.tensor(x), M, H, F)
+        except RB.RefError:                  # the reference declines the batched form for Q8_0: its executor's unfused fallback
+            tg, tu = be.empty(M * F), be.empty(M * F)
+            be.call("q8_0_matmul", tg, W0, be.tensor(x), M, H, F)
+            be.call("q8_0_matmul", tu, W1, be.tensor(x), M, H, F)
+            be.call("silu_mul_n", th, tg, tu, M * F)
         res.append((fan, be.download(th, (M, F))))
     ref, got = res
     assert got[0] is not None
