@@ -69,6 +69,8 @@ int  qb_sm_count(qb_ctx *ctx);
 
 /* DeviceBackend::tensor_f32/f16/i32, scratch_f32 (device_backend.hpp:124-213) reduced to
  * bytes; copy_to_host (:148), copy_i32_from_host (:2454), copy_d2d (:2514), zero_tensor. */
+/* DeviceBackend::free_device_bytes / total_device_bytes (device_backend.hpp:97-103). */
+int qb_mem_info(qb_ctx *ctx, size_t *free_bytes, size_t *total_bytes);
 int qb_malloc(qb_ctx *ctx, size_t bytes, void **dev_ptr);
 int qb_free(qb_ctx *ctx, void *dev_ptr);
 int qb_memcpy_h2d(qb_ctx *ctx, void *dev_dst, const void *host_src, size_t bytes);

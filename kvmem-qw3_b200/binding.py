@@ -46,6 +46,7 @@ SIGNATURES = {
     "qb_synchronize": (i32, [vp]),
     "qb_stream": (vp, [vp]),
     "qb_sm_count": (i32, [vp]),
+    "qb_mem_info": (i32, [vp, C.POINTER(sz), C.POINTER(sz)]),
     "qb_malloc": (i32, [vp, sz, C.POINTER(vp)]),
     "qb_free": (i32, [vp, vp]),
     "qb_memcpy_h2d": (i32, [vp, vp, vp, sz]),
@@ -239,6 +240,12 @@ class Context:
 
     def sync(self):
         check(lib().qb_synchronize(self.h))
+
+    def mem_info(self):
+        """(free, total) bytes of the context's device."""
+        f, t = sz(), sz()
+        check(lib().qb_mem_info(self.h, C.byref(f), C.byref(t)))
+        return f.value, t.value
 
     def flush_l2(self):
         check(lib().qb_flush_l2(self.h))

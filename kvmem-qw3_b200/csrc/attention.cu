@@ -418,11 +418,8 @@ __global__ void attn_merge_kernel(AttnArgs a, const int32_t *__restrict__ seq_po
 template <int HD, int JW>
 int launch_split(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t R, uint32_t n_seqs, uint32_t max_splits) {
     using L = AttSmem<HD>;
-    static bool attr = false;
-    if (!attr) {
-        QB_CUDA(cudaFuncSetAttribute((attn_split_kernel<HD, JW>), cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-        attr = true;
-    }
+    // the attribute belongs to the current device: set on every launch (a process may drive several GPUs)
+    QB_CUDA(cudaFuncSetAttribute((attn_split_kernel<HD, JW>), cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     dim3 grid(max_splits, a.n_kv, n_seqs * ((R + QR - 1) / QR));
     QB_CUDA(qb_launch_pdl(ctx->stream, (attn_split_kernel<HD, JW>), dim3(grid), dim3(64 * JW), (size_t)(L::TOTAL), a, seq_pos, R, max_splits));
     QB_LAUNCHED(ctx, "attn_split_kernel");

@@ -99,6 +99,16 @@ int qb_ctx_scratch2(qb_ctx *ctx, size_t bytes, void **out) {
     return QB_OK;
 }
 
+extern "C" int qb_mem_info(qb_ctx *ctx, size_t *free_bytes, size_t *total_bytes) {
+    QB_REQUIRE(ctx, "qb_mem_info: null context");
+    QB_CUDA(cudaSetDevice(ctx->device));
+    size_t f = 0, t = 0;
+    QB_CUDA(cudaMemGetInfo(&f, &t));
+    if (free_bytes) *free_bytes = f;
+    if (total_bytes) *total_bytes = t;
+    return QB_OK;
+}
+
 extern "C" int qb_malloc(qb_ctx *ctx, size_t bytes, void **dev_ptr) {
     QB_CUDA(cudaSetDevice(ctx->device));
     QB_CUDA(cudaMalloc(dev_ptr, bytes ? bytes : 16));

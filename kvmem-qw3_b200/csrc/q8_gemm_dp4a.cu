@@ -12,6 +12,8 @@
 // warp broadcasts.
 #include "qb_internal.h"
 
+#include <mutex>
+
 int qb_prof_begin(qb_ctx *ctx);
 int qb_prof_end(qb_ctx *ctx, double bytes);
 
@@ -135,11 +137,8 @@ __global__ void __launch_bounds__(THREADS) gemm_dp4a_kernel(const uint8_t *__res
 template <int MPT>
 int launch(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S) {
     using L = Smem<MPT>;
-    static bool attr = false;
-    if (!attr) {
-        QB_CUDA(cudaFuncSetAttribute(gemm_dp4a_kernel<MPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-        attr = true;
-    }
+    // the attribute belongs to the current device: set on every launch (a process may drive several GPUs)
+    QB_CUDA(cudaFuncSetAttribute(gemm_dp4a_kernel<MPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     dim3 grid(w->rows_pad / TILE_N, S, (M + L::NC - 1) / L::NC);
     QB_CUDA(qb_launch_pdl(ctx->stream, gemm_dp4a_kernel<MPT>, dim3(grid), dim3(THREADS), (size_t)(L::TOTAL), w->rec, w->cols, w->rows, q, d, M, qb_act_ld(M), part, S));
     QB_LAUNCHED(ctx, "gemm_dp4a_kernel");
@@ -336,7 +335,9 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[QB_NOALLOC_SCRA
 // address a kernel may use comes from cudaGetSymbolAddress, once per device, with that device current.
 static int noalloc_scratch_ptr(qb_ctx *ctx, unsigned char **out) {
     static unsigned char *ptrs[64] = {nullptr};
+    static std::mutex lock;
     QB_REQUIRE(ctx->device >= 0 && ctx->device < 64, "no-alloc matmul: device ordinal %d out of range", ctx->device);
+    std::lock_guard<std::mutex> guard(lock);
     if (!ptrs[ctx->device]) {
         QB_CUDA(cudaSetDevice(ctx->device));
         void *p = nullptr;

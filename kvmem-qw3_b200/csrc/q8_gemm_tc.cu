@@ -20,6 +20,8 @@
 #include "qb_internal.h"
 #include "tc_common.cuh"
 
+#include <mutex>
+
 namespace {
 using namespace qbtc;
 
@@ -275,10 +277,13 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
                             if (q + 1 < C::KPS * NCH) tmem_ld<16>(tbase + ((q + 1) / NCH) * MT + ((q + 1) % NCH) * 16, v[(q + 1) & 1]);
                             const float dw = __half2float(wd[kb * 128 + r]);
                             const f32x2 dw2 = pack2(dw, dw);
-                            const f32x2 *xd2 = reinterpret_cast<const f32x2 *>(xd + kb * MT + c0);
+                            const float4 *xd4 = reinterpret_cast<const float4 *>(xd + kb * MT + c0);      // four scales per shared-memory load
 #pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                acc2[c0 / 2 + i] = fma2(mul2(dw2, xd2[i]), pack2((float)v[q & 1][2 * i], (float)v[q & 1][2 * i + 1]), acc2[c0 / 2 + i]);
+                            for (int i = 0; i < 4; ++i) {
+                                const float4 x4 = xd4[i];
+                                acc2[c0 / 2 + 2 * i] = fma2(mul2(dw2, pack2(x4.x, x4.y)), pack2((float)v[q & 1][4 * i], (float)v[q & 1][4 * i + 1]), acc2[c0 / 2 + 2 * i]);
+                                acc2[c0 / 2 + 2 * i + 1] = fma2(mul2(dw2, pack2(x4.z, x4.w)), pack2((float)v[q & 1][4 * i + 2], (float)v[q & 1][4 * i + 3]), acc2[c0 / 2 + 2 * i + 1]);
+                            }
                         }
                         tc_fence_before();
                         __syncwarp();
@@ -359,34 +364,42 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
     }
 }
 
+// Tensor maps of the activation buffers, cached per (device, buffer, shape): the engine reuses a handful of buffers,
+// the op-level entry points may see many, so the cache is emptied when it grows large.  One lock for both maps.
 struct MapKey {
-    const void *p; uint32_t a, b, c;
-    bool operator<(const MapKey &o) const { return std::tie(p, a, b, c) < std::tie(o.p, o.a, o.b, o.c); }
+    int dev; const void *p; uint32_t a, b, c;
+    bool operator<(const MapKey &o) const { return std::tie(dev, p, a, b, c) < std::tie(o.dev, o.p, o.a, o.b, o.c); }
 };
 std::map<MapKey, CUtensorMap> g_xq_maps, g_xd_maps;
+std::mutex g_map_lock;
+constexpr size_t MAP_CACHE_MAX = 4096;
 
 template <int MT, int NLD>
 int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, uint32_t M, float *part, uint32_t S,
               const QbGemmPush *push, uint32_t *grid_out, const QbGemmSwiglu *swiglu) {
     using C = TcCfg<MT, NLD>;
-    static bool attr = false;
-    if (!attr) {
-        QB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MT, NLD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
-        attr = true;
-    }
+    // the attribute belongs to the current device: set on every launch (a process may drive several GPUs)
+    QB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MT, NLD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
     const uint32_t K = w->cols, ld = qb_act_ld(M);
-    MapKey kq{q, M, K, (uint32_t)MT}, kd{d, M, K, (uint32_t)MT};
-    auto iq = g_xq_maps.find(kq);
-    if (iq == g_xq_maps.end()) {
-        CUtensorMap mq;
-        QB_TRY(qb_make_tmap_2d(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, K, M, K, 128, MT, CU_TENSOR_MAP_SWIZZLE_128B));
-        iq = g_xq_maps.emplace(kq, mq).first;
-    }
-    auto id = g_xd_maps.find(kd);
-    if (id == g_xd_maps.end()) {
-        CUtensorMap md;
-        QB_TRY(qb_make_tmap_2d(&md, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, d, ld, K / 32, (uint64_t)ld * 4, MT, 4, CU_TENSOR_MAP_SWIZZLE_NONE));
-        id = g_xd_maps.emplace(kd, md).first;
+    MapKey kq{ctx->device, q, M, K, (uint32_t)MT}, kd{ctx->device, d, M, K, (uint32_t)MT};
+    CUtensorMap map_q, map_d;
+    {
+        std::lock_guard<std::mutex> lock(g_map_lock);
+        if (g_xq_maps.size() > MAP_CACHE_MAX) g_xq_maps.clear();
+        if (g_xd_maps.size() > MAP_CACHE_MAX) g_xd_maps.clear();
+        auto iq = g_xq_maps.find(kq);
+        if (iq == g_xq_maps.end()) {
+            CUtensorMap mq;
+            QB_TRY(qb_make_tmap_2d(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, K, M, K, 128, MT, CU_TENSOR_MAP_SWIZZLE_128B));
+            iq = g_xq_maps.emplace(kq, mq).first;
+        }
+        auto id = g_xd_maps.find(kd);
+        if (id == g_xd_maps.end()) {
+            CUtensorMap md;
+            QB_TRY(qb_make_tmap_2d(&md, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, d, ld, K / 32, (uint64_t)ld * 4, MT, 4, CU_TENSOR_MAP_SWIZZLE_NONE));
+            id = g_xd_maps.emplace(kd, md).first;
+        }
+        map_q = iq->second; map_d = id->second;
     }
     const uint32_t tiles = w->rows_pad / 128;
     const uint32_t units = tiles * S * ((M + MT - 1) / MT);
@@ -402,7 +415,7 @@ int launch_tc(qb_ctx *ctx, const qb_weight *w, const int8_t *q, const float *d, 
     attrs[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
-    QB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, NLD>, (const uint8_t *)w->rec, iq->second, id->second, K, w->rows, M, part, S,
+    QB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MT, NLD>, (const uint8_t *)w->rec, map_q, map_d, K, w->rows, M, part, S,
                                tiles, units, ctx->err_flag_dev, qb_timeline_slot(ctx, grid, (double)w->rows_pad * K / 32.0 * 34.0 + (double)M * K * 1.125 + (double)S * M * w->rows * 4.0), push ? *push : QbGemmPush(),
                                swiglu ? *swiglu : QbGemmSwiglu()));
     if (grid_out) *grid_out = grid;

@@ -126,13 +126,4 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
 }
 
 
-// D[tmem] (+)= A[smem] * B[smem], fp16 x fp16 -> fp32; accumulate = 0 overwrites D.
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
-}
-
 }  // namespace qbtc

@@ -52,3 +52,28 @@ def test_noalloc_matmul_refuses_what_does_not_fit(qb, orc, ctx):
     assert status == 4                                                    # QB_ERR_CAPACITY
     assert b"work area" in qb.lib().qb_last_error()
     w.free()
+
+
+def test_noalloc_matmul_leaves_device_memory_alone(qb, orc, ctx):
+    """The point of the entry point: between two readings of the device's free memory it allocates nothing, whatever
+    the shapes it is given (the ordinary entry point may grow the context's work area meanwhile, so it is not called)."""
+    rng = np.random.default_rng(97)
+    shapes = [(640, 2048, 4, 3), (1024, 4096, 16, 0), (384, 512, 7, 1)]
+    prepared = []
+    for (N, K, M, ksplit) in shapes:
+        blocks = orc.quantize_q8_0((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+        w = qb.Weight.from_blocks(ctx, blocks, N, K)
+        prepared.append((w, ctx.array(rng.standard_normal((M, K)).astype(np.float32)), ctx.empty((M, N), np.float32), M, K, N, ksplit))
+    L = qb.lib()
+    w0, x0, y0, M0, K0, N0, k0 = prepared[0]
+    qb.binding.check(L.qb_q8_0_matmul_noalloc(ctx.h, w0.h, x0.ptr, M0, K0, y0.ptr, N0, k0))      # first call on the device: address look-up
+    ctx.sync()
+    free_before, _ = ctx.mem_info()
+    for _ in range(3):
+        for (w, x, y, M, K, N, ksplit) in prepared:
+            qb.binding.check(L.qb_q8_0_matmul_noalloc(ctx.h, w.h, x.ptr, M, K, y.ptr, N, ksplit))
+    ctx.sync()
+    free_after, _ = ctx.mem_info()
+    assert free_after == free_before
+    for p in prepared:
+        p[0].free()
