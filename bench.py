@@ -466,7 +466,8 @@ def run_ours(args, rank, world, local_rank, dist):
         if world == 1:
             sub = sub_records(pkg, ctx, model, cfg)
         else:
-            sub = {"tp_ffn": tp_ffn_record(pkg, ctx, dist, rank, world, local_rank)}
+            sub = {"tp_ffn": tp_ffn_record(pkg, ctx, dist, rank, world, local_rank),
+                   "tp_step": tp_step_record(pkg, ctx, dist, rank, world, cfg, prompts[0])}
     if rank != 0:
         if run:
             run.close()
@@ -662,6 +663,78 @@ def tp_ffn_record(pkg, ctx, dist, rank, world, local, Ms=(4, 16, 64, 128, 512), 
         dist.barrier()
         return {"workload": "tensor-parallel FFN pair 5120 -> 17408 -> 5120 split over %d GPUs, one process per GPU, cold L2" % world,
                 "world": world, "weight_MB_per_rank": round((2 * f * H + H * f) / 32 * 34 / 1e6, 1), "rows": rows}
+    except Exception as e:
+        return {"error": str(e)}
+
+
+def tp_step_record(pkg, ctx, dist, rank, world, cfg, prompt, steps=20, warmup=2):
+    """The latency configuration: ONE request served by all ranks of the launch, the FFN pairs of every layer sharded
+    over them (all-reduce fused into the down GEMM, plain peer stores); attention, DeltaNet and the LM head replicated.
+    Greedy continuation and the speculative run at the same rank count; max over ranks of the device time."""
+    import torch
+    try:
+        model = pkg.Model.synth_tp(ctx, cfg, pkg.configs.MODEL_SEED, rank, world)
+        f = cfg.n_ff // world
+        sched = accept_schedule(warmup + steps + 1, warmup)
+        n_tok = int((sched + 1).sum()) + K_DRAFT + 4
+        max_ctx = len(prompt) + max(n_tok, (warmup + steps + 3) * (K_DRAFT + 1)) + 16
+        b = pkg.Batch(model, 1, max_ctx, K_DRAFT)
+        group, area, opened = pkg.tp.ipc_group(ctx, dist, b.max_rows, cfg.n_embd, f, cfg.n_embd)
+        b.set_tp(group)
+        e0, e1 = ctx.event(), ctx.event()
+        ctx.sync(); dist.barrier()
+        b.prefill(0, prompt)
+        first = b.read_output()[0][0]
+        snap = b.snapshot()
+        greedy = [first]
+        ctx.sync(); dist.barrier(); ctx.record(e0)
+        for _ in range(n_tok - 1):
+            b.greedy_step()
+            greedy += b.read_output()[0]
+        ctx.record(e1); ctx.sync()
+        greedy_ms = ctx.elapsed_ms(e0, e1) / (n_tok - 1)
+        b.restore(snap)
+        stride = max_ctx + 8
+        stream = np.zeros(stride, np.int32)
+        stream[:len(prompt)] = prompt
+        stream[len(prompt):len(prompt) + len(greedy)] = greedy
+        forced, _ = forced_table(stream, len(prompt), sched, cfg.vocab_size)
+        sdev = ctx.array(forced.reshape(1, -1))
+
+        def step():
+            b.mtp_draft(); b.mtp_force_drafts(sdev, stride); b.mtp_verify(); b.mtp_accept_commit()
+
+        for _ in range(warmup):
+            step(); b.read_output()
+        p0 = b.position(0)
+        ctx.sync(); dist.barrier(); ctx.record(e0)
+        for _ in range(steps):
+            step()
+        ctx.record(e1); ctx.sync()
+        ms = ctx.elapsed_ms(e0, e1)
+        b.read_output()
+        p1 = b.position(0)
+        # phase split on a few more steps: events at the boundaries only
+        ev = [ctx.event() for _ in range(4)]
+        ctx.sync(); dist.barrier()
+        ctx.record(ev[0]); b.mtp_draft(); b.mtp_force_drafts(sdev, stride)
+        ctx.record(ev[1]); b.mtp_verify()
+        ctx.record(ev[2]); b.mtp_accept_commit()
+        ctx.record(ev[3]); ctx.sync()
+        out = b.read_output()[0]
+        p2 = b.position(0)
+        lossless = (p1 - p0) == int((sched[warmup:warmup + steps] + 1).sum()) and out == list(stream[p2 - len(out) + 1:p2 + 1])
+        t = torch.tensor([ms, greedy_ms, ctx.elapsed_ms(ev[0], ev[1]), ctx.elapsed_ms(ev[1], ev[2]), ctx.elapsed_ms(ev[2], ev[3]), 0.0 if lossless else 1.0],
+                         dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ctx.sync(); dist.barrier()
+        b.free_snapshot(snap); b.close(); group.close(); pkg.tp.ipc_release(ctx, opened); model.close()
+        dist.barrier()
+        ms, greedy_ms = float(t[0]), float(t[1])
+        return {"workload": "configuration 2 as ONE request over %d GPUs: FFN pairs tensor-sharded, all-reduce fused into the down GEMM" % world,
+                "world": world, "steps": steps, "ms_per_step": ms / steps, "tok_per_s": (p1 - p0) / (ms * 1e-3), "greedy_ms_per_token": greedy_ms,
+                "draft_us": float(t[2]) * 1e3, "verify_us": float(t[3]) * 1e3, "accept_commit_us": float(t[4]) * 1e3,
+                "lossless_vs_greedy_at_same_rank_count": bool(float(t[5]) == 0.0)}
     except Exception as e:
         return {"error": str(e)}
 

@@ -456,6 +456,14 @@ int qb_tp_ffn_push(qb_ctx *ctx, qb_tp_group *g, const qb_weight *gate_up_shard, 
 int qb_tp_ffn_reduce(qb_ctx *ctx, qb_tp_group *g, uint32_t M, float *y_dev, uint32_t y_stride);
 int qb_tp_ffn(qb_ctx *ctx, qb_tp_group *g, const qb_weight *gate_up_shard, const qb_weight *down_shard,
               const float *x_dev, uint32_t M, float *y_dev, uint32_t y_stride);
+/* The sharded FFN inside the step (the latency configuration: one request served by `world` GPUs).
+ * qb_model_create_synth_tp: the seeded model with every FFN pair sharded as above (rank's gate/up rows and down columns
+ * are windows of the same seeded tensors, everything else replicated).  qb_batch_set_tp: the batch's forward passes run
+ * their FFN blocks through `group` (sized for qb_batch_max_rows rows); every rank runs the same calls on the same tokens
+ * and all get the same bits, so a speculative run still equals the greedy run of the same rank count exactly. */
+int qb_model_create_synth_tp(qb_ctx *ctx, const qb_model_config *cfg, uint64_t seed, uint32_t rank, uint32_t world, qb_model **out);
+int qb_batch_set_tp(qb_ctx *ctx, qb_batch *b, qb_tp_group *group);
+uint32_t qb_batch_max_rows(const qb_batch *b);
 /* CUDA IPC: export a qb_malloc'ed buffer as a 64-byte handle another process opens (peer access is
  * enabled on open). */
 int qb_ipc_export(qb_ctx *ctx, const void *dev_ptr, void *handle64);

@@ -98,6 +98,9 @@ SIGNATURES = {
     "qb_model_load_gguf": (i32, [vp, C.c_char_p, C.POINTER(vp), C.POINTER(ModelConfig)]),
     "qb_gguf_read_config": (i32, [C.c_char_p, C.POINTER(ModelConfig), C.POINTER(u64), C.POINTER(u64)]),
     "qb_model_get_config": (C.POINTER(ModelConfig), [vp]),
+    "qb_model_create_synth_tp": (i32, [vp, C.POINTER(ModelConfig), u64, u32, u32, C.POINTER(vp)]),
+    "qb_batch_set_tp": (i32, [vp, vp, vp]),
+    "qb_batch_max_rows": (u32, [vp]),
     "qb_model_destroy": (None, [vp, vp]),
     "qb_model_weight_bytes": (sz, [vp]),
     "qb_batch_create": (i32, [vp, vp, u32, u32, u32, u32, i32, C.POINTER(vp)]),
@@ -442,6 +445,16 @@ class Model:
         self.h = h
 
     @classmethod
+    def synth_tp(cls, ctx, cfg, seed, rank, world):
+        """The seeded model with its FFN pairs sharded: this rank's part of `world`."""
+        self = cls.__new__(cls)
+        self.ctx, self.cfg = ctx, cfg
+        h = vp()
+        check(lib().qb_model_create_synth_tp(ctx.h, C.byref(cfg), seed, rank, world, C.byref(h)))
+        self.h = h
+        return self
+
+    @classmethod
     def from_tensors(cls, ctx, cfg, tensors):
         """Model from the caller's host tensors ({GGUF tensor name: numpy array}, see tensor_descs)."""
         self = cls.__new__(cls)
@@ -528,6 +541,14 @@ class Batch:
         """limits: per-sequence draft depth of the next steps (None = k everywhere); eos_token ends a chain when drafted."""
         lim = None if limits is None else np.ascontiguousarray(limits, np.int32)
         check(lib().qb_batch_set_draft_policy(self.ctx.h, self.h, _np_ptr(lim) if lim is not None else None, int(eos_token)))
+
+    def set_tp(self, group):
+        """Run the FFN blocks through a tensor-parallel group (tp.TpGroup) or back on one GPU (None)."""
+        check(lib().qb_batch_set_tp(self.ctx.h, self.h, group.h if group is not None else None))
+
+    @property
+    def max_rows(self):
+        return int(lib().qb_batch_max_rows(self.h))
 
     def set_penalties(self, presence=0.0, repetition=1.0):
         check(lib().qb_batch_set_penalties(self.ctx.h, self.h, presence, repetition))

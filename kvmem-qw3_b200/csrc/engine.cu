@@ -47,6 +47,7 @@ struct qb_model {
     // MTP head: embedding table and LM head (nextn.embed_tokens / nextn.shared_head_head, else the target's)
     qb_weight *mtp_embd = nullptr, *mtp_head = nullptr;
     bool output_tied = false;        // no output.weight: the LM head is token_embd
+    uint32_t tp_rank = 0, tp_world = 1;   // FFN weights are shard tp_rank of tp_world (tensor-parallel form), else whole
     float *ones = nullptr;           // every RMSNorm gain of the seeded model is 1.0
     const float *output_norm = nullptr, *enorm = nullptr, *hnorm = nullptr, *shared_head_norm = nullptr;
     std::vector<float *> owned_f32;  // fp32 tensors uploaded for this model
@@ -104,13 +105,16 @@ static int build_layer(qb_ctx *ctx, qb_model *m, LayerW &L, uint32_t il, bool re
         QB_TRY(upload_f32(ctx, sa, &L.ssm_a));
         QB_TRY(upload_f32(ctx, dt, &L.dt_bias));
     }
-    QB_TRY(qb_weight_alloc(ctx, 2 * c.n_ff, c.n_embd, &L.w_gate_up));
-    // gate and up interleaved in groups of 64 rows: a 128-row tile holds both halves of 64 hidden indices
-    QB_REQUIRE(c.n_ff % 64 == 0, "model: FFN dimension %u is not a multiple of 64", c.n_ff);
-    QB_TRY(qb_weight_fill_synth(ctx, L.w_gate_up, 0, c.n_ff, seed, tensor_id(il, T_FFN_GATE), sg, 64));
-    QB_TRY(qb_weight_fill_synth(ctx, L.w_gate_up, 64, c.n_ff, seed, tensor_id(il, T_FFN_UP), sg, 64));
-    QB_TRY(qb_weight_alloc(ctx, c.n_embd, c.n_ff, &L.w_down));
-    QB_TRY(qb_weight_fill_synth(ctx, L.w_down, 0, c.n_embd, seed, tensor_id(il, T_FFN_DOWN), sg));
+    // gate and up interleaved in groups of 64 rows: a 128-row tile holds both halves of 64 hidden indices.  In the
+    // tensor-parallel form this rank holds FFN indices [lo, lo + f): those rows of gate and up, those columns of down.
+    QB_REQUIRE(c.n_ff % (64 * m->tp_world) == 0 && (c.n_ff / m->tp_world) % 128 == 0, "model: FFN dimension %u does not split into %u shards of whole tiles",
+               c.n_ff, m->tp_world);
+    const uint32_t f = c.n_ff / m->tp_world, lo = m->tp_rank * f;
+    QB_TRY(qb_weight_alloc(ctx, 2 * f, c.n_embd, &L.w_gate_up));
+    QB_TRY(qb_weight_fill_synth_window(ctx, L.w_gate_up, 0, f, seed, tensor_id(il, T_FFN_GATE), sg, 64, lo, c.n_embd / 32, 0));
+    QB_TRY(qb_weight_fill_synth_window(ctx, L.w_gate_up, 64, f, seed, tensor_id(il, T_FFN_UP), sg, 64, lo, c.n_embd / 32, 0));
+    QB_TRY(qb_weight_alloc(ctx, c.n_embd, f, &L.w_down));
+    QB_TRY(qb_weight_fill_synth_window(ctx, L.w_down, 0, c.n_embd, seed, tensor_id(il, T_FFN_DOWN), sg, 0, 0, c.n_ff / 32, lo / 32));
     m->weight_bytes += weight_bytes_of(L.w_in) + weight_bytes_of(L.w_out) + weight_bytes_of(L.w_gate_up) + weight_bytes_of(L.w_down);
     return QB_OK;
 }
@@ -141,12 +145,27 @@ static int model_begin(qb_ctx *ctx, const qb_model_config &c, qb_model **out) {
     return QB_OK;
 }
 
+static int model_create_synth(qb_ctx *ctx, const qb_model_config *cfg, uint64_t seed, uint32_t tp_rank, uint32_t tp_world, qb_model **out);
+
 extern "C" int qb_model_create_synth(qb_ctx *ctx, const qb_model_config *cfg, uint64_t seed, qb_model **out) {
+    return model_create_synth(ctx, cfg, seed, 0, 1, out);
+}
+
+// The seeded model with its FFN pairs tensor-sharded: rank `rank` of `world` holds gate/up rows and down columns
+// [rank * n_ff / world, (rank + 1) * n_ff / world) of every layer (and of the MTP layer); everything else is replicated.
+// The shards are windows of the same seeded tensors, so the ranks together hold exactly the model of qb_model_create_synth.
+extern "C" int qb_model_create_synth_tp(qb_ctx *ctx, const qb_model_config *cfg, uint64_t seed, uint32_t rank, uint32_t world, qb_model **out) {
+    QB_REQUIRE(world >= 1 && world <= 8 && rank < world, "qb_model_create_synth_tp: rank %u of %u (at most 8)", rank, world);
+    return model_create_synth(ctx, cfg, seed, rank, world, out);
+}
+
+static int model_create_synth(qb_ctx *ctx, const qb_model_config *cfg, uint64_t seed, uint32_t tp_rank, uint32_t tp_world, qb_model **out) {
     QB_REQUIRE(ctx && cfg && out, "qb_model_create_synth: null argument");
     const qb_model_config &c = *cfg;
     qb_model *m = nullptr;
     int st = model_begin(ctx, c, &m);
     if (st != QB_OK) { qb_model_destroy(ctx, m); return st; }
+    m->tp_rank = tp_rank; m->tp_world = tp_world;
     auto body = [&]() -> int {
         for (uint32_t il = 0; il < c.n_layers; ++il) QB_TRY(build_layer(ctx, m, m->layers[il], il, !m->is_attn(il), seed));
         if (c.mtp_layers) {
@@ -390,6 +409,8 @@ struct qb_batch {
     uint32_t *seen = nullptr;              // [n_seqs][seen_words] bitmap of prompt + emitted tokens (token penalties), or null
     uint32_t seen_words = 0;
     float pen_presence = 0.0f, pen_repetition = 1.0f;
+    qb_tp_group *tp = nullptr;             // tensor-parallel FFN group of the batch's model shard, or null
+    float *normed = nullptr, *tp_y = nullptr;   // [rows_cap][H]: fp32 FFN input / all-reduced FFN output of the tensor-parallel form
     int32_t *tok_stage = nullptr;          // pinned staging of the prompt tokens being ingested
     uint32_t tok_stage_cap = 0;
     double *first_draw_stage = nullptr;    // pinned: the first-token draw of a sampled request per sequence
@@ -542,7 +563,8 @@ extern "C" void qb_batch_destroy(qb_ctx *ctx, qb_batch *b) {
     for (auto p : b->conv_alt) if (p) cudaFree(p);
     void *ptrs[] = {b->page_table, b->ctl, b->stats, b->hid, b->mtp_h, b->embd, b->act, b->parts,
                     b->logits, b->am_val, b->am_idx, b->att_acc, b->att_ml, b->xq_h.q, b->xq_h.d, b->xq_attn.q,
-                    b->xq_attn.d, b->xq_dn.q, b->xq_dn.d, b->xq_ffn.q, b->xq_ffn.d, b->xq_cat.q, b->xq_cat.d, b->samp_u, b->seen, b->swap_tmp};
+                    b->xq_attn.d, b->xq_dn.q, b->xq_dn.d, b->xq_ffn.q, b->xq_ffn.d, b->xq_cat.q, b->xq_cat.d, b->samp_u, b->seen, b->swap_tmp,
+                    b->normed, b->tp_y};
     for (void *p : ptrs) if (p) cudaFree(p);
     if (b->out_rec_host) cudaFreeHost(b->out_rec_host);
     if (b->limit_host) cudaFreeHost(b->limit_host);
@@ -766,11 +788,12 @@ static int gemm_parts(qb_ctx *ctx, qb_batch *b, const qb_weight *w, const QBuf &
 
 // h += parts ; xq = quant(rmsnorm(h) * w)
 static int residual_norm_quant(qb_ctx *ctx, qb_batch *b, float *h, uint32_t rows, uint32_t S, const float *norm_w, const QBuf &dst,
-                               uint32_t q_col_off = 0, bool add_x = true) {
+                               uint32_t q_col_off = 0, bool add_x = true, const float *parts = nullptr, float *normed_out = nullptr) {
     const qb_model_config &c = b->m->cfg;
     NormQuantArgs a;
     a.x = add_x ? h : nullptr; a.x_stride = c.n_embd;
-    a.parts = b->parts; a.S = S; a.part_ld = c.n_embd;
+    a.parts = parts ? parts : b->parts; a.S = S; a.part_ld = c.n_embd;
+    a.normed_out = normed_out;
     a.h_out = h; a.h_stride = c.n_embd;
     a.w = norm_w; a.eps = c.rms_eps; a.n = c.n_embd; a.M = rows;
     a.q = dst.q; a.q_pitch = dst.K; a.q_col_off = q_col_off; a.d = dst.d; a.d_ld = qb_act_ld(rows); a.d_kb_off = q_col_off / 32;
@@ -822,11 +845,17 @@ static int attention_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t c
     QB_TRY(qb_attn_run(ctx, a, rs.seq_pos, rs.ns, nullptr, b->xq_attn.q, b->xq_attn.K, b->xq_attn.d, qb_act_ld(rows)));
     uint32_t S = 1;
     QB_TRY(gemm_parts(ctx, b, L.w_out, b->xq_attn, rows, &S));
-    return residual_norm_quant(ctx, b, h, rows, S, next_norm_w, b->xq_h);
+    return residual_norm_quant(ctx, b, h, rows, S, next_norm_w, b->xq_h, 0, true, nullptr, b->tp ? b->normed : nullptr);
 }
 
 static int ffn_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, float *h, uint32_t rows, const float *next_norm_w) {
     const qb_model_config &c = b->m->cfg;
+    if (b->tp) {
+        // tensor-parallel form: this rank's shard of gate/up and down on the fp32 normalised rows, the all-reduce fused
+        // into the down GEMM; every rank gets the same [rows][H] sum, added to the residual stream like one K segment
+        QB_TRY(qb_tp_ffn(ctx, b->tp, L.w_gate_up, L.w_down, b->normed, rows, b->tp_y, c.n_embd));
+        return residual_norm_quant(ctx, b, h, rows, 1, next_norm_w, b->xq_h, 0, true, b->tp_y);
+    }
     QB_TRY(qb_ffn_gate_up_swiglu(ctx, L.w_gate_up, b->xq_h.q, b->xq_h.d, rows, b->act, b->parts, b->parts_floats, b->xq_ffn.q, b->xq_ffn.K,
                                  b->xq_ffn.d, qb_act_ld(rows), b->gemm_impl, 0));
     uint32_t S = 1;
@@ -855,7 +884,7 @@ static int deltanet_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t il
     QB_TRY(qb_launch_deltanet(ctx, d));
     uint32_t S = 1;
     QB_TRY(gemm_parts(ctx, b, L.w_out, b->xq_dn, rows, &S));
-    return residual_norm_quant(ctx, b, h, rows, S, next_norm_w, b->xq_h);
+    return residual_norm_quant(ctx, b, h, rows, S, next_norm_w, b->xq_h, 0, true, nullptr, b->tp ? b->normed : nullptr);
 }
 
 // Target model on a row set.  tokens on the device ([rows]).  Leaves the pre-output-norm hidden rows
@@ -1143,6 +1172,23 @@ extern "C" int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b) {
     advance_host_pos(b, (int32_t)(k + 1));               // upper bound until the host reads the step record
     return QB_OK;
 }
+
+// Tensor-parallel form of a batch: its model is a shard (qb_model_create_synth_tp) and `group` the FFN group of the ranks
+// (created for at least as many rows as the batch forwards at once: qb_batch_max_rows).  Every rank must then run the
+// same calls on the same tokens; all of them get the same bits.  NULL goes back to the single-GPU form.
+extern "C" int qb_batch_set_tp(qb_ctx *ctx, qb_batch *b, qb_tp_group *group) {
+    QB_REQUIRE(ctx && b, "qb_batch_set_tp: null argument");
+    QB_REQUIRE(!group || b->m->tp_world > 1 || b->m->tp_world == 1, "qb_batch_set_tp: bad model");
+    if (group && !b->normed) {
+        const size_t n = (size_t)b->rows_cap * b->m->cfg.n_embd * sizeof(float);
+        QB_CUDA(cudaMalloc(&b->normed, n));
+        QB_CUDA(cudaMalloc(&b->tp_y, n));
+    }
+    b->tp = group;
+    qb_tp_group_set_ileave(group, 64);        // the model's gate/up shards are interleaved in groups of 64 rows
+    return QB_OK;
+}
+extern "C" uint32_t qb_batch_max_rows(const qb_batch *b) { return b ? b->rows_cap : 0; }
 
 // Chain policy of the speculative loop (src/qwen_native_backend.cpp:1625-1628, 15817-15848): limits_host[s] = draft depth of
 // sequence s from the next step on (the reference passes min(k, tokens still wanted), at least 1; 0 here makes the step

@@ -56,8 +56,11 @@ __device__ __forceinline__ uint32_t q8_dest_row(uint32_t row_off, uint32_t row, 
 }
 
 // One thread per 32-block.
+// The weight may be a window of the seeded tensor (a tensor-parallel shard): destination row r, block kb hold the tensor's
+// row src_row0 + r, block src_kb0 + kb, the tensor having src_nb blocks per row.
 __global__ void q8_synth_kernel(uint8_t *rec, uint32_t cols, uint32_t row_off, uint32_t rows,
-                                const float *__restrict__ table, uint64_t seed, uint32_t tensor_id, float sigma, uint32_t ileave) {
+                                const float *__restrict__ table, uint64_t seed, uint32_t tensor_id, float sigma, uint32_t ileave,
+                                uint32_t src_row0, uint32_t src_nb, uint32_t src_kb0) {
     const uint32_t nb = cols / 32;
     const uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= (uint64_t)rows * nb) return;
@@ -65,7 +68,7 @@ __global__ void q8_synth_kernel(uint8_t *rec, uint32_t cols, uint32_t row_off, u
     const uint32_t row = q8_dest_row(0, (uint32_t)(b / nb), ileave);
     uint16_t dbits;
     __align__(16) int8_t qq[32];
-    qs_synth_q8_0_block(table, seed, tensor_id, b, sigma, &dbits, qq);
+    qs_synth_q8_0_block(table, seed, tensor_id, ((uint64_t)src_row0 + b / nb) * src_nb + src_kb0 + kb, sigma, &dbits, qq);
     *reinterpret_cast<int4 *>(rec + qb_q_offset(cols, row_off + row, kb * 32)) = reinterpret_cast<const int4 *>(qq)[0];
     *reinterpret_cast<int4 *>(rec + qb_q_offset(cols, row_off + row, kb * 32 + 16)) = reinterpret_cast<const int4 *>(qq)[1];
     *reinterpret_cast<uint16_t *>(rec + qb_d_offset(cols, row_off + row, kb)) = dbits;
@@ -73,6 +76,11 @@ __global__ void q8_synth_kernel(uint8_t *rec, uint32_t cols, uint32_t row_off, u
 
 int qb_weight_fill_synth(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, uint64_t seed,
                          uint32_t tensor_id, float sigma, uint32_t ileave) {
+    return qb_weight_fill_synth_window(ctx, w, row_off, rows, seed, tensor_id, sigma, ileave, 0, w->cols / 32, 0);
+}
+
+int qb_weight_fill_synth_window(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, uint64_t seed, uint32_t tensor_id, float sigma,
+                                uint32_t ileave, uint32_t src_row0, uint32_t src_nb, uint32_t src_kb0) {
     QB_REQUIRE(ileave ? (rows % ileave == 0 && row_off + 2 * rows - ileave <= w->rows_pad) : row_off + rows <= w->rows_pad,
                "synth fill out of range");
     const uint64_t nblocks = (uint64_t)rows * (w->cols / 32);
@@ -80,7 +88,7 @@ int qb_weight_fill_synth(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t r
     const uint64_t grid = (nblocks + threads - 1) / threads;
     QB_REQUIRE(grid < (1ull << 31), "synth fill too large");
     q8_synth_kernel<<<(uint32_t)grid, threads, 0, ctx->stream>>>(w->rec, w->cols, row_off, rows, ctx->normal_table_dev, seed,
-                                                                tensor_id, sigma, ileave);
+                                                                tensor_id, sigma, ileave, src_row0, src_nb, src_kb0);
     QB_LAUNCHED(ctx, "q8_synth_kernel");
     return QB_OK;
 }

@@ -142,6 +142,8 @@ __host__ __device__ inline size_t qb_d_offset(uint32_t cols, uint32_t row, uint3
 int qb_weight_alloc(qb_ctx *ctx, uint32_t rows, uint32_t cols, qb_weight **out);
 int qb_weight_fill_synth(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, uint64_t seed,
                          uint32_t tensor_id, float sigma, uint32_t ileave = 0);
+int qb_weight_fill_synth_window(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, uint64_t seed, uint32_t tensor_id, float sigma,
+                                uint32_t ileave, uint32_t src_row0, uint32_t src_nb, uint32_t src_kb0);
 int qb_weight_fill_upload(qb_ctx *ctx, qb_weight *w, uint32_t row_off, uint32_t rows, const void *host_blocks,
                           uint32_t ileave = 0);
 // rows [row_off, row_off+rows) of w as a weight of its own (row_off multiple of 128).
@@ -249,6 +251,9 @@ bool qb_gemm_tc_supported(const qb_weight *w, uint32_t M);
 int qb_ffn_gate_up_swiglu(qb_ctx *ctx, const qb_weight *w, const int8_t *xq, const float *xd, uint32_t M, float *act, float *parts,
                           size_t parts_floats, int8_t *hq, uint32_t hq_pitch, float *hd, uint32_t hd_ld, int gemm_impl, int mode);
 uint32_t qb_ksplit(uint32_t N, uint32_t K);
+// Row order of a tensor-parallel group's gate/up shards: 0 = [gate; up] (the op-level entry points), 64 = the model's
+// interleaved order.
+void qb_tp_group_set_ileave(qb_tp_group *g, uint32_t ileave);
 // y[m][n] = sum_s part[s][m][n] (ascending s).
 int qb_launch_reduce_parts(qb_ctx *ctx, const float *part, uint32_t S, uint32_t M, uint32_t N, float *y,
                            uint32_t y_stride);

@@ -26,7 +26,9 @@ struct qb_tp_group {
     size_t region_floats = 0, slot_floats = 0;
     float *dn_parts = nullptr;           // local split partials of the down GEMM (many-row form)
     uint32_t pushed_S[2] = {1, 1};       // segments per rank in the slot of each parity
+    uint32_t gu_ileave = 0;              // row order of the gate/up shard: 0 = [gate; up], 64 = interleaved in groups of 64 (the engine's)
 };
+void qb_tp_group_set_ileave(qb_tp_group *g, uint32_t ileave) { if (g) g->gu_ileave = ileave; }
 
 namespace {
 
@@ -139,7 +141,7 @@ extern "C" int qb_tp_ffn_push(qb_ctx *ctx, qb_tp_group *g, const qb_weight *gate
     const uint32_t S_gu = qb_ksplit(gate_up->rows, gate_up->cols);
     QB_TRY(qb_launch_gemm(ctx, gate_up, g->xq, g->xd, M, g->gu_parts, S_gu, 0));
     QB_TRY(qb_launch_swiglu_quant(ctx, g->gu_parts, 2 * g->f_shard, M, g->f_shard, g->hq, g->f_shard, g->hd, ld, S_gu,
-                                  (size_t)M * 2 * g->f_shard));
+                                  (size_t)M * 2 * g->f_shard, g->gu_ileave));
     const uint32_t par = g->step & 1;
     QbGemmPush push;
     push.n = g->world;

@@ -208,3 +208,111 @@ def test_tp_ffn_one_process_per_gpu(world, tmp_path):
     assert out.returncode == 0, out.stderr[-3000:]
     r = json.loads([ln for ln in out.stdout.splitlines() if ln.startswith("{")][-1])
     assert r["ranks_identical"] and r["worst_rel_err"] < TOL, r
+
+
+STEP_WORKER = r"""
+import json, os, sys
+import numpy as np
+sys.path.insert(0, %(root)r)
+import __graft_entry__ as entry
+import torch
+import torch.distributed as dist
+rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+torch.cuda.set_device(local)
+dist.init_process_group("gloo")
+pkg = entry.load_package()
+O = entry.load_oracle()
+ctx = pkg.Context(local)
+cfg = pkg.configs.tiny()
+K, N_NEW = 3, 40
+prompt = O.synth_prompt(pkg.configs.PROMPT_SEED + 31, cfg.vocab_size, 50)
+model = pkg.Model.synth_tp(ctx, cfg, pkg.configs.MODEL_SEED, rank, world)
+f = cfg.n_ff // world
+
+
+def run(k):
+    b = pkg.Batch(model, 1, 256, k)
+    group, area, opened = pkg.tp.ipc_group(ctx, dist, b.max_rows, cfg.n_embd, f, cfg.n_embd)
+    b.set_tp(group)
+    ctx.sync(); dist.barrier()
+    b.prefill(0, prompt)
+    toks, logits = list(b.read_output()[0]), [b.last_logits(1)[0].copy()]
+    while len(toks) < N_NEW:
+        b.mtp_step() if k else b.greedy_step()
+        toks += b.read_output()[0]
+    st = b.stats()
+    ctx.sync(); dist.barrier()
+    b.close(); group.close(); pkg.tp.ipc_release(ctx, opened)
+    return toks[:N_NEW], logits[0], st
+
+greedy, lg, _ = run(0)
+spec, _, st = run(K)
+everyone = [None] * world
+dist.all_gather_object(everyone, (greedy, spec, lg.tobytes()))
+out = {"world": world, "lossless": spec == greedy, "ranks_identical": all(e == everyone[0] for e in everyone), "steps": st["steps"]}
+if rank == 0:
+    # the single-GPU model of the same seed: same function up to the order of the FFN's additions
+    whole = pkg.Model(ctx, cfg, pkg.configs.MODEL_SEED)
+    b = pkg.Batch(whole, 1, 256, 0)
+    b.prefill(0, prompt)
+    ref = b.last_logits(1)[0]
+    out["prefill_logit_rel_err_vs_one_gpu"] = float(np.abs(lg - ref).max() / np.abs(ref).max())
+    b.close(); whole.close()
+    print(json.dumps(out))
+model.close()
+dist.barrier()
+dist.destroy_process_group()
+"""
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_step_is_lossless_one_process_per_gpu(world, tmp_path):
+    """The FFN pairs of the whole step tensor-sharded over `world` GPUs (qb_model_create_synth_tp + qb_batch_set_tp):
+    every rank emits the same tokens, the speculative stream equals the greedy stream of the same rank count exactly, and
+    the prefill logits stay within the model's rounding noise of the single-GPU model."""
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    script = tmp_path / "tp_step_worker.py"
+    script.write_text(STEP_WORKER % dict(root=ROOT))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % world,
+                          "--master-addr", "127.0.0.1", "--master-port", "29673", str(script)],
+                         capture_output=True, text=True, env=env, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    r = json.loads([ln for ln in out.stdout.splitlines() if ln.startswith("{")][-1])
+    print(r)
+    assert r["lossless"] and r["ranks_identical"] and r["steps"] > 0, r
+    assert r["prefill_logit_rel_err_vs_one_gpu"] < 2.5e-2, r
+
+
+def test_tp_step_path_on_one_gpu(qb, orc, ctx):
+    """The tensor-parallel form of the step with a group of one rank (nothing waits): the speculative stream equals the
+    greedy stream of the same form exactly, and its logits stay within the rounding noise of the ordinary form (the FFN
+    output is added to the residual stream as one sum instead of segment by segment)."""
+    cfg = qb.configs.tiny()
+    prompt = orc.synth_prompt(qb.configs.PROMPT_SEED + 32, cfg.vocab_size, 40)
+    model = qb.Model.synth_tp(ctx, cfg, qb.configs.MODEL_SEED, 0, 1)
+    plain = qb.Model(ctx, cfg, qb.configs.MODEL_SEED)
+    assert model.weight_bytes == plain.weight_bytes
+    streams, logits = [], []
+    for k in (0, 3):
+        b = qb.Batch(model, 1, 256, k)
+        groups, _areas = qb.tp.local_groups(ctx, 1, b.max_rows, cfg.n_embd, cfg.n_ff, cfg.n_embd)
+        b.set_tp(groups[0])
+        b.prefill(0, prompt)
+        toks = list(b.read_output()[0])
+        logits.append(b.last_logits(1)[0].copy())
+        while len(toks) < 30:
+            b.mtp_step() if k else b.greedy_step()
+            toks += b.read_output()[0]
+        streams.append(toks[:30])
+        b.close()
+        groups[0].close()
+    assert streams[0] == streams[1]
+    assert np.array_equal(logits[0], logits[1])
+    b = qb.Batch(plain, 1, 256, 0)
+    b.prefill(0, prompt)
+    ref = b.last_logits(1)[0]
+    assert float(np.abs(logits[0] - ref).max() / np.abs(ref).max()) < 2.5e-2
+    b.close(); model.close(); plain.close()
