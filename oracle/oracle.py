@@ -240,6 +240,14 @@ def sample_rows(logits, draft, u_acc, u_res, temp, top_p=1.0, top_k=0, min_p=0.0
     return tok, acc, pd
 
 
+def sampling_distribution(logits, temp, top_p=1.0, top_k=0, min_p=0.0):
+    """The full-vocabulary probability vector one row is sampled from."""
+    x = _f32(logits).reshape(-1)
+    out = np.empty(x.size, np.float32)
+    lib().orc_sampling_distribution(_p(x), C.c_uint32(x.size), C.c_float(temp), C.c_float(top_p), C.c_int32(top_k), C.c_float(min_p), _p(out))
+    return out
+
+
 def synth_prompt(seed, vocab, n):
     out = np.empty(n, np.int32)
     lib().orc_synth_prompt(C.c_uint64(seed), C.c_uint32(vocab), C.c_uint32(n), _p(out))

@@ -880,6 +880,13 @@ void orc_sample_rows(const float *logits, uint32_t rows, uint32_t V, uint32_t st
     }
 }
 
+// The distribution itself (one row), for the tests that pin it against the reference's function.
+void orc_sampling_distribution(const float *logits, uint32_t V, float temp, float top_p, int32_t top_k, float min_p, float *out) {
+    std::vector<float> p;
+    sampling_distribution(logits, (int)V, temp, top_p, top_k, min_p, p);
+    memcpy(out, p.data(), (size_t)V * sizeof(float));
+}
+
 void orc_argmax_rows(const float *x, uint32_t M, uint32_t n, uint32_t stride, int32_t *out) {
     for (uint32_t m = 0; m < M; ++m) out[m] = argmax(x + (size_t)m * stride, n);
 }
