@@ -377,8 +377,11 @@ int qb_sample_rows(qb_ctx *ctx, const float *logits_dev, uint32_t rows, uint32_t
                    int32_t *token_dev, int32_t *accepted_dev, float *p_draft_dev);
 /* The same decision for the rows of the last qb_mtp_verify, left where qb_mtp_accept_commit reads the row tokens: call
  * between the two.  u_host: double [n_seqs][k+1], the caller's uniform draws in the order the reference consumes its
- * generator: row i accepts with u[i], a rejection at row i draws with u[i+1], the bonus draw is u[k]; a step that
- * rejects after a acceptances uses the first a + 2 of them, a fully accepted chain all k + 1. */
+ * generator: row i accepts with u[i], a rejection at row i draws with u[i+1], the bonus draw of a chain of depth d is u[d]
+ * (d = k, or less under qb_batch_set_draft_policy: the sequence's limit, or the index of a drafted end-of-sequence token);
+ * a step that rejects after a acceptances uses the first a + 2 of them, a fully accepted chain d + 1.  One difference to
+ * the reference's generator remains: std::discrete_distribution draws nothing when fewer than two tokens are left to
+ * choose from, this function counts that draw as used; the sampled distribution is the same. */
 int qb_mtp_sample_rows(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host);
 /* Token penalties of sampling requests (apply_token_penalties, src/qwen_native_backend.cpp:262-280: a seen token's logit is
  * divided by repetition when >= 0, multiplied when < 0, then lowered by presence): from this call on the batch records the

@@ -1208,8 +1208,9 @@ extern "C" int qb_batch_set_draft_policy(qb_ctx *ctx, qb_batch *b, const int32_t
 // place of the row's argmax -- the draft itself when accepted, the residual draw when rejected, the bonus draw on the last
 // row -- so the longest-matching-prefix commit that follows is the reference's accept loop.  u_host: double [n_seqs][k+1],
 // the caller's uniform draws in the order its generator is consumed: row i accepts with u[i]; a rejection at row i draws
-// its residual with u[i+1]; the bonus draw is u[k].  A step that rejects after `a` acceptances consumes a + 2 of them
-// (a + 1 acceptance tests and the residual draw), a fully accepted chain all k + 1.
+// its residual with u[i+1]; the bonus draw of a chain of depth d (k, or the sequence's draft limit, or the index of a
+// drafted end-of-sequence token) is u[d].  A step that rejects after `a` acceptances consumes a + 2 of them (a + 1
+// acceptance tests and the residual draw), a fully accepted chain of depth d consumes d + 1.
 extern "C" int qb_mtp_sample_rows(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host) {
     QB_REQUIRE(ctx && b && u_host && b->k > 0, "qb_mtp_sample_rows: needs draws and a batch with draft depth > 0");
     QB_CUDA(cudaSetDevice(ctx->device));
@@ -1226,7 +1227,7 @@ extern "C" int qb_mtp_sample_rows(qb_ctx *ctx, qb_batch *b, float temp, float to
     const qb_model_config &c = b->m->cfg;
     return qb_launch_sample_rows(ctx, b->logits, rows, c.vocab_size, c.vocab_size, b->drafts, K1, b->samp_u, b->samp_u + rows, temp, top_p,
                                  top_k, min_p, nullptr, nullptr, nullptr, b->am_val, b->am_idx, QB_ARGMAX_BLOCKS, b->pen_presence, b->pen_repetition,
-                                 b->seen, b->seen_words);
+                                 b->seen, b->seen_words, b->limit, b->eos_token);
 }
 
 extern "C" int qb_mtp_step_sampled(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32_t top_k, float min_p, const double *u_host) {

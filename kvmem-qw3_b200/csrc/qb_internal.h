@@ -267,7 +267,8 @@ static const uint32_t QB_ARGMAX_BLOCKS = 64;
 int qb_launch_sample_rows(qb_ctx *ctx, const float *logits, uint32_t rows, uint32_t V, uint32_t stride, const int32_t *draft,
                           uint32_t K1, const double *u_acc, const double *u_res, float temp, float top_p, int32_t top_k,
                           float min_p, int32_t *token, int32_t *accepted, float *p_draft, float *pval, int32_t *pidx,
-                          uint32_t nblk, float presence, float repetition, const uint32_t *seen, uint32_t seen_words);
+                          uint32_t nblk, float presence, float repetition, const uint32_t *seen, uint32_t seen_words,
+                          const int32_t *chain_limit = nullptr, int32_t eos = -1);
 
 // Attention over the paged cache.  Rows are grouped per sequence: sequence s owns rows
 // [s*R, (s+1)*R), R = rows / n_seqs, at positions seq_pos[s] .. seq_pos[s]+R-1 (seq_pos on the device).

@@ -31,6 +31,8 @@ struct SampleParams {
     float presence, repetition;               // token penalties (0 / 1 = off)
     const uint32_t *seen;                     // bitmap [sequence][seen_words] of the tokens a request has seen, or null
     uint32_t seen_words;
+    const int32_t *chain_limit;               // [sequence] draft depth of this step (K1 > 0 form), or null = K1 - 1 everywhere
+    int32_t eos;                              // a chain ends before the first draft equal to this token (-1: none)
 };
 
 __device__ __forceinline__ uint32_t okey(float f) {      // ascending key order == ascending float order
@@ -172,6 +174,17 @@ sample_rows_kernel(const float *__restrict__ logits, uint32_t V, uint32_t stride
     // token penalties (apply_token_penalties, src/qwen_native_backend.cpp:262-280) against the request's seen tokens and
     // the drafts of the earlier rows of this step (the running prefix of the accept loop, :432-447)
     const uint32_t seq = K1 ? row / K1 : row, n_prior = K1 ? row % K1 : 0;
+    // the row that follows the last draft of a shortened chain (depth limit, or a drafted end-of-sequence token:
+    // src/qwen_native_backend.cpp:15817-15821) is that step's bonus row: no acceptance test, one plain draw -- the draw
+    // the row would otherwise have tested its draft with
+    bool chain_end = false;
+    if (K1 && p.chain_limit && draft) {
+        uint32_t kk = min(K1 - 1, (uint32_t)max(p.chain_limit[seq], 0));
+        if (p.eos >= 0)
+            for (uint32_t i = 0; i < kk; ++i)
+                if (draft[(size_t)seq * (K1 - 1) + i] == p.eos) { kk = i; break; }
+        chain_end = n_prior >= kk && n_prior + 1 < K1;
+    }
     const bool pen_rep = p.repetition > 0.0f && p.repetition != 1.0f, pen_pres = p.presence != 0.0f;
     auto penalised = [&](uint32_t idx, float v) -> float {
         if (!(pen_rep || pen_pres)) return v;
@@ -298,7 +311,7 @@ sample_rows_kernel(const float *__restrict__ logits, uint32_t V, uint32_t stride
         return 0.0f;
     };
     // ranks of the boundary ties in index order: this thread's first tie rank, and the rank of the draft
-    const int d = !draft ? -1 : K1 == 0 ? draft[row] : (row % K1 + 1 < K1 ? draft[(row / K1) * (K1 - 1) + row % K1] : -1);
+    const int d = !draft || chain_end ? -1 : K1 == 0 ? draft[row] : (row % K1 + 1 < K1 ? draft[(row / K1) * (K1 - 1) + row % K1] : -1);
     const bool has_d = d >= 0 && (uint32_t)d < V;
     long long tie_ex = 0, d_rank = 0;
     if (rank_ties) {
@@ -351,7 +364,7 @@ sample_rows_kernel(const float *__restrict__ logits, uint32_t V, uint32_t stride
         long long cand = 0x7fffffff;
         double last_nz = -1.0;
         if (total > 0.0) {
-            const double u = u_res[row];
+            const double u = chain_end ? u_acc[row] : u_res[row];
             double run = off + ex;
             long long tr = tie_ex;
 #pragma unroll
@@ -395,12 +408,14 @@ sample_rows_kernel(const float *__restrict__ logits, uint32_t V, uint32_t stride
 int qb_launch_sample_rows(qb_ctx *ctx, const float *logits, uint32_t rows, uint32_t V, uint32_t stride, const int32_t *draft,
                           uint32_t K1, const double *u_acc, const double *u_res, float temp, float top_p, int32_t top_k,
                           float min_p, int32_t *token, int32_t *accepted, float *p_draft, float *pval, int32_t *pidx,
-                          uint32_t nblk, float presence, float repetition, const uint32_t *seen, uint32_t seen_words) {
+                          uint32_t nblk, float presence, float repetition, const uint32_t *seen, uint32_t seen_words,
+                          const int32_t *chain_limit, int32_t eos) {
     QB_REQUIRE(temp > 0.0f, "sampling needs temp > 0 (temp <= 0 is the argmax path)");
     QB_REQUIRE(rows > 0 && V > 0 && u_res != nullptr, "qb_launch_sample_rows: bad arguments");
     SampleParams p;
     p.inv_t = 1.0f / temp; p.top_p = top_p; p.min_p = min_p; p.top_k = top_k;
     p.presence = presence; p.repetition = repetition; p.seen = seen; p.seen_words = seen_words;
+    p.chain_limit = chain_limit; p.eos = eos;
     QB_REQUIRE(V <= (uint32_t)(CL * ST * EPT), "sampling: rows of %u logits exceed the kernel's %d", V, CL * ST * EPT);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(rows * CL);

@@ -81,9 +81,11 @@ class DrawQueue:
     def consume(self, n):
         del self.buf[:n]
 
-    def consume_step(self, n_out):
-        """Draws used by a speculative step that emitted n_out tokens (accepted drafts + the residual or bonus token)."""
-        self.consume(self.width if n_out >= self.width else n_out + 1)
+    def consume_step(self, n_out, depth=None):
+        """Draws used by a speculative step of chain depth `depth` (default: the full width - 1) that emitted n_out tokens
+        (accepted drafts + the residual or bonus token): a fully accepted chain depth + 1, a rejecting one n_out + 1."""
+        depth = self.width - 1 if depth is None else min(depth, self.width - 1)
+        self.consume(depth + 1 if n_out >= depth + 1 else n_out + 1)
 
     def take(self):
         v = self.peek()[0]

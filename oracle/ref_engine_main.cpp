@@ -5,6 +5,10 @@
 // CUDA DeviceBackend where they lie (oracle/Makefile target ref-engine); nothing here is part of the product.
 //
 //   qw3ref_engine <model.gguf> <greedy|mtp> <chain k> <max_tokens> <ctx> <token id> [<token id> ...]
+//
+// Sampling requests (GenerationOptions temperature / top_p / top_k / min_p / seed / presence_penalty / repetition_penalty,
+// include/qw3/qw3.hpp:224-230) come from the environment: QW3REF_TEMPERATURE (default 0 = greedy), QW3REF_TOP_P,
+// QW3REF_TOP_K, QW3REF_MIN_P, QW3REF_SEED, QW3REF_PRESENCE, QW3REF_REPETITION.
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -32,9 +36,14 @@ int main(int argc, char **argv) {
         eo.verbose = true;
         qw3::GenerationOptions go;
         go.max_tokens = std::atoi(argv[4]);
-        go.temperature = 0.0f;
-        go.top_k = 0;
-        go.top_p = 1.0f;
+        auto envf = [](const char *name, double dflt) { const char *v = std::getenv(name); return v && *v ? std::atof(v) : dflt; };
+        go.temperature = (float)envf("QW3REF_TEMPERATURE", 0.0);
+        go.top_k = (int)envf("QW3REF_TOP_K", 0.0);
+        go.top_p = (float)envf("QW3REF_TOP_P", 1.0);
+        go.min_p = (float)envf("QW3REF_MIN_P", 0.0);
+        go.presence_penalty = (float)envf("QW3REF_PRESENCE", 0.0);
+        go.repetition_penalty = (float)envf("QW3REF_REPETITION", 1.0);
+        if (const char *v = std::getenv("QW3REF_SEED")) go.seed = std::strtoull(v, nullptr, 10);
         go.raw_prompt = true;
         go.ignore_eos = true;
         for (int i = 6; i < argc; ++i) go.prompt_token_ids_override.push_back((uint32_t)std::strtoul(argv[i], nullptr, 10));

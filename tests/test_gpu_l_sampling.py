@@ -232,7 +232,9 @@ def test_sampled_stream_replays_through_one_continuous_generator(qb, orc, ctx, m
     assert b.stats()["emitted"] == 1
     seen |= set(first)
     emitted, rejected, full = list(first), 0, 0
-    for step in range(14):
+    for step in range(16):
+        depth = (k, 1, 2, k)[step % 4]                      # the chain policy: the row after the last draft is the bonus row
+        b.set_draft_policy([depth])
         u = np.array([dq.peek()], np.float64)
         b.mtp_draft()
         b.mtp_verify()
@@ -241,11 +243,11 @@ def test_sampled_stream_replays_through_one_continuous_generator(qb, orc, ctx, m
         b.mtp_sample_rows(u, temp, top_p, top_k)
         b.mtp_accept_commit()
         out = b.read_output()[0]
-        dq.consume_step(len(out))
+        dq.consume_step(len(out), depth)
         # the reference's loop on the continuous generator
         want, ctxset = [], set(seen)
-        for i in range(k + 1):
-            d = int(drafts[i]) if i < k else -1
+        for i in range(depth + 1):
+            d = int(drafts[i]) if i < depth else -1
             row = penalise(logits[i], ctxset)
             if d >= 0:
                 ua = one()

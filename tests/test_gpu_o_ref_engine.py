@@ -28,9 +28,11 @@ def pin_config(qb):
                           ssm_head_dim=128, full_attention_interval=4, vocab_size=4096, mtp_layers=1, weight_sigma=0.02)
 
 
-def run_reference(path, mode, prompt, n_new):
+def run_reference(path, mode, prompt, n_new, sampling=None):
     import gguf_synth as G
     env = dict(os.environ, QW3_PAGED_KV_PREFILL="0", QW3_Q8_BF16_MAIN="0", QW3_FATTN_NSPLIT="1")
+    for key, v in (sampling or {}).items():          # temperature, top_p, top_k, min_p, seed (see oracle/ref_engine_main.cpp)
+        env["QW3REF_" + key.upper()] = repr(v)
     cmd = [ENGINE, path, mode, str(K), str(n_new), str(CTX)] + [str(int(t)) for t in prompt]
     r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=240)
     assert r.returncode == 0, "reference engine failed:\n" + r.stderr[-3000:]
@@ -152,3 +154,49 @@ def test_reference_engine_greedy_and_mtp(qb, orc, ctx, tmp_path, predictable):
     if predictable:
         assert r_accepted >= r_drafted // 5, "the predictable model should accept a good share of its drafts"
         assert e_stats["accepted"] >= e_stats["drafted"] // 5
+
+
+@pytest.mark.skipif(not os.path.exists(ENGINE), reason="oracle/_ref/qw3ref_engine not built (make -C oracle ref-engine REF=<reference tree>)")
+def test_reference_engine_sampled_mtp(qb, orc, ctx, tmp_path):
+    """A sampling request (temperature > 0) through the reference's speculative loop and through the product's, on the
+    same generator: the reference seeds one std::mt19937_64 per request with options.seed; the product is handed that
+    generator's draws (oracle/ref_sampling.py replays the engine and libstdc++'s conversion to a uniform) through a
+    DrawQueue -- the first draw picks the token after the prompt, a step is handed k + 1 and returns the unused ones.
+    While both implementations see the same logits up to their numeric noise, the two token streams are the same; a
+    draw that lands inside that noise at a boundary of the cumulative distribution ends the common prefix (from there on
+    the two requests are different texts).  The sampler's functions themselves are pinned bit-exactly on the reference
+    in tests/test_sampling_ref_pin_cpu.py; this test pins the order in which the loop consumes the generator."""
+    import gguf_synth as G
+    import ref_sampling as R
+    cfg = pin_config(qb)
+    ocfg = orc.ModelConfig(**cfg.as_dict())
+    t = G.seeded_model_tensors(ocfg, 0x5EED + 1, gain_sigma=0.05, branch_scale=0.01, eh_identity=True)
+    path = G.write_gguf(str(tmp_path / "pin_s.gguf"), ocfg, t, context_length=CTX)
+    prompt = orc.synth_prompt(4242, cfg.vocab_size, PROMPT_LEN)
+    model = qb.Model.from_gguf(ctx, path)
+    temp, top_p, top_k = 0.7, 1.0, 6
+    prefixes, n_new = [], 32
+    for seed in (11, 12, 13, 14):
+        r_tok, summ, hist, _ = run_reference(path, "mtp", prompt, n_new, dict(temperature=temp, top_p=top_p, top_k=top_k, seed=seed))
+        assert len(r_tok) == n_new and summ.get("enabled") == "true"
+        b = qb.Batch(model, 1, CTX, K)
+        dq = qb.serve.DrawQueue(R.MT64(seed), K + 1)
+        b.prefill_sampled(0, prompt, dq.take(), temp, top_p, top_k)
+        e_tok, e_acc = list(b.read_output()[0]), []
+        while len(e_tok) < n_new:
+            depth = max(1, min(K, n_new - len(e_tok)))
+            b.set_draft_policy([depth])
+            b.mtp_step_sampled(np.array([dq.peek()], np.float64), temp, top_p, top_k)
+            out = b.read_output()[0]
+            dq.consume_step(len(out), depth)
+            e_acc.append(len(out) - 1)
+            e_tok += out
+        b.close()
+        n = common_prefix(r_tok, e_tok[:n_new])
+        prefixes.append(n)
+        print("seed %d: common prefix %d of %d; reference hist %s accepted %s/%s; product accepted lengths %s"
+              % (seed, n, n_new, hist, summ.get("accepted"), summ.get("drafted"), np.bincount(e_acc, minlength=K + 1).tolist()))
+    model.close()
+    # a wrong draw order would break every stream within its first step or two; numeric noise breaks one only where a
+    # draw falls next to a boundary
+    assert max(prefixes) >= 12 and sorted(prefixes)[1] >= 4, prefixes
