@@ -199,4 +199,5 @@ def test_reference_engine_sampled_mtp(qb, orc, ctx, tmp_path):
     model.close()
     # a wrong draw order would break every stream within its first step or two; numeric noise breaks one only where a
     # draw falls next to a boundary
-    assert max(prefixes) >= 12 and sorted(prefixes)[1] >= 4, prefixes
+    # (measured: all four requests equal to the reference's for all 32 tokens, accepted-length histograms equal)
+    assert sorted(prefixes)[1] == n_new and min(prefixes) >= 4, prefixes
