@@ -397,6 +397,10 @@ int qb_mtp_step_sampled(qb_ctx *ctx, qb_batch *b, float temp, float top_p, int32
 int qb_read_step_output(qb_ctx *ctx, qb_batch *b, int32_t *n_out_host, int32_t *tokens_host);
 /* Counters since creation: [steps, drafted, accepted, emitted] per batch. */
 int qb_batch_stats(qb_ctx *ctx, qb_batch *b, int64_t *out4);
+/* Counters behind the reference's `native mtp_spec_summary:` / `native mtp_accept_hist:` lines
+ * (src/qwen_native_backend.cpp:16313-16392): out[0] = steps that rejected a draft (rejected = rollbacks there),
+ * out[1 + a] = steps that accepted exactly a drafts (len<a>), for a = 0 .. min(k, n - 2). */
+int qb_batch_accept_hist(qb_ctx *ctx, qb_batch *b, int64_t *out, uint32_t n);
 /* Position (committed tokens) of a sequence; reads a device counter (syncs). */
 int qb_seq_position(qb_ctx *ctx, qb_batch *b, uint32_t seq, int32_t *pos);
 /* Slot recycling of the continuous-batching loop (request retirement and admission,

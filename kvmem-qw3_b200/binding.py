@@ -123,6 +123,7 @@ SIGNATURES = {
     "qb_batch_set_active": (i32, [vp, vp, u32]),
     "qb_seq_swap": (i32, [vp, vp, u32, u32]),
     "qb_batch_set_penalties": (i32, [vp, vp, C.c_float, C.c_float]),
+    "qb_batch_accept_hist": (i32, [vp, vp, vp, u32]),
     "qb_sample_rows": (i32, [vp, vp, u32, u32, u32, vp, vp, vp, C.c_float, C.c_float, i32, C.c_float, vp, vp, vp]),
     "qb_mtp_sample_rows": (i32, [vp, vp, C.c_float, C.c_float, i32, C.c_float, vp]),
     "qb_mtp_step_sampled": (i32, [vp, vp, C.c_float, C.c_float, i32, C.c_float, vp]),
@@ -571,6 +572,25 @@ class Batch:
         out = np.zeros(4, np.int64)
         check(lib().qb_batch_stats(self.ctx.h, self.h, _np_ptr(out)))
         return dict(steps=int(out[0]), drafted=int(out[1]), accepted=int(out[2]), emitted=int(out[3]))
+
+    def accept_hist(self):
+        """(steps that rejected a draft, [steps that accepted exactly a drafts for a = 0 .. k])."""
+        out = np.zeros(self.k + 2, np.int64)
+        check(lib().qb_batch_accept_hist(self.ctx.h, self.h, _np_ptr(out), out.size))
+        return int(out[0]), [int(v) for v in out[1:]]
+
+    def spec_summary_lines(self):
+        """The speculative loop's counters in the form of the reference's log lines (native mtp_spec_summary: and
+        native mtp_accept_hist:, src/qwen_native_backend.cpp:16313-16392), so that its log parsers keep working; fields
+        this engine has no counterpart for (adaptive policy, per-phase host timers) carry their neutral values."""
+        st = self.stats()
+        rejected, hist = self.accept_hist()
+        acc = st["accepted"] / st["drafted"] if st["drafted"] else 0.0
+        summary = ("native mtp_spec_summary: enabled=true batches=%d drafted=%d accepted=%d rejected=%d rollbacks=%d adaptive=false "
+                   "promotions=0 reject_budget=off fallback=false acceptance=%.4f state_ckpt_count=%d batched_verify_batches=%d "
+                   "batched_verify_tokens=%d" % (st["steps"], st["drafted"], st["accepted"], rejected, rejected, acc, self.k,
+                                                  st["steps"], st["steps"] * (self.k + 1)))
+        return [summary, "native mtp_accept_hist:" + "".join(" len%d=%d" % (a, n) for a, n in enumerate(hist))]
 
     def reset(self, seq):
         """Retire the request in slot `seq`: position 0, zero recurrent state; prefill admits the next one."""

@@ -393,7 +393,7 @@ struct qb_batch {
     int32_t *tok_buf = nullptr, *seqpos_buf = nullptr, *prefix_pos = nullptr, *prefix_tok = nullptr;
     int32_t *out_rec = nullptr;            // [n_out (n_seqs) | tokens (n_seqs*(k+1)) | pos (n_seqs)]
     int32_t *map_prevh = nullptr, *map_prefix = nullptr, *map_chunk = nullptr, *map_last = nullptr;
-    long long *stats = nullptr;            // steps, drafted, accepted, emitted
+    long long *stats = nullptr;            // [QB_STATS]: steps, drafted, accepted, emitted, rejecting steps, -, -, -, then steps by accepted length
     int32_t *out_rec_host = nullptr;       // pinned mirror of out_rec
     // activations
     float *hid = nullptr;                  // [rows_cap + n_seqs][H]; rows rows_cap+s hold prev hidden of seq s
@@ -419,9 +419,21 @@ struct qb_batch {
     int32_t eos_token = -1;                // a draft equal to it ends the chain (-1: none)
     void *swap_tmp = nullptr;              // one sequence's largest per-layer state block (qb_seq_swap)
     size_t swap_bytes = 0;
+    // sampled steps: pinned staging ring of the step's draws (a slot is reused when its copy of four steps ago has landed)
+    static constexpr int SAMP_RING = 4;
+    double *samp_stage = nullptr;
+    cudaEvent_t samp_ev[SAMP_RING] = {};
+    uint32_t samp_slot = 0;
+    // position probe: keeps host_pos near the device's positions when nobody reads the step records (see probe_tick)
+    int32_t *probe_host = nullptr;         // pinned [n_seqs]
+    cudaEvent_t probe_ev = nullptr;
+    bool probe_pending = false;
+    int32_t probe_adv = 0;                 // positions enqueued since the probe's copy
+    uint32_t steps_since_probe = 0;
 };
 
 static size_t ctl_count(const qb_batch *b);
+static constexpr size_t QB_STATS = 16;
 
 static int alloc_qbuf(QBuf &b, uint32_t rows, uint32_t K) {
     b.K = K;
@@ -506,8 +518,8 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
         if (draft_k)
             QB_CUDA(cudaMemcpyAsync(b->map_prefix, mp.data(), mp.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
         QB_CUDA(cudaStreamSynchronize(ctx->stream));
-        QB_CUDA(cudaMalloc(&b->stats, 4 * sizeof(long long)));
-        QB_CUDA(cudaMemsetAsync(b->stats, 0, 4 * sizeof(long long), ctx->stream));
+        QB_CUDA(cudaMalloc(&b->stats, QB_STATS * sizeof(long long)));
+        QB_CUDA(cudaMemsetAsync(b->stats, 0, QB_STATS * sizeof(long long), ctx->stream));
         QB_CUDA(cudaHostAlloc(&b->out_rec_host, (size_t)n_seqs * (K1 + 2) * sizeof(int32_t), cudaHostAllocDefault));
         QB_CUDA(cudaHostAlloc(&b->limit_host, (size_t)n_seqs * sizeof(int32_t), cudaHostAllocDefault));
         for (uint32_t s = 0; s < n_seqs; ++s) b->limit_host[s] = (int32_t)draft_k;
@@ -570,6 +582,10 @@ extern "C" void qb_batch_destroy(qb_ctx *ctx, qb_batch *b) {
     if (b->limit_host) cudaFreeHost(b->limit_host);
     if (b->tok_stage) cudaFreeHost(b->tok_stage);
     if (b->first_draw_stage) cudaFreeHost(b->first_draw_stage);
+    if (b->samp_stage) cudaFreeHost(b->samp_stage);
+    for (cudaEvent_t e : b->samp_ev) if (e) cudaEventDestroy(e);
+    if (b->probe_host) cudaFreeHost(b->probe_host);
+    if (b->probe_ev) cudaEventDestroy(b->probe_ev);
     delete b;
 }
 
@@ -683,6 +699,8 @@ __global__ void accept_commit_kernel(const float *pval, const int32_t *pidx, uin
         atomicAdd(&stats[1], (unsigned long long)kk);
         atomicAdd(&stats[2], (unsigned long long)a);
         atomicAdd(&stats[3], (unsigned long long)(a + 1));
+        if (a < kk) atomicAdd(&stats[4], 1ull);                      // a step that rejected a draft (mtp_spec_rejected)
+        atomicAdd(&stats[8 + min(a, 7u)], 1ull);                     // mtp_accept_len_hist
     }
     __syncthreads();
     const uint32_t a = (uint32_t)s_acc;
@@ -968,6 +986,33 @@ static uint32_t max_host_pos(const qb_batch *b) {
 }
 static void advance_host_pos(qb_batch *b, int32_t by) {
     for (uint32_t s = 0; s < b->n_active; ++s) b->host_pos[s] += by;
+    b->probe_adv += by;
+}
+// host_pos is an upper bound: a speculative step advances it by k + 1 although the device commits 1 .. k + 1 positions.
+// A caller that reads the step records gets the exact positions back (qb_read_step_output); for one that does not, every
+// PROBE_EVERY steps the device positions are copied to pinned memory behind the step, and once that copy has landed
+// (cudaEventQuery: never a wait) the bound becomes copied position + positions enqueued since.  Anything else that
+// rewrites host_pos (prefill, reset, swap, restore, a change of the active count) drops a probe in flight.
+static constexpr uint32_t PROBE_EVERY = 8;
+static void probe_cancel(qb_batch *b) { b->probe_pending = false; b->steps_since_probe = 0; }
+static int probe_tick(qb_ctx *ctx, qb_batch *b) {
+    if (b->probe_pending) {
+        if (cudaEventQuery(b->probe_ev) == cudaSuccess) {
+            for (uint32_t s = 0; s < b->n_active; ++s) b->host_pos[s] = std::min(b->host_pos[s], b->probe_host[s] + b->probe_adv);
+            probe_cancel(b);
+        }
+        return QB_OK;
+    }
+    if (++b->steps_since_probe < PROBE_EVERY) return QB_OK;
+    if (!b->probe_host) {
+        QB_CUDA(cudaHostAlloc(&b->probe_host, (size_t)b->n_seqs * sizeof(int32_t), cudaHostAllocDefault));
+        QB_CUDA(cudaEventCreateWithFlags(&b->probe_ev, cudaEventDisableTiming));
+    }
+    QB_CUDA(cudaMemcpyAsync(b->probe_host, b->pos, (size_t)b->n_active * sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    QB_CUDA(cudaEventRecord(b->probe_ev, ctx->stream));
+    b->probe_pending = true;
+    b->probe_adv = 0;
+    return QB_OK;
 }
 
 static int mark_seen_record(qb_ctx *ctx, qb_batch *b, uint32_t seq0, uint32_t ns) {
@@ -1059,6 +1104,7 @@ static int prefill_impl(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *t
             QB_LAUNCHED(ctx, "advance_kernel");
         }
         b->host_pos[seq] += (int32_t)M;
+        probe_cancel(b);
     }
     return QB_OK;
 }
@@ -1105,7 +1151,7 @@ extern "C" int qb_decode_greedy_step(qb_ctx *ctx, qb_batch *b) {
     QB_LAUNCHED(ctx, "greedy_commit_kernel");
     QB_TRY(mark_seen_record(ctx, b, 0, b->n_active));
     advance_host_pos(b, 1);
-    return QB_OK;
+    return probe_tick(ctx, b);
 }
 
 extern "C" int qb_mtp_draft(qb_ctx *ctx, qb_batch *b) {
@@ -1170,7 +1216,7 @@ extern "C" int qb_mtp_accept_commit(qb_ctx *ctx, qb_batch *b) {
     rs.seq0 = 0; rs.ns = ns; rs.R = k; rs.seq_pos = b->prefix_pos; rs.max_pos = max_host_pos(b) + k + 1;
     QB_TRY(mtp_forward(ctx, b, b->prefix_tok, b->hid, b->map_prefix, rs, true));
     advance_host_pos(b, (int32_t)(k + 1));               // upper bound until the host reads the step record
-    return QB_OK;
+    return probe_tick(ctx, b);
 }
 
 // Tensor-parallel form of a batch: its model is a shard (qb_model_create_synth_tp) and `group` the FFN group of the ranks
@@ -1216,14 +1262,22 @@ extern "C" int qb_mtp_sample_rows(qb_ctx *ctx, qb_batch *b, float temp, float to
     QB_CUDA(cudaSetDevice(ctx->device));
     const uint32_t ns = b->n_active, k = b->k, K1 = k + 1, rows = ns * K1;
     if (!b->samp_u) QB_CUDA(cudaMalloc(&b->samp_u, 2 * (size_t)b->n_seqs * K1 * sizeof(double)));
-    std::vector<double> u(2 * (size_t)rows, 0.0);
+    const size_t slot_doubles = 2 * (size_t)b->n_seqs * K1;
+    if (!b->samp_stage) {
+        QB_CUDA(cudaHostAlloc(&b->samp_stage, qb_batch::SAMP_RING * slot_doubles * sizeof(double), cudaHostAllocDefault));
+        for (cudaEvent_t &e : b->samp_ev) QB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    // no stream synchronisation: the draws go through a pinned ring; a slot waits only for its own copy of four steps ago
+    const uint32_t slot = b->samp_slot++ % qb_batch::SAMP_RING;
+    QB_CUDA(cudaEventSynchronize(b->samp_ev[slot]));
+    double *u = b->samp_stage + slot * slot_doubles;
     for (uint32_t s = 0; s < ns; ++s)
         for (uint32_t i = 0; i < K1; ++i) {
             u[(size_t)s * K1 + i] = u_host[(size_t)s * K1 + i];                                  // acceptance draw of row i
             u[(size_t)rows + s * K1 + i] = u_host[(size_t)s * K1 + (i < k ? i + 1 : k)];          // residual / bonus draw
         }
-    QB_CUDA(cudaMemcpyAsync(b->samp_u, u.data(), u.size() * sizeof(double), cudaMemcpyHostToDevice, ctx->stream));
-    QB_CUDA(cudaStreamSynchronize(ctx->stream));       // the vector goes out of scope
+    QB_CUDA(cudaMemcpyAsync(b->samp_u, u, 2 * (size_t)rows * sizeof(double), cudaMemcpyHostToDevice, ctx->stream));
+    QB_CUDA(cudaEventRecord(b->samp_ev[slot], ctx->stream));
     const qb_model_config &c = b->m->cfg;
     return qb_launch_sample_rows(ctx, b->logits, rows, c.vocab_size, c.vocab_size, b->drafts, K1, b->samp_u, b->samp_u + rows, temp, top_p,
                                  top_k, min_p, nullptr, nullptr, nullptr, b->am_val, b->am_idx, QB_ARGMAX_BLOCKS, b->pen_presence, b->pen_repetition,
@@ -1252,6 +1306,20 @@ extern "C" int qb_read_step_output(qb_ctx *ctx, qb_batch *b, int32_t *n_out_host
     if (n_out_host) memcpy(n_out_host, b->out_rec_host, ns * sizeof(int32_t));
     if (tokens_host) memcpy(tokens_host, b->out_rec_host + ns, (size_t)ns * K1 * sizeof(int32_t));
     for (uint32_t s = 0; s < ns; ++s) b->host_pos[s] = b->out_rec_host[ns + (size_t)ns * K1 + s];
+    probe_cancel(b);
+    return QB_OK;
+}
+
+// Counters of the speculative loop as the reference's summary lines report them (native mtp_spec_summary: /
+// mtp_accept_hist:, src/qwen_native_backend.cpp:16313-16392): out[0] = steps that rejected a draft, out[1 + a] = steps that
+// accepted exactly a drafts, a = 0 .. min(k, n - 2).
+extern "C" int qb_batch_accept_hist(qb_ctx *ctx, qb_batch *b, int64_t *out, uint32_t n) {
+    QB_REQUIRE(ctx && b && out && n >= 1, "qb_batch_accept_hist: bad arguments");
+    long long h[QB_STATS];
+    QB_CUDA(cudaMemcpyAsync(h, b->stats, sizeof(h), cudaMemcpyDeviceToHost, ctx->stream));
+    QB_CUDA(cudaStreamSynchronize(ctx->stream));
+    out[0] = h[4];
+    for (uint32_t a = 0; a + 1 < n && a <= b->k && a < 8; ++a) out[1 + a] = h[8 + a];
     return QB_OK;
 }
 
@@ -1289,6 +1357,7 @@ extern "C" int qb_seq_reset(qb_ctx *ctx, qb_batch *b, uint32_t seq) {
     QB_CUDA(cudaMemsetAsync(b->hid + (size_t)(b->rows_cap + seq) * c.n_embd, 0, (size_t)c.n_embd * sizeof(float), ctx->stream));
     if (b->seen) QB_CUDA(cudaMemsetAsync(b->seen + (size_t)seq * b->seen_words, 0, (size_t)b->seen_words * sizeof(uint32_t), ctx->stream));
     b->host_pos[seq] = 0;
+    probe_cancel(b);
     return QB_OK;
 }
 
@@ -1297,6 +1366,7 @@ extern "C" int qb_seq_reset(qb_ctx *ctx, qb_batch *b, uint32_t seq) {
 extern "C" int qb_batch_set_active(qb_ctx *ctx, qb_batch *b, uint32_t n) {
     QB_REQUIRE(ctx && b && n <= b->n_seqs, "qb_batch_set_active: bad arguments");
     b->n_active = n;
+    probe_cancel(b);
     return QB_OK;
 }
 
@@ -1336,6 +1406,7 @@ extern "C" int qb_seq_swap(qb_ctx *ctx, qb_batch *b, uint32_t s1, uint32_t s2) {
     QB_CUDA(qb_launch_pdl(ctx->stream, swap_ctl_kernel, dim3(1), dim3(32), (size_t)0, b->pos, b->sel, b->cur, b->prefix_pos, b->out_rec, b->limit, b->n_seqs, K1, s1, s2));
     QB_LAUNCHED(ctx, "swap_ctl_kernel");
     std::swap(b->host_pos[s1], b->host_pos[s2]);
+    probe_cancel(b);
     return QB_OK;
 }
 
@@ -1364,7 +1435,7 @@ static int for_each_state_block(qb_batch *b, F f) {
     const size_t csz = (size_t)b->n_seqs * K1 * b->m->qkv_dim() * 3 * sizeof(float);
     QB_TRY(f((void *)b->ctl, ctl_count(b) * sizeof(int32_t)));
     QB_TRY(f((void *)(b->hid + (size_t)b->rows_cap * c.n_embd), (size_t)b->n_seqs * c.n_embd * sizeof(float)));
-    QB_TRY(f((void *)b->stats, 4 * sizeof(long long)));
+    QB_TRY(f((void *)b->stats, QB_STATS * sizeof(long long)));
     QB_TRY(f((void *)b->page_table, (size_t)b->n_seqs * b->pages_per_seq * sizeof(int32_t)));      // qb_seq_swap exchanges rows
     for (uint32_t il = 0; il < c.n_layers; ++il) {
         if (!b->state[il]) continue;
@@ -1403,6 +1474,7 @@ extern "C" int qb_batch_restore(qb_ctx *ctx, qb_batch *b, const qb_snapshot *sn)
         return QB_OK;
     }));
     b->host_pos = sn->host_pos; b->conv_par = sn->conv_par; b->n_active = sn->n_active;
+    probe_cancel(b);
     return QB_OK;
 }
 

@@ -206,3 +206,34 @@ def test_capacity_error_is_reported_not_faulted(qb, orc, ctx, tiny):
     with pytest.raises(qb.QbError):
         b.prefill(0, tiny["prompt"])
     b.close()
+
+
+def test_unread_steps_do_not_exhaust_the_position_bound(qb, orc, ctx, tiny):
+    """A loop that never reads the step records: the host's position bound advances by k + 1 per step although the
+    random model accepts next to nothing, so without a correction 256 positions would be "used up" after 64 steps.  The
+    engine refreshes the bound from the device's positions without a synchronisation; 150 unread steps must fit, the
+    tokens must be the ones a loop that reads every step gets, and the speculative counters must add up."""
+    k, n_steps = 3, 150
+    prompt = tiny["prompt"][:20]
+    a = qb.Batch(tiny["model"], 1, 20 + 256, k)
+    a.prefill(0, prompt)
+    want = list(a.read_output()[0])
+    for _ in range(n_steps):
+        a.mtp_step()
+        want += a.read_output()[0]
+    a.close()
+    assert len(want) < 256
+    b = qb.Batch(tiny["model"], 1, 20 + 256, k)
+    b.prefill(0, prompt)
+    b.read_output()
+    for _ in range(n_steps):
+        b.mtp_step()                       # no read_output, no synchronisation
+    st = b.stats()
+    rejected, hist = b.accept_hist()
+    assert st["steps"] == n_steps and st["emitted"] == len(want)
+    assert sum(hist) == n_steps and sum(a_ * n for a_, n in enumerate(hist)) == st["accepted"]
+    assert rejected == n_steps - hist[k]
+    lines = b.spec_summary_lines()
+    assert lines[0].startswith("native mtp_spec_summary: enabled=true batches=%d drafted=%d accepted=%d" % (n_steps, st["drafted"], st["accepted"]))
+    assert lines[1] == "native mtp_accept_hist:" + "".join(" len%d=%d" % (i, n) for i, n in enumerate(hist))
+    b.close()

@@ -40,13 +40,20 @@ def run_reference(path, mode, prompt, n_new, sampling=None):
     assert m, r.stdout[-2000:]
     toks = G.parse_token_text(m.group(1).strip())
     log = r.stderr + r.stdout
+    summary, hist = parse_summary(log)
+    return toks, summary, hist, log
+
+
+def parse_summary(log):
+    """The `native mtp_spec_summary:` / `native mtp_accept_hist:` lines of a log (the reference's, or the product's
+    Batch.spec_summary_lines())."""
     summary = {}
     sm = re.search(r"native mtp_spec_summary:(.*)", log)
     if sm:
         summary = dict(kv.split("=", 1) for kv in sm.group(1).split() if "=" in kv)
     hm = re.search(r"native mtp_accept_hist:(.*)", log)
     hist = [int(v.split("=")[1]) for v in hm.group(1).split()] if hm else None
-    return toks, summary, hist, log
+    return summary, hist
 
 
 def engine_streams(qb, model, prompt, n_new):
@@ -69,6 +76,7 @@ def engine_streams(qb, model, prompt, n_new):
         acc.append(len(t) - 1)
         spec += t
     st = b.stats()
+    st["summary"], st["hist"] = parse_summary("\n".join(b.spec_summary_lines()))
     b.close()
     return greedy[:n_new], spec[:n_new], acc, st
 
@@ -148,6 +156,11 @@ def test_reference_engine_greedy_and_mtp(qb, orc, ctx, tmp_path, predictable):
     if n_re == N_NEW:
         # same token stream: the step structure must be the same too
         assert r_batches == len(e_acc) and r_drafted == e_stats["drafted"]
+        # the product's own summary lines, read by the same parser: same step structure, field by field
+        for key in ("enabled", "batches", "drafted"):
+            assert e_stats["summary"][key] == summ[key], key
+        if r_accepted == e_stats["accepted"]:
+            assert e_stats["hist"] == hist and e_stats["summary"]["rejected"] == summ["rejected"]
         tol = max(2, r_drafted // 10)
         assert abs(r_accepted - e_stats["accepted"]) <= tol
         assert abs(r_accepted - sum(o_acc)) <= tol
