@@ -313,6 +313,38 @@ size_t qb_model_weight_bytes(const qb_model *m);
  * 2 = seeded shuffle (the alloc modes of src/qwen_executor.cpp:1752-1774). */
 int  qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_ctx, uint32_t draft_k,
                      uint32_t page_size, int page_order, qb_batch **out);
+/* The pooled form of the same (GlobalKvPagePool, src/qwen_native_backend.cpp:1155-1265; allocate_continuous_kv_cache /
+ * _mtp_kv_cache, :6603-6709): the K/V caches hold pool_pages pages in all, shared by the n_seqs sequences; a sequence's
+ * page-table row grows page by page as its position grows (most recently freed page first) and goes back to the pool at
+ * qb_seq_reset.  A call that needs more pages than are free returns QB_ERR_CAPACITY before anything is launched. */
+int  qb_batch_create_pooled(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_ctx, uint32_t draft_k,
+                            uint32_t page_size, uint32_t pool_pages, qb_batch **out);
+int  qb_batch_pool_info(qb_ctx *ctx, qb_batch *b, uint32_t *free_pages, uint32_t *total_pages, uint32_t *page_size);
+/* The pages sequence `seq` holds, in position order (at most cap written; *n_out = how many it holds). */
+int  qb_seq_pages(qb_ctx *ctx, qb_batch *b, uint32_t seq, int32_t *pages_out, uint32_t cap, uint32_t *n_out);
+/* The allocator of the pooled batches on its own, for a caller that keeps its own page tables over the op-level entry
+ * points (host side only, thread-safe): a LIFO free stack that hands out page 0 first; a page may have several holders
+ * (qb_page_pool_share) and returns to the stack when the last one drops it.  alloc: page id or -1 when exhausted;
+ * share: 1, or 0 for a page that is not in use; drop: holders left, or -1 for a page that is not in use. */
+void    *qb_page_pool_create(uint32_t total_pages);
+void     qb_page_pool_destroy(void *pool);
+int32_t  qb_page_pool_alloc(void *pool);
+int32_t  qb_page_pool_share(void *pool, int32_t page);
+int32_t  qb_page_pool_drop(void *pool, int32_t page);
+uint32_t qb_page_pool_free_count(void *pool);
+/* Shared prompt prefixes (the server's prefix cache, src/qwen_native_backend.cpp:9785-10410: a hit seeds the request from
+ * the cached entry, whose pages stay pinned while it lives).  qb_prefix_capture takes an entry from a sequence of a pooled
+ * batch that has ingested exactly the prefix with qb_prefill_chunk (a whole number of pages): the entry holds the
+ * prefix's K/V pages once more and copies of the DeltaNet state, conv windows and last hidden row at its end;
+ * tokens_host (the prefix's tokens; may be NULL unless token penalties are on) feeds the seen-token record.
+ * qb_prefix_attach makes an empty sequence (after qb_seq_reset) of the same batch continue from the prefix end: it shares
+ * the pages and receives the copies; the caller goes on with qb_prefill / qb_prefill_chunk of the rest of its prompt.
+ * qb_prefix_release drops the entry's hold on the pages (they return to the pool when no sequence uses them either). */
+typedef struct qb_prefix qb_prefix;
+int  qb_prefix_capture(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n_tokens, qb_prefix **out);
+int  qb_prefix_attach(qb_ctx *ctx, qb_batch *b, uint32_t seq, const qb_prefix *prefix);
+uint32_t qb_prefix_tokens(const qb_prefix *prefix);
+void qb_prefix_release(qb_ctx *ctx, qb_prefix *prefix);
 void qb_batch_destroy(qb_ctx *ctx, qb_batch *b);
 
 /* forward_n_tokens prefill branch + prime_mtp_prefix (src/qwen_executor.cpp:6003-6836,

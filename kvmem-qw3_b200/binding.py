@@ -104,6 +104,19 @@ SIGNATURES = {
     "qb_model_destroy": (None, [vp, vp]),
     "qb_model_weight_bytes": (sz, [vp]),
     "qb_batch_create": (i32, [vp, vp, u32, u32, u32, u32, i32, C.POINTER(vp)]),
+    "qb_batch_create_pooled": (i32, [vp, vp, u32, u32, u32, u32, u32, C.POINTER(vp)]),
+    "qb_batch_pool_info": (i32, [vp, vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]),
+    "qb_seq_pages": (i32, [vp, vp, u32, vp, u32, C.POINTER(u32)]),
+    "qb_prefix_capture": (i32, [vp, vp, u32, vp, u32, C.POINTER(vp)]),
+    "qb_prefix_attach": (i32, [vp, vp, u32, vp]),
+    "qb_prefix_tokens": (u32, [vp]),
+    "qb_prefix_release": (None, [vp, vp]),
+    "qb_page_pool_create": (vp, [u32]),
+    "qb_page_pool_destroy": (None, [vp]),
+    "qb_page_pool_alloc": (i32, [vp]),
+    "qb_page_pool_share": (i32, [vp, i32]),
+    "qb_page_pool_drop": (i32, [vp, i32]),
+    "qb_page_pool_free_count": (u32, [vp]),
     "qb_batch_destroy": (None, [vp, vp]),
     "qb_prefill": (i32, [vp, vp, u32, vp, u32]),
     "qb_prefill_chunk": (i32, [vp, vp, u32, vp, u32]),
@@ -489,11 +502,15 @@ class Model:
 class Batch:
     """Executor state of n_seqs requests (the QwenExecutor-side state of the reference)."""
 
-    def __init__(self, model, n_seqs, max_ctx, k, page_size=16, page_order=0):
+    def __init__(self, model, n_seqs, max_ctx, k, page_size=16, page_order=0, pool_pages=0):
+        """pool_pages > 0: the pooled form (one K/V page pool shared by the sequences, pages handed out as positions grow)."""
         self.ctx, self.model, self.n_seqs, self.k, self.max_ctx = model.ctx, model, n_seqs, k, max_ctx
         self.n_active = n_seqs
         h = vp()
-        check(lib().qb_batch_create(self.ctx.h, model.h, n_seqs, max_ctx, k, page_size, page_order, C.byref(h)))
+        if pool_pages:
+            check(lib().qb_batch_create_pooled(self.ctx.h, model.h, n_seqs, max_ctx, k, page_size, pool_pages, C.byref(h)))
+        else:
+            check(lib().qb_batch_create(self.ctx.h, model.h, n_seqs, max_ctx, k, page_size, page_order, C.byref(h)))
         self.h = h
         self._n = np.zeros(n_seqs, np.int32)
         self._t = np.zeros((n_seqs, k + 1), np.int32)
@@ -502,6 +519,30 @@ class Batch:
         if self.h:
             lib().qb_batch_destroy(self.ctx.h, self.h)
             self.h = None
+
+    def pool_info(self):
+        f, t, ps = u32(), u32(), u32()
+        check(lib().qb_batch_pool_info(self.ctx.h, self.h, C.byref(f), C.byref(t), C.byref(ps)))
+        return dict(free=f.value, total=t.value, page_size=ps.value)
+
+    def seq_pages(self, seq):
+        n = u32()
+        out = np.zeros(4096, np.int32)
+        check(lib().qb_seq_pages(self.ctx.h, self.h, seq, _np_ptr(out), out.size, C.byref(n)))
+        return out[:n.value].tolist()
+
+    def prefix_capture(self, seq, tokens=None):
+        """An entry of the prefix cache from sequence `seq`, which must stand at the end of a prefill(..., more=True)."""
+        t = None if tokens is None else np.ascontiguousarray(tokens, np.int32)
+        h = vp()
+        check(lib().qb_prefix_capture(self.ctx.h, self.h, seq, _np_ptr(t) if t is not None else None, 0 if t is None else len(t), C.byref(h)))
+        return h
+
+    def prefix_attach(self, seq, prefix):
+        check(lib().qb_prefix_attach(self.ctx.h, self.h, seq, prefix))
+
+    def prefix_release(self, prefix):
+        lib().qb_prefix_release(self.ctx.h, prefix)
 
     def prefill(self, seq, tokens, more=False):
         """Ingests prompt tokens of sequence `seq`; more=True: the prompt continues in a later call (no token is chosen)."""

@@ -78,7 +78,12 @@ __global__ void qk_norm_rope_append_kernel(AttnArgs a, const int32_t *__restrict
     }
     if (kind == 0) { base[i] = v; return; }
     const uint32_t pg = (uint32_t)pos / a.page_size;
-    const size_t slot = (size_t)a.page_table[(size_t)seq * a.pt_stride + pg] * a.page_size + (uint32_t)pos % a.page_size;
+    const int32_t page = a.page_table[(size_t)seq * a.pt_stride + pg];
+    if (page < 0) {                                     // no page assigned (pooled page tables): recorded, not dereferenced
+        if (i == 0 && a.err_flag) atomicExch(a.err_flag, 3002);
+        return;
+    }
+    const size_t slot = (size_t)page * a.page_size + (uint32_t)pos % a.page_size;
     const uint32_t h = kind == 1 ? unit - a.n_heads : unit - a.n_heads - a.n_kv;
     __half *dst = (kind == 1 ? a.k_cache : a.v_cache) + (slot * a.n_kv + h) * hd;
     dst[i] = __float2half_rn(v);

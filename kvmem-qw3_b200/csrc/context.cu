@@ -1,5 +1,6 @@
 // Context, memory, events and TMA tensor-map encoding of libqw3b200.
 #include "qb_internal.h"
+#include "page_pool.h"
 
 #include <cudaTypedefs.h>
 
@@ -62,7 +63,7 @@ extern "C" int qb_synchronize(qb_ctx *ctx) {
     QB_CUDA(cudaMemcpy(&flag, ctx->err_flag_dev, sizeof(int), cudaMemcpyDeviceToHost));
     if (flag != 0) {
         cudaMemset(ctx->err_flag_dev, 0, sizeof(int));
-        return qb_fail(QB_ERR_CUDA, "a kernel gave up a bounded wait (code %d)", flag);
+        return qb_fail(QB_ERR_CUDA, "a kernel recorded an error (code %d: 3001 / 3002 = a K/V append to an unassigned page, skipped; other codes = a bounded wait that ran out)", flag);
     }
     return QB_OK;
 }
@@ -290,3 +291,13 @@ extern "C" int qb_trace_summary(qb_ctx *ctx, char *buf, size_t buf_bytes) {
     if (buf_bytes) buf[std::min(off, buf_bytes - 1)] = 0;
     return QB_OK;
 }
+
+// ---- the page pool on its own (host side only; no device needed) -----------------------------------------------------
+// For a caller that keeps its own page tables over the op-level entry points (qb_kv_append / qb_attention_paged take
+// page indices): the allocator the pooled batches use, GlobalKvPagePool's role (src/qwen_native_backend.cpp:1155-1265).
+extern "C" void *qb_page_pool_create(uint32_t total_pages) { return total_pages ? new QbPagePool(total_pages) : nullptr; }
+extern "C" void qb_page_pool_destroy(void *pool) { delete (QbPagePool *)pool; }
+extern "C" int32_t qb_page_pool_alloc(void *pool) { return pool ? ((QbPagePool *)pool)->alloc() : -1; }
+extern "C" int32_t qb_page_pool_share(void *pool, int32_t page) { return pool && ((QbPagePool *)pool)->share(page) ? 1 : 0; }
+extern "C" int32_t qb_page_pool_drop(void *pool, int32_t page) { return pool ? ((QbPagePool *)pool)->drop(page) : -1; }
+extern "C" uint32_t qb_page_pool_free_count(void *pool) { return pool ? ((QbPagePool *)pool)->free_count() : 0; }

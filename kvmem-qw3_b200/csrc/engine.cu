@@ -11,6 +11,7 @@
 // device memory and are updated by kernels, so a step needs no host decision and no mid-step
 // synchronisation; the host reads back one small record per step.
 #include "qb_internal.h"
+#include "page_pool.h"
 
 #include <string>
 
@@ -387,6 +388,11 @@ struct qb_batch {
     std::vector<float *> conv_alt;         // second conv-state buffer: a forward reads one and writes the other
     int conv_par = 0;                      // which of the two holds the valid conv state (the same for all sequences)
     int32_t *page_table = nullptr;         // [n_seqs][pages_per_seq]
+    // pooled form (qb_batch_create_pooled): the caches hold pool->total() pages shared by all sequences; a sequence's
+    // page-table row grows as its position grows and goes back to the pool at qb_seq_reset
+    QbPagePool *pool = nullptr;
+    std::vector<std::vector<int32_t>> seq_pages;   // host mirror of the page-table rows (pooled form)
+    std::vector<int32_t> chunk_end_pos;            // position after the sequence's last qb_prefill_chunk, -1 once anything else moved it
     // device control block (all int32)
     int32_t *ctl = nullptr;
     int32_t *pos = nullptr, *sel = nullptr, *cur = nullptr, *drafts = nullptr, *zero_sel = nullptr;
@@ -447,8 +453,8 @@ static uint32_t env_u32(const char *name, uint32_t dflt) {
     return (v && *v) ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
 }
 
-extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_ctx, uint32_t draft_k,
-                               uint32_t page_size, int page_order, qb_batch **out) {
+static int batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_ctx, uint32_t draft_k,
+                        uint32_t page_size, int page_order, uint32_t pool_pages, qb_batch **out) {
     QB_REQUIRE(ctx && m && out && n_seqs > 0 && max_ctx > 0 && page_size > 0, "qb_batch_create: bad arguments");
     QB_REQUIRE(draft_k <= 7, "draft depth %u unsupported (<= 7)", draft_k);
     QB_REQUIRE(draft_k == 0 || m->cfg.mtp_layers == 1, "draft depth > 0 needs the MTP layer");
@@ -462,7 +468,7 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
     b->rows_cap = std::max(b->chunk, b->logit_rows);
     b->gemm_impl = (int)env_u32("QW3B200_GEMM_IMPL", 0);
     const uint32_t H = c.n_embd, K1 = draft_k + 1, L = c.n_layers, rows = b->rows_cap;
-    const size_t slots = (size_t)n_seqs * b->pages_per_seq * page_size;
+    const size_t slots = (size_t)(pool_pages ? pool_pages : n_seqs * b->pages_per_seq) * page_size;
     const uint32_t kvd = m->kvd();
     b->kc.assign(L + 1, nullptr); b->vc.assign(L + 1, nullptr); b->state.assign(L, nullptr); b->conv.assign(L, nullptr); b->conv_alt.assign(L, nullptr);
     for (uint32_t il = 0; il <= L; ++il) {
@@ -491,6 +497,12 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
         if (page_order == 1) std::reverse(pt.begin(), pt.end());
         if (page_order == 2)
             for (size_t i = total - 1; i > 0; --i) std::swap(pt[i], pt[qs_rand_u32(0x9a6e5, 7, i) % (i + 1)]);
+        if (pool_pages) {
+            // no page is assigned yet: -1 everywhere (the append kernel refuses a negative page and records it)
+            std::fill(pt.begin(), pt.end(), -1);
+            b->pool = new QbPagePool(pool_pages);
+            b->seq_pages.assign(n_seqs, {});
+        }
         QB_CUDA(cudaMalloc(&b->page_table, total * sizeof(int32_t)));
         QB_CUDA(cudaMemcpyAsync(b->page_table, pt.data(), total * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
         QB_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -560,14 +572,30 @@ extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32
     QB_TRY(alloc_qbuf(b->xq_ffn, rows, F));
     QB_TRY(alloc_qbuf(b->xq_cat, rows, 2 * H));
     b->host_pos.assign(n_seqs, 0);
+    b->chunk_end_pos.assign(n_seqs, -1);
     QB_CUDA(cudaStreamSynchronize(ctx->stream));
     *out = b;
     return QB_OK;
 }
 
+extern "C" int qb_batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_ctx, uint32_t draft_k,
+                               uint32_t page_size, int page_order, qb_batch **out) {
+    return batch_create(ctx, m, n_seqs, max_ctx, draft_k, page_size, page_order, 0, out);
+}
+
+// The pooled form: the K/V caches of every attention layer and of the MTP layer hold pool_pages pages in all (one pool,
+// one page table per sequence shared by all layers: allocate_continuous_kv_cache / _mtp_kv_cache,
+// src/qwen_native_backend.cpp:6603-6709), handed to sequences page by page as their positions grow.
+extern "C" int qb_batch_create_pooled(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_ctx, uint32_t draft_k,
+                                      uint32_t page_size, uint32_t pool_pages, qb_batch **out) {
+    QB_REQUIRE(pool_pages > 0, "qb_batch_create_pooled: needs a pool size");
+    return batch_create(ctx, m, n_seqs, max_ctx, draft_k, page_size, 0, pool_pages, out);
+}
+
 extern "C" void qb_batch_destroy(qb_ctx *ctx, qb_batch *b) {
     if (!b) return;
     cudaStreamSynchronize(ctx->stream);
+    delete b->pool;
     for (auto p : b->kc) if (p) cudaFree(p);
     for (auto p : b->vc) if (p) cudaFree(p);
     for (auto p : b->state) if (p) cudaFree(p);
@@ -845,6 +873,7 @@ static int attention_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t c
     a.rows = rows; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.hd = c.head_dim; a.rope_dim = c.rope_dim; a.eps = c.rms_eps;
     a.q_norm_w = L.q_norm; a.k_norm_w = L.k_norm; a.inv_freq = m->inv_freq;
     a.page_table = b->page_table + (size_t)rs.seq0 * b->pages_per_seq; a.pt_stride = b->pages_per_seq; a.page_size = b->page_size;
+    a.err_flag = ctx->err_flag_dev;
     a.k_cache = b->kc[cache_idx]; a.v_cache = b->vc[cache_idx];
     a.max_pos = rs.max_pos; a.part_acc = b->att_acc; a.part_ml = b->att_ml; a.kv_only = kv_only;
     if (kv_only) {
@@ -1044,12 +1073,192 @@ extern "C" int qb_batch_set_penalties(qb_ctx *ctx, qb_batch *b, float presence, 
 // no logits, no token is committed, nothing is counted as emitted or seen beyond the prompt tokens themselves.  samp
 // (temp > 0): the first token is drawn from the last row (pick_from_last_logits, src/qwen_native_backend.cpp:15399-15428:
 // penalties against the prompt, then sample_token with the request's first draw) instead of its argmax.
+// ---- pooled page tables ------------------------------------------------------------------------------------------
+// New entries of one page-table row, passed by value (no staging buffer to keep alive).
+struct PageRun { int32_t p[16]; };
+__global__ void set_pages_kernel(int32_t *row, uint32_t first, uint32_t n, PageRun run) {
+    QB_PDL_ENTER();
+    if (threadIdx.x < n) row[first + threadIdx.x] = run.p[threadIdx.x];
+}
+static int upload_pages(qb_ctx *ctx, qb_batch *b, uint32_t seq, uint32_t first, uint32_t n) {
+    const std::vector<int32_t> &pg = b->seq_pages[seq];
+    for (uint32_t off = 0; off < n; off += 16) {
+        PageRun run;
+        const uint32_t m = std::min(16u, n - off);
+        for (uint32_t i = 0; i < 16; ++i) run.p[i] = i < m ? pg[first + off + i] : -1;
+        QB_CUDA(qb_launch_pdl(ctx->stream, set_pages_kernel, dim3(1), dim3(32), (size_t)0, b->page_table + (size_t)seq * b->pages_per_seq,
+                              first + off, m, run));
+        QB_LAUNCHED(ctx, "set_pages_kernel");
+    }
+    return QB_OK;
+}
+// Pages for positions [0, upto) of a sequence (pooled form; nothing to do otherwise).  Allocation follows the host's
+// position bound, which is never below the device's position, so a page is there before a row is appended to it; the
+// pool hands out its most recently freed page first.  An exhausted pool is reported before anything is launched.
+static int ensure_pages(qb_ctx *ctx, qb_batch *b, uint32_t seq, uint32_t upto) {
+    if (!b->pool) return QB_OK;
+    std::vector<int32_t> &pg = b->seq_pages[seq];
+    const uint32_t need = std::min(b->pages_per_seq, (upto + b->page_size - 1) / b->page_size);
+    if (pg.size() >= need) return QB_OK;
+    const uint32_t first = (uint32_t)pg.size();
+    if (b->pool->free_count() < need - first)
+        return qb_fail(QB_ERR_CAPACITY, "K/V page pool exhausted: sequence %u needs %u more pages, %u of %u free", seq, need - first,
+                       b->pool->free_count(), b->pool->total());
+    while (pg.size() < need) pg.push_back(b->pool->alloc());
+    return upload_pages(ctx, b, seq, first, need - first);
+}
+static int ensure_step_pages(qb_ctx *ctx, qb_batch *b, uint32_t extra) {
+    if (!b->pool) return QB_OK;
+    for (uint32_t s = 0; s < b->n_active; ++s) QB_TRY(ensure_pages(ctx, b, s, (uint32_t)b->host_pos[s] + extra));
+    return QB_OK;
+}
+static void release_pages(qb_batch *b, uint32_t seq) {
+    if (!b->pool) return;
+    // last allocated first, so that the pool's next page is this sequence's first one again
+    for (auto it = b->seq_pages[seq].rbegin(); it != b->seq_pages[seq].rend(); ++it) b->pool->drop(*it);
+    b->seq_pages[seq].clear();
+}
+
+extern "C" int qb_batch_pool_info(qb_ctx *ctx, qb_batch *b, uint32_t *free_pages, uint32_t *total_pages, uint32_t *page_size) {
+    QB_REQUIRE(ctx && b, "qb_batch_pool_info: null argument");
+    QB_REQUIRE(b->pool, "qb_batch_pool_info: the batch has no page pool (qb_batch_create_pooled)");
+    if (free_pages) *free_pages = b->pool->free_count();
+    if (total_pages) *total_pages = b->pool->total();
+    if (page_size) *page_size = b->page_size;
+    return QB_OK;
+}
+// The pages a sequence holds, in position order (pooled form).
+extern "C" int qb_seq_pages(qb_ctx *ctx, qb_batch *b, uint32_t seq, int32_t *pages_out, uint32_t cap, uint32_t *n_out) {
+    QB_REQUIRE(ctx && b && seq < b->n_seqs && n_out, "qb_seq_pages: bad arguments");
+    QB_REQUIRE(b->pool, "qb_seq_pages: the batch has no page pool (qb_batch_create_pooled)");
+    const std::vector<int32_t> &pg = b->seq_pages[seq];
+    *n_out = (uint32_t)pg.size();
+    for (uint32_t i = 0; i < pg.size() && i < cap && pages_out; ++i) pages_out[i] = pg[i];
+    return QB_OK;
+}
+
+// ---- shared prompt prefixes (the prefix cache of the reference's server, src/qwen_native_backend.cpp:9785-10410:
+// seed_from_shared_prefix on a hit, pages pinned while an entry lives) -------------------------------------------------
+// An entry is taken from a sequence that has ingested a prefix with qb_prefill_chunk and nothing since: it holds the K/V
+// pages of the prefix once more (target layers and MTP layer share the page ids), and copies of what is not paged: every
+// DeltaNet layer's state and conv window at the prefix end, the last hidden row (the MTP pass of the next chunk pairs its
+// first token with it), the prefix's tokens (seen-token record).  Attaching it to an empty sequence makes that sequence
+// continue from the prefix end without ingesting it: same pages, copied state.  The prefix length must be a whole number
+// of pages, so the sequences' own tokens go to pages of their own.
+struct qb_prefix {
+    qb_batch *owner = nullptr;
+    uint32_t n_tokens = 0;
+    std::vector<int32_t> pages;
+    std::vector<float *> state, conv;     // per layer (recurrent layers only)
+    float *hid = nullptr;
+    int32_t *tokens_dev = nullptr;
+};
+__global__ void set_seq_ctl_kernel(int32_t *pos, int32_t *sel, int32_t *cur, uint32_t s, int32_t p) {
+    QB_PDL_ENTER();
+    if (threadIdx.x == 0) { pos[s] = p; sel[s] = 0; cur[s] = 0; }
+}
+
+extern "C" void qb_prefix_release(qb_ctx *ctx, qb_prefix *px) {
+    if (!px) return;
+    cudaStreamSynchronize(ctx->stream);
+    for (auto it = px->pages.rbegin(); it != px->pages.rend(); ++it) px->owner->pool->drop(*it);
+    for (float *p : px->state) if (p) cudaFree(p);
+    for (float *p : px->conv) if (p) cudaFree(p);
+    if (px->hid) cudaFree(px->hid);
+    if (px->tokens_dev) cudaFree(px->tokens_dev);
+    delete px;
+}
+
+extern "C" int qb_prefix_capture(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n_tokens, qb_prefix **out) {
+    QB_REQUIRE(ctx && b && out && seq < b->n_seqs, "qb_prefix_capture: bad arguments");
+    QB_REQUIRE(b->pool, "qb_prefix_capture: the batch has no page pool (qb_batch_create_pooled)");
+    const int32_t n = b->host_pos[seq];
+    QB_REQUIRE(n > 0 && b->chunk_end_pos[seq] == n, "qb_prefix_capture: sequence %u is not at the end of a qb_prefill_chunk", seq);
+    QB_REQUIRE((uint32_t)n % b->page_size == 0, "qb_prefix_capture: a prefix of %d tokens is not a whole number of %u-token pages", n, b->page_size);
+    QB_REQUIRE(!tokens_host || n_tokens == (uint32_t)n, "qb_prefix_capture: %u tokens given for a prefix of %d", n_tokens, n);
+    QB_REQUIRE(tokens_host || !b->seen, "qb_prefix_capture: a batch with token penalties needs the prefix's tokens");
+    QB_CUDA(cudaSetDevice(ctx->device));
+    const qb_model_config &c = b->m->cfg;
+    const uint32_t K1 = b->k + 1;
+    const size_t sfl = (size_t)c.ssm_num_v_heads * c.ssm_head_dim * c.ssm_head_dim, cfl = (size_t)b->m->qkv_dim() * 3;
+    qb_prefix *px = new qb_prefix();
+    px->owner = b; px->n_tokens = (uint32_t)n;
+    px->state.assign(c.n_layers, nullptr); px->conv.assign(c.n_layers, nullptr);
+    auto fail = [&](int st) { qb_prefix_release(ctx, px); return st; };
+    for (uint32_t il = 0; il < c.n_layers; ++il) {
+        if (!b->state[il]) continue;
+        // a sequence at a chunk end has its state in slot 0 and its conv window in slot 0 of the valid buffer
+        if (cudaMalloc(&px->state[il], sfl * sizeof(float)) != cudaSuccess || cudaMalloc(&px->conv[il], cfl * sizeof(float)) != cudaSuccess)
+            return fail(qb_fail(QB_ERR_CUDA, "qb_prefix_capture: out of device memory"));
+        const float *cv = b->conv_par ? b->conv_alt[il] : b->conv[il];
+        QB_CUDA(cudaMemcpyAsync(px->state[il], b->state[il] + (size_t)seq * K1 * sfl, sfl * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+        QB_CUDA(cudaMemcpyAsync(px->conv[il], cv + (size_t)seq * K1 * cfl, cfl * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    }
+    QB_CUDA(cudaMalloc(&px->hid, (size_t)c.n_embd * sizeof(float)));
+    QB_CUDA(cudaMemcpyAsync(px->hid, b->hid + (size_t)(b->rows_cap + seq) * c.n_embd, (size_t)c.n_embd * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    if (tokens_host) {
+        QB_CUDA(cudaMalloc(&px->tokens_dev, (size_t)n * sizeof(int32_t)));
+        QB_CUDA(cudaMemcpyAsync(px->tokens_dev, tokens_host, (size_t)n * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        QB_CUDA(cudaStreamSynchronize(ctx->stream));          // the caller's array may go away
+    }
+    for (uint32_t i = 0; i < (uint32_t)n / b->page_size; ++i) {
+        const int32_t pg = b->seq_pages[seq][i];
+        if (!b->pool->share(pg)) return fail(qb_fail(QB_ERR_INVALID, "qb_prefix_capture: page %d of sequence %u is not in use", pg, seq));
+        px->pages.push_back(pg);
+    }
+    *out = px;
+    return QB_OK;
+}
+
+extern "C" int qb_prefix_attach(qb_ctx *ctx, qb_batch *b, uint32_t seq, const qb_prefix *px) {
+    QB_REQUIRE(ctx && b && px && seq < b->n_seqs, "qb_prefix_attach: bad arguments");
+    QB_REQUIRE(px->owner == b, "qb_prefix_attach: the prefix belongs to another batch (its pages are in that batch's pool)");
+    QB_REQUIRE(b->host_pos[seq] == 0 && b->seq_pages[seq].empty(), "qb_prefix_attach: sequence %u is not empty (qb_seq_reset first)", seq);
+    QB_REQUIRE(px->n_tokens < b->max_ctx, "qb_prefix_attach: the prefix fills the context");
+    QB_REQUIRE(!b->seen || px->tokens_dev, "qb_prefix_attach: the batch has token penalties on and the prefix carries no tokens");
+    QB_CUDA(cudaSetDevice(ctx->device));
+    const qb_model_config &c = b->m->cfg;
+    const uint32_t K1 = b->k + 1;
+    const size_t sfl = (size_t)c.ssm_num_v_heads * c.ssm_head_dim * c.ssm_head_dim, cfl = (size_t)b->m->qkv_dim() * 3;
+    for (int32_t pg : px->pages) {
+        QB_REQUIRE(b->pool->share(pg), "qb_prefix_attach: page %d of the prefix is not in use", pg);
+        b->seq_pages[seq].push_back(pg);
+    }
+    QB_TRY(upload_pages(ctx, b, seq, 0, (uint32_t)px->pages.size()));
+    for (uint32_t il = 0; il < c.n_layers; ++il) {
+        if (!b->state[il]) continue;
+        float *cv = b->conv_par ? b->conv_alt[il] : b->conv[il];
+        QB_CUDA(cudaMemcpyAsync(b->state[il] + (size_t)seq * K1 * sfl, px->state[il], sfl * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+        QB_CUDA(cudaMemcpyAsync(cv + (size_t)seq * K1 * cfl, px->conv[il], cfl * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    }
+    QB_CUDA(cudaMemcpyAsync(b->hid + (size_t)(b->rows_cap + seq) * c.n_embd, px->hid, (size_t)c.n_embd * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    QB_CUDA(qb_launch_pdl(ctx->stream, set_seq_ctl_kernel, dim3(1), dim3(32), (size_t)0, b->pos, b->sel, b->cur, seq, (int32_t)px->n_tokens));
+    QB_LAUNCHED(ctx, "set_seq_ctl_kernel");
+    if (b->seen) {
+        QB_CUDA(qb_launch_pdl(ctx->stream, mark_seen_tokens_kernel, dim3((px->n_tokens + 127) / 128), dim3(128), (size_t)0, (const int32_t *)px->tokens_dev,
+                              px->n_tokens, b->seen + (size_t)seq * b->seen_words, c.vocab_size));
+        QB_LAUNCHED(ctx, "mark_seen_tokens_kernel");
+    }
+    b->host_pos[seq] = (int32_t)px->n_tokens;
+    b->chunk_end_pos[seq] = (int32_t)px->n_tokens;
+    probe_cancel(b);
+    return QB_OK;
+}
+extern "C" uint32_t qb_prefix_tokens(const qb_prefix *px) { return px ? px->n_tokens : 0; }
+
 static int prefill_impl(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n, bool more_follows,
                         const qb_sampling *samp) {
     QB_REQUIRE(ctx && b && tokens_host && n > 0 && seq < b->n_seqs, "qb_prefill: bad arguments");
     QB_REQUIRE((uint32_t)b->host_pos[seq] + n <= b->max_ctx, "qb_prefill: %u tokens at position %d exceed max_ctx %u", n, b->host_pos[seq],
                b->max_ctx);
     QB_REQUIRE(!samp || samp->temp > 0.0f, "qb_prefill_sampled: temp must be > 0 (temp <= 0 is the greedy qb_prefill)");
+    if (b->pool) {      // the whole call's pages must be there before its first chunk runs
+        const uint32_t need = std::min(b->pages_per_seq, ((uint32_t)b->host_pos[seq] + n + b->page_size - 1) / b->page_size);
+        const uint32_t have = (uint32_t)b->seq_pages[seq].size();
+        if (need > have && b->pool->free_count() < need - have)
+            return qb_fail(QB_ERR_CAPACITY, "K/V page pool exhausted: sequence %u needs %u more pages, %u of %u free", seq, need - have,
+                           b->pool->free_count(), b->pool->total());
+    }
     QB_CUDA(cudaSetDevice(ctx->device));
     qb_model *m = b->m;
     const qb_model_config &c = m->cfg;
@@ -1067,6 +1276,7 @@ static int prefill_impl(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *t
         const uint32_t M = std::min(b->chunk, n - off);
         const bool last = off + M == n && !more_follows;
         const uint32_t p0 = (uint32_t)b->host_pos[seq];
+        QB_TRY(ensure_pages(ctx, b, seq, p0 + M));
         QB_CUDA(cudaMemcpyAsync(b->tok_buf, b->tok_stage + off, M * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
         if (b->seen) {
             QB_CUDA(qb_launch_pdl(ctx->stream, mark_seen_tokens_kernel, dim3((M + 127) / 128), dim3(128), (size_t)0, b->tok_buf, M,
@@ -1106,6 +1316,7 @@ static int prefill_impl(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *t
         b->host_pos[seq] += (int32_t)M;
         probe_cancel(b);
     }
+    b->chunk_end_pos[seq] = more_follows ? b->host_pos[seq] : -1;
     return QB_OK;
 }
 
@@ -1141,6 +1352,7 @@ extern "C" int qb_decode_greedy_step(qb_ctx *ctx, qb_batch *b) {
     QB_REQUIRE(ctx && b, "qb_decode_greedy_step: null argument");
     QB_TRY(check_room(b, 1));
     QB_CUDA(cudaSetDevice(ctx->device));
+    QB_TRY(ensure_step_pages(ctx, b, 1));
     const qb_model_config &c = b->m->cfg;
     RowSet rs;
     rs.seq0 = 0; rs.ns = b->n_active; rs.R = 1; rs.seq_pos = b->pos; rs.max_pos = max_host_pos(b) + 1;
@@ -1158,6 +1370,7 @@ extern "C" int qb_mtp_draft(qb_ctx *ctx, qb_batch *b) {
     QB_REQUIRE(ctx && b && b->k > 0, "qb_mtp_draft: needs a batch with draft depth > 0");
     QB_TRY(check_room(b, b->k + 1));
     QB_CUDA(cudaSetDevice(ctx->device));
+    QB_TRY(ensure_step_pages(ctx, b, b->k + 1));         // covers the drafts, the verify rows and the MTP prefix rows of the step
     const uint32_t ns = b->n_active, k = b->k;
     for (uint32_t i = 0; i < k; ++i) {
         QB_CUDA(qb_launch_pdl(ctx->stream, prep_draft_kernel, dim3((ns + 127) / 128), dim3(128), (size_t)(0), b->cur, b->drafts, b->pos, ns, k, i, b->tok_buf, b->seqpos_buf));
@@ -1192,6 +1405,7 @@ extern "C" int qb_mtp_verify(qb_ctx *ctx, qb_batch *b) {
     QB_REQUIRE(ctx && b && b->k > 0, "qb_mtp_verify: needs a batch with draft depth > 0");
     QB_TRY(check_room(b, b->k + 1));
     QB_CUDA(cudaSetDevice(ctx->device));
+    QB_TRY(ensure_step_pages(ctx, b, b->k + 1));
     const uint32_t ns = b->n_active, K1 = b->k + 1;
     QB_CUDA(qb_launch_pdl(ctx->stream, prep_verify_kernel, dim3((ns * K1 + 127) / 128), dim3(128), (size_t)(0), b->cur, b->drafts, ns, b->k, b->tok_buf));
     QB_LAUNCHED(ctx, "prep_verify_kernel");
@@ -1358,6 +1572,8 @@ extern "C" int qb_seq_reset(qb_ctx *ctx, qb_batch *b, uint32_t seq) {
     if (b->seen) QB_CUDA(cudaMemsetAsync(b->seen + (size_t)seq * b->seen_words, 0, (size_t)b->seen_words * sizeof(uint32_t), ctx->stream));
     b->host_pos[seq] = 0;
     probe_cancel(b);
+    b->chunk_end_pos[seq] = -1;
+    release_pages(b, seq);                                   // stream order keeps earlier readers of these pages ahead of their next writer
     return QB_OK;
 }
 
@@ -1406,6 +1622,8 @@ extern "C" int qb_seq_swap(qb_ctx *ctx, qb_batch *b, uint32_t s1, uint32_t s2) {
     QB_CUDA(qb_launch_pdl(ctx->stream, swap_ctl_kernel, dim3(1), dim3(32), (size_t)0, b->pos, b->sel, b->cur, b->prefix_pos, b->out_rec, b->limit, b->n_seqs, K1, s1, s2));
     QB_LAUNCHED(ctx, "swap_ctl_kernel");
     std::swap(b->host_pos[s1], b->host_pos[s2]);
+    if (b->pool) std::swap(b->seq_pages[s1], b->seq_pages[s2]);
+    std::swap(b->chunk_end_pos[s1], b->chunk_end_pos[s2]);
     probe_cancel(b);
     return QB_OK;
 }
@@ -1417,6 +1635,8 @@ extern "C" int qb_seq_swap(qb_ctx *ctx, qb_batch *b, uint32_t s1, uint32_t s2) {
 // entries below it are never rewritten.
 struct qb_snapshot {
     std::vector<void *> bufs;
+    QbPagePool::State pool;
+    std::vector<std::vector<int32_t>> seq_pages;
     std::vector<int32_t> host_pos;
     int conv_par = 0;
     uint32_t n_active = 0;
@@ -1460,6 +1680,7 @@ extern "C" int qb_batch_snapshot(qb_ctx *ctx, qb_batch *b, qb_snapshot **out) {
     });
     if (st != QB_OK) { for (void *p : sn->bufs) cudaFree(p); delete sn; return st; }
     sn->host_pos = b->host_pos; sn->conv_par = b->conv_par; sn->n_active = b->n_active; sn->ctl_ints = ctl_count(b);
+    if (b->pool) { sn->pool = b->pool->save(); sn->seq_pages = b->seq_pages; }
     *out = sn;
     return QB_OK;
 }
@@ -1474,6 +1695,7 @@ extern "C" int qb_batch_restore(qb_ctx *ctx, qb_batch *b, const qb_snapshot *sn)
         return QB_OK;
     }));
     b->host_pos = sn->host_pos; b->conv_par = sn->conv_par; b->n_active = sn->n_active;
+    if (b->pool) { b->pool->load(sn->pool); b->seq_pages = sn->seq_pages; }
     probe_cancel(b);
     return QB_OK;
 }

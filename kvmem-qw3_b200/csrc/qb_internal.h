@@ -286,6 +286,7 @@ struct AttnArgs {
     bool kv_only = false;            // prepare: skip the q heads
     bool no_gate = false;            // merge: leave the output ungated (attention_decode + a separate apply_attn_gate)
     uint32_t split_keys = 0;         // keys per split (set by qb_attn_run)
+    int *err_flag = nullptr;         // an append to a page-table entry < 0 is skipped and recorded here (3002)
 };
 int qb_attn_prepare(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t n_seqs);
 // split partials, then merge + gate; out fp32 [rows][n_heads*hd] and/or int8 (q8 [rows][q_pitch], d [.][d_ld]).
