@@ -90,27 +90,33 @@ __global__ void qk_norm_rope_append_kernel(AttnArgs a, const int32_t *__restrict
 }
 
 // ---- split attention ---------------------------------------------------------------------------
-// One CTA = one split (QB_ATTN_SPLIT keys = 4 tiles of 64) of one KV head for up to 32 queries (<= 4 rows x
-// GQA group).  Tensor-core math on fp16 operands with fp32 accumulation (mma.sync m16n8k16; the kernel streams
-// the cache once and is bound by HBM, not by the tensor pipe): S = Q K^T with Q (scaled, fp16) held in
-// registers as A fragments, P = exp(S - m) written to shared memory as fp16, O += P V with V read through
-// ldmatrix.trans.  Warp w = (h, j), j < JW (8 for head dims 128 / 256, 4 for 64): query rows [16h, 16h+16), keys
-// [j*64/JW, (j+1)*64/JW) of the tile for S and output dims [j*HD/JW, (j+1)*HD/JW) for O.  The running maximum of a
-// row is shared by the JW warps that hold it (one exchange per tile through shared memory); each warp keeps its
-// own partial row sum, added in warp order at the end.  K/V tiles arrive through a 3-stage cp.async pipeline (zero-filled past the last key).
-template <int HD>
+// One CTA = a run of splits (QB_ATTN_SPLIT keys = 4 tiles of 64 each) of one KV head for up to 16 * MT queries (query rows
+// x GQA group).  Tensor-core math on fp16 operands with fp32 accumulation (mma.sync m16n8k16; the kernel streams
+// the cache once and is bound by HBM, not by the tensor pipe): S = Q K^T with Q (scaled, fp16) as A fragments,
+// P = exp(S - m) written to shared memory as fp16, O += P V with V read through ldmatrix.trans.  Warp w = (h, j),
+// h < MT, j < JW: query rows [16h, 16h+16), keys [j*64/JW, (j+1)*64/JW) of the tile for S and output dims
+// [j*HD/JW, (j+1)*HD/JW) for O.  The running maximum of a row is shared by the JW warps that hold it (one exchange
+// per tile through shared memory); row sums are kept per group of 8 keys and added in key order at the end.
+// Two shapes of the same arithmetic: MT = 2 for decode and verify rows (<= 4 rows x GQA group: 8 key slices per
+// tile, Q fragments in registers, 3 K/V stages) and MT = 4 for prompt chunks (64 queries per CTA, so a chunk reads
+// its K/V a quarter as often; 2 stages).  A query row gets the same bits from either: the same MMA chains per
+// output element (even and odd 16-deep steps of Q K^T in two accumulators, then added), the same 8-key groups of
+// row sums in the same order, the same tile and split order.
+constexpr uint32_t QB_ATTN_RUN_PAGES = 128;                  // pages a CTA's run of splits may touch (first slot of each kept in shared memory)
+template <int HD, int MT>
 struct AttSmem {
+    static constexpr int NQ = 16 * MT;                      // queries per CTA
     static constexpr int ROWB = HD * 2 + 16;                // bytes per key / query row (padded: conflict-free ldmatrix)
     static constexpr int KV_TILE = TK * ROWB;
     static constexpr int STAGE = 2 * KV_TILE;               // K then V
-    static constexpr int NSTAGE = 3;
+    static constexpr int NSTAGE = MT > 2 ? 2 : 3;
     static constexpr int Q_OFF = NSTAGE * STAGE;
-    static constexpr int Q_BYTES = 32 * ROWB;
+    static constexpr int Q_BYTES = NQ * ROWB;
     static constexpr int P_ROWB = TK * 2 + 16;
     static constexpr int P_OFF = Q_OFF + Q_BYTES;
-    static constexpr int P_BYTES = 32 * P_ROWB;
-    static constexpr int RED_OFF = P_OFF + P_BYTES;         // float [up to 8 warps j][32 rows]
-    static constexpr int TOTAL = RED_OFF + 8 * 32 * 4;
+    static constexpr int P_BYTES = NQ * P_ROWB;
+    static constexpr int RED_OFF = P_OFF + P_BYTES;         // float [8 key groups][NQ rows]
+    static constexpr int TOTAL = RED_OFF + 8 * NQ * 4;
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -127,55 +133,63 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], u
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// grid (max_splits, n_kv, n_seqs * ceil(R/QR)).
-template <int HD, int JW>
-__global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const int32_t *__restrict__ seq_pos, uint32_t R,
-                                                                 uint32_t max_splits) {
+// grid (ceil(max_splits / spc), n_kv, n_seqs * ceil(R / qr)), qr = query rows per CTA.  A CTA walks a run of `spc`
+// consecutive splits of its KV head: the K/V tiles of the whole run go through one continuous load pipeline and the
+// queries are staged once, but every split still gets its own (max, sum, accumulator) triple written to its own partial
+// slot, so the result does not depend on spc (the launcher picks it from the grid size alone: about one wave of CTAs at
+// long contexts).
+template <int HD, int JW, int MT>
+__global__ void __launch_bounds__(32 * JW * MT) attn_split_kernel(AttnArgs a, const int32_t *__restrict__ seq_pos, uint32_t R,
+                                                                      uint32_t max_splits, uint32_t spc, uint32_t qr) {
     QB_PDL_ENTER();
-    using L = AttSmem<HD>;
-    constexpr int THREADS = 64 * JW, WARPS = 2 * JW;             // JW warps share a 16-query m-tile
+    using L = AttSmem<HD, MT>;
+    constexpr int THREADS = 32 * JW * MT, WARPS = JW * MT;       // JW warps share a 16-query m-tile
+    constexpr int NQM = L::NQ;
     constexpr int KW = TK / JW, NTS = KW / 8;                    // keys (8-key n-tiles) of a tile per warp
     constexpr int DW = HD / JW;                                  // output dims per warp
+    constexpr bool QREG = MT <= 2;                               // Q fragments live in registers (else re-read per step)
+    constexpr int D = L::NSTAGE - 1;                             // tiles in flight ahead of the one being used
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     float *red = reinterpret_cast<float *>(smem + L::RED_OFF);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t h = warp & 1, j = warp >> 1;                  // query m-tile, key / output-dim slice
+    const uint32_t h = warp % MT, j = warp / MT;                 // query m-tile, key / output-dim slice
     const uint32_t g4 = lane >> 2, t4 = lane & 3;                // accumulator row / column pair of this lane
-    const uint32_t split = blockIdx.x, kvh = blockIdx.y;
-    const uint32_t chunks = (R + QR - 1) / QR;
+    const uint32_t split0 = blockIdx.x * spc, kvh = blockIdx.y;  // first split of this CTA's run
+    const uint32_t chunks = (R + qr - 1) / qr;
     const uint32_t seq = blockIdx.z / chunks, chunk = blockIdx.z % chunks;
-    const uint32_t r_begin = chunk * QR, r_count = min((uint32_t)QR, R - r_begin);
+    const uint32_t r_begin = chunk * qr, r_count = min(qr, R - r_begin);
     const uint32_t G = a.n_heads / a.n_kv;
     const uint32_t NQ = r_count * G;
     const int base_pos = seq_pos[seq] + (int)r_begin;            // position of the chunk's first row
     const int last_key = base_pos + (int)r_count - 1;            // highest key index any row here sees
-    const int k_begin = (int)(split * a.split_keys);
+    const int k_begin = (int)(split0 * a.split_keys);
     if (k_begin > last_key) return;
-    const int k_end = min(k_begin + (int)a.split_keys, last_key + 1);
+    const int k_end = min(k_begin + (int)(spc * a.split_keys), last_key + 1);
     const int n_tiles = (k_end - k_begin + TK - 1) / TK;
+    const int tps = (int)a.split_keys / TK;                      // tiles per split
     const float scale = rsqrtf((float)HD);
     const int32_t *pt = a.page_table + (size_t)seq * a.pt_stride;
     const bool active = h * 16 < NQ;                             // this warp's query rows exist
 
-    // a thread copies one 16-byte column of every (256 / CH)-th key row: one page-table lookup per row, no
+    // a thread copies one 16-byte column of every (THREADS / CH)-th key row: one page-table lookup per row, no
     // division when the page size is a power of two
     const uint32_t psz = a.page_size;
     const bool pow2 = (psz & (psz - 1)) == 0;
     const int psh = __ffs((int)psz) - 1;
-    // first slot of every page the split touches, looked up once (the tile loop then reads shared memory only)
-    __shared__ int page_slot[64];
+    // first slot of every page the run touches, looked up once (the tile loop then reads shared memory only)
+    __shared__ int page_slot[QB_ATTN_RUN_PAGES];
     {
         const uint32_t pg0 = pow2 ? (uint32_t)k_begin >> psh : (uint32_t)k_begin / psz;
         const uint32_t pg1 = pow2 ? (uint32_t)(k_end - 1) >> psh : (uint32_t)(k_end - 1) / psz;
-        for (uint32_t i = tid; i <= pg1 - pg0 && i < 64; i += THREADS) page_slot[i] = pt[pg0 + i] * (int)psz;
+        for (uint32_t i = tid; i <= pg1 - pg0 && i < QB_ATTN_RUN_PAGES; i += THREADS) page_slot[i] = pt[pg0 + i] * (int)psz;
         __syncthreads();
     }
     const uint32_t pg_first = pow2 ? (uint32_t)k_begin >> psh : (uint32_t)k_begin / psz;
     auto load_tile = [&](int tile, int slot) {
         uint8_t *ks = smem + slot * L::STAGE, *vs = ks + L::KV_TILE;
         constexpr int CH = HD * 2 / 16;                          // 16-byte chunks per key row
-        constexpr int RPP = THREADS / CH;                    // rows per pass
+        constexpr int RPP = THREADS / CH;                        // rows per pass
         const int p = tid % CH;
 #pragma unroll
         for (int t = tid / CH; t < TK; t += RPP) {
@@ -191,13 +205,14 @@ __global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const i
             cp_async16(vs + t * L::ROWB + p * 16, a.v_cache + off + p * 8, valid);
         }
     };
-    load_tile(0, 0);
-    cp_async_commit();
-    if (n_tiles > 1) load_tile(1, 1);
-    cp_async_commit();
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+        if (d < n_tiles) load_tile(d, d);
+        cp_async_commit();
+    }
 
     // stage the queries (scaled, fp16): query index qi = r_local * G + g, head = kvh*G + g; missing rows are zero
-    for (uint32_t qi = warp; qi < 32; qi += WARPS) {
+    for (uint32_t qi = warp; qi < (uint32_t)NQM; qi += WARPS) {
         const uint32_t rl = qi / G, gq = qi - rl * G;
         const float *src = a.qkv + ((size_t)seq * R + r_begin + rl) * a.row_stride + (size_t)(kvh * G + gq) * 2 * HD;
 #pragma unroll
@@ -211,16 +226,25 @@ __global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const i
         }
     }
     __syncthreads();
-    uint32_t qf[HD / 16][4];
+    const uint32_t qaddr = smem_base + L::Q_OFF + (h * 16 + (lane & 15)) * L::ROWB + ((lane >> 4) * 8) * 2;
+    uint32_t qf[QREG ? HD / 16 : 1][4];
+    if constexpr (QREG) {
 #pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks)
-        ldsm_x4(qf[ks], smem_base + L::Q_OFF + (h * 16 + (lane & 15)) * L::ROWB + (ks * 16 + (lane >> 4) * 8) * 2);
+        for (int ks = 0; ks < HD / 16; ++ks) ldsm_x4(qf[ks], qaddr + ks * 32);
+    }
+    auto q_frag = [&](int ks, uint32_t (&q)[4]) {
+        if constexpr (QREG) { q[0] = qf[ks][0]; q[1] = qf[ks][1]; q[2] = qf[ks][2]; q[3] = qf[ks][3]; }
+        else ldsm_x4(q, qaddr + ks * 32);
+    };
 
     constexpr int NT_O = DW / 8;                                 // 8-wide output tiles per warp
     float o[NT_O][4];
 #pragma unroll
     for (int n = 0; n < NT_O; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};   // rows g4 and g4 + 8 of the m-tile
+    float m_run[2] = {-INFINITY, -INFINITY};                     // rows g4 and g4 + 8 of the m-tile
+    float l_run[2][NTS];                                         // row sums per 8-key group of this warp
+#pragma unroll
+    for (int nt = 0; nt < NTS; ++nt) l_run[0][nt] = l_run[1][nt] = 0.0f;
     // positions of this lane's two query rows (rows past NQ get -1: everything masked)
     int qpos[2];
 #pragma unroll
@@ -230,37 +254,58 @@ __global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const i
     }
 
     for (int tile = 0; tile < n_tiles; ++tile) {
-        cp_async_wait<1>();
+        cp_async_wait<D - 1>();
         __syncthreads();                                         // tile landed; everyone is done with tile - 1
-        if (tile + 2 < n_tiles) load_tile(tile + 2, (tile + 2) % L::NSTAGE);
+        if (tile + D < n_tiles) load_tile(tile + D, (tile + D) % L::NSTAGE);
         cp_async_commit();
+        if (tile % tps == 0 && tile > 0) {                       // a new split of the run: fresh running state
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+            m_run[0] = m_run[1] = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < NTS; ++nt) l_run[0][nt] = l_run[1][nt] = 0.0f;
+        }
         const uint32_t ks_base = smem_base + (tile % L::NSTAGE) * L::STAGE, vs_base = ks_base + L::KV_TILE;
         const int key0 = k_begin + tile * TK + (int)j * KW;     // first key of this warp's KW
 
-        // S = Q K^T for 16 queries x KW keys
+        // S = Q K^T for 16 queries x KW keys: even and odd 16-deep steps in two accumulators (half the dependent
+        // chain), added at the end -- the same two chains in every shape of the kernel
         float sc[NTS][4];
 #pragma unroll
         for (int nt = 0; nt < NTS; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.0f; }
         if (active) {
-            if constexpr (NTS == 2) {
-                const uint32_t kaddr = ks_base + (j * KW + (lane & 7) + ((lane >> 4) << 3)) * L::ROWB + (((lane >> 3) & 1) * 8) * 2;
+            if constexpr (NTS >= 2) {
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    uint32_t b[4];
-                    ldsm_x4(b, kaddr + ks * 32);
-                    mma_f16(sc[0], qf[ks], b[0], b[1]);
-                    mma_f16(sc[1], qf[ks], b[2], b[3]);
+                for (int np = 0; np < NTS / 2; ++np) {
+                    float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                    const uint32_t kaddr = ks_base + (j * KW + np * 16 + (lane & 7) + ((lane >> 4) << 3)) * L::ROWB + (((lane >> 3) & 1) * 8) * 2;
+#pragma unroll
+                    for (int ks = 0; ks < HD / 16; ks += 2) {
+                        uint32_t b[4], q[4];
+                        q_frag(ks, q);
+                        ldsm_x4(b, kaddr + ks * 32);
+                        mma_f16(sc[2 * np], q, b[0], b[1]);
+                        mma_f16(sc[2 * np + 1], q, b[2], b[3]);
+                        q_frag(ks + 1, q);
+                        ldsm_x4(b, kaddr + (ks + 1) * 32);
+                        mma_f16(s2[0], q, b[0], b[1]);
+                        mma_f16(s2[1], q, b[2], b[3]);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) { sc[2 * np][c] += s2[0][c]; sc[2 * np + 1][c] += s2[1][c]; }
                 }
             } else {
                 // one 8-key n-tile: an x4 load covers two k-steps (d 0-7, 8-15, 16-23, 24-31)
                 const uint32_t kaddr = ks_base + (j * KW + (lane & 7)) * L::ROWB + ((lane >> 3) * 8) * 2;
+                float s2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                float s2[4] = {0.f, 0.f, 0.f, 0.f};               // second accumulator: halves the dependent chain
                 for (int ks = 0; ks < HD / 16; ks += 2) {
-                    uint32_t b[4];
+                    uint32_t b[4], q[4];
                     ldsm_x4(b, kaddr + ks * 32);
-                    mma_f16(sc[0], qf[ks], b[0], b[1]);
-                    mma_f16(s2, qf[ks + 1], b[2], b[3]);
+                    q_frag(ks, q);
+                    mma_f16(sc[0], q, b[0], b[1]);
+                    q_frag(ks + 1, q);
+                    mma_f16(s2, q, b[2], b[3]);
                 }
 #pragma unroll
                 for (int c = 0; c < 4; ++c) sc[0][c] += s2[c];
@@ -280,7 +325,7 @@ __global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const i
         for (int e = 0; e < 2; ++e) {
             mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 1));
             mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 2));
-            if (t4 == 0) red[j * 32 + h * 16 + g4 + 8 * e] = mx[e];
+            if (t4 == 0) red[j * NQM + h * 16 + g4 + 8 * e] = mx[e];
         }
         __syncthreads();
         float corr[2];
@@ -290,10 +335,10 @@ __global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const i
             const uint32_t r = h * 16 + g4 + 8 * e;
             float m_tile = red[r];
 #pragma unroll
-            for (int w = 1; w < JW; ++w) m_tile = fmaxf(m_tile, red[w * 32 + r]);
+            for (int w = 1; w < JW; ++w) m_tile = fmaxf(m_tile, red[w * NQM + r]);
             const float m_new = fmaxf(m_run[e], m_tile);
             corr[e] = 1.0f;
-            float psum = 0.0f;
+            if (m_new != -INFINITY) corr[e] = __expf(m_run[e] - m_new);
 #pragma unroll
             for (int nt = 0; nt < NTS; ++nt) {
                 float p0 = 0.0f, p1 = 0.0f;
@@ -301,11 +346,9 @@ __global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const i
                 const __half2 hp = __floats2half2_rn(p0, p1);
                 // the row sum uses the rounded probabilities, the values the tensor cores multiply with V
                 const float2 fp = __half22float2(hp);
-                psum += fp.x + fp.y;
+                l_run[e][nt] = l_run[e][nt] * corr[e] + (0.0f + (fp.x + fp.y));
                 pk[nt][e] = *reinterpret_cast<const uint32_t *>(&hp);
             }
-            if (m_new != -INFINITY) corr[e] = __expf(m_run[e] - m_new);
-            l_run[e] = l_run[e] * corr[e] + psum;
             m_run[e] = m_new;
         }
 #pragma unroll
@@ -332,36 +375,40 @@ __global__ void __launch_bounds__(64 * JW) attn_split_kernel(AttnArgs a, const i
                 }
             }
         }
-    }
-    cp_async_wait<0>();
-    // row sums: quad first, then the four warps of a row in order
-    __syncthreads();
+        if (tile % tps != tps - 1 && tile != n_tiles - 1) continue;
+        // the split is complete: row sums (quad first, then the 8-key groups of a row in key order) and its partial
+        const uint32_t split = split0 + (uint32_t)(tile / tps);
+        __syncthreads();
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-        float l = l_run[e];
-        l += __shfl_xor_sync(0xffffffffu, l, 1);
-        l += __shfl_xor_sync(0xffffffffu, l, 2);
-        if (t4 == 0) red[j * 32 + h * 16 + g4 + 8 * e] = l;
-    }
-    __syncthreads();
+        for (int e = 0; e < 2; ++e)
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-        const uint32_t qi = h * 16 + g4 + 8 * e;
-        if (qi >= NQ) continue;
-        const size_t row = (size_t)seq * R + r_begin + qi / G;
-        const uint32_t head = kvh * G + qi % G;
-        const size_t pidx = (row * a.n_heads + head) * max_splits + split;
-        float *dst = a.part_acc + pidx * HD + j * DW + t4 * 2;
+            for (int nt = 0; nt < NTS; ++nt) {
+                float l = l_run[e][nt];
+                l += __shfl_xor_sync(0xffffffffu, l, 1);
+                l += __shfl_xor_sync(0xffffffffu, l, 2);
+                if (t4 == 0) red[(j * NTS + nt) * NQM + h * 16 + g4 + 8 * e] = l;
+            }
+        __syncthreads();
 #pragma unroll
-        for (int n = 0; n < NT_O; ++n) *reinterpret_cast<float2 *>(dst + n * 8) = make_float2(o[n][2 * e], o[n][2 * e + 1]);
-        if (j == 0 && t4 == 0) {
-            a.part_ml[pidx * 2] = m_run[e];
-            float l = red[qi];
+        for (int e = 0; e < 2; ++e) {
+            const uint32_t qi = h * 16 + g4 + 8 * e;
+            if (qi >= NQ) continue;
+            const size_t row = (size_t)seq * R + r_begin + qi / G;
+            const uint32_t head = kvh * G + qi % G;
+            const size_t pidx = (row * a.n_heads + head) * max_splits + split;
+            float *dst = a.part_acc + pidx * HD + j * DW + t4 * 2;
 #pragma unroll
-            for (int w = 1; w < JW; ++w) l += red[w * 32 + qi];
-            a.part_ml[pidx * 2 + 1] = l;
+            for (int n = 0; n < NT_O; ++n) *reinterpret_cast<float2 *>(dst + n * 8) = make_float2(o[n][2 * e], o[n][2 * e + 1]);
+            if (j == 0 && t4 == 0) {
+                a.part_ml[pidx * 2] = m_run[e];
+                float l = red[qi];
+#pragma unroll
+                for (int w = 1; w < TK / 8; ++w) l += red[w * NQM + qi];
+                a.part_ml[pidx * 2 + 1] = l;
+            }
         }
     }
+    cp_async_wait<0>();
 }
 
 // Merge split partials in ascending order, apply the sigmoid gate, write fp32 and/or int8.
@@ -420,13 +467,21 @@ __global__ void attn_merge_kernel(AttnArgs a, const int32_t *__restrict__ seq_po
     }
 }
 
-template <int HD, int JW>
+template <int HD, int JW, int MT>
 int launch_split(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t R, uint32_t n_seqs, uint32_t max_splits) {
-    using L = AttSmem<HD>;
+    using L = AttSmem<HD, MT>;
     // the attribute belongs to the current device: set on every launch (a process may drive several GPUs)
-    QB_CUDA(cudaFuncSetAttribute((attn_split_kernel<HD, JW>), cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    dim3 grid(max_splits, a.n_kv, n_seqs * ((R + QR - 1) / QR));
-    QB_CUDA(qb_launch_pdl(ctx->stream, (attn_split_kernel<HD, JW>), dim3(grid), dim3(64 * JW), (size_t)(L::TOTAL), a, seq_pos, R, max_splits));
+    QB_CUDA(cudaFuncSetAttribute((attn_split_kernel<HD, JW, MT>), cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    const uint32_t G = a.n_heads / a.n_kv;
+    const uint32_t qr = std::max(1u, (uint32_t)L::NQ / G);          // query rows per CTA
+    // splits per CTA: 1 while the grid fits one wave of CTAs (one per SM), else as many as bring it back to about one
+    // wave, at most what the per-CTA page list holds
+    const uint32_t zdim = n_seqs * ((R + qr - 1) / qr);
+    const uint32_t cap = std::max(1u, std::min(8u, QB_ATTN_RUN_PAGES / std::max(1u, a.split_keys / a.page_size)));
+    const uint32_t ctas = max_splits * a.n_kv * zdim;
+    const uint32_t spc = std::min(cap, std::max(1u, (ctas + (uint32_t)ctx->sm_count - 1) / (uint32_t)ctx->sm_count));
+    dim3 grid((max_splits + spc - 1) / spc, a.n_kv, zdim);
+    QB_CUDA(qb_launch_pdl(ctx->stream, (attn_split_kernel<HD, JW, MT>), dim3(grid), dim3(32 * JW * MT), (size_t)(L::TOTAL), a, seq_pos, R, max_splits, spc, qr));
     QB_LAUNCHED(ctx, "attn_split_kernel");
     return QB_OK;
 }
@@ -471,12 +526,14 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
     const uint32_t ms = max_splits_for(a.max_pos);
     AttnArgs aa = a;
     aa.split_keys = split_keys();
-    QB_REQUIRE(aa.split_keys / a.page_size <= 64, "attention: a split of %u keys spans more than 64 pages of %u", aa.split_keys, a.page_size);
+    QB_REQUIRE(aa.split_keys / a.page_size <= QB_ATTN_RUN_PAGES, "attention: a split of %u keys spans more than %u pages of %u", aa.split_keys, QB_ATTN_RUN_PAGES, a.page_size);
     QB_REQUIRE(((uintptr_t)a.qkv & 7) == 0 && a.row_stride % 2 == 0, "attention: q rows must be 8-byte aligned");
     int st = QB_OK;
-    if (a.hd == 256) st = launch_split<256, 8>(ctx, aa, seq_pos, R, n_seqs, ms);
-    else if (a.hd == 128) st = launch_split<128, 8>(ctx, aa, seq_pos, R, n_seqs, ms);
-    else if (a.hd == 64) st = launch_split<64, 4>(ctx, aa, seq_pos, R, n_seqs, ms);
+    // prompt chunks (many rows per sequence) take the 64-query shape: a quarter of the passes over the cache
+    const bool wide = R * G > 64;
+    if (a.hd == 256) st = wide ? launch_split<256, 4, 4>(ctx, aa, seq_pos, R, n_seqs, ms) : launch_split<256, 8, 2>(ctx, aa, seq_pos, R, n_seqs, ms);
+    else if (a.hd == 128) st = wide ? launch_split<128, 4, 4>(ctx, aa, seq_pos, R, n_seqs, ms) : launch_split<128, 8, 2>(ctx, aa, seq_pos, R, n_seqs, ms);
+    else if (a.hd == 64) st = wide ? launch_split<64, 4, 4>(ctx, aa, seq_pos, R, n_seqs, ms) : launch_split<64, 4, 2>(ctx, aa, seq_pos, R, n_seqs, ms);
     else return qb_fail(QB_ERR_UNSUPPORTED, "attention: head_dim %u unsupported", a.hd);
     QB_TRY(st);
     dim3 grid(a.rows, a.n_heads);

@@ -107,6 +107,49 @@ def test_attention_single_row_and_tiny_heads(qb, orc, ctx):
     _attn_case(qb, orc, ctx, 16, 2, 128, 32, 16, [257], 5, "identity", seed=34)     # GQA 8, 5 rows (k=4)
 
 
+@pytest.mark.parametrize("n_heads,n_kv,hd,base,R", [(24, 4, 256, 700, 45), (4, 2, 64, 130, 70), (16, 2, 128, 0, 33)])
+def test_attention_prompt_chunk_shape_has_the_bits_of_the_verify_shape(qb, orc, ctx, n_heads, n_kv, hd, base, R):
+    """A prompt chunk (many rows of one sequence) runs the 64-query shape of the attention kernel, decode and verify
+    rows the 32-query shape; a row must get the same bits from either, or a request's tokens would depend on how its
+    prompt was cut into chunks.  The chunk's rows are recomputed four at a time and compared bit for bit; the chunk
+    itself is checked against the oracle by _attn_case."""
+    _attn_case(qb, orc, ctx, n_heads, n_kv, hd, 16 if hd == 64 else 64, 16, [base], R, "shuffle", seed=70 + R)
+    rng = np.random.default_rng(90 + R)
+    page_size, rope_dim = 16, 16 if hd == 64 else 64
+    max_pos = base + R
+    pps = (max_pos + page_size) // page_size + 1
+    pt = rng.permutation(pps).astype(np.int32).reshape(1, pps)
+    kvd = n_kv * hd
+    stride = n_heads * 2 * hd + 2 * kvd
+    kc = np.zeros((pps * page_size, kvd), np.uint16)
+    vc = np.zeros_like(kc)
+    invf = orc.inv_freq(rope_dim, 1e7)
+    qw = rng.uniform(0.5, 1.5, hd).astype(np.float32)
+    kw = rng.uniform(0.5, 1.5, hd).astype(np.float32)
+    if base:
+        hist = rng.standard_normal((base, stride)).astype(np.float32)
+        orc.qk_norm_rope_append(hist, qw, kw, invf, n_heads, n_kv, hd, rope_dim, 1e-6, np.zeros(base, np.int32),
+                                np.arange(base, dtype=np.int32), pt, page_size, kc, vc)
+    qkv = rng.standard_normal((R, stride)).astype(np.float32)
+    d_qkv, d_kc, d_vc, d_pt = ctx.array(qkv), ctx.array(kc), ctx.array(vc), ctx.array(pt)
+    L = qb.lib()
+    qb.binding.check(L.qb_qk_norm_rope_append(ctx.h, d_qkv.ptr, R, stride, ctx.array(qw).ptr, ctx.array(kw).ptr, ctx.array(invf).ptr,
+                                              n_heads, n_kv, hd, rope_dim, 1e-6, ctx.array(np.array([base], np.int32)).ptr, 1,
+                                              d_pt.ptr, pps, page_size, d_kc.ptr, d_vc.ptr))
+    wide = ctx.empty((R, n_heads * hd), np.float32)
+    qb.binding.check(L.qb_attention_paged_gated(ctx.h, d_qkv.ptr, R, stride, n_heads, n_kv, hd, ctx.array(np.array([base], np.int32)).ptr, 1,
+                                                d_pt.ptr, pps, page_size, d_kc.ptr, d_vc.ptr, max_pos, wide.ptr))
+    want = wide.download()
+    normed = d_qkv.download()
+    for r0 in range(0, R, 4):
+        n = min(4, R - r0)
+        part = ctx.array(np.ascontiguousarray(normed[r0:r0 + n]))
+        out = ctx.empty((n, n_heads * hd), np.float32)
+        qb.binding.check(L.qb_attention_paged_gated(ctx.h, part.ptr, n, stride, n_heads, n_kv, hd, ctx.array(np.array([base + r0], np.int32)).ptr, 1,
+                                                    d_pt.ptr, pps, page_size, d_kc.ptr, d_vc.ptr, max_pos, out.ptr))
+        assert np.array_equal(out.download(), want[r0:r0 + n]), r0
+
+
 def _dn_inputs(rng, nk, nv, hd, n_seqs, R, n_slots):
     C_ = (2 * nk + nv) * hd
     stride = C_ + nv * hd + 2 * nv + 3    # a padded row stride
