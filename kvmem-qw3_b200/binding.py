@@ -506,6 +506,7 @@ class Batch:
         """pool_pages > 0: the pooled form (one K/V page pool shared by the sequences, pages handed out as positions grow)."""
         self.ctx, self.model, self.n_seqs, self.k, self.max_ctx = model.ctx, model, n_seqs, k, max_ctx
         self.n_active = n_seqs
+        self.page_size, self.pool_pages = page_size, pool_pages
         h = vp()
         if pool_pages:
             check(lib().qb_batch_create_pooled(self.ctx.h, model.h, n_seqs, max_ctx, k, page_size, pool_pages, C.byref(h)))

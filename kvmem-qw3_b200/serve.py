@@ -112,9 +112,18 @@ def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=
     draws = {}                                           # rid -> DrawQueue
     finished, step = [], 0
     engine.set_active(0)
+    # an engine with one K/V page pool for all slots (binding.Batch(pool_pages=...)): a request is admitted only when the
+    # pages of its whole life (prompt + budget + one step's rows) fit beside those promised to the requests already in,
+    # so a decode step never finds the pool empty; requests wait in arrival order
+    pool_pages = getattr(engine, "pool_pages", 0)
+    reserved = {}                                        # rid -> pages promised
+
+    def pages_of(req):
+        return -(-(len(req.prompt) + req.max_new_tokens + per_step) // engine.page_size)
 
     def retire(s):
         req = live[s]
+        reserved.pop(req.rid, None)
         req.finished_step = step
         req._trim()
         finished.append(req)
@@ -129,9 +138,16 @@ def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=
     while (pending or live or ingest) and step < max_steps:
         # admission: a free slot beyond the live range per arrived request
         while pending and pending[0].arrival_step <= step and len(live) + len(ingest) < engine.n_seqs:
-            req = pending.popleft()
+            req = pending[0]
             if len(req.prompt) + req.max_new_tokens + per_step > engine.max_ctx:
                 raise ValueError("request %r does not fit max_ctx %d" % (req.rid, engine.max_ctx))
+            if pool_pages:
+                if pages_of(req) > pool_pages:
+                    raise ValueError("request %r needs %d pages, the pool has %d" % (req.rid, pages_of(req), pool_pages))
+                if sum(reserved.values()) + pages_of(req) > pool_pages:
+                    break                                          # waits for a retirement
+                reserved[req.rid] = pages_of(req)
+            pending.popleft()
             slot = next(s for s in range(len(live), engine.n_seqs) if s not in ingest)
             engine.reset(slot)
             req.slot, req.admitted_step = slot, step

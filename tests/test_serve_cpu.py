@@ -262,3 +262,46 @@ def test_compacting_loop_sampled_draws_follow_the_request_through_swaps():
         heads = eng.first[(i + 1,)]
         assert eng.first_draws[(i + 1,)] == 1000 * i + 1        # the request's first draw picked its first token
         assert heads[0] == 1000 * i + 2 and all(b > a for a, b in zip(heads, heads[1:])) and all(1000 * i < h < 1000 * (i + 1) for h in heads)
+
+
+def test_pooled_engine_admits_only_what_its_page_pool_can_hold():
+    """With one page pool for all slots a request is admitted when the pages of its whole life fit beside those promised to
+    the requests already in; the others wait in arrival order, and everybody still gets the stream they get alone."""
+    serve = entry.load_package().serve
+
+    class Pooled(CompactEngine):
+        page_size, pool_pages = 16, 6
+
+        def __init__(self, *a):
+            super().__init__(*a)
+            self.held = [0] * self.n_seqs
+            self.peak = 0
+
+        def _pages(self, s):
+            return -(-(self.pos[s] + self.k + 1) // self.page_size) if self.prompt[s] is not None else 0
+
+        def _account(self):
+            used = sum(self._pages(s) for s in range(self.n_seqs))
+            assert used <= self.pool_pages, "the loop let the pool run dry"
+            self.peak = max(self.peak, used)
+
+        def prefill(self, s, tokens, more=False):
+            super().prefill(s, tokens, more)
+            self._account()
+
+        def _step(self, width):
+            super()._step(width)
+            self._account()
+
+    eng = Pooled(4, 3, 256)
+    # lives of 3, 3, 2 and 4 pages: the third waits for a retirement although a slot is free, the fourth for two
+    spec = [(20, 20), (30, 10), (10, 14), (40, 16)]
+    reqs = [serve.Request(i, list(range(i, i + n)), new) for i, (n, new) in enumerate(spec)]
+    done = serve.run_compact(eng, reqs)
+    assert sorted(r.rid for r in done) == [0, 1, 2, 3]
+    for r in done:
+        assert r.tokens == stream(r.prompt, r.max_new_tokens), r.rid
+    assert reqs[2].admitted_step > 0 and reqs[3].admitted_step >= reqs[2].admitted_step
+    assert eng.peak <= 6
+    with _pytest.raises(ValueError, match="pages"):
+        serve.run_compact(Pooled(4, 3, 256), [serve.Request(9, list(range(100)), 20)])
