@@ -418,6 +418,8 @@ struct qb_batch {
     qb_tp_group *tp = nullptr;             // tensor-parallel FFN group of the batch's model shard, or null
     float *normed = nullptr, *tp_y = nullptr;   // [rows_cap][H]: fp32 FFN input / all-reduced FFN output of the tensor-parallel form
     int32_t *tok_stage = nullptr;          // pinned staging of the prompt tokens being ingested
+    int32_t *tok_all = nullptr;            // the same on the device: one copy per call, the chunks index into it
+    cudaEvent_t tok_ev = nullptr;          // that copy has landed (the staging area may be rewritten)
     uint32_t tok_stage_cap = 0;
     double *first_draw_stage = nullptr;    // pinned: the first-token draw of a sampled request per sequence
     int32_t *limit = nullptr;              // [n_seqs] device: draft depth of the next step per sequence (<= k)
@@ -609,6 +611,8 @@ extern "C" void qb_batch_destroy(qb_ctx *ctx, qb_batch *b) {
     if (b->out_rec_host) cudaFreeHost(b->out_rec_host);
     if (b->limit_host) cudaFreeHost(b->limit_host);
     if (b->tok_stage) cudaFreeHost(b->tok_stage);
+    if (b->tok_all) cudaFree(b->tok_all);
+    if (b->tok_ev) cudaEventDestroy(b->tok_ev);
     if (b->first_draw_stage) cudaFreeHost(b->first_draw_stage);
     if (b->samp_stage) cudaFreeHost(b->samp_stage);
     for (cudaEvent_t e : b->samp_ev) if (e) cudaEventDestroy(e);
@@ -1263,29 +1267,36 @@ static int prefill_impl(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *t
     qb_model *m = b->m;
     const qb_model_config &c = m->cfg;
     const uint32_t K1 = b->k + 1;
-    // pinned staging for the chunk's tokens: the copies are asynchronous and the caller's array may go away
+    // the call's tokens go to the device in one asynchronous copy through pinned staging (the caller's array may go away);
+    // a later call waits for nothing but that copy of the call before it, which lies ahead of that call's kernels
+    if (!b->tok_ev) QB_CUDA(cudaEventCreateWithFlags(&b->tok_ev, cudaEventDisableTiming));
     if (b->tok_stage_cap < n) {
-        if (b->tok_stage) { QB_CUDA(cudaStreamSynchronize(ctx->stream)); QB_CUDA(cudaFreeHost(b->tok_stage)); b->tok_stage = nullptr; }
+        QB_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (b->tok_stage) { QB_CUDA(cudaFreeHost(b->tok_stage)); b->tok_stage = nullptr; }
+        if (b->tok_all) { QB_CUDA(cudaFree(b->tok_all)); b->tok_all = nullptr; }
         QB_CUDA(cudaHostAlloc(&b->tok_stage, (size_t)n * sizeof(int32_t), cudaHostAllocDefault));
+        QB_CUDA(cudaMalloc(&b->tok_all, (size_t)n * sizeof(int32_t)));
         b->tok_stage_cap = n;
     } else {
-        QB_CUDA(cudaStreamSynchronize(ctx->stream));     // an earlier call's copies out of the staging area are done
+        QB_CUDA(cudaEventSynchronize(b->tok_ev));
     }
     memcpy(b->tok_stage, tokens_host, (size_t)n * sizeof(int32_t));
+    QB_CUDA(cudaMemcpyAsync(b->tok_all, b->tok_stage, (size_t)n * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+    QB_CUDA(cudaEventRecord(b->tok_ev, ctx->stream));
     for (uint32_t off = 0; off < n; off += b->chunk) {
         const uint32_t M = std::min(b->chunk, n - off);
         const bool last = off + M == n && !more_follows;
         const uint32_t p0 = (uint32_t)b->host_pos[seq];
         QB_TRY(ensure_pages(ctx, b, seq, p0 + M));
-        QB_CUDA(cudaMemcpyAsync(b->tok_buf, b->tok_stage + off, M * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        const int32_t *toks = b->tok_all + off;
         if (b->seen) {
-            QB_CUDA(qb_launch_pdl(ctx->stream, mark_seen_tokens_kernel, dim3((M + 127) / 128), dim3(128), (size_t)0, b->tok_buf, M,
+            QB_CUDA(qb_launch_pdl(ctx->stream, mark_seen_tokens_kernel, dim3((M + 127) / 128), dim3(128), (size_t)0, toks, M,
                                   b->seen + (size_t)seq * b->seen_words, c.vocab_size));
             QB_LAUNCHED(ctx, "mark_seen_tokens_kernel");
         }
         RowSet rs;
         rs.seq0 = seq; rs.ns = 1; rs.R = M; rs.seq_pos = b->pos + seq; rs.max_pos = p0 + M;
-        QB_TRY(target_forward(ctx, b, b->tok_buf, rs, false, last ? 2 : 0));
+        QB_TRY(target_forward(ctx, b, toks, rs, false, last ? 2 : 0));
         if (c.mtp_layers && b->k > 0) {
             // MTP-layer K/V of the chunk: row r pairs token r with the target hidden of row r-1 (row 0: the previous chunk's
             // last hidden, kept behind the chunk rows)
@@ -1293,7 +1304,7 @@ static int prefill_impl(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *t
                                   (int32_t)(b->rows_cap + seq)));
             QB_LAUNCHED(ctx, "chunk_map_kernel");
             // the MTP pass overwrites the logits' argmax partials only in full mode; kv_only leaves them alone
-            QB_TRY(mtp_forward(ctx, b, b->tok_buf, b->hid, b->map_chunk, rs, true));
+            QB_TRY(mtp_forward(ctx, b, toks, b->hid, b->map_chunk, rs, true));
         }
         if (last) {
             if (samp) {
