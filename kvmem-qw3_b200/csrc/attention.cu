@@ -411,45 +411,64 @@ __global__ void __launch_bounds__(32 * JW * MT) attn_split_kernel(AttnArgs a, co
     cp_async_wait<0>();
 }
 
-// Merge split partials in ascending order, apply the sigmoid gate, write fp32 and/or int8.
-// grid (rows, n_heads), blockDim = HD.
-__global__ void attn_merge_kernel(AttnArgs a, const int32_t *__restrict__ seq_pos, uint32_t R, uint32_t max_splits,
-                                  float *out, int8_t *q8, uint32_t q_pitch, float *dsc, uint32_t d_ld) {
+// Merge split partials, apply the sigmoid gate, write fp32 and/or int8.  The splits are folded in blocks of 16 (absolute
+// indices): within a block in ascending order, then the block sums in ascending order -- an order that depends on the
+// row's own split count only, so a row's bits do not depend on the launch it is in, and that lets the NG thread groups
+// of a CTA fold different blocks at the same time (at 32 K context a row has 129 splits; one group walking them all
+// was a 36 us chain of dependent loads).  Up to 16 splits (contexts below 4096) it is the plain ascending sum.
+// grid (rows, n_heads), block (hd, NG); dynamic shared memory: [nb_max][hd + 1] floats.
+constexpr uint32_t MERGE_BLOCK = 16;
+__global__ void __launch_bounds__(1024) attn_merge_kernel(AttnArgs a, const int32_t *__restrict__ seq_pos, uint32_t R, uint32_t max_splits,
+                                                          float *out, int8_t *q8, uint32_t q_pitch, float *dsc, uint32_t d_ld) {
     QB_PDL_ENTER();
-    __shared__ float wsplit[256];
-    __shared__ float red_m[8];
-    const uint32_t row = blockIdx.x, head = blockIdx.y, i = threadIdx.x, hd = a.hd, lane = i & 31;
+    extern __shared__ float blk[];                                       // [block][hd] numerators, then [block] denominators
+    __shared__ float wsplit[1024], lsplit[1024];                         // weight and row sum of every split of a pass
+    __shared__ float red_m[32];
+    const uint32_t row = blockIdx.x, head = blockIdx.y, i = threadIdx.x, g = threadIdx.y, NG = blockDim.y, hd = a.hd, lane = i & 31;
+    const uint32_t tid = g * hd + i, nthreads = hd * NG;
     const int pos = seq_pos[row / R] + (int)(row % R);
     const uint32_t nsplit = ((uint32_t)pos + a.split_keys) / a.split_keys;
+    const uint32_t nb = (nsplit + MERGE_BLOCK - 1) / MERGE_BLOCK;
     const size_t p0 = ((size_t)row * a.n_heads + head) * max_splits;
+    float *blk_den = blk + (size_t)nb * hd;
     // block-wide maximum of the split maxima (all loads in flight together)
     float mx = -INFINITY;
-    for (uint32_t s = i; s < nsplit; s += hd) mx = fmaxf(mx, a.part_ml[(p0 + s) * 2]);
+    for (uint32_t s = tid; s < nsplit; s += nthreads) mx = fmaxf(mx, a.part_ml[(p0 + s) * 2]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) red_m[i >> 5] = mx;
+    if ((tid & 31) == 0) red_m[tid >> 5] = mx;
     __syncthreads();
     mx = red_m[0];
-    for (uint32_t k = 1; k < hd / 32; ++k) mx = fmaxf(mx, red_m[k]);
-    // splits in ascending order, 256 at a time: weights computed in parallel, then every thread walks them
-    float num = 0.0f, den = 0.0f;
-    for (uint32_t s0 = 0; s0 < nsplit; s0 += 256) {
-        const uint32_t cnt = min(256u, nsplit - s0);
+    for (uint32_t k = 1; k < nthreads / 32; ++k) mx = fmaxf(mx, red_m[k]);
+    // 1024 splits at a time: weights computed by everybody, then group g folds the blocks b = g, g + NG, ...
+    for (uint32_t s0 = 0; s0 < nsplit; s0 += 1024) {
+        const uint32_t cnt = min(1024u, nsplit - s0);
         __syncthreads();
-        for (uint32_t s = i; s < cnt; s += hd) wsplit[s] = expf(a.part_ml[(p0 + s0 + s) * 2] - mx);
-        __syncthreads();
-        const float *acc = a.part_acc + (p0 + s0) * hd + i;
-        const float *ml = a.part_ml + (p0 + s0) * 2 + 1;
-        uint32_t s = 0;
-        for (; s + 8 <= cnt; s += 8) {
-            float va[8], vl[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) { va[u] = acc[(size_t)(s + u) * hd]; vl[u] = ml[(s + u) * 2]; }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) { num = fmaf(va[u], wsplit[s + u], num); den = fmaf(vl[u], wsplit[s + u], den); }
+        for (uint32_t s = tid; s < cnt; s += nthreads) {
+            const float2 ml = *reinterpret_cast<const float2 *>(a.part_ml + (p0 + s0 + s) * 2);
+            wsplit[s] = expf(ml.x - mx);
+            lsplit[s] = ml.y;
         }
-        for (; s < cnt; ++s) { num = fmaf(acc[(size_t)s * hd], wsplit[s], num); den = fmaf(ml[s * 2], wsplit[s], den); }
+        __syncthreads();
+        for (uint32_t bl = g; bl * MERGE_BLOCK < cnt; bl += NG) {
+            const uint32_t sb = bl * MERGE_BLOCK, n = min(MERGE_BLOCK, cnt - sb);
+            const float *acc = a.part_acc + (p0 + s0 + sb) * hd + i;
+            float va[MERGE_BLOCK];
+#pragma unroll
+            for (uint32_t u = 0; u < MERGE_BLOCK; ++u) va[u] = u < n ? acc[(size_t)u * hd] : 0.0f;       // all in flight together
+            float num = 0.0f, den = 0.0f;
+#pragma unroll
+            for (uint32_t u = 0; u < MERGE_BLOCK; ++u)
+                if (u < n) { num = fmaf(va[u], wsplit[sb + u], num); den = fmaf(lsplit[sb + u], wsplit[sb + u], den); }
+            const uint32_t b_abs = s0 / MERGE_BLOCK + bl;
+            blk[(size_t)b_abs * hd + i] = num;
+            if (i == 0) blk_den[b_abs] = den;
+        }
     }
+    __syncthreads();
+    if (g != 0) return;
+    float num = 0.0f, den = 0.0f;
+    for (uint32_t bq = 0; bq < nb; ++bq) { num += blk[(size_t)bq * hd + i]; den += blk_den[bq]; }
     float o = __fdiv_rn(num, den);
     if (!a.no_gate) {
         const float gate = qb_ldsum(a.qkv, (size_t)row * a.row_stride + (size_t)head * 2 * hd + hd + i, a.in_S, a.in_pstride);
@@ -465,6 +484,20 @@ __global__ void attn_merge_kernel(AttnArgs a, const int32_t *__restrict__ seq_po
         q8[(size_t)row * q_pitch + col] = (int8_t)((amax == 0.0f) ? 0 : __float2int_rn(__fmul_rn(o, d_inv)));
         if (lane == 0) dsc[(size_t)(col / 32) * d_ld + row] = (amax == 0.0f) ? 0.0f : __fdiv_rn(1.0f, d_inv);
     }
+}
+
+// One place for the merge launch: NG thread groups by the host's bound of the split count (the result does not depend on NG).
+static int launch_merge(qb_ctx *ctx, const AttnArgs &aa, const int32_t *seq_pos, uint32_t R, uint32_t ms, float *out, int8_t *q8,
+                        uint32_t q_pitch, float *d, uint32_t d_ld) {
+    const uint32_t nb_max = (ms + MERGE_BLOCK - 1) / MERGE_BLOCK;
+    const uint32_t ng = std::max(1u, std::min(std::min(nb_max, 1024u / aa.hd), 8u));
+    const size_t smem = (size_t)nb_max * (aa.hd + 1) * sizeof(float);
+    QB_REQUIRE(smem <= 200 * 1024, "attention: %u splits exceed the merge kernel's shared memory", ms);
+    if (smem > 48 * 1024) QB_CUDA(cudaFuncSetAttribute(attn_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(aa.rows, aa.n_heads), block(aa.hd, ng);
+    QB_CUDA(qb_launch_pdl(ctx->stream, attn_merge_kernel, dim3(grid), dim3(block), smem, aa, seq_pos, R, ms, out, q8, q_pitch, d, d_ld));
+    QB_LAUNCHED(ctx, "attn_merge_kernel");
+    return QB_OK;
 }
 
 template <int HD, int JW, int MT>
@@ -529,6 +562,15 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
     QB_REQUIRE(aa.split_keys / a.page_size <= QB_ATTN_RUN_PAGES, "attention: a split of %u keys spans more than %u pages of %u", aa.split_keys, QB_ATTN_RUN_PAGES, a.page_size);
     QB_REQUIRE(((uintptr_t)a.qkv & 7) == 0 && a.row_stride % 2 == 0, "attention: q rows must be 8-byte aligned");
     int st = QB_OK;
+    // decode and verify rows (a handful per sequence) run on the tensor-memory kernel; QW3B200_ATTN_TC=0 keeps them on
+    // the mma.sync shapes (the two differ in the last bits, so rows of prompt chunks never take it: a request's bits
+    // must not depend on how its prompt was cut)
+    const char *tc_env = getenv("QW3B200_ATTN_TC");                  // read per call: tests switch it
+    const bool tc_on = !(tc_env && tc_env[0] == '0');
+    if (tc_on && !a.ingest && R <= 8 && qb_attn_tc_supports(aa)) {
+        QB_TRY(qb_attn_tc_launch(ctx, aa, seq_pos, R, n_seqs, ms));
+        return launch_merge(ctx, aa, seq_pos, R, ms, out, q8, q_pitch, d, d_ld);
+    }
     // prompt chunks (many rows per sequence) take the 64-query shape: a quarter of the passes over the cache
     const bool wide = R * G > 64;
     if (a.hd == 256) st = wide ? launch_split<256, 4, 4>(ctx, aa, seq_pos, R, n_seqs, ms) : launch_split<256, 8, 2>(ctx, aa, seq_pos, R, n_seqs, ms);
@@ -536,8 +578,5 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
     else if (a.hd == 64) st = wide ? launch_split<64, 4, 4>(ctx, aa, seq_pos, R, n_seqs, ms) : launch_split<64, 4, 2>(ctx, aa, seq_pos, R, n_seqs, ms);
     else return qb_fail(QB_ERR_UNSUPPORTED, "attention: head_dim %u unsupported", a.hd);
     QB_TRY(st);
-    dim3 grid(a.rows, a.n_heads);
-    QB_CUDA(qb_launch_pdl(ctx->stream, attn_merge_kernel, dim3(grid), dim3(a.hd), (size_t)(0), aa, seq_pos, R, ms, out, q8, q_pitch, d, d_ld));
-    QB_LAUNCHED(ctx, "attn_merge_kernel");
-    return QB_OK;
+    return launch_merge(ctx, aa, seq_pos, R, ms, out, q8, q_pitch, d, d_ld);
 }

@@ -864,6 +864,7 @@ struct RowSet {
     uint32_t seq0 = 0, ns = 0, R = 0;      // sequences [seq0, seq0+ns), R rows each
     const int32_t *seq_pos = nullptr;      // device [ns]: position of each sequence's first row
     uint32_t max_pos = 0;                  // host upper bound of any row position
+    bool ingest = false;                   // rows of a prompt chunk (not of a decode / verify step)
     uint32_t rows() const { return ns * R; }
 };
 
@@ -878,6 +879,7 @@ static int attention_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t c
     a.q_norm_w = L.q_norm; a.k_norm_w = L.k_norm; a.inv_freq = m->inv_freq;
     a.page_table = b->page_table + (size_t)rs.seq0 * b->pages_per_seq; a.pt_stride = b->pages_per_seq; a.page_size = b->page_size;
     a.err_flag = ctx->err_flag_dev;
+    a.ingest = rs.ingest;
     a.k_cache = b->kc[cache_idx]; a.v_cache = b->vc[cache_idx];
     a.max_pos = rs.max_pos; a.part_acc = b->att_acc; a.part_ml = b->att_ml; a.kv_only = kv_only;
     if (kv_only) {
@@ -1295,7 +1297,7 @@ static int prefill_impl(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *t
             QB_LAUNCHED(ctx, "mark_seen_tokens_kernel");
         }
         RowSet rs;
-        rs.seq0 = seq; rs.ns = 1; rs.R = M; rs.seq_pos = b->pos + seq; rs.max_pos = p0 + M;
+        rs.seq0 = seq; rs.ns = 1; rs.R = M; rs.seq_pos = b->pos + seq; rs.max_pos = p0 + M; rs.ingest = true;
         QB_TRY(target_forward(ctx, b, toks, rs, false, last ? 2 : 0));
         if (c.mtp_layers && b->k > 0) {
             // MTP-layer K/V of the chunk: row r pairs token r with the target hidden of row r-1 (row 0: the previous chunk's

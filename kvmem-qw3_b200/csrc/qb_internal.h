@@ -287,7 +287,11 @@ struct AttnArgs {
     bool no_gate = false;            // merge: leave the output ungated (attention_decode + a separate apply_attn_gate)
     uint32_t split_keys = 0;         // keys per split (set by qb_attn_run)
     int *err_flag = nullptr;         // an append to a page-table entry < 0 is skipped and recorded here (3002)
+    bool ingest = false;             // rows of a prompt chunk: always the mma.sync shapes, whose rows do not depend on the chunking
 };
+// Decode / verify rows on tcgen05 (attention_tc.cu): same partials as attn_split_kernel, merged by the same kernel.
+bool qb_attn_tc_supports(const AttnArgs &a);
+int qb_attn_tc_launch(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t R, uint32_t n_seqs, uint32_t max_splits);
 int qb_attn_prepare(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t n_seqs);
 // split partials, then merge + gate; out fp32 [rows][n_heads*hd] and/or int8 (q8 [rows][q_pitch], d [.][d_ld]).
 int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t n_seqs, float *out, int8_t *q8,

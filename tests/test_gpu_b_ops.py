@@ -108,12 +108,13 @@ def test_attention_single_row_and_tiny_heads(qb, orc, ctx):
 
 
 @pytest.mark.parametrize("n_heads,n_kv,hd,base,R", [(24, 4, 256, 700, 45), (4, 2, 64, 130, 70), (16, 2, 128, 0, 33)])
-def test_attention_prompt_chunk_shape_has_the_bits_of_the_verify_shape(qb, orc, ctx, n_heads, n_kv, hd, base, R):
+def test_attention_prompt_chunk_shape_has_the_bits_of_the_verify_shape(qb, orc, ctx, monkeypatch, n_heads, n_kv, hd, base, R):
     """A prompt chunk (many rows of one sequence) runs the 64-query shape of the attention kernel, decode and verify
     rows the 32-query shape; a row must get the same bits from either, or a request's tokens would depend on how its
     prompt was cut into chunks.  The chunk's rows are recomputed four at a time and compared bit for bit; the chunk
     itself is checked against the oracle by _attn_case."""
     _attn_case(qb, orc, ctx, n_heads, n_kv, hd, 16 if hd == 64 else 64, 16, [base], R, "shuffle", seed=70 + R)
+    monkeypatch.setenv("QW3B200_ATTN_TC", "0")       # the four-row calls below on the mma.sync shape, not on the tcgen05 kernel
     rng = np.random.default_rng(90 + R)
     page_size, rope_dim = 16, 16 if hd == 64 else 64
     max_pos = base + R
@@ -148,6 +149,18 @@ def test_attention_prompt_chunk_shape_has_the_bits_of_the_verify_shape(qb, orc, 
         qb.binding.check(L.qb_attention_paged_gated(ctx.h, part.ptr, n, stride, n_heads, n_kv, hd, ctx.array(np.array([base + r0], np.int32)).ptr, 1,
                                                     d_pt.ptr, pps, page_size, d_kc.ptr, d_vc.ptr, max_pos, out.ptr))
         assert np.array_equal(out.download(), want[r0:r0 + n]), r0
+
+
+@pytest.mark.parametrize("n_heads,n_kv,hd,bases,R", [(24, 4, 256, [0, 61, 255, 700, 3000], 4), (16, 2, 128, [257, 1, 1023], 5),
+                                                    (24, 4, 256, [9000], 1), (8, 4, 128, [130, 511], 8)])
+def test_attention_tensor_memory_kernel_vs_mma_sync_kernel(qb, orc, ctx, monkeypatch, n_heads, n_kv, hd, bases, R):
+    """Decode / verify rows run the tcgen05 kernel (keys as the MMA's M, S and O in tensor memory, TMA-fed); the same
+    call on the mma.sync kernel (QW3B200_ATTN_TC=0) must agree within the fp16 rounding of the probabilities, and both are
+    checked against the oracle by _attn_case (contexts that end inside a tile, inside a split, and span many splits)."""
+    got_tc = _attn_case(qb, orc, ctx, n_heads, n_kv, hd, 64, 16, bases, R, "shuffle", seed=120 + R)
+    monkeypatch.setenv("QW3B200_ATTN_TC", "0")
+    got_mma = _attn_case(qb, orc, ctx, n_heads, n_kv, hd, 64, 16, bases, R, "shuffle", seed=120 + R)
+    assert np.allclose(got_tc, got_mma, rtol=2e-3, atol=1e-3), float(np.abs(got_tc - got_mma).max())
 
 
 def _dn_inputs(rng, nk, nv, hd, n_seqs, R, n_slots):
