@@ -139,7 +139,9 @@ attn_tc_kernel(AttnArgs a, const __grid_constant__ CUtensorMap map_k, const __gr
                const int32_t *__restrict__ seq_pos, uint32_t R, uint32_t max_splits, uint32_t spc, uint32_t qr) {
     using C = AtcCfg<HD>;
     constexpr uint32_t NST = C::NST, UPT = C::UPT;
-    QB_PDL_ENTER();
+    // programmatic dependent launch: announce the dependents at once; everything that needs nothing of the preceding
+    // kernel (barriers, tensor memory, the tensor maps' first fetch) is set up before this kernel waits for it
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *misc = smem + C::MISC_OFF;
@@ -154,6 +156,23 @@ attn_tc_kernel(AttnArgs a, const __grid_constant__ CUtensorMap map_k, const __gr
     int *page_slot = reinterpret_cast<int *>(misc + 1536);               // [128]
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (uint32_t i = 0; i < NST; ++i) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
+        mbar_init(bar_sfull, 1);
+        mbar_init(bar_pready, 256);
+        for (uint32_t i = 0; i < 2; ++i) { mbar_init(bar_ofull + 8 * i, 1); mbar_init(bar_ofree + 8 * i, 256); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    __syncthreads();                                                     // barriers initialised before warp 0 loads against them
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t split0 = blockIdx.x * spc, kvh = blockIdx.y;
     const uint32_t chunks = (R + qr - 1) / qr;
     const uint32_t seq = blockIdx.z / chunks, chunk = blockIdx.z % chunks;
@@ -163,23 +182,58 @@ attn_tc_kernel(AttnArgs a, const __grid_constant__ CUtensorMap map_k, const __gr
     const int base_pos = seq_pos[seq] + (int)r_begin;
     const int last_key = base_pos + (int)r_count - 1;
     const int k_begin = (int)(split0 * a.split_keys);
-    if (k_begin > last_key) return;                                      // before any barrier or allocation: uniform per CTA
+    if (k_begin > last_key) {                                            // nothing to do (uniform per CTA): give the tensor memory back
+        tc_fence_before();
+        __syncthreads();
+        if (warp == 1) {
+            tc_fence_after();
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(*tmem_slot), "r"(C::TMEM_COLS) : "memory");
+        }
+        return;
+    }
     const int k_end = min(k_begin + (int)(spc * a.split_keys), last_key + 1);
     const uint32_t n_splits = (uint32_t)(k_end - k_begin + (int)a.split_keys - 1) / a.split_keys;
     const int32_t *pt = a.page_table + (size_t)seq * a.pt_stride;
     const int pg_last = (k_end - 1) >> 4;                                // pages are 16 keys (checked by the launcher)
     const int pg_first = k_begin >> 4;
 
-    if (tid == 0) {
-        for (uint32_t i = 0; i < NST; ++i) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
-        mbar_init(bar_sfull, 1);
-        mbar_init(bar_pready, 256);
-        for (uint32_t i = 0; i < 2; ++i) { mbar_init(bar_ofull + 8 * i, 1); mbar_init(bar_ofree + 8 * i, 256); }
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // tiles of split s: 1 or 2 (the last split of a sequence may stop inside its first tile)
+    auto tiles_of = [&](uint32_t s) -> uint32_t {
+        const int kb = k_begin + (int)(s * a.split_keys);
+        return (k_end - kb) > ATC_TILE ? 2u : 1u;
+    };
+    // The loader's cursor over the units of the run: per split K0 [K1] V0 [V1], a tile being UPT units.
+    struct Cursor { uint32_t s, item, n_items; };
+    auto cur_start = [&]() { Cursor c; c.s = 0; c.item = 0; c.n_items = 2 * tiles_of(0) * UPT; return c; };
+    auto cur_next = [&](Cursor &c) {
+        if (++c.item >= c.n_items) { ++c.s; c.item = 0; c.n_items = c.s < n_splits ? 2 * tiles_of(c.s) * UPT : 0; }
+    };
+    auto load_unit = [&](const Cursor &c, uint32_t st) {                 // whole warp 0
+        const uint32_t nt = c.n_items / (2 * UPT);
+        const uint32_t tile_item = c.item / UPT, u = c.item % UPT, t = tile_item % nt;
+        const bool is_v = tile_item >= nt;
+        const uint32_t full = bar_full + 8 * st;
+        if (lane == 0) mbar_expect_tx(full, C::UNIT_BYTES);
+        __syncwarp();
+        const int key0 = k_begin + (int)(c.s * a.split_keys) + (int)t * ATC_TILE;
+        if (lane < 16) {
+            const uint32_t pg_in = lane >> 1, cb = lane & 1;                    // page of the tile, column block of the unit
+            // pages past the last key of the run are not looked up: the last valid page is loaded again (finite values,
+            // masked by the softmax)
+            const int pg = min((key0 >> 4) + (int)pg_in, pg_last);
+            const uint32_t dst = smem_u32(smem + (size_t)st * C::UNIT_BYTES) + cb * (ATC_TILE * 128) + pg_in * 2048;
+            tma_load_2d(dst, is_v ? &map_v : &map_k, (int)(kvh * HD + (u * 2 + cb) * 64), page_slot[pg - pg_first], full);
+        }
+    };
+    Cursor lc = cur_start();
+    uint32_t l_git = 0;
+    if (warp == 0) {
+        // barriers, the run's page slots (8 splits x 16 pages at most) and the first ring-full of loads, before the rest of
+        // the CTA has staged the queries and allocated tensor memory
+        for (int i = (int)lane; i <= pg_last - pg_first && i < 128; i += 32) page_slot[i] = pt[pg_first + i] * 16;
+        __syncwarp();
+        for (; l_git < NST && lc.s < n_splits; ++l_git, cur_next(lc)) load_unit(lc, l_git);
     }
-    // first slot of every page the run touches (8 splits x 16 pages at most)
-    for (int i = (int)tid; i <= pg_last - pg_first && i < 128; i += ATC_THREADS) page_slot[i] = pt[pg_first + i] * 16;
     if (tid < ATC_NQ) {
         qpos[tid] = tid < NQ ? base_pos + (int)(tid / G) : -1;
         qidx[tid] = (uint32_t)(((size_t)seq * R + r_begin + tid / G) * a.n_heads + kvh * G + tid % G);
@@ -205,47 +259,18 @@ attn_tc_kernel(AttnArgs a, const __grid_constant__ CUtensorMap map_k, const __gr
         }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");        // the MMAs read Q through the async proxy
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 64;      // O buffer b at tmem_o + 64 * b
 
-    // tiles of split s: 1 or 2 (the last split of a sequence may stop inside its first tile)
-    auto tiles_of = [&](uint32_t s) -> uint32_t {
-        const int kb = k_begin + (int)(s * a.split_keys);
-        return (k_end - kb) > ATC_TILE ? 2u : 1u;
-    };
-
     if (warp == 0) {
-        // ---- loader: per split the units K0 [K1] V0 [V1], a tile being UPT units of two 128-byte columns (32 KB) ----
-        uint32_t git = 0;
-        bool ok = true;
-        for (uint32_t s = 0; s < n_splits && ok; ++s) {
-            const uint32_t nt = tiles_of(s);
-            for (uint32_t item = 0; item < 2 * nt * UPT && ok; ++item, ++git) {
-                const uint32_t tile_item = item / UPT, u = item % UPT;
-                const uint32_t t = tile_item % nt;
-                const bool is_v = tile_item >= nt;
-                const uint32_t st = git % NST, ph = (git / NST) & 1;
-                if (!__all_sync(0xffffffffu, mbar_wait_idle(bar_empty + 8 * st, ph ^ 1, abort_flag, 100))) { ok = false; break; }
-                const uint32_t full = bar_full + 8 * st;
-                if (lane == 0) mbar_expect_tx(full, C::UNIT_BYTES);
-                __syncwarp();
-                const int key0 = k_begin + (int)(s * a.split_keys) + (int)t * ATC_TILE;
-                if (lane < 16) {
-                    const uint32_t pg_in = lane >> 1, cb = lane & 1;                    // page of the tile, column block of the unit
-                    // pages past the last key of the run are not looked up: the last valid page is loaded again (finite
-                    // values, masked by the softmax)
-                    const int pg = min((key0 >> 4) + (int)pg_in, pg_last);
-                    const uint32_t dst = smem_u32(smem + (size_t)st * C::UNIT_BYTES) + cb * (ATC_TILE * 128) + pg_in * 2048;
-                    tma_load_2d(dst, is_v ? &map_v : &map_k, (int)(kvh * HD + (u * 2 + cb) * 64), page_slot[pg - pg_first], full);
-                }
-            }
+        // ---- loader: the rest of the units, each into the ring unit its predecessor of NST units ago has left ----
+        for (; lc.s < n_splits; ++l_git, cur_next(lc)) {
+            const uint32_t st = l_git % NST, ph = (l_git / NST) & 1;
+            if (!__all_sync(0xffffffffu, mbar_wait_idle(bar_empty + 8 * st, ph ^ 1, abort_flag, 100))) break;
+            load_unit(lc, st);
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
