@@ -339,7 +339,8 @@ uint32_t qb_page_pool_free_count(void *pool);
  * tokens_host (the prefix's tokens; may be NULL unless token penalties are on) feeds the seen-token record.
  * qb_prefix_attach makes an empty sequence (after qb_seq_reset) of the same batch continue from the prefix end: it shares
  * the pages and receives the copies; the caller goes on with qb_prefill / qb_prefill_chunk of the rest of its prompt.
- * qb_prefix_release drops the entry's hold on the pages (they return to the pool when no sequence uses them either). */
+ * qb_prefix_release drops the entry's hold on the pages (they return to the pool when no sequence uses them either); an
+ * entry must be released before its batch is destroyed (the pool lives in the batch). */
 typedef struct qb_prefix qb_prefix;
 int  qb_prefix_capture(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *tokens_host, uint32_t n_tokens, qb_prefix **out);
 int  qb_prefix_attach(qb_ctx *ctx, qb_batch *b, uint32_t seq, const qb_prefix *prefix);

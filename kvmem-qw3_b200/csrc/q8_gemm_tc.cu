@@ -277,12 +277,13 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
                             if (q + 1 < C::KPS * NCH) tmem_ld<16>(tbase + ((q + 1) / NCH) * MT + ((q + 1) % NCH) * 16, v[(q + 1) & 1]);
                             const float dw = __half2float(wd[kb * 128 + r]);
                             const f32x2 dw2 = pack2(dw, dw);
-                            const float4 *xd4 = reinterpret_cast<const float4 *>(xd + kb * MT + c0);      // four scales per shared-memory load
+                            // four scales per shared-memory load, read as the two packed pairs the arithmetic takes (no repacking)
+                            const ulonglong2 *xd4 = reinterpret_cast<const ulonglong2 *>(xd + kb * MT + c0);
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
-                                const float4 x4 = xd4[i];
-                                acc2[c0 / 2 + 2 * i] = fma2(mul2(dw2, pack2(x4.x, x4.y)), pack2((float)v[q & 1][4 * i], (float)v[q & 1][4 * i + 1]), acc2[c0 / 2 + 2 * i]);
-                                acc2[c0 / 2 + 2 * i + 1] = fma2(mul2(dw2, pack2(x4.z, x4.w)), pack2((float)v[q & 1][4 * i + 2], (float)v[q & 1][4 * i + 3]), acc2[c0 / 2 + 2 * i + 1]);
+                                const ulonglong2 x4 = xd4[i];
+                                acc2[c0 / 2 + 2 * i] = fma2(mul2(dw2, x4.x), pack2((float)v[q & 1][4 * i], (float)v[q & 1][4 * i + 1]), acc2[c0 / 2 + 2 * i]);
+                                acc2[c0 / 2 + 2 * i + 1] = fma2(mul2(dw2, x4.y), pack2((float)v[q & 1][4 * i + 2], (float)v[q & 1][4 * i + 3]), acc2[c0 / 2 + 2 * i + 1]);
                             }
                         }
                         tc_fence_before();
