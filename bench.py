@@ -861,16 +861,19 @@ def workload_serve(args):
     cfg = pkg.configs.qwen27b(args.layers)
     model = pkg.Model(ctx, cfg, pkg.configs.MODEL_SEED)
     rs = np.random.RandomState(9)
-    for loop in ("run", "run_compact"):
+    # the third run: one K/V page pool for all slots, 60 % of what private pages would hold; admission reserves pages
+    for loop, pooled in (("run", False), ("run_compact", False), ("run_compact", True)):
         reqs = [pkg.serve.Request(i, rs.randint(0, cfg.vocab_size, int(rs.randint(256, 513))).tolist(), int(rs.randint(48, 97)), arrival_step=2 * i)
                 for i in range(args.requests)]
-        b = pkg.Batch(model, args.slots, 1024, K_DRAFT)
+        pages_private = args.slots * ((1024 + K_DRAFT + 1 + 15) // 16)
+        b = pkg.Batch(model, args.slots, 1024, K_DRAFT, pool_pages=int(0.6 * pages_private) if pooled else 0)
         ctx.sync()
         t0 = time.perf_counter()
         done = getattr(pkg.serve, loop)(b, reqs)
         ctx.sync()
         dt = time.perf_counter() - t0
-        print(json.dumps({"loop": loop, "slots": args.slots, "requests": len(done), "emitted": sum(len(r.tokens) for r in done),
+        print(json.dumps({"loop": loop, "kv_pages": int(0.6 * pages_private) if pooled else pages_private, "pooled": pooled, "slots": args.slots,
+                          "requests": len(done), "emitted": sum(len(r.tokens) for r in done),
                           "wall_s": round(dt, 2), "tok_per_s": round(sum(len(r.tokens) for r in done) / dt, 1)}), flush=True)
         b.close()
     model.close(); ctx.close()
