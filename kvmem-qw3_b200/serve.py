@@ -93,11 +93,74 @@ class DrawQueue:
         return v
 
 
-def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=None, rng_of=None, prefill_chunk=0):
+class PrefixCache:
+    """Host policy over the engine's shared-prefix entries (prefix_capture / prefix_attach / prefix_release), the role of the
+    reference server's prefix cache (src/qwen_native_backend.cpp:9785-10410): a prompt is looked up by its page-aligned
+    prefixes, longest first; a hit seeds the request from the entry instead of ingesting those tokens; a miss ingests the
+    prompt in two parts so that an entry of its page-aligned prefix can be taken; entries nobody has used for longest are
+    released first when the page pool runs short or the table is full.  Entries hold K/V pages: `pages_held` is what the
+    admission control of run_compact counts against the pool."""
+
+    def __init__(self, engine, max_entries=16, min_tokens=None):
+        self.engine, self.max_entries = engine, max_entries
+        self.page = engine.page_size
+        self.min_tokens = self.page if min_tokens is None else max(self.page, min_tokens)
+        self.table = collections.OrderedDict()          # tuple(tokens) -> entry handle, least recently used first
+        self.hits = self.misses = self.evictions = 0
+
+    def aligned(self, n_prompt):
+        """Longest prefix length an entry may have for a prompt of n_prompt tokens: whole pages, at least one token left."""
+        n = (n_prompt - 1) // self.page * self.page
+        return n if n >= self.min_tokens else 0
+
+    def lookup(self, prompt):
+        """(entry, n_tokens) of the longest cached page-aligned prefix of `prompt`, or (None, 0)."""
+        n = self.aligned(len(prompt))
+        while n >= self.min_tokens:
+            key = tuple(prompt[:n])
+            if key in self.table:
+                self.table.move_to_end(key)
+                self.hits += 1
+                return self.table[key], n
+            n -= self.page
+        self.misses += 1
+        return None, 0
+
+    def wants(self, prompt):
+        """Prefix length to take an entry of while this prompt is ingested (0: none, or already there)."""
+        n = self.aligned(len(prompt))
+        return n if n and tuple(prompt[:n]) not in self.table else 0
+
+    def insert(self, slot, tokens):
+        while len(self.table) >= self.max_entries and self.evict_one():
+            pass
+        if len(self.table) >= self.max_entries:
+            return False
+        self.table[tuple(tokens)] = self.engine.prefix_capture(slot, list(tokens))
+        return True
+
+    def evict_one(self):
+        if not self.table:
+            return False
+        _, entry = self.table.popitem(last=False)
+        self.engine.prefix_release(entry)
+        self.evictions += 1
+        return True
+
+    def pages_held(self):
+        return sum(len(k) // self.page for k in self.table)
+
+    def clear(self):
+        while self.evict_one():
+            pass
+
+
+def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=None, rng_of=None, prefill_chunk=0, prefix_cache=None):
     """The loop for engines with set_active(n) and swap(s1, s2): live requests are kept in slots [0, n_live) and only those
     are decoded; a retiring request's slot is filled by the last live one (swap), a new request is ingested in a slot
     beyond the live range -- `prefill_chunk` tokens per iteration when that is set, so decoding goes on meanwhile -- and
-    swapped to the end of the live range when its prompt is in."""
+    swapped to the end of the live range when its prompt is in.  prefix_cache: a PrefixCache over the same (pooled) engine:
+    admitted requests start from the longest cached prefix of their prompt, and leave an entry of their own."""
     pending = collections.deque(sorted(requests, key=lambda r: (r.arrival_step, r.rid)))
     per_step = engine.k + 1 if speculative else 1
     if sampling is not None:
@@ -144,20 +207,31 @@ def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=
             if pool_pages:
                 if pages_of(req) > pool_pages:
                     raise ValueError("request %r needs %d pages, the pool has %d" % (req.rid, pages_of(req), pool_pages))
-                if sum(reserved.values()) + pages_of(req) > pool_pages:
+                held = prefix_cache.pages_held() if prefix_cache else 0
+                while sum(reserved.values()) + held + pages_of(req) > pool_pages and prefix_cache and prefix_cache.evict_one():
+                    held = prefix_cache.pages_held()               # cached prefixes make room before a request has to wait
+                if sum(reserved.values()) + held + pages_of(req) > pool_pages:
                     break                                          # waits for a retirement
                 reserved[req.rid] = pages_of(req)
             pending.popleft()
             slot = next(s for s in range(len(live), engine.n_seqs) if s not in ingest)
             engine.reset(slot)
             req.slot, req.admitted_step = slot, step
-            ingest[slot] = [req, 0]
+            done_n = 0
+            if prefix_cache:
+                entry, done_n = prefix_cache.lookup(req.prompt)
+                if entry is not None:
+                    engine.prefix_attach(slot, entry)
+            ingest[slot] = [req, done_n]
         # ingestion: one chunk per request and iteration (the whole prompt when prefill_chunk is 0)
         for slot in sorted(ingest):
             if slot not in ingest:                                 # moved by a swap earlier in this iteration
                 continue
             req, done_n = ingest[slot]
             n = len(req.prompt) - done_n if not prefill_chunk else min(prefill_chunk, len(req.prompt) - done_n)
+            cut = prefix_cache.wants(req.prompt) if prefix_cache else 0
+            if cut > done_n:                                       # stop at the page-aligned prefix: an entry is taken there
+                n = min(n, cut - done_n)
             final = done_n + n == len(req.prompt)
             if not final:
                 engine.prefill(slot, req.prompt[done_n:done_n + n], more=True)     # no token is chosen, nothing counted
@@ -167,6 +241,8 @@ def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=
             else:
                 engine.prefill(slot, req.prompt[done_n:])
             ingest[slot][1] = done_n + n
+            if prefix_cache and cut and done_n + n == cut:
+                prefix_cache.insert(slot, req.prompt[:cut])
             if not final:
                 continue
             req.tokens.extend(engine.read_output()[slot])          # the prefill's last row gives the first token

@@ -145,3 +145,45 @@ def test_request_continues_from_a_shared_prefix(qb, orc, ctx, tiny_model, penalt
     b.prefix_release(entry)
     assert b.pool_info()["free"] == 16
     b.close()
+
+
+def test_serving_loop_with_prefix_cache_and_page_pool(qb, orc, ctx, tiny_model):
+    """The compacting loop on a pooled batch with the prefix-cache policy: requests that share a system prompt start from
+    the cached entry (fewer prompt tokens ingested), pages are reserved at admission, and every request still gets exactly
+    the token stream it gets alone."""
+    V, k = tiny_model.cfg.vocab_size, 3
+    system = [int(t) for t in orc.synth_prompt(500, V, 40)]
+    tails = [[int(t) for t in orc.synth_prompt(510 + i, V, n)] for i, n in enumerate((5, 17, 9, 30))]
+    prompts = [system + tails[0], system + tails[1], [int(t) for t in orc.synth_prompt(520, V, 50)], system + tails[2], system[:33] + tails[3]]
+
+    def alone(prompt, n):
+        b = qb.Batch(tiny_model, 1, 256, k)
+        b.prefill(0, prompt)
+        out = list(b.read_output()[0])
+        while len(out) < n:
+            b.mtp_step()
+            out += b.read_output()[0]
+        b.close()
+        return out[:n]
+
+    want = [alone(p, 12) for p in prompts]
+    eng = qb.Batch(tiny_model, 2, 256, k, pool_pages=20)
+    counted = {"n": 0}
+    raw_prefill = eng.prefill
+
+    def counting_prefill(seq, tokens, more=False):
+        counted["n"] += len(tokens)
+        raw_prefill(seq, tokens, more)
+
+    eng.prefill = counting_prefill
+    cache = qb.serve.PrefixCache(eng, max_entries=3)
+    reqs = [qb.serve.Request(i, p, 12, arrival_step=3 * i) for i, p in enumerate(prompts)]
+    done = qb.serve.run_compact(eng, reqs, prefix_cache=cache)
+    assert sorted(r.rid for r in done) == list(range(len(prompts)))
+    for r in done:
+        assert r.tokens == want[r.rid], r.rid
+    assert cache.hits == 3                                   # requests 1, 3 and 4 start from the 32-token entry of request 0
+    assert counted["n"] == sum(len(p) for p in prompts) - 3 * 32
+    cache.clear()
+    assert eng.pool_info()["free"] == 20                     # every page is back: requests retired, entries released
+    eng.close()

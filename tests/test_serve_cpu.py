@@ -305,3 +305,68 @@ def test_pooled_engine_admits_only_what_its_page_pool_can_hold():
     assert eng.peak <= 6
     with _pytest.raises(ValueError, match="pages"):
         serve.run_compact(Pooled(4, 3, 256), [serve.Request(9, list(range(100)), 20)])
+
+
+def test_prefix_cache_policy_hits_longest_prefix_and_evicts_least_recently_used():
+    """Requests whose prompts share page-aligned prefixes: a later one starts from the longest cached prefix (it ingests only
+    the rest), everybody gets the stream they get alone, the table evicts its least recently used entry when it is full,
+    and cached prefixes give way before a request has to wait for pages."""
+    serve = entry.load_package().serve
+
+    class Eng(CompactEngine):
+        page_size, pool_pages = 16, 40
+
+        def __init__(self, *a):
+            super().__init__(*a)
+            self.ingested = 0                      # prompt tokens that went through prefill
+            self.entries = {}                      # handle -> tokens
+            self.next_handle = 1
+
+        def prefill(self, s, tokens, more=False):
+            self.ingested += len(tokens)
+            super().prefill(s, tokens, more)
+
+        def prefix_capture(self, s, tokens):
+            assert self.prompt[s] == list(tokens) and self.emitted[s] == 0 and len(tokens) % self.page_size == 0
+            h = self.next_handle
+            self.next_handle += 1
+            self.entries[h] = list(tokens)
+            return h
+
+        def prefix_attach(self, s, h):
+            assert self.prompt[s] is None and self.pos[s] == 0, "attach into a slot that is not empty"
+            self.prompt[s] = list(self.entries[h])
+            self.pos[s] = len(self.entries[h])
+            self.out[s], self.emitted[s] = [], 0
+
+        def prefix_release(self, h):
+            del self.entries[h]
+
+    system = list(range(1000, 1040))                          # 40 shared tokens: 2 whole pages
+    prompts = [system + [7, 8, 9], system + [7, 8, 9, 10, 11], system[:20] + [5] * 30, system + [1], list(range(50))]
+    eng = Eng(2, 3, 512)
+    cache = serve.PrefixCache(eng, max_entries=2)
+    reqs = [serve.Request(i, p, 6, arrival_step=4 * i) for i, p in enumerate(prompts)]
+    done = serve.run_compact(eng, reqs, prefix_cache=cache)
+    assert sorted(r.rid for r in done) == list(range(len(prompts)))
+    for r in done:
+        assert r.tokens == stream(r.prompt, r.max_new_tokens), r.rid
+    # request 0 misses and leaves an entry of 32 tokens; 1 and 3 hit it (45 - 32 and 41 - 32 tokens ingested); 2 shares only
+    # 20 tokens with the system prompt and no entry of 16 tokens exists: a miss that leaves its own entry (48 tokens); 4 is
+    # unrelated: its entry pushes out the least recently used one, which is request 2's
+    assert cache.hits == 2 and cache.misses == 3
+    assert eng.ingested == 43 + (45 - 32) + 50 + (41 - 32) + 50
+    assert cache.evictions == 1 and len(cache.table) == 2 and len(eng.entries) == 2
+    # the entry the hits keep using survives the evictions
+    assert tuple(system[:32]) in cache.table
+    cache.clear()
+    assert eng.entries == {}
+    # pool pressure: with the pool nearly promised away a cached prefix is released rather than a request kept waiting
+    eng2 = Eng(2, 3, 512)
+    eng2.pool_pages = 7
+    cache2 = serve.PrefixCache(eng2)
+    a = serve.Request(0, list(range(100, 170)), 20)           # 70 + 20 + 4 -> 6 pages; leaves an entry of 64 tokens = 4 pages
+    b = serve.Request(1, list(range(300, 340)), 20, arrival_step=40)   # 4 pages: fits only if the entry goes
+    done2 = serve.run_compact(eng2, [a, b], prefix_cache=cache2)
+    assert [r.rid for r in done2] == [0, 1] and cache2.evictions >= 1
+    assert done2[1].tokens == stream(b.prompt, 20)
