@@ -804,9 +804,12 @@ __global__ void chunk_map_kernel(int32_t *map, uint32_t M, int32_t prev_row) {
     if (r < M) map[r] = r == 0 ? prev_row : (int32_t)r - 1;
 }
 
-__global__ void advance_kernel(int32_t *pos, int32_t *sel, uint32_t s, int32_t adv, uint32_t rows_cap, uint32_t H, uint32_t last_row, float *hid) {
+// (every kernel that moves pos[s] also writes the position field of the sequence's step record: the host refreshes its
+// position bound of ALL sequences from those fields, also of sequences that took no part in the last step)
+__global__ void advance_kernel(int32_t *pos, int32_t *sel, uint32_t s, int32_t adv, uint32_t rows_cap, uint32_t H, uint32_t last_row, float *hid,
+                               int32_t *opos) {
     QB_PDL_ENTER();
-    if (threadIdx.x == 0) { pos[s] += adv; sel[s] = 0; }
+    if (threadIdx.x == 0) { pos[s] += adv; sel[s] = 0; opos[s] = pos[s]; }
     const float *src = hid + (size_t)last_row * H;
     float *dst = hid + (size_t)(rows_cap + s) * H;
     for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
@@ -1159,9 +1162,9 @@ struct qb_prefix {
     float *hid = nullptr;
     int32_t *tokens_dev = nullptr;
 };
-__global__ void set_seq_ctl_kernel(int32_t *pos, int32_t *sel, int32_t *cur, uint32_t s, int32_t p) {
+__global__ void set_seq_ctl_kernel(int32_t *pos, int32_t *sel, int32_t *cur, int32_t *opos, uint32_t s, int32_t p) {
     QB_PDL_ENTER();
-    if (threadIdx.x == 0) { pos[s] = p; sel[s] = 0; cur[s] = 0; }
+    if (threadIdx.x == 0) { pos[s] = p; sel[s] = 0; cur[s] = 0; opos[s] = p; }
 }
 
 extern "C" void qb_prefix_release(qb_ctx *ctx, qb_prefix *px) {
@@ -1238,7 +1241,8 @@ extern "C" int qb_prefix_attach(qb_ctx *ctx, qb_batch *b, uint32_t seq, const qb
         QB_CUDA(cudaMemcpyAsync(cv + (size_t)seq * K1 * cfl, px->conv[il], cfl * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
     }
     QB_CUDA(cudaMemcpyAsync(b->hid + (size_t)(b->rows_cap + seq) * c.n_embd, px->hid, (size_t)c.n_embd * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
-    QB_CUDA(qb_launch_pdl(ctx->stream, set_seq_ctl_kernel, dim3(1), dim3(32), (size_t)0, b->pos, b->sel, b->cur, seq, (int32_t)px->n_tokens));
+    QB_CUDA(qb_launch_pdl(ctx->stream, set_seq_ctl_kernel, dim3(1), dim3(32), (size_t)0, b->pos, b->sel, b->cur,
+                          b->out_rec + b->n_seqs + (size_t)b->n_seqs * K1, seq, (int32_t)px->n_tokens));
     QB_LAUNCHED(ctx, "set_seq_ctl_kernel");
     if (b->seen) {
         QB_CUDA(qb_launch_pdl(ctx->stream, mark_seen_tokens_kernel, dim3((px->n_tokens + 127) / 128), dim3(128), (size_t)0, (const int32_t *)px->tokens_dev,
@@ -1323,7 +1327,8 @@ static int prefill_impl(qb_ctx *ctx, qb_batch *b, uint32_t seq, const int32_t *t
             QB_LAUNCHED(ctx, "greedy_commit_kernel");
             QB_TRY(mark_seen_record(ctx, b, seq, 1));
         } else {
-            QB_CUDA(qb_launch_pdl(ctx->stream, advance_kernel, dim3(1), dim3(256), (size_t)(0), b->pos, b->sel, seq, (int32_t)M, b->rows_cap, c.n_embd, M - 1, b->hid));
+            QB_CUDA(qb_launch_pdl(ctx->stream, advance_kernel, dim3(1), dim3(256), (size_t)(0), b->pos, b->sel, seq, (int32_t)M, b->rows_cap, c.n_embd, M - 1, b->hid,
+                                  b->out_rec + b->n_seqs + (size_t)b->n_seqs * K1));
             QB_LAUNCHED(ctx, "advance_kernel");
         }
         b->host_pos[seq] += (int32_t)M;

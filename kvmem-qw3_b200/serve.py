@@ -197,6 +197,8 @@ def run_compact(engine, requests, speculative=True, max_steps=1 << 30, sampling=
             live[s].slot = s
         live.pop()
         engine.set_active(len(live))
+        if pool_pages:
+            engine.reset(last)                           # the retired request's pages go back to the pool now, not at the next admission
 
     while (pending or live or ingest) and step < max_steps:
         # admission: a free slot beyond the live range per arrived request

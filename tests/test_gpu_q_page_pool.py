@@ -187,3 +187,39 @@ def test_serving_loop_with_prefix_cache_and_page_pool(qb, orc, ctx, tiny_model):
     cache.clear()
     assert eng.pool_info()["free"] == 20                     # every page is back: requests retired, entries released
     eng.close()
+
+
+def test_sequence_being_ingested_survives_the_steps_of_the_others(qb, orc, ctx, tiny_model):
+    """A request whose prompt arrives in parts while another request decodes and the host reads every step record: the
+    host's position bound of the ingesting sequence must stay where its last chunk left it (it decides which pages the next
+    chunk gets), and the request must end with the stream it gets alone."""
+    V, k = tiny_model.cfg.vocab_size, 3
+    pa, pb = orc.synth_prompt(801, V, 30), orc.synth_prompt(802, V, 61)
+    solo = qb.Batch(tiny_model, 1, 192, k)
+    solo.prefill(0, pb)
+    want, _ = run_steps(solo, 6)
+    solo.close()
+    b = qb.Batch(tiny_model, 2, 192, k, pool_pages=12)
+    b.set_active(0)
+    b.prefill(0, pa)
+    b.read_output()
+    b.set_active(1)
+    for lo, hi in ((0, 20), (20, 48), (48, 61)):
+        if hi < 61:
+            b.prefill(1, pb[lo:hi], more=True)
+        else:
+            b.prefill(1, pb[lo:hi])
+        assert len(b.seq_pages(1)) == -(-hi // PAGE)
+        b.mtp_step()                      # request A decodes in between; its record is read
+        b.read_output()
+    b.swap(0, 1)
+    b.set_active(1)
+    b.reset(1)
+    # (the first token of B was emitted by its last prefill call, before A's step overwrote nothing of it)
+    got = [b.current_token(0)] if hasattr(b, "current_token") else None
+    outs = []
+    for _ in range(6):
+        b.mtp_step()
+        outs += b.read_output()[0]
+    assert outs == want[0][1:1 + len(outs)]
+    b.close()
