@@ -564,10 +564,11 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
     int st = QB_OK;
     // decode and verify rows (a handful per sequence) run on the tensor-memory kernel; QW3B200_ATTN_TC=0 keeps them on
     // the mma.sync shapes (the two differ in the last bits, so rows of prompt chunks never take it: a request's bits
-    // must not depend on how its prompt was cut)
+    // must not depend on how its prompt was cut; for the same reason a batch fixes a.prefer_tc once, from its capacity,
+    // never from the positions of a call)
     const char *tc_env = getenv("QW3B200_ATTN_TC");                  // read per call: tests switch it
     const bool tc_on = !(tc_env && tc_env[0] == '0');
-    if (tc_on && !a.ingest && R <= 8 && qb_attn_tc_supports(aa)) {
+    if (tc_on && a.prefer_tc && !a.ingest && R <= 8 && qb_attn_tc_supports(aa)) {
         QB_TRY(qb_attn_tc_launch(ctx, aa, seq_pos, R, n_seqs, ms));
         return launch_merge(ctx, aa, seq_pos, R, ms, out, q8, q_pitch, d, d_ld);
     }

@@ -382,6 +382,7 @@ struct QBuf {   // quantised activation buffer for one K
 struct qb_batch {
     qb_model *m = nullptr;
     uint32_t n_seqs = 0, max_ctx = 0, k = 0, page_size = 0, pages_per_seq = 0, rows_cap = 0, chunk = 0, logit_rows = 0;
+    bool attn_tc = false;                  // decode / verify attention on the tensor-memory kernel: decided once, from n_seqs * max_ctx
     uint32_t n_active = 0;                 // the decode steps run sequences [0, n_active); the rest keep their state untouched
     std::vector<__half *> kc, vc;          // per layer (attention layers only), + MTP layer at index n_layers
     std::vector<float *> state, conv;      // per layer (recurrent layers only): [n_seqs][k+1][...]
@@ -466,6 +467,10 @@ static int batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_
     b->m = m; b->n_seqs = n_seqs; b->n_active = n_seqs; b->max_ctx = max_ctx; b->k = draft_k; b->page_size = page_size;
     b->pages_per_seq = (max_ctx + draft_k + 1 + page_size - 1) / page_size;
     b->chunk = std::max(1u, env_u32("QW3B200_PREFILL_CHUNK", 128));
+    // The tensor-memory attention kernel wins once a call has enough keys to fill the GPU (one long context, or many
+    // sequences) and costs a few microseconds per call below that; the two kernels differ in the last bits, so the choice
+    // is a property of the batch (the keys it can hold), the same for every row the batch ever computes.
+    b->attn_tc = (uint64_t)n_seqs * max_ctx >= env_u32("QW3B200_ATTN_TC_MIN_KEYS", 16384);
     b->logit_rows = n_seqs * (draft_k + 1);
     b->rows_cap = std::max(b->chunk, b->logit_rows);
     b->gemm_impl = (int)env_u32("QW3B200_GEMM_IMPL", 0);
@@ -883,6 +888,7 @@ static int attention_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t c
     a.page_table = b->page_table + (size_t)rs.seq0 * b->pages_per_seq; a.pt_stride = b->pages_per_seq; a.page_size = b->page_size;
     a.err_flag = ctx->err_flag_dev;
     a.ingest = rs.ingest;
+    a.prefer_tc = b->attn_tc;
     a.k_cache = b->kc[cache_idx]; a.v_cache = b->vc[cache_idx];
     a.max_pos = rs.max_pos; a.part_acc = b->att_acc; a.part_ml = b->att_ml; a.kv_only = kv_only;
     if (kv_only) {

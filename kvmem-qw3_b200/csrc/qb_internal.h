@@ -288,6 +288,7 @@ struct AttnArgs {
     uint32_t split_keys = 0;         // keys per split (set by qb_attn_run)
     int *err_flag = nullptr;         // an append to a page-table entry < 0 is skipped and recorded here (3002)
     bool ingest = false;             // rows of a prompt chunk: always the mma.sync shapes, whose rows do not depend on the chunking
+    bool prefer_tc = true;           // decode / verify rows on the tensor-memory kernel where it applies (a batch decides once, by its capacity)
 };
 // Decode / verify rows on tcgen05 (attention_tc.cu): same partials as attn_split_kernel, merged by the same kernel.
 bool qb_attn_tc_supports(const AttnArgs &a);

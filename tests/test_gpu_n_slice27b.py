@@ -134,3 +134,32 @@ def test_three_unequal_requests_in_one_batch(qb, orc, ctx, slice27):
     print("27B slice, 3 unequal requests: logit max-rel-err max %.3g mean %.3g (floor max %.3g mean %.3g)" % (
         max(errs), float(np.mean(errs)), max(floor), float(np.mean(floor))))
     assert max(errs) < noise_cap(floor, TOL) and float(np.mean(errs)) < 1.25 * max(TOL, float(np.mean(floor))), errs
+
+
+@pytest.mark.parametrize("min_keys", ["0", "100000000"], ids=["tensor-memory", "mma.sync"])
+def test_speculation_is_lossless_under_either_attention_kernel(qb, orc, ctx, slice27, monkeypatch, min_keys):
+    """A batch picks the attention kernel of its decode / verify rows once, from its capacity (QW3B200_ATTN_TC_MIN_KEYS,
+    read when the batch is created).  Under either choice the speculative stream must equal the greedy stream of a batch
+    created the same way, token for token: every row of one batch runs the same kernel."""
+    monkeypatch.setenv("QW3B200_ATTN_TC_MIN_KEYS", min_keys)
+    cfg, model = slice27["cfg"], slice27["model"]
+    prompt = orc.synth_prompt(qb.configs.PROMPT_SEED + 31, cfg.vocab_size, 280)
+    n_tok = 24
+    g = qb.Batch(model, 1, 512, 0)
+    g.prefill(0, prompt)
+    greedy = [g.read_output()[0][0]]
+    while len(greedy) < n_tok:
+        g.greedy_step()
+        greedy.append(g.read_output()[0][0])
+    g.close()
+    b = qb.Batch(model, 1, 512, 3, page_order=2)
+    b.prefill(0, prompt)
+    spec = [b.read_output()[0][0]]
+    steps = 0
+    while len(spec) < n_tok:
+        b.mtp_step()
+        spec += b.read_output()[0]
+        steps += 1
+    b.close()
+    print("attention %s: %d tokens in %d speculative steps" % ("tensor-memory" if min_keys == "0" else "mma.sync", len(spec), steps))
+    assert spec[:n_tok] == greedy
