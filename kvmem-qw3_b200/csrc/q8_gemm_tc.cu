@@ -37,6 +37,10 @@ struct TcCfg {
     // handshake chain of one CTA, not the memory system, limits a single chain to ~33 GB/s), so each CTA
     // takes half the tensor memory and half the shared memory.
     static constexpr int CTAS_PER_SM = MT == 16 ? 2 : 1;
+    // Second launch bound.  Left unspecified, the compiler keeps several variants at 64 registers with spills inside
+    // the drain loop (it assumes more resident CTAs than the shared memory allows); told the real residency it uses
+    // 94-168 registers and no spills.  The 32-column variant measured faster with the default, so it keeps it (0).
+    static constexpr int MIN_CTAS = MT == 32 ? 0 : CTAS_PER_SM;
     static constexpr int NSLOT = 512 / CTAS_PER_SM / (KPS * MT);
     static constexpr int TMEM_COLS = NSLOT * KPS * MT;
     static constexpr int B_OFF = (int)QB_REC_BYTES;            // 17 * 1024: the activation tile stays 1024-aligned
@@ -63,7 +67,7 @@ struct TcCfg {
 // Persistent kernel: CTA b works on units b, b + gridDim.x, ...; a unit is (activation tile, K segment,
 // 128-row weight tile).  The TMA / MMA / TMEM pipeline keeps running across unit boundaries.
 template <int MT, int NLD>
-__global__ void __launch_bounds__((TcCfg<MT, NLD>::THREADS))
+__global__ void __launch_bounds__((TcCfg<MT, NLD>::THREADS), (TcCfg<MT, NLD>::MIN_CTAS))
 gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensorMap map_xq,
                const __grid_constant__ CUtensorMap map_xd, uint32_t K, uint32_t N, uint32_t M, float *__restrict__ part,
                uint32_t S, uint32_t tiles, uint32_t units, int *err_flag, unsigned long long *tl,
@@ -257,14 +261,16 @@ gemm_tc_kernel(const uint8_t *__restrict__ rec, const __grid_constant__ CUtensor
 #pragma unroll
                 for (int i = 0; i < NC / 2; ++i) acc2[i] = pack2(0.0f, 0.0f);
                 for (uint32_t it = 0; it < n_it && ok; ++it, ++git) {
-                    const uint32_t st = git % NST, ph = (git / NST) & 1;
-                    // warp-uniform results: the TMEM loads below are .aligned
-                    if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * st, ph, abort_flag))) { ok = false; break; }
+                    // The stage's own barrier is not waited for: the MMAs whose completion the slot barrier reports were
+                    // issued after the stage had landed, and a wait that has nothing to wait for still costs this warp a
+                    // barrier round trip per stage (the drain is a chain of such latencies).
+                    const uint32_t st = git % NST;
                     const uint8_t *stage = smem + (size_t)st * C::STAGE;
                     const __half *wd = reinterpret_cast<const __half *>(stage + QB_REC_Q_BYTES);
                     const float *xd = reinterpret_cast<const float *>(stage + C::XD_OFF) + c_base;
                     for (int sp = 0; sp < C::SPS; ++sp, ++j) {
                         const uint32_t slot = j % NSLOT, sph = (j / NSLOT) & 1;
+                        // warp-uniform results: the TMEM loads below are .aligned
                         if (!__all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * slot, sph, abort_flag))) { ok = false; break; }
                         tc_fence_after();
                         const uint32_t tbase = tmem_base + ((quarter * 32u) << 16) + slot * (C::KPS * MT) + c_base;
