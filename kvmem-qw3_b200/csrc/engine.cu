@@ -466,7 +466,7 @@ static int batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_
     qb_batch *b = new qb_batch();
     b->m = m; b->n_seqs = n_seqs; b->n_active = n_seqs; b->max_ctx = max_ctx; b->k = draft_k; b->page_size = page_size;
     b->pages_per_seq = (max_ctx + draft_k + 1 + page_size - 1) / page_size;
-    b->chunk = std::max(1u, env_u32("QW3B200_PREFILL_CHUNK", 128));
+    b->chunk = std::max(1u, env_u32("QW3B200_PREFILL_CHUNK", 512));
     // The tensor-memory attention kernel wins once a call has enough keys to fill the GPU (one long context, or many
     // sequences) and costs a few microseconds per call below that; the two kernels differ in the last bits, so the choice
     // is a property of the batch (the keys it can hold), the same for every row the batch ever computes.
