@@ -23,6 +23,7 @@ Other workloads, one GPU, for profiling (each prints its own lines):
     --workload attn      paged gated attention alone at --ctx (comma list), cold L2
     --workload timeline  per-launch device timeline of the tensor-core GEMMs of one step
     --workload serve     the continuous-batching loops at the 27B shape, wall clock
+    --workload tokenizer the byte-level BPE tokenizer on the host (no GPU): MB/s beside the reference's own, where built
 """
 import argparse
 import json
@@ -55,7 +56,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="step", choices=["step", "gemm", "attn", "timeline", "serve"])
+    ap.add_argument("--workload", default="step", choices=["step", "gemm", "attn", "timeline", "serve", "tokenizer"])
     ap.add_argument("--sub", default="all", choices=["all", "none"], help="the short runs of configurations 3, 4, 5 / the TP FFN pair")
     ap.add_argument("--layers", type=int, default=64, help="target layers (64 = the 27B-class shape)")
     ap.add_argument("--prompt", type=int, default=PROMPT_LEN)
@@ -879,13 +880,66 @@ def workload_serve(args):
     model.close(); ctx.close()
 
 
+def workload_tokenizer(args):
+    """Host only.  A seeded chat-shaped text (about 2 MB) through the product's tokenizer and, as the CPU baseline, through
+    the reference's own (oracle/_ref/libqw3ref_tokenizer.so, where it has been built) on the same seeded vocabulary."""
+    import ctypes
+    import tempfile
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import gguf_synth as G              # the seeded vocabulary and its file writer (test infrastructure)
+    os.environ["LC_ALL"] = "C"
+    pkg = entry.load_package()
+    tokens, merges = G.synth_bpe_vocab(0x70C)
+    bos = tokens.index(b"<|endoftext|>")
+    words = G.synth_corpus(11, 40000)
+    rs = np.random.RandomState(12)
+    msgs, at = [], 0
+    while at < len(words):
+        n = int(rs.randint(20, 400))
+        body = " ".join(words[at:at + n])
+        msgs.append("<|im_start|>%s\n%s<|im_end|>\n" % ("user" if len(msgs) % 2 == 0 else "assistant", body))
+        at += n
+    text = ("".join(msgs) * 8).encode("utf-8")
+    tok = pkg.binding.Tokenizer.from_tables(tokens, merges, bos, bos, False)
+
+    def best(fn, reps=3):
+        out, t = None, float("inf")
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            out = fn()
+            t = min(t, time.perf_counter() - t0)
+        return out, t
+
+    ids, t_enc = best(lambda: tok.encode(text))
+    dec, t_dec = best(lambda: tok.decode(ids))
+    rec = {"workload": "tokenizer: seeded chat-shaped text, %d-entry byte-level BPE vocabulary, one host thread" % len(tokens), "text_MB": round(len(text) / 1e6, 2),
+           "tokens": int(ids.size), "encode_MB_per_s": round(len(text) / 1e6 / t_enc, 2), "encode_tok_per_s": round(ids.size / t_enc),
+           "decode_MB_per_s": round(len(text) / 1e6 / t_dec, 1), "round_trip_exact": dec == text, "cpu_baseline": None}
+    ref = os.path.join(ROOT, "oracle", "_ref", "libqw3ref_tokenizer.so")
+    if os.path.exists(ref):
+        L = ctypes.CDLL(ref)
+        L.rt_open.restype = ctypes.c_void_p
+        L.rt_open.argtypes = [ctypes.c_char_p]
+        L.rt_encode.restype = ctypes.c_int64
+        L.rt_encode.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_uint64, ctypes.c_int, ctypes.c_void_p, ctypes.c_uint64]
+        with tempfile.TemporaryDirectory() as d:
+            h = L.rt_open(G.write_tokenizer_gguf(os.path.join(d, "tok.gguf"), tokens, merges, bos, bos, False).encode())
+            out = np.zeros(len(text) + 8, np.int32)
+            n, t_ref = best(lambda: L.rt_encode(h, text, len(text), 0, out.ctypes.data, out.size), reps=2)
+        rec["cpu_baseline"] = {"kind": "reference", "what": "qw3::QwenTokenizer::encode on the same text and vocabulary (it uses up to all host threads above 512 KiB)",
+                               "encode_MB_per_s": round(len(text) / 1e6 / t_ref, 2), "same_ids": bool(n == ids.size and np.array_equal(out[:n], ids))}
+    print(json.dumps(rec), flush=True)
+    tok.close()
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.workload != "step":
-        return {"gemm": workload_gemm, "attn": workload_attn, "timeline": workload_timeline, "serve": workload_serve}[args.workload](args)
+        return {"gemm": workload_gemm, "attn": workload_attn, "timeline": workload_timeline, "serve": workload_serve,
+                "tokenizer": workload_tokenizer}[args.workload](args)
     if args.impl == "reference":
         run_reference(args, rank)
         return

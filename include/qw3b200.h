@@ -307,6 +307,36 @@ const qb_model_config *qb_model_get_config(const qb_model *m);
 void qb_model_destroy(qb_ctx *ctx, qb_model *m);
 size_t qb_model_weight_bytes(const qb_model *m);
 
+/* ---- tokenizer (host only; no device) ----------------------------------------------------------------------------
+ * qw3::QwenTokenizer (include/qw3/tokenizer.hpp:30-45, src/tokenizer.cpp): the byte-level BPE tokenizer of the
+ * checkpoint, built from tokenizer.ggml.tokens / tokenizer.ggml.merges and the bos / eos / add_bos hints
+ * (src/tokenizer.cpp:180-216).  The chat-template special tokens the vocabulary holds (<|im_start|>, <think>, ...,
+ * :327-358) are matched whole; the text between them is cut by the Qwen split pattern (:376-514) and merged piece by
+ * piece (:516-562).  Token ids are what qb_prefill takes. */
+typedef struct qb_tokenizer qb_tokenizer;
+/* QwenTokenizer(const GgufFile &) */
+int  qb_tokenizer_load_gguf(const char *path, qb_tokenizer **out);
+/* The same from the caller's own tables: n_tokens strings (id = index), n_merges lines "left right" (rank = index). */
+int  qb_tokenizer_create(const char *const *tokens, const uint32_t *token_lens, uint32_t n_tokens, const char *const *merges,
+                         const uint32_t *merge_lens, uint32_t n_merges, int32_t bos_id, int32_t eos_id, int add_bos,
+                         qb_tokenizer **out);
+void qb_tokenizer_destroy(qb_tokenizer *t);
+/* vocab_size(), bos_id(), eos_id(), add_bos_default() (tokenizer.hpp:40-43) and the number of special tokens found;
+ * any output may be NULL. */
+int  qb_tokenizer_info(const qb_tokenizer *t, int32_t *vocab_size, int32_t *bos_id, int32_t *eos_id, int *add_bos_default,
+                       uint32_t *n_special);
+/* token_id() (tokenizer.hpp:47-50): the id of a literal vocabulary string, -1 if absent. */
+int  qb_tokenizer_token_id(const qb_tokenizer *t, const char *token, uint32_t len);
+/* encode() (src/tokenizer.cpp:574-717): BOS first when add_bos or the checkpoint's default asks for it.  *n_out is
+ * the number of tokens even when cap is too small (the call then fails with the capacity error). */
+int  qb_tokenizer_encode(const qb_tokenizer *t, const char *text, size_t len, int add_bos, int32_t *ids, size_t cap, size_t *n_out);
+/* decode() (src/tokenizer.cpp:719-745): bytes, not necessarily whole UTF-8 sequences; ids outside the vocabulary are
+ * skipped. */
+int  qb_tokenizer_decode(const qb_tokenizer *t, const int32_t *ids, size_t n, char *text, size_t cap, size_t *len_out);
+/* detail::qwen_pre_tokenize (src/tokenizer_internal.hpp): the piece boundaries of a text without special tokens,
+ * piece_ends[i] = byte offset one past piece i. */
+int  qb_tokenizer_split(const char *text, size_t len, uint32_t *piece_ends, size_t cap, size_t *n_out);
+
 /* Per-request executor state of `n_seqs` sequences (QwenExecutor state, src/qwen_executor.hpp:763-819
  * KvPageTable; GlobalKvPagePool src/qwen_native_backend.cpp:1155-1265): paged fp16 K/V for the target
  * and the MTP layer, DeltaNet/conv state slots, positions.  page_order: 0 = identity, 1 = reverse,

@@ -97,6 +97,15 @@ SIGNATURES = {
     "qb_model_create": (i32, [vp, C.POINTER(ModelConfig), C.POINTER(TensorDesc), sz, C.POINTER(vp)]),
     "qb_model_load_gguf": (i32, [vp, C.c_char_p, C.POINTER(vp), C.POINTER(ModelConfig)]),
     "qb_gguf_read_config": (i32, [C.c_char_p, C.POINTER(ModelConfig), C.POINTER(u64), C.POINTER(u64)]),
+    "qb_tokenizer_load_gguf": (i32, [C.c_char_p, C.POINTER(vp)]),
+    "qb_tokenizer_create": (i32, [C.POINTER(C.c_char_p), C.POINTER(u32), u32, C.POINTER(C.c_char_p), C.POINTER(u32), u32, C.c_int32, C.c_int32, i32,
+                                  C.POINTER(vp)]),
+    "qb_tokenizer_destroy": (None, [vp]),
+    "qb_tokenizer_info": (i32, [vp, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(i32), C.POINTER(u32)]),
+    "qb_tokenizer_token_id": (i32, [vp, C.c_char_p, u32]),
+    "qb_tokenizer_encode": (i32, [vp, C.c_char_p, sz, i32, vp, sz, C.POINTER(sz)]),
+    "qb_tokenizer_decode": (i32, [vp, vp, sz, vp, sz, C.POINTER(sz)]),
+    "qb_tokenizer_split": (i32, [C.c_char_p, sz, vp, sz, C.POINTER(sz)]),
     "qb_model_get_config": (C.POINTER(ModelConfig), [vp]),
     "qb_model_create_synth_tp": (i32, [vp, C.POINTER(ModelConfig), u64, u32, u32, C.POINTER(vp)]),
     "qb_batch_set_tp": (i32, [vp, vp, vp]),
@@ -429,6 +438,81 @@ def gguf_read_config(path):
     cfg, n, b = ModelConfig(), u64(), u64()
     check(lib().qb_gguf_read_config(os.fsencode(path), C.byref(cfg), C.byref(n), C.byref(b)))
     return cfg, n.value, b.value
+
+
+class Tokenizer:
+    """qb_tokenizer: the checkpoint's byte-level BPE tokenizer (host only).  Texts are bytes (str is encoded as UTF-8)."""
+
+    def __init__(self, handle):
+        self.h = handle
+        v, b, e, a, n = C.c_int32(), C.c_int32(), C.c_int32(), C.c_int(), u32()
+        check(lib().qb_tokenizer_info(self.h, C.byref(v), C.byref(b), C.byref(e), C.byref(a), C.byref(n)))
+        self.vocab_size, self.bos_id, self.eos_id, self.add_bos_default, self.n_special = v.value, b.value, e.value, bool(a.value), n.value
+
+    @classmethod
+    def from_gguf(cls, path):
+        h = vp()
+        check(lib().qb_tokenizer_load_gguf(os.fsencode(path), C.byref(h)))
+        return cls(h)
+
+    @classmethod
+    def from_tables(cls, tokens, merges, bos_id=0, eos_id=0, add_bos=False):
+        """tokens / merges: sequences of bytes (id = index, rank = index; a merge line is b"left right")."""
+        def table(items):
+            arr = (C.c_char_p * max(1, len(items)))(*items)
+            lens = (u32 * max(1, len(items)))(*[len(x) for x in items])
+            return arr, lens
+        ta, tl = table(list(tokens))
+        ma, ml = table(list(merges))
+        h = vp()
+        check(lib().qb_tokenizer_create(ta, tl, len(tokens), ma, ml, len(merges), bos_id, eos_id, int(add_bos), C.byref(h)))
+        return cls(h)
+
+    @staticmethod
+    def _bytes(text):
+        return text.encode("utf-8") if isinstance(text, str) else bytes(text)
+
+    def encode(self, text, add_bos=False):
+        raw = self._bytes(text)
+        out = np.empty(len(raw) + 1, np.int32)
+        n = sz()
+        check(lib().qb_tokenizer_encode(self.h, raw, len(raw), int(add_bos), _np_ptr(out), out.size, C.byref(n)))
+        return out[:n.value].copy()
+
+    def decode(self, ids):
+        ids = np.ascontiguousarray(ids, np.int32)
+        n = sz()
+        cap = 64
+        while True:
+            buf = C.create_string_buffer(cap)
+            st = lib().qb_tokenizer_decode(self.h, _np_ptr(ids), ids.size, buf, cap, C.byref(n))
+            if st == 0:
+                return buf.raw[:n.value]
+            if n.value <= cap:
+                check(st)
+            cap = n.value
+
+    def token_id(self, token):
+        raw = self._bytes(token)
+        return int(lib().qb_tokenizer_token_id(self.h, raw, len(raw)))
+
+    @staticmethod
+    def split(text):
+        """Pieces of a text without special tokens (the split pattern alone), as bytes."""
+        raw = Tokenizer._bytes(text)
+        ends = np.empty(len(raw) + 1, np.uint32)
+        n = sz()
+        check(lib().qb_tokenizer_split(raw, len(raw), _np_ptr(ends), ends.size, C.byref(n)))
+        out, b = [], 0
+        for e in ends[:n.value].tolist():
+            out.append(raw[b:e])
+            b = e
+        return out
+
+    def close(self):
+        if self.h:
+            lib().qb_tokenizer_destroy(self.h)
+            self.h = None
 
 
 def tensor_descs(tensors):

@@ -2,107 +2,16 @@
 // reference's QwenConfig reads (src/qwen_config.cpp:53-108), lists the tensors (src/gguf.cpp:216-278) and hands
 // them to qb_model_create.  Only the two tensor types the reference maps from a GGUF file are accepted
 // (F32 = 0, Q8_0 = 8; src/model_source.cpp:120-121).  Host code only.
-#include "qb_internal.h"
+#include "gguf_reader.h"
 
-#include <fcntl.h>
-#include <sys/mman.h>
-#include <sys/stat.h>
-#include <unistd.h>
-
-#include <string>
-#include <unordered_map>
-
-namespace {
-
-struct Reader {
-    const uint8_t *p; size_t n, at = 0; bool bad = false;
-    template <typename T> T get() {
-        T v{};
-        if (at + sizeof(T) > n) { bad = true; return v; }
-        memcpy(&v, p + at, sizeof(T));
-        at += sizeof(T);
-        return v;
-    }
-    std::string str() {
-        const uint64_t len = get<uint64_t>();
-        if (bad || len > n - at) { bad = true; return {}; }
-        std::string s((const char *)p + at, (size_t)len);
-        at += (size_t)len;
-        return s;
-    }
-    void skip(uint64_t bytes) { if (bytes > n - at) bad = true; else at += (size_t)bytes; }
-};
-
-// GGUF metadata value types
-enum : uint32_t { GT_U8, GT_I8, GT_U16, GT_I16, GT_U32, GT_I32, GT_F32, GT_BOOL, GT_STR, GT_ARR, GT_U64, GT_I64, GT_F64 };
-uint32_t scalar_bytes(uint32_t t) {
-    switch (t) {
-        case GT_U8: case GT_I8: case GT_BOOL: return 1;
-        case GT_U16: case GT_I16: return 2;
-        case GT_U32: case GT_I32: case GT_F32: return 4;
-        case GT_U64: case GT_I64: case GT_F64: return 8;
-        default: return 0;
-    }
-}
-struct Meta { double num = 0; std::string s; uint64_t array_len = 0; bool is_num = false, is_str = false, is_array = false; };
-
-bool read_value(Reader &r, uint32_t type, Meta &m) {
-    switch (type) {
-        case GT_U8: m.num = r.get<uint8_t>(); m.is_num = true; return true;
-        case GT_I8: m.num = r.get<int8_t>(); m.is_num = true; return true;
-        case GT_BOOL: m.num = r.get<uint8_t>() ? 1 : 0; m.is_num = true; return true;
-        case GT_U16: m.num = r.get<uint16_t>(); m.is_num = true; return true;
-        case GT_I16: m.num = r.get<int16_t>(); m.is_num = true; return true;
-        case GT_U32: m.num = r.get<uint32_t>(); m.is_num = true; return true;
-        case GT_I32: m.num = r.get<int32_t>(); m.is_num = true; return true;
-        case GT_F32: m.num = r.get<float>(); m.is_num = true; return true;
-        case GT_U64: m.num = (double)r.get<uint64_t>(); m.is_num = true; return true;
-        case GT_I64: m.num = (double)r.get<int64_t>(); m.is_num = true; return true;
-        case GT_F64: m.num = r.get<double>(); m.is_num = true; return true;
-        case GT_STR: m.s = r.str(); m.is_str = true; return true;
-        case GT_ARR: {
-            const uint32_t et = r.get<uint32_t>();
-            const uint64_t cnt = r.get<uint64_t>();
-            m.is_array = true; m.array_len = cnt;
-            if (et == GT_STR) { for (uint64_t i = 0; i < cnt && !r.bad; ++i) r.skip(r.get<uint64_t>()); return true; }
-            const uint32_t sb = scalar_bytes(et);
-            if (!sb) return false;                       // nested arrays are not used by this checkpoint format
-            r.skip(cnt * sb);
-            return true;
-        }
-        default: return false;
-    }
-}
-
-struct Mapping {
-    int fd = -1; void *base = MAP_FAILED; size_t size = 0;
-    ~Mapping() { if (base != MAP_FAILED) munmap(base, size); if (fd >= 0) close(fd); }
-};
-
-}  // namespace
+using namespace qbgguf;
 
 // Maps and parses the file: configuration, tensor descriptors (pointing into the mapping) and their names.
 static int parse_gguf(const char *path, Mapping &mp, qb_model_config &c, std::vector<std::string> &names, std::vector<qb_tensor_desc> &descs) {
-    mp.fd = open(path, O_RDONLY);
-    if (mp.fd < 0) return qb_fail(QB_ERR_INVALID, "gguf: cannot open %s: %s", path, strerror(errno));
-    struct stat st {};
-    if (fstat(mp.fd, &st) != 0 || st.st_size < 24) return qb_fail(QB_ERR_INVALID, "gguf: %s is not a readable GGUF file", path);
-    mp.size = (size_t)st.st_size;
-    mp.base = mmap(nullptr, mp.size, PROT_READ, MAP_PRIVATE, mp.fd, 0);
-    if (mp.base == MAP_FAILED) return qb_fail(QB_ERR_INVALID, "gguf: mmap of %s failed: %s", path, strerror(errno));
-    Reader r{(const uint8_t *)mp.base, mp.size};
-    if (r.get<uint32_t>() != 0x46554747u) return qb_fail(QB_ERR_INVALID, "gguf: %s has no GGUF magic", path);
-    const uint32_t version = r.get<uint32_t>();
-    if (version != 3) return qb_fail(QB_ERR_UNSUPPORTED, "gguf: version %u (only v3 is read, as in the reference)", version);
-    const uint64_t n_tensors = r.get<uint64_t>(), n_meta = r.get<uint64_t>();
+    Reader r;
+    uint64_t n_tensors = 0;
     std::unordered_map<std::string, Meta> meta;
-    for (uint64_t i = 0; i < n_meta; ++i) {
-        std::string key = r.str();
-        const uint32_t type = r.get<uint32_t>();
-        Meta m;
-        if (r.bad || !read_value(r, type, m) || r.bad) return qb_fail(QB_ERR_INVALID, "gguf: bad metadata entry %llu (%s)", (unsigned long long)i, key.c_str());
-        meta.emplace(std::move(key), std::move(m));
-    }
+    QB_TRY(open_and_read_meta(path, mp, r, n_tensors, meta, nullptr));
     struct TInfo { std::string name; uint32_t type; uint64_t rows, cols, elements, rel; };
     std::vector<TInfo> infos((size_t)n_tensors);
     for (TInfo &t : infos) {
