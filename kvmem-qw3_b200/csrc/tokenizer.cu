@@ -316,6 +316,7 @@ extern "C" int qb_tokenizer_token_id(const qb_tokenizer *t, const char *token, u
 
 extern "C" int qb_tokenizer_encode(const qb_tokenizer *t, const char *text, size_t len, int add_bos, int32_t *ids, size_t cap, size_t *n_out) {
     QB_REQUIRE(t && (text || len == 0) && n_out && (ids || cap == 0), "qb_tokenizer_encode: bad arguments");
+    QB_REQUIRE(len < 0xFFFFFFFFull, "qb_tokenizer_encode: texts of 4 GiB and more are not taken in one call");
     std::vector<int32_t> out;
     out.reserve(len / 3 + 4);
     if ((add_bos || t->add_bos) && t->bos < (int32_t)t->tokens.size()) out.push_back(t->bos);
