@@ -168,10 +168,13 @@ def _kv(key, typ, payload):
     return _s(key) + struct.pack("<I", typ) + payload
 
 
-def write_gguf(path, cfg, tensors, context_length=4096, eos_id=None):
-    """GGUF v3, alignment 32, metadata of a qwen35 checkpoint, tensors in dict order."""
+def write_gguf(path, cfg, tensors, context_length=4096, eos_id=None, tokens=None, merges=None):
+    """GGUF v3, alignment 32, metadata of a qwen35 checkpoint, tensors in dict order.  tokens / merges: the tokenizer's
+    tables (bytes; default: the fixed-width synthetic token strings and no merges); a shorter token table is filled up
+    to the vocabulary size with unused names."""
     c, p = cfg, "qwen35."
-    toks = token_strings(c.vocab_size)
+    toks = token_strings(c.vocab_size) if tokens is None else list(tokens) + [b"<unused%d>" % i for i in range(len(tokens), c.vocab_size)]
+    assert len(toks) == c.vocab_size
     u32 = lambda k, v: _kv(k, T_U32, struct.pack("<I", int(v)))
     f32 = lambda k, v: _kv(k, T_F32, struct.pack("<f", float(v)))
     strs = lambda k, a: _kv(k, T_ARR, struct.pack("<IQ", T_STR, len(a)) + b"".join(_s(x) for x in a))
@@ -189,7 +192,7 @@ def write_gguf(path, cfg, tensors, context_length=4096, eos_id=None):
         u32(p + "ssm.inner_size", (2 * c.ssm_num_k_heads + c.ssm_num_v_heads) * c.ssm_head_dim),
         u32(p + "full_attention_interval", c.full_attention_interval),
         _kv("tokenizer.ggml.model", T_STR, _s("gpt2")),
-        strs("tokenizer.ggml.tokens", toks), strs("tokenizer.ggml.merges", []),
+        strs("tokenizer.ggml.tokens", toks), strs("tokenizer.ggml.merges", [] if merges is None else list(merges)),
         u32("tokenizer.ggml.bos_token_id", 0), u32("tokenizer.ggml.eos_token_id", c.vocab_size - 1 if eos_id is None else eos_id),
         _kv("tokenizer.ggml.add_bos_token", T_BOOL, struct.pack("<B", 0)),
     ]

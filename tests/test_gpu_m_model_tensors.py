@@ -93,6 +93,29 @@ def test_model_with_gains_matches_oracle_and_gguf_path(qb, orc, ctx, G, tmp_path
     model.close(); fm.close()
 
 
+def test_one_checkpoint_file_feeds_tokenizer_and_model(qb, orc, ctx, G, tmp_path):
+    """Text in, text out through one GGUF file: its token and merge tables build the tokenizer, its tensors the model; the
+    stream of the text's ids equals the stream of the same ids on the model built from the tensors in memory."""
+    cfg, ocfg = qb.configs.tiny(), tiny_ocfg(orc, qb)
+    t = G.seeded_model_tensors(ocfg, 0xF11E, gain_sigma=0.1)
+    tokens, merges = G.synth_bpe_vocab(0x70C)
+    assert len(tokens) <= cfg.vocab_size
+    eos = tokens.index(b"<|im_end|>")
+    path = G.write_gguf(str(tmp_path / "chat.gguf"), ocfg, t, eos_id=eos, tokens=tokens, merges=merges)
+    tok = qb.binding.Tokenizer.from_gguf(path)
+    assert tok.vocab_size == cfg.vocab_size and tok.eos_id == eos
+    text = "<|im_start|>user\nthe rate is 42 percent, isn't it?<|im_end|>\n<|im_start|>assistant\n"
+    ids = tok.encode(text)
+    assert ids.size < len(text) and int(ids.max()) < len(tokens) and ids[0] == tokens.index(b"<|im_start|>")
+    assert tok.decode(ids) == text.encode()
+    fm, mm = qb.Model.from_gguf(ctx, path), qb.Model.from_tensors(ctx, cfg, t)
+    a, b = run_stream(qb, fm, ids.tolist(), 3, 4), run_stream(qb, mm, ids.tolist(), 3, 4)
+    assert a[2] == b[2] and a[1] == b[1]
+    out = tok.decode(np.array(a[2], np.int32))                # tokens beyond the tables decode to their placeholder names
+    assert isinstance(out, bytes) and len(out) > 0
+    fm.close(); mm.close(); tok.close()
+
+
 def test_own_mtp_tables_and_tied_output(qb, orc, ctx, G):
     """nextn.embed_tokens / nextn.shared_head_head of their own, and a checkpoint without output.weight (LM head =
     token_embd): drafts and tokens equal the oracle's from the same tensors."""
