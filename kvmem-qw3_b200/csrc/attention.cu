@@ -530,10 +530,10 @@ static uint32_t split_keys() {
     }();
     return v;
 }
-static uint32_t max_splits_for(uint32_t max_pos) { return max_pos / split_keys() + 1; }
+static uint32_t max_splits_for(uint32_t max_pos, uint32_t split) { return max_pos / split + 1; }
 
-size_t qb_attention_scratch_floats(uint32_t rows, uint32_t n_heads, uint32_t hd, uint32_t max_pos, size_t *ml_floats) {
-    const size_t ms = max_splits_for(max_pos);
+size_t qb_attention_scratch_floats(uint32_t rows, uint32_t n_heads, uint32_t hd, uint32_t max_pos, size_t *ml_floats, uint32_t split) {
+    const size_t ms = max_splits_for(max_pos, split ? split : split_keys());
     if (ml_floats) *ml_floats = (size_t)rows * n_heads * ms * 2;
     return (size_t)rows * n_heads * ms * hd;
 }
@@ -556,9 +556,9 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
     const uint32_t R = a.rows / n_seqs;
     const uint32_t G = a.n_heads / a.n_kv;
     QB_REQUIRE(G * a.n_kv == a.n_heads && G <= 8, "attention: GQA group %u unsupported (<= 8)", G);
-    const uint32_t ms = max_splits_for(a.max_pos);
     AttnArgs aa = a;
-    aa.split_keys = split_keys();
+    if (aa.split_keys == 0) aa.split_keys = split_keys();       // a batch names its own (a multiple of 64); the op-level calls take the default
+    const uint32_t ms = max_splits_for(a.max_pos, aa.split_keys);
     QB_REQUIRE(aa.split_keys / a.page_size <= QB_ATTN_RUN_PAGES, "attention: a split of %u keys spans more than %u pages of %u", aa.split_keys, QB_ATTN_RUN_PAGES, a.page_size);
     QB_REQUIRE(((uintptr_t)a.qkv & 7) == 0 && a.row_stride % 2 == 0, "attention: q rows must be 8-byte aligned");
     int st = QB_OK;

@@ -383,6 +383,7 @@ struct qb_batch {
     qb_model *m = nullptr;
     uint32_t n_seqs = 0, max_ctx = 0, k = 0, page_size = 0, pages_per_seq = 0, rows_cap = 0, chunk = 0, logit_rows = 0;
     bool attn_tc = false;                  // decode / verify attention on the tensor-memory kernel: decided once, from n_seqs * max_ctx
+    uint32_t attn_split = 0;               // keys per attention split of this batch (absolute boundaries): decided once with attn_tc
     uint32_t n_active = 0;                 // the decode steps run sequences [0, n_active); the rest keep their state untouched
     std::vector<__half *> kc, vc;          // per layer (attention layers only), + MTP layer at index n_layers
     std::vector<float *> state, conv;      // per layer (recurrent layers only): [n_seqs][k+1][...]
@@ -471,6 +472,13 @@ static int batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_
     // sequences) and costs a few microseconds per call below that; the two kernels differ in the last bits, so the choice
     // is a property of the batch (the keys it can hold), the same for every row the batch ever computes.
     b->attn_tc = (uint64_t)n_seqs * max_ctx >= env_u32("QW3B200_ATTN_TC_MIN_KEYS", 16384);
+    // Splits of 256 keys where the tensor-memory kernel runs (its tile pair); 128 keys otherwise: a short context then
+    // spreads over twice the SMs, each streaming half the K/V bytes (7.87 against 8.01 ms per step at 2 K context).
+    {
+        const bool tc_shape = (c.head_dim == 256 || c.head_dim == 128) && page_size == 16 && c.n_heads / std::max(1u, c.n_kv_heads) <= 8;
+        b->attn_split = b->attn_tc && tc_shape ? 256 : env_u32("QW3B200_ATTN_SPLIT_SMALL", 128);
+        if (b->attn_split < 64 || b->attn_split % 64) b->attn_split = 128;
+    }
     b->logit_rows = n_seqs * (draft_k + 1);
     b->rows_cap = std::max(b->chunk, b->logit_rows);
     b->gemm_impl = (int)env_u32("QW3B200_GEMM_IMPL", 0);
@@ -569,7 +577,7 @@ static int batch_create(qb_ctx *ctx, qb_model *m, uint32_t n_seqs, uint32_t max_
     }
     {
         size_t ml = 0;
-        const size_t acc = qb_attention_scratch_floats(rows, c.n_heads, c.head_dim, max_ctx + draft_k + 1, &ml);
+        const size_t acc = qb_attention_scratch_floats(rows, c.n_heads, c.head_dim, max_ctx + draft_k + 1, &ml, b->attn_split);
         QB_CUDA(cudaMalloc(&b->att_acc, acc * sizeof(float)));
         QB_CUDA(cudaMalloc(&b->att_ml, ml * sizeof(float)));
     }
@@ -889,6 +897,7 @@ static int attention_block(qb_ctx *ctx, qb_batch *b, const LayerW &L, uint32_t c
     a.err_flag = ctx->err_flag_dev;
     a.ingest = rs.ingest;
     a.prefer_tc = b->attn_tc;
+    a.split_keys = b->attn_split;
     a.k_cache = b->kc[cache_idx]; a.v_cache = b->vc[cache_idx];
     a.max_pos = rs.max_pos; a.part_acc = b->att_acc; a.part_ml = b->att_ml; a.kv_only = kv_only;
     if (kv_only) {

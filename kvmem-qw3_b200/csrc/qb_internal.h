@@ -285,7 +285,7 @@ struct AttnArgs {
     float *part_acc = nullptr, *part_ml = nullptr;   // split partials
     bool kv_only = false;            // prepare: skip the q heads
     bool no_gate = false;            // merge: leave the output ungated (attention_decode + a separate apply_attn_gate)
-    uint32_t split_keys = 0;         // keys per split (set by qb_attn_run)
+    uint32_t split_keys = 0;         // keys per split: 0 = the library default (256, QW3B200_ATTN_SPLIT); a batch sets its own
     int *err_flag = nullptr;         // an append to a page-table entry < 0 is skipped and recorded here (3002)
     bool ingest = false;             // rows of a prompt chunk: always the mma.sync shapes, whose rows do not depend on the chunking
     bool prefer_tc = true;           // decode / verify rows on the tensor-memory kernel where it applies (a batch decides once, by its capacity)
@@ -298,7 +298,7 @@ int qb_attn_prepare(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint
 int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t n_seqs, float *out, int8_t *q8,
                 uint32_t q_pitch, float *d, uint32_t d_ld);
 size_t qb_attention_scratch_floats(uint32_t rows, uint32_t n_heads, uint32_t hd, uint32_t max_pos,
-                                   size_t *ml_floats);
+                                   size_t *ml_floats, uint32_t split = 0);
 static const uint32_t QB_ATTN_SPLIT = 256;   // keys per split (four 64-key tiles), fixed absolute boundaries
 
 struct DnArgs {
