@@ -209,6 +209,55 @@ __global__ void __launch_bounds__(512, MINB) dn_fused_kernel(DnArgs a) {
             float kr[RPL], qr[RPL];
 #pragma unroll
             for (int r = 0; r < RPL; ++r) { qr[r] = xs[t][r * 32 + lane]; kr[r] = xs[t][HD + r * 32 + lane]; }
+            if constexpr (CPW == 4 && RB > 4) {
+                // Ingestion form: the four columns' 32-lane sums share their shuffles.  Each exchange step halves the
+                // values a lane carries (lanes 16+ keep columns 2 and 3, then lanes with bit 3 the odd one), so a
+                // lane ends with the total of one column; every partial sum is the same pair added in the same
+                // step as in the plain butterfly, hence the same bits.  The totals come back with four broadcasts.
+                const bool hi16 = (lane & 16) != 0, hi8 = (lane & 8) != 0;
+                auto sum4 = [&](const float (&v)[4]) -> float {
+                    float k0 = hi16 ? v[2] : v[0], k1 = hi16 ? v[3] : v[1];
+                    const float s0 = hi16 ? v[0] : v[2], s1 = hi16 ? v[1] : v[3];
+                    k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+                    k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+                    float k = hi8 ? k1 : k0;
+                    const float sd = hi8 ? k0 : k1;
+                    k += __shfl_xor_sync(0xffffffffu, sd, 8);
+                    k += __shfl_xor_sync(0xffffffffu, k, 4);
+                    k += __shfl_xor_sync(0xffffffffu, k, 2);
+                    k += __shfl_xor_sync(0xffffffffu, k, 1);
+                    return k;                                  // total of column 2 * hi16 + hi8
+                };
+                float kvp[4];
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    float kv = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < RPL; ++r) kv += s[cc][r] * kr[r];
+                    kvp[cc] = kv;
+                }
+                const float kvt = sum4(kvp);
+                float atp[4];
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    const float kv = __shfl_sync(0xffffffffu, kvt, 8 * (cc & 1) + 16 * (cc >> 1));
+                    const float delta = (xs[t][2 * HD + warp * CPW + cc] - g * kv) * beta;
+                    float at = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < RPL; ++r) {
+                        s[cc][r] = g * s[cc][r] + kr[r] * delta;
+                        at += s[cc][r] * qr[r];
+                    }
+                    atp[cc] = at;
+                    if (a.write_all && rb0 + t < a.n_slots) {
+#pragma unroll
+                        for (int r = 0; r < RPL; ++r)
+                            state_seq[(size_t)(rb0 + t) * ssz + ((size_t)vh * HD + col0 + cc) * HD + r * 32 + lane] = s[cc][r];
+                    }
+                }
+                const float att = sum4(atp);
+                if ((lane & 7) == 0) core_s[t][warp * CPW + 2 * (lane >> 4) + ((lane >> 3) & 1)] = att * oscale;
+            } else {
 #pragma unroll
             for (int cc = 0; cc < CPW; ++cc) {
                 float kv = 0.0f;
@@ -229,6 +278,7 @@ __global__ void __launch_bounds__(512, MINB) dn_fused_kernel(DnArgs a) {
                     for (int r = 0; r < RPL; ++r)
                         state_seq[(size_t)(rb0 + t) * ssz + ((size_t)vh * HD + col0 + cc) * HD + r * 32 + lane] = s[cc][r];
                 }
+            }
             }
         }
         __syncthreads();
