@@ -209,8 +209,8 @@ __global__ void __launch_bounds__(512, MINB) dn_fused_kernel(DnArgs a) {
             float kr[RPL], qr[RPL];
 #pragma unroll
             for (int r = 0; r < RPL; ++r) { qr[r] = xs[t][r * 32 + lane]; kr[r] = xs[t][HD + r * 32 + lane]; }
-            if constexpr (CPW == 4 && RB > 4) {
-                // Ingestion form: the four columns' 32-lane sums share their shuffles.  Each exchange step halves the
+            if constexpr (CPW == 4) {
+                // Four columns per warp: their 32-lane sums share their shuffles.  Each exchange step halves the
                 // values a lane carries (lanes 16+ keep columns 2 and 3, then lanes with bit 3 the odd one), so a
                 // lane ends with the total of one column; every partial sum is the same pair added in the same
                 // step as in the plain butterfly, hence the same bits.  The totals come back with four broadcasts.
@@ -257,6 +257,47 @@ __global__ void __launch_bounds__(512, MINB) dn_fused_kernel(DnArgs a) {
                 }
                 const float att = sum4(atp);
                 if ((lane & 7) == 0) core_s[t][warp * CPW + 2 * (lane >> 4) + ((lane >> 3) & 1)] = att * oscale;
+            } else if constexpr (CPW == 2) {
+                // two columns per warp: the same sharing, one halving step
+                const bool hi16 = (lane & 16) != 0;
+                auto sum2 = [&](float v0, float v1) -> float {
+                    float k = hi16 ? v1 : v0;
+                    const float sd = hi16 ? v0 : v1;
+                    k += __shfl_xor_sync(0xffffffffu, sd, 16);
+                    k += __shfl_xor_sync(0xffffffffu, k, 8);
+                    k += __shfl_xor_sync(0xffffffffu, k, 4);
+                    k += __shfl_xor_sync(0xffffffffu, k, 2);
+                    k += __shfl_xor_sync(0xffffffffu, k, 1);
+                    return k;                                  // total of column hi16
+                };
+                float kvp[2], atp[2];
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    float kv = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < RPL; ++r) kv += s[cc][r] * kr[r];
+                    kvp[cc] = kv;
+                }
+                const float kvt = sum2(kvp[0], kvp[1]);
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    const float kv = __shfl_sync(0xffffffffu, kvt, 16 * cc);
+                    const float delta = (xs[t][2 * HD + warp * CPW + cc] - g * kv) * beta;
+                    float at = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < RPL; ++r) {
+                        s[cc][r] = g * s[cc][r] + kr[r] * delta;
+                        at += s[cc][r] * qr[r];
+                    }
+                    atp[cc] = at;
+                    if (a.write_all && rb0 + t < a.n_slots) {
+#pragma unroll
+                        for (int r = 0; r < RPL; ++r)
+                            state_seq[(size_t)(rb0 + t) * ssz + ((size_t)vh * HD + col0 + cc) * HD + r * 32 + lane] = s[cc][r];
+                    }
+                }
+                const float att = sum2(atp[0], atp[1]);
+                if ((lane & 15) == 0) core_s[t][warp * CPW + (lane >> 4)] = att * oscale;
             } else {
 #pragma unroll
             for (int cc = 0; cc < CPW; ++cc) {
