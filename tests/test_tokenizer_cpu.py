@@ -89,6 +89,26 @@ def test_file_and_tables_build_the_same_tokenizer(qb, tok, vocab, tmp_path):
         qb.binding.Tokenizer.from_gguf(bad)
 
 
+def test_damaged_files_are_refused(qb, vocab, tmp_path):
+    tokens, merges, bos, eos = vocab
+    good = G.write_tokenizer_gguf(str(tmp_path / "tok.gguf"), tokens, merges, bos, eos, False)
+    raw = open(good, "rb").read()
+    for cut in (0, 3, 20, 24, 200, len(raw) // 2, len(raw) - 40):      # truncations inside the header, a key, a string array
+        bad = str(tmp_path / ("cut%d.gguf" % cut))
+        open(bad, "wb").write(raw[:cut])
+        with pytest.raises(qb.binding.QbError):
+            qb.binding.Tokenizer.from_gguf(bad)
+    huge = bytearray(raw)
+    at = raw.index(b"tokenizer.ggml.tokens") + len(b"tokenizer.ggml.tokens") + 4 + 4      # the array's element count
+    huge[at:at + 8] = (2 ** 62).to_bytes(8, "little")
+    bad = str(tmp_path / "count.gguf")
+    open(bad, "wb").write(bytes(huge))
+    with pytest.raises(qb.binding.QbError):
+        qb.binding.Tokenizer.from_gguf(bad)
+    with pytest.raises(qb.binding.QbError):
+        qb.binding.Tokenizer.from_gguf(str(tmp_path / "missing.gguf"))
+
+
 def test_capacity_is_reported_not_overrun(qb, tok):
     L = qb.lib()
     text = b"one two three four five"
