@@ -13,6 +13,7 @@ static int parse_gguf(const char *path, Mapping &mp, qb_model_config &c, std::ve
     std::unordered_map<std::string, Meta> meta;
     QB_TRY(open_and_read_meta(path, mp, r, n_tensors, meta, nullptr));
     struct TInfo { std::string name; uint32_t type; uint64_t rows, cols, elements, rel; };
+    if (n_tensors > (r.n - r.at) / 32) return qb_fail(QB_ERR_INVALID, "gguf: %s names more tensors than it has room for", path);   // a header takes 32 bytes at least
     std::vector<TInfo> infos((size_t)n_tensors);
     for (TInfo &t : infos) {
         t.name = r.str();

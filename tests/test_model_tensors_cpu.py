@@ -50,6 +50,9 @@ def test_gguf_parser_rejects_bad_files(qb, orc, G, tmp_path):
     bad.write_bytes(raw.replace(b"qwen35.ssm.group_count", b"qwen35.ssm.group_counx"))
     with pytest.raises(qb.QbError, match="ssm.group_count"):
         qb.binding.gguf_read_config(str(bad))
+    bad.write_bytes(raw[:8] + struct.pack("<Q", 2 ** 61) + raw[16:])          # an absurd tensor count
+    with pytest.raises(qb.QbError, match="more tensors"):
+        qb.binding.gguf_read_config(str(bad))
     with pytest.raises(qb.QbError, match="cannot open"):
         qb.binding.gguf_read_config(str(tmp_path / "missing.gguf"))
 
