@@ -885,13 +885,11 @@ def workload_tokenizer(args):
     the reference's own (oracle/_ref/libqw3ref_tokenizer.so, where it has been built) on the same seeded vocabulary."""
     import ctypes
     import tempfile
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import gguf_synth as G              # the seeded vocabulary and its file writer (test infrastructure)
     os.environ["LC_ALL"] = "C"
     pkg = entry.load_package()
-    tokens, merges = G.synth_bpe_vocab(0x70C)
+    tokens, merges = pkg.synth_vocab.synth_bpe_vocab(0x70C)
     bos = tokens.index(b"<|endoftext|>")
-    words = G.synth_corpus(11, 40000)
+    words = pkg.synth_vocab.synth_corpus(11, 40000)
     rs = np.random.RandomState(12)
     msgs, at = [], 0
     while at < len(words):
@@ -917,6 +915,9 @@ def workload_tokenizer(args):
            "decode_MB_per_s": round(len(text) / 1e6 / t_dec, 1), "round_trip_exact": dec == text, "cpu_baseline": None}
     ref = os.path.join(ROOT, "oracle", "_ref", "libqw3ref_tokenizer.so")
     if os.path.exists(ref):
+        # the CPU baseline leg: the reference's tokenizer reads the same tables from a file (writer: test infrastructure)
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import gguf_synth as G
         L = ctypes.CDLL(ref)
         L.rt_open.restype = ctypes.c_void_p
         L.rt_open.argtypes = [ctypes.c_char_p]
