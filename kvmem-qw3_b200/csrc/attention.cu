@@ -90,7 +90,8 @@ __global__ void qk_norm_rope_append_kernel(AttnArgs a, const int32_t *__restrict
 }
 
 // ---- split attention ---------------------------------------------------------------------------
-// One CTA = a run of splits (QB_ATTN_SPLIT keys = 4 tiles of 64 each) of one KV head for up to 16 * MT queries (query rows
+// One CTA = a run of splits (a.split_keys keys each: 256 = 4 tiles of 64 by default, 128 in batches that name it) of one KV
+// head for up to 16 * MT queries (query rows
 // x GQA group).  Tensor-core math on fp16 operands with fp32 accumulation (mma.sync m16n8k16; the kernel streams
 // the cache once and is bound by HBM, not by the tensor pipe): S = Q K^T with Q (scaled, fp16) as A fragments,
 // P = exp(S - m) written to shared memory as fp16, O += P V with V read through ldmatrix.trans.  Warp w = (h, j),

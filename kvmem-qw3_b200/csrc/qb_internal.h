@@ -299,7 +299,7 @@ int qb_attn_run(qb_ctx *ctx, const AttnArgs &a, const int32_t *seq_pos, uint32_t
                 uint32_t q_pitch, float *d, uint32_t d_ld);
 size_t qb_attention_scratch_floats(uint32_t rows, uint32_t n_heads, uint32_t hd, uint32_t max_pos,
                                    size_t *ml_floats, uint32_t split = 0);
-static const uint32_t QB_ATTN_SPLIT = 256;   // keys per split (four 64-key tiles), fixed absolute boundaries
+static const uint32_t QB_ATTN_SPLIT = 256;   // default keys per split (four 64-key tiles), fixed absolute boundaries; a batch may name 128
 
 struct DnArgs {
     const float *proj = nullptr; uint32_t proj_stride = 0;   // rows [qkv | z | alpha | beta]
